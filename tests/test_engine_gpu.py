@@ -1,0 +1,75 @@
+"""The engine against the plain implementation, in float32 and in bfloat16, under every way of
+cutting the work: whole prompts, a decoded tail, portions of changing size, and mixed batches with
+so few pages that they are used again."""
+import math
+import random
+
+import pytest
+import torch
+
+import tiny
+import traces
+from plain import qwen2_plain as P
+from replay_util import compare, first_bad, run_trace
+
+pytestmark = pytest.mark.gpu
+
+# Tolerances, absolute on logits of magnitude ~3: float32 differs from the plain implementation by the
+# order of sums only; bfloat16 is compared with the plain implementation rounding its activations to
+# bfloat16 at the same places, so what is left is the order of sums again, seen through bfloat16 steps.
+TOL = {"float32": 2e-4, "bfloat16": 6e-2}
+
+
+def make_requests(cfg, lengths, seed):
+    rng = random.Random(seed)
+    return {f"r{i}": [rng.randrange(cfg["vocab_size"]) for _ in range(n)] for i, n in enumerate(lengths)}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    return {name: tiny.make_model_dir(root, name) for name in tiny.CONFIGS}
+
+
+def expected_logits(model_dir, requests, dtype):
+    cfg, w = P.load(model_dir)
+    act = torch.bfloat16 if dtype == "bfloat16" else None
+    return {rid: P.forward(cfg, w, toks, act) for rid, toks in requests.items()}
+
+
+LENGTHS = {"A": [7, 13, 70, 45], "B": [1, 17, 40, 90], "C": [60, 5, 100, 33], "D": [50, 130, 9]}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("family", ["whole", "tail", "chunks", "mixed"])
+def test_cuts_match_plain(models, name, dtype, family):
+    from zedinfer_b200.engine.core import EngineCore
+    cfg, _ = tiny.CONFIGS[name]
+    requests = make_requests(cfg, LENGTHS[name] + ([64, 31, 77] if family == "mixed" else []), seed=11)
+    steps = {"whole": traces.whole, "tail": traces.tail_decode, "chunks": traces.chunks,
+             "mixed": traces.mixed}[family](requests)
+    page = {"A": 4, "B": 8, "C": 16, "D": 16}[name]
+    need = traces.max_live_tokens(steps, round_to=page)
+    core = EngineCore(models[name], dtype, page_size=page, num_pages=need // page, max_requests=4)
+    got = run_trace(core, steps)
+    exp = expected_logits(models[name], requests, dtype)
+    bad = first_bad(got, exp, requests, TOL[dtype])
+    worst, where = compare(got, exp, requests)
+    assert bad is None, f"first wrong position {bad}; worst {worst} at {where}"
+    assert core.cache.num_live == 0 and all(g.pool.num_used == 0 for g in core.cache.groups)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_float32_is_the_same_however_it_is_cut(models, name):
+    """In float32 every sum has one order, so the cuts agree to the last bit."""
+    from zedinfer_b200.engine.core import EngineCore
+    cfg, _ = tiny.CONFIGS[name]
+    requests = make_requests(cfg, [70, 45, 64, 31], seed=5)
+    outs = []
+    for fam in (traces.whole, traces.tail_decode, traces.chunks, traces.mixed):
+        core = EngineCore(models[name], "float32", page_size=8, num_pages=64, max_requests=4)
+        outs.append(run_trace(core, fam(requests)))
+    for other in outs[1:]:
+        for key, ref in outs[0].items():
+            assert torch.equal(ref, other[key]), f"{key} differs between cuts"

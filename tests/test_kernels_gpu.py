@@ -1,0 +1,271 @@
+"""Each CUDA kernel alone against a plain float32 formula, at sizes other than the engine's tiny models:
+widths and vocabularies that are no power of two, head sizes in steps of 16, odd group sizes, shuffled
+page tables, windows, and inputs built so that a single wrong key, page or row shows."""
+import math
+
+import pytest
+import torch
+
+from plain import qwen2_plain as P
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def rand(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(dev())
+
+
+@pytest.mark.parametrize("table_dtype,out_dtype", [("float32", "float32"), ("bfloat16", "float32"), ("bfloat16", "bfloat16")])
+def test_embedding(table_dtype, out_dtype):
+    from zedinfer_b200 import ops
+    table = rand(1003, 136, dtype=DT[table_dtype])
+    ids = torch.tensor([0, 1002, 17, 17, 500, 999, 3], dtype=torch.int32, device=dev())
+    out = torch.empty(7, 136, dtype=DT[out_dtype], device=dev())
+    ops.embedding(table, ids, out)
+    assert torch.equal(out.float(), table[ids.long()].to(DT[out_dtype]).float())
+
+
+@pytest.mark.parametrize("hidden", [48, 1000, 1536, 5120])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_rmsnorm_and_fused_add(hidden, dtype):
+    from zedinfer_b200 import ops
+    t = DT[dtype]
+    rows, eps = 9, 1e-5
+    res = rand(rows, hidden, scale=3.0)
+    delta = rand(rows, hidden, dtype=t, seed=1)
+    w = (1 + rand(hidden, scale=0.1, seed=2)).to(t)
+    out = torch.empty(rows, hidden, dtype=t, device=dev())
+    res2 = res.clone()
+    ops.add_rmsnorm(res2, delta, w, eps, out)
+    ref_res = res + delta.float()
+    ref = P.rms_norm(ref_res.cpu(), w.float().cpu(), eps)
+    assert torch.allclose(res2.cpu(), ref_res.cpu(), atol=0, rtol=0)
+    tol = 1e-5 if dtype == "float32" else 2e-2
+    assert torch.allclose(out.float().cpu(), ref, atol=tol, rtol=tol)
+    # rows picked by index, residual untouched
+    idx = torch.tensor([8, 0, 3], dtype=torch.int32, device=dev())
+    out3 = torch.empty(3, hidden, dtype=t, device=dev())
+    res3 = res.clone()
+    ops.add_rmsnorm(res3, delta, w, eps, out3, row_idx=idx, write_residual=False)
+    assert torch.equal(res3, res)
+    assert torch.allclose(out3.float().cpu(), ref[idx.long().cpu()], atol=tol, rtol=tol)
+    # plain norm
+    x = rand(rows, hidden, dtype=t, seed=4)
+    out4 = torch.empty_like(x)
+    ops.rmsnorm(x, w, eps, out4)
+    assert torch.allclose(out4.float().cpu(), P.rms_norm(x.float().cpu(), w.float().cpu(), eps), atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows,inter", [(5, 176), (3, 8960), (1, 7)])
+def test_silu_mul(dtype, rows, inter):
+    from zedinfer_b200 import ops
+    t = DT[dtype]
+    gu = rand(rows, 2 * inter, dtype=t, scale=3.0)
+    out = torch.empty(rows, inter, dtype=t, device=dev())
+    ops.silu_mul(gu, out)
+    ref = P.swiglu(gu[:, :inter].float().cpu(), gu[:, inter:].float().cpu())
+    tol = 1e-6 if dtype == "float32" else 2e-2
+    assert torch.allclose(out.float().cpu(), ref, atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1000, 96), (7, 130, 1536), (64, 257, 100), (130, 64, 33), (2, 5, 3)])
+@pytest.mark.parametrize("types", [("float32", "float32", "float32"), ("bfloat16", "bfloat16", "bfloat16"),
+                                   ("bfloat16", "float32", "bfloat16"), ("bfloat16", "bfloat16", "float32")])
+def test_gemm_simt(m, n, k, types):
+    from zedinfer_b200 import ops
+    ta, tw, tc = (DT[x] for x in types)
+    a, w, b = rand(m, k, dtype=ta), rand(n, k, dtype=tw, seed=1), rand(n, dtype=tw, seed=2)
+    out = torch.empty(m, n, dtype=tc, device=dev())
+    ops.gemm_nt(a, w, b, out)
+    ref = (a.double().cpu() @ w.double().cpu().t() + b.double().cpu()).float()
+    tol = 1e-4 if tc == torch.float32 else 0.1
+    assert torch.allclose(out.float().cpu(), ref, atol=tol, rtol=1e-2 if tc == torch.bfloat16 else 1e-5)
+    # a row's result does not depend on what else is in the batch
+    if m > 1:
+        out1 = torch.empty(1, n, dtype=tc, device=dev())
+        ops.gemm_nt(a[m - 1:m], w, b, out1)
+        assert torch.equal(out1[0], out[m - 1])
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1000, 96), (8, 2048, 1536), (64, 1536, 8960), (300, 130, 64)])
+def test_linear_bf16(m, n, k):
+    from zedinfer_b200 import ops
+    a, w, b = rand(m, k, dtype=torch.bfloat16), rand(n, k, dtype=torch.bfloat16, seed=1, scale=0.05), \
+        rand(n, dtype=torch.bfloat16, seed=2)
+    ref = (a.double().cpu() @ w.double().cpu().t() + b.double().cpu()).float()
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.empty(m, n, dtype=out_dtype, device=dev())
+        ops.linear(a, w, b, out)
+        assert torch.allclose(out.float().cpu(), ref, atol=0.05, rtol=2e-2)
+
+
+def build_cache(n_req, lens, nkv, hd, ps, dtype, seed=0, n_calls=2, call=1):
+    """A pool with shuffled pages holding random k, v for each request; returns what the kernels need."""
+    g = torch.Generator().manual_seed(seed)
+    blocks = [-(-l // ps) for l in lens]
+    total = sum(blocks) + 3
+    perm = torch.randperm(total, generator=g).tolist()
+    pool = torch.full((total + 1, n_calls, 2, nkv, ps, hd), 1000.0).to(dtype).to(dev())   # stale pages hold junk
+    width = max(blocks) + 1
+    tables = torch.full((n_req, width), -1, dtype=torch.int32)
+    ks, vs = [], []
+    it = iter(perm)
+    for r, l in enumerate(lens):
+        k = torch.randn(l, nkv, hd, generator=g)
+        v = torch.randn(l, nkv, hd, generator=g)
+        ks.append(k.to(dtype).float()), vs.append(v.to(dtype).float())
+        for b in range(blocks[r]):
+            page = next(it)
+            tables[r, b] = page
+            n = min(ps, l - b * ps)
+            pool[page, call, 0, :, :n] = k[b * ps:b * ps + n].transpose(0, 1).to(dtype).to(dev())
+            pool[page, call, 1, :, :n] = v[b * ps:b * ps + n].transpose(0, 1).to(dtype).to(dev())
+    view = pool[:, call]
+    return pool, view, tables.to(dev()), ks, vs, pool.stride(0), pool.stride(2)
+
+
+def plain_attention_rows(q, k, v, positions, scale, window):
+    """q [n, nh, hd] at the given positions of a sequence whose k, v are [L, nkv, hd]."""
+    out = torch.zeros_like(q)
+    nh, nkv = q.shape[1], k.shape[1]
+    for i, p in enumerate(positions):
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(nh):
+            kvh = h // (nh // nkv)
+            s = (k[lo:p + 1, kvh] @ q[i, h]) * scale
+            pr = torch.softmax(s, dim=0)
+            out[i, h] = pr @ v[lo:p + 1, kvh]
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(4, 2, 16, 4, None), (3, 1, 32, 8, None), (6, 3, 48, 16, 24),
+                                                  (12, 2, 128, 16, None), (7, 7, 64, 32, 100), (5, 1, 256, 16, None),
+                                                  (14, 2, 80, 16, None)])
+def test_paged_attention_generic(dtype, nh, nkv, hd, ps, window):
+    from zedinfer_b200 import ops
+    t = DT[dtype]
+    lens = [37, 300, 5]
+    pool, view, tables, ks, vs, page_stride, kv_stride = build_cache(3, lens, nkv, hd, ps, t)
+    # queries: the last 3 positions of request 0 (a chunk), one decode token of request 1, all of request 2
+    spec = [(0, [34, 35, 36]), (1, [299]), (2, [0, 1, 2, 3, 4])]
+    g = torch.Generator().manual_seed(3)
+    qs, seg, pos = [], [], []
+    for r, ps_list in spec:
+        for p in ps_list:
+            qs.append(torch.randn(nh, hd, generator=g))
+            seg.append(r), pos.append(p)
+    q = torch.stack(qs)
+    # one far key stands out: scale a key of request 1 and point the decode query at it
+    far = 2 if not window else 299 - window + 1
+    q[3, :, :] = ks[1][far, 0][None, :] * 3.0
+    qd = q.to(t).to(dev())
+    out = torch.empty(len(seg), nh * hd, dtype=t, device=dev())
+    scale = 1.0 / math.sqrt(hd)
+    ops.paged_attention(qd, view, out, tables, torch.tensor(seg, dtype=torch.int32, device=dev()),
+                        torch.tensor(pos, dtype=torch.int32, device=dev()), nh, nkv, hd, ps, page_stride, kv_stride,
+                        window, scale)
+    got = out.float().cpu().view(len(seg), nh, hd)
+    qf = qd.float().cpu()
+    i = 0
+    for r, ps_list in spec:
+        ref = plain_attention_rows(qf[i:i + len(ps_list)], ks[r], vs[r], ps_list, scale, window)
+        tol = 2e-5 if dtype == "float32" else 2e-2
+        assert torch.allclose(got[i:i + len(ps_list)], ref, atol=tol, rtol=tol), (r, float((got[i:i + len(ps_list)] - ref).abs().max()))
+        i += len(ps_list)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(4, 2, 16, 4), (12, 2, 128, 16), (3, 1, 48, 8)])
+def test_rope_append(dtype, nh, nkv, hd, ps):
+    from zedinfer_b200 import ops
+    t = DT[dtype]
+    theta = 10000.0
+    # two requests: one appends a chunk at positions 5..10, the other a single token at position 21
+    seg = [0] * 6 + [1]
+    pos = list(range(5, 11)) + [21]
+    n = len(seg)
+    pool = torch.zeros((9, 3, 2, nkv, ps, hd), dtype=t, device=dev())
+    tables = torch.tensor([[4, 7, 1, 0, 0, 0], [2, 8, 5, 3, 6, 0]][:2], dtype=torch.int32, device=dev())
+    qkv = rand(n, (nh + 2 * nkv) * hd + 8, dtype=t)[:, :(nh + 2 * nkv) * hd]      # rows with a stride
+    q_out = torch.empty(n, nh, hd, dtype=t, device=dev())
+    expo = torch.arange(0, hd, 2, dtype=torch.float32) / float(hd)
+    inv = (1.0 / torch.pow(torch.tensor(theta), expo)).to(dev())
+    call = 1
+    ops.rope_append(qkv, q_out, pool[:, call], tables, torch.tensor(seg, dtype=torch.int32, device=dev()),
+                    torch.tensor(pos, dtype=torch.int32, device=dev()), inv, nh, nkv, hd, ps, pool.stride(0),
+                    pool.stride(2))
+    x = qkv.float().cpu()
+    qr = P.rope(x[:, :nh * hd].reshape(n, nh, hd), torch.tensor(pos), theta)
+    kr = P.rope(x[:, nh * hd:(nh + nkv) * hd].reshape(n, nkv, hd), torch.tensor(pos), theta)
+    v = x[:, (nh + nkv) * hd:].reshape(n, nkv, hd)
+    tol = 1e-5 if dtype == "float32" else 2e-2
+    assert torch.allclose(q_out.float().cpu(), qr, atol=tol, rtol=tol)
+    tab = tables.cpu()
+    touched = torch.zeros(pool.shape, dtype=torch.bool)
+    for i in range(n):
+        page, off = int(tab[seg[i], pos[i] // ps]), pos[i] % ps
+        assert torch.allclose(pool[page, call, 0, :, off].float().cpu(), kr[i], atol=tol, rtol=tol)
+        assert torch.equal(pool[page, call, 1, :, off].float().cpu(), v[i].to(t).float())
+        touched[page, call, :, :, off] = True
+    assert float(pool.float().cpu()[~touched].abs().max()) == 0.0          # nothing else was written
+
+
+def test_argmax_ties_and_rows():
+    from zedinfer_b200 import ops
+    logits = torch.randn(5, 151937)
+    logits[1, 70000] = 50.0
+    logits[1, 90000] = 50.0         # tie: the lower index wins
+    logits[2, 0] = 60.0
+    logits[3, 151936] = 60.0
+    logits[4] = -1.0                # all equal
+    out = torch.empty(5, dtype=torch.int32, device=dev())
+    ops.argmax(logits.to(dev()), out)
+    exp = [P.greedy(logits[i]) for i in range(5)]
+    assert out.cpu().tolist() == exp
+    assert exp[1] == 70000 and exp[4] == 0
+
+
+@pytest.mark.parametrize("vocab", [777, 151936])
+def test_sample_matches_plain_distribution(vocab):
+    from zedinfer_b200 import ops
+    g = torch.Generator().manual_seed(1)
+    cases = [(0.7, 0, 1.0), (1.0, 5, 1.0), (1.3, 0, 0.6), (0.5, 20, 0.9), (0.0, 0, 1.0)]
+    rows = len(cases)
+    logits = torch.randn(rows, vocab, generator=g) * 3.0
+    temp = torch.tensor([c[0] for c in cases])
+    top_k = torch.tensor([c[1] for c in cases], dtype=torch.int32)
+    top_p = torch.tensor([c[2] for c in cases])
+    dl = logits.to(dev())
+    for u in (0.0, 0.123, 0.5, 0.77, 0.999):
+        uni = torch.full((rows,), u)
+        out = torch.empty(rows, dtype=torch.int32, device=dev())
+        ops.sample(dl, out, temp.to(dev()), top_k.to(dev()), top_p.to(dev()), uni.to(dev()))
+        got = out.cpu().tolist()
+        for r, (t, k, p) in enumerate(cases):
+            if t <= 0:
+                assert got[r] == P.greedy(logits[r])
+                continue
+            dist = P.sampling_distribution(logits[r], t, k, p)
+            assert dist[got[r]] > 0, f"row {r}: token {got[r]} is outside the kept set"
+            # the running sum just before and at the chosen token brackets u (up to rounding of the sums)
+            cum = torch.cumsum(dist.double(), 0)
+            lo = float(cum[got[r]] - dist[got[r]].double())
+            hi = float(cum[got[r]])
+            assert lo - 1e-4 <= u <= hi + 1e-4, (r, u, lo, hi)
+
+
+def test_repetition_penalty():
+    from zedinfer_b200 import ops
+    row = torch.tensor([2.0, -1.0, 0.5, 4.0, -3.0])
+    d = row.to(dev())
+    ops.repetition_penalty(d, torch.tensor([0, 1, 9, 3], dtype=torch.int32, device=dev()), 2.0)
+    assert torch.allclose(d.cpu(), torch.tensor([1.0, -2.0, 0.5, 2.0, -3.0]))

@@ -1,0 +1,90 @@
+"""Architecture-neutral description of a model: parts, layers, and the run order.
+
+A model is data: a tuple of :class:`LayerSpec` (which mixer, feed-forward, norms
+and arrangement a layer has, each with its own sizes and constants) and a
+*schedule*, the list of :class:`LayerCall` that says in which order layers run.
+The schedule may name a layer twice (its weights are then used twice, each call
+with a cache of its own) or let a call read the cache that an earlier call
+wrote.  Nothing in here knows about a particular architecture; the files under
+``zedinfer_b200/models`` translate an architecture's ``config.json`` into these
+objects.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Mapping, Optional, Tuple
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    """One part of a layer: a registered ``kind`` plus its constructor keywords."""
+
+    kind: str
+    params: Mapping[str, Any] = field(default_factory=dict)
+
+    def with_params(self, **kw: Any) -> "PartSpec":
+        merged = dict(self.params)
+        merged.update(kw)
+        return PartSpec(self.kind, merged)
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    """A layer: the arrangement (``block``) of a mixer, a feed-forward and norms.
+
+    ``prefixes`` maps the role of each part inside the block (``"mixer"``,
+    ``"ffn"``, ``"norm1"``, ``"norm2"``, ...) to the tensor-name prefix below the
+    layer's own prefix, e.g. ``{"mixer": "self_attn.", "norm1": "input_layernorm."}``.
+    """
+
+    block: str
+    mixer: PartSpec
+    ffn: PartSpec
+    norms: Mapping[str, PartSpec]
+    prefixes: Mapping[str, str]
+
+
+@dataclass(frozen=True)
+class LayerCall:
+    """One entry of the run order.
+
+    ``layer`` indexes :attr:`ModelSpec.layers`.  ``cache_of`` is ``None`` when the
+    call owns a cache of its own, else the index (into the schedule) of an earlier
+    call whose cache this call reads without writing to it.
+    """
+
+    layer: int
+    cache_of: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class ModelSpec:
+    architecture: str
+    vocab_size: int
+    hidden_size: int
+    layers: Tuple[LayerSpec, ...]
+    schedule: Tuple[LayerCall, ...]
+    final_norm: PartSpec
+    tie_word_embeddings: bool
+    max_position_embeddings: int
+    layer_prefix: str = "layers.{i}."
+    embed_name: str = "embed_tokens.weight"
+    final_norm_prefix: str = "norm."
+    head_name: str = "lm_head.weight"
+    bos_token_id: Optional[int] = None
+    eos_token_ids: Tuple[int, ...] = ()
+
+    def validate(self) -> None:
+        if self.vocab_size <= 0 or self.hidden_size <= 0:
+            raise ValueError("vocab_size and hidden_size must be positive")
+        if not self.layers:
+            raise ValueError("a model needs at least one layer")
+        for pos, call in enumerate(self.schedule):
+            if not 0 <= call.layer < len(self.layers):
+                raise ValueError(f"schedule[{pos}] names layer {call.layer}, "
+                                 f"but the model has {len(self.layers)} layers")
+            if call.cache_of is not None:
+                if not 0 <= call.cache_of < pos:
+                    raise ValueError(f"schedule[{pos}].cache_of={call.cache_of} must name an earlier call")
+                if self.schedule[call.cache_of].cache_of is not None:
+                    raise ValueError(f"schedule[{pos}].cache_of names a call that itself borrows a cache")

@@ -1,0 +1,252 @@
+// Row-wise and element-wise kernels: embedding gather, RMSNorm (plain, and fused with the
+// residual add), rotate-half RoPE fused with the append to the paged cache, SiLU-mul, cast.
+// All arithmetic is float32; storage types are float32 or bfloat16 per tensor.
+#include "zi_common.cuh"
+
+ZI_DEFINE_LAST_ERROR(elementwise)
+
+// ---------------------------------------------------------------------------------------
+// Embedding: out[n, :] = table[ids[n], :]
+// ---------------------------------------------------------------------------------------
+template <typename TT, typename TO>
+__global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
+                                 TO* __restrict__ out, int hidden, int vocab) {
+    const int n = blockIdx.x;
+    int id = ids[n];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);   // the host refuses ids outside the table
+    const TT* src = table + (size_t)id * hidden;
+    TO* dst = out + (size_t)n * hidden;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) dst[j] = from_f32<TO>(to_f32<TT>(src[j]));
+}
+
+ZI_EXPORT int zi_embedding(const void* table, int table_dtype, const int* ids, void* out, int out_dtype,
+                           int n_tokens, int hidden, int vocab, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (hidden <= 0 || vocab <= 0) return zi_fail("embedding: hidden=%d vocab=%d must be positive", hidden, vocab);
+    const int threads = hidden >= 1024 ? 256 : 128;
+    ZI_DISPATCH(table_dtype, TT, ZI_DISPATCH(out_dtype, TO, {
+        embedding_kernel<TT, TO><<<n_tokens, threads, 0, stream>>>((const TT*)table, ids, (TO*)out, hidden, vocab);
+    }););
+    return zi_check_launch("embedding");
+}
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm.  y = (w * x) * rstd, rstd = 1/sqrt(mean(x^2) + eps), all in float32.
+//   delta != null : x = residual[row] + delta[row] (float32 add); written back to residual
+//                   when write_residual is set.
+//   row_idx != null : output row r reads input row row_idx[r] (used for the rows whose
+//                   logits are wanted); the residual is then never written.
+// One block per output row, a fixed block size, so the sum's order is a function of the
+// width alone.
+// ---------------------------------------------------------------------------------------
+#define NORM_THREADS 256
+template <typename TD, typename TW, typename TO>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const TW* __restrict__ w,
+               TO* __restrict__ out, const int* __restrict__ row_idx, float eps, int hidden,
+               int write_residual) {
+    extern __shared__ float row[];           // hidden floats
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const size_t src = row_idx ? (size_t)row_idx[r] : (size_t)r;
+    float* res = residual + src * hidden;
+    const TD* d = delta ? delta + src * hidden : nullptr;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < hidden; j += NORM_THREADS) {
+        float x = res[j];
+        if (d) x = x + to_f32<TD>(d[j]);
+        row[j] = x;
+        ss = fmaf(x, x, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = 1.0f / sqrtf(ss / (float)hidden + eps);
+    const bool wb = d && write_residual && !row_idx;
+    TO* o = out + (size_t)r * hidden;
+    for (int j = threadIdx.x; j < hidden; j += NORM_THREADS) {
+        const float x = row[j];
+        if (wb) res[j] = x;
+        o[j] = from_f32<TO>((to_f32<TW>(w[j]) * x) * rstd);
+    }
+}
+
+// Plain norm of a tensor that is not the float32 residual (used by parts tested alone).
+template <typename TX, typename TW, typename TO>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_plain_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out, float eps,
+                     int hidden) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    const TX* xr = x + (size_t)blockIdx.x * hidden;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < hidden; j += NORM_THREADS) {
+        const float v = to_f32<TX>(xr[j]);
+        row[j] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = 1.0f / sqrtf(ss / (float)hidden + eps);
+    TO* o = out + (size_t)blockIdx.x * hidden;
+    for (int j = threadIdx.x; j < hidden; j += NORM_THREADS)
+        o[j] = from_f32<TO>((to_f32<TW>(w[j]) * row[j]) * rstd);
+}
+
+static int norm_smem_ok(int hidden, const void* fn) {
+    const size_t bytes = (size_t)hidden * sizeof(float);
+    if (bytes > 200 * 1024) return zi_fail("rmsnorm: width %d needs %zu bytes of shared memory (limit 200 KiB)", hidden, bytes);
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return zi_fail("rmsnorm: cannot reserve %zu bytes of shared memory: %s", bytes, cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+// residual: float32 [*, hidden] (in/out).  delta: nullable, [*, hidden] of delta_dtype.
+ZI_EXPORT int zi_add_rmsnorm(void* residual, const void* delta, int delta_dtype, const void* w, int w_dtype,
+                             void* out, int out_dtype, const int* row_idx, int rows, int hidden, float eps,
+                             int write_residual, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0) return zi_fail("rmsnorm: width %d must be positive", hidden);
+    const size_t smem = (size_t)hidden * sizeof(float);
+    ZI_DISPATCH(delta_dtype, TD, ZI_DISPATCH(w_dtype, TW, ZI_DISPATCH(out_dtype, TO, {
+        auto fn = rmsnorm_kernel<TD, TW, TO>;
+        if (norm_smem_ok(hidden, (const void*)fn)) return 1;
+        fn<<<rows, NORM_THREADS, smem, stream>>>((float*)residual, (const TD*)delta, (const TW*)w, (TO*)out,
+                                                 row_idx, eps, hidden, write_residual);
+    });););
+    return zi_check_launch("add_rmsnorm");
+}
+
+ZI_EXPORT int zi_rmsnorm(const void* x, int x_dtype, const void* w, int w_dtype, void* out, int out_dtype,
+                         int rows, int hidden, float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0) return zi_fail("rmsnorm: width %d must be positive", hidden);
+    const size_t smem = (size_t)hidden * sizeof(float);
+    ZI_DISPATCH(x_dtype, TX, ZI_DISPATCH(w_dtype, TW, ZI_DISPATCH(out_dtype, TO, {
+        auto fn = rmsnorm_plain_kernel<TX, TW, TO>;
+        if (norm_smem_ok(hidden, (const void*)fn)) return 1;
+        fn<<<rows, NORM_THREADS, smem, stream>>>((const TX*)x, (const TW*)w, (TO*)out, eps, hidden);
+    });););
+    return zi_check_launch("rmsnorm");
+}
+
+// ---------------------------------------------------------------------------------------
+// RoPE (rotate-half over the whole head) on q and k, fused with the append of k and v
+// to the paged cache.
+//   qkv      [n_tokens, row_stride]: q heads, then k heads, then v heads, head_dim each
+//   q_out    [n_tokens, n_heads, head_dim]
+//   cache    one call's slice of the pool: element (page, kv, kvh, off, d) is at
+//            cache + page*page_stride + kv*kv_stride + (kvh*page_size + off)*head_dim + d
+//   tables   [n_segments, max_blocks] page ids;  tok_seg[n] = segment of token n
+//   pos[n]   absolute position of token n;  inv_freq[head_dim/2] float32
+// angle = float(pos) * inv_freq[k]; y[k] = a*c - b*s; y[k+half] = b*c + a*s.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ cache,
+                                   const int* __restrict__ tables, const int* __restrict__ tok_seg,
+                                   const int* __restrict__ pos, const float* __restrict__ inv_freq,
+                                   int row_stride, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                   int max_blocks, long long page_stride, long long kv_stride, int write_kv) {
+    extern __shared__ float cs[];            // cos[half], sin[half]
+    const int n = blockIdx.x;
+    const int half = head_dim >> 1;
+    const int p = pos[n];
+    for (int k = threadIdx.x; k < half; k += blockDim.x) {
+        float s, c;
+        sincosf((float)p * inv_freq[k], &s, &c);
+        cs[k] = c;
+        cs[half + k] = s;
+    }
+    __syncthreads();
+    const T* row = qkv + (size_t)n * row_stride;
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (write_kv) {
+        const int seg = tok_seg[n];
+        const int page = tables[(size_t)seg * max_blocks + p / page_size];
+        const int off = p % page_size;
+        kdst = cache + (size_t)page * page_stride + (size_t)off * head_dim;
+        vdst = kdst + kv_stride;
+    }
+    const int rot_heads = n_heads + (write_kv ? n_kv_heads : 0);
+    for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
+        const int h = idx / half, k = idx - h * half;
+        const float a = to_f32<T>(row[h * head_dim + k]);
+        const float b = to_f32<T>(row[h * head_dim + k + half]);
+        const float c = cs[k], s = cs[half + k];
+        const float y0 = a * c - b * s;
+        const float y1 = b * c + a * s;
+        T* dst = (h < n_heads) ? q_out + ((size_t)n * n_heads + h) * head_dim
+                               : kdst + (size_t)(h - n_heads) * page_size * head_dim;
+        dst[k] = from_f32<T>(y0);
+        dst[k + half] = from_f32<T>(y1);
+    }
+    if (write_kv) {
+        const T* vrow = row + (size_t)(n_heads + n_kv_heads) * head_dim;
+        for (int idx = threadIdx.x; idx < n_kv_heads * head_dim; idx += blockDim.x) {
+            const int h = idx / head_dim, d = idx - h * head_dim;
+            vdst[(size_t)h * page_size * head_dim + d] = vrow[idx];
+        }
+    }
+}
+
+ZI_EXPORT int zi_rope_append(const void* qkv, void* q_out, void* cache, int dtype, const int* tables,
+                             const int* tok_seg, const int* pos, const float* inv_freq, int n_tokens,
+                             int row_stride, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                             int max_blocks, long long page_stride, long long kv_stride, int write_kv,
+                             cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (head_dim <= 0 || (head_dim & 1)) return zi_fail("rope: head_dim=%d must be positive and even", head_dim);
+    if (n_heads <= 0 || n_kv_heads <= 0 || page_size <= 0) return zi_fail("rope: bad head counts or page size");
+    const size_t smem = (size_t)head_dim * sizeof(float);
+    ZI_DISPATCH(dtype, T, {
+        rope_append_kernel<T><<<n_tokens, 128, smem, stream>>>((const T*)qkv, (T*)q_out, (T*)cache, tables, tok_seg,
+                                                               pos, inv_freq, row_stride, n_heads, n_kv_heads,
+                                                               head_dim, page_size, max_blocks, page_stride,
+                                                               kv_stride, write_kv);
+    });
+    return zi_check_launch("rope_append");
+}
+
+// ---------------------------------------------------------------------------------------
+// SiLU-mul: out[n, j] = up * gate / (1 + exp(-gate)),  gate = x[n, j], up = x[n, inter + j]
+// (src/backend/ops/swiglu/cpu/swiglu_cpu.cpp:13-20)
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int inter, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = i / inter, j = i - n * inter;
+        const float g = to_f32<T>(x[n * 2 * inter + j]);
+        const float u = to_f32<T>(x[n * 2 * inter + inter + j]);
+        out[i] = from_f32<T>(u * g / (1.0f + expf(-g)));
+    }
+}
+
+ZI_EXPORT int zi_silu_mul(const void* gate_up, void* out, int dtype, int rows, int inter, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (inter <= 0) return zi_fail("silu_mul: width %d must be positive", inter);
+    const size_t total = (size_t)rows * inter;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads > 148 * 16 ? 148 * 16 : (total + threads - 1) / threads);
+    ZI_DISPATCH(dtype, T, { silu_mul_kernel<T><<<blocks, threads, 0, stream>>>((const T*)gate_up, (T*)out, inter, total); });
+    return zi_check_launch("silu_mul");
+}
+
+// ---------------------------------------------------------------------------------------
+// Cast between float32 and bfloat16 (round to nearest even).
+// ---------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = from_f32<TO>(to_f32<TI>(in[i]));
+}
+
+ZI_EXPORT int zi_cast(const void* in, int in_dtype, void* out, int out_dtype, long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const int threads = 256;
+    const long long want = (total + threads - 1) / threads;
+    const int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
+    ZI_DISPATCH(in_dtype, TI, ZI_DISPATCH(out_dtype, TO, {
+        cast_kernel<TI, TO><<<blocks, threads, 0, stream>>>((const TI*)in, (TO*)out, (size_t)total);
+    }););
+    return zi_check_launch("cast");
+}

@@ -1,0 +1,125 @@
+// Shared helpers for the sm_100a kernels: dtype codes, conversions, 16-byte loads,
+// block reductions with a fixed order, and the error channel of the C entry points.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#define ZI_EXPORT extern "C" __attribute__((visibility("default")))
+
+// dtype codes shared with the Python side (zedinfer_b200/ops/_lib.py)
+#define ZI_F32 0
+#define ZI_BF16 1
+
+typedef __nv_bfloat16 bf16;
+
+// ---- error channel -------------------------------------------------------------------
+// Every entry point returns 0 on success.  On failure it returns non-zero and leaves a
+// message that zi_last_error() of the same library returns.
+static thread_local char zi_error_buf[512];
+
+static inline int zi_fail(const char* fmt, ...) __attribute__((format(printf, 1, 2)));
+#include <stdarg.h>
+static inline int zi_fail(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(zi_error_buf, sizeof(zi_error_buf), fmt, ap);
+    va_end(ap);
+    return 1;
+}
+
+static inline int zi_check_launch(const char* what) {
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return zi_fail("%s: launch failed: %s", what, cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+#define ZI_DEFINE_LAST_ERROR(libname)                                            \
+    ZI_EXPORT const char* zi_last_error_##libname() { return zi_error_buf; }
+
+// ---- conversions ----------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// Load 8 consecutive elements (16-byte aligned for bf16, 32-byte for float) as floats.
+__device__ __forceinline__ void load8(const float* p, float* out) {
+    float4 a = *reinterpret_cast<const float4*>(p);
+    float4 b = *reinterpret_cast<const float4*>(p + 4);
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+    out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float* out) {
+    uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 f = __bfloat1622float2(h[i]);
+        out[2 * i] = f.x;
+        out[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void store8(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(bf16* p, const float* v) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+}
+
+// ---- reductions with a fixed order -----------------------------------------------------
+// The order of additions depends only on the block size, never on the data or the grid,
+// so a row's result is the same whatever else is in the batch.
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// Block sum; `scratch` holds at least 32 floats of shared memory.  All threads get the result.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : 0.0f;
+    r = warp_sum(r);
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : -INFINITY;
+    r = warp_max(r);
+    return r;
+}
+
+// Dispatch a dtype code to a type.  Usage: ZI_DISPATCH(code, T, { kernel<T><<<...>>>(...); })
+#define ZI_DISPATCH(code, T, ...)                        \
+    do {                                                 \
+        if ((code) == ZI_F32) { typedef float T; __VA_ARGS__ }        \
+        else if ((code) == ZI_BF16) { typedef bf16 T; __VA_ARGS__ }   \
+        else return zi_fail("unknown dtype code %d", (int)(code));    \
+    } while (0)

@@ -1,0 +1,228 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+:class:`EngineCore` owns the model, the cache manager and the device-side descriptor of a
+step.  ``step(entries)`` takes any mix of prompt portions and single decoded tokens, cut
+anywhere; it runs only the tokens it is given, appends their keys and values to the pages of
+their requests, and returns float32 logits at the places asked for.  Generation, trace replay
+and the benchmark all go through this one function.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, RequestCache
+from ..config.registry import load_model_config
+from ..parts.base import StepContext
+from ..weights.loader import load_weights
+from .model import Model
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    if dtype not in _DTYPES:
+        raise ValueError(f"dtype must be 'bfloat16' or 'float32', got {dtype!r}")
+    return _DTYPES[dtype]
+
+
+@dataclass
+class StepEntry:
+    """A request's next tokens in one step, and the places (indices into ``tokens``) whose logits are wanted."""
+    request_id: object
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=tuple)
+
+
+def require_gpu(device) -> torch.device:
+    if not torch.cuda.is_available():
+        raise RuntimeError("zedinfer_b200 runs on an NVIDIA GPU only: no CUDA device is visible, "
+                           "and there is no CPU path")
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        raise RuntimeError(f"zedinfer_b200 runs on an NVIDIA GPU only, not on {dev}")
+    return dev
+
+
+class _PinnedRing:
+    """A few pinned staging buffers; a buffer is reused only after the copy out of it has finished."""
+
+    def __init__(self, n: int = 4):
+        self.bufs: List[Optional[torch.Tensor]] = [None] * n
+        self.events: List[Optional[torch.cuda.Event]] = [None] * n
+        self.i = 0
+
+    def stage(self, host: np.ndarray, device: torch.device) -> torch.Tensor:
+        i = self.i
+        self.i = (i + 1) % len(self.bufs)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        buf = self.bufs[i]
+        if buf is None or buf.numel() < host.size:
+            buf = torch.empty(max(host.size, 4096), dtype=torch.int32).pin_memory()
+            self.bufs[i] = buf
+        buf[:host.size].numpy()[:] = host
+        dev = torch.empty(host.size, dtype=torch.int32, device=device)
+        dev.copy_(buf[:host.size], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+        return dev
+
+
+class EngineCore:
+    def __init__(self, model_dir: str, dtype="bfloat16", *, page_size: int = 16, num_pages: Optional[int] = None,
+                 max_tokens: Optional[int] = None, gpu_memory_utilization: float = 0.9, max_requests: int = 64,
+                 max_seq_len: Optional[int] = None, device="cuda:0"):
+        """``num_pages``: pages per cache group; ``max_tokens``: size the pool for that many cached tokens
+        instead; neither: whatever ``gpu_memory_utilization`` of the device leaves after the weights."""
+        self.device = require_gpu(device)
+        self.dtype = parse_dtype(dtype)
+        torch.cuda.set_device(self.device)
+        self.arch, self.config, self.spec = load_model_config(model_dir)
+        self.model = Model(self.spec)
+        tensors = load_weights(model_dir, self.model.tensor_specs(), self.dtype, self.device)
+        self.model.bind(tensors, self.dtype, self.device)
+        del tensors
+        self.page_size = int(page_size)
+        self.max_seq_len = min(int(max_seq_len or self.spec.max_position_embeddings),
+                               self.spec.max_position_embeddings)
+        self.cache = CacheManager(self.model.cache_needs(), self.page_size, max_requests=max_requests)
+        if num_pages is None and max_tokens is not None:
+            num_pages = (int(max_tokens) + self.page_size - 1) // self.page_size
+        if num_pages is None:
+            free, total = torch.cuda.mem_get_info(self.device)
+            budget = int(total * gpu_memory_utilization) - (total - free)
+            # leave room for the activations of a step
+            budget -= 2 << 30
+            num_pages = self.cache.pages_for_budget(max(budget, 0), self.dtype)
+            per_request = (self.max_seq_len + self.page_size - 1) // self.page_size
+            num_pages = min(num_pages, per_request * max_requests)
+            if num_pages <= 0:
+                raise RuntimeError("no device memory left for the cache after the weights "
+                                   f"(free {free >> 20} MiB of {total >> 20} MiB, utilization {gpu_memory_utilization})")
+        self.cache.allocate_device(int(num_pages), self.dtype, self.device)
+        self.views = {call: self.cache.view_for_call(call) for call, _ in self.model.cache_needs()}
+        self.table_width = max(1, (self.max_seq_len + self.page_size - 1) // self.page_size)
+        self._ring = _PinnedRing()
+
+    @staticmethod
+    def kernel_libraries(dtype) -> List[str]:
+        """The kernel libraries a run in ``dtype`` loads, for building them ahead of the first step."""
+        libs = ["elementwise", "gemm_simt", "attention_generic", "sampling"]
+        return libs
+
+    # ---- requests -------------------------------------------------------------------------
+    def request(self, request_id) -> Optional[RequestCache]:
+        return self.cache.get(request_id)
+
+    def end(self, request_id) -> None:
+        rc = self.cache.get(request_id)
+        if rc is not None:
+            self.cache.close(rc)
+
+    # ---- the step -------------------------------------------------------------------------
+    def build_context(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache],
+                      pad_segments: int = 0) -> Tuple[StepContext, Optional[torch.Tensor]]:
+        """Flatten the entries into one device descriptor (a single host-to-device copy)."""
+        n_seg = len(entries) + pad_segments
+        n_tok = sum(len(e.tokens) for e in entries) + pad_segments
+        width = self.table_width
+        n_groups = len(self.cache.groups)
+        n_want = sum(len(e.want) for e in entries)
+        # layout: ids | pos | tok_seg | want rows | slots | tables[g]...
+        off_ids, off_pos, off_seg = 0, n_tok, 2 * n_tok
+        off_want = 3 * n_tok
+        off_slots = off_want + n_want
+        off_tab = off_slots + n_seg
+        total = off_tab + n_groups * n_seg * width
+        host = np.zeros(total, dtype=np.int32)
+        seg_start, seg_len, seg_pos0, slots = [], [], [], []
+        t = 0
+        w = 0
+        max_kv = 0
+        vocab = self.spec.vocab_size
+        for s, (e, rc) in enumerate(zip(entries, rcs)):
+            toks = np.asarray(e.tokens, dtype=np.int64)
+            k = toks.size
+            if k and (toks.min() < 0 or toks.max() >= vocab):
+                raise ValueError(f"request {e.request_id!r}: token id outside [0, {vocab})")
+            host[off_ids + t: off_ids + t + k] = toks
+            host[off_pos + t: off_pos + t + k] = np.arange(rc.length, rc.length + k, dtype=np.int32)
+            host[off_seg + t: off_seg + t + k] = s
+            for j in e.want:
+                if not 0 <= j < k:
+                    raise ValueError(f"request {e.request_id!r}: wanted place {j} is outside its {k} tokens")
+                host[off_want + w] = t + j
+                w += 1
+            host[off_slots + s] = rc.slot
+            for g in range(n_groups):
+                tab = rc.tables[g]
+                base = off_tab + (g * n_seg + s) * width
+                host[base: base + len(tab)] = tab
+            seg_start.append(t), seg_len.append(k), seg_pos0.append(rc.length), slots.append(rc.slot)
+            max_kv = max(max_kv, rc.length + k)
+            t += k
+        scratch = self.cache.scratch_page if self.cache.groups else 0
+        for s in range(len(entries), n_seg):         # padding: one token at position 0 of the scratch page
+            host[off_seg + t] = s
+            host[off_slots + s] = -1
+            for g in range(n_groups):
+                host[off_tab + (g * n_seg + s) * width] = scratch
+            seg_start.append(t), seg_len.append(1), seg_pos0.append(0), slots.append(-1)
+            t += 1
+        dev = self._ring.stage(host, self.device)
+        tables = [dev[off_tab + g * n_seg * width: off_tab + (g + 1) * n_seg * width].view(n_seg, width)
+                  for g in range(n_groups)]
+        ctx = StepContext(
+            n_tokens=n_tok, n_segments=n_seg, dtype=self.dtype, device=self.device,
+            token_ids=dev[off_ids: off_ids + n_tok], positions=dev[off_pos: off_pos + n_tok],
+            tok_seg=dev[off_seg: off_seg + n_tok], tables=tables, slots=dev[off_slots: off_slots + n_seg],
+            seg_start_host=seg_start, seg_len_host=seg_len, seg_pos0_host=seg_pos0, slots_host=slots,
+            decode_only=all(k == 1 for k in seg_len), max_kv_len=max_kv)
+        want = dev[off_want: off_want + n_want] if n_want else None
+        return ctx, want
+
+    def prepare(self, entries: Sequence[StepEntry]) -> List[RequestCache]:
+        """Open new requests and make sure every entry has pages for its tokens; all or nothing."""
+        seen = set()
+        for e in entries:
+            if e.request_id in seen:
+                raise ValueError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            if len(e.tokens) == 0:
+                raise ValueError(f"request {e.request_id!r} brings no tokens")
+        opened: List[RequestCache] = []
+        rcs: List[RequestCache] = []
+        try:
+            for e in entries:
+                rc = self.cache.get(e.request_id)
+                if rc is None:
+                    rc = self.cache.open(e.request_id)
+                    opened.append(rc)
+                new_len = rc.length + len(e.tokens)
+                if new_len > self.max_seq_len:
+                    raise ValueError(f"request {e.request_id!r} would reach {new_len} tokens; the context limit "
+                                     f"is {self.max_seq_len}")
+                self.cache.ensure(rc, new_len)
+                rcs.append(rc)
+        except Exception:
+            for rc in opened:
+                self.cache.close(rc)
+            raise
+        return rcs
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch; returns float32 logits ``[wanted, vocab]`` on the device, or None if nothing is wanted."""
+        if not entries:
+            return None
+        rcs = self.prepare(entries)
+        ctx, want = self.build_context(entries, rcs)
+        logits = self.model.forward(ctx, self.views, want)
+        for e, rc in zip(entries, rcs):
+            self.cache.commit(rc, rc.length + len(e.tokens))
+        return logits

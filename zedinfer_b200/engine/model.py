@@ -1,0 +1,87 @@
+"""A model put together from a :class:`ModelSpec`: embedding, blocks in schedule order, final
+norm, output head.  It knows no architecture: which parts a layer has, their sizes and the
+order of the calls all come from the spec."""
+from __future__ import annotations
+
+from typing import Dict, List, Mapping, Optional, Tuple
+
+import torch
+
+from ..cache.manager import CallCacheView
+from ..config.spec import ModelSpec
+from ..parts.base import Block, ResidualStream, StepContext, block_class, build_part
+from ..parts.embedding import OutputHead, TokenEmbedding
+from ..weights.loader import TensorSpec
+
+
+class Model:
+    def __init__(self, spec: ModelSpec):
+        spec.validate()
+        self.spec = spec
+        self.blocks: List[Block] = []
+        for layer in spec.layers:
+            cls = block_class(layer.block)
+            mixer = build_part("mixer", layer.mixer)
+            ffn = build_part("ffn", layer.ffn)
+            norms = {role: build_part("norm", ns) for role, ns in layer.norms.items()}
+            self.blocks.append(cls(mixer, ffn, norms))
+        self.embedding = TokenEmbedding(spec.vocab_size, spec.hidden_size, spec.embed_name)
+        self.final_norm = build_part("norm", spec.final_norm)
+        self.head = OutputHead(spec.vocab_size, spec.hidden_size, spec.tie_word_embeddings, spec.head_name)
+        self.dtype: Optional[torch.dtype] = None
+        self.device: Optional[torch.device] = None
+
+    # ---- tensors ----------------------------------------------------------------------------
+    def _part_prefixes(self):
+        """(part, global name prefix) for every part that loads tensors."""
+        for i, (layer, blk) in enumerate(zip(self.spec.layers, self.blocks)):
+            base = self.spec.layer_prefix.format(i=i)
+            for role, part in blk.parts().items():
+                yield part, base + layer.prefixes.get(role, role + ".")
+        yield self.final_norm, self.spec.final_norm_prefix
+        yield self.embedding, ""
+        yield self.head, ""
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        out: Dict[str, TensorSpec] = {}
+        for part, prefix in self._part_prefixes():
+            for local, ts in part.tensor_specs().items():
+                out[prefix + local] = ts
+        return out
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype, device) -> None:
+        self.dtype, self.device = dtype, torch.device(device)
+        for part, prefix in self._part_prefixes():
+            local = {name: tensors[prefix + name] for name in part.tensor_specs() if prefix + name in tensors}
+            if part is self.head:
+                self.head.bind(local, embedding=self.embedding.table)
+            else:
+                part.bind(local)
+
+    # ---- cache ------------------------------------------------------------------------------
+    def cache_needs(self) -> List[Tuple[int, object]]:
+        """(schedule index, need) for each call that owns a cache."""
+        out = []
+        for pos, call in enumerate(self.spec.schedule):
+            if call.cache_of is None:
+                out.append((pos, self.blocks[call.layer].mixer.cache_need()))
+        return out
+
+    # ---- one step ---------------------------------------------------------------------------
+    def forward(self, ctx: StepContext, cache_views: Mapping[int, CallCacheView],
+                logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """Run the step's tokens through every call; return float32 logits of ``logit_rows`` (or None)."""
+        h = torch.empty((ctx.n_tokens, self.spec.hidden_size), dtype=torch.float32, device=ctx.device)
+        self.embedding.forward(ctx.token_ids, h)
+        stream = ResidualStream(h)
+        for pos, call in enumerate(self.spec.schedule):
+            owner = pos if call.cache_of is None else call.cache_of
+            self.blocks[call.layer].forward(stream, ctx, cache_views[owner], owns_cache=call.cache_of is None)
+        if logit_rows is None or logit_rows.numel() == 0:
+            return None
+        rows = logit_rows.numel()
+        normed = ctx.empty(rows, self.spec.hidden_size)
+        self.final_norm.forward_residual(stream, normed, row_idx=logit_rows)
+        logits = torch.empty((rows, self.spec.vocab_size), dtype=torch.float32, device=ctx.device)
+        self.head.forward(normed, logits)
+        return logits

@@ -1,0 +1,216 @@
+"""Python faces of the CUDA kernels.  Every function writes into tensors the caller gives.
+
+Nothing here runs on the CPU and nothing falls back to a library model or a library
+attention; matrix products of bfloat16 operands go to cuBLAS through ``torch.mm`` where
+the reference's engine calls cuBLASLt (src/backend/ops/linear/nvidia/linear_cublas.cu:201-231),
+and 32-bit products go to the SIMT kernel of ``csrc/gemm_simt.cu`` so that no
+reduced-precision matrix mode can slip in.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ._lib import (BF16, F32, KernelError, Library, c_float, c_int, c_ll, dtype_code, need_contiguous, need_cuda,
+                   need_int32, ptr, stream)
+
+_elementwise = Library("elementwise")
+_gemm_simt = Library("gemm_simt")
+_attention_generic = Library("attention_generic")
+_sampling = Library("sampling")
+
+__all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "silu_mul", "cast",
+           "gemm_nt", "linear", "paged_attention", "attention", "argmax", "sample", "repetition_penalty"]
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    need_cuda(table, ids, out)
+    need_int32("ids", ids)
+    need_contiguous("table", table), need_contiguous("out", out), need_contiguous("ids", ids)
+    n, hidden = ids.numel(), table.shape[1]
+    if out.shape != (n, hidden):
+        raise KernelError(f"embedding: out has shape {tuple(out.shape)}, expected {(n, hidden)}")
+    _elementwise.call("zi_embedding", ptr(table), c_int(dtype_code(table.dtype)), ptr(ids), ptr(out),
+                      c_int(dtype_code(out.dtype)), c_int(n), c_int(hidden), c_int(table.shape[0]), stream())
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    need_cuda(x, w, out)
+    need_contiguous("x", x), need_contiguous("w", w), need_contiguous("out", out)
+    rows, hidden = x.shape
+    if w.numel() != hidden or out.shape != x.shape:
+        raise KernelError(f"rmsnorm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
+    _elementwise.call("zi_rmsnorm", ptr(x), c_int(dtype_code(x.dtype)), ptr(w), c_int(dtype_code(w.dtype)), ptr(out),
+                      c_int(dtype_code(out.dtype)), c_int(rows), c_int(hidden), c_float(eps), stream())
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, eps: float,
+                out: torch.Tensor, row_idx: Optional[torch.Tensor] = None, write_residual: bool = True) -> None:
+    """``residual (+= delta)``, then ``out = rmsnorm(residual) * w``.  ``residual`` is float32.
+
+    With ``row_idx`` the output row ``r`` is computed from input row ``row_idx[r]`` and the
+    residual is left untouched.
+    """
+    need_cuda(residual, delta, w, out, row_idx)
+    if residual.dtype != torch.float32:
+        raise KernelError(f"add_rmsnorm: the residual stream is float32, got {residual.dtype}")
+    need_contiguous("residual", residual), need_contiguous("w", w), need_contiguous("out", out)
+    hidden = residual.shape[1]
+    if delta is not None:
+        need_contiguous("delta", delta)
+        if delta.shape != residual.shape:
+            raise KernelError(f"add_rmsnorm: delta {tuple(delta.shape)} vs residual {tuple(residual.shape)}")
+    if row_idx is not None:
+        need_int32("row_idx", row_idx), need_contiguous("row_idx", row_idx)
+        rows = row_idx.numel()
+    else:
+        rows = residual.shape[0]
+    if w.numel() != hidden or out.shape != (rows, hidden):
+        raise KernelError(f"add_rmsnorm: w {tuple(w.shape)} / out {tuple(out.shape)} do not fit {(rows, hidden)}")
+    _elementwise.call("zi_add_rmsnorm", ptr(residual), ptr(delta),
+                      c_int(dtype_code(delta.dtype) if delta is not None else F32), ptr(w), c_int(dtype_code(w.dtype)),
+                      ptr(out), c_int(dtype_code(out.dtype)), ptr(row_idx), c_int(rows), c_int(hidden), c_float(eps),
+                      c_int(1 if write_residual else 0), stream())
+
+
+def rope_append(qkv: torch.Tensor, q_out: torch.Tensor, cache: Optional[torch.Tensor], tables: torch.Tensor,
+                tok_seg: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, n_heads: int, n_kv_heads: int,
+                head_dim: int, page_size: int, page_stride: int, kv_stride: int, write_kv: bool = True) -> None:
+    """Rotate q (and k) by position and append k, v to the cache pages of each token's request."""
+    need_cuda(qkv, q_out, cache, tables, tok_seg, pos, inv_freq)
+    need_int32("tables", tables), need_int32("tok_seg", tok_seg), need_int32("pos", pos)
+    need_contiguous("q_out", q_out)
+    n = qkv.shape[0]
+    if qkv.stride(1) != 1 or qkv.shape[1] < (n_heads + 2 * n_kv_heads) * head_dim:
+        raise KernelError(f"rope_append: qkv {tuple(qkv.shape)} does not hold {n_heads}+2*{n_kv_heads} heads of {head_dim}")
+    if q_out.dtype != qkv.dtype or (cache is not None and cache.dtype != qkv.dtype):
+        raise KernelError("rope_append: qkv, q_out and the cache must share one dtype")
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() != head_dim // 2:
+        raise KernelError("rope_append: inv_freq must be float32 of head_dim/2 entries")
+    if write_kv and cache is None:
+        raise KernelError("rope_append: write_kv needs a cache")
+    _elementwise.call("zi_rope_append", ptr(qkv), ptr(q_out), ptr(cache), c_int(dtype_code(qkv.dtype)), ptr(tables),
+                      ptr(tok_seg), ptr(pos), ptr(inv_freq), c_int(n), c_int(qkv.stride(0)), c_int(n_heads),
+                      c_int(n_kv_heads), c_int(head_dim), c_int(page_size), c_int(tables.shape[1]),
+                      c_ll(page_stride), c_ll(kv_stride), c_int(1 if write_kv else 0), stream())
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    need_cuda(gate_up, out)
+    need_contiguous("gate_up", gate_up), need_contiguous("out", out)
+    rows, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (rows, two_i // 2) or out.dtype != gate_up.dtype:
+        raise KernelError(f"silu_mul: gate_up {tuple(gate_up.shape)} vs out {tuple(out.shape)}")
+    _elementwise.call("zi_silu_mul", ptr(gate_up), ptr(out), c_int(dtype_code(out.dtype)), c_int(rows),
+                      c_int(two_i // 2), stream())
+
+
+def cast(x: torch.Tensor, out: torch.Tensor) -> None:
+    need_cuda(x, out)
+    need_contiguous("x", x), need_contiguous("out", out)
+    if x.numel() != out.numel():
+        raise KernelError("cast: sizes differ")
+    _elementwise.call("zi_cast", ptr(x), c_int(dtype_code(x.dtype)), ptr(out), c_int(dtype_code(out.dtype)),
+                      c_ll(x.numel()), stream())
+
+
+def gemm_nt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """``out = a @ w.T + bias`` on the SIMT cores: float32 FMA chains in rising k, any operand types."""
+    need_cuda(a, w, bias, out)
+    if a.dim() != 2 or w.dim() != 2 or out.dim() != 2:
+        raise KernelError("gemm_nt: operands must be matrices")
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape != (m, n) or (bias is not None and bias.numel() != n):
+        raise KernelError(f"gemm_nt: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
+    if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm_nt: rows must be contiguous")
+    _gemm_simt.call("zi_gemm_nt", ptr(a), c_int(dtype_code(a.dtype)), ptr(w), c_int(dtype_code(w.dtype)), ptr(bias),
+                    c_int(dtype_code(bias.dtype) if bias is not None else F32), ptr(out),
+                    c_int(dtype_code(out.dtype)), c_int(m), c_int(n), c_int(k), c_ll(a.stride(0)), c_ll(w.stride(0)),
+                    c_ll(out.stride(0)), stream())
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """``out = x @ w.T + bias``; picks the kernel by operand types.
+
+    * any float32 operand: the SIMT kernel (true 32-bit arithmetic);
+    * bfloat16 x bfloat16: cuBLAS with float32 accumulation, the library product the reference's
+      engine uses as well; the output may be bfloat16 or float32.
+    """
+    need_cuda(x, w, bias, out)
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and (bias is None or bias.dtype == torch.bfloat16):
+        if out.dtype == torch.bfloat16:
+            if bias is not None:
+                torch.addmm(bias, x, w.t(), out=out)
+            else:
+                torch.mm(x, w.t(), out=out)
+        else:
+            res = torch.mm(x, w.t(), out_dtype=torch.float32)
+            if bias is not None:
+                res += bias.float()
+            out.copy_(res)
+        return
+    gemm_nt(x, w, bias, out)
+
+
+def paged_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
+                    tok_seg: torch.Tensor, pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                    page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float) -> None:
+    """Causal attention of each token over its request's cache pages (general kernel)."""
+    need_cuda(q, cache, out, tables, tok_seg, pos)
+    need_int32("tables", tables), need_int32("tok_seg", tok_seg), need_int32("pos", pos)
+    need_contiguous("q", q), need_contiguous("out", out)
+    if q.dtype != cache.dtype or out.dtype != q.dtype:
+        raise KernelError("paged_attention: q, cache and out must share one dtype")
+    n = q.shape[0]
+    _attention_generic.call("zi_paged_attention", ptr(q), ptr(cache), ptr(out), c_int(dtype_code(q.dtype)),
+                            ptr(tables), ptr(tok_seg), ptr(pos), c_int(n), c_int(n_heads), c_int(n_kv_heads),
+                            c_int(head_dim), c_int(page_size), c_int(tables.shape[1]), c_ll(page_stride),
+                            c_ll(kv_stride), c_int(window or 0), c_float(scale), stream())
+
+
+def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
+              window: Optional[int], scale: float) -> None:
+    """Attention of a step's tokens over the cache (``cache`` is a CallCacheView, ``ctx`` a StepContext).
+
+    Picks a kernel by dtype and by the shape of the step; all of them compute the same function.
+    """
+    paged_attention(q, cache.tensor, out, ctx.tables[cache.group], ctx.tok_seg, ctx.positions, n_heads, n_kv_heads,
+                    head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    need_cuda(logits, out)
+    need_int32("out", out)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("argmax: logits must be float32 [rows, vocab] with contiguous rows")
+    _sampling.call("zi_argmax", ptr(logits), ptr(out), c_int(logits.shape[0]), c_int(logits.shape[1]),
+                   c_ll(logits.stride(0)), stream())
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+           top_p: torch.Tensor, uniform: torch.Tensor) -> None:
+    """One token per row; rows with ``temperature <= 0`` are greedy."""
+    need_cuda(logits, out, temperature, top_k, top_p, uniform)
+    need_int32("out", out), need_int32("top_k", top_k)
+    rows = logits.shape[0]
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be float32 [rows, vocab] with contiguous rows")
+    for name, t in (("temperature", temperature), ("top_p", top_p), ("uniform", uniform)):
+        if t.dtype != torch.float32 or t.numel() != rows:
+            raise KernelError(f"sample: {name} must be float32 with one entry per row")
+    if top_k.numel() != rows or out.numel() != rows:
+        raise KernelError("sample: top_k and out need one entry per row")
+    _sampling.call("zi_sample", ptr(logits), ptr(out), ptr(temperature), ptr(top_k), ptr(top_p), ptr(uniform),
+                   c_int(rows), c_int(logits.shape[1]), c_ll(logits.stride(0)), stream())
+
+
+def repetition_penalty(logits_row: torch.Tensor, tokens: torch.Tensor, penalty: float) -> None:
+    need_cuda(logits_row, tokens)
+    need_int32("tokens", tokens)
+    if logits_row.dtype != torch.float32 or logits_row.dim() != 1 or not logits_row.is_contiguous():
+        raise KernelError("repetition_penalty: one contiguous float32 row")
+    _sampling.call("zi_repetition_penalty", ptr(logits_row), ptr(tokens), c_int(tokens.numel()),
+                   c_int(logits_row.numel()), c_float(penalty), stream())

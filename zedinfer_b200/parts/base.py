@@ -1,0 +1,176 @@
+"""Interfaces of the parts a layer is put together from, and the registries that name them.
+
+A part knows its own sizes and constants (constructor keywords) and nothing about the model
+it sits in.  The kinds are:
+
+* **Norm** — ``forward(x, out)`` and ``forward_residual(stream, out, ...)``, which first folds
+  the pending branch output into the float32 residual.
+* **PositionEncoding** — owns the constants of a position rule and applies it to the freshly
+  projected q and k of a step, appending k and v to the cache on the way.
+* **Mixer** — mixes information between tokens.  It says what cache it needs per request
+  (pages of keys and values, a fixed-size state, or nothing) and runs on the tokens of one
+  step: ``forward(x, ctx, cache, owns_cache) -> y``.
+* **FeedForward** — works on each token alone: ``forward(x, ctx) -> y``.
+* **Block** — the arrangement of the above around the residual stream.
+
+Every part declares the tensors it loads (``tensor_specs``: local name → shape and init
+rule) and receives them in ``bind``.  New kinds are added with the ``register_*`` functions
+from anywhere, a test file included; nothing in the framework's own files has to change.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Mapping, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CallCacheView
+from ..weights.loader import TensorSpec
+
+
+# ---- what a step hands to the parts ---------------------------------------------------------
+@dataclass
+class StepContext:
+    """One batch of (request, its next tokens), flattened.  Device tensors are int32.
+
+    Token ``n`` belongs to segment ``tok_seg[n]`` and sits at absolute position ``positions[n]``
+    of its request.  Segment ``s`` covers tokens ``seg_start[s] .. seg_start[s] + seg_len[s]``,
+    the first of them at position ``seg_pos0[s]``.  ``tables[g][s]`` is the block table of
+    segment ``s`` in cache group ``g``; ``slots[s]`` its state slot (``-1`` without state).
+    The ``*_host`` lists carry the same numbers for parts that loop on the host.
+    """
+    n_tokens: int
+    n_segments: int
+    dtype: torch.dtype
+    device: torch.device
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    tok_seg: torch.Tensor
+    tables: List[torch.Tensor]
+    slots: Optional[torch.Tensor]
+    seg_start_host: Sequence[int]
+    seg_len_host: Sequence[int]
+    seg_pos0_host: Sequence[int]
+    slots_host: Sequence[int]
+    decode_only: bool = False
+    max_kv_len: int = 0                       # longest context (after this step) among the segments
+    extras: Dict[str, Any] = field(default_factory=dict)   # device tensors of special paths (decode kernels)
+
+    def empty(self, *shape: int, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+
+
+@dataclass
+class ResidualStream:
+    """The float32 residual ``h`` and a branch output ``delta`` that is not added to it yet."""
+    h: torch.Tensor
+    delta: Optional[torch.Tensor] = None
+
+
+# ---- part interfaces ------------------------------------------------------------------------
+class Part:
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        """Receive the loaded tensors (local names).  May fuse or re-lay them out."""
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, out: torch.Tensor) -> None:
+        raise NotImplementedError
+
+    def forward_residual(self, stream: ResidualStream, out: torch.Tensor,
+                         row_idx: Optional[torch.Tensor] = None) -> None:
+        """Fold ``stream.delta`` into ``stream.h`` (float32 add) and write ``norm(h)`` to ``out``.
+
+        With ``row_idx`` only those rows are produced and the stream is left as it is.
+        """
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def rotate_append(self, qkv: torch.Tensor, q_out: torch.Tensor, cache: CallCacheView, ctx: StepContext,
+                      n_heads: int, n_kv_heads: int, head_dim: int, write_kv: bool) -> None:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_need(self):
+        """``PagedKVNeed``, ``StateNeed`` or ``None``."""
+        return None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CallCacheView, owns_cache: bool) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block:
+    """Arrangement of a mixer, a feed-forward and norms around the residual stream."""
+
+    def __init__(self, mixer: Mixer, ffn: FeedForward, norms: Mapping[str, Norm]):
+        self.mixer, self.ffn, self.norms = mixer, ffn, dict(norms)
+
+    def parts(self) -> Dict[str, Part]:
+        out: Dict[str, Part] = {"mixer": self.mixer, "ffn": self.ffn}
+        out.update(self.norms)
+        return out
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, cache: CallCacheView, owns_cache: bool) -> None:
+        raise NotImplementedError
+
+
+# ---- registries -----------------------------------------------------------------------------
+_REGISTRIES: Dict[str, Dict[str, Callable[..., Any]]] = {
+    "norm": {}, "position": {}, "mixer": {}, "ffn": {}, "block": {},
+}
+
+
+def _register(family: str, kind: str):
+    def deco(cls):
+        _REGISTRIES[family][kind] = cls
+        return cls
+    return deco
+
+
+def register_norm(kind: str):
+    return _register("norm", kind)
+
+
+def register_position(kind: str):
+    return _register("position", kind)
+
+
+def register_mixer(kind: str):
+    return _register("mixer", kind)
+
+
+def register_feed_forward(kind: str):
+    return _register("ffn", kind)
+
+
+def register_block(kind: str):
+    return _register("block", kind)
+
+
+def unregister(family: str, kind: str) -> None:
+    _REGISTRIES[family].pop(kind, None)
+
+
+def build_part(family: str, spec) -> Any:
+    """Construct a part from a :class:`~zedinfer_b200.config.spec.PartSpec`."""
+    table = _REGISTRIES[family]
+    if spec.kind not in table:
+        raise KeyError(f"no {family} of kind {spec.kind!r} is registered (known: {', '.join(sorted(table)) or 'none'})")
+    return table[spec.kind](**dict(spec.params))
+
+
+def block_class(kind: str):
+    table = _REGISTRIES["block"]
+    if kind not in table:
+        raise KeyError(f"no block arrangement {kind!r} is registered (known: {', '.join(sorted(table)) or 'none'})")
+    return table[kind]

@@ -1,0 +1,22 @@
+"""Pre-norm residual arrangement (src/frontend/models/transformer_forward.cpp:63-149):
+
+    h = h + mixer(norm1(h));  h = h + ffn(norm2(h))
+
+The adds are fused into the norm that follows them: a branch output stays "pending" in the
+stream until the next norm folds it into the float32 residual."""
+from __future__ import annotations
+
+from ..cache.manager import CallCacheView
+from .base import Block, ResidualStream, StepContext, register_block
+
+
+@register_block("pre_norm")
+class PreNormBlock(Block):
+    def forward(self, stream: ResidualStream, ctx: StepContext, cache: CallCacheView, owns_cache: bool) -> None:
+        n, hidden = stream.h.shape
+        normed = ctx.empty(n, hidden)
+        self.norms["norm1"].forward_residual(stream, normed)
+        stream.delta = self.mixer.forward(normed, ctx, cache, owns_cache)
+        normed2 = ctx.empty(n, hidden)
+        self.norms["norm2"].forward_residual(stream, normed2)
+        stream.delta = self.ffn.forward(normed2, ctx)
