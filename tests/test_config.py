@@ -1,0 +1,136 @@
+"""Configuration: config.json keys, defaults, errors, the registry, and the spec it builds."""
+import json
+import os
+
+import pytest
+
+import tiny
+from zedinfer_b200.config import (ConfigError, GenerationConfig, LayerCall, ModelSpec, SchedulerConfig,
+                                  load_model_config, register_architecture, resolve_architecture,
+                                  resolve_max_new_tokens, supported_architectures, unregister_architecture)
+from zedinfer_b200.models.qwen2 import build_qwen2_spec, parse_qwen2_config
+
+
+def test_defaults_follow_the_reference():
+    raw = {"architectures": ["Qwen2ForCausalLM"], "hidden_size": 64, "intermediate_size": 100, "vocab_size": 50,
+           "num_hidden_layers": 2, "num_attention_heads": 4, "max_position_embeddings": 128}
+    c = parse_qwen2_config(raw)
+    assert c.num_key_value_heads == 4 and c.head_dim == 16
+    assert c.rms_norm_eps == 1e-6 and c.rope_theta == 10000.0
+    assert c.tie_word_embeddings is False and c.torch_dtype == "bfloat16"
+    assert c.eos_token_ids == (151643,) and c.bos_token_id == 151643
+    assert c.use_sliding_window is False and c.sliding_window == 4096 and c.max_window_layers == 21
+
+
+def test_eos_as_list_and_head_dim_given():
+    raw = dict(tiny.TINY_D, eos_token_id=[5, 9])
+    c = parse_qwen2_config(raw)
+    assert c.eos_token_ids == (5, 9)
+    assert c.head_dim == 128 and c.q_dim == 12 * 128 and c.kv_dim == 256
+
+
+@pytest.mark.parametrize("key", ["hidden_size", "intermediate_size", "vocab_size", "num_hidden_layers",
+                                 "num_attention_heads", "max_position_embeddings"])
+def test_missing_required_key_is_named(key):
+    raw = dict(tiny.TINY_A)
+    del raw[key]
+    with pytest.raises(ConfigError, match=key):
+        parse_qwen2_config(raw)
+
+
+@pytest.mark.parametrize("patch,word", [
+    ({"num_key_value_heads": 3}, "num_key_value_heads"),
+    ({"head_dim": 15}, "head_dim"),
+    ({"rope_scaling": {"type": "yarn", "factor": 4}}, "rope_scaling"),
+    ({"hidden_act": "gelu"}, "hidden_act"),
+    ({"rms_norm_eps": 0}, "rms_norm_eps"),
+    ({"rope_theta": -1.0}, "rope_theta"),
+    ({"vocab_size": "many"}, "vocab_size"),
+    ({"torch_dtype": "int8"}, "torch_dtype"),
+    ({"eos_token_id": "x"}, "eos_token_id"),
+    ({"use_sliding_window": True, "sliding_window": 0}, "sliding_window"),
+    ({"num_hidden_layers": 0}, "num_hidden_layers"),
+])
+def test_bad_values_are_refused(patch, word):
+    raw = dict(tiny.TINY_A)
+    raw.update(patch)
+    with pytest.raises(ConfigError, match=word):
+        parse_qwen2_config(raw)
+
+
+def test_registry_by_architecture_and_by_model_type():
+    assert "Qwen2ForCausalLM" in supported_architectures()
+    assert resolve_architecture({"architectures": ["Qwen2ForCausalLM"]}).name == "Qwen2ForCausalLM"
+    assert resolve_architecture({"model_type": "qwen2"}).name == "Qwen2ForCausalLM"
+    with pytest.raises(ConfigError, match="Qwen2ForCausalLM"):
+        resolve_architecture({"architectures": ["LlamaForCausalLM"], "model_type": "llama"})
+
+
+def test_spec_layer_by_layer():
+    spec = build_qwen2_spec(parse_qwen2_config(tiny.TINY_C))
+    assert len(spec.layers) == 3 and [c.layer for c in spec.schedule] == [0, 1, 2]
+    windows = [l.mixer.params["window"] for l in spec.layers]
+    assert windows == [None, 24, 24]
+    m = spec.layers[0].mixer.params
+    assert (m["num_heads"], m["num_kv_heads"], m["head_dim"]) == (6, 3, 48)
+    assert m["qkv_bias"] is True and m["out_bias"] is False
+    assert m["position"].params == {"head_dim": 48, "theta": 50000.0}
+    assert spec.layers[0].norms["norm1"].params["eps"] == 1e-4
+    assert spec.layers[0].ffn.params["intermediate_size"] == 200
+    assert not spec.tie_word_embeddings
+    assert build_qwen2_spec(parse_qwen2_config(tiny.TINY_A)).tie_word_embeddings
+
+
+def test_schedule_validation():
+    spec = build_qwen2_spec(parse_qwen2_config(tiny.TINY_A))
+    import dataclasses
+    ok = dataclasses.replace(spec, schedule=(LayerCall(0), LayerCall(1), LayerCall(0), LayerCall(1, cache_of=1)))
+    ok.validate()
+    with pytest.raises(ValueError, match="layer 5"):
+        dataclasses.replace(spec, schedule=(LayerCall(5),)).validate()
+    with pytest.raises(ValueError, match="earlier"):
+        dataclasses.replace(spec, schedule=(LayerCall(0, cache_of=0),)).validate()
+    with pytest.raises(ValueError, match="borrows"):
+        dataclasses.replace(spec, schedule=(LayerCall(0), LayerCall(1, cache_of=0), LayerCall(0, cache_of=1))).validate()
+
+
+def test_load_model_config_errors(tmp_path):
+    with pytest.raises(ConfigError, match="Failed to open config file"):
+        load_model_config(str(tmp_path))
+    (tmp_path / "config.json").write_text("{not json")
+    with pytest.raises(ConfigError, match="not valid JSON"):
+        load_model_config(str(tmp_path))
+    (tmp_path / "config.json").write_text(json.dumps(tiny.TINY_B))
+    arch, cfg, spec = load_model_config(str(tmp_path))
+    assert arch.name == "Qwen2ForCausalLM" and cfg.vocab_size == 1000 and spec.vocab_size == 1000
+
+
+def test_another_architecture_can_be_registered():
+    def parse(raw):
+        return parse_qwen2_config(dict(raw, model_type="qwen2"))
+    register_architecture("ToyForCausalLM", model_types=("toy",), parse=parse, build_spec=build_qwen2_spec)
+    try:
+        assert resolve_architecture({"model_type": "toy"}).name == "ToyForCausalLM"
+    finally:
+        unregister_architecture("ToyForCausalLM")
+    with pytest.raises(ConfigError):
+        resolve_architecture({"model_type": "toy"})
+
+
+def test_engine_options():
+    SchedulerConfig().validate()
+    assert SchedulerConfig().max_batch_tokens == 2048 and SchedulerConfig().max_prefill_tokens == 512
+    assert SchedulerConfig().max_batch_requests == 64 and SchedulerConfig().kv_block_size == 16
+    with pytest.raises(ValueError):
+        SchedulerConfig(on_exhaust="swap").validate()
+    with pytest.raises(ValueError):
+        GenerationConfig(use_argmax=False, temperature=0.0).validate()
+    with pytest.raises(ValueError):
+        GenerationConfig(use_argmax=False, top_p=0.0).validate()
+    with pytest.raises(ValueError):
+        GenerationConfig(max_new_tokens=-1).validate()
+    assert resolve_max_new_tokens(0, 10, 100) == 90
+    assert resolve_max_new_tokens(500, 10, 100) == 90
+    assert resolve_max_new_tokens(5, 10, 100) == 5
+    with pytest.raises(ValueError, match="no room"):
+        resolve_max_new_tokens(5, 100, 100)

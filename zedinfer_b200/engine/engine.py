@@ -1,0 +1,148 @@
+"""The Python entry point, in the manner of the reference's engine and serving loop
+(include/zedinfer/engine.hpp:85-202, include/zedinfer/serving_loop.hpp:31-81):
+
+    engine = InferenceEngine.create(model_path, SchedulerConfig(...), dtype="bfloat16")
+    result = engine.generate_tokens(prompt_ids, GenerationConfig(max_new_tokens=32))
+    future = engine.submit_async(InferenceRequest(prompt_ids, config)); engine.run_loop(); future.result()
+
+Requests are token ids in, token ids out: tokenizer and chat templates are not part of this engine.
+"""
+from __future__ import annotations
+
+import time
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..config.engine_config import GenerationConfig, SchedulerConfig
+from ..sampling.sampler import Sampler, fresh_seed
+from .core import EngineCore, StepEntry
+from .request import GenerationResult, InferenceRequest, RequestPhase
+from .scheduler import ScheduledBatch, Scheduler
+
+
+class RequestFuture:
+    """Handle returned by :meth:`InferenceEngine.submit_async`; ``result()`` is ready once the request finished."""
+
+    def __init__(self, request: InferenceRequest):
+        self.request = request
+
+    def done(self) -> bool:
+        return self.request.phase == RequestPhase.COMPLETE
+
+    def result(self) -> GenerationResult:
+        if not self.done():
+            raise RuntimeError("the request has not finished; drive the engine with step() or run_loop()")
+        return self.request.result()
+
+
+class InferenceEngine:
+    def __init__(self, core: EngineCore, scheduler_config: SchedulerConfig):
+        self.core = core
+        self.scheduler_config = scheduler_config
+        self.scheduler = Scheduler(scheduler_config, core.cache, core.max_seq_len, core.spec.eos_token_ids)
+        self.sampler = Sampler(core.device)
+        self.steps_run = 0
+        self.on_step: Optional[Callable[[ScheduledBatch], None]] = None
+
+    @classmethod
+    def create(cls, model_path: str, scheduler_config: Optional[SchedulerConfig] = None, dtype="bfloat16",
+               device="cuda:0") -> "InferenceEngine":
+        cfg = scheduler_config or SchedulerConfig()
+        cfg.validate()
+        core = EngineCore(model_path, dtype, page_size=cfg.kv_block_size, num_pages=cfg.num_kv_pages,
+                          gpu_memory_utilization=cfg.gpu_memory_utilization, max_requests=cfg.max_batch_requests,
+                          max_seq_len=cfg.max_seq_len, device=device)
+        return cls(core, cfg)
+
+    # ---- intake -----------------------------------------------------------------------------
+    def submit_async(self, request: InferenceRequest) -> RequestFuture:
+        request.sample_seed = request.config.seed if request.config.seed != 0 else fresh_seed()
+        request.arrival_time = time.perf_counter()
+        self.scheduler.submit(request)
+        return RequestFuture(request)
+
+    def generate_tokens(self, input_ids: Sequence[int], config: Optional[GenerationConfig] = None,
+                        stream_callback=None) -> GenerationResult:
+        """Run one request to its end on the caller's thread (src/zedinfer/serving_loop.cpp:97-107)."""
+        fut = self.submit_async(InferenceRequest(list(input_ids), config, stream_callback))
+        while not fut.done():
+            if not self.step():
+                break
+        return fut.result()
+
+    def generate_batch(self, prompts: Sequence[Sequence[int]], config: Optional[GenerationConfig] = None
+                       ) -> List[GenerationResult]:
+        futs = [self.submit_async(InferenceRequest(list(p), config)) for p in prompts]
+        self.run_loop()
+        return [f.result() for f in futs]
+
+    # ---- the loop ---------------------------------------------------------------------------
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def run_loop(self) -> None:
+        """Step until every submitted request has finished (src/zedinfer/serving_loop.cpp:424-430)."""
+        while self.scheduler.has_work():
+            self.step()
+
+    def entries_for(self, batch: ScheduledBatch) -> List[StepEntry]:
+        entries = [StepEntry(r.request_id, [r.output_ids[-1]], [0]) for r in batch.decode_requests]
+        for r, start, size in zip(batch.prefill_requests, batch.prefill_chunk_starts, batch.prefill_chunk_sizes):
+            seq = r.sequence()
+            want = [size - 1] if start + size >= len(seq) else []
+            entries.append(StepEntry(r.request_id, seq[start:start + size], want))
+        return entries
+
+    def step(self) -> bool:
+        """schedule → forward → sample → process results.  Returns False when there was nothing to do."""
+        batch = self.scheduler.schedule()
+        if batch.empty():
+            return self.scheduler.has_work()
+        if self.on_step is not None:
+            self.on_step(batch)
+        try:
+            logits = self.core.step(self.entries_for(batch))
+            rows = batch.rows_wanted()
+            tokens = self.sampler.sample(logits, [r for r, _ in rows]) if rows else []
+        except Exception as e:                       # keep serving: fail what was in the step
+            self.scheduler.fail_batch(batch, f"step failed: {e}")
+            if isinstance(e, (torch.cuda.OutOfMemoryError, KeyboardInterrupt)):
+                raise
+            return True
+        self.scheduler.process_results(batch, tokens)
+        self.steps_run += 1
+        return True
+
+    # ---- measurement (src/zedinfer/profiler.cpp:119-162) ------------------------------------
+    def profile(self, prefill_len: int, decode_len: int, seed: int = 12345) -> Tuple[float, float]:
+        """One request of random ids: milliseconds for the prompt, and for ``decode_len - 1`` decode steps."""
+        g = torch.Generator().manual_seed(seed)
+        vocab = self.core.spec.vocab_size
+        lo, hi = (100, vocab - 100) if vocab > 300 else (0, vocab)
+        ids = torch.randint(lo, hi, (prefill_len,), generator=g).tolist()
+        rid = ("profile", time.perf_counter_ns())
+        start, mid, end = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        out = torch.empty(1, dtype=torch.int32, device=self.core.device)
+        try:
+            torch.cuda.synchronize()
+            start.record()
+            logits = self.core.step([StepEntry(rid, ids, [prefill_len - 1])])
+            from .. import ops
+            ops.argmax(logits, out)
+            tok = int(out.item())
+            mid.record()
+            for _ in range(decode_len - 1):
+                logits = self.core.step([StepEntry(rid, [tok], [0])])
+                ops.argmax(logits, out)
+                tok = int(out.item())
+            end.record()
+            torch.cuda.synchronize()
+        finally:
+            self.core.end(rid)
+        return start.elapsed_time(mid), mid.elapsed_time(end)
+
+    def cache_stats(self) -> dict:
+        c = self.core.cache
+        return {"page_size": c.page_size, "pages_per_group": c.num_pages, "free_pages": c.free_pages(),
+                "live_requests": c.num_live, "groups": len(c.groups), "preemptions": self.scheduler.num_preemptions}

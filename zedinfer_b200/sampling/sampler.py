@@ -1,0 +1,69 @@
+"""Token choice for the rows of a step: greedy, or temperature with top-k / top-p and a
+repetition penalty on the tokens generated so far (src/frontend/sampler/sampler.cpp:195-318).
+
+Everything runs in the CUDA kernels of ``csrc/sampling.cu``; one device-to-host copy brings the
+chosen tokens back.  The reference draws from one generator shared by all requests
+(src/zedinfer/scheduler.cpp:576-601), so its draws depend on what else is in the batch; here the
+uniform number of a draw is a function of (request seed, index of the generated token) alone.
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+
+_MASK = (1 << 64) - 1
+
+
+def _splitmix64(x: int) -> int:
+    x = (x + 0x9E3779B97F4A7C15) & _MASK
+    z = x
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _MASK
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _MASK
+    return z ^ (z >> 31)
+
+
+def uniform_for(seed: int, index: int) -> float:
+    """A number in [0, 1) with 24 random bits, from (seed, index)."""
+    z = _splitmix64(_splitmix64(seed & _MASK) ^ ((index + 1) * 0xD1342543DE82EF95 & _MASK))
+    return (z >> 40) / float(1 << 24)
+
+
+def fresh_seed() -> int:
+    return int.from_bytes(os.urandom(8), "little") | 1
+
+
+class Sampler:
+    def __init__(self, device: torch.device):
+        self.device = device
+
+    def sample(self, logits: torch.Tensor, requests: Sequence) -> List[int]:
+        """One token per row of ``logits`` (float32 ``[rows, vocab]``); ``requests[i]`` gives row i's options."""
+        rows = logits.shape[0]
+        if rows != len(requests):
+            raise ValueError(f"{rows} rows of logits for {len(requests)} requests")
+        out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        if all(r.config.use_argmax for r in requests):
+            ops.argmax(logits, out)
+            return out.cpu().tolist()
+        par = np.zeros((4, rows), dtype=np.float32)      # temperature, top_p, uniform, top_k (as int bits)
+        top_k = np.zeros(rows, dtype=np.int32)
+        for i, r in enumerate(requests):
+            c = r.config
+            if c.use_argmax:
+                par[0, i], par[1, i] = 0.0, 1.0
+                continue
+            par[0, i], par[1, i] = c.temperature, c.top_p
+            par[2, i] = uniform_for(r.sample_seed, len(r.output_ids))
+            top_k[i] = c.top_k
+            if c.repetition_penalty != 1.0 and r.output_ids:
+                recent = torch.tensor(r.output_ids, dtype=torch.int32).to(self.device, non_blocking=True)
+                ops.repetition_penalty(logits[i], recent, c.repetition_penalty)
+        fl = torch.from_numpy(par[:3].copy()).to(self.device, non_blocking=True)
+        tk = torch.from_numpy(top_k).to(self.device, non_blocking=True)
+        ops.sample(logits, out, fl[0], tk, fl[1], fl[2])
+        return out.cpu().tolist()
