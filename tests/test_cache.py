@@ -1,0 +1,157 @@
+"""The cache manager on the host: no page lost, held twice or freed twice, under random orders of requests;
+groups with a window give pages back as the window passes them; state slots."""
+import random
+
+import pytest
+import torch
+
+from zedinfer_b200.cache import (CacheManager, OutOfPages, PagedKVNeed, PagePool, StateNeed, StateSlotPool)
+
+
+def test_pool_is_lifo_and_guards_misuse():
+    p = PagePool(4)
+    a, b = p.allocate(), p.allocate()
+    assert (a, b) == (0, 1) and p.num_free == 2 and p.num_used == 2
+    p.free(a)
+    assert p.allocate() == a                      # the page just given back is handed out next
+    with pytest.raises(ValueError, match="twice"):
+        p.free(3)                                 # never handed out
+    p.free(b)
+    with pytest.raises(ValueError, match="twice"):
+        p.free(b)
+    with pytest.raises(ValueError, match="not of this pool"):
+        p.free(9)
+    p.allocate_many(3)
+    with pytest.raises(OutOfPages):
+        p.allocate()
+    with pytest.raises(OutOfPages):
+        p.allocate_many(1)
+    p.check()
+
+
+def test_state_slots():
+    s = StateSlotPool(2)
+    a, b = s.acquire_slot(), s.acquire_slot()
+    assert s.num_free_slots == 0
+    with pytest.raises(OutOfPages):
+        s.acquire_slot()
+    s.release_slot(a)
+    with pytest.raises(ValueError):
+        s.release_slot(a)
+    assert s.acquire_slot() == a
+    s.check()
+    assert StateSlotPool(0).num_free_slots == 0
+
+
+def manager(page_size=4, pages=16, window=None, max_requests=4):
+    needs = [(0, PagedKVNeed(2, 16, None)), (1, PagedKVNeed(2, 16, window)), (2, PagedKVNeed(2, 16, None))]
+    m = CacheManager(needs, page_size, max_requests=max_requests)
+    m.set_num_pages(pages)
+    return m
+
+
+def test_groups_follow_page_shape_and_window():
+    m = manager(window=None)
+    assert len(m.groups) == 1 and m.groups[0].calls == [0, 1, 2]
+    m = manager(window=8)
+    assert len(m.groups) == 2 and m.groups[0].calls == [0, 2] and m.groups[1].calls == [1]
+    v0, v1 = m.view_for_call(0), m.view_for_call(1)
+    assert (v0.group, v1.group) == (0, 1) and v1.window == 8 and v0.window is None
+    assert v0.page_stride == 2 * 2 * 2 * 4 * 16 and v0.kv_stride == 2 * 4 * 16
+    assert m.view_for_call(7).kind == "none"
+
+
+def test_ensure_is_all_or_nothing_and_close_returns_everything():
+    m = manager(pages=5, window=8)
+    a = m.open("a")
+    m.ensure(a, 10)                               # 3 pages in each group
+    assert [len(t) for t in a.tables] == [3, 3] and m.free_pages() == [2, 2]
+    b = m.open("b")
+    with pytest.raises(OutOfPages):
+        m.ensure(b, 9)                            # would need 3
+    assert b.tables == [[], []] and m.free_pages() == [2, 2]
+    m.ensure(b, 8)
+    m.check()
+    assert m.pages_needed(a, 13) == [1, 1] and not m.can_ensure(a, 13)
+    m.close(a)
+    assert m.free_pages() == [3, 3] and m.can_ensure(b, 13)
+    with pytest.raises(ValueError, match="twice"):
+        m.close(a)
+    with pytest.raises(RuntimeError, match="closed"):
+        m.ensure(a, 4)
+    m.close(b)
+    assert m.free_pages() == [5, 5] and m.num_live == 0
+    m.check()
+
+
+def test_window_gives_pages_back_as_it_passes():
+    m = manager(page_size=4, pages=32, window=6)
+    r = m.open("r")
+    m.ensure(r, 20)
+    m.commit(r, 20)
+    # the next query sits at position >= 20 and reads keys from 15 on: blocks 0..2 (tokens 0..11) are dead
+    assert r.tables[1][:3] == [-1, -1, -1] and all(p >= 0 for p in r.tables[1][3:])
+    assert all(p >= 0 for p in r.tables[0])                       # the full-attention group keeps everything
+    assert m.free_pages() == [32 - 5, 32 - 2]
+    m.ensure(r, 21)
+    m.commit(r, 21)                                               # first needed token 16 -> block 3 now dead too
+    assert r.tables[1][:4] == [-1] * 4 and len(r.tables[1]) == 6
+    m.check()
+    m.close(r)
+    assert m.free_pages() == [32, 32]
+
+
+def test_state_slots_limit_admission():
+    needs = [(0, PagedKVNeed(1, 16, None)), (1, StateNeed((3, 5)))]
+    m = CacheManager(needs, 4, max_requests=2)
+    m.set_num_pages(8)
+    a, b = m.open("a"), m.open("b")
+    assert {a.slot, b.slot} == {0, 1} and not m.can_open()
+    with pytest.raises(OutOfPages):
+        m.open("c")
+    slot_of_a = a.slot
+    m.close(a)
+    assert m.can_open() and m.open("c").slot == slot_of_a
+    assert m.view_for_call(1).kind == "state"
+    with pytest.raises(ValueError, match="already live"):
+        m.open("c")
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_never_lose_or_share_a_page(seed):
+    rng = random.Random(seed)
+    m = manager(page_size=rng.choice([2, 4, 8]), pages=rng.choice([6, 13, 40]), window=rng.choice([None, 5, 17]),
+                max_requests=5)
+    live = {}
+    next_id = 0
+    for _ in range(600):
+        op = rng.random()
+        if op < 0.25 and len(live) < 5:
+            live[next_id] = m.open(next_id)
+            next_id += 1
+        elif op < 0.8 and live:
+            rc = live[rng.choice(list(live))]
+            new_len = rc.length + rng.choice([1, 1, 1, 2, 5, 9, 23])
+            try:
+                m.ensure(rc, new_len)
+                m.commit(rc, new_len)
+            except OutOfPages:
+                before = [list(t) for t in rc.tables]
+                assert before == rc.tables
+        elif live:
+            rid = rng.choice(list(live))
+            m.close(live.pop(rid))
+        m.check()
+        for g in m.groups:
+            assert g.pool.num_free + g.pool.num_used == g.pool.num_pages
+    for rc in live.values():
+        m.close(rc)
+    m.check()
+    assert all(g.pool.num_used == 0 for g in m.groups) and m.num_live == 0
+
+
+def test_budget_to_pages():
+    m = CacheManager([(i, PagedKVNeed(2, 128, None)) for i in range(28)], 16)
+    per_page = 28 * 2 * 2 * 16 * 128 * 2
+    assert m.bytes_per_page_all_groups(torch.bfloat16) == per_page
+    assert m.pages_for_budget(per_page * 101, torch.bfloat16) == 100      # one page is the scratch page

@@ -1,0 +1,183 @@
+"""The scheduler's decisions, on the host, with made-up tokens in place of a model
+(the reference tests its scheduler the same way, tests/zedinfer/test_scheduler_sampling.cpp:64-170)."""
+import pytest
+
+from zedinfer_b200.cache import CacheManager, PagedKVNeed
+from zedinfer_b200.config import GenerationConfig, SchedulerConfig
+from zedinfer_b200.engine.request import InferenceRequest, RequestPhase
+from zedinfer_b200.engine.scheduler import Scheduler
+
+
+def make(pages=64, page_size=4, max_seq_len=256, stop=(), **kw):
+    cache = CacheManager([(0, PagedKVNeed(1, 16, None)), (1, PagedKVNeed(1, 16, None))], page_size,
+                         max_requests=kw.get("max_batch_requests", 64))
+    cache.set_num_pages(pages)
+    cfg = SchedulerConfig(kv_block_size=page_size, **kw)
+    return Scheduler(cfg, cache, max_seq_len, stop), cache
+
+
+def req(n, max_new=4, **kw):
+    return InferenceRequest(list(range(1, n + 1)), GenerationConfig(max_new_tokens=max_new, **kw))
+
+
+def run_step(s, cache, token=7):
+    """Pretend to be the step function: commit the lengths, hand back one token per wanted row."""
+    batch = s.schedule()
+    for r in batch.decode_requests:
+        cache.commit(r.cache, r.cache.length + 1)
+    for r, size in zip(batch.prefill_requests, batch.prefill_chunk_sizes):
+        cache.commit(r.cache, r.cache.length + size)
+    tokens = [token(r) if callable(token) else token for r, _ in batch.rows_wanted()]
+    done = s.process_results(batch, tokens)
+    cache.check()
+    return batch, done
+
+
+def test_prompt_is_cut_into_portions_and_blocks_the_queue():
+    s, cache = make(max_prefill_tokens=8, max_batch_tokens=64)
+    a, b = req(20), req(5)
+    s.submit(a), s.submit(b)
+    batch, _ = run_step(s, cache)
+    assert batch.prefill_requests == [a] and batch.prefill_chunk_starts == [0] and batch.prefill_chunk_sizes == [8]
+    assert batch.rows_wanted() == [] and a.phase == RequestPhase.PREFILL
+    batch, _ = run_step(s, cache)
+    assert batch.prefill_chunk_starts == [8] and batch.prefill_chunk_sizes == [8]
+    batch, _ = run_step(s, cache)                       # a's last 4 tokens, and b beside them under the budget
+    assert batch.prefill_requests == [a, b] and batch.prefill_chunk_sizes == [4, 4]
+    assert [r for r, _ in batch.rows_wanted()] == [a] and a.output_ids == [7] and a.phase == RequestPhase.DECODE
+    batch, _ = run_step(s, cache)                       # decode first, then the rest of b
+    assert batch.decode_requests == [a] and batch.prefill_requests == [b] and batch.prefill_chunk_sizes == [1]
+    assert [r for r, _ in batch.rows_wanted()] == [a, b]
+    assert a.output_ids == [7, 7] and b.output_ids == [7]
+
+
+def test_token_budget_covers_decode_and_prefill():
+    s, cache = make(max_batch_tokens=6, max_prefill_tokens=512)
+    rs = [req(3, max_new=50) for _ in range(4)]
+    for r in rs:
+        s.submit(r)
+    batch, _ = run_step(s, cache)
+    assert batch.num_tokens() == 6 and batch.prefill_chunk_sizes == [3, 3]
+    batch, _ = run_step(s, cache)
+    assert len(batch.decode_requests) == 2 and batch.prefill_chunk_sizes == [3, 1] and batch.num_tokens() == 6
+
+
+def test_finishing_by_stop_token_length_and_cancel():
+    s, cache = make(stop=(99,))
+    a, b, c, d = req(3, max_new=3), req(3, max_new=10), req(3, max_new=10, ignore_eos=True), req(3, max_new=10)
+    for r in (a, b, c, d):
+        s.submit(r)
+    run_step(s, cache, token=lambda r: 99 if r in (b, c) else 5)
+    assert b.phase == RequestPhase.COMPLETE and b.finish_reason == "stop" and b.output_ids == [99] and b.cache is None
+    assert c.phase == RequestPhase.DECODE
+    s.cancel(d)
+    run_step(s, cache, token=5)
+    assert d.finish_reason == "cancelled"
+    run_step(s, cache, token=5)
+    assert a.finish_reason == "length" and a.output_ids == [5, 5, 5]
+    assert cache.num_live == 1                      # only c is left
+
+
+def test_max_new_tokens_of_one():
+    s, cache = make()
+    a = req(5, max_new=1)
+    s.submit(a)
+    _, done = run_step(s, cache)
+    assert done == [a] and a.finish_reason == "length" and a.output_ids == [7] and not s.has_work()
+    assert cache.free_pages() == [64]
+
+
+def test_request_that_can_never_fit_fails_instead_of_waiting():
+    s, cache = make(pages=4, page_size=4)
+    big = req(40)
+    s.submit(big)
+    batch = s.schedule()
+    assert batch.empty() and big.phase == RequestPhase.COMPLETE and big.finish_reason == "error"
+    assert "Cannot admit" in big.error and not s.has_work()
+
+
+def test_admission_waits_while_others_can_free_pages():
+    s, cache = make(pages=6, page_size=4)
+    a, b = req(16, max_new=2), req(16, max_new=2)
+    s.submit(a), s.submit(b)
+    batch, _ = run_step(s, cache)
+    assert batch.prefill_requests == [a]            # b does not fit beside a (4 + 4 pages > 6)
+    assert b.phase == RequestPhase.WAITING and b.error is None
+    run_step(s, cache)                              # a decodes and finishes by length
+    assert a.finish_reason == "length"
+    batch, _ = run_step(s, cache)
+    assert batch.prefill_requests == [b]
+
+
+def test_pages_run_out_during_decode_fail_policy():
+    s, cache = make(pages=4, page_size=4, on_exhaust="fail")
+    a, b = req(7, max_new=50), req(8, max_new=50)
+    s.submit(a), s.submit(b)
+    run_step(s, cache)                              # both prompts in: 2 + 2 pages, a has one free slot, b none
+    batch, _ = run_step(s, cache)
+    assert batch.decode_requests == [a]
+    assert b.finish_reason == "error" and "KV cache exhausted during decode" in b.error
+    assert a.phase == RequestPhase.DECODE and cache.num_live == 1
+
+
+def test_pages_run_out_during_decode_preempts_the_youngest():
+    s, cache = make(pages=4, page_size=4, on_exhaust="preempt")
+    a, b = req(7, max_new=6), req(8, max_new=6)
+    s.submit(a), s.submit(b)
+    run_step(s, cache)
+    batch, _ = run_step(s, cache)                   # b (the youngest) is taken off, a goes on
+    assert batch.decode_requests == [a] and b.phase == RequestPhase.WAITING and b.cache is None
+    assert b.stats.preemptions == 1 and s.waiting[0] is b and b.output_ids == [7]
+    assert cache.free_pages() == [2]
+    while a.phase != RequestPhase.COMPLETE:
+        run_step(s, cache)
+    # b comes back with prompt + generated as its sequence and finishes with all its tokens
+    while s.has_work():
+        batch, _ = run_step(s, cache)
+    assert b.finish_reason == "length" and len(b.output_ids) == 6 and a.finish_reason == "length"
+    assert cache.free_pages() == [4] and cache.num_live == 0
+
+
+def test_the_only_request_preempts_itself_and_then_fails_for_good():
+    s, cache = make(pages=2, page_size=4, on_exhaust="preempt")
+    a = req(8, max_new=5)
+    s.submit(a)
+    run_step(s, cache)
+    batch = s.schedule()                            # needs a third page: preempted, then can never fit again
+    assert batch.empty() and a.finish_reason == "error" and a.stats.preemptions == 1
+    assert cache.free_pages() == [2]
+
+
+def test_queue_full_and_request_limit():
+    s, cache = make(max_queue_size=2, max_batch_requests=1)
+    s.submit(req(3)), s.submit(req(3))
+    with pytest.raises(RuntimeError, match="Queue full"):
+        s.submit(req(3))
+    batch, _ = run_step(s, cache)
+    assert len(batch.prefill_requests) == 1
+    batch, _ = run_step(s, cache)
+    assert len(batch.decode_requests) == 1 and batch.prefill_requests == []     # one live request at a time
+    with pytest.raises(ValueError, match="at least one prompt token"):
+        s.submit(InferenceRequest([]))
+    with pytest.raises(ValueError, match="no room"):
+        s.submit(req(256))
+
+
+def test_generation_reserve_is_taken_at_admission():
+    s, cache = make(pages=8, page_size=4, generation_reserve=256)
+    a = req(6, max_new=9)
+    s.submit(a)
+    s.schedule()
+    assert cache.free_pages() == [8 - 4]            # ceil((6 + 9) / 4)
+
+
+def test_failed_step_fails_its_requests_and_serving_goes_on():
+    s, cache = make()
+    a, b = req(3), req(3)
+    s.submit(a)
+    batch = s.schedule()
+    s.fail_batch(batch, "step failed: boom")
+    assert a.finish_reason == "error" and "boom" in a.error and cache.num_live == 0
+    s.submit(b)
+    _, _ = run_step(s, cache)
+    assert b.output_ids == [7]

@@ -235,3 +235,19 @@ ZI_EXPORT int zi_sample(const float* logits, int* out, const float* temperature,
     sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, out, temperature, top_k, top_p, uniform, vocab, row_stride);
     return zi_check_launch("sample");
 }
+
+// Hand-over between decode steps that run back to back on the device: the chosen token becomes
+// the next input and every position moves on by one.
+__global__ void advance_decode_kernel(int* __restrict__ ids, int* __restrict__ pos, const int* __restrict__ sampled, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        ids[i] = sampled[i];
+        pos[i] += 1;
+    }
+}
+
+ZI_EXPORT int zi_advance_decode(int* ids, int* pos, const int* sampled, int n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    advance_decode_kernel<<<(n + 127) / 128, 128, 0, stream>>>(ids, pos, sampled, n);
+    return zi_check_launch("advance_decode");
+}

@@ -48,6 +48,23 @@ def require_gpu(device) -> torch.device:
     return dev
 
 
+def _random_tensors_on_device(specs, seed: int, dtype: torch.dtype, device) -> Dict[str, torch.Tensor]:
+    """Random weights drawn on the device by each tensor's init rule (see weights/random_init.py)."""
+    gen = torch.Generator(device=device)
+    out: Dict[str, torch.Tensor] = {}
+    for i, name in enumerate(sorted(specs)):
+        spec = specs[name]
+        if spec.optional:
+            continue
+        gen.manual_seed((seed * 1000003 + i) & 0x7fffffffffff)
+        rule, std = spec.init
+        t = torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device) * std
+        if rule == "one_plus_normal":
+            t += 1.0
+        out[name] = t.to(dtype)
+    return out
+
+
 class _PinnedRing:
     """A few pinned staging buffers; a buffer is reused only after the copy out of it has finished."""
 
@@ -55,6 +72,24 @@ class _PinnedRing:
         self.bufs: List[Optional[torch.Tensor]] = [None] * n
         self.events: List[Optional[torch.cuda.Event]] = [None] * n
         self.i = 0
+        self.bytes_staged = 0
+
+    def stage_into(self, host: np.ndarray, dst: torch.Tensor) -> None:
+        """Copy ``host`` into the device tensor ``dst`` (same length) through a pinned buffer."""
+        i = self.i
+        self.i = (i + 1) % len(self.bufs)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        buf = self.bufs[i]
+        if buf is None or buf.numel() < host.size:
+            buf = torch.empty(max(host.size, 4096), dtype=torch.int32).pin_memory()
+            self.bufs[i] = buf
+        buf[:host.size].numpy()[:] = host
+        self.bytes_staged += host.size * 4
+        dst.copy_(buf[:host.size], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
 
     def stage(self, host: np.ndarray, device: torch.device) -> torch.Tensor:
         i = self.i
@@ -66,6 +101,7 @@ class _PinnedRing:
             buf = torch.empty(max(host.size, 4096), dtype=torch.int32).pin_memory()
             self.bufs[i] = buf
         buf[:host.size].numpy()[:] = host
+        self.bytes_staged += host.size * 4
         dev = torch.empty(host.size, dtype=torch.int32, device=device)
         dev.copy_(buf[:host.size], non_blocking=True)
         ev = torch.cuda.Event()
@@ -75,17 +111,32 @@ class _PinnedRing:
 
 
 class EngineCore:
-    def __init__(self, model_dir: str, dtype="bfloat16", *, page_size: int = 16, num_pages: Optional[int] = None,
-                 max_tokens: Optional[int] = None, gpu_memory_utilization: float = 0.9, max_requests: int = 64,
-                 max_seq_len: Optional[int] = None, device="cuda:0"):
+    def __init__(self, model_dir: Optional[str], dtype="bfloat16", *, page_size: int = 16,
+                 num_pages: Optional[int] = None, max_tokens: Optional[int] = None,
+                 gpu_memory_utilization: float = 0.9, max_requests: int = 64, max_seq_len: Optional[int] = None,
+                 device="cuda:0", cuda_graphs: bool = False, config: Optional[dict] = None,
+                 random_seed: Optional[int] = None):
         """``num_pages``: pages per cache group; ``max_tokens``: size the pool for that many cached tokens
-        instead; neither: whatever ``gpu_memory_utilization`` of the device leaves after the weights."""
+        instead; neither: whatever ``gpu_memory_utilization`` of the device leaves after the weights.
+
+        ``model_dir=None`` with ``config`` (a config.json dict) and ``random_seed`` builds the model with
+        random weights drawn on the device, without a folder (benchmarks of large shapes)."""
         self.device = require_gpu(device)
         self.dtype = parse_dtype(dtype)
         torch.cuda.set_device(self.device)
-        self.arch, self.config, self.spec = load_model_config(model_dir)
-        self.model = Model(self.spec)
-        tensors = load_weights(model_dir, self.model.tensor_specs(), self.dtype, self.device)
+        if model_dir is not None:
+            self.arch, self.config, self.spec = load_model_config(model_dir)
+            self.model = Model(self.spec)
+            tensors = load_weights(model_dir, self.model.tensor_specs(), self.dtype, self.device)
+        else:
+            if config is None or random_seed is None:
+                raise ValueError("without a model folder, give config= and random_seed=")
+            from ..config.registry import resolve_architecture
+            self.arch = resolve_architecture(config)
+            self.config = self.arch.parse(config)
+            self.spec = self.arch.build_spec(self.config)
+            self.model = Model(self.spec)
+            tensors = _random_tensors_on_device(self.model.tensor_specs(), random_seed, self.dtype, self.device)
         self.model.bind(tensors, self.dtype, self.device)
         del tensors
         self.page_size = int(page_size)
@@ -109,6 +160,9 @@ class EngineCore:
         self.views = {call: self.cache.view_for_call(call) for call, _ in self.model.cache_needs()}
         self.table_width = max(1, (self.max_seq_len + self.page_size - 1) // self.page_size)
         self._ring = _PinnedRing()
+        self.cuda_graphs = bool(cuda_graphs)
+        self.max_requests = int(max_requests)
+        self._decode_graphs: Dict[int, "DecodeGraph"] = {}
 
     @staticmethod
     def kernel_libraries(dtype) -> List[str]:
@@ -216,13 +270,30 @@ class EngineCore:
             raise
         return rcs
 
+    def decode_graph(self, n: int) -> "DecodeGraph":
+        """The captured decode step for ``n`` requests (bucket: the next power of two)."""
+        from .decode_graph import DecodeGraph
+        bucket = 1
+        while bucket < n:
+            bucket *= 2
+        bucket = min(bucket, max(self.max_requests, n))
+        g = self._decode_graphs.get(bucket)
+        if g is None:
+            g = DecodeGraph(self, bucket)
+            self._decode_graphs[bucket] = g
+        return g
+
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one batch; returns float32 logits ``[wanted, vocab]`` on the device, or None if nothing is wanted."""
         if not entries:
             return None
         rcs = self.prepare(entries)
-        ctx, want = self.build_context(entries, rcs)
-        logits = self.model.forward(ctx, self.views, want)
+        if (self.cuda_graphs and len(entries) <= self.max_requests
+                and all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries)):
+            logits = self.decode_graph(len(entries)).run(entries, rcs)
+        else:
+            ctx, want = self.build_context(entries, rcs)
+            logits = self.model.forward(ctx, self.views, want)
         for e, rc in zip(entries, rcs):
             self.cache.commit(rc, rc.length + len(e.tokens))
         return logits

@@ -1,0 +1,117 @@
+"""A decode-only step captured as a CUDA graph.
+
+A decode step launches a few hundred small kernels; issued one by one from the host they take
+longer to launch than to run.  For every batch-size bucket the step is captured once over static
+device buffers (token ids, positions, block tables) and replayed: the host then only refreshes
+the buffers.  Requests missing from a bucket are padded with tokens that sit at position 0 of the
+cache's scratch page, which nothing reads.  The captured work is the same ``Model.forward`` that
+runs eagerly, so the two paths cannot drift apart.
+
+``loop=True`` also captures the greedy choice and the hand-over of the chosen token to the next
+step (ids := argmax, positions += 1), so that steps can be replayed back to back without the host;
+the benchmark uses this to time the device alone.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..parts.base import StepContext
+
+
+class DecodeGraph:
+    def __init__(self, core, bucket: int, loop: bool = False):
+        self.core, self.bucket, self.loop = core, bucket, loop
+        b, width, ng = bucket, core.table_width, len(core.cache.groups)
+        self.off_ids, self.off_pos, self.off_seg, self.off_want, self.off_slots = 0, b, 2 * b, 3 * b, 4 * b
+        self.off_tab = 5 * b
+        total = self.off_tab + ng * b * width
+        self.host = np.zeros(total, dtype=np.int32)
+        self.host[self.off_seg: self.off_seg + b] = np.arange(b)
+        self.host[self.off_want: self.off_want + b] = np.arange(b)
+        self._pad_rows(0)
+        self.dev = torch.zeros(total, dtype=torch.int32, device=core.device)
+        core._ring.stage_into(self.host, self.dev)
+        self._uploaded = self.host.copy()
+        d = self.dev
+        tables = [d[self.off_tab + g * b * width: self.off_tab + (g + 1) * b * width].view(b, width) for g in range(ng)]
+        self.ctx = StepContext(
+            n_tokens=b, n_segments=b, dtype=core.dtype, device=core.device,
+            token_ids=d[self.off_ids: self.off_ids + b], positions=d[self.off_pos: self.off_pos + b],
+            tok_seg=d[self.off_seg: self.off_seg + b], tables=tables, slots=d[self.off_slots: self.off_slots + b],
+            seg_start_host=list(range(b)), seg_len_host=[1] * b, seg_pos0_host=[0] * b, slots_host=[-1] * b,
+            decode_only=True, max_kv_len=core.max_seq_len)
+        self.want = d[self.off_want: self.off_want + b]
+        self.sampled = torch.zeros(b, dtype=torch.int32, device=core.device)
+        self.launches = 0
+        # warm up on a side stream (loads the libraries, lets cuBLAS pick its kernels), then capture
+        side = torch.cuda.Stream(device=core.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self._body()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        from ..ops import _lib
+        before = _lib.launch_count()
+        with torch.cuda.graph(self.graph):
+            self.logits = self._body()
+        self.launches = _lib.launch_count() - before
+
+    def _body(self) -> torch.Tensor:
+        logits = self.core.model.forward(self.ctx, self.core.views, self.want)
+        if self.loop:
+            ops.argmax(logits, self.sampled)
+            ops.advance_decode(self.ctx.token_ids, self.ctx.positions, self.sampled)
+        return logits
+
+    def _pad_rows(self, first: int) -> None:
+        b, width, ng = self.bucket, self.core.table_width, len(self.core.cache.groups)
+        scratch = self.core.cache.scratch_page if ng else 0
+        h = self.host
+        h[self.off_ids + first: self.off_ids + b] = 0
+        h[self.off_pos + first: self.off_pos + b] = 0
+        h[self.off_slots + first: self.off_slots + b] = -1
+        for g in range(ng):
+            base = self.off_tab + g * b * width
+            rows = h[base: base + b * width].reshape(b, width)
+            rows[first:, :] = 0
+            rows[first:, 0] = scratch
+
+    def fill(self, tokens: Sequence[int], rcs: Sequence, reserve_ahead: int = 0) -> None:
+        """Refresh the static buffers for these requests (one token each) and upload what changed."""
+        n = len(rcs)
+        b, width, ng = self.bucket, self.core.table_width, len(self.core.cache.groups)
+        h = self.host
+        vocab = self.core.spec.vocab_size
+        for i, (tok, rc) in enumerate(zip(tokens, rcs)):
+            if not 0 <= tok < vocab:
+                raise ValueError(f"request {rc.request_id!r}: token id outside [0, {vocab})")
+            h[self.off_ids + i] = tok
+            h[self.off_pos + i] = rc.length
+            h[self.off_slots + i] = rc.slot
+            for g in range(ng):
+                tab = rc.tables[g]
+                base = self.off_tab + (g * b + i) * width
+                h[base: base + len(tab)] = tab
+                h[base + len(tab): base + width] = 0
+        self._pad_rows(n)
+        head = self.off_seg                                   # ids and positions change every step
+        if np.array_equal(h[head:], self._uploaded[head:]):
+            self.core._ring.stage_into(h[:head], self.dev[:head])
+            self._uploaded[:head] = h[:head]
+        else:
+            self.core._ring.stage_into(h, self.dev)
+            self._uploaded[:] = h
+
+    def run(self, entries: Sequence, rcs: Sequence) -> torch.Tensor:
+        self.fill([e.tokens[0] for e in entries], rcs)
+        self.graph.replay()
+        return self.logits[:len(entries)]
+
+    def replay(self) -> None:
+        self.graph.replay()

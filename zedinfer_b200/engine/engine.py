@@ -40,6 +40,7 @@ class InferenceEngine:
     def __init__(self, core: EngineCore, scheduler_config: SchedulerConfig):
         self.core = core
         self.scheduler_config = scheduler_config
+        core.cuda_graphs = bool(scheduler_config.cuda_graphs)
         self.scheduler = Scheduler(scheduler_config, core.cache, core.max_seq_len, core.spec.eos_token_ids)
         self.sampler = Sampler(core.device)
         self.steps_run = 0
@@ -88,9 +89,10 @@ class InferenceEngine:
 
     def entries_for(self, batch: ScheduledBatch) -> List[StepEntry]:
         entries = [StepEntry(r.request_id, [r.output_ids[-1]], [0]) for r in batch.decode_requests]
-        for r, start, size in zip(batch.prefill_requests, batch.prefill_chunk_starts, batch.prefill_chunk_sizes):
+        for r, start, size, completes in zip(batch.prefill_requests, batch.prefill_chunk_starts,
+                                             batch.prefill_chunk_sizes, batch.prefill_completes):
             seq = r.sequence()
-            want = [size - 1] if start + size >= len(seq) else []
+            want = [size - 1] if completes else []
             entries.append(StepEntry(r.request_id, seq[start:start + size], want))
         return entries
 

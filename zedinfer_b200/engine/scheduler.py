@@ -40,6 +40,7 @@ class ScheduledBatch:
     prefill_requests: List[InferenceRequest] = field(default_factory=list)
     prefill_chunk_starts: List[int] = field(default_factory=list)
     prefill_chunk_sizes: List[int] = field(default_factory=list)
+    prefill_completes: List[bool] = field(default_factory=list)     # this portion ends the request's sequence
 
     def empty(self) -> bool:
         return not self.decode_requests and not self.prefill_requests
@@ -50,8 +51,8 @@ class ScheduledBatch:
     def rows_wanted(self) -> List[Tuple[InferenceRequest, bool]]:
         """(request, is_prefill) for each logits row the step returns, in order."""
         rows = [(r, False) for r in self.decode_requests]
-        for r, start, size in zip(self.prefill_requests, self.prefill_chunk_starts, self.prefill_chunk_sizes):
-            if start + size >= len(r.sequence()):
+        for r, completes in zip(self.prefill_requests, self.prefill_completes):
+            if completes:
                 rows.append((r, True))
         return rows
 
@@ -189,6 +190,7 @@ class Scheduler:
                 batch.prefill_requests.append(req)
                 batch.prefill_chunk_starts.append(req.prefill_progress)
                 batch.prefill_chunk_sizes.append(chunk)
+                batch.prefill_completes.append(req.prefill_progress + chunk >= seq_len)
                 prefill_budget -= chunk
                 req.phase = RequestPhase.PREFILL
                 if req.prefill_progress + chunk >= seq_len:

@@ -21,7 +21,7 @@ _attention_generic = Library("attention_generic")
 _sampling = Library("sampling")
 
 __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "silu_mul", "cast",
-           "gemm_nt", "linear", "paged_attention", "attention", "argmax", "sample", "repetition_penalty"]
+           "gemm_nt", "linear", "paged_attention", "attention", "argmax", "sample", "repetition_penalty", "advance_decode"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
@@ -205,6 +205,13 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: torch.Tensor, t
         raise KernelError("sample: top_k and out need one entry per row")
     _sampling.call("zi_sample", ptr(logits), ptr(out), ptr(temperature), ptr(top_k), ptr(top_p), ptr(uniform),
                    c_int(rows), c_int(logits.shape[1]), c_ll(logits.stride(0)), stream())
+
+
+def advance_decode(ids: torch.Tensor, pos: torch.Tensor, sampled: torch.Tensor) -> None:
+    """Hand the chosen tokens to the next decode step: ``ids := sampled``, ``pos += 1``."""
+    need_cuda(ids, pos, sampled)
+    need_int32("ids", ids), need_int32("pos", pos), need_int32("sampled", sampled)
+    _sampling.call("zi_advance_decode", ptr(ids), ptr(pos), ptr(sampled), c_int(ids.numel()), stream())
 
 
 def repetition_penalty(logits_row: torch.Tensor, tokens: torch.Tensor, penalty: float) -> None:

@@ -50,6 +50,14 @@ def need_int32(name: str, t: torch.Tensor) -> None:
         raise KernelError(f"{name} must be int32, got {t.dtype}")
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernel entry points of this package have been called (each launches one kernel)."""
+    return _launches
+
+
 class Library:
     """A lazily compiled and loaded kernel library; ``call`` raises on a non-zero return."""
 
@@ -64,6 +72,8 @@ class Library:
         return self._lib
 
     def call(self, fn_name: str, *args) -> None:
+        global _launches
+        _launches += 1
         rc = getattr(self.lib, fn_name)(*args)
         if rc != 0:
             raise KernelError(f"{fn_name}: {build.last_error(self.name)}")
