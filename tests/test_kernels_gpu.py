@@ -269,3 +269,100 @@ def test_repetition_penalty():
     d = row.to(dev())
     ops.repetition_penalty(d, torch.tensor([0, 1, 9, 3], dtype=torch.int32, device=dev()), 2.0)
     assert torch.allclose(d.cpu(), torch.tensor([1.0, -2.0, 0.5, 2.0, -3.0]))
+
+
+# ---- tensor-core attention (bfloat16, head_dim 64 / 128) -------------------------------------------------
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(12, 2, 128, 16, None), (7, 1, 64, 4, None), (20, 1, 128, 16, None),
+                                                  (4, 4, 64, 24, None), (12, 2, 128, 16, 300), (6, 3, 64, 8, 70),
+                                                  (28, 4, 128, 32, None)])
+def test_decode_attention_mma(nh, nkv, hd, ps, window):
+    from zedinfer_b200 import ops
+    t = torch.bfloat16
+    lens = [1, 255, 256, 257, 700, 64, 513]          # around the chunk edges (256) and the tile edges (64)
+    pool, view, tables, ks, vs, page_stride, kv_stride = build_cache(len(lens), lens, nkv, hd, ps, t, seed=5)
+    g = torch.Generator().manual_seed(9)
+    q = torch.randn(len(lens), nh, hd, generator=g)
+    # a far key that must dominate: request 4 (700 keys) looks hard at key 3 (or at the window's first key)
+    far = 3 if not window else 699 - window + 1
+    q[4, :, :] = ks[4][far, 0][None, :] * 4.0
+    qd = q.to(t).to(dev())
+    n = len(lens)
+    pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=dev())
+    seg = torch.arange(n, dtype=torch.int32, device=dev())
+    n_chunks = -(-max(lens) // ops.DECODE_CHUNK_KEYS) + 1                   # one spare chunk, as a captured step has
+    o_part = torch.full((n * nh * n_chunks * hd,), float("nan"), device=dev())
+    ml_part = torch.full((n * nh * n_chunks * 2,), float("nan"), device=dev())
+    out = torch.empty(n, nh * hd, dtype=t, device=dev())
+    scale = 1.0 / math.sqrt(hd)
+    ops.decode_attention(qd, view, out, o_part, ml_part, tables, seg, pos, nh, nkv, hd, ps, page_stride, kv_stride,
+                         window, scale, n_chunks)
+    got = out.float().cpu().view(n, nh, hd)
+    qf = qd.float().cpu()
+    for r in range(n):
+        ref = plain_attention_rows(qf[r:r + 1], ks[r], vs[r], [lens[r] - 1], scale, window)
+        err = float((got[r:r + 1] - ref).abs().max())
+        assert err < 2e-2, (r, lens[r], err)
+    # the general kernel computes the same function
+    out2 = torch.empty_like(out)
+    ops.paged_attention(qd, view, out2, tables, seg, pos, nh, nkv, hd, ps, page_stride, kv_stride, window, scale)
+    assert float((out2.float() - out.float()).abs().max()) < 2e-2
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(12, 2, 128, 16, None), (3, 1, 64, 4, None), (5, 5, 128, 24, None),
+                                                  (6, 2, 64, 16, 50), (12, 2, 128, 16, 130)])
+def test_prefill_attention_mma(nh, nkv, hd, ps, window):
+    from zedinfer_b200 import ops
+    t = torch.bfloat16
+    lens = [200, 70, 64, 333, 1]
+    pool, view, tables, ks, vs, page_stride, kv_stride = build_cache(len(lens), lens, nkv, hd, ps, t, seed=6)
+    # portions: (request, first position, count).  Whole prompts, a portion in mid-prompt, one decoded token.
+    portions = [(0, 0, 200), (1, 60, 10), (2, 0, 64), (3, 130, 203), (4, 0, 1), ]
+    g = torch.Generator().manual_seed(4)
+    qs, pos, tiles = [], [], []
+    n = 0
+    for si, (r, p0, cnt) in enumerate(portions):
+        for q0 in range(0, cnt, 64):
+            tiles.append((n + q0, min(64, cnt - q0), si))
+        for i in range(cnt):
+            qs.append(torch.randn(nh, hd, generator=g))
+            pos.append(p0 + i)
+        n += cnt
+    q = torch.stack(qs)
+    # the last query of request 3 looks hard at one far key (or the first key inside its window)
+    far = 7 if not window else 332 - window + 1
+    q[200 + 10 + 64 + 202, :, :] = ks[3][far, 0][None, :] * 4.0
+    qd = q.to(t).to(dev())
+    seg_tables = torch.stack([tables[r] for r, _, _ in portions])
+    out = torch.empty(n, nh * hd, dtype=t, device=dev())
+    scale = 1.0 / math.sqrt(hd)
+    ops.prefill_attention(qd, view, out, seg_tables, torch.tensor(tiles, dtype=torch.int32, device=dev()),
+                          torch.tensor(pos, dtype=torch.int32, device=dev()), nh, nkv, hd, ps, page_stride, kv_stride,
+                          window, scale)
+    got = out.float().cpu().view(n, nh, hd)
+    qf = qd.float().cpu()
+    i = 0
+    for r, p0, cnt in portions:
+        ref = plain_attention_rows(qf[i:i + cnt], ks[r], vs[r], list(range(p0, p0 + cnt)), scale, window)
+        err = float((got[i:i + cnt] - ref).abs().max())
+        assert err < 2e-2, (r, p0, cnt, err)
+        i += cnt
+
+
+def test_attention_kernels_refuse_what_they_cannot_do():
+    from zedinfer_b200 import ops
+    t = torch.bfloat16
+    pool, view, tables, ks, vs, page_stride, kv_stride = build_cache(1, [10], 1, 32, 4, t)
+    q = torch.zeros(1, 2, 32, dtype=t, device=dev())
+    out = torch.empty(1, 64, dtype=t, device=dev())
+    z = torch.zeros(1, dtype=torch.int32, device=dev())
+    with pytest.raises(ops.KernelError, match="head_dim 64 or 128"):
+        ops.decode_attention(q, view, out, torch.empty(64, device=dev()), torch.empty(4, device=dev()), tables, z, z,
+                             2, 1, 32, 4, page_stride, kv_stride, None, 1.0, 1)
+    with pytest.raises(ops.KernelError, match="multiple of 8"):
+        ops.paged_attention(torch.zeros(1, 2, 12, dtype=t, device=dev()), view, torch.empty(1, 24, dtype=t, device=dev()),
+                            tables, z, z, 2, 1, 12, 4, page_stride, kv_stride, None, 1.0)
+    with pytest.raises(ops.KernelError, match="cannot share"):
+        ops.paged_attention(torch.zeros(1, 3, 32, dtype=t, device=dev()), view, torch.empty(1, 96, dtype=t, device=dev()),
+                            tables, z, z, 3, 2, 32, 4, page_stride, kv_stride, None, 1.0)
+    with pytest.raises(ops.KernelError, match="GPU only"):
+        ops.silu_mul(torch.zeros(2, 4), torch.zeros(2, 2))

@@ -1,0 +1,521 @@
+// Paged causal attention for bfloat16 on the tensor cores (mma.sync m16n8k16, float32 accumulate),
+// head_dim 64 or 128, any number of heads and groups, any page size, optional window.
+//
+//   decode  : one query token per request.  The query heads that share a key/value head form the
+//             rows of one 16-row tile, so the keys and values of a request cross the memory bus once
+//             per key/value head.  The context is cut into chunks of DEC_CHUNK keys at absolute
+//             positions (a function of constants only, never of the batch); each chunk is one thread
+//             block and leaves an un-normalised partial result, and a second kernel merges the chunks
+//             of a query in rising order.
+//   prefill : a portion of a prompt.  One thread block per (64 query rows, query head); it walks the
+//             keys from the window's start to the diagonal in tiles of 64 with an online softmax.
+//
+// Keys and values are gathered row by row through the block table with 16-byte cp.async copies
+// into shared memory (double buffered, XOR-swizzled so that ldmatrix is conflict free).  Rows
+// outside the range a query may see are zero-filled, never read: pages hold stale data beyond a
+// request's length, and pages that a window has passed may be gone.
+//
+// Cache addressing (one call's slice of the pool): element (page, kv, kvh, off, d) lives at
+//   cache + page*page_stride + kv*kv_stride + (kvh*page_size + off)*head_dim + d.
+#include "zi_common.cuh"
+
+ZI_DEFINE_LAST_ERROR(attention_mma)
+
+#define ATT_THREADS 128
+#define TILE_KEYS 64
+#define DEC_CHUNK 256
+#define LOG2E 1.4426950408889634f
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int sz = valid ? 16 : 0;                       // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(sz));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Byte offset of 16-byte chunk `c` of row `row` in a swizzled [rows][HD] bfloat16 tile.
+template <int HD> __device__ __forceinline__ uint32_t swz(int row, int c) {
+    return (uint32_t)(row * HD * 2 + ((c ^ (row & 7)) << 4));
+}
+
+struct CacheRef {
+    const bf16* base;
+    const int* table;
+    long long page_stride, kv_stride;
+    int page_size, page_shift, kvh;
+};
+
+__device__ __forceinline__ const bf16* key_row(const CacheRef& cr, int key, int hd) {
+    int blk, off;
+    if (cr.page_shift >= 0) { blk = key >> cr.page_shift; off = key & (cr.page_size - 1); }
+    else { blk = key / cr.page_size; off = key - blk * cr.page_size; }
+    const int page = cr.table[blk];
+    return cr.base + (long long)page * cr.page_stride + ((long long)cr.kvh * cr.page_size + off) * hd;
+}
+
+// Copy keys key0 .. key0+63 (K and V rows) into the swizzled tiles; rows outside [lo, hi] become zeros.
+template <int HD>
+__device__ __forceinline__ void load_kv_tile(const CacheRef& cr, uint32_t sK, uint32_t sV, int key0, int lo, int hi) {
+    constexpr int CH = HD / 8;
+    for (int i = threadIdx.x; i < TILE_KEYS * CH; i += ATT_THREADS) {
+        const int row = i / CH, c = i - row * CH;
+        const int key = key0 + row;
+        const bool valid = key >= lo && key <= hi;
+        const bf16* src = valid ? key_row(cr, key, HD) + c * 8 : cr.base;
+        const uint32_t off = swz<HD>(row, c);
+        cp_async16(sK + off, src, valid);
+        cp_async16(sV + off, valid ? src + cr.kv_stride : src, valid);
+    }
+}
+
+// S[nt] (16 rows x 8 keys each) = Q (16 x HD, fragments in registers) . K^T for NKT*8 keys from row `row0`.
+template <int HD, int NKT>
+__device__ __forceinline__ void qk_scores(float (&S)[NKT][4], const uint32_t (&qf)[HD / 16][4], uint32_t sK, int row0, int lane) {
+#pragma unroll
+    for (int nt = 0; nt < NKT; ++nt) {
+        S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.0f;
+        const int row = row0 + nt * 8 + (lane & 7);
+#pragma unroll
+        for (int kk = 0; kk < HD / 32; ++kk) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4(b0, b1, b2, b3, sK + swz<HD>(row, kk * 4 + (lane >> 3)));
+            mma_bf16(S[nt], qf[2 * kk], b0, b1);
+            mma_bf16(S[nt], qf[2 * kk + 1], b2, b3);
+        }
+    }
+}
+
+// O (16 x HD) += P (16 x NKT*8, probabilities in S) . V for the keys from row `row0`.
+template <int HD, int NKT>
+__device__ __forceinline__ void pv_accumulate(float (&O)[HD / 8][4], const float (&S)[NKT][4], uint32_t sV, int row0, int lane) {
+#pragma unroll
+    for (int kt = 0; kt < NKT / 2; ++kt) {
+        uint32_t a[4];
+        a[0] = pack_bf16(S[2 * kt][0], S[2 * kt][1]);
+        a[1] = pack_bf16(S[2 * kt][2], S[2 * kt][3]);
+        a[2] = pack_bf16(S[2 * kt + 1][0], S[2 * kt + 1][1]);
+        a[3] = pack_bf16(S[2 * kt + 1][2], S[2 * kt + 1][3]);
+        const int row = row0 + kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+        for (int dn = 0; dn < HD / 16; ++dn) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(b0, b1, b2, b3, sV + swz<HD>(row, dn * 2 + (lane >> 4)));
+            mma_bf16(O[2 * dn], a, b0, b1);
+            mma_bf16(O[2 * dn + 1], a, b2, b3);
+        }
+    }
+}
+
+// Online softmax step on a warp's score tile.  Thread holds rows g = lane/4 (values [0],[1]) and g+8
+// ([2],[3]) at keys key0 + nt*8 + (lane%4)*2 + {0,1}.  row_hi / row_lo: last / first key each row may
+// see.  S comes in as raw dot products and leaves as probabilities relative to the running maximum.
+template <int HD, int NKT>
+__device__ __forceinline__ void softmax_step(float (&S)[NKT][4], float (&O)[HD / 8][4], float (&m)[2], float (&l)[2],
+                                             int key0, int lane, int lo0, int hi0, int lo1, int hi1, float scale2) {
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < NKT; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int key = key0 + nt * 8 + (lane & 3) * 2 + e;
+            const float s0 = (key >= lo0 && key <= hi0) ? S[nt][e] * scale2 : -INFINITY;
+            const float s1 = (key >= lo1 && key <= hi1) ? S[nt][2 + e] * scale2 : -INFINITY;
+            S[nt][e] = s0;
+            S[nt][2 + e] = s1;
+            mx0 = fmaxf(mx0, s0);
+            mx1 = fmaxf(mx1, s1);
+        }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+    const float use0 = mn0 == -INFINITY ? 0.0f : mn0, use1 = mn1 == -INFINITY ? 0.0f : mn1;
+    const float c0 = exp2f(m[0] - use0), c1 = exp2f(m[1] - use1);     // first tile: exp2(-inf) = 0
+    m[0] = mn0;
+    m[1] = mn1;
+    float r0 = 0.0f, r1 = 0.0f;
+#pragma unroll
+    for (int nt = 0; nt < NKT; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const float p0 = exp2f(S[nt][e] - use0), p1 = exp2f(S[nt][2 + e] - use1);
+            S[nt][e] = p0;
+            S[nt][2 + e] = p1;
+            r0 += p0;
+            r1 += p1;
+        }
+    }
+    l[0] = l[0] * c0 + r0;           // per-thread part of the row sum; the four threads of a row add up at the end
+    l[1] = l[1] * c1 + r1;
+#pragma unroll
+    for (int dn = 0; dn < HD / 8; ++dn) {
+        O[dn][0] *= c0; O[dn][1] *= c0;
+        O[dn][2] *= c1; O[dn][3] *= c1;
+    }
+}
+
+// =======================================================================================
+// decode
+// =======================================================================================
+// grid (n_chunks, n_kv_heads * q_blocks, n_tokens); q_blocks = ceil(group / 16).
+// o_part [n_tokens, n_heads, n_chunks, HD] float32 (un-normalised), ml_part [n_tokens, n_heads, n_chunks, 2]
+// (running maximum in log2 units, and the sum).
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS)
+decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, float* __restrict__ o_part,
+                        float* __restrict__ ml_part, const int* __restrict__ tables, const int* __restrict__ tok_seg,
+                        const int* __restrict__ pos, int n_heads, int n_kv_heads, int q_blocks, int page_size,
+                        int page_shift, int max_blocks, long long page_stride, long long kv_stride, int window,
+                        float scale2) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    constexpr int TILE_BYTES = TILE_KEYS * HD * 2;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int chunk = blockIdx.x, n_chunks = gridDim.x;
+    const int kvh = blockIdx.y / q_blocks, qb = blockIdx.y - kvh * q_blocks;
+    const int n = blockIdx.z;
+    const int group = n_heads / n_kv_heads;
+    const int P = pos[n];
+    const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
+    const int c_begin = chunk * DEC_CHUNK;
+    const int k_begin = c_begin > lo ? c_begin : lo;
+    const int k_end = (c_begin + DEC_CHUNK - 1 < P) ? c_begin + DEC_CHUNK - 1 : P;      // inclusive
+    if (k_begin > k_end) return;                                                          // nothing of this chunk is visible
+
+    CacheRef cr;
+    cr.base = cache; cr.table = tables + (size_t)tok_seg[n] * max_blocks;
+    cr.page_stride = page_stride; cr.kv_stride = kv_stride; cr.page_size = page_size; cr.page_shift = page_shift; cr.kvh = kvh;
+
+    const uint32_t sQ = smem_u32(smem_raw);                      // [16][HD]
+    const uint32_t sKV = sQ + 16 * HD * 2;                        // 2 stages x (K tile, V tile)
+
+    // the group's queries -> shared memory (rows beyond the group are zeros)
+    const int rows_valid = (group - qb * 16) < 16 ? (group - qb * 16) : 16;
+    for (int i = threadIdx.x; i < 16 * (HD / 8); i += ATT_THREADS) {
+        const int row = i / (HD / 8), c = i - row * (HD / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < rows_valid) {
+            const int h = kvh * group + qb * 16 + row;
+            v = *reinterpret_cast<const uint4*>(q + ((size_t)n * n_heads + h) * HD + c * 8);
+        }
+        *reinterpret_cast<uint4*>(smem_raw + swz<HD>(row, c)) = v;
+    }
+    const int t_first = k_begin / TILE_KEYS, t_last = k_end / TILE_KEYS;
+    load_kv_tile<HD>(cr, sKV, sKV + TILE_BYTES, t_first * TILE_KEYS, k_begin, k_end);
+    cp_async_commit();
+    __syncthreads();
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+        ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3],
+                    sQ + swz<HD>((lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
+
+    float O[HD / 8][4];
+#pragma unroll
+    for (int dn = 0; dn < HD / 8; ++dn) O[dn][0] = O[dn][1] = O[dn][2] = O[dn][3] = 0.0f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+
+    for (int t = t_first; t <= t_last; ++t) {
+        const int stage = (t - t_first) & 1;
+        if (t + 1 <= t_last) {
+            const uint32_t nb = sKV + (stage ^ 1) * 2 * TILE_BYTES;
+            load_kv_tile<HD>(cr, nb, nb + TILE_BYTES, (t + 1) * TILE_KEYS, k_begin, k_end);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t sK = sKV + stage * 2 * TILE_BYTES, sV = sK + TILE_BYTES;
+        const int key0 = t * TILE_KEYS + warp * 16;
+        if (key0 <= k_end && key0 + 15 >= k_begin) {          // this warp's 16 keys hold something visible
+            float S[2][4];
+            qk_scores<HD, 2>(S, qf, sK, warp * 16, lane);
+            softmax_step<HD, 2>(S, O, m, l, key0, lane, k_begin, k_end, k_begin, k_end, scale2);
+            pv_accumulate<HD, 2>(O, S, sV, warp * 16, lane);
+        }
+        __syncthreads();
+    }
+    // row sums over the four threads of a row
+    l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1); l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
+    l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1); l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+
+    // merge the four warps (each saw other keys) in warp order
+    float* red_m = reinterpret_cast<float*>(smem_raw);            // [4][16]
+    float* red_l = red_m + 64;                                    // [4][16]
+    float* red_o = red_l + 64;                                    // [16][HD]
+    const int g = lane >> 2, tq = lane & 3;
+    if (tq == 0) {
+        red_m[warp * 16 + g] = m[0]; red_m[warp * 16 + g + 8] = m[1];
+        red_l[warp * 16 + g] = l[0]; red_l[warp * 16 + g + 8] = l[1];
+    }
+    __syncthreads();
+    float M0 = -INFINITY, M1 = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) { M0 = fmaxf(M0, red_m[w * 16 + g]); M1 = fmaxf(M1, red_m[w * 16 + g + 8]); }
+    const float u0 = M0 == -INFINITY ? 0.0f : M0, u1 = M1 == -INFINITY ? 0.0f : M1;
+    const float f0 = exp2f(m[0] - u0), f1 = exp2f(m[1] - u1);
+    for (int w = 0; w < 4; ++w) {
+        if (warp == w) {
+#pragma unroll
+            for (int dn = 0; dn < HD / 8; ++dn) {
+                float* r0 = red_o + g * HD + dn * 8 + tq * 2;
+                float* r1 = red_o + (g + 8) * HD + dn * 8 + tq * 2;
+                if (w == 0) {
+                    r0[0] = O[dn][0] * f0; r0[1] = O[dn][1] * f0; r1[0] = O[dn][2] * f1; r1[1] = O[dn][3] * f1;
+                } else {
+                    r0[0] += O[dn][0] * f0; r0[1] += O[dn][1] * f0; r1[0] += O[dn][2] * f1; r1[1] += O[dn][3] * f1;
+                }
+            }
+        }
+        __syncthreads();
+    }
+    for (int i = threadIdx.x; i < rows_valid * HD; i += ATT_THREADS) {
+        const int row = i / HD, d = i - row * HD;
+        const int h = kvh * group + qb * 16 + row;
+        o_part[(((size_t)n * n_heads + h) * n_chunks + chunk) * HD + d] = red_o[row * HD + d];
+    }
+    if (threadIdx.x < rows_valid) {
+        const int row = threadIdx.x;
+        float Mr = -INFINITY;
+        for (int w = 0; w < 4; ++w) Mr = fmaxf(Mr, red_m[w * 16 + row]);
+        const float ur = Mr == -INFINITY ? 0.0f : Mr;
+        float Lr = 0.0f;
+        for (int w = 0; w < 4; ++w) Lr += red_l[w * 16 + row] * exp2f(red_m[w * 16 + row] - ur);
+        const int h = kvh * group + qb * 16 + row;
+        float* ml = ml_part + (((size_t)n * n_heads + h) * n_chunks + chunk) * 2;
+        ml[0] = Mr;
+        ml[1] = Lr;
+    }
+}
+
+// Merge the chunks a query saw, in rising order.  grid (n_tokens * n_heads), HD threads.
+template <int HD>
+__global__ void __launch_bounds__(HD)
+decode_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part, bf16* __restrict__ out,
+                    const int* __restrict__ pos, int n_heads, int n_chunks, int window) {
+    const int item = blockIdx.x, n = item / n_heads;
+    const int d = threadIdx.x;
+    const int P = pos[n];
+    const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
+    const int c0 = lo / DEC_CHUNK, c1 = P / DEC_CHUNK;
+    const float* ml = ml_part + (size_t)item * n_chunks * 2;
+    const float* op = o_part + (size_t)item * n_chunks * HD;
+    float M = -INFINITY;
+    for (int c = c0; c <= c1; ++c) M = fmaxf(M, ml[c * 2]);
+    float acc = 0.0f, L = 0.0f;
+    for (int c = c0; c <= c1; ++c) {
+        const float f = exp2f(ml[c * 2] - M);
+        L += ml[c * 2 + 1] * f;
+        acc += op[(size_t)c * HD + d] * f;
+    }
+    out[(size_t)item * HD + d] = __float2bfloat16_rn(acc / L);
+}
+
+// =======================================================================================
+// prefill
+// =======================================================================================
+// tiles [n_tiles, 3] = (index of the tile's first token, number of rows (1..64), segment).  grid (n_tiles, n_heads).
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS)
+prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, bf16* __restrict__ out,
+                         const int* __restrict__ tables, const int* __restrict__ tiles, const int* __restrict__ pos,
+                         int n_heads, int n_kv_heads, int page_size, int page_shift, int max_blocks,
+                         long long page_stride, long long kv_stride, int window, float scale2) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    constexpr int TILE_BYTES = TILE_KEYS * HD * 2;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n0 = tiles[blockIdx.x * 3], rows = tiles[blockIdx.x * 3 + 1], seg = tiles[blockIdx.x * 3 + 2];
+    const int h = blockIdx.y;
+    const int kvh = h / (n_heads / n_kv_heads);
+    const int p0 = pos[n0];                                       // positions of a portion are consecutive
+    const int p_last = p0 + rows - 1;
+    const int lo_tile = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
+
+    CacheRef cr;
+    cr.base = cache; cr.table = tables + (size_t)seg * max_blocks;
+    cr.page_stride = page_stride; cr.kv_stride = kv_stride; cr.page_size = page_size; cr.page_shift = page_shift; cr.kvh = kvh;
+
+    const uint32_t sQ = smem_u32(smem_raw);                      // [64][HD]
+    const uint32_t sKV = sQ + TILE_BYTES;
+    for (int i = threadIdx.x; i < 64 * (HD / 8); i += ATT_THREADS) {
+        const int row = i / (HD / 8), c = i - row * (HD / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < rows) v = *reinterpret_cast<const uint4*>(q + ((size_t)(n0 + row) * n_heads + h) * HD + c * 8);
+        *reinterpret_cast<uint4*>(smem_raw + swz<HD>(row, c)) = v;
+    }
+    const int t_first = lo_tile / TILE_KEYS, t_last = p_last / TILE_KEYS;
+    load_kv_tile<HD>(cr, sKV, sKV + TILE_BYTES, t_first * TILE_KEYS, lo_tile, p_last);
+    cp_async_commit();
+    __syncthreads();
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+        ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3],
+                    sQ + swz<HD>(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
+
+    float O[HD / 8][4];
+#pragma unroll
+    for (int dn = 0; dn < HD / 8; ++dn) O[dn][0] = O[dn][1] = O[dn][2] = O[dn][3] = 0.0f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+
+    // the two rows of this thread and what they may see
+    const int g = lane >> 2;
+    const int r0 = warp * 16 + g, r1 = r0 + 8;
+    const int hi0 = r0 < rows ? p0 + r0 : -1, hi1 = r1 < rows ? p0 + r1 : -1;      // padding rows see nothing
+    const int lo0 = (window > 0 && hi0 - window + 1 > 0) ? hi0 - window + 1 : 0;
+    const int lo1 = (window > 0 && hi1 - window + 1 > 0) ? hi1 - window + 1 : 0;
+    // what this warp's 16 rows may see at most
+    const int w_rows = rows - warp * 16;                         // rows of this warp that exist
+    const int w_hi = p0 + warp * 16 + (w_rows < 16 ? w_rows : 16) - 1;
+    const int w_lo = (window > 0 && p0 + warp * 16 - window + 1 > 0) ? p0 + warp * 16 - window + 1 : 0;
+
+    for (int t = t_first; t <= t_last; ++t) {
+        const int stage = (t - t_first) & 1;
+        if (t + 1 <= t_last) {
+            const uint32_t nb = sKV + (stage ^ 1) * 2 * TILE_BYTES;
+            load_kv_tile<HD>(cr, nb, nb + TILE_BYTES, (t + 1) * TILE_KEYS, lo_tile, p_last);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t sK = sKV + stage * 2 * TILE_BYTES, sV = sK + TILE_BYTES;
+        const int key0 = t * TILE_KEYS;
+        if (w_rows > 0 && key0 <= w_hi && key0 + TILE_KEYS - 1 >= w_lo) {
+            float S[8][4];
+            qk_scores<HD, 8>(S, qf, sK, 0, lane);
+            softmax_step<HD, 8>(S, O, m, l, key0, lane, lo0, hi0, lo1, hi1, scale2);
+            pv_accumulate<HD, 8>(O, S, sV, 0, lane);
+        }
+        __syncthreads();
+    }
+    l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1); l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
+    l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1); l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+    const int tq = lane & 3;
+    if (r0 < rows) {
+        const float inv = 1.0f / l[0];
+        bf16* o = out + ((size_t)(n0 + r0) * n_heads + h) * HD;
+#pragma unroll
+        for (int dn = 0; dn < HD / 8; ++dn)
+            *reinterpret_cast<uint32_t*>(o + dn * 8 + tq * 2) = pack_bf16(O[dn][0] * inv, O[dn][1] * inv);
+    }
+    if (r1 < rows) {
+        const float inv = 1.0f / l[1];
+        bf16* o = out + ((size_t)(n0 + r1) * n_heads + h) * HD;
+#pragma unroll
+        for (int dn = 0; dn < HD / 8; ++dn)
+            *reinterpret_cast<uint32_t*>(o + dn * 8 + tq * 2) = pack_bf16(O[dn][2] * inv, O[dn][3] * inv);
+    }
+}
+
+// =======================================================================================
+// entry points
+// =======================================================================================
+static int page_shift_of(int page_size) {
+    if (page_size > 0 && (page_size & (page_size - 1)) == 0) {
+        int s = 0;
+        while ((1 << s) < page_size) ++s;
+        return s;
+    }
+    return -1;
+}
+
+static int check_common(const char* what, int n_heads, int n_kv_heads, int head_dim, int page_size, int max_blocks) {
+    if (head_dim != 64 && head_dim != 128)
+        return zi_fail("%s: the tensor-core kernels take head_dim 64 or 128, got %d (the general kernel takes the rest)", what, head_dim);
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
+        return zi_fail("%s: %d query heads cannot share %d key/value heads", what, n_heads, n_kv_heads);
+    if (page_size <= 0 || max_blocks <= 0) return zi_fail("%s: page_size=%d max_blocks=%d", what, page_size, max_blocks);
+    return 0;
+}
+
+template <typename K> static int set_smem(K kernel, size_t bytes, const char* what) {
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return zi_fail("%s: cannot reserve %zu bytes of shared memory: %s", what, bytes, cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+ZI_EXPORT int zi_decode_chunk_keys() { return DEC_CHUNK; }
+
+// n_chunks must be at least ceil((largest position + 1) / DEC_CHUNK); o_part and ml_part are scratch of
+// n_tokens*n_heads*n_chunks*head_dim and n_tokens*n_heads*n_chunks*2 floats.
+ZI_EXPORT int zi_decode_attention(const void* q, const void* cache, void* out, float* o_part, float* ml_part,
+                                  const int* tables, const int* tok_seg, const int* pos, int n_tokens, int n_heads,
+                                  int n_kv_heads, int head_dim, int page_size, int max_blocks, long long page_stride,
+                                  long long kv_stride, int window, float scale, int n_chunks, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (check_common("decode_attention", n_heads, n_kv_heads, head_dim, page_size, max_blocks)) return 1;
+    if (n_chunks <= 0 || n_chunks > 65535) return zi_fail("decode_attention: n_chunks=%d out of range", n_chunks);
+    if (n_tokens > 65535) return zi_fail("decode_attention: %d tokens are more than one launch takes (65535)", n_tokens);
+    const int group = n_heads / n_kv_heads, q_blocks = (group + 15) / 16;
+    dim3 grid(n_chunks, n_kv_heads * q_blocks, n_tokens);
+    const float scale2 = scale * LOG2E;
+    const int shift = page_shift_of(page_size);
+    if (head_dim == 128) {
+        const size_t smem = 16 * 128 * 2 + 4 * TILE_KEYS * 128 * 2;
+        if (set_smem(decode_attention_kernel<128>, smem, "decode_attention")) return 1;
+        decode_attention_kernel<128><<<grid, ATT_THREADS, smem, stream>>>(
+            (const bf16*)q, (const bf16*)cache, o_part, ml_part, tables, tok_seg, pos, n_heads, n_kv_heads, q_blocks,
+            page_size, shift, max_blocks, page_stride, kv_stride, window, scale2);
+        decode_merge_kernel<128><<<n_tokens * n_heads, 128, 0, stream>>>(o_part, ml_part, (bf16*)out, pos, n_heads, n_chunks, window);
+    } else {
+        const size_t smem = 16 * 64 * 2 + 4 * TILE_KEYS * 64 * 2;
+        if (set_smem(decode_attention_kernel<64>, smem, "decode_attention")) return 1;
+        decode_attention_kernel<64><<<grid, ATT_THREADS, smem, stream>>>(
+            (const bf16*)q, (const bf16*)cache, o_part, ml_part, tables, tok_seg, pos, n_heads, n_kv_heads, q_blocks,
+            page_size, shift, max_blocks, page_stride, kv_stride, window, scale2);
+        decode_merge_kernel<64><<<n_tokens * n_heads, 64, 0, stream>>>(o_part, ml_part, (bf16*)out, pos, n_heads, n_chunks, window);
+    }
+    return zi_check_launch("decode_attention");
+}
+
+ZI_EXPORT int zi_prefill_attention(const void* q, const void* cache, void* out, const int* tables, const int* tiles,
+                                   const int* pos, int n_tiles, int n_heads, int n_kv_heads, int head_dim,
+                                   int page_size, int max_blocks, long long page_stride, long long kv_stride,
+                                   int window, float scale, cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (check_common("prefill_attention", n_heads, n_kv_heads, head_dim, page_size, max_blocks)) return 1;
+    if (n_heads > 65535) return zi_fail("prefill_attention: %d heads are more than one launch takes", n_heads);
+    dim3 grid(n_tiles, n_heads);
+    const float scale2 = scale * LOG2E;
+    const int shift = page_shift_of(page_size);
+    if (head_dim == 128) {
+        const size_t smem = 5 * TILE_KEYS * 128 * 2;
+        if (set_smem(prefill_attention_kernel<128>, smem, "prefill_attention")) return 1;
+        prefill_attention_kernel<128><<<grid, ATT_THREADS, smem, stream>>>(
+            (const bf16*)q, (const bf16*)cache, (bf16*)out, tables, tiles, pos, n_heads, n_kv_heads, page_size, shift,
+            max_blocks, page_stride, kv_stride, window, scale2);
+    } else {
+        const size_t smem = 5 * TILE_KEYS * 64 * 2;
+        if (set_smem(prefill_attention_kernel<64>, smem, "prefill_attention")) return 1;
+        prefill_attention_kernel<64><<<grid, ATT_THREADS, smem, stream>>>(
+            (const bf16*)q, (const bf16*)cache, (bf16*)out, tables, tiles, pos, n_heads, n_kv_heads, page_size, shift,
+            max_blocks, page_stride, kv_stride, window, scale2);
+    }
+    return zi_check_launch("prefill_attention");
+}

@@ -37,6 +37,7 @@ SOURCES: Dict[str, str] = {
     "gemm_simt": "gemm_simt.cu",
     "attention_generic": "attention_generic.cu",
     "sampling": "sampling.cu",
+    "attention_mma": "attention_mma.cu",
 }
 EXTRA_FLAGS: Dict[str, List[str]] = {}
 EXTRA_LIBS: Dict[str, List[str]] = {}

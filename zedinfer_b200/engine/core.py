@@ -168,6 +168,8 @@ class EngineCore:
     def kernel_libraries(dtype) -> List[str]:
         """The kernel libraries a run in ``dtype`` loads, for building them ahead of the first step."""
         libs = ["elementwise", "gemm_simt", "attention_generic", "sampling"]
+        if parse_dtype(dtype) == torch.bfloat16:
+            libs.append("attention_mma")
         return libs
 
     # ---- requests -------------------------------------------------------------------------
@@ -188,17 +190,21 @@ class EngineCore:
         width = self.table_width
         n_groups = len(self.cache.groups)
         n_want = sum(len(e.want) for e in entries)
-        # layout: ids | pos | tok_seg | want rows | slots | tables[g]...
+        # layout: ids | pos | tok_seg | want rows | slots | attention tiles | tables[g]...
+        tile_rows = 64
+        n_tiles = sum(-(-len(e.tokens) // tile_rows) for e in entries) + pad_segments
         off_ids, off_pos, off_seg = 0, n_tok, 2 * n_tok
         off_want = 3 * n_tok
         off_slots = off_want + n_want
-        off_tab = off_slots + n_seg
+        off_tiles = off_slots + n_seg
+        off_tab = off_tiles + 3 * n_tiles
         total = off_tab + n_groups * n_seg * width
         host = np.zeros(total, dtype=np.int32)
         seg_start, seg_len, seg_pos0, slots = [], [], [], []
         t = 0
         w = 0
         max_kv = 0
+        n_tile_done = 0
         vocab = self.spec.vocab_size
         for s, (e, rc) in enumerate(zip(entries, rcs)):
             toks = np.asarray(e.tokens, dtype=np.int64)
@@ -218,6 +224,9 @@ class EngineCore:
                 tab = rc.tables[g]
                 base = off_tab + (g * n_seg + s) * width
                 host[base: base + len(tab)] = tab
+            for q0 in range(0, k, tile_rows):
+                host[off_tiles + 3 * n_tile_done: off_tiles + 3 * n_tile_done + 3] = (t + q0, min(tile_rows, k - q0), s)
+                n_tile_done += 1
             seg_start.append(t), seg_len.append(k), seg_pos0.append(rc.length), slots.append(rc.slot)
             max_kv = max(max_kv, rc.length + k)
             t += k
@@ -227,6 +236,8 @@ class EngineCore:
             host[off_slots + s] = -1
             for g in range(n_groups):
                 host[off_tab + (g * n_seg + s) * width] = scratch
+            host[off_tiles + 3 * n_tile_done: off_tiles + 3 * n_tile_done + 3] = (t, 1, s)
+            n_tile_done += 1
             seg_start.append(t), seg_len.append(1), seg_pos0.append(0), slots.append(-1)
             t += 1
         dev = self._ring.stage(host, self.device)
@@ -237,7 +248,8 @@ class EngineCore:
             token_ids=dev[off_ids: off_ids + n_tok], positions=dev[off_pos: off_pos + n_tok],
             tok_seg=dev[off_seg: off_seg + n_tok], tables=tables, slots=dev[off_slots: off_slots + n_seg],
             seg_start_host=seg_start, seg_len_host=seg_len, seg_pos0_host=seg_pos0, slots_host=slots,
-            decode_only=all(k == 1 for k in seg_len), max_kv_len=max_kv)
+            decode_only=all(k == 1 for k in seg_len), max_kv_len=max(max_kv, 1))
+        ctx.extras["attn_tiles"] = dev[off_tiles: off_tiles + 3 * n_tiles].view(n_tiles, 3)
         want = dev[off_want: off_want + n_want] if n_want else None
         return ctx, want
 

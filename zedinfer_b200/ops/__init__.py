@@ -19,9 +19,10 @@ _elementwise = Library("elementwise")
 _gemm_simt = Library("gemm_simt")
 _attention_generic = Library("attention_generic")
 _sampling = Library("sampling")
+_attention_mma = Library("attention_mma")
 
 __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "silu_mul", "cast",
-           "gemm_nt", "linear", "paged_attention", "attention", "argmax", "sample", "repetition_penalty", "advance_decode"]
+           "gemm_nt", "linear", "paged_attention", "attention", "decode_attention", "prefill_attention", "argmax", "sample", "repetition_penalty", "advance_decode"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
@@ -171,13 +172,75 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tab
                             c_ll(kv_stride), c_int(window or 0), c_float(scale), stream())
 
 
+DECODE_CHUNK_KEYS = 256          # keys per thread block of the decode kernel (csrc/attention_mma.cu: DEC_CHUNK)
+PREFILL_TILE_ROWS = 64           # query rows per thread block of the prefill kernel
+
+
+def decode_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, o_part: torch.Tensor,
+                     ml_part: torch.Tensor, tables: torch.Tensor, tok_seg: torch.Tensor, pos: torch.Tensor,
+                     n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, page_stride: int, kv_stride: int,
+                     window: Optional[int], scale: float, n_chunks: int) -> None:
+    """One query token per request, bfloat16, tensor cores, context cut into chunks of 256 keys.
+
+    ``o_part`` (float32, ``n * n_heads * n_chunks * head_dim``) and ``ml_part`` (float32,
+    ``n * n_heads * n_chunks * 2``) are scratch; ``n_chunks >= ceil((largest position + 1) / 256)``.
+    """
+    need_cuda(q, cache, out, o_part, ml_part, tables, tok_seg, pos)
+    need_int32("tables", tables), need_int32("tok_seg", tok_seg), need_int32("pos", pos)
+    need_contiguous("q", q), need_contiguous("out", out)
+    n = q.shape[0]
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("decode_attention: bfloat16 only")
+    if o_part.dtype != torch.float32 or ml_part.dtype != torch.float32 or \
+            o_part.numel() < n * n_heads * n_chunks * head_dim or ml_part.numel() < n * n_heads * n_chunks * 2:
+        raise KernelError("decode_attention: scratch too small or not float32")
+    _attention_mma.call("zi_decode_attention", ptr(q), ptr(cache), ptr(out), ptr(o_part), ptr(ml_part), ptr(tables),
+                        ptr(tok_seg), ptr(pos), c_int(n), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
+                        c_int(page_size), c_int(tables.shape[1]), c_ll(page_stride), c_ll(kv_stride),
+                        c_int(window or 0), c_float(scale), c_int(n_chunks), stream())
+
+
+def prefill_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
+                      tiles: torch.Tensor, pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                      page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float) -> None:
+    """Portions of prompts, bfloat16, tensor cores.  ``tiles`` int32 ``[n_tiles, 3]``: (first token, rows <= 64,
+    segment); the positions of a tile's tokens are consecutive."""
+    need_cuda(q, cache, out, tables, tiles, pos)
+    need_int32("tables", tables), need_int32("tiles", tiles), need_int32("pos", pos)
+    need_contiguous("q", q), need_contiguous("out", out), need_contiguous("tiles", tiles)
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("prefill_attention: bfloat16 only")
+    _attention_mma.call("zi_prefill_attention", ptr(q), ptr(cache), ptr(out), ptr(tables), ptr(tiles), ptr(pos),
+                        c_int(tiles.shape[0]), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size),
+                        c_int(tables.shape[1]), c_ll(page_stride), c_ll(kv_stride), c_int(window or 0),
+                        c_float(scale), stream())
+
+
 def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
               window: Optional[int], scale: float) -> None:
     """Attention of a step's tokens over the cache (``cache`` is a CallCacheView, ``ctx`` a StepContext).
 
     Picks a kernel by dtype and by the shape of the step; all of them compute the same function.
+    bfloat16 with head_dim 64 or 128 runs on the tensor cores (decode-only steps on the chunked decode
+    kernel, anything else on the tiled prefill kernel); float32 and other head sizes on the general kernel.
     """
-    paged_attention(q, cache.tensor, out, ctx.tables[cache.group], ctx.tok_seg, ctx.positions, n_heads, n_kv_heads,
+    tables = ctx.tables[cache.group]
+    if q.dtype == torch.bfloat16 and head_dim in (64, 128):
+        n = q.shape[0]
+        if ctx.decode_only:
+            n_chunks = max(1, -(-ctx.max_kv_len // DECODE_CHUNK_KEYS))
+            o_part = torch.empty(n * n_heads * n_chunks * head_dim, dtype=torch.float32, device=q.device)
+            ml_part = torch.empty(n * n_heads * n_chunks * 2, dtype=torch.float32, device=q.device)
+            decode_attention(q, cache.tensor, out, o_part, ml_part, tables, ctx.tok_seg, ctx.positions, n_heads,
+                             n_kv_heads, head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale,
+                             n_chunks)
+            return
+        tiles = ctx.extras.get("attn_tiles")
+        if tiles is not None:
+            prefill_attention(q, cache.tensor, out, tables, tiles, ctx.positions, n_heads, n_kv_heads, head_dim,
+                              cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
+            return
+    paged_attention(q, cache.tensor, out, tables, ctx.tok_seg, ctx.positions, n_heads, n_kv_heads,
                     head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
 
 
