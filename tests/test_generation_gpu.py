@@ -1,0 +1,203 @@
+"""Generation through the Python entry point and bin/trace_run as a user runs it."""
+import json
+import os
+import random
+import struct
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import tiny
+import traces
+from plain import qwen2_plain as P
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("gen_models")
+    return {name: tiny.make_model_dir(root, name) for name in tiny.CONFIGS}
+
+
+def plain_greedy(model_dir, prompt, n_new, act=None):
+    cfg, w = P.load(model_dir)
+    seq, out = list(prompt), []
+    for _ in range(n_new):
+        tok = P.greedy(P.forward(cfg, w, seq, act)[-1])
+        out.append(tok)
+        seq.append(tok)
+    return out
+
+
+@pytest.mark.parametrize("name,graphs", [("A", False), ("B", True), ("C", False), ("D", True)])
+def test_greedy_generation_float32_equals_plain(models, name, graphs):
+    from zedinfer_b200 import GenerationConfig, SchedulerConfig
+    from zedinfer_b200.engine import InferenceEngine
+    cfg, _ = tiny.CONFIGS[name]
+    rng = random.Random(3)
+    prompts = [[rng.randrange(cfg["vocab_size"]) for _ in range(n)] for n in (7, 13, 1)]
+    engine = InferenceEngine.create(models[name], SchedulerConfig(num_kv_pages=40, kv_block_size=4, max_batch_requests=4,
+                                                                  max_prefill_tokens=5, cuda_graphs=graphs),
+                                    dtype="float32")
+    results = engine.generate_batch(prompts, GenerationConfig(max_new_tokens=8, ignore_eos=True))
+    for p, r in zip(prompts, results):
+        assert r.finish_reason == "length"
+        assert r.output_ids == plain_greedy(models[name], p, 8)
+    assert engine.cache_stats()["live_requests"] == 0
+    assert engine.cache_stats()["free_pages"] == [40] * engine.cache_stats()["groups"]
+
+
+def test_single_request_and_first_tokens(models):
+    """One-token prompts and the first positions of a sequence: nothing before them in the cache."""
+    from zedinfer_b200 import GenerationConfig, SchedulerConfig
+    from zedinfer_b200.engine import InferenceEngine
+    engine = InferenceEngine.create(models["B"], SchedulerConfig(num_kv_pages=16, kv_block_size=8), dtype="float32")
+    for prompt in ([0], [999], [5, 6]):
+        r = engine.generate_tokens(prompt, GenerationConfig(max_new_tokens=3, ignore_eos=True))
+        assert r.output_ids == plain_greedy(models["B"], prompt, 3)
+        assert r.stats.prompt_tokens == len(prompt) and r.stats.generated_tokens == 3
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_stays_on_the_plain_path(models, dtype):
+    """Several hundred decoded tokens, fed one by one, each compared with the whole-sequence logits: a fault
+    that builds up over a long decode, or at a page's edge far from the start, shows here."""
+    from zedinfer_b200.engine.core import EngineCore, StepEntry
+    cfg, _ = tiny.CONFIGS["D"]
+    rng = random.Random(8)
+    toks = [rng.randrange(cfg["vocab_size"]) for _ in range(700)]
+    pcfg, w = P.load(models["D"])
+    ref = P.forward(pcfg, w, toks, torch.bfloat16 if dtype == "bfloat16" else None)
+    for graphs in (False, True):
+        core = EngineCore(models["D"], dtype, page_size=16, num_pages=44, max_requests=2, cuda_graphs=graphs)
+        got = [core.step([StepEntry("x", toks[:100], list(range(100)))]).cpu()]
+        for i in range(100, 700):
+            got.append(core.step([StepEntry("x", [toks[i]], [0])]).cpu().clone())
+        got = torch.cat(got)
+        err = (got - ref).abs().amax(dim=1)
+        tol = 3e-4 if dtype == "float32" else 8e-2
+        bad = torch.nonzero(err > tol)
+        assert bad.numel() == 0, f"first wrong position {int(bad[0])}, error {float(err[bad[0]])} (graphs={graphs})"
+        core.end("x")
+
+
+def test_temperature_sampling_is_deterministic_per_seed(models):
+    from zedinfer_b200 import GenerationConfig, SchedulerConfig
+    from zedinfer_b200.engine import InferenceEngine
+    from zedinfer_b200.sampling import uniform_for
+    engine = InferenceEngine.create(models["B"], SchedulerConfig(num_kv_pages=64, kv_block_size=8, max_prefill_tokens=5),
+                                    dtype="float32")
+    prompts = [[1], list(range(10, 27)), list(range(100, 140))]
+    gc = GenerationConfig(max_new_tokens=6, use_argmax=False, temperature=0.7, seed=2, ignore_eos=True)
+    together = [r.output_ids for r in engine.generate_batch(prompts, gc)]
+    alone = [engine.generate_tokens(p, gc).output_ids for p in prompts]
+    assert together == alone                      # a draw does not depend on who else is in the batch
+    other = [r.output_ids for r in engine.generate_batch(prompts, GenerationConfig(
+        max_new_tokens=6, use_argmax=False, temperature=0.7, seed=3, ignore_eos=True))]
+    assert other != together
+    # each token is the plain implementation's pick for the same uniform number
+    cfg, w = P.load(models["B"])
+    seq = list(prompts[1])
+    for i, tok in enumerate(alone[1]):
+        dist = P.sampling_distribution(P.forward(cfg, w, seq)[-1], 0.7, 0, 1.0)
+        u = uniform_for(2, i)
+        cum = torch.cumsum(dist.double(), 0)
+        lo, hi = float(cum[tok] - dist[tok].double()), float(cum[tok])
+        assert lo - 1e-4 <= u <= hi + 1e-4
+        seq.append(tok)
+
+
+def test_top_k_one_is_greedy_and_stop_token_ends(models):
+    from zedinfer_b200 import GenerationConfig, SchedulerConfig
+    from zedinfer_b200.engine import InferenceEngine
+    engine = InferenceEngine.create(models["A"], SchedulerConfig(num_kv_pages=32, kv_block_size=4), dtype="float32")
+    prompt = [3, 1, 4, 1, 5, 9, 2, 6]
+    greedy = plain_greedy(models["A"], prompt, 6)
+    r = engine.generate_tokens(prompt, GenerationConfig(max_new_tokens=6, use_argmax=False, temperature=1.5, top_k=1,
+                                                        seed=5, ignore_eos=True))
+    assert r.output_ids == greedy
+    engine.scheduler.stop_token_ids = frozenset([greedy[2]])
+    r = engine.generate_tokens(prompt, GenerationConfig(max_new_tokens=6))
+    first = greedy.index(greedy[2])
+    assert r.finish_reason == "stop" and r.output_ids == greedy[:first + 1]
+
+
+def test_preemption_recomputes_and_gives_the_same_tokens(models):
+    """So few pages that the youngest request is taken off the GPU in mid-decode and recomputed later."""
+    from zedinfer_b200 import GenerationConfig, SchedulerConfig
+    from zedinfer_b200.engine import InferenceEngine
+    prompts = [list(range(1, 8)), list(range(20, 28))]
+    engine = InferenceEngine.create(models["A"], SchedulerConfig(num_kv_pages=6, kv_block_size=4, on_exhaust="preempt"),
+                                    dtype="float32")
+    results = engine.generate_batch(prompts, GenerationConfig(max_new_tokens=9, ignore_eos=True))
+    assert engine.scheduler.num_preemptions >= 1
+    for p, r in zip(prompts, results):
+        assert r.finish_reason == "length" and r.output_ids == plain_greedy(models["A"], p, 9)
+    engine = InferenceEngine.create(models["A"], SchedulerConfig(num_kv_pages=6, kv_block_size=4, on_exhaust="fail"),
+                                    dtype="float32")
+    results = engine.generate_batch(prompts, GenerationConfig(max_new_tokens=9, ignore_eos=True))
+    assert sorted(r.finish_reason for r in results) == ["error", "length"]
+    assert "KV cache exhausted during decode" in [r for r in results if r.error][0].error
+
+
+def test_fails_loudly_without_a_gpu_tensor_or_a_known_architecture(models, tmp_path):
+    from zedinfer_b200.config import ConfigError
+    from zedinfer_b200.engine.core import EngineCore
+    with pytest.raises(RuntimeError, match="GPU only"):
+        EngineCore(models["A"], "float32", device="cpu")
+    bad = tmp_path / "other"
+    bad.mkdir()
+    (bad / "config.json").write_text(json.dumps(dict(tiny.TINY_A, architectures=["MambaForCausalLM"], model_type="mamba")))
+    with pytest.raises(ConfigError, match="Unsupported model"):
+        EngineCore(str(bad), "float32")
+
+
+# ---- bin/trace_run, as a separate program ----------------------------------------------------------------
+def run_trace_program(model_dir, dtype, steps, out_dir, max_tokens):
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
+           "--out", str(out_dir), "--max-tokens", str(max_tokens)]
+    proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+    for st in steps:                              # the next step goes in only after "done <step>" came back
+        proc.stdin.write(json.dumps(st) + "\n")
+        proc.stdin.flush()
+        line = proc.stdout.readline().strip()
+        assert line == f"done {st['step']}", line
+    proc.stdin.close()
+    assert proc.wait(timeout=60) == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(models, tmp_path, dtype):
+    cfg, _ = tiny.CONFIGS["B"]
+    rng = random.Random(21)
+    requests = {f"q{i}": [rng.randrange(cfg["vocab_size"]) for _ in range(n)] for i, n in enumerate([40, 64, 90, 17, 70, 33])}
+    steps = traces.mixed(requests, seed=4)
+    steps[3]["entries"][0]["want"] = []           # a step may want nothing of a request
+    need = traces.max_live_tokens(steps, round_to=64)
+    out = tmp_path / f"out_{dtype}"
+    run_trace_program(models["B"], dtype, steps, out, need)
+    pcfg, w = P.load(models["B"])
+    act = torch.bfloat16 if dtype == "bfloat16" else None
+    ref = {rid: P.forward(pcfg, w, toks, act) for rid, toks in requests.items()}
+    progress = {}
+    worst = 0.0
+    for st in steps:
+        wanted = sum(len(e["want"]) for e in st["entries"])
+        path = out / f"{st['step']}.f32"
+        if wanted == 0:
+            assert not path.exists()
+        else:
+            arr = np.fromfile(path, dtype="<f4").reshape(wanted, cfg["vocab_size"])
+        row = 0
+        for e in st["entries"]:
+            base = progress.get(e["id"], 0)
+            for j in e["want"]:
+                worst = max(worst, float(np.abs(arr[row] - ref[e["id"]][base + j].numpy()).max()))
+                row += 1
+            progress[e["id"]] = base + len(e["tokens"])
+    assert worst < (2e-4 if dtype == "float32" else 6e-2), worst

@@ -65,7 +65,7 @@ def _random_tensors_on_device(specs, seed: int, dtype: torch.dtype, device) -> D
     return out
 
 
-class _PinnedRing:
+class PinnedStaging:
     """A few pinned staging buffers; a buffer is reused only after the copy out of it has finished."""
 
     def __init__(self, n: int = 4):
@@ -108,6 +108,79 @@ class _PinnedRing:
         ev.record()
         self.events[i] = ev
         return dev
+
+
+def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache], cache: CacheManager,
+                       table_width: int, dtype: torch.dtype, device: torch.device, vocab: int,
+                       ring: "PinnedStaging", pad_segments: int = 0) -> Tuple[StepContext, Optional[torch.Tensor]]:
+    """Flatten the entries into one device descriptor (a single host-to-device copy)."""
+    n_seg = len(entries) + pad_segments
+    n_tok = sum(len(e.tokens) for e in entries) + pad_segments
+    width = table_width
+    n_groups = len(cache.groups)
+    n_want = sum(len(e.want) for e in entries)
+    # layout: ids | pos | tok_seg | want rows | slots | attention tiles | tables[g]...
+    tile_rows = 64
+    n_tiles = sum(-(-len(e.tokens) // tile_rows) for e in entries) + pad_segments
+    off_ids, off_pos, off_seg = 0, n_tok, 2 * n_tok
+    off_want = 3 * n_tok
+    off_slots = off_want + n_want
+    off_tiles = off_slots + n_seg
+    off_tab = off_tiles + 3 * n_tiles
+    total = off_tab + n_groups * n_seg * width
+    host = np.zeros(total, dtype=np.int32)
+    seg_start, seg_len, seg_pos0, slots = [], [], [], []
+    t = 0
+    w = 0
+    max_kv = 0
+    n_tile_done = 0
+    for s, (e, rc) in enumerate(zip(entries, rcs)):
+        toks = np.asarray(e.tokens, dtype=np.int64)
+        k = toks.size
+        if k and (toks.min() < 0 or toks.max() >= vocab):
+            raise ValueError(f"request {e.request_id!r}: token id outside [0, {vocab})")
+        host[off_ids + t: off_ids + t + k] = toks
+        host[off_pos + t: off_pos + t + k] = np.arange(rc.length, rc.length + k, dtype=np.int32)
+        host[off_seg + t: off_seg + t + k] = s
+        for j in e.want:
+            if not 0 <= j < k:
+                raise ValueError(f"request {e.request_id!r}: wanted place {j} is outside its {k} tokens")
+            host[off_want + w] = t + j
+            w += 1
+        host[off_slots + s] = rc.slot
+        for g in range(n_groups):
+            tab = rc.tables[g]
+            base = off_tab + (g * n_seg + s) * width
+            host[base: base + len(tab)] = tab
+        for q0 in range(0, k, tile_rows):
+            host[off_tiles + 3 * n_tile_done: off_tiles + 3 * n_tile_done + 3] = (t + q0, min(tile_rows, k - q0), s)
+            n_tile_done += 1
+        seg_start.append(t), seg_len.append(k), seg_pos0.append(rc.length), slots.append(rc.slot)
+        max_kv = max(max_kv, rc.length + k)
+        t += k
+    scratch = cache.scratch_page if cache.groups else 0
+    for s in range(len(entries), n_seg):         # padding: one token at position 0 of the scratch page
+        host[off_seg + t] = s
+        host[off_slots + s] = -1
+        for g in range(n_groups):
+            host[off_tab + (g * n_seg + s) * width] = scratch
+        host[off_tiles + 3 * n_tile_done: off_tiles + 3 * n_tile_done + 3] = (t, 1, s)
+        n_tile_done += 1
+        seg_start.append(t), seg_len.append(1), seg_pos0.append(0), slots.append(-1)
+        t += 1
+    dev = ring.stage(host, device)
+    tables = [dev[off_tab + g * n_seg * width: off_tab + (g + 1) * n_seg * width].view(n_seg, width)
+              for g in range(n_groups)]
+    ctx = StepContext(
+        n_tokens=n_tok, n_segments=n_seg, dtype=dtype, device=device,
+        token_ids=dev[off_ids: off_ids + n_tok], positions=dev[off_pos: off_pos + n_tok],
+        tok_seg=dev[off_seg: off_seg + n_tok], tables=tables, slots=dev[off_slots: off_slots + n_seg],
+        seg_start_host=seg_start, seg_len_host=seg_len, seg_pos0_host=seg_pos0, slots_host=slots,
+        decode_only=all(k == 1 for k in seg_len), max_kv_len=max(max_kv, 1))
+    ctx.extras["attn_tiles"] = dev[off_tiles: off_tiles + 3 * n_tiles].view(n_tiles, 3)
+    want = dev[off_want: off_want + n_want] if n_want else None
+    return ctx, want
+
 
 
 class EngineCore:
@@ -159,7 +232,7 @@ class EngineCore:
         self.cache.allocate_device(int(num_pages), self.dtype, self.device)
         self.views = {call: self.cache.view_for_call(call) for call, _ in self.model.cache_needs()}
         self.table_width = max(1, (self.max_seq_len + self.page_size - 1) // self.page_size)
-        self._ring = _PinnedRing()
+        self._ring = PinnedStaging()
         self.cuda_graphs = bool(cuda_graphs)
         self.max_requests = int(max_requests)
         self._decode_graphs: Dict[int, "DecodeGraph"] = {}
@@ -185,73 +258,8 @@ class EngineCore:
     def build_context(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache],
                       pad_segments: int = 0) -> Tuple[StepContext, Optional[torch.Tensor]]:
         """Flatten the entries into one device descriptor (a single host-to-device copy)."""
-        n_seg = len(entries) + pad_segments
-        n_tok = sum(len(e.tokens) for e in entries) + pad_segments
-        width = self.table_width
-        n_groups = len(self.cache.groups)
-        n_want = sum(len(e.want) for e in entries)
-        # layout: ids | pos | tok_seg | want rows | slots | attention tiles | tables[g]...
-        tile_rows = 64
-        n_tiles = sum(-(-len(e.tokens) // tile_rows) for e in entries) + pad_segments
-        off_ids, off_pos, off_seg = 0, n_tok, 2 * n_tok
-        off_want = 3 * n_tok
-        off_slots = off_want + n_want
-        off_tiles = off_slots + n_seg
-        off_tab = off_tiles + 3 * n_tiles
-        total = off_tab + n_groups * n_seg * width
-        host = np.zeros(total, dtype=np.int32)
-        seg_start, seg_len, seg_pos0, slots = [], [], [], []
-        t = 0
-        w = 0
-        max_kv = 0
-        n_tile_done = 0
-        vocab = self.spec.vocab_size
-        for s, (e, rc) in enumerate(zip(entries, rcs)):
-            toks = np.asarray(e.tokens, dtype=np.int64)
-            k = toks.size
-            if k and (toks.min() < 0 or toks.max() >= vocab):
-                raise ValueError(f"request {e.request_id!r}: token id outside [0, {vocab})")
-            host[off_ids + t: off_ids + t + k] = toks
-            host[off_pos + t: off_pos + t + k] = np.arange(rc.length, rc.length + k, dtype=np.int32)
-            host[off_seg + t: off_seg + t + k] = s
-            for j in e.want:
-                if not 0 <= j < k:
-                    raise ValueError(f"request {e.request_id!r}: wanted place {j} is outside its {k} tokens")
-                host[off_want + w] = t + j
-                w += 1
-            host[off_slots + s] = rc.slot
-            for g in range(n_groups):
-                tab = rc.tables[g]
-                base = off_tab + (g * n_seg + s) * width
-                host[base: base + len(tab)] = tab
-            for q0 in range(0, k, tile_rows):
-                host[off_tiles + 3 * n_tile_done: off_tiles + 3 * n_tile_done + 3] = (t + q0, min(tile_rows, k - q0), s)
-                n_tile_done += 1
-            seg_start.append(t), seg_len.append(k), seg_pos0.append(rc.length), slots.append(rc.slot)
-            max_kv = max(max_kv, rc.length + k)
-            t += k
-        scratch = self.cache.scratch_page if self.cache.groups else 0
-        for s in range(len(entries), n_seg):         # padding: one token at position 0 of the scratch page
-            host[off_seg + t] = s
-            host[off_slots + s] = -1
-            for g in range(n_groups):
-                host[off_tab + (g * n_seg + s) * width] = scratch
-            host[off_tiles + 3 * n_tile_done: off_tiles + 3 * n_tile_done + 3] = (t, 1, s)
-            n_tile_done += 1
-            seg_start.append(t), seg_len.append(1), seg_pos0.append(0), slots.append(-1)
-            t += 1
-        dev = self._ring.stage(host, self.device)
-        tables = [dev[off_tab + g * n_seg * width: off_tab + (g + 1) * n_seg * width].view(n_seg, width)
-                  for g in range(n_groups)]
-        ctx = StepContext(
-            n_tokens=n_tok, n_segments=n_seg, dtype=self.dtype, device=self.device,
-            token_ids=dev[off_ids: off_ids + n_tok], positions=dev[off_pos: off_pos + n_tok],
-            tok_seg=dev[off_seg: off_seg + n_tok], tables=tables, slots=dev[off_slots: off_slots + n_seg],
-            seg_start_host=seg_start, seg_len_host=seg_len, seg_pos0_host=seg_pos0, slots_host=slots,
-            decode_only=all(k == 1 for k in seg_len), max_kv_len=max(max_kv, 1))
-        ctx.extras["attn_tiles"] = dev[off_tiles: off_tiles + 3 * n_tiles].view(n_tiles, 3)
-        want = dev[off_want: off_want + n_want] if n_want else None
-        return ctx, want
+        return build_step_context(entries, rcs, self.cache, self.table_width, self.dtype, self.device,
+                                  self.spec.vocab_size, self._ring, pad_segments)
 
     def prepare(self, entries: Sequence[StepEntry]) -> List[RequestCache]:
         """Open new requests and make sure every entry has pages for its tokens; all or nothing."""
