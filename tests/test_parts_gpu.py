@@ -81,7 +81,7 @@ def test_attention_part_with_rope_over_portions(dtype, nh, nkv, hd, window):
     specs = mixer.tensor_specs()
     assert "q_proj.bias" in specs and "o_proj.bias" not in specs
     g = torch.Generator().manual_seed(1)
-    t = {k: (torch.randn(v.shape, generator=g) * 0.3).to(dtype).to(DEV) for k, v in specs.items()}
+    t = {k: (torch.randn(v.shape, generator=g) * 0.08).to(dtype).to(DEV) for k, v in specs.items()}
     mixer.bind(t)
     cache = CacheManager([(0, mixer.cache_need())], 4, max_requests=2)
     cache.allocate_device(16, dtype, DEV)
@@ -104,7 +104,8 @@ def test_attention_part_with_rope_over_portions(dtype, nh, nkv, hd, window):
     pos = torch.arange(total)
     a = r(P.attention(r(P.rope(q, pos, theta)), r(P.rope(k, pos, theta)), v, 1.0 / math.sqrt(hd), window))
     ref = P.linear(a.reshape(total, nh * hd), f["o_proj.weight"], None)
-    tol = 1e-4 if dtype == torch.float32 else 6e-2
+    # relative to the size of the outputs: float32 differs by the order of sums, bfloat16 by its 2^-8 steps
+    tol = (1e-5 if dtype == torch.float32 else 2e-2) * max(1.0, float(ref.abs().max()))
     assert float((got - ref).abs().max()) < tol
     for bad in (dict(head_dim=40), dict(num_kv_heads=5), dict(window=0), dict(head_dim=512)):
         kw = dict(hidden_size=hidden, num_heads=nh, num_kv_heads=nkv, head_dim=hd,

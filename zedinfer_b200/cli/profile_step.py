@@ -1,0 +1,72 @@
+"""Run a few decode or prefill steps of a random-weight Qwen2-shaped model between cudaProfilerStart/Stop,
+for ``ncu --profile-from-start off``.  Steps are launched kernel by kernel (no CUDA graph), so every
+kernel shows up as a launch of its own.  Prints the mean time of a step measured with CUDA events."""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+
+def main(argv=None) -> int:
+    p = argparse.ArgumentParser(prog="zedinfer-profile-step", description=__doc__)
+    p.add_argument("--mode", choices=["decode", "prefill"], default="decode")
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=3072, help="decode: tokens already cached per request")
+    p.add_argument("--tokens", type=int, default=2048, help="prefill: tokens of the portion")
+    p.add_argument("--layers", type=int, default=28)
+    p.add_argument("--steps", type=int, default=2)
+    p.add_argument("--hidden", type=int, default=1536)
+    p.add_argument("--heads", type=int, default=12)
+    p.add_argument("--kv-heads", type=int, default=2)
+    p.add_argument("--head-dim", type=int, default=128)
+    p.add_argument("--intermediate", type=int, default=8960)
+    p.add_argument("--vocab", type=int, default=151936)
+    p.add_argument("--graphs", action="store_true", help="decode through the captured step instead")
+    args = p.parse_args(argv)
+    import torch
+    from ..engine.core import EngineCore, StepEntry
+    cfg = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": args.layers,
+           "hidden_size": args.hidden, "num_attention_heads": args.heads, "num_key_value_heads": args.kv_heads,
+           "head_dim": args.head_dim, "intermediate_size": args.intermediate, "vocab_size": args.vocab,
+           "max_position_embeddings": 8192}
+    span = (args.context + args.steps + 8) if args.mode == "decode" else args.tokens
+    core = EngineCore(None, "bfloat16", config=cfg, random_seed=3, page_size=16,
+                      max_tokens=args.batch * (span + 64), max_requests=max(args.batch, 1), max_seq_len=span + 64,
+                      cuda_graphs=args.graphs)
+    g = torch.Generator().manual_seed(0)
+    rand = lambda n: torch.randint(0, args.vocab, (n,), generator=g).tolist()      # noqa: E731
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.mode == "decode":
+        for r in range(args.batch):
+            left = args.context
+            while left > 0:
+                n = min(left, 2048)
+                core.step([StepEntry(r, rand(n), [])])
+                left -= n
+        step = lambda: core.step([StepEntry(r, rand(1), [0]) for r in range(args.batch)])   # noqa: E731
+    else:
+        counter = [0]
+
+        def step():
+            rid = ("p", counter[0])
+            counter[0] += 1
+            core.step([StepEntry(rid, rand(args.tokens), [args.tokens - 1])])
+            core.end(rid)
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    a.record()
+    for _ in range(args.steps):
+        step()
+    b.record()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print(json.dumps({"mode": args.mode, "batch": args.batch, "layers": args.layers,
+                      "ms_per_step": round(a.elapsed_time(b) / args.steps, 4)}))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
