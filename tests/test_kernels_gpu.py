@@ -366,3 +366,47 @@ def test_attention_kernels_refuse_what_they_cannot_do():
                             tables, z, z, 3, 2, 32, 4, page_stride, kv_stride, None, 1.0)
     with pytest.raises(ops.KernelError, match="GPU only"):
         ops.silu_mul(torch.zeros(2, 4), torch.zeros(2, 2))
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(1000, 96), (2048, 1536), (1536, 8960), (50, 64)])
+def test_gemm_smallm(m, n, k):
+    from zedinfer_b200 import ops
+    x = rand(m, k, dtype=torch.bfloat16)
+    w = rand(n, k, dtype=torch.bfloat16, seed=1, scale=0.05)
+    b = rand(n, dtype=torch.bfloat16, seed=2)
+    ref = x.double().cpu() @ w.double().cpu().t()
+    for out_dtype, bias in ((torch.bfloat16, b), (torch.float32, None)):
+        out = torch.full((m, n), float("nan"), dtype=out_dtype, device=dev())
+        ops.gemm_smallm(x, w, bias, out)
+        r = (ref + b.double().cpu()) if bias is not None else ref
+        tol = 2e-2 if out_dtype == torch.bfloat16 else 2e-3
+        assert torch.allclose(out.double().cpu(), r, atol=tol * 3, rtol=tol)
+        # a token's result does not depend on how many tokens are in the step
+        if m > 1:
+            one = torch.empty(1, n, dtype=out_dtype, device=dev())
+            ops.gemm_smallm(x[m - 1:m], w, bias, one)
+            assert torch.equal(one[0], out[m - 1])
+    # ops.linear routes here for few rows and agrees with the SIMT product
+    out_l = torch.empty(m, n, dtype=torch.float32, device=dev())
+    ops.linear(x, w, None, out_l)
+    out_s = torch.empty(m, n, dtype=torch.float32, device=dev())
+    ops.gemm_nt(x, w, None, out_s)
+    assert torch.allclose(out_l, out_s, atol=2e-3, rtol=2e-3)
+
+
+@pytest.mark.parametrize("m,inter,k", [(1, 176, 64), (8, 8960, 1536), (13, 200, 96)])
+def test_gemm_smallm_fused_activation(m, inter, k):
+    from zedinfer_b200 import ops
+    x = rand(m, k, dtype=torch.bfloat16)
+    w = rand(2 * inter, k, dtype=torch.bfloat16, seed=3, scale=0.1)
+    fused = torch.empty(m, inter, dtype=torch.bfloat16, device=dev())
+    ops.gemm_smallm(x, w, None, fused, silu_mul=True)
+    gu = torch.empty(m, 2 * inter, dtype=torch.bfloat16, device=dev())
+    ops.gemm_smallm(x, w, None, gu)
+    unfused = torch.empty_like(fused)
+    ops.silu_mul(gu, unfused)
+    assert torch.equal(fused, unfused)                   # same sums, same roundings
+    g = (x.double().cpu() @ w[:inter].double().cpu().t()).float().to(torch.bfloat16).float()
+    u = (x.double().cpu() @ w[inter:].double().cpu().t()).float().to(torch.bfloat16).float()
+    assert torch.allclose(fused.float().cpu(), P.swiglu(g, u), atol=3e-2, rtol=3e-2)

@@ -38,6 +38,7 @@ SOURCES: Dict[str, str] = {
     "attention_generic": "attention_generic.cu",
     "sampling": "sampling.cu",
     "attention_mma": "attention_mma.cu",
+    "gemm_smallm": "gemm_smallm.cu",
 }
 EXTRA_FLAGS: Dict[str, List[str]] = {}
 EXTRA_LIBS: Dict[str, List[str]] = {}

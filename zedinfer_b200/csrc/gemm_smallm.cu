@@ -1,0 +1,174 @@
+// C[M,N] = X[M,K] . W[N,K]^T (+ bias[N]) for few rows (M <= 16: decode steps), bfloat16 operands,
+// float32 accumulation on the tensor cores (mma.sync m16n8k16), output bfloat16 or float32.
+//
+// The product is bound by reading W once.  Roles are swapped: 16 rows of W are the "A" tile of the
+// MMA and 8 tokens its "N" side, so a decode batch of 8 fills an instruction exactly.  Weights go
+// from global memory straight into MMA fragments, no shared memory in between: a thread loads 16
+// contiguous bytes (8 k-values) of weight rows g and g+8 and treats them as the k-slots its lane owns
+// in two consecutive k16 steps; the activations are loaded with the same assignment, and since a dot
+// product does not care in which order k is walked, the result is the plain product.  Per 32
+// k-values a warp reads 64 contiguous bytes of each of its 16 rows.
+//
+// One thread block owns 16 output columns (rows of W) over all of K; its 8 warps take interleaved
+// k-steps (warp w: steps w, w+8, ...) and their partial sums are added in warp order through shared
+// memory: no atomics, the same bits every time, and a token's result does not depend on the batch.
+//
+// ACT_SILU_MUL variant: W holds gate rows and up rows ([2*I, K], gate first); the block computes
+// both for its 16 columns and writes up * gate / (1 + exp(-gate)): the feed-forward's activation
+// never makes a round trip through memory.
+#include "zi_common.cuh"
+
+ZI_DEFINE_LAST_ERROR(gemm_smallm)
+
+#define GS_WARPS 8
+#define GS_THREADS (GS_WARPS * 32)
+#define GS_UNROLL 4
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const bf16* p) {
+    // weights are read once: do not keep them in L1
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// Accumulate 16 rows of W (starting at `row0`, clamped to n_rows) against NT*8 tokens over this warp's k-steps.
+template <int NT>
+__device__ __forceinline__ void accumulate_rows(float (&acc)[NT][4], const bf16* __restrict__ W, const bf16* __restrict__ X,
+                                                int row0, int n_rows, int M, int K, long long ldw, long long ldx,
+                                                int warp, int lane) {
+    const int g = lane >> 2, tq = lane & 3;
+    const int r0 = min(row0 + g, n_rows - 1), r1 = min(row0 + g + 8, n_rows - 1);
+    const bf16* w0 = W + (long long)r0 * ldw + tq * 8;
+    const bf16* w1 = W + (long long)r1 * ldw + tq * 8;
+    const bf16* xp[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) xp[nt] = X + (long long)min(nt * 8 + g, M - 1) * ldx + tq * 8;
+    const int steps = K / 32;
+    int s = warp;
+    for (; s + (GS_UNROLL - 1) * GS_WARPS < steps; s += GS_UNROLL * GS_WARPS) {
+        uint4 a[GS_UNROLL], b[GS_UNROLL];
+#pragma unroll
+        for (int u = 0; u < GS_UNROLL; ++u) {
+            const int k = (s + u * GS_WARPS) * 32;
+            a[u] = ldg_stream(w0 + k);
+            b[u] = ldg_stream(w1 + k);
+        }
+#pragma unroll
+        for (int u = 0; u < GS_UNROLL; ++u) {
+            const int k = (s + u * GS_WARPS) * 32;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint4 x = *reinterpret_cast<const uint4*>(xp[nt] + k);
+                mma_bf16_16816(acc[nt], a[u].x, b[u].x, a[u].y, b[u].y, x.x, x.y);
+                mma_bf16_16816(acc[nt], a[u].z, b[u].z, a[u].w, b[u].w, x.z, x.w);
+            }
+        }
+    }
+    for (; s < steps; s += GS_WARPS) {
+        const int k = s * 32;
+        const uint4 a = ldg_stream(w0 + k), b = ldg_stream(w1 + k);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const uint4 x = *reinterpret_cast<const uint4*>(xp[nt] + k);
+            mma_bf16_16816(acc[nt], a.x, b.x, a.y, b.y, x.x, x.y);
+            mma_bf16_16816(acc[nt], a.z, b.z, a.w, b.w, x.z, x.w);
+        }
+    }
+}
+
+// Fragment bookkeeping: a thread's 16 bytes of row g are e0..e7.  First MMA: a0 = (e0,e1) = .x for row g,
+// a1 = .x of row g+8, a2 = (e2,e3) = .y for row g, a3 = .y of row g+8; b0 = x.x, b1 = x.y.  Second MMA: .z/.w.
+// Slot (tq*2, tq*2+1) of A meets slot (tq*2, tq*2+1) of B and slot (tq*2+8, +9) meets (tq*2+8, +9): each
+// pairs weight and activation of the same k.
+
+template <int NT, typename TC, bool SILU_MUL>
+__global__ void __launch_bounds__(GS_THREADS)
+gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const bf16* __restrict__ bias,
+                   TC* __restrict__ C, int M, int N, int K, long long ldx, long long ldw, long long ldc) {
+    // N: number of output columns.  With SILU_MUL, W has 2*N rows (gate rows, then up rows).
+    __shared__ float red[SILU_MUL ? 2 : 1][GS_WARPS][16][NT * 8 + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row0 = blockIdx.x * 16;
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+    accumulate_rows<NT>(acc, W, X, row0, N, M, K, ldw, ldx, warp, lane);
+    const int g = lane >> 2, tq = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        red[0][warp][g][nt * 8 + tq * 2] = acc[nt][0];
+        red[0][warp][g][nt * 8 + tq * 2 + 1] = acc[nt][1];
+        red[0][warp][g + 8][nt * 8 + tq * 2] = acc[nt][2];
+        red[0][warp][g + 8][nt * 8 + tq * 2 + 1] = acc[nt][3];
+    }
+    if (SILU_MUL) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+        accumulate_rows<NT>(acc, W + (long long)N * ldw, X, row0, N, M, K, ldw, ldx, warp, lane);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            red[SILU_MUL ? 1 : 0][warp][g][nt * 8 + tq * 2] = acc[nt][0];
+            red[SILU_MUL ? 1 : 0][warp][g][nt * 8 + tq * 2 + 1] = acc[nt][1];
+            red[SILU_MUL ? 1 : 0][warp][g + 8][nt * 8 + tq * 2] = acc[nt][2];
+            red[SILU_MUL ? 1 : 0][warp][g + 8][nt * 8 + tq * 2 + 1] = acc[nt][3];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 16 * NT * 8; i += GS_THREADS) {
+        const int r = i % 16, m = i / 16;             // consecutive threads -> consecutive output columns
+        const int n = row0 + r;
+        if (n >= N || m >= M) continue;
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < GS_WARPS; ++w) v += red[0][w][r][m];
+        if (SILU_MUL) {
+            float u = 0.0f;
+#pragma unroll
+            for (int w = 0; w < GS_WARPS; ++w) u += red[SILU_MUL ? 1 : 0][w][r][m];
+            // the unfused path rounds gate and up to bfloat16 before the activation; do the same
+            const float gr = __bfloat162float(__float2bfloat16_rn(v)), ur = __bfloat162float(__float2bfloat16_rn(u));
+            v = ur * gr / (1.0f + expf(-gr));
+        } else if (bias) {
+            v += __bfloat162float(bias[n]);
+        }
+        C[(long long)m * ldc + n] = from_f32<TC>(v);
+    }
+}
+
+template <int NT, typename TC, bool SILU>
+static void launch(const void* X, const void* W, const void* bias, void* C, int M, int N, int K, long long ldx,
+                   long long ldw, long long ldc, cudaStream_t stream) {
+    gemm_smallm_kernel<NT, TC, SILU><<<(N + 15) / 16, GS_THREADS, 0, stream>>>(
+        (const bf16*)X, (const bf16*)W, (const bf16*)bias, (TC*)C, M, N, K, ldx, ldw, ldc);
+}
+
+ZI_EXPORT int zi_gemm_smallm_max_rows() { return 16; }
+
+// silu_mul != 0: W is [2*N, K] (gate rows then up rows), C[m, n] = up * silu(gate); bias must be null.
+ZI_EXPORT int zi_gemm_smallm(const void* X, const void* W, const void* bias, void* C, int c_dtype, int M, int N, int K,
+                             long long ldx, long long ldw, long long ldc, int silu_mul, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 16) return zi_fail("gemm_smallm: M=%d rows; this kernel takes at most 16", M);
+    if (K <= 0 || K % 32 != 0) return zi_fail("gemm_smallm: K=%d must be a positive multiple of 32", K);
+    if (ldx % 8 != 0 || ldw % 8 != 0) return zi_fail("gemm_smallm: row strides (%lld, %lld) must be multiples of 8 elements", ldx, ldw);
+    if (((uintptr_t)X | (uintptr_t)W) & 15) return zi_fail("gemm_smallm: operands must be 16-byte aligned");
+    if (silu_mul && bias) return zi_fail("gemm_smallm: the fused activation takes no bias");
+    if (c_dtype != ZI_F32 && c_dtype != ZI_BF16) return zi_fail("gemm_smallm: unknown output dtype %d", c_dtype);
+    const bool f32 = c_dtype == ZI_F32;
+    if (silu_mul) {
+        if (M <= 8) { if (f32) launch<1, float, true>(X, W, bias, C, M, N, K, ldx, ldw, ldc, stream); else launch<1, bf16, true>(X, W, bias, C, M, N, K, ldx, ldw, ldc, stream); }
+        else        { if (f32) launch<2, float, true>(X, W, bias, C, M, N, K, ldx, ldw, ldc, stream); else launch<2, bf16, true>(X, W, bias, C, M, N, K, ldx, ldw, ldc, stream); }
+    } else {
+        if (M <= 8) { if (f32) launch<1, float, false>(X, W, bias, C, M, N, K, ldx, ldw, ldc, stream); else launch<1, bf16, false>(X, W, bias, C, M, N, K, ldx, ldw, ldc, stream); }
+        else        { if (f32) launch<2, float, false>(X, W, bias, C, M, N, K, ldx, ldw, ldc, stream); else launch<2, bf16, false>(X, W, bias, C, M, N, K, ldx, ldw, ldc, stream); }
+    }
+    return zi_check_launch("gemm_smallm");
+}

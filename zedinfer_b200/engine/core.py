@@ -242,7 +242,7 @@ class EngineCore:
         """The kernel libraries a run in ``dtype`` loads, for building them ahead of the first step."""
         libs = ["elementwise", "gemm_simt", "attention_generic", "sampling"]
         if parse_dtype(dtype) == torch.bfloat16:
-            libs.append("attention_mma")
+            libs += ["attention_mma", "gemm_smallm"]
         return libs
 
     # ---- requests -------------------------------------------------------------------------

@@ -20,9 +20,11 @@ _gemm_simt = Library("gemm_simt")
 _attention_generic = Library("attention_generic")
 _sampling = Library("sampling")
 _attention_mma = Library("attention_mma")
+_gemm_smallm = Library("gemm_smallm")
+SMALL_M_ROWS = 16                # the weight-streaming kernel takes up to this many rows
 
 __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "silu_mul", "cast",
-           "gemm_nt", "linear", "paged_attention", "attention", "decode_attention", "prefill_attention", "argmax", "sample", "repetition_penalty", "advance_decode"]
+           "gemm_nt", "linear", "gemm_smallm", "can_fuse_silu_mul", "paged_attention", "attention", "decode_attention", "prefill_attention", "argmax", "sample", "repetition_penalty", "advance_decode"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
@@ -133,15 +135,46 @@ def gemm_nt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
                     c_ll(out.stride(0)), stream())
 
 
+def _small_m_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= SMALL_M_ROWS
+            and x.shape[1] % 32 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_smallm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                silu_mul: bool = False) -> None:
+    """``out = x @ w.T + bias`` for at most 16 rows of ``x``: weights stream once from memory into the
+    tensor cores.  ``silu_mul``: ``w`` is ``[2*I, K]`` (gate rows, then up rows) and ``out[m, j] =
+    up * gate / (1 + exp(-gate))``."""
+    need_cuda(x, w, bias, out)
+    m, k = x.shape
+    n = w.shape[0] // 2 if silu_mul else w.shape[0]
+    if w.shape[1] != k or out.shape != (m, n) or out.stride(1) != 1:
+        raise KernelError(f"gemm_smallm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or (bias is not None and bias.dtype != torch.bfloat16):
+        raise KernelError("gemm_smallm: bfloat16 operands only")
+    _gemm_smallm.call("zi_gemm_smallm", ptr(x), ptr(w), ptr(bias), ptr(out), c_int(dtype_code(out.dtype)), c_int(m),
+                      c_int(n), c_int(k), c_ll(x.stride(0)), c_ll(w.stride(0)), c_ll(out.stride(0)),
+                      c_int(1 if silu_mul else 0), stream())
+
+
+def can_fuse_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, bias: Optional[torch.Tensor]) -> bool:
+    return bias is None and _small_m_ok(x, w_gate_up)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
     """``out = x @ w.T + bias``; picks the kernel by operand types.
 
     * any float32 operand: the SIMT kernel (true 32-bit arithmetic);
-    * bfloat16 x bfloat16: cuBLAS with float32 accumulation, the library product the reference's
-      engine uses as well; the output may be bfloat16 or float32.
+    * bfloat16 x bfloat16 with at most 16 rows (decode steps): the weight-streaming tensor-core kernel;
+    * bfloat16 x bfloat16 otherwise: cuBLAS with float32 accumulation, the library product the
+      reference's engine uses as well; the output may be bfloat16 or float32.
     """
     need_cuda(x, w, bias, out)
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and (bias is None or bias.dtype == torch.bfloat16):
+        if _small_m_ok(x, w) and out.stride(1) == 1:
+            gemm_smallm(x, w, bias, out)
+            return
         if out.dtype == torch.bfloat16:
             if bias is not None:
                 torch.addmm(bias, x, w.t(), out=out)
