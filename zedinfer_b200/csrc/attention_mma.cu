@@ -196,6 +196,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
     const int kvh = blockIdx.y / q_blocks, qb = blockIdx.y - kvh * q_blocks;
     const int n = blockIdx.z;
     const int group = n_heads / n_kv_heads;
+    pdl_launch_dependents();
+    pdl_wait();
     const int P = pos[n];
     const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
     const int c_begin = chunk * DEC_CHUNK;
@@ -317,6 +319,8 @@ decode_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ 
                     const int* __restrict__ pos, int n_heads, int n_chunks, int window) {
     const int item = blockIdx.x, n = item / n_heads;
     const int d = threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const int P = pos[n];
     const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
     const int c0 = lo / DEC_CHUNK, c1 = P / DEC_CHUNK;
@@ -479,17 +483,17 @@ ZI_EXPORT int zi_decode_attention(const void* q, const void* cache, void* out, f
     if (head_dim == 128) {
         const size_t smem = 16 * 128 * 2 + 4 * TILE_KEYS * 128 * 2;
         if (set_smem(decode_attention_kernel<128>, smem, "decode_attention")) return 1;
-        decode_attention_kernel<128><<<grid, ATT_THREADS, smem, stream>>>(
+        zi_launch(decode_attention_kernel<128>, grid, dim3(ATT_THREADS), smem, stream,
             (const bf16*)q, (const bf16*)cache, o_part, ml_part, tables, tok_seg, pos, n_heads, n_kv_heads, q_blocks,
             page_size, shift, max_blocks, page_stride, kv_stride, window, scale2);
-        decode_merge_kernel<128><<<n_tokens * n_heads, 128, 0, stream>>>(o_part, ml_part, (bf16*)out, pos, n_heads, n_chunks, window);
+        zi_launch(decode_merge_kernel<128>, dim3(n_tokens * n_heads), dim3(128), 0, stream, (const float*)o_part, (const float*)ml_part, (bf16*)out, pos, n_heads, n_chunks, window);
     } else {
         const size_t smem = 16 * 64 * 2 + 4 * TILE_KEYS * 64 * 2;
         if (set_smem(decode_attention_kernel<64>, smem, "decode_attention")) return 1;
-        decode_attention_kernel<64><<<grid, ATT_THREADS, smem, stream>>>(
+        zi_launch(decode_attention_kernel<64>, grid, dim3(ATT_THREADS), smem, stream,
             (const bf16*)q, (const bf16*)cache, o_part, ml_part, tables, tok_seg, pos, n_heads, n_kv_heads, q_blocks,
             page_size, shift, max_blocks, page_stride, kv_stride, window, scale2);
-        decode_merge_kernel<64><<<n_tokens * n_heads, 64, 0, stream>>>(o_part, ml_part, (bf16*)out, pos, n_heads, n_chunks, window);
+        zi_launch(decode_merge_kernel<64>, dim3(n_tokens * n_heads), dim3(64), 0, stream, (const float*)o_part, (const float*)ml_part, (bf16*)out, pos, n_heads, n_chunks, window);
     }
     return zi_check_launch("decode_attention");
 }

@@ -12,6 +12,8 @@ template <typename TT, typename TO>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                                  TO* __restrict__ out, int hidden, int vocab) {
     const int n = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     int id = ids[n];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);   // the host refuses ids outside the table
     const TT* src = table + (size_t)id * hidden;
@@ -25,7 +27,7 @@ ZI_EXPORT int zi_embedding(const void* table, int table_dtype, const int* ids, v
     if (hidden <= 0 || vocab <= 0) return zi_fail("embedding: hidden=%d vocab=%d must be positive", hidden, vocab);
     const int threads = hidden >= 1024 ? 256 : 128;
     ZI_DISPATCH(table_dtype, TT, ZI_DISPATCH(out_dtype, TO, {
-        embedding_kernel<TT, TO><<<n_tokens, threads, 0, stream>>>((const TT*)table, ids, (TO*)out, hidden, vocab);
+        zi_launch(embedding_kernel<TT, TO>, dim3(n_tokens), dim3(threads), 0, stream, (const TT*)table, ids, (TO*)out, hidden, vocab);
     }););
     return zi_check_launch("embedding");
 }
@@ -48,6 +50,8 @@ rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const
     extern __shared__ float row[];           // hidden floats
     __shared__ float scratch[32];
     const int r = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t src = row_idx ? (size_t)row_idx[r] : (size_t)r;
     float* res = residual + src * hidden;
     const TD* d = delta ? delta + src * hidden : nullptr;
@@ -77,6 +81,8 @@ rmsnorm_plain_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __r
     extern __shared__ float row[];
     __shared__ float scratch[32];
     const TX* xr = x + (size_t)blockIdx.x * hidden;
+    pdl_launch_dependents();
+    pdl_wait();
     float ss = 0.0f;
     for (int j = threadIdx.x; j < hidden; j += NORM_THREADS) {
         const float v = to_f32<TX>(xr[j]);
@@ -110,8 +116,8 @@ ZI_EXPORT int zi_add_rmsnorm(void* residual, const void* delta, int delta_dtype,
     ZI_DISPATCH(delta_dtype, TD, ZI_DISPATCH(w_dtype, TW, ZI_DISPATCH(out_dtype, TO, {
         auto fn = rmsnorm_kernel<TD, TW, TO>;
         if (norm_smem_ok(hidden, (const void*)fn)) return 1;
-        fn<<<rows, NORM_THREADS, smem, stream>>>((float*)residual, (const TD*)delta, (const TW*)w, (TO*)out,
-                                                 row_idx, eps, hidden, write_residual);
+        zi_launch(fn, dim3(rows), dim3(NORM_THREADS), smem, stream, (float*)residual, (const TD*)delta, (const TW*)w,
+                  (TO*)out, row_idx, eps, hidden, write_residual);
     });););
     return zi_check_launch("add_rmsnorm");
 }
@@ -124,7 +130,7 @@ ZI_EXPORT int zi_rmsnorm(const void* x, int x_dtype, const void* w, int w_dtype,
     ZI_DISPATCH(x_dtype, TX, ZI_DISPATCH(w_dtype, TW, ZI_DISPATCH(out_dtype, TO, {
         auto fn = rmsnorm_plain_kernel<TX, TW, TO>;
         if (norm_smem_ok(hidden, (const void*)fn)) return 1;
-        fn<<<rows, NORM_THREADS, smem, stream>>>((const TX*)x, (const TW*)w, (TO*)out, eps, hidden);
+        zi_launch(fn, dim3(rows), dim3(NORM_THREADS), smem, stream, (const TX*)x, (const TW*)w, (TO*)out, eps, hidden);
     });););
     return zi_check_launch("rmsnorm");
 }
@@ -140,52 +146,42 @@ ZI_EXPORT int zi_rmsnorm(const void* x, int x_dtype, const void* w, int w_dtype,
 //   pos[n]   absolute position of token n;  inv_freq[head_dim/2] float32
 // angle = float(pos) * inv_freq[k]; y[k] = a*c - b*s; y[k+half] = b*c + a*s.
 // ---------------------------------------------------------------------------------------
+// grid (n_tokens, n_heads + 2*n_kv_heads): one block per (token, head); q heads and k heads are rotated,
+// v heads copied.  head_dim/2 threads would do; 64 are launched and loop.
 template <typename T>
 __global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ cache,
                                    const int* __restrict__ tables, const int* __restrict__ tok_seg,
                                    const int* __restrict__ pos, const float* __restrict__ inv_freq,
                                    int row_stride, int n_heads, int n_kv_heads, int head_dim, int page_size,
                                    int max_blocks, long long page_stride, long long kv_stride, int write_kv) {
-    extern __shared__ float cs[];            // cos[half], sin[half]
-    const int n = blockIdx.x;
+    const int n = blockIdx.x, h = blockIdx.y;
     const int half = head_dim >> 1;
+    pdl_launch_dependents();
+    if (!write_kv && h >= n_heads) return;
+    pdl_wait();
     const int p = pos[n];
-    for (int k = threadIdx.x; k < half; k += blockDim.x) {
-        float s, c;
-        sincosf((float)p * inv_freq[k], &s, &c);
-        cs[k] = c;
-        cs[half + k] = s;
-    }
-    __syncthreads();
-    const T* row = qkv + (size_t)n * row_stride;
-    T* kdst = nullptr;
-    T* vdst = nullptr;
-    if (write_kv) {
+    const T* src = qkv + (size_t)n * row_stride + (size_t)h * head_dim;
+    T* dst;
+    if (h < n_heads) {
+        dst = q_out + ((size_t)n * n_heads + h) * head_dim;
+    } else {
         const int seg = tok_seg[n];
         const int page = tables[(size_t)seg * max_blocks + p / page_size];
         const int off = p % page_size;
-        kdst = cache + (size_t)page * page_stride + (size_t)off * head_dim;
-        vdst = kdst + kv_stride;
-    }
-    const int rot_heads = n_heads + (write_kv ? n_kv_heads : 0);
-    for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
-        const int h = idx / half, k = idx - h * half;
-        const float a = to_f32<T>(row[h * head_dim + k]);
-        const float b = to_f32<T>(row[h * head_dim + k + half]);
-        const float c = cs[k], s = cs[half + k];
-        const float y0 = a * c - b * s;
-        const float y1 = b * c + a * s;
-        T* dst = (h < n_heads) ? q_out + ((size_t)n * n_heads + h) * head_dim
-                               : kdst + (size_t)(h - n_heads) * page_size * head_dim;
-        dst[k] = from_f32<T>(y0);
-        dst[k + half] = from_f32<T>(y1);
-    }
-    if (write_kv) {
-        const T* vrow = row + (size_t)(n_heads + n_kv_heads) * head_dim;
-        for (int idx = threadIdx.x; idx < n_kv_heads * head_dim; idx += blockDim.x) {
-            const int h = idx / head_dim, d = idx - h * head_dim;
-            vdst[(size_t)h * page_size * head_dim + d] = vrow[idx];
+        const int kvh = (h - n_heads) % n_kv_heads;
+        const bool is_v = (h - n_heads) >= n_kv_heads;
+        dst = cache + (size_t)page * page_stride + (is_v ? kv_stride : 0) + ((size_t)kvh * page_size + off) * head_dim;
+        if (is_v) {
+            for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = src[d];
+            return;
         }
+    }
+    for (int k = threadIdx.x; k < half; k += blockDim.x) {
+        float s, c;
+        sincosf((float)p * inv_freq[k], &s, &c);
+        const float a = to_f32<T>(src[k]), b = to_f32<T>(src[k + half]);
+        dst[k] = from_f32<T>(a * c - b * s);
+        dst[k + half] = from_f32<T>(b * c + a * s);
     }
 }
 
@@ -197,12 +193,13 @@ ZI_EXPORT int zi_rope_append(const void* qkv, void* q_out, void* cache, int dtyp
     if (n_tokens <= 0) return 0;
     if (head_dim <= 0 || (head_dim & 1)) return zi_fail("rope: head_dim=%d must be positive and even", head_dim);
     if (n_heads <= 0 || n_kv_heads <= 0 || page_size <= 0) return zi_fail("rope: bad head counts or page size");
-    const size_t smem = (size_t)head_dim * sizeof(float);
+    if (n_heads + 2 * n_kv_heads > 65535) return zi_fail("rope: too many heads for one launch");
+    dim3 grid(n_tokens, n_heads + 2 * n_kv_heads);
+    const int threads = head_dim >= 128 ? 64 : 32;
     ZI_DISPATCH(dtype, T, {
-        rope_append_kernel<T><<<n_tokens, 128, smem, stream>>>((const T*)qkv, (T*)q_out, (T*)cache, tables, tok_seg,
-                                                               pos, inv_freq, row_stride, n_heads, n_kv_heads,
-                                                               head_dim, page_size, max_blocks, page_stride,
-                                                               kv_stride, write_kv);
+        zi_launch(rope_append_kernel<T>, grid, dim3(threads), 0, stream, (const T*)qkv, (T*)q_out, (T*)cache, tables,
+                  tok_seg, pos, inv_freq, row_stride, n_heads, n_kv_heads, head_dim, page_size, max_blocks,
+                  page_stride, kv_stride, write_kv);
     });
     return zi_check_launch("rope_append");
 }

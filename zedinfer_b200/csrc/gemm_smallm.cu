@@ -40,10 +40,12 @@ __device__ __forceinline__ uint4 ldg_stream(const bf16* p) {
 }
 
 // Accumulate 16 rows of W (starting at `row0`, clamped to n_rows) against NT*8 tokens over this warp's k-steps.
+// first_pass: the first weight loads are issued before pdl_wait(), so that they overlap with the tail of the
+// kernel that produces X.
 template <int NT>
 __device__ __forceinline__ void accumulate_rows(float (&acc)[NT][4], const bf16* __restrict__ W, const bf16* __restrict__ X,
                                                 int row0, int n_rows, int M, int K, long long ldw, long long ldx,
-                                                int warp, int lane) {
+                                                int warp, int lane, bool first_pass) {
     const int g = lane >> 2, tq = lane & 3;
     const int r0 = min(row0 + g, n_rows - 1), r1 = min(row0 + g + 8, n_rows - 1);
     const bf16* w0 = W + (long long)r0 * ldw + tq * 8;
@@ -53,6 +55,7 @@ __device__ __forceinline__ void accumulate_rows(float (&acc)[NT][4], const bf16*
     for (int nt = 0; nt < NT; ++nt) xp[nt] = X + (long long)min(nt * 8 + g, M - 1) * ldx + tq * 8;
     const int steps = K / 32;
     int s = warp;
+    bool waited = !first_pass;
     for (; s + (GS_UNROLL - 1) * GS_WARPS < steps; s += GS_UNROLL * GS_WARPS) {
         uint4 a[GS_UNROLL], b[GS_UNROLL];
 #pragma unroll
@@ -61,6 +64,7 @@ __device__ __forceinline__ void accumulate_rows(float (&acc)[NT][4], const bf16*
             a[u] = ldg_stream(w0 + k);
             b[u] = ldg_stream(w1 + k);
         }
+        if (!waited) { pdl_wait(); waited = true; }
 #pragma unroll
         for (int u = 0; u < GS_UNROLL; ++u) {
             const int k = (s + u * GS_WARPS) * 32;
@@ -75,6 +79,7 @@ __device__ __forceinline__ void accumulate_rows(float (&acc)[NT][4], const bf16*
     for (; s < steps; s += GS_WARPS) {
         const int k = s * 32;
         const uint4 a = ldg_stream(w0 + k), b = ldg_stream(w1 + k);
+        if (!waited) { pdl_wait(); waited = true; }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             const uint4 x = *reinterpret_cast<const uint4*>(xp[nt] + k);
@@ -82,6 +87,7 @@ __device__ __forceinline__ void accumulate_rows(float (&acc)[NT][4], const bf16*
             mma_bf16_16816(acc[nt], a.z, b.z, a.w, b.w, x.z, x.w);
         }
     }
+    if (!waited) pdl_wait();
 }
 
 // Fragment bookkeeping: a thread's 16 bytes of row g are e0..e7.  First MMA: a0 = (e0,e1) = .x for row g,
@@ -100,7 +106,8 @@ gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const
     float acc[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
-    accumulate_rows<NT>(acc, W, X, row0, N, M, K, ldw, ldx, warp, lane);
+    pdl_launch_dependents();
+    accumulate_rows<NT>(acc, W, X, row0, N, M, K, ldw, ldx, warp, lane, true);
     const int g = lane >> 2, tq = lane & 3;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -112,7 +119,7 @@ gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const
     if (SILU_MUL) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
-        accumulate_rows<NT>(acc, W + (long long)N * ldw, X, row0, N, M, K, ldw, ldx, warp, lane);
+        accumulate_rows<NT>(acc, W + (long long)N * ldw, X, row0, N, M, K, ldw, ldx, warp, lane, false);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             red[SILU_MUL ? 1 : 0][warp][g][nt * 8 + tq * 2] = acc[nt][0];
@@ -146,8 +153,8 @@ gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const
 template <int NT, typename TC, bool SILU>
 static void launch(const void* X, const void* W, const void* bias, void* C, int M, int N, int K, long long ldx,
                    long long ldw, long long ldc, cudaStream_t stream) {
-    gemm_smallm_kernel<NT, TC, SILU><<<(N + 15) / 16, GS_THREADS, 0, stream>>>(
-        (const bf16*)X, (const bf16*)W, (const bf16*)bias, (TC*)C, M, N, K, ldx, ldw, ldc);
+    zi_launch(gemm_smallm_kernel<NT, TC, SILU>, dim3((N + 15) / 16), dim3(GS_THREADS), 0, stream,
+              (const bf16*)X, (const bf16*)W, (const bf16*)bias, (TC*)C, M, N, K, ldx, ldw, ldc);
 }
 
 ZI_EXPORT int zi_gemm_smallm_max_rows() { return 16; }

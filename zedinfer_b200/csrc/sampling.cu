@@ -69,6 +69,8 @@ __device__ ArgPair block_argmax(const float* __restrict__ row, int vocab, ArgPai
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab, long long row_stride) {
     __shared__ ArgPair scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const ArgPair r = block_argmax(logits + (size_t)blockIdx.x * row_stride, vocab, scratch);
     if (threadIdx.x == 0) out[blockIdx.x] = r.i;
 }
@@ -76,7 +78,7 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
 ZI_EXPORT int zi_argmax(const float* logits, int* out, int rows, int vocab, long long row_stride, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return zi_fail("argmax: vocab=%d must be positive", vocab);
-    argmax_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, out, vocab, row_stride);
+    zi_launch(argmax_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, out, vocab, row_stride);
     return zi_check_launch("argmax");
 }
 
@@ -240,6 +242,8 @@ ZI_EXPORT int zi_sample(const float* logits, int* out, const float* temperature,
 // the next input and every position moves on by one.
 __global__ void advance_decode_kernel(int* __restrict__ ids, int* __restrict__ pos, const int* __restrict__ sampled, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     if (i < n) {
         ids[i] = sampled[i];
         pos[i] += 1;
@@ -248,6 +252,6 @@ __global__ void advance_decode_kernel(int* __restrict__ ids, int* __restrict__ p
 
 ZI_EXPORT int zi_advance_decode(int* ids, int* pos, const int* sampled, int n, cudaStream_t stream) {
     if (n <= 0) return 0;
-    advance_decode_kernel<<<(n + 127) / 128, 128, 0, stream>>>(ids, pos, sampled, n);
+    zi_launch(advance_decode_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, ids, pos, (const int*)sampled, n);
     return zi_check_launch("advance_decode");
 }

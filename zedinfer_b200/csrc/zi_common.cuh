@@ -116,6 +116,34 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return r;
 }
 
+// ---- programmatic dependent launch -------------------------------------------------------
+// Kernels of a step run back to back on one stream, each reading what the one before wrote.
+// Launched with zi_launch they may start while their predecessor is still draining: everything a
+// kernel does before pdl_wait() (index arithmetic, loads of weights, which no kernel of the step
+// writes) overlaps with the predecessor's tail; pdl_wait() returns once the predecessor has
+// finished and its writes are visible.  Every kernel launched this way calls pdl_wait() before it
+// touches anything another kernel of the step produces or still reads, and pdl_launch_dependents()
+// to let its own successor be scheduled early.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t zi_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Dispatch a dtype code to a type.  Usage: ZI_DISPATCH(code, T, { kernel<T><<<...>>>(...); })
 #define ZI_DISPATCH(code, T, ...)                        \
     do {                                                 \
