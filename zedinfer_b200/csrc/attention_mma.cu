@@ -5,8 +5,9 @@
 //             rows of one 16-row tile, so the keys and values of a request cross the memory bus once
 //             per key/value head.  The context is cut into chunks of DEC_CHUNK keys at absolute
 //             positions (a function of constants only, never of the batch); each chunk is one thread
-//             block and leaves an un-normalised partial result, and a second kernel merges the chunks
-//             of a query in rising order.
+//             block that has all of its keys and values in flight at once and leaves an un-normalised
+//             partial result; the block that finishes last for a query merges the query's chunks in
+//             rising order (an arrival counter, no waiting).
 //   prefill : a portion of a prompt.  One thread block per (64 query rows, query head); it walks the
 //             keys from the window's start to the diagonal in tiles of 64 with an online softmax.
 //
@@ -17,13 +18,14 @@
 //
 // Cache addressing (one call's slice of the pool): element (page, kv, kvh, off, d) lives at
 //   cache + page*page_stride + kv*kv_stride + (kvh*page_size + off)*head_dim + d.
+#define ZI_PDL_BIT 4
 #include "zi_common.cuh"
 
 ZI_DEFINE_LAST_ERROR(attention_mma)
 
 #define ATT_THREADS 128
 #define TILE_KEYS 64
-#define DEC_CHUNK 256
+#define DEC_CHUNK 128
 #define LOG2E 1.4426950408889634f
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -184,8 +186,9 @@ __device__ __forceinline__ void softmax_step(float (&S)[NKT][4], float (&O)[HD /
 // (running maximum in log2 units, and the sum).
 template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS)
-decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, float* __restrict__ o_part,
-                        float* __restrict__ ml_part, const int* __restrict__ tables, const int* __restrict__ tok_seg,
+decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, bf16* __restrict__ out,
+                        float* __restrict__ o_part, float* __restrict__ ml_part, int* __restrict__ counters,
+                        const int* __restrict__ tables, const int* __restrict__ tok_seg,
                         const int* __restrict__ pos, int n_heads, int n_kv_heads, int q_blocks, int page_size,
                         int page_shift, int max_blocks, long long page_stride, long long kv_stride, int window,
                         float scale2) {
@@ -196,9 +199,9 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
     const int kvh = blockIdx.y / q_blocks, qb = blockIdx.y - kvh * q_blocks;
     const int n = blockIdx.z;
     const int group = n_heads / n_kv_heads;
-    pdl_launch_dependents();
+    pdl_trigger_early();
     pdl_wait();
-    const int P = pos[n];
+    const int P = ld_dep(pos + n);
     const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
     const int c_begin = chunk * DEC_CHUNK;
     const int k_begin = c_begin > lo ? c_begin : lo;
@@ -219,13 +222,18 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
         uint4 v = make_uint4(0, 0, 0, 0);
         if (row < rows_valid) {
             const int h = kvh * group + qb * 16 + row;
-            v = *reinterpret_cast<const uint4*>(q + ((size_t)n * n_heads + h) * HD + c * 8);
+            v = ld_dep16(q + ((size_t)n * n_heads + h) * HD + c * 8);
         }
         *reinterpret_cast<uint4*>(smem_raw + swz<HD>(row, c)) = v;
     }
+    // a chunk is two tiles of 64 keys; both are requested before anything is computed
     const int t_first = k_begin / TILE_KEYS, t_last = k_end / TILE_KEYS;
     load_kv_tile<HD>(cr, sKV, sKV + TILE_BYTES, t_first * TILE_KEYS, k_begin, k_end);
     cp_async_commit();
+    if (t_last > t_first) {
+        load_kv_tile<HD>(cr, sKV + 2 * TILE_BYTES, sKV + 3 * TILE_BYTES, t_last * TILE_KEYS, k_begin, k_end);
+        cp_async_commit();
+    }
     __syncthreads();
     uint32_t qf[HD / 16][4];
 #pragma unroll
@@ -239,15 +247,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
 
     for (int t = t_first; t <= t_last; ++t) {
-        const int stage = (t - t_first) & 1;
-        if (t + 1 <= t_last) {
-            const uint32_t nb = sKV + (stage ^ 1) * 2 * TILE_BYTES;
-            load_kv_tile<HD>(cr, nb, nb + TILE_BYTES, (t + 1) * TILE_KEYS, k_begin, k_end);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        const int stage = t - t_first;
+        if (t == t_first && t_last > t_first) cp_async_wait<1>(); else cp_async_wait<0>();
         __syncthreads();
         const uint32_t sK = sKV + stage * 2 * TILE_BYTES, sV = sK + TILE_BYTES;
         const int key0 = t * TILE_KEYS + warp * 16;
@@ -257,8 +258,9 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
             softmax_step<HD, 2>(S, O, m, l, key0, lane, k_begin, k_end, k_begin, k_end, scale2);
             pv_accumulate<HD, 2>(O, S, sV, warp * 16, lane);
         }
-        __syncthreads();
     }
+    __syncthreads();                                          // the tiles are read; their memory is reused below
+    pdl_trigger_late();
     // row sums over the four threads of a row
     l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1); l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
     l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1); l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
@@ -310,31 +312,35 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
         ml[0] = Mr;
         ml[1] = Lr;
     }
-}
-
-// Merge the chunks a query saw, in rising order.  grid (n_tokens * n_heads), HD threads.
-template <int HD>
-__global__ void __launch_bounds__(HD)
-decode_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part, bf16* __restrict__ out,
-                    const int* __restrict__ pos, int n_heads, int n_chunks, int window) {
-    const int item = blockIdx.x, n = item / n_heads;
-    const int d = threadIdx.x;
-    pdl_launch_dependents();
-    pdl_wait();
-    const int P = pos[n];
-    const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
-    const int c0 = lo / DEC_CHUNK, c1 = P / DEC_CHUNK;
-    const float* ml = ml_part + (size_t)item * n_chunks * 2;
-    const float* op = o_part + (size_t)item * n_chunks * HD;
-    float M = -INFINITY;
-    for (int c = c0; c <= c1; ++c) M = fmaxf(M, ml[c * 2]);
-    float acc = 0.0f, L = 0.0f;
-    for (int c = c0; c <= c1; ++c) {
-        const float f = exp2f(ml[c * 2] - M);
-        L += ml[c * 2 + 1] * f;
-        acc += op[(size_t)c * HD + d] * f;
+    // The block that arrives last for this (token, head block) merges all of the query's chunks, in rising order.
+    __shared__ int is_last;
+    const int c_lo = lo / DEC_CHUNK, c_hi = P / DEC_CHUNK;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* counter = counters + (size_t)n * gridDim.y + blockIdx.y;
+        const int prev = atomicAdd(counter, 1);
+        is_last = (prev == c_hi - c_lo);
+        if (is_last) *counter = 0;                            // ready for the next launch
     }
-    out[(size_t)item * HD + d] = __float2bfloat16_rn(acc / L);
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < rows_valid * HD; i += ATT_THREADS) {
+        const int row = i / HD, d = i - row * HD;
+        const int h = kvh * group + qb * 16 + row;
+        const float* ml = ml_part + ((size_t)n * n_heads + h) * n_chunks * 2;
+        const float* op = o_part + ((size_t)n * n_heads + h) * n_chunks * HD;
+        float M = -INFINITY;
+        for (int c = c_lo; c <= c_hi; ++c) M = fmaxf(M, ld_dep(ml + c * 2));
+        float acc = 0.0f, L = 0.0f;
+        for (int c = c_lo; c <= c_hi; ++c) {
+            const float f = exp2f(ld_dep(ml + c * 2) - M);
+            L += ld_dep(ml + c * 2 + 1) * f;
+            acc += ld_dep(op + (size_t)c * HD + d) * f;
+        }
+        out[((size_t)n * n_heads + h) * HD + d] = __float2bfloat16_rn(acc / L);
+    }
 }
 
 // =======================================================================================
@@ -467,14 +473,16 @@ template <typename K> static int set_smem(K kernel, size_t bytes, const char* wh
 ZI_EXPORT int zi_decode_chunk_keys() { return DEC_CHUNK; }
 
 // n_chunks must be at least ceil((largest position + 1) / DEC_CHUNK); o_part and ml_part are scratch of
-// n_tokens*n_heads*n_chunks*head_dim and n_tokens*n_heads*n_chunks*2 floats.
+// n_tokens*n_heads*n_chunks*head_dim and n_tokens*n_heads*n_chunks*2 floats; counters holds one int per
+// (token, key/value head, block of 16 query heads), zero before the first launch and left at zero.
 ZI_EXPORT int zi_decode_attention(const void* q, const void* cache, void* out, float* o_part, float* ml_part,
-                                  const int* tables, const int* tok_seg, const int* pos, int n_tokens, int n_heads,
+                                  int* counters, const int* tables, const int* tok_seg, const int* pos, int n_tokens, int n_heads,
                                   int n_kv_heads, int head_dim, int page_size, int max_blocks, long long page_stride,
                                   long long kv_stride, int window, float scale, int n_chunks, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (check_common("decode_attention", n_heads, n_kv_heads, head_dim, page_size, max_blocks)) return 1;
     if (n_chunks <= 0 || n_chunks > 65535) return zi_fail("decode_attention: n_chunks=%d out of range", n_chunks);
+    if (!counters || !o_part || !ml_part) return zi_fail("decode_attention: scratch is missing");
     if (n_tokens > 65535) return zi_fail("decode_attention: %d tokens are more than one launch takes (65535)", n_tokens);
     const int group = n_heads / n_kv_heads, q_blocks = (group + 15) / 16;
     dim3 grid(n_chunks, n_kv_heads * q_blocks, n_tokens);
@@ -484,16 +492,14 @@ ZI_EXPORT int zi_decode_attention(const void* q, const void* cache, void* out, f
         const size_t smem = 16 * 128 * 2 + 4 * TILE_KEYS * 128 * 2;
         if (set_smem(decode_attention_kernel<128>, smem, "decode_attention")) return 1;
         zi_launch(decode_attention_kernel<128>, grid, dim3(ATT_THREADS), smem, stream,
-            (const bf16*)q, (const bf16*)cache, o_part, ml_part, tables, tok_seg, pos, n_heads, n_kv_heads, q_blocks,
-            page_size, shift, max_blocks, page_stride, kv_stride, window, scale2);
-        zi_launch(decode_merge_kernel<128>, dim3(n_tokens * n_heads), dim3(128), 0, stream, (const float*)o_part, (const float*)ml_part, (bf16*)out, pos, n_heads, n_chunks, window);
+            (const bf16*)q, (const bf16*)cache, (bf16*)out, o_part, ml_part, counters, tables, tok_seg, pos, n_heads,
+            n_kv_heads, q_blocks, page_size, shift, max_blocks, page_stride, kv_stride, window, scale2);
     } else {
         const size_t smem = 16 * 64 * 2 + 4 * TILE_KEYS * 64 * 2;
         if (set_smem(decode_attention_kernel<64>, smem, "decode_attention")) return 1;
         zi_launch(decode_attention_kernel<64>, grid, dim3(ATT_THREADS), smem, stream,
-            (const bf16*)q, (const bf16*)cache, o_part, ml_part, tables, tok_seg, pos, n_heads, n_kv_heads, q_blocks,
-            page_size, shift, max_blocks, page_stride, kv_stride, window, scale2);
-        zi_launch(decode_merge_kernel<64>, dim3(n_tokens * n_heads), dim3(64), 0, stream, (const float*)o_part, (const float*)ml_part, (bf16*)out, pos, n_heads, n_chunks, window);
+            (const bf16*)q, (const bf16*)cache, (bf16*)out, o_part, ml_part, counters, tables, tok_seg, pos, n_heads,
+            n_kv_heads, q_blocks, page_size, shift, max_blocks, page_stride, kv_stride, window, scale2);
     }
     return zi_check_launch("decode_attention");
 }

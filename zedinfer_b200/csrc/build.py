@@ -29,6 +29,7 @@ NVCC_FLAGS = [
     "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "-shared",
 ]
+NVCC_FLAGS += os.environ.get("ZEDINFER_NVCC_FLAGS", "").split()      # experiments, e.g. -DZI_PDL_TRIGGER=0
 # No --use_fast_math: division, sqrt, expf and sincosf keep their IEEE / full-range versions.
 
 # Libraries of the engine: name -> source file.  Extra nvcc arguments per library.

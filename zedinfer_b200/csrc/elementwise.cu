@@ -1,6 +1,7 @@
 // Row-wise and element-wise kernels: embedding gather, RMSNorm (plain, and fused with the
 // residual add), rotate-half RoPE fused with the append to the paged cache, SiLU-mul, cast.
 // All arithmetic is float32; storage types are float32 or bfloat16 per tensor.
+#define ZI_PDL_BIT 1
 #include "zi_common.cuh"
 
 ZI_DEFINE_LAST_ERROR(elementwise)
@@ -12,9 +13,10 @@ template <typename TT, typename TO>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                                  TO* __restrict__ out, int hidden, int vocab) {
     const int n = blockIdx.x;
-    pdl_launch_dependents();
+    pdl_trigger_early();
     pdl_wait();
-    int id = ids[n];
+    pdl_trigger_late();
+    int id = ld_dep(ids + n);
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);   // the host refuses ids outside the table
     const TT* src = table + (size_t)id * hidden;
     TO* dst = out + (size_t)n * hidden;
@@ -50,19 +52,20 @@ rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const
     extern __shared__ float row[];           // hidden floats
     __shared__ float scratch[32];
     const int r = blockIdx.x;
-    pdl_launch_dependents();
+    pdl_trigger_early();
     pdl_wait();
     const size_t src = row_idx ? (size_t)row_idx[r] : (size_t)r;
     float* res = residual + src * hidden;
     const TD* d = delta ? delta + src * hidden : nullptr;
     float ss = 0.0f;
     for (int j = threadIdx.x; j < hidden; j += NORM_THREADS) {
-        float x = res[j];
-        if (d) x = x + to_f32<TD>(d[j]);
+        float x = ld_dep(res + j);
+        if (d) x = x + ld_dep_f32<TD>(d + j);
         row[j] = x;
         ss = fmaf(x, x, ss);
     }
     ss = block_sum(ss, scratch);
+    pdl_trigger_late();
     const float rstd = 1.0f / sqrtf(ss / (float)hidden + eps);
     const bool wb = d && write_residual && !row_idx;
     TO* o = out + (size_t)r * hidden;
@@ -81,11 +84,11 @@ rmsnorm_plain_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __r
     extern __shared__ float row[];
     __shared__ float scratch[32];
     const TX* xr = x + (size_t)blockIdx.x * hidden;
-    pdl_launch_dependents();
+    pdl_trigger_early();
     pdl_wait();
     float ss = 0.0f;
     for (int j = threadIdx.x; j < hidden; j += NORM_THREADS) {
-        const float v = to_f32<TX>(xr[j]);
+        const float v = ld_dep_f32<TX>(xr + j);
         row[j] = v;
         ss = fmaf(v, v, ss);
     }
@@ -156,10 +159,11 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_
                                    int max_blocks, long long page_stride, long long kv_stride, int write_kv) {
     const int n = blockIdx.x, h = blockIdx.y;
     const int half = head_dim >> 1;
-    pdl_launch_dependents();
+    pdl_trigger_early();
     if (!write_kv && h >= n_heads) return;
     pdl_wait();
-    const int p = pos[n];
+    pdl_trigger_late();
+    const int p = ld_dep(pos + n);
     const T* src = qkv + (size_t)n * row_stride + (size_t)h * head_dim;
     T* dst;
     if (h < n_heads) {
@@ -172,14 +176,14 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_
         const bool is_v = (h - n_heads) >= n_kv_heads;
         dst = cache + (size_t)page * page_stride + (is_v ? kv_stride : 0) + ((size_t)kvh * page_size + off) * head_dim;
         if (is_v) {
-            for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = src[d];
+            for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = ld_dep(src + d);
             return;
         }
     }
     for (int k = threadIdx.x; k < half; k += blockDim.x) {
         float s, c;
         sincosf((float)p * inv_freq[k], &s, &c);
-        const float a = to_f32<T>(src[k]), b = to_f32<T>(src[k + half]);
+        const float a = ld_dep_f32<T>(src + k), b = ld_dep_f32<T>(src + k + half);
         dst[k] = from_f32<T>(a * c - b * s);
         dst[k + half] = from_f32<T>(b * c + a * s);
     }

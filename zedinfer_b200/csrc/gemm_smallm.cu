@@ -16,6 +16,7 @@
 // ACT_SILU_MUL variant: W holds gate rows and up rows ([2*I, K], gate first); the block computes
 // both for its 16 columns and writes up * gate / (1 + exp(-gate)): the feed-forward's activation
 // never makes a round trip through memory.
+#define ZI_PDL_BIT 2
 #include "zi_common.cuh"
 
 ZI_DEFINE_LAST_ERROR(gemm_smallm)
@@ -44,8 +45,8 @@ __device__ __forceinline__ uint4 ldg_stream(const bf16* p) {
 // kernel that produces X.
 template <int NT>
 __device__ __forceinline__ void accumulate_rows(float (&acc)[NT][4], const bf16* __restrict__ W, const bf16* __restrict__ X,
-                                                int row0, int n_rows, int M, int K, long long ldw, long long ldx,
-                                                int warp, int lane, bool first_pass) {
+                                                int row0, int n_rows, int M, int step_begin, int step_end,
+                                                long long ldw, long long ldx, int warp, int lane, bool first_pass) {
     const int g = lane >> 2, tq = lane & 3;
     const int r0 = min(row0 + g, n_rows - 1), r1 = min(row0 + g + 8, n_rows - 1);
     const bf16* w0 = W + (long long)r0 * ldw + tq * 8;
@@ -53,8 +54,8 @@ __device__ __forceinline__ void accumulate_rows(float (&acc)[NT][4], const bf16*
     const bf16* xp[NT];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) xp[nt] = X + (long long)min(nt * 8 + g, M - 1) * ldx + tq * 8;
-    const int steps = K / 32;
-    int s = warp;
+    const int steps = step_end;
+    int s = step_begin + warp;
     bool waited = !first_pass;
     for (; s + (GS_UNROLL - 1) * GS_WARPS < steps; s += GS_UNROLL * GS_WARPS) {
         uint4 a[GS_UNROLL], b[GS_UNROLL];
@@ -70,7 +71,7 @@ __device__ __forceinline__ void accumulate_rows(float (&acc)[NT][4], const bf16*
             const int k = (s + u * GS_WARPS) * 32;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                const uint4 x = *reinterpret_cast<const uint4*>(xp[nt] + k);
+                const uint4 x = ld_dep16(xp[nt] + k);
                 mma_bf16_16816(acc[nt], a[u].x, b[u].x, a[u].y, b[u].y, x.x, x.y);
                 mma_bf16_16816(acc[nt], a[u].z, b[u].z, a[u].w, b[u].w, x.z, x.w);
             }
@@ -82,7 +83,7 @@ __device__ __forceinline__ void accumulate_rows(float (&acc)[NT][4], const bf16*
         if (!waited) { pdl_wait(); waited = true; }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            const uint4 x = *reinterpret_cast<const uint4*>(xp[nt] + k);
+            const uint4 x = ld_dep16(xp[nt] + k);
             mma_bf16_16816(acc[nt], a.x, b.x, a.y, b.y, x.x, x.y);
             mma_bf16_16816(acc[nt], a.z, b.z, a.w, b.w, x.z, x.w);
         }
@@ -98,16 +99,23 @@ __device__ __forceinline__ void accumulate_rows(float (&acc)[NT][4], const bf16*
 template <int NT, typename TC, bool SILU_MUL>
 __global__ void __launch_bounds__(GS_THREADS)
 gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const bf16* __restrict__ bias,
-                   TC* __restrict__ C, int M, int N, int K, long long ldx, long long ldw, long long ldc) {
+                   TC* __restrict__ C, float* __restrict__ part, int* __restrict__ counters, int M, int N, int K,
+                   long long ldx, long long ldw, long long ldc) {
     // N: number of output columns.  With SILU_MUL, W has 2*N rows (gate rows, then up rows).
+    // gridDim.y > 1: K is cut into gridDim.y ranges, one block each; the blocks of a column tile leave their
+    // sums in `part` [gridDim.y][16][N] and the last one to arrive adds them in range order.
     __shared__ float red[SILU_MUL ? 2 : 1][GS_WARPS][16][NT * 8 + 1];
+    __shared__ int is_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row0 = blockIdx.x * 16;
+    const int ksplit = gridDim.y, ks = blockIdx.y;
+    const int steps = K / 32, per = (steps + ksplit - 1) / ksplit;
+    const int step_begin = ks * per, step_end = min(steps, step_begin + per);
     float acc[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
-    pdl_launch_dependents();
-    accumulate_rows<NT>(acc, W, X, row0, N, M, K, ldw, ldx, warp, lane, true);
+    pdl_trigger_early();
+    accumulate_rows<NT>(acc, W, X, row0, N, M, step_begin, step_end, ldw, ldx, warp, lane, true);
     const int g = lane >> 2, tq = lane & 3;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -119,7 +127,7 @@ gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const
     if (SILU_MUL) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
-        accumulate_rows<NT>(acc, W + (long long)N * ldw, X, row0, N, M, K, ldw, ldx, warp, lane, false);
+        accumulate_rows<NT>(acc, W + (long long)N * ldw, X, row0, N, M, step_begin, step_end, ldw, ldx, warp, lane, false);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             red[SILU_MUL ? 1 : 0][warp][g][nt * 8 + tq * 2] = acc[nt][0];
@@ -128,14 +136,40 @@ gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const
             red[SILU_MUL ? 1 : 0][warp][g + 8][nt * 8 + tq * 2 + 1] = acc[nt][3];
         }
     }
+    pdl_trigger_late();
     __syncthreads();
+    if (ksplit > 1) {
+        // leave this block's sums, then find out whether it is the last of its column tile
+        for (int i = threadIdx.x; i < 16 * NT * 8; i += GS_THREADS) {
+            const int r = i % 16, m = i / 16;
+            if (row0 + r >= N || m >= M) continue;
+            float v = 0.0f;
+#pragma unroll
+            for (int w = 0; w < GS_WARPS; ++w) v += red[0][w][r][m];
+            part[((size_t)ks * 16 + m) * N + row0 + r] = v;
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const int prev = atomicAdd(&counters[blockIdx.x], 1);
+            is_last = (prev == ksplit - 1);
+            if (is_last) counters[blockIdx.x] = 0;          // ready for the next launch
+        }
+        __syncthreads();
+        if (!is_last) return;
+        __threadfence();
+    }
     for (int i = threadIdx.x; i < 16 * NT * 8; i += GS_THREADS) {
         const int r = i % 16, m = i / 16;             // consecutive threads -> consecutive output columns
         const int n = row0 + r;
         if (n >= N || m >= M) continue;
         float v = 0.0f;
+        if (ksplit > 1) {
+            for (int k2 = 0; k2 < ksplit; ++k2) v += ld_dep(part + ((size_t)k2 * 16 + m) * N + n);
+        } else {
 #pragma unroll
-        for (int w = 0; w < GS_WARPS; ++w) v += red[0][w][r][m];
+            for (int w = 0; w < GS_WARPS; ++w) v += red[0][w][r][m];
+        }
         if (SILU_MUL) {
             float u = 0.0f;
 #pragma unroll
@@ -151,17 +185,37 @@ gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const
 }
 
 template <int NT, typename TC, bool SILU>
-static void launch(const void* X, const void* W, const void* bias, void* C, int M, int N, int K, long long ldx,
-                   long long ldw, long long ldc, cudaStream_t stream) {
-    zi_launch(gemm_smallm_kernel<NT, TC, SILU>, dim3((N + 15) / 16), dim3(GS_THREADS), 0, stream,
-              (const bf16*)X, (const bf16*)W, (const bf16*)bias, (TC*)C, M, N, K, ldx, ldw, ldc);
+static void launch(const void* X, const void* W, const void* bias, void* C, float* part, int* counters, int ksplit,
+                   int M, int N, int K, long long ldx, long long ldw, long long ldc, cudaStream_t stream) {
+    zi_launch(gemm_smallm_kernel<NT, TC, SILU>, dim3((N + 15) / 16, ksplit), dim3(GS_THREADS), 0, stream,
+              (const bf16*)X, (const bf16*)W, (const bf16*)bias, (TC*)C, part, counters, M, N, K, ldx, ldw, ldc);
 }
+
+// How many ranges K is cut into: a function of the weight's shape only.  Few column tiles (narrow outputs)
+// would leave most of the GPU idle, so their K is shared out until about two blocks per SM exist.
+ZI_EXPORT int zi_gemm_smallm_ksplit(int N, int K, int silu_mul) {
+    const int tiles = (N + 15) / 16, steps = K / 32;
+    if (silu_mul || tiles >= 296) return 1;
+    int ks = (296 + tiles - 1) / tiles;
+    if (ks > 8) ks = 8;
+    while (ks > 1 && steps / ks < GS_WARPS) --ks;          // at least one k-step per warp
+    return ks < 1 ? 1 : ks;
+}
+
+// Scratch the split needs: floats of `part` and ints of `counters` (zero before the first launch; the
+// kernel leaves them zero).
+ZI_EXPORT long long zi_gemm_smallm_part_floats(int N, int K, int silu_mul) {
+    const int ks = zi_gemm_smallm_ksplit(N, K, silu_mul);
+    return ks > 1 ? (long long)ks * 16 * N : 0;
+}
+ZI_EXPORT int zi_gemm_smallm_counter_ints(int N) { return (N + 15) / 16; }
 
 ZI_EXPORT int zi_gemm_smallm_max_rows() { return 16; }
 
 // silu_mul != 0: W is [2*N, K] (gate rows then up rows), C[m, n] = up * silu(gate); bias must be null.
-ZI_EXPORT int zi_gemm_smallm(const void* X, const void* W, const void* bias, void* C, int c_dtype, int M, int N, int K,
-                             long long ldx, long long ldw, long long ldc, int silu_mul, cudaStream_t stream) {
+ZI_EXPORT int zi_gemm_smallm(const void* X, const void* W, const void* bias, void* C, int c_dtype, float* part,
+                             int* counters, int M, int N, int K, long long ldx, long long ldw, long long ldc,
+                             int silu_mul, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 16) return zi_fail("gemm_smallm: M=%d rows; this kernel takes at most 16", M);
     if (K <= 0 || K % 32 != 0) return zi_fail("gemm_smallm: K=%d must be a positive multiple of 32", K);
@@ -170,12 +224,14 @@ ZI_EXPORT int zi_gemm_smallm(const void* X, const void* W, const void* bias, voi
     if (silu_mul && bias) return zi_fail("gemm_smallm: the fused activation takes no bias");
     if (c_dtype != ZI_F32 && c_dtype != ZI_BF16) return zi_fail("gemm_smallm: unknown output dtype %d", c_dtype);
     const bool f32 = c_dtype == ZI_F32;
+    const int ksplit = zi_gemm_smallm_ksplit(N, K, silu_mul);
+    if (ksplit > 1 && (!part || !counters)) return zi_fail("gemm_smallm: N=%d K=%d is split %d ways and needs scratch", N, K, ksplit);
     if (silu_mul) {
-        if (M <= 8) { if (f32) launch<1, float, true>(X, W, bias, C, M, N, K, ldx, ldw, ldc, stream); else launch<1, bf16, true>(X, W, bias, C, M, N, K, ldx, ldw, ldc, stream); }
-        else        { if (f32) launch<2, float, true>(X, W, bias, C, M, N, K, ldx, ldw, ldc, stream); else launch<2, bf16, true>(X, W, bias, C, M, N, K, ldx, ldw, ldc, stream); }
+        if (M <= 8) { if (f32) launch<1, float, true>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); else launch<1, bf16, true>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); }
+        else        { if (f32) launch<2, float, true>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); else launch<2, bf16, true>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); }
     } else {
-        if (M <= 8) { if (f32) launch<1, float, false>(X, W, bias, C, M, N, K, ldx, ldw, ldc, stream); else launch<1, bf16, false>(X, W, bias, C, M, N, K, ldx, ldw, ldc, stream); }
-        else        { if (f32) launch<2, float, false>(X, W, bias, C, M, N, K, ldx, ldw, ldc, stream); else launch<2, bf16, false>(X, W, bias, C, M, N, K, ldx, ldw, ldc, stream); }
+        if (M <= 8) { if (f32) launch<1, float, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); else launch<1, bf16, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); }
+        else        { if (f32) launch<2, float, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); else launch<2, bf16, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); }
     }
     return zi_check_launch("gemm_smallm");
 }

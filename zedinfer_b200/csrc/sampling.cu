@@ -14,6 +14,7 @@
 // The reference's CPU sampler walks the kept set in order of probability instead of index;
 // the distribution is the same.  All sums run in a fixed order (per-thread contiguous chunks,
 // then a fixed tree), so a row's result does not depend on the other rows.
+#define ZI_PDL_BIT 8
 #include "zi_common.cuh"
 
 ZI_DEFINE_LAST_ERROR(sampling)
@@ -37,7 +38,7 @@ __device__ __forceinline__ ArgPair better(ArgPair a, ArgPair b) {
 __device__ ArgPair block_argmax(const float* __restrict__ row, int vocab, ArgPair* scratch) {
     ArgPair best; best.v = -INFINITY; best.i = 0x7fffffff;
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        float v = row[i];
+        float v = ld_dep(row + i);
         if (v != v) v = -INFINITY;
         ArgPair c; c.v = v; c.i = i;
         best = better(best, c);
@@ -69,8 +70,9 @@ __device__ ArgPair block_argmax(const float* __restrict__ row, int vocab, ArgPai
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab, long long row_stride) {
     __shared__ ArgPair scratch[32];
-    pdl_launch_dependents();
+    pdl_trigger_early();
     pdl_wait();
+    pdl_trigger_late();
     const ArgPair r = block_argmax(logits + (size_t)blockIdx.x * row_stride, vocab, scratch);
     if (threadIdx.x == 0) out[blockIdx.x] = r.i;
 }
@@ -242,10 +244,11 @@ ZI_EXPORT int zi_sample(const float* logits, int* out, const float* temperature,
 // the next input and every position moves on by one.
 __global__ void advance_decode_kernel(int* __restrict__ ids, int* __restrict__ pos, const int* __restrict__ sampled, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    pdl_launch_dependents();
+    pdl_trigger_early();
     pdl_wait();
+    pdl_trigger_late();
     if (i < n) {
-        ids[i] = sampled[i];
+        ids[i] = ld_dep(sampled + i);
         pos[i] += 1;
     }
 }

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #define ZI_EXPORT extern "C" __attribute__((visibility("default")))
@@ -126,6 +127,55 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 // to let its own successor be scheduled early.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+// Where a kernel lets its successor be scheduled: at its start (ZI_PDL_TRIGGER=0), once its main loads are
+// issued (1, the default), or never before it ends (2).
+#ifndef ZI_PDL_TRIGGER
+#define ZI_PDL_TRIGGER 1
+#endif
+__device__ __forceinline__ void pdl_trigger_early() { if (ZI_PDL_TRIGGER == 0) pdl_launch_dependents(); }
+__device__ __forceinline__ void pdl_trigger_late() { if (ZI_PDL_TRIGGER == 1) pdl_launch_dependents(); }
+
+// Data that the predecessor wrote must be read with coherent loads after pdl_wait(): a load through the
+// read-only (non-coherent) path, which the compiler picks for `const __restrict__` pointers, may return what
+// the cache held before the predecessor's write, because this kernel was launched before that write.
+// ld_dep() loads through L2 only.
+__device__ __forceinline__ float ld_dep(const float* p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];\n" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ int ld_dep(const int* p) {
+    int v;
+    asm volatile("ld.global.cg.s32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ bf16 ld_dep(const bf16* p) {
+    unsigned short v;
+    asm volatile("ld.global.cg.u16 %0, [%1];\n" : "=h"(v) : "l"(p) : "memory");
+    return __ushort_as_bfloat16(v);
+}
+__device__ __forceinline__ uint4 ld_dep16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+template <typename T> __device__ __forceinline__ float ld_dep_f32(const T* p) { return to_f32<T>(ld_dep(p)); }
+
+// ZEDINFER_NO_PDL=1 launches the same kernels without the attribute (plain stream order); griddepcontrol
+// instructions are then no-ops.
+#ifndef ZI_PDL_BIT
+#define ZI_PDL_BIT 1
+#endif
+static inline bool zi_pdl_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* e = getenv("ZEDINFER_NO_PDL");
+        enabled = (e && e[0] == '1') ? 0 : 1;
+        const char* m = getenv("ZEDINFER_PDL_MASK");          // experiments: bit per library
+        if (enabled && m) enabled = (atoi(m) & ZI_PDL_BIT) ? 1 : 0;
+    }
+    return enabled == 1;
+}
 
 template <typename... KArgs, typename... Args>
 static inline cudaError_t zi_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -140,7 +190,7 @@ static inline cudaError_t zi_launch(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = zi_pdl_enabled() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -153,9 +153,32 @@ def gemm_smallm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
         raise KernelError(f"gemm_smallm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or (bias is not None and bias.dtype != torch.bfloat16):
         raise KernelError("gemm_smallm: bfloat16 operands only")
-    _gemm_smallm.call("zi_gemm_smallm", ptr(x), ptr(w), ptr(bias), ptr(out), c_int(dtype_code(out.dtype)), c_int(m),
-                      c_int(n), c_int(k), c_ll(x.stride(0)), c_ll(w.stride(0)), c_ll(out.stride(0)),
-                      c_int(1 if silu_mul else 0), stream())
+    part, counters = _smallm_scratch(x.device, n, k, silu_mul)
+    _gemm_smallm.call("zi_gemm_smallm", ptr(x), ptr(w), ptr(bias), ptr(out), c_int(dtype_code(out.dtype)), ptr(part),
+                      ptr(counters), c_int(m), c_int(n), c_int(k), c_ll(x.stride(0)), c_ll(w.stride(0)),
+                      c_ll(out.stride(0)), c_int(1 if silu_mul else 0), stream())
+
+
+_scratch = {}
+
+
+def _smallm_scratch(device, n: int, k: int, silu_mul: bool):
+    """Scratch of the split-K decode product: partial sums and arrival counters.  Allocated once per device and
+    grown on demand; the counters start at zero and every launch leaves them at zero.  One stream at a time."""
+    lib = _gemm_smallm.lib
+    lib.zi_gemm_smallm_part_floats.restype = c_ll
+    need = lib.zi_gemm_smallm_part_floats(c_int(n), c_int(k), c_int(1 if silu_mul else 0))
+    if need == 0:
+        return None, None
+    key = ("smallm", device)
+    if key not in _scratch:
+        # K is only split while there are fewer than 296 column tiles (N < 4736), at most 8 ways, 16 rows
+        _scratch[key] = (torch.empty(8 * 16 * 4736, dtype=torch.float32, device=device),
+                         torch.zeros(512, dtype=torch.int32, device=device))
+    part, counters = _scratch[key]
+    if part.numel() < need:
+        raise KernelError(f"gemm_smallm: scratch of {part.numel()} floats is too small for N={n}, K={k}")
+    return part, counters
 
 
 def can_fuse_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, bias: Optional[torch.Tensor]) -> bool:
@@ -205,7 +228,7 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tab
                             c_ll(kv_stride), c_int(window or 0), c_float(scale), stream())
 
 
-DECODE_CHUNK_KEYS = 256          # keys per thread block of the decode kernel (csrc/attention_mma.cu: DEC_CHUNK)
+DECODE_CHUNK_KEYS = 128          # keys per thread block of the decode kernel (csrc/attention_mma.cu: DEC_CHUNK)
 PREFILL_TILE_ROWS = 64           # query rows per thread block of the prefill kernel
 
 
@@ -213,10 +236,10 @@ def decode_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, o_
                      ml_part: torch.Tensor, tables: torch.Tensor, tok_seg: torch.Tensor, pos: torch.Tensor,
                      n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, page_stride: int, kv_stride: int,
                      window: Optional[int], scale: float, n_chunks: int) -> None:
-    """One query token per request, bfloat16, tensor cores, context cut into chunks of 256 keys.
+    """One query token per request, bfloat16, tensor cores, context cut into chunks of 128 keys.
 
     ``o_part`` (float32, ``n * n_heads * n_chunks * head_dim``) and ``ml_part`` (float32,
-    ``n * n_heads * n_chunks * 2``) are scratch; ``n_chunks >= ceil((largest position + 1) / 256)``.
+    ``n * n_heads * n_chunks * 2``) are scratch; ``n_chunks >= ceil((largest position + 1) / 128)``.
     """
     need_cuda(q, cache, out, o_part, ml_part, tables, tok_seg, pos)
     need_int32("tables", tables), need_int32("tok_seg", tok_seg), need_int32("pos", pos)
@@ -227,7 +250,14 @@ def decode_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, o_
     if o_part.dtype != torch.float32 or ml_part.dtype != torch.float32 or \
             o_part.numel() < n * n_heads * n_chunks * head_dim or ml_part.numel() < n * n_heads * n_chunks * 2:
         raise KernelError("decode_attention: scratch too small or not float32")
-    _attention_mma.call("zi_decode_attention", ptr(q), ptr(cache), ptr(out), ptr(o_part), ptr(ml_part), ptr(tables),
+    key = ("attn", q.device)
+    if key not in _scratch:
+        _scratch[key] = torch.zeros(1 << 16, dtype=torch.int32, device=q.device)       # arrival counters, left at zero
+    counters = _scratch[key]
+    if n * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16) > counters.numel():
+        raise KernelError("decode_attention: too many (token, head block) pairs for the arrival counters")
+    _attention_mma.call("zi_decode_attention", ptr(q), ptr(cache), ptr(out), ptr(o_part), ptr(ml_part), ptr(counters),
+                        ptr(tables),
                         ptr(tok_seg), ptr(pos), c_int(n), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
                         c_int(page_size), c_int(tables.shape[1]), c_ll(page_stride), c_ll(kv_stride),
                         c_int(window or 0), c_float(scale), c_int(n_chunks), stream())
