@@ -265,40 +265,34 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
     l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1); l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
     l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1); l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
 
-    // merge the four warps (each saw other keys) in warp order
+    // merge the four warps (each saw other keys) in warp order: every warp leaves m, l and its O in shared
+    // memory, then each thread adds the four contributions of a few (row, d) places
+    constexpr int OS = HD + 8;                                    // padded row of a warp's O
     float* red_m = reinterpret_cast<float*>(smem_raw);            // [4][16]
     float* red_l = red_m + 64;                                    // [4][16]
-    float* red_o = red_l + 64;                                    // [16][HD]
+    float* red_o = red_l + 64;                                    // [4][16][OS]
     const int g = lane >> 2, tq = lane & 3;
     if (tq == 0) {
         red_m[warp * 16 + g] = m[0]; red_m[warp * 16 + g + 8] = m[1];
         red_l[warp * 16 + g] = l[0]; red_l[warp * 16 + g + 8] = l[1];
     }
-    __syncthreads();
-    float M0 = -INFINITY, M1 = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) { M0 = fmaxf(M0, red_m[w * 16 + g]); M1 = fmaxf(M1, red_m[w * 16 + g + 8]); }
-    const float u0 = M0 == -INFINITY ? 0.0f : M0, u1 = M1 == -INFINITY ? 0.0f : M1;
-    const float f0 = exp2f(m[0] - u0), f1 = exp2f(m[1] - u1);
-    for (int w = 0; w < 4; ++w) {
-        if (warp == w) {
-#pragma unroll
-            for (int dn = 0; dn < HD / 8; ++dn) {
-                float* r0 = red_o + g * HD + dn * 8 + tq * 2;
-                float* r1 = red_o + (g + 8) * HD + dn * 8 + tq * 2;
-                if (w == 0) {
-                    r0[0] = O[dn][0] * f0; r0[1] = O[dn][1] * f0; r1[0] = O[dn][2] * f1; r1[1] = O[dn][3] * f1;
-                } else {
-                    r0[0] += O[dn][0] * f0; r0[1] += O[dn][1] * f0; r1[0] += O[dn][2] * f1; r1[1] += O[dn][3] * f1;
-                }
-            }
-        }
-        __syncthreads();
+    for (int dn = 0; dn < HD / 8; ++dn) {
+        *reinterpret_cast<float2*>(red_o + ((size_t)warp * 16 + g) * OS + dn * 8 + tq * 2) = make_float2(O[dn][0], O[dn][1]);
+        *reinterpret_cast<float2*>(red_o + ((size_t)warp * 16 + g + 8) * OS + dn * 8 + tq * 2) = make_float2(O[dn][2], O[dn][3]);
     }
+    __syncthreads();
     for (int i = threadIdx.x; i < rows_valid * HD; i += ATT_THREADS) {
         const int row = i / HD, d = i - row * HD;
+        float Mr = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) Mr = fmaxf(Mr, red_m[w * 16 + row]);
+        const float ur = Mr == -INFINITY ? 0.0f : Mr;
+        float acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) acc += red_o[((size_t)w * 16 + row) * OS + d] * exp2f(red_m[w * 16 + row] - ur);
         const int h = kvh * group + qb * 16 + row;
-        o_part[(((size_t)n * n_heads + h) * n_chunks + chunk) * HD + d] = red_o[row * HD + d];
+        o_part[(((size_t)n * n_heads + h) * n_chunks + chunk) * HD + d] = acc;
     }
     if (threadIdx.x < rows_valid) {
         const int row = threadIdx.x;
@@ -326,20 +320,41 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    // factors f[row][c] = exp2(m_c - M_row) and 1 / sum(l_c f_c), computed once per row into shared memory
+    float* fac = reinterpret_cast<float*>(smem_raw);                       // [16][n_c + 1]
+    const int n_c = c_hi - c_lo + 1;
+    for (int row = warp; row < rows_valid; row += ATT_THREADS / 32) {
+        const int h = kvh * group + qb * 16 + row;
+        const float* ml = ml_part + ((size_t)n * n_heads + h) * n_chunks * 2;
+        float M = -INFINITY;
+        for (int c = lane; c < n_c; c += 32) M = fmaxf(M, ld_l2(ml + (c_lo + c) * 2));
+        M = warp_max(M);
+        float L = 0.0f;
+        for (int c = lane; c < n_c; c += 32) {
+            const float f = exp2f(ld_l2(ml + (c_lo + c) * 2) - M);
+            fac[row * (n_c + 1) + c] = f;
+            L += ld_l2(ml + (c_lo + c) * 2 + 1) * f;
+        }
+        L = warp_sum(L);
+        if (lane == 0) fac[row * (n_c + 1) + n_c] = 1.0f / L;
+    }
+    __syncthreads();
     for (int i = threadIdx.x; i < rows_valid * HD; i += ATT_THREADS) {
         const int row = i / HD, d = i - row * HD;
         const int h = kvh * group + qb * 16 + row;
-        const float* ml = ml_part + ((size_t)n * n_heads + h) * n_chunks * 2;
-        const float* op = o_part + ((size_t)n * n_heads + h) * n_chunks * HD;
-        float M = -INFINITY;
-        for (int c = c_lo; c <= c_hi; ++c) M = fmaxf(M, ld_dep(ml + c * 2));
-        float acc = 0.0f, L = 0.0f;
-        for (int c = c_lo; c <= c_hi; ++c) {
-            const float f = exp2f(ld_dep(ml + c * 2) - M);
-            L += ld_dep(ml + c * 2 + 1) * f;
-            acc += ld_dep(op + (size_t)c * HD + d) * f;
+        const float* op = o_part + (((size_t)n * n_heads + h) * n_chunks + c_lo) * HD + d;
+        const float* f = fac + row * (n_c + 1);
+        float acc = 0.0f;
+        int c = 0;
+        for (; c + 8 <= n_c; c += 8) {                                      // eight loads in flight
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = ld_l2(op + (size_t)(c + e) * HD);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc += v[e] * f[c + e];
         }
-        out[((size_t)n * n_heads + h) * HD + d] = __float2bfloat16_rn(acc / L);
+        for (; c < n_c; ++c) acc += ld_l2(op + (size_t)c * HD) * f[c];
+        out[((size_t)n * n_heads + h) * HD + d] = __float2bfloat16_rn(acc * f[n_c]);
     }
 }
 
@@ -481,7 +496,8 @@ ZI_EXPORT int zi_decode_attention(const void* q, const void* cache, void* out, f
                                   long long kv_stride, int window, float scale, int n_chunks, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (check_common("decode_attention", n_heads, n_kv_heads, head_dim, page_size, max_blocks)) return 1;
-    if (n_chunks <= 0 || n_chunks > 65535) return zi_fail("decode_attention: n_chunks=%d out of range", n_chunks);
+    if (n_chunks <= 0 || n_chunks > 1000)
+        return zi_fail("decode_attention: n_chunks=%d out of range (contexts up to %d tokens)", n_chunks, 1000 * DEC_CHUNK);
     if (!counters || !o_part || !ml_part) return zi_fail("decode_attention: scratch is missing");
     if (n_tokens > 65535) return zi_fail("decode_attention: %d tokens are more than one launch takes (65535)", n_tokens);
     const int group = n_heads / n_kv_heads, q_blocks = (group + 15) / 16;

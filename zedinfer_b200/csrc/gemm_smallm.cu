@@ -165,7 +165,7 @@ gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const
         if (n >= N || m >= M) continue;
         float v = 0.0f;
         if (ksplit > 1) {
-            for (int k2 = 0; k2 < ksplit; ++k2) v += ld_dep(part + ((size_t)k2 * 16 + m) * N + n);
+            for (int k2 = 0; k2 < ksplit; ++k2) v += ld_l2(part + ((size_t)k2 * 16 + m) * N + n);
         } else {
 #pragma unroll
             for (int w = 0; w < GS_WARPS; ++w) v += red[0][w][r][m];
@@ -198,7 +198,7 @@ ZI_EXPORT int zi_gemm_smallm_ksplit(int N, int K, int silu_mul) {
     if (silu_mul || tiles >= 296) return 1;
     int ks = (296 + tiles - 1) / tiles;
     if (ks > 8) ks = 8;
-    while (ks > 1 && steps / ks < GS_WARPS) --ks;          // at least one k-step per warp
+    while (ks > 1 && steps / ks < 8 * GS_WARPS) --ks;      // a split costs a round trip: keep 8 k-steps per warp
     return ks < 1 ? 1 : ks;
 }
 
