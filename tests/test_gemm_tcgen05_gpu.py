@@ -1,0 +1,57 @@
+"""The tcgen05 / TMA / TMEM matrix product against a float64 product, in both orientations, with tails in
+every dimension."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def rand(*shape, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16).to(DEV)
+
+
+def check(m, n, k, swapped, out_dtype, with_bias, ld_pad=0):
+    from zedinfer_b200 import ops
+    x = rand(m, k + ld_pad, seed=1)[:, :k]
+    w = rand(n, k + ld_pad, seed=2, scale=0.05)[:, :k]
+    b = rand(n, seed=3) if with_bias else None
+    out = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEV)
+    ops.gemm_tcgen05(x, w, b, out, swapped=swapped)
+    torch.cuda.synchronize()
+    assert ops.tcgen05_status(DEV) == 0
+    ref = x.double().cpu() @ w.double().cpu().t()
+    if with_bias:
+        ref = ref + b.double().cpu()
+    got = out.double().cpu()
+    assert torch.isfinite(got).all()
+    tol = 2e-2 if out_dtype == torch.bfloat16 else 2e-3
+    assert torch.allclose(got, ref, atol=3 * tol, rtol=tol), float((got - ref).abs().max())
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (128, 16, 128), (256, 256, 1536), (300, 130, 200), (2048, 2048, 1536),
+                                   (1000, 1536, 8960), (130, 48, 72)])
+def test_normal_orientation(m, n, k):
+    check(m, n, k, False, torch.bfloat16, True)
+    check(m, n, k, False, torch.float32, False)
+
+
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 64, 100, 256])
+@pytest.mark.parametrize("n,k", [(128, 64), (1000, 1536), (1536, 8960), (200, 104)])
+def test_swapped_orientation(m, n, k):
+    check(m, n, k, True, torch.bfloat16, True)
+    check(m, n, k, True, torch.float32, False)
+
+
+def test_strided_rows_and_the_step_shapes():
+    check(64, 2048, 1536, True, torch.bfloat16, True, ld_pad=8)
+    check(2048, 17920, 1536, False, torch.bfloat16, False)
+    check(8, 151936, 1536, True, torch.float32, False)
+
+
+def test_refuses_what_tma_cannot_address():
+    from zedinfer_b200 import ops
+    x, w = rand(4, 36), rand(8, 36)
+    with pytest.raises(ops.KernelError, match="multiples of 8"):
+        ops.gemm_tcgen05(x, w, None, torch.empty(4, 8, dtype=torch.bfloat16, device=DEV))

@@ -21,10 +21,11 @@ _attention_generic = Library("attention_generic")
 _sampling = Library("sampling")
 _attention_mma = Library("attention_mma")
 _gemm_smallm = Library("gemm_smallm")
+_gemm_tcgen05 = Library("gemm_tcgen05")
 SMALL_M_ROWS = 16                # the weight-streaming kernel takes up to this many rows
 
 __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "silu_mul", "cast",
-           "gemm_nt", "linear", "gemm_smallm", "can_fuse_silu_mul", "paged_attention", "attention", "decode_attention", "prefill_attention", "argmax", "sample", "repetition_penalty", "advance_decode"]
+           "gemm_nt", "linear", "gemm_smallm", "gemm_tcgen05", "tcgen05_status", "can_fuse_silu_mul", "paged_attention", "attention", "decode_attention", "prefill_attention", "argmax", "sample", "repetition_penalty", "advance_decode"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
@@ -179,6 +180,44 @@ def _smallm_scratch(device, n: int, k: int, silu_mul: bool):
     if part.numel() < need:
         raise KernelError(f"gemm_smallm: scratch of {part.numel()} floats is too small for N={n}, K={k}")
     return part, counters
+
+
+def _tc_status(device) -> torch.Tensor:
+    key = ("tc_status", device)
+    if key not in _scratch:
+        _scratch[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _scratch[key]
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                 swapped: Optional[bool] = None) -> None:
+    """``out = x @ w.T + bias`` on the tcgen05 tensor cores (TMA-fed, accumulator in TMEM), bfloat16 operands.
+
+    ``swapped`` puts the weights on the 128-row side of the MMA and up to 256 rows of ``x`` on the narrow side
+    (decode); by default it is chosen by the number of rows.  A bounded wait that runs out inside the kernel is
+    reported by :func:`tcgen05_status`.
+    """
+    need_cuda(x, w, bias, out)
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape != (m, n) or out.stride(1) != 1 or x.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError(f"gemm_tcgen05: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or (bias is not None and bias.dtype != torch.bfloat16):
+        raise KernelError("gemm_tcgen05: bfloat16 operands only")
+    if swapped is None:
+        swapped = m <= 64
+    _gemm_tcgen05.call("zi_gemm_tcgen05", ptr(x), ptr(w), ptr(bias), ptr(out), c_int(dtype_code(out.dtype)),
+                       ptr(_tc_status(x.device)), c_int(m), c_int(n), c_int(k), c_ll(x.stride(0)), c_ll(w.stride(0)),
+                       c_ll(out.stride(0)), c_int(1 if swapped else 0), stream())
+
+
+def tcgen05_status(device) -> int:
+    """0, or the code of the role whose bounded wait ran out (1 producer, 2 MMA issuer, 3 epilogue); resets it."""
+    st = _tc_status(torch.device(device))
+    v = int(st.item())
+    if v:
+        st.zero_()
+    return v
 
 
 def can_fuse_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, bias: Optional[torch.Tensor]) -> bool:
