@@ -278,7 +278,7 @@ def test_repetition_penalty():
 def test_decode_attention_mma(nh, nkv, hd, ps, window):
     from zedinfer_b200 import ops
     t = torch.bfloat16
-    lens = [1, 255, 256, 257, 700, 64, 513]          # around the chunk edges (256) and the tile edges (64)
+    lens = [1, 255, 256, 257, 700, 64, 513, 1500]    # around tile edges (64), fewer tiles than blocks, several rounds
     pool, view, tables, ks, vs, page_stride, kv_stride = build_cache(len(lens), lens, nkv, hd, ps, t, seed=5)
     g = torch.Generator().manual_seed(9)
     q = torch.randn(len(lens), nh, hd, generator=g)
@@ -289,13 +289,9 @@ def test_decode_attention_mma(nh, nkv, hd, ps, window):
     n = len(lens)
     pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=dev())
     seg = torch.arange(n, dtype=torch.int32, device=dev())
-    n_chunks = -(-max(lens) // ops.DECODE_CHUNK_KEYS) + 1                   # one spare chunk, as a captured step has
-    o_part = torch.full((n * nh * n_chunks * hd,), float("nan"), device=dev())
-    ml_part = torch.full((n * nh * n_chunks * 2,), float("nan"), device=dev())
     out = torch.empty(n, nh * hd, dtype=t, device=dev())
     scale = 1.0 / math.sqrt(hd)
-    ops.decode_attention(qd, view, out, o_part, ml_part, tables, seg, pos, nh, nkv, hd, ps, page_stride, kv_stride,
-                         window, scale, n_chunks)
+    ops.decode_attention(qd, view, out, tables, seg, pos, nh, nkv, hd, ps, page_stride, kv_stride, window, scale)
     got = out.float().cpu().view(n, nh, hd)
     qf = qd.float().cpu()
     for r in range(n):
@@ -356,8 +352,7 @@ def test_attention_kernels_refuse_what_they_cannot_do():
     out = torch.empty(1, 64, dtype=t, device=dev())
     z = torch.zeros(1, dtype=torch.int32, device=dev())
     with pytest.raises(ops.KernelError, match="head_dim 64 or 128"):
-        ops.decode_attention(q, view, out, torch.empty(64, device=dev()), torch.empty(4, device=dev()), tables, z, z,
-                             2, 1, 32, 4, page_stride, kv_stride, None, 1.0, 1)
+        ops.decode_attention(q, view, out, tables, z, z, 2, 1, 32, 4, page_stride, kv_stride, None, 1.0)
     with pytest.raises(ops.KernelError, match="multiple of 8"):
         ops.paged_attention(torch.zeros(1, 2, 12, dtype=t, device=dev()), view, torch.empty(1, 24, dtype=t, device=dev()),
                             tables, z, z, 2, 1, 12, 4, page_stride, kv_stride, None, 1.0)

@@ -3,11 +3,11 @@
 //
 //   decode  : one query token per request.  The query heads that share a key/value head form the
 //             rows of one 16-row tile, so the keys and values of a request cross the memory bus once
-//             per key/value head.  The context is cut into chunks of DEC_CHUNK keys at absolute
-//             positions (a function of constants only, never of the batch); each chunk is one thread
-//             block that has all of its keys and values in flight at once and leaves an un-normalised
-//             partial result; the block that finishes last for a query merges the query's chunks in
-//             rising order (an arrival counter, no waiting).
+//             per key/value head.  A cluster of eight thread blocks shares a query group: the 64-key
+//             tiles of the context are dealt out to the blocks in turn (a function of the query's own
+//             position, never of the batch), each block keeps three tiles in flight, and the eight
+//             partial results are merged in rank order through distributed shared memory.  No scratch
+//             in global memory, no atomics.
 //   prefill : a portion of a prompt.  One thread block per (64 query rows, query head); it walks the
 //             keys from the window's start to the diagonal in tiles of 64 with an online softmax.
 //
@@ -21,11 +21,14 @@
 #define ZI_PDL_BIT 4
 #include "zi_common.cuh"
 
+#include <cooperative_groups.h>
+
 ZI_DEFINE_LAST_ERROR(attention_mma)
 
 #define ATT_THREADS 128
 #define TILE_KEYS 64
-#define DEC_CHUNK 128
+#define DEC_CLUSTER 8
+#define DEC_STAGES 3
 #define LOG2E 1.4426950408889634f
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -181,21 +184,26 @@ __device__ __forceinline__ void softmax_step(float (&S)[NKT][4], float (&O)[HD /
 // =======================================================================================
 // decode
 // =======================================================================================
-// grid (n_chunks, n_kv_heads * q_blocks, n_tokens); q_blocks = ceil(group / 16).
-// o_part [n_tokens, n_heads, n_chunks, HD] float32 (un-normalised), ml_part [n_tokens, n_heads, n_chunks, 2]
-// (running maximum in log2 units, and the sum).
+// grid (DEC_CLUSTER, n_kv_heads * q_blocks, n_tokens), thread-block clusters of DEC_CLUSTER along x;
+// q_blocks = ceil(group / 16).  The blocks of a cluster share one query group: block r takes the 64-key
+// tiles r, r + DEC_CLUSTER, ... of the visible range (a function of the query's own position only), streams
+// them through a three-stage cp.async ring, and leaves (m, l, O) of its keys in its shared memory.  After a
+// cluster barrier every block reads the eight partial results through distributed shared memory and writes
+// one eighth of the output columns, adding the blocks in rank order.
 template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS)
 decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, bf16* __restrict__ out,
-                        float* __restrict__ o_part, float* __restrict__ ml_part, int* __restrict__ counters,
                         const int* __restrict__ tables, const int* __restrict__ tok_seg,
                         const int* __restrict__ pos, int n_heads, int n_kv_heads, int q_blocks, int page_size,
                         int page_shift, int max_blocks, long long page_stride, long long kv_stride, int window,
                         float scale2) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int TILE_BYTES = TILE_KEYS * HD * 2;
+    constexpr int OS = HD + 8;                                    // padded row of float32 partial results
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int chunk = blockIdx.x, n_chunks = gridDim.x;
+    const int rank = blockIdx.x;                                  // gridDim.x == DEC_CLUSTER: rank in the cluster
     const int kvh = blockIdx.y / q_blocks, qb = blockIdx.y - kvh * q_blocks;
     const int n = blockIdx.z;
     const int group = n_heads / n_kv_heads;
@@ -203,19 +211,22 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
     pdl_wait();
     const int P = ld_dep(pos + n);
     const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
-    const int c_begin = chunk * DEC_CHUNK;
-    const int k_begin = c_begin > lo ? c_begin : lo;
-    const int k_end = (c_begin + DEC_CHUNK - 1 < P) ? c_begin + DEC_CHUNK - 1 : P;      // inclusive
-    if (k_begin > k_end) return;                                                          // nothing of this chunk is visible
+    const int t_lo = lo / TILE_KEYS, t_hi = P / TILE_KEYS;
+    const int n_mine = (t_hi - t_lo - rank >= 0) ? (t_hi - t_lo - rank) / DEC_CLUSTER + 1 : 0;
 
     CacheRef cr;
     cr.base = cache; cr.table = tables + (size_t)tok_seg[n] * max_blocks;
     cr.page_stride = page_stride; cr.kv_stride = kv_stride; cr.page_size = page_size; cr.page_shift = page_shift; cr.kvh = kvh;
 
-    const uint32_t sQ = smem_u32(smem_raw);                      // [16][HD]
-    const uint32_t sKV = sQ + 16 * HD * 2;                        // 2 stages x (K tile, V tile)
+    // shared memory: Q [16][HD] | DEC_STAGES x (K tile, V tile) | result of this block: m[16], l[16], O[16][OS]
+    // | in-block merge of the four warps: m[4][16], l[4][16], O[4][16][OS] (overlays the tile ring)
+    const uint32_t sQ = smem_u32(smem_raw);
+    unsigned char* ring = smem_raw + 16 * HD * 2;
+    const uint32_t sKV = smem_u32(ring);
+    float* res_m = reinterpret_cast<float*>(ring + (size_t)DEC_STAGES * 2 * TILE_BYTES);
+    float* res_l = res_m + 16;
+    float* res_o = res_l + 16;
 
-    // the group's queries -> shared memory (rows beyond the group are zeros)
     const int rows_valid = (group - qb * 16) < 16 ? (group - qb * 16) : 16;
     for (int i = threadIdx.x; i < 16 * (HD / 8); i += ATT_THREADS) {
         const int row = i / (HD / 8), c = i - row * (HD / 8);
@@ -226,12 +237,13 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
         }
         *reinterpret_cast<uint4*>(smem_raw + swz<HD>(row, c)) = v;
     }
-    // a chunk is two tiles of 64 keys; both are requested before anything is computed
-    const int t_first = k_begin / TILE_KEYS, t_last = k_end / TILE_KEYS;
-    load_kv_tile<HD>(cr, sKV, sKV + TILE_BYTES, t_first * TILE_KEYS, k_begin, k_end);
-    cp_async_commit();
-    if (t_last > t_first) {
-        load_kv_tile<HD>(cr, sKV + 2 * TILE_BYTES, sKV + 3 * TILE_BYTES, t_last * TILE_KEYS, k_begin, k_end);
+    // prologue: the first DEC_STAGES tiles of this block; one commit group per stage whether it holds a tile or not
+#pragma unroll
+    for (int s = 0; s < DEC_STAGES; ++s) {
+        if (s < n_mine) {
+            const int t = t_lo + rank + s * DEC_CLUSTER;
+            load_kv_tile<HD>(cr, sKV + s * 2 * TILE_BYTES, sKV + s * 2 * TILE_BYTES + TILE_BYTES, t * TILE_KEYS, lo, P);
+        }
         cp_async_commit();
     }
     __syncthreads();
@@ -246,29 +258,34 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
     for (int dn = 0; dn < HD / 8; ++dn) O[dn][0] = O[dn][1] = O[dn][2] = O[dn][3] = 0.0f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
 
-    for (int t = t_first; t <= t_last; ++t) {
-        const int stage = t - t_first;
-        if (t == t_first && t_last > t_first) cp_async_wait<1>(); else cp_async_wait<0>();
+    for (int i = 0; i < n_mine; ++i) {
+        const int stage = i % DEC_STAGES;
+        cp_async_wait<DEC_STAGES - 1>();                      // all but the newest DEC_STAGES-1 groups: tile i is here
         __syncthreads();
         const uint32_t sK = sKV + stage * 2 * TILE_BYTES, sV = sK + TILE_BYTES;
-        const int key0 = t * TILE_KEYS + warp * 16;
-        if (key0 <= k_end && key0 + 15 >= k_begin) {          // this warp's 16 keys hold something visible
+        const int key0 = (t_lo + rank + i * DEC_CLUSTER) * TILE_KEYS + warp * 16;
+        if (key0 <= P && key0 + 15 >= lo) {                   // this warp's 16 keys hold something visible
             float S[2][4];
             qk_scores<HD, 2>(S, qf, sK, warp * 16, lane);
-            softmax_step<HD, 2>(S, O, m, l, key0, lane, k_begin, k_end, k_begin, k_end, scale2);
+            softmax_step<HD, 2>(S, O, m, l, key0, lane, lo, P, lo, P, scale2);
             pv_accumulate<HD, 2>(O, S, sV, warp * 16, lane);
         }
+        __syncthreads();                                      // the stage is free again
+        if (i + DEC_STAGES < n_mine) {
+            const int t = t_lo + rank + (i + DEC_STAGES) * DEC_CLUSTER;
+            load_kv_tile<HD>(cr, sK, sV, t * TILE_KEYS, lo, P);
+        }
+        cp_async_commit();
     }
-    __syncthreads();                                          // the tiles are read; their memory is reused below
+    cp_async_wait<0>();
+    __syncthreads();
     pdl_trigger_late();
     // row sums over the four threads of a row
     l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1); l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
     l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1); l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
 
-    // merge the four warps (each saw other keys) in warp order: every warp leaves m, l and its O in shared
-    // memory, then each thread adds the four contributions of a few (row, d) places
-    constexpr int OS = HD + 8;                                    // padded row of a warp's O
-    float* red_m = reinterpret_cast<float*>(smem_raw);            // [4][16]
+    // merge the four warps (each saw other keys) in warp order, through the memory of the tile ring
+    float* red_m = reinterpret_cast<float*>(ring);               // [4][16]
     float* red_l = red_m + 64;                                    // [4][16]
     float* red_o = red_l + 64;                                    // [4][16][OS]
     const int g = lane >> 2, tq = lane & 3;
@@ -282,7 +299,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
         *reinterpret_cast<float2*>(red_o + ((size_t)warp * 16 + g + 8) * OS + dn * 8 + tq * 2) = make_float2(O[dn][2], O[dn][3]);
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < rows_valid * HD; i += ATT_THREADS) {
+    for (int i = threadIdx.x; i < 16 * HD; i += ATT_THREADS) {
         const int row = i / HD, d = i - row * HD;
         float Mr = -INFINITY;
 #pragma unroll
@@ -291,71 +308,45 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
         float acc = 0.0f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) acc += red_o[((size_t)w * 16 + row) * OS + d] * exp2f(red_m[w * 16 + row] - ur);
-        const int h = kvh * group + qb * 16 + row;
-        o_part[(((size_t)n * n_heads + h) * n_chunks + chunk) * HD + d] = acc;
+        res_o[(size_t)row * OS + d] = acc;
     }
-    if (threadIdx.x < rows_valid) {
+    if (threadIdx.x < 16) {
         const int row = threadIdx.x;
         float Mr = -INFINITY;
         for (int w = 0; w < 4; ++w) Mr = fmaxf(Mr, red_m[w * 16 + row]);
         const float ur = Mr == -INFINITY ? 0.0f : Mr;
         float Lr = 0.0f;
         for (int w = 0; w < 4; ++w) Lr += red_l[w * 16 + row] * exp2f(red_m[w * 16 + row] - ur);
-        const int h = kvh * group + qb * 16 + row;
-        float* ml = ml_part + (((size_t)n * n_heads + h) * n_chunks + chunk) * 2;
-        ml[0] = Mr;
-        ml[1] = Lr;
+        res_m[row] = Mr;
+        res_l[row] = Lr;
     }
-    // The block that arrives last for this (token, head block) merges all of the query's chunks, in rising order.
-    __shared__ int is_last;
-    const int c_lo = lo / DEC_CHUNK, c_hi = P / DEC_CHUNK;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int* counter = counters + (size_t)n * gridDim.y + blockIdx.y;
-        const int prev = atomicAdd(counter, 1);
-        is_last = (prev == c_hi - c_lo);
-        if (is_last) *counter = 0;                            // ready for the next launch
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    // factors f[row][c] = exp2(m_c - M_row) and 1 / sum(l_c f_c), computed once per row into shared memory
-    float* fac = reinterpret_cast<float*>(smem_raw);                       // [16][n_c + 1]
-    const int n_c = c_hi - c_lo + 1;
-    for (int row = warp; row < rows_valid; row += ATT_THREADS / 32) {
-        const int h = kvh * group + qb * 16 + row;
-        const float* ml = ml_part + ((size_t)n * n_heads + h) * n_chunks * 2;
+    cluster.sync();                                               // every block's (m, l, O) is in place
+    // block `rank` writes the columns d with d / (HD / DEC_CLUSTER) == rank, adding the blocks in rank order
+    constexpr int DW = HD / DEC_CLUSTER;
+    for (int i = threadIdx.x; i < rows_valid * DW; i += ATT_THREADS) {
+        const int row = i / DW, d = rank * DW + (i - row * DW);
+        float pm[DEC_CLUSTER], pl[DEC_CLUSTER], po[DEC_CLUSTER];
+#pragma unroll
+        for (int r = 0; r < DEC_CLUSTER; ++r) {
+            const float* rm = cluster.map_shared_rank(res_m, r);
+            pm[r] = rm[row];
+            pl[r] = rm[16 + row];
+            po[r] = rm[32 + (size_t)row * OS + d];
+        }
         float M = -INFINITY;
-        for (int c = lane; c < n_c; c += 32) M = fmaxf(M, ld_l2(ml + (c_lo + c) * 2));
-        M = warp_max(M);
-        float L = 0.0f;
-        for (int c = lane; c < n_c; c += 32) {
-            const float f = exp2f(ld_l2(ml + (c_lo + c) * 2) - M);
-            fac[row * (n_c + 1) + c] = f;
-            L += ld_l2(ml + (c_lo + c) * 2 + 1) * f;
+#pragma unroll
+        for (int r = 0; r < DEC_CLUSTER; ++r) M = fmaxf(M, pm[r]);
+        float acc = 0.0f, L = 0.0f;
+#pragma unroll
+        for (int r = 0; r < DEC_CLUSTER; ++r) {
+            const float f = exp2f(pm[r] - M);                     // blocks without keys: exp2(-inf) = 0
+            L += pl[r] * f;
+            acc += po[r] * f;
         }
-        L = warp_sum(L);
-        if (lane == 0) fac[row * (n_c + 1) + n_c] = 1.0f / L;
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < rows_valid * HD; i += ATT_THREADS) {
-        const int row = i / HD, d = i - row * HD;
         const int h = kvh * group + qb * 16 + row;
-        const float* op = o_part + (((size_t)n * n_heads + h) * n_chunks + c_lo) * HD + d;
-        const float* f = fac + row * (n_c + 1);
-        float acc = 0.0f;
-        int c = 0;
-        for (; c + 8 <= n_c; c += 8) {                                      // eight loads in flight
-            float v[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = ld_l2(op + (size_t)(c + e) * HD);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc += v[e] * f[c + e];
-        }
-        for (; c < n_c; ++c) acc += ld_l2(op + (size_t)c * HD) * f[c];
-        out[((size_t)n * n_heads + h) * HD + d] = __float2bfloat16_rn(acc * f[n_c]);
+        out[((size_t)n * n_heads + h) * HD + d] = __float2bfloat16_rn(acc / L);
     }
+    cluster.sync();                                               // nobody leaves while its memory is still read
 }
 
 // =======================================================================================
@@ -485,38 +476,45 @@ template <typename K> static int set_smem(K kernel, size_t bytes, const char* wh
     return 0;
 }
 
-ZI_EXPORT int zi_decode_chunk_keys() { return DEC_CHUNK; }
+template <typename K, typename... Args>
+static cudaError_t launch_cluster(K kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = DEC_CLUSTER; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
 
-// n_chunks must be at least ceil((largest position + 1) / DEC_CHUNK); o_part and ml_part are scratch of
-// n_tokens*n_heads*n_chunks*head_dim and n_tokens*n_heads*n_chunks*2 floats; counters holds one int per
-// (token, key/value head, block of 16 query heads), zero before the first launch and left at zero.
-ZI_EXPORT int zi_decode_attention(const void* q, const void* cache, void* out, float* o_part, float* ml_part,
-                                  int* counters, const int* tables, const int* tok_seg, const int* pos, int n_tokens, int n_heads,
-                                  int n_kv_heads, int head_dim, int page_size, int max_blocks, long long page_stride,
-                                  long long kv_stride, int window, float scale, int n_chunks, cudaStream_t stream) {
+ZI_EXPORT int zi_decode_attention(const void* q, const void* cache, void* out, const int* tables, const int* tok_seg,
+                                  const int* pos, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                  int page_size, int max_blocks, long long page_stride, long long kv_stride,
+                                  int window, float scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (check_common("decode_attention", n_heads, n_kv_heads, head_dim, page_size, max_blocks)) return 1;
-    if (n_chunks <= 0 || n_chunks > 1000)
-        return zi_fail("decode_attention: n_chunks=%d out of range (contexts up to %d tokens)", n_chunks, 1000 * DEC_CHUNK);
-    if (!counters || !o_part || !ml_part) return zi_fail("decode_attention: scratch is missing");
     if (n_tokens > 65535) return zi_fail("decode_attention: %d tokens are more than one launch takes (65535)", n_tokens);
     const int group = n_heads / n_kv_heads, q_blocks = (group + 15) / 16;
-    dim3 grid(n_chunks, n_kv_heads * q_blocks, n_tokens);
+    if (n_kv_heads * q_blocks > 65535) return zi_fail("decode_attention: too many head blocks for one launch");
+    dim3 grid(DEC_CLUSTER, n_kv_heads * q_blocks, n_tokens);
     const float scale2 = scale * LOG2E;
     const int shift = page_shift_of(page_size);
+    cudaError_t e;
     if (head_dim == 128) {
-        const size_t smem = 16 * 128 * 2 + 4 * TILE_KEYS * 128 * 2;
+        const size_t smem = 16 * 128 * 2 + DEC_STAGES * 2 * TILE_KEYS * 128 * 2 + (32 + 16 * (128 + 8)) * 4;
         if (set_smem(decode_attention_kernel<128>, smem, "decode_attention")) return 1;
-        zi_launch(decode_attention_kernel<128>, grid, dim3(ATT_THREADS), smem, stream,
-            (const bf16*)q, (const bf16*)cache, (bf16*)out, o_part, ml_part, counters, tables, tok_seg, pos, n_heads,
-            n_kv_heads, q_blocks, page_size, shift, max_blocks, page_stride, kv_stride, window, scale2);
+        e = launch_cluster(decode_attention_kernel<128>, grid, dim3(ATT_THREADS), smem, stream,
+                           (const bf16*)q, (const bf16*)cache, (bf16*)out, tables, tok_seg, pos, n_heads, n_kv_heads,
+                           q_blocks, page_size, shift, max_blocks, page_stride, kv_stride, window, scale2);
     } else {
-        const size_t smem = 16 * 64 * 2 + 4 * TILE_KEYS * 64 * 2;
+        const size_t smem = 16 * 64 * 2 + DEC_STAGES * 2 * TILE_KEYS * 64 * 2 + (32 + 16 * (64 + 8)) * 4;
         if (set_smem(decode_attention_kernel<64>, smem, "decode_attention")) return 1;
-        zi_launch(decode_attention_kernel<64>, grid, dim3(ATT_THREADS), smem, stream,
-            (const bf16*)q, (const bf16*)cache, (bf16*)out, o_part, ml_part, counters, tables, tok_seg, pos, n_heads,
-            n_kv_heads, q_blocks, page_size, shift, max_blocks, page_stride, kv_stride, window, scale2);
+        e = launch_cluster(decode_attention_kernel<64>, grid, dim3(ATT_THREADS), smem, stream,
+                           (const bf16*)q, (const bf16*)cache, (bf16*)out, tables, tok_seg, pos, n_heads, n_kv_heads,
+                           q_blocks, page_size, shift, max_blocks, page_stride, kv_stride, window, scale2);
     }
+    if (e != cudaSuccess) { cudaGetLastError(); return zi_fail("decode_attention: launch failed: %s", cudaGetErrorString(e)); }
     return zi_check_launch("decode_attention");
 }
 

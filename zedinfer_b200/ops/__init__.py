@@ -267,39 +267,24 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tab
                             c_ll(kv_stride), c_int(window or 0), c_float(scale), stream())
 
 
-DECODE_CHUNK_KEYS = 128          # keys per thread block of the decode kernel (csrc/attention_mma.cu: DEC_CHUNK)
 PREFILL_TILE_ROWS = 64           # query rows per thread block of the prefill kernel
 
 
-def decode_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, o_part: torch.Tensor,
-                     ml_part: torch.Tensor, tables: torch.Tensor, tok_seg: torch.Tensor, pos: torch.Tensor,
-                     n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, page_stride: int, kv_stride: int,
-                     window: Optional[int], scale: float, n_chunks: int) -> None:
-    """One query token per request, bfloat16, tensor cores, context cut into chunks of 128 keys.
-
-    ``o_part`` (float32, ``n * n_heads * n_chunks * head_dim``) and ``ml_part`` (float32,
-    ``n * n_heads * n_chunks * 2``) are scratch; ``n_chunks >= ceil((largest position + 1) / 128)``.
-    """
-    need_cuda(q, cache, out, o_part, ml_part, tables, tok_seg, pos)
+def decode_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
+                     tok_seg: torch.Tensor, pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                     page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float) -> None:
+    """One query token per request, bfloat16, tensor cores; a cluster of eight thread blocks per
+    (request, key/value head) shares the context and merges through distributed shared memory."""
+    need_cuda(q, cache, out, tables, tok_seg, pos)
     need_int32("tables", tables), need_int32("tok_seg", tok_seg), need_int32("pos", pos)
     need_contiguous("q", q), need_contiguous("out", out)
     n = q.shape[0]
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("decode_attention: bfloat16 only")
-    if o_part.dtype != torch.float32 or ml_part.dtype != torch.float32 or \
-            o_part.numel() < n * n_heads * n_chunks * head_dim or ml_part.numel() < n * n_heads * n_chunks * 2:
-        raise KernelError("decode_attention: scratch too small or not float32")
-    key = ("attn", q.device)
-    if key not in _scratch:
-        _scratch[key] = torch.zeros(1 << 16, dtype=torch.int32, device=q.device)       # arrival counters, left at zero
-    counters = _scratch[key]
-    if n * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16) > counters.numel():
-        raise KernelError("decode_attention: too many (token, head block) pairs for the arrival counters")
-    _attention_mma.call("zi_decode_attention", ptr(q), ptr(cache), ptr(out), ptr(o_part), ptr(ml_part), ptr(counters),
-                        ptr(tables),
-                        ptr(tok_seg), ptr(pos), c_int(n), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
-                        c_int(page_size), c_int(tables.shape[1]), c_ll(page_stride), c_ll(kv_stride),
-                        c_int(window or 0), c_float(scale), c_int(n_chunks), stream())
+    _attention_mma.call("zi_decode_attention", ptr(q), ptr(cache), ptr(out), ptr(tables), ptr(tok_seg), ptr(pos),
+                        c_int(n), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size),
+                        c_int(tables.shape[1]), c_ll(page_stride), c_ll(kv_stride), c_int(window or 0),
+                        c_float(scale), stream())
 
 
 def prefill_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
@@ -330,12 +315,8 @@ def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv
     if q.dtype == torch.bfloat16 and head_dim in (64, 128):
         n = q.shape[0]
         if ctx.decode_only:
-            n_chunks = max(1, -(-ctx.max_kv_len // DECODE_CHUNK_KEYS))
-            o_part = torch.empty(n * n_heads * n_chunks * head_dim, dtype=torch.float32, device=q.device)
-            ml_part = torch.empty(n * n_heads * n_chunks * 2, dtype=torch.float32, device=q.device)
-            decode_attention(q, cache.tensor, out, o_part, ml_part, tables, ctx.tok_seg, ctx.positions, n_heads,
-                             n_kv_heads, head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale,
-                             n_chunks)
+            decode_attention(q, cache.tensor, out, tables, ctx.tok_seg, ctx.positions, n_heads, n_kv_heads, head_dim,
+                             cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
             return
         tiles = ctx.extras.get("attn_tiles")
         if tiles is not None:
