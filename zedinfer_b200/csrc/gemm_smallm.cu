@@ -235,3 +235,65 @@ ZI_EXPORT int zi_gemm_smallm(const void* X, const void* W, const void* bias, voi
     }
     return zi_check_launch("gemm_smallm");
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// The same product with built-in scratch, for callers that must not allocate (see gemm_smallm_noalloc.h).
+// ---------------------------------------------------------------------------------------------------------
+#include "gemm_smallm_noalloc.h"
+
+// Partial sums of the K ranges, then the arrival counters.  In host code this name is only a handle for
+// cudaGetSymbolAddress; the kernel receives the device address that call returns.
+static __device__ __align__(256) unsigned char zi_noalloc_scratch[ZI_NOALLOC_SCRATCH_BYTES];
+
+#define ZI_NOALLOC_MAX_DEVICES 64
+static void* zi_noalloc_base[ZI_NOALLOC_MAX_DEVICES];      // device address of the array, per device ordinal
+
+// Set-up, once per device, with that device current: resolve the array's address on this device.
+static int zi_noalloc_setup(int device, void** base) {
+    if (device < 0 || device >= ZI_NOALLOC_MAX_DEVICES) return zi_fail("gemm_smallm_noalloc: device ordinal %d out of range", device);
+    if (!zi_noalloc_base[device]) {
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void**)&ptr, zi_noalloc_scratch);
+        if (e != cudaSuccess || !ptr) {
+            cudaGetLastError();
+            return zi_fail("gemm_smallm_noalloc: cudaGetSymbolAddress failed on device %d: %s", device, cudaGetErrorString(e));
+        }
+        zi_noalloc_base[device] = ptr;
+    }
+    *base = zi_noalloc_base[device];
+    return 0;
+}
+
+ZI_EXPORT int zi_gemm_smallm_noalloc(const void* X, const void* W, const void* bias, void* C, int c_dtype, int M, int N,
+                                     int K, long long ldx, long long ldw, long long ldc, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 16) return zi_fail("gemm_smallm_noalloc: M=%d rows; this kernel takes at most 16", M);
+    if (K <= 0 || K % 32 != 0) return zi_fail("gemm_smallm_noalloc: K=%d must be a positive multiple of 32", K);
+    if (ldx % 8 != 0 || ldw % 8 != 0) return zi_fail("gemm_smallm_noalloc: row strides (%lld, %lld) must be multiples of 8 elements", ldx, ldw);
+    if (((uintptr_t)X | (uintptr_t)W) & 15) return zi_fail("gemm_smallm_noalloc: operands must be 16-byte aligned");
+    if (c_dtype != ZI_F32 && c_dtype != ZI_BF16) return zi_fail("gemm_smallm_noalloc: unknown output dtype %d", c_dtype);
+    const int ksplit = zi_gemm_smallm_ksplit(N, K, 0);
+    const int tiles = (N + 15) / 16;
+    float* part = nullptr;
+    int* counters = nullptr;
+    if (ksplit > 1) {
+        const long long need = (long long)ksplit * 16 * N;
+        if (need > ZI_NOALLOC_PART_FLOATS || tiles > ZI_NOALLOC_COUNTER_INTS || ksplit > ZI_NOALLOC_MAX_SPLIT)
+            return zi_fail("gemm_smallm_noalloc: N=%d, K=%d is cut into %d K ranges and needs %lld floats of scratch; "
+                           "the built-in array holds %d (N up to %d)", N, K, ksplit, need, ZI_NOALLOC_PART_FLOATS, ZI_NOALLOC_MAX_N);
+        int device = -1;
+        cudaError_t e = cudaGetDevice(&device);
+        if (e != cudaSuccess) return zi_fail("gemm_smallm_noalloc: cudaGetDevice failed: %s", cudaGetErrorString(e));
+        void* base = nullptr;
+        if (zi_noalloc_setup(device, &base)) return 1;
+        part = reinterpret_cast<float*>(base);
+        counters = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(base) + (size_t)ZI_NOALLOC_PART_FLOATS * 4);
+        // the counters must start at zero whatever an earlier (possibly aborted) call left behind
+        e = cudaMemsetAsync(counters, 0, (size_t)tiles * sizeof(int), stream);
+        if (e != cudaSuccess) return zi_fail("gemm_smallm_noalloc: clearing the counters failed: %s", cudaGetErrorString(e));
+    }
+    const bool f32 = c_dtype == ZI_F32;
+    if (M <= 8) { if (f32) launch<1, float, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); else launch<1, bf16, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); }
+    else        { if (f32) launch<2, float, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); else launch<2, bf16, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); }
+    return zi_check_launch("gemm_smallm_noalloc");
+}
