@@ -79,17 +79,26 @@ __device__ __forceinline__ const bf16* key_row(const CacheRef& cr, int key, int 
 }
 
 // Copy keys key0 .. key0+63 (K and V rows) into the swizzled tiles; rows outside [lo, hi] become zeros.
+// Two threads share a row and take alternate 16-byte chunks, so the page lookup and the address
+// arithmetic happen once per row and thread, and a pair of threads reads whole 32-byte sectors.
 template <int HD>
 __device__ __forceinline__ void load_kv_tile(const CacheRef& cr, uint32_t sK, uint32_t sV, int key0, int lo, int hi) {
     constexpr int CH = HD / 8;
-    for (int i = threadIdx.x; i < TILE_KEYS * CH; i += ATT_THREADS) {
-        const int row = i / CH, c = i - row * CH;
+    const int h = threadIdx.x & 1;
+    for (int row = threadIdx.x >> 1; row < TILE_KEYS; row += ATT_THREADS / 2) {
         const int key = key0 + row;
         const bool valid = key >= lo && key <= hi;
-        const bf16* src = valid ? key_row(cr, key, HD) + c * 8 : cr.base;
-        const uint32_t off = swz<HD>(row, c);
-        cp_async16(sK + off, src, valid);
-        cp_async16(sV + off, valid ? src + cr.kv_stride : src, valid);
+        const bf16* src = valid ? key_row(cr, key, HD) : cr.base;
+        const bf16* srcv = valid ? src + cr.kv_stride : cr.base;
+        const uint32_t rowoff = (uint32_t)(row * HD * 2);
+        const int r7 = row & 7;
+#pragma unroll
+        for (int j = 0; j < CH / 2; ++j) {
+            const int c = 2 * j + h;
+            const uint32_t off = rowoff + (uint32_t)((c ^ r7) << 4);
+            cp_async16(sK + off, valid ? src + c * 8 : src, valid);
+            cp_async16(sV + off, valid ? srcv + c * 8 : srcv, valid);
+        }
     }
 }
 
@@ -131,10 +140,18 @@ __device__ __forceinline__ void pv_accumulate(float (&O)[HD / 8][4], const float
     }
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));       // exp2(-inf) = +0
+    return y;
+}
+
 // Online softmax step on a warp's score tile.  Thread holds rows g = lane/4 (values [0],[1]) and g+8
-// ([2],[3]) at keys key0 + nt*8 + (lane%4)*2 + {0,1}.  row_hi / row_lo: last / first key each row may
-// see.  S comes in as raw dot products and leaves as probabilities relative to the running maximum.
-template <int HD, int NKT>
+// ([2],[3]) at keys key0 + nt*8 + (lane%4)*2 + {0,1}.  lo / hi: first / last key each row may see.
+// S comes in as raw dot products and leaves as probabilities relative to the running maximum; m is kept
+// in units of raw scores (scale2 > 0, so the maximum is the same), and exp2(s*scale2 - m*scale2) is one
+// fused multiply-add and one ex2.  MASKED = false is for tiles every row of the warp sees in full.
+template <int HD, int NKT, bool MASKED = true>
 __device__ __forceinline__ void softmax_step(float (&S)[NKT][4], float (&O)[HD / 8][4], float (&m)[2], float (&l)[2],
                                              int key0, int lane, int lo0, int hi0, int lo1, int hi1, float scale2) {
     float mx0 = -INFINITY, mx1 = -INFINITY;
@@ -142,13 +159,13 @@ __device__ __forceinline__ void softmax_step(float (&S)[NKT][4], float (&O)[HD /
     for (int nt = 0; nt < NKT; ++nt) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-            const int key = key0 + nt * 8 + (lane & 3) * 2 + e;
-            const float s0 = (key >= lo0 && key <= hi0) ? S[nt][e] * scale2 : -INFINITY;
-            const float s1 = (key >= lo1 && key <= hi1) ? S[nt][2 + e] * scale2 : -INFINITY;
-            S[nt][e] = s0;
-            S[nt][2 + e] = s1;
-            mx0 = fmaxf(mx0, s0);
-            mx1 = fmaxf(mx1, s1);
+            if (MASKED) {
+                const int key = key0 + nt * 8 + (lane & 3) * 2 + e;
+                if (!(key >= lo0 && key <= hi0)) S[nt][e] = -INFINITY;
+                if (!(key >= lo1 && key <= hi1)) S[nt][2 + e] = -INFINITY;
+            }
+            mx0 = fmaxf(mx0, S[nt][e]);
+            mx1 = fmaxf(mx1, S[nt][2 + e]);
         }
     }
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
@@ -157,7 +174,8 @@ __device__ __forceinline__ void softmax_step(float (&S)[NKT][4], float (&O)[HD /
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
     const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
     const float use0 = mn0 == -INFINITY ? 0.0f : mn0, use1 = mn1 == -INFINITY ? 0.0f : mn1;
-    const float c0 = exp2f(m[0] - use0), c1 = exp2f(m[1] - use1);     // first tile: exp2(-inf) = 0
+    const float c0 = fast_exp2((m[0] - use0) * scale2), c1 = fast_exp2((m[1] - use1) * scale2);   // first tile: 0
+    const float b0 = -use0 * scale2, b1 = -use1 * scale2;
     m[0] = mn0;
     m[1] = mn1;
     float r0 = 0.0f, r1 = 0.0f;
@@ -165,7 +183,7 @@ __device__ __forceinline__ void softmax_step(float (&S)[NKT][4], float (&O)[HD /
     for (int nt = 0; nt < NKT; ++nt) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-            const float p0 = exp2f(S[nt][e] - use0), p1 = exp2f(S[nt][2 + e] - use1);
+            const float p0 = fast_exp2(fmaf(S[nt][e], scale2, b0)), p1 = fast_exp2(fmaf(S[nt][2 + e], scale2, b1));
             S[nt][e] = p0;
             S[nt][2 + e] = p1;
             r0 += p0;
@@ -280,6 +298,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
     cp_async_wait<0>();
     __syncthreads();
     pdl_trigger_late();
+    m[0] *= scale2;                                               // from raw-score units to log2 units (-inf stays)
+    m[1] *= scale2;
     // row sums over the four threads of a row
     l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1); l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
     l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1); l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
@@ -362,7 +382,9 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ ca
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int TILE_BYTES = TILE_KEYS * HD * 2;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int n0 = tiles[blockIdx.x * 3], rows = tiles[blockIdx.x * 3 + 1], seg = tiles[blockIdx.x * 3 + 2];
+    // tiles later in a portion see more keys: start them first so that the short ones fill the tail
+    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int n0 = tiles[tile * 3], rows = tiles[tile * 3 + 1], seg = tiles[tile * 3 + 2];
     const int h = blockIdx.y;
     const int kvh = h / (n_heads / n_kv_heads);
     const int p0 = pos[n0];                                       // positions of a portion are consecutive
@@ -423,7 +445,11 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ ca
         if (w_rows > 0 && key0 <= w_hi && key0 + TILE_KEYS - 1 >= w_lo) {
             float S[8][4];
             qk_scores<HD, 8>(S, qf, sK, 0, lane);
-            softmax_step<HD, 8>(S, O, m, l, key0, lane, lo0, hi0, lo1, hi1, scale2);
+            // every existing row of the warp sees the whole tile: rows sit at p0 + warp*16 .. w_hi
+            const bool full = w_rows >= 16 && key0 + TILE_KEYS - 1 <= p0 + warp * 16 &&
+                              (window <= 0 || key0 >= w_hi - window + 1);
+            if (full) softmax_step<HD, 8, false>(S, O, m, l, key0, lane, lo0, hi0, lo1, hi1, scale2);
+            else softmax_step<HD, 8, true>(S, O, m, l, key0, lane, lo0, hi0, lo1, hi1, scale2);
             pv_accumulate<HD, 8>(O, S, sV, 0, lane);
         }
         __syncthreads();
