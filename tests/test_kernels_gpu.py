@@ -405,83 +405,3 @@ def test_gemm_smallm_fused_activation(m, inter, k):
     g = (x.double().cpu() @ w[:inter].double().cpu().t()).float().to(torch.bfloat16).float()
     u = (x.double().cpu() @ w[inter:].double().cpu().t()).float().to(torch.bfloat16).float()
     assert torch.allclose(fused.float().cpu(), P.swiglu(g, u), atol=3e-2, rtol=3e-2)
-
-
-# ---- fused kernels of a decode step ------------------------------------------------------------------------
-@pytest.mark.parametrize("m", [1, 8, 13])
-def test_fused_norm_product_and_residual_chain(m):
-    """embedding(+sums of squares) -> [norm -> product] -> [product + residual add (+ new sums)] -> [norm -> gated
-    product] against the separate kernels."""
-    from zedinfer_b200 import ops
-    hidden, inter, vocab, eps = 192, 352, 500, 1e-5
-    table = rand(vocab, hidden, dtype=torch.bfloat16, seed=1)
-    ids = torch.randint(0, vocab, (m,), dtype=torch.int32).to(dev())
-    wn1 = (1 + rand(hidden, scale=0.1, seed=2)).to(torch.bfloat16)
-    w1 = rand(256, hidden, dtype=torch.bfloat16, seed=3, scale=0.1)
-    b1 = rand(256, dtype=torch.bfloat16, seed=4)
-    w2 = rand(hidden, 256, dtype=torch.bfloat16, seed=5, scale=0.1)
-    wn2 = (1 + rand(hidden, scale=0.1, seed=6)).to(torch.bfloat16)
-    wgu = rand(2 * inter, hidden, dtype=torch.bfloat16, seed=7, scale=0.1)
-    # fused chain
-    h = torch.empty(m, hidden, device=dev())
-    ssq = torch.zeros(16, device=dev())
-    ops.embedding(table, ids, h, ssq)
-    assert torch.allclose(ssq[:m].cpu(), (h * h).sum(-1).cpu(), rtol=1e-5)
-    y = torch.empty(m, 256, dtype=torch.bfloat16, device=dev())
-    ops.fused_norm_gemm(h, ssq, 1, wn1, eps, w1, b1, y)
-    h_f = h.clone()
-    ssq2 = torch.zeros(((hidden + 15) // 16) * 16, device=dev())
-    n_part = ops.gemm_residual(y, w2, None, h_f, ssq2)
-    act = torch.empty(m, inter, dtype=torch.bfloat16, device=dev())
-    ops.fused_norm_gemm(h_f, ssq2, n_part, wn2, eps, wgu, None, act, silu_mul=True)
-    # separate kernels
-    normed = torch.empty(m, hidden, dtype=torch.bfloat16, device=dev())
-    ops.add_rmsnorm(h.clone(), None, wn1, eps, normed)
-    y_ref = torch.empty_like(y)
-    ops.gemm_smallm(normed, w1, b1, y_ref)
-    assert torch.equal(y, y_ref)                            # same sums, same roundings
-    delta = torch.empty(m, hidden, dtype=torch.bfloat16, device=dev())
-    ops.gemm_smallm(y_ref, w2, None, delta)
-    h_ref = h.clone()
-    normed2 = torch.empty_like(normed)
-    ops.add_rmsnorm(h_ref, delta, wn2, eps, normed2)
-    assert torch.equal(h_f, h_ref)
-    assert torch.allclose(ssq2.view(n_part, 16)[:, :m].sum(0).cpu(), (h_ref * h_ref).sum(-1).cpu(), rtol=1e-5)
-    act_ref = torch.empty_like(act)
-    ops.gemm_smallm(normed2, wgu, None, act_ref, silu_mul=True)
-    # the row's RMS comes from differently ordered partial sums: agreement to a bfloat16 step
-    assert torch.allclose(act.float(), act_ref.float(), atol=2e-2, rtol=2e-2)
-
-
-@pytest.mark.parametrize("nh,nkv,hd,ps", [(12, 2, 128, 16), (3, 1, 32, 8), (6, 3, 64, 4)])
-def test_fused_norm_qkv_rope(nh, nkv, hd, ps):
-    from zedinfer_b200 import ops
-    hidden, eps, theta = 96, 1e-6, 10000.0
-    m = 5
-    seg = [0, 0, 0, 1, 2]
-    pos = [5, 6, 7, 21, 0]
-    h = rand(m, hidden, scale=2.0, seed=1)
-    ssq = torch.zeros(16, device=dev())
-    ssq[:m] = (h * h).sum(-1)
-    wn = (1 + rand(hidden, scale=0.1, seed=2)).to(torch.bfloat16)
-    n_out = (nh + 2 * nkv) * hd
-    w = rand(n_out, hidden, dtype=torch.bfloat16, seed=3, scale=0.1)
-    b = rand(n_out, dtype=torch.bfloat16, seed=4)
-    tables = torch.tensor([[4, 7, 1, 0, 0, 0], [2, 8, 5, 3, 6, 0], [0, 0, 0, 0, 0, 0]], dtype=torch.int32, device=dev())
-    d_seg, d_pos = torch.tensor(seg, dtype=torch.int32, device=dev()), torch.tensor(pos, dtype=torch.int32, device=dev())
-    expo = torch.arange(0, hd, 2, dtype=torch.float32) / float(hd)
-    inv = (1.0 / torch.pow(torch.tensor(theta), expo)).to(dev())
-    pool_f = torch.zeros((9, 2, 2, nkv, ps, hd), dtype=torch.bfloat16, device=dev())
-    pool_r = torch.zeros_like(pool_f)
-    q_f = torch.empty(m, nh, hd, dtype=torch.bfloat16, device=dev())
-    ops.fused_norm_qkv_rope(h, ssq, 1, wn, eps, w, b, q_f, pool_f[:, 1], tables, d_seg, d_pos, inv, nh, nkv, hd, ps,
-                            pool_f.stride(0), pool_f.stride(2), True)
-    normed = torch.empty(m, hidden, dtype=torch.bfloat16, device=dev())
-    ops.add_rmsnorm(h.clone(), None, wn, eps, normed)
-    qkv = torch.empty(m, n_out, dtype=torch.bfloat16, device=dev())
-    ops.gemm_smallm(normed, w, b, qkv)
-    q_r = torch.empty_like(q_f)
-    ops.rope_append(qkv, q_r, pool_r[:, 1], tables, d_seg, d_pos, inv, nh, nkv, hd, ps, pool_r.stride(0), pool_r.stride(2))
-    assert torch.allclose(q_f.float(), q_r.float(), atol=2e-2, rtol=2e-2)
-    assert torch.allclose(pool_f.float(), pool_r.float(), atol=2e-2, rtol=2e-2)
-    assert float(pool_r.float().abs().max()) > 0.1

@@ -28,7 +28,7 @@ TINY_C = {
 TINY_D = {
     "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
     "num_hidden_layers": 2, "hidden_size": 192, "num_attention_heads": 12, "num_key_value_heads": 2,
-    "head_dim": 128, "intermediate_size": 352, "vocab_size": 1311, "rope_theta": 10000.0,
+    "head_dim": 128, "intermediate_size": 328, "vocab_size": 1311, "rope_theta": 10000.0,
     "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "use_sliding_window": False,
     "max_position_embeddings": 1024,
 }

@@ -41,7 +41,6 @@ SOURCES: Dict[str, str] = {
     "attention_mma": "attention_mma.cu",
     "gemm_smallm": "gemm_smallm.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
-    "decode_fused": "decode_fused.cu",
 }
 EXTRA_FLAGS: Dict[str, List[str]] = {}
 EXTRA_LIBS: Dict[str, List[str]] = {}

@@ -9,11 +9,9 @@ ZI_DEFINE_LAST_ERROR(elementwise)
 // ---------------------------------------------------------------------------------------
 // Embedding: out[n, :] = table[ids[n], :]
 // ---------------------------------------------------------------------------------------
-// ssq != null: also leaves sum(out[n, :]^2) in ssq[n] (the fused decode kernels take the row's RMS from it).
 template <typename TT, typename TO>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
-                                 TO* __restrict__ out, float* __restrict__ ssq, int hidden, int vocab) {
-    __shared__ float scratch[32];
+                                 TO* __restrict__ out, int hidden, int vocab) {
     const int n = blockIdx.x;
     pdl_trigger_early();
     pdl_wait();
@@ -22,26 +20,16 @@ __global__ void embedding_kernel(const TT* __restrict__ table, const int* __rest
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);   // the host refuses ids outside the table
     const TT* src = table + (size_t)id * hidden;
     TO* dst = out + (size_t)n * hidden;
-    float ss = 0.0f;
-    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
-        const TO v = from_f32<TO>(to_f32<TT>(src[j]));
-        dst[j] = v;
-        const float f = to_f32<TO>(v);
-        ss = fmaf(f, f, ss);
-    }
-    if (ssq) {
-        ss = block_sum(ss, scratch);
-        if (threadIdx.x == 0) ssq[n] = ss;
-    }
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) dst[j] = from_f32<TO>(to_f32<TT>(src[j]));
 }
 
-ZI_EXPORT int zi_embedding(const void* table, int table_dtype, const int* ids, void* out, int out_dtype, float* ssq,
+ZI_EXPORT int zi_embedding(const void* table, int table_dtype, const int* ids, void* out, int out_dtype,
                            int n_tokens, int hidden, int vocab, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hidden <= 0 || vocab <= 0) return zi_fail("embedding: hidden=%d vocab=%d must be positive", hidden, vocab);
     const int threads = hidden >= 1024 ? 256 : 128;
     ZI_DISPATCH(table_dtype, TT, ZI_DISPATCH(out_dtype, TO, {
-        zi_launch(embedding_kernel<TT, TO>, dim3(n_tokens), dim3(threads), 0, stream, (const TT*)table, ids, (TO*)out, ssq, hidden, vocab);
+        zi_launch(embedding_kernel<TT, TO>, dim3(n_tokens), dim3(threads), 0, stream, (const TT*)table, ids, (TO*)out, hidden, vocab);
     }););
     return zi_check_launch("embedding");
 }

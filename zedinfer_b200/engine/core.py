@@ -178,9 +178,6 @@ def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache]
         seg_start_host=seg_start, seg_len_host=seg_len, seg_pos0_host=seg_pos0, slots_host=slots,
         decode_only=all(k == 1 for k in seg_len), max_kv_len=max(max_kv, 1))
     ctx.extras["attn_tiles"] = dev[off_tiles: off_tiles + 3 * n_tiles].view(n_tiles, 3)
-    # every token's logits are wanted, in order (a decode step): lets the head take the final norm in its prologue
-    ctx.extras["want_all"] = pad_segments == 0 and n_want == n_tok and all(
-        list(e.want) == list(range(len(e.tokens))) for e in entries)
     want = dev[off_want: off_want + n_want] if n_want else None
     return ctx, want
 
@@ -245,7 +242,7 @@ class EngineCore:
         """The kernel libraries a run in ``dtype`` loads, for building them ahead of the first step."""
         libs = ["elementwise", "gemm_simt", "attention_generic", "sampling"]
         if parse_dtype(dtype) == torch.bfloat16:
-            libs += ["attention_mma", "gemm_smallm", "decode_fused"]
+            libs += ["attention_mma", "gemm_smallm"]
         return libs
 
     # ---- requests -------------------------------------------------------------------------

@@ -44,7 +44,6 @@ class DecodeGraph:
             tok_seg=d[self.off_seg: self.off_seg + b], tables=tables, slots=d[self.off_slots: self.off_slots + b],
             seg_start_host=list(range(b)), seg_len_host=[1] * b, seg_pos0_host=[0] * b, slots_host=[-1] * b,
             decode_only=True, max_kv_len=core.max_seq_len)
-        self.ctx.extras["want_all"] = True
         self.want = d[self.off_want: self.off_want + b]
         self.sampled = torch.zeros(b, dtype=torch.int32, device=core.device)
         self.launches = 0

@@ -7,7 +7,6 @@ from typing import Dict, List, Mapping, Optional, Tuple
 
 import torch
 
-from .. import ops
 from ..cache.manager import CallCacheView
 from ..config.spec import ModelSpec
 from ..parts.base import Block, ResidualStream, StepContext, block_class, build_part
@@ -73,23 +72,14 @@ class Model:
                 logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Run the step's tokens through every call; return float32 logits of ``logit_rows`` (or None)."""
         h = torch.empty((ctx.n_tokens, self.spec.hidden_size), dtype=torch.float32, device=ctx.device)
-        few = ctx.dtype == torch.bfloat16 and ctx.n_tokens <= ops.FUSED_DECODE_ROWS
-        ssq = torch.empty(16, dtype=torch.float32, device=ctx.device) if few else None
-        self.embedding.forward(ctx.token_ids, h, ssq)
-        stream = ResidualStream(h, ssq=ssq, n_part=1 if few else 0)
+        self.embedding.forward(ctx.token_ids, h)
+        stream = ResidualStream(h)
         for pos, call in enumerate(self.spec.schedule):
             owner = pos if call.cache_of is None else call.cache_of
             self.blocks[call.layer].forward(stream, ctx, cache_views[owner], owns_cache=call.cache_of is None)
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         rows = logit_rows.numel()
-        if (stream.ssq is not None and stream.delta is None and ctx.extras.get("want_all")
-                and getattr(self.final_norm, "fused_ok", lambda: False)() and ops._bf16_rows_ok(self.head.weight)):
-            # every row is wanted, in order: the final norm rides in the head product's prologue
-            logits = torch.empty((rows, self.spec.vocab_size), dtype=torch.float32, device=ctx.device)
-            ops.fused_norm_gemm(stream.h, stream.ssq, stream.n_part, self.final_norm.weight, self.final_norm.eps,
-                                self.head.weight, None, logits)
-            return logits
         normed = ctx.empty(rows, self.spec.hidden_size)
         self.final_norm.forward_residual(stream, normed, row_idx=logit_rows)
         logits = torch.empty((rows, self.spec.vocab_size), dtype=torch.float32, device=ctx.device)

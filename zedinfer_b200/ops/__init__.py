@@ -22,26 +22,21 @@ _sampling = Library("sampling")
 _attention_mma = Library("attention_mma")
 _gemm_smallm = Library("gemm_smallm")
 _gemm_tcgen05 = Library("gemm_tcgen05")
-_decode_fused = Library("decode_fused")
-FUSED_DECODE_ROWS = 16           # the fused decode kernels take up to this many tokens
 SMALL_M_ROWS = 16                # the weight-streaming kernel takes up to this many rows
 
 __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "silu_mul", "cast",
-           "gemm_nt", "linear", "gemm_smallm", "gemm_tcgen05", "tcgen05_status", "fused_norm_gemm", "fused_norm_qkv_rope", "gemm_residual", "can_fuse_silu_mul", "paged_attention", "attention", "decode_attention", "prefill_attention", "argmax", "sample", "repetition_penalty", "advance_decode"]
+           "gemm_nt", "linear", "gemm_smallm", "gemm_tcgen05", "tcgen05_status", "can_fuse_silu_mul", "paged_attention", "attention", "decode_attention", "prefill_attention", "argmax", "sample", "repetition_penalty", "advance_decode"]
 
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, ssq: Optional[torch.Tensor] = None) -> None:
-    """``out[n] = table[ids[n]]``; with ``ssq`` (float32, one entry per token) also ``ssq[n] = sum(out[n]^2)``."""
-    need_cuda(table, ids, out, ssq)
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    need_cuda(table, ids, out)
     need_int32("ids", ids)
     need_contiguous("table", table), need_contiguous("out", out), need_contiguous("ids", ids)
     n, hidden = ids.numel(), table.shape[1]
     if out.shape != (n, hidden):
         raise KernelError(f"embedding: out has shape {tuple(out.shape)}, expected {(n, hidden)}")
-    if ssq is not None and (ssq.dtype != torch.float32 or ssq.numel() < n):
-        raise KernelError("embedding: ssq must be float32 with one entry per token")
     _elementwise.call("zi_embedding", ptr(table), c_int(dtype_code(table.dtype)), ptr(ids), ptr(out),
-                      c_int(dtype_code(out.dtype)), ptr(ssq), c_int(n), c_int(hidden), c_int(table.shape[0]), stream())
+                      c_int(dtype_code(out.dtype)), c_int(n), c_int(hidden), c_int(table.shape[0]), stream())
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor) -> None:
@@ -223,63 +218,6 @@ def tcgen05_status(device) -> int:
     if v:
         st.zero_()
     return v
-
-
-# ---- fused kernels of a decode step (csrc/decode_fused.cu) ------------------------------------------------
-def _bf16_rows_ok(w: torch.Tensor) -> bool:
-    return (w.dtype == torch.bfloat16 and w.dim() == 2 and w.stride(1) == 1 and w.stride(0) % 8 == 0
-            and w.data_ptr() % 16 == 0 and w.shape[1] % 32 == 0)
-
-
-def fused_norm_gemm(h: torch.Tensor, ssq: torch.Tensor, n_part: int, w_norm: torch.Tensor, eps: float,
-                    w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, silu_mul: bool = False) -> None:
-    """``out = RMSNorm(h) @ w.T (+ bias)`` for at most 16 rows; ``h`` is the float32 residual and ``ssq``
-    ``[n_part, 16]`` holds partial sums of squares of its rows.  ``silu_mul``: ``w = [gate rows; up rows]``."""
-    need_cuda(h, ssq, w_norm, w, bias, out)
-    m, k = h.shape
-    n = w.shape[0] // 2 if silu_mul else w.shape[0]
-    if h.dtype != torch.float32 or not h.is_contiguous() or w_norm.dtype != torch.bfloat16 or not _bf16_rows_ok(w) \
-            or w.shape[1] != k or out.shape != (m, n) or out.stride(1) != 1 or ssq.dtype != torch.float32:
-        raise KernelError("fused_norm_gemm: operands do not fit the fused kernel")
-    _decode_fused.call("zi_fused_norm_gemm", ptr(h), ptr(ssq), c_int(n_part), ptr(w_norm), c_float(eps), ptr(w),
-                       ptr(bias), ptr(out), c_int(dtype_code(out.dtype)), c_int(m), c_int(n), c_int(k),
-                       c_ll(w.stride(0)), c_ll(out.stride(0)), c_int(1 if silu_mul else 0), stream())
-
-
-def fused_norm_qkv_rope(h: torch.Tensor, ssq: torch.Tensor, n_part: int, w_norm: torch.Tensor, eps: float,
-                        w_qkv: torch.Tensor, b_qkv: Optional[torch.Tensor], q_out: torch.Tensor,
-                        cache: Optional[torch.Tensor], tables: torch.Tensor, tok_seg: torch.Tensor, pos: torch.Tensor,
-                        inv_freq: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int,
-                        page_stride: int, kv_stride: int, write_kv: bool) -> None:
-    """Norm, stacked q/k/v projection, bias, RoPE and the append of k, v to the cache in one kernel."""
-    need_cuda(h, ssq, w_norm, w_qkv, b_qkv, q_out, cache, tables, tok_seg, pos, inv_freq)
-    m, k = h.shape
-    if h.dtype != torch.float32 or not h.is_contiguous() or w_norm.dtype != torch.bfloat16 or not _bf16_rows_ok(w_qkv) \
-            or w_qkv.shape != ((n_heads + 2 * n_kv_heads) * head_dim, k) or q_out.dtype != torch.bfloat16 \
-            or not q_out.is_contiguous() or (cache is not None and cache.dtype != torch.bfloat16):
-        raise KernelError("fused_norm_qkv_rope: operands do not fit the fused kernel")
-    _decode_fused.call("zi_fused_norm_qkv_rope", ptr(h), ptr(ssq), c_int(n_part), ptr(w_norm), c_float(eps), ptr(w_qkv),
-                       ptr(b_qkv), ptr(q_out), ptr(cache), ptr(tables), ptr(tok_seg), ptr(pos), ptr(inv_freq), c_int(m),
-                       c_int(k), c_ll(w_qkv.stride(0)), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
-                       c_int(page_size), c_int(tables.shape[1]), c_ll(page_stride), c_ll(kv_stride),
-                       c_int(1 if write_kv else 0), stream())
-
-
-def gemm_residual(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], h: torch.Tensor,
-                  ssq_out: torch.Tensor) -> int:
-    """``h += x @ w.T (+ bias)`` in float32 for at most 16 rows; ``ssq_out`` ``[ceil(N/16), 16]`` receives the
-    partial sums of squares of the new rows.  Returns the number of partial sums (column tiles)."""
-    need_cuda(x, w, bias, h, ssq_out)
-    m, k = x.shape
-    n = w.shape[0]
-    tiles = (n + 15) // 16
-    if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.stride(0) % 8 or not _bf16_rows_ok(w) or w.shape[1] != k \
-            or h.dtype != torch.float32 or h.shape != (m, n) or not h.is_contiguous() or ssq_out.numel() < tiles * 16:
-        raise KernelError("gemm_residual: operands do not fit the fused kernel")
-    part, counters = _smallm_scratch(x.device, n, k, False)
-    _decode_fused.call("zi_gemm_residual", ptr(x), ptr(w), ptr(bias), ptr(h), ptr(ssq_out), ptr(part), ptr(counters),
-                       c_int(m), c_int(n), c_int(k), c_ll(x.stride(0)), c_ll(w.stride(0)), stream())
-    return tiles
 
 
 def can_fuse_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, bias: Optional[torch.Tensor]) -> bool:

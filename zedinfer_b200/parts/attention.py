@@ -73,28 +73,6 @@ class AttentionMixer(Mixer):
         if self.out_bias:
             self.b_o = tensors["o_proj.bias"].contiguous()
 
-    def fused_ok(self) -> bool:
-        from .rope import RotaryPosition
-        bias_ok = all(b is None or (b.dtype == torch.bfloat16) for b in (self.b_qkv, self.b_o))
-        return (isinstance(self.position, RotaryPosition) and bias_ok and ops._bf16_rows_ok(self.w_qkv)
-                and ops._bf16_rows_ok(self.w_o) and self.hidden_size % 32 == 0)
-
-    def forward_fused(self, stream, norm, ctx: StepContext, cache: CallCacheView, owns_cache: bool) -> None:
-        """norm -> q/k/v -> RoPE -> cache append in one kernel, attention, output projection + residual add."""
-        if cache.kind != "paged":
-            raise RuntimeError("attention needs a paged key/value cache")
-        n = stream.h.shape[0]
-        q = ctx.empty(n, self.num_heads, self.head_dim)
-        ops.fused_norm_qkv_rope(stream.h, stream.ssq, stream.n_part, norm.weight, norm.eps, self.w_qkv, self.b_qkv, q,
-                                cache.tensor, ctx.tables[cache.group], ctx.tok_seg, ctx.positions,
-                                self.position._table(q.device), self.num_heads, self.num_kv_heads, self.head_dim,
-                                cache.page_size, cache.page_stride, cache.kv_stride, owns_cache)
-        attn = ctx.empty(n, self.q_dim)
-        ops.attention(q, cache, attn, ctx, self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale)
-        ssq = ctx.empty(((self.hidden_size + 15) // 16) * 16, dtype=torch.float32)
-        stream.n_part = ops.gemm_residual(attn, self.w_o, self.b_o, stream.h, ssq)
-        stream.ssq = ssq
-
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CallCacheView, owns_cache: bool) -> torch.Tensor:
         if cache.kind != "paged":
             raise RuntimeError("attention needs a paged key/value cache")

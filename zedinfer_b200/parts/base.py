@@ -62,16 +62,9 @@ class StepContext:
 
 @dataclass
 class ResidualStream:
-    """The float32 residual ``h`` and a branch output ``delta`` that is not added to it yet.
-
-    ``ssq`` (float32 ``[n_part, 16]``), when present, holds partial sums of squares of the rows of ``h`` as
-    the kernel that last wrote ``h`` left them; the fused kernels of a decode step take the rows' RMS from it
-    instead of running a norm kernel.  Whoever changes ``h`` without refreshing ``ssq`` sets it to ``None``.
-    """
+    """The float32 residual ``h`` and a branch output ``delta`` that is not added to it yet."""
     h: torch.Tensor
     delta: Optional[torch.Tensor] = None
-    ssq: Optional[torch.Tensor] = None
-    n_part: int = 0
 
 
 # ---- part interfaces ------------------------------------------------------------------------

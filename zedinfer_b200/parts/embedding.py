@@ -26,8 +26,8 @@ class TokenEmbedding(Part):
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.table = tensors[self.name].contiguous()
 
-    def forward(self, ids: torch.Tensor, out: torch.Tensor, ssq: Optional[torch.Tensor] = None) -> None:
-        ops.embedding(self.table, ids, out, ssq)
+    def forward(self, ids: torch.Tensor, out: torch.Tensor) -> None:
+        ops.embedding(self.table, ids, out)
 
 
 class OutputHead(Part):

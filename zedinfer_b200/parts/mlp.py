@@ -47,20 +47,6 @@ class GatedMLP(FeedForward):
             self.b_gate_up = _stack([tensors["gate_proj.bias"], tensors["up_proj.bias"]])
             self.b_down = tensors["down_proj.bias"].contiguous()
 
-    def fused_ok(self) -> bool:
-        return (not self.bias and ops._bf16_rows_ok(self.w_gate_up) and ops._bf16_rows_ok(self.w_down)
-                and self.hidden_size % 32 == 0)
-
-    def forward_fused(self, stream, norm, ctx: StepContext) -> None:
-        """norm -> gate/up -> SiLU-mul in one kernel, down projection + residual add in another."""
-        n = stream.h.shape[0]
-        act = ctx.empty(n, self.intermediate_size)
-        ops.fused_norm_gemm(stream.h, stream.ssq, stream.n_part, norm.weight, norm.eps, self.w_gate_up, None, act,
-                            silu_mul=True)
-        ssq = ctx.empty(((self.hidden_size + 15) // 16) * 16, dtype=torch.float32)
-        stream.n_part = ops.gemm_residual(act, self.w_down, None, stream.h, ssq)
-        stream.ssq = ssq
-
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         n = x.shape[0]
         act = ctx.empty(n, self.intermediate_size)

@@ -27,9 +27,6 @@ class RMSNorm(Norm):
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"].contiguous()
 
-    def fused_ok(self) -> bool:
-        return self.weight is not None and self.weight.dtype == torch.bfloat16 and self.weight.data_ptr() % 16 == 0
-
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> None:
         ops.rmsnorm(x, self.weight, self.eps, out)
 
