@@ -63,11 +63,12 @@ class PagedGroup:
 
 class RequestCache:
     """What one live request holds: its committed length, a block table per group, a state slot."""
-    __slots__ = ("request_id", "length", "tables", "slot", "closed")
+    __slots__ = ("request_id", "length", "tables", "slot", "closed", "version")
 
     def __init__(self, request_id, n_groups: int, slot: int):
         self.request_id = request_id
         self.length = 0
+        self.version = 0                      # bumped whenever a block table changes (pages added or given back)
         self.tables: List[List[int]] = [[] for _ in range(n_groups)]
         self.slot = slot
         self.closed = False
@@ -217,13 +218,17 @@ class CacheManager:
         """Give ``rc`` pages for tokens ``[rc.length, new_len)`` in every group, or change nothing and raise."""
         if rc.closed:
             raise RuntimeError(f"request {rc.request_id!r} is closed")
+        if all(new_len <= len(t) * self.page_size for t in rc.tables):
+            return                              # the pages are there already (the usual case of a decode step)
         needed = self.pages_needed(rc, new_len)
         for n, g in zip(needed, self.groups):
             if n > g.pool.num_free:
                 raise OutOfPages(f"request {rc.request_id!r} needs {n} more pages for {new_len} tokens, "
                                  f"{g.pool.num_free} free")
         for gi, (n, g) in enumerate(zip(needed, self.groups)):
-            rc.tables[gi].extend(g.pool.allocate_many(n))
+            if n:
+                rc.tables[gi].extend(g.pool.allocate_many(n))
+                rc.version += 1
 
     def commit(self, rc: RequestCache, new_len: int) -> None:
         """The step that wrote tokens up to ``new_len`` is done: advance, release what a window has passed."""
@@ -238,6 +243,7 @@ class CacheManager:
                 if table[b] >= 0:
                     g.pool.free(table[b])
                     table[b] = -1
+                    rc.version += 1
 
     def close(self, rc: RequestCache) -> None:
         if rc.closed:

@@ -149,43 +149,57 @@ ZI_EXPORT int zi_rmsnorm(const void* x, int x_dtype, const void* w, int w_dtype,
 //   pos[n]   absolute position of token n;  inv_freq[head_dim/2] float32
 // angle = float(pos) * inv_freq[k]; y[k] = a*c - b*s; y[k+half] = b*c + a*s.
 // ---------------------------------------------------------------------------------------
-// grid (n_tokens, n_heads + 2*n_kv_heads): one block per (token, head); q heads and k heads are rotated,
-// v heads copied.  head_dim/2 threads would do; 64 are launched and loop.
+// grid (n_tokens, ceil(heads / heads_per_block)), heads = n_heads + 2*n_kv_heads: q heads and k heads are rotated,
+// v heads copied.  Few tokens (decode): one head per block, so that the step's handful of tokens still fills
+// the GPU.  Many tokens (prefill): all heads of a token in one block, cos/sin computed once per token.
 template <typename T>
 __global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ cache,
                                    const int* __restrict__ tables, const int* __restrict__ tok_seg,
                                    const int* __restrict__ pos, const float* __restrict__ inv_freq,
                                    int row_stride, int n_heads, int n_kv_heads, int head_dim, int page_size,
-                                   int max_blocks, long long page_stride, long long kv_stride, int write_kv) {
-    const int n = blockIdx.x, h = blockIdx.y;
+                                   int max_blocks, long long page_stride, long long kv_stride, int write_kv,
+                                   int heads_per_block) {
+    extern __shared__ float cs[];            // cos[half], sin[half]
+    const int n = blockIdx.x;
     const int half = head_dim >> 1;
+    const int total_heads = n_heads + (write_kv ? 2 * n_kv_heads : 0);
+    const int h_begin = blockIdx.y * heads_per_block;
+    const int h_end = min(h_begin + heads_per_block, total_heads);
     pdl_trigger_early();
-    if (!write_kv && h >= n_heads) return;
+    if (h_begin >= h_end) return;
     pdl_wait();
     pdl_trigger_late();
     const int p = ld_dep(pos + n);
-    const T* src = qkv + (size_t)n * row_stride + (size_t)h * head_dim;
-    T* dst;
-    if (h < n_heads) {
-        dst = q_out + ((size_t)n * n_heads + h) * head_dim;
-    } else {
-        const int seg = tok_seg[n];
-        const int page = tables[(size_t)seg * max_blocks + p / page_size];
-        const int off = p % page_size;
-        const int kvh = (h - n_heads) % n_kv_heads;
-        const bool is_v = (h - n_heads) >= n_kv_heads;
-        dst = cache + (size_t)page * page_stride + (is_v ? kv_stride : 0) + ((size_t)kvh * page_size + off) * head_dim;
-        if (is_v) {
-            for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = ld_dep(src + d);
-            return;
-        }
-    }
     for (int k = threadIdx.x; k < half; k += blockDim.x) {
         float s, c;
         sincosf((float)p * inv_freq[k], &s, &c);
-        const float a = ld_dep_f32<T>(src + k), b = ld_dep_f32<T>(src + k + half);
-        dst[k] = from_f32<T>(a * c - b * s);
-        dst[k + half] = from_f32<T>(b * c + a * s);
+        cs[k] = c;
+        cs[half + k] = s;
+    }
+    __syncthreads();
+    T* page_base = nullptr;
+    if (h_end > n_heads) {
+        const int seg = tok_seg[n];
+        const int page = tables[(size_t)seg * max_blocks + p / page_size];
+        page_base = cache + (size_t)page * page_stride + (size_t)(p % page_size) * head_dim;
+    }
+    const T* row = qkv + (size_t)n * row_stride;
+    for (int idx = threadIdx.x; idx < (h_end - h_begin) * half; idx += blockDim.x) {
+        const int hh = idx / half, k = idx - hh * half;
+        const int h = h_begin + hh;
+        const T* src = row + (size_t)h * head_dim;
+        if (h < n_heads + n_kv_heads) {
+            T* dst = h < n_heads ? q_out + ((size_t)n * n_heads + h) * head_dim
+                                 : page_base + (size_t)(h - n_heads) * page_size * head_dim;
+            const float a = ld_dep_f32<T>(src + k), b = ld_dep_f32<T>(src + k + half);
+            const float c = cs[k], sn = cs[half + k];
+            dst[k] = from_f32<T>(a * c - b * sn);
+            dst[k + half] = from_f32<T>(b * c + a * sn);
+        } else {
+            T* dst = page_base + kv_stride + (size_t)(h - n_heads - n_kv_heads) * page_size * head_dim;
+            dst[k] = ld_dep(src + k);
+            dst[k + half] = ld_dep(src + k + half);
+        }
     }
 }
 
@@ -197,13 +211,16 @@ ZI_EXPORT int zi_rope_append(const void* qkv, void* q_out, void* cache, int dtyp
     if (n_tokens <= 0) return 0;
     if (head_dim <= 0 || (head_dim & 1)) return zi_fail("rope: head_dim=%d must be positive and even", head_dim);
     if (n_heads <= 0 || n_kv_heads <= 0 || page_size <= 0) return zi_fail("rope: bad head counts or page size");
-    if (n_heads + 2 * n_kv_heads > 65535) return zi_fail("rope: too many heads for one launch");
-    dim3 grid(n_tokens, n_heads + 2 * n_kv_heads);
-    const int threads = head_dim >= 128 ? 64 : 32;
+    const int total_heads = n_heads + 2 * n_kv_heads;
+    if (total_heads > 65535) return zi_fail("rope: too many heads for one launch");
+    const int hpb = n_tokens <= 64 ? 1 : total_heads;
+    dim3 grid(n_tokens, (total_heads + hpb - 1) / hpb);
+    const int threads = hpb == 1 ? (head_dim >= 128 ? 64 : 32) : 256;
+    const size_t smem = (size_t)head_dim * sizeof(float);
     ZI_DISPATCH(dtype, T, {
-        zi_launch(rope_append_kernel<T>, grid, dim3(threads), 0, stream, (const T*)qkv, (T*)q_out, (T*)cache, tables,
+        zi_launch(rope_append_kernel<T>, grid, dim3(threads), smem, stream, (const T*)qkv, (T*)q_out, (T*)cache, tables,
                   tok_seg, pos, inv_freq, row_stride, n_heads, n_kv_heads, head_dim, page_size, max_blocks,
-                  page_stride, kv_stride, write_kv);
+                  page_stride, kv_stride, write_kv, hpb);
     });
     return zi_check_launch("rope_append");
 }

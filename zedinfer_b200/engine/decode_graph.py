@@ -35,7 +35,8 @@ class DecodeGraph:
         self._pad_rows(0)
         self.dev = torch.zeros(total, dtype=torch.int32, device=core.device)
         core._ring.stage_into(self.host, self.dev)
-        self._uploaded = self.host.copy()
+        self._slot_sig: List[Optional[tuple]] = [None] * b
+        self._n_filled = 0
         d = self.dev
         tables = [d[self.off_tab + g * b * width: self.off_tab + (g + 1) * b * width].view(b, width) for g in range(ng)]
         self.ctx = StepContext(
@@ -83,30 +84,46 @@ class DecodeGraph:
             rows[first:, 0] = scratch
 
     def fill(self, tokens: Sequence[int], rcs: Sequence, reserve_ahead: int = 0) -> None:
-        """Refresh the static buffers for these requests (one token each) and upload what changed."""
+        """Refresh the static buffers for these requests (one token each) and upload what changed.
+
+        Token ids and positions change every step and are always sent.  A row of block tables is rewritten only
+        when another request sits in the slot or the request's tables changed (its ``version``), which for a
+        steady decode is once every ``page_size`` steps; the tables go up only then.
+        """
         n = len(rcs)
         b, width, ng = self.bucket, self.core.table_width, len(self.core.cache.groups)
         h = self.host
         vocab = self.core.spec.vocab_size
-        for i, (tok, rc) in enumerate(zip(tokens, rcs)):
-            if not 0 <= tok < vocab:
-                raise ValueError(f"request {rc.request_id!r}: token id outside [0, {vocab})")
-            h[self.off_ids + i] = tok
-            h[self.off_pos + i] = rc.length
+        toks = np.asarray(tokens, dtype=np.int64)
+        if n and (toks.min() < 0 or toks.max() >= vocab):
+            raise ValueError(f"token id outside [0, {vocab})")
+        h[self.off_ids: self.off_ids + n] = toks
+        h[self.off_pos: self.off_pos + n] = [rc.length for rc in rcs]
+        tables_dirty = False
+        sigs = self._slot_sig
+        for i, rc in enumerate(rcs):
+            sig = (rc.request_id, rc.version)
+            if sigs[i] == sig:
+                continue
+            sigs[i] = sig
+            tables_dirty = True
             h[self.off_slots + i] = rc.slot
             for g in range(ng):
                 tab = rc.tables[g]
                 base = self.off_tab + (g * b + i) * width
                 h[base: base + len(tab)] = tab
                 h[base + len(tab): base + width] = 0
-        self._pad_rows(n)
-        head = self.off_seg                                   # ids and positions change every step
-        if np.array_equal(h[head:], self._uploaded[head:]):
-            self.core._ring.stage_into(h[:head], self.dev[:head])
-            self._uploaded[:head] = h[:head]
-        else:
+        if n != self._n_filled:
+            self._pad_rows(n)
+            for i in range(n, b):
+                sigs[i] = None
+            self._n_filled = n
+            tables_dirty = True
+        head = self.off_seg                                   # ids and positions
+        if tables_dirty:
             self.core._ring.stage_into(h, self.dev)
-            self._uploaded[:] = h
+        else:
+            self.core._ring.stage_into(h[:head], self.dev[:head])
 
     def run(self, entries: Sequence, rcs: Sequence) -> torch.Tensor:
         self.fill([e.tokens[0] for e in entries], rcs)
