@@ -55,3 +55,54 @@ def test_refuses_what_tma_cannot_address():
     x, w = rand(4, 36), rand(8, 36)
     with pytest.raises(ops.KernelError, match="multiples of 8"):
         ops.gemm_tcgen05(x, w, None, torch.empty(4, 8, dtype=torch.bfloat16, device=DEV))
+
+
+def check_tiles(m, n, k, out_dtype, with_bias, silu_mul=False, tile_width=0, ld_pad=0, pairs=False):
+    from zedinfer_b200 import ops
+    x = rand(m, k + ld_pad, seed=4)[:, :k]
+    w = rand(2 * n if silu_mul else n, k + ld_pad, seed=5, scale=0.05)[:, :k]
+    b = rand(n, seed=6) if with_bias else None
+    out = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEV)
+    ops.gemm_tcgen05_tiles(x, w, b, out, silu_mul=silu_mul, tile_width=tile_width, pairs=pairs)
+    torch.cuda.synchronize()
+    assert ops.tcgen05_status(DEV) == 0
+    ref = x.double().cpu() @ w.double().cpu().t()
+    if silu_mul:
+        g, u = ref[:, :n], ref[:, n:]
+        ref = g / (1.0 + torch.exp(-g)) * u
+    if with_bias:
+        ref = ref + b.double().cpu()
+    got = out.double().cpu()
+    assert torch.isfinite(got).all()
+    tol = 2e-2 if out_dtype == torch.bfloat16 else 2e-3
+    assert torch.allclose(got, ref, atol=3 * tol, rtol=tol), float((got - ref).abs().max())
+
+
+PAIRS = pytest.mark.parametrize("pairs", [False, True], ids=["one_sm", "sm_pair"])
+
+
+@PAIRS
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 16, 128), (300, 130, 200), (2048, 2048, 1536), (1000, 1536, 8960),
+                                   (130, 48, 72), (2048, 1536, 1536), (17, 1000, 328), (5000, 520, 264)])
+def test_persistent_tiles(m, n, k, pairs):
+    check_tiles(m, n, k, torch.bfloat16, True, pairs=pairs)
+    check_tiles(m, n, k, torch.float32, False, pairs=pairs)
+
+
+@PAIRS
+@pytest.mark.parametrize("width", [16, 48, 128, 192, 240, 256])
+def test_persistent_tiles_every_width(width, pairs):
+    check_tiles(700, 1000, 456, torch.bfloat16, True, tile_width=width, pairs=pairs)
+
+
+@PAIRS
+@pytest.mark.parametrize("m,n,k,width", [(128, 128, 64, 0), (300, 328, 136, 0), (2048, 8960, 1536, 0), (77, 176, 64, 32),
+                                         (640, 1000, 512, 96), (640, 1000, 512, 256)])
+def test_persistent_tiles_silu_mul(m, n, k, width, pairs):
+    check_tiles(m, n, k, torch.bfloat16, False, silu_mul=True, tile_width=width, pairs=pairs)
+
+
+@PAIRS
+def test_persistent_tiles_many_tiles_per_cta_and_strides(pairs):
+    check_tiles(2048, 17920, 1536, torch.bfloat16, False, pairs=pairs)   # 7.6 tiles per CTA: both TMEM buffers turn over
+    check_tiles(4096, 1536, 264, torch.bfloat16, True, ld_pad=8, pairs=pairs)

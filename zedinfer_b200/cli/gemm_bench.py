@@ -15,6 +15,7 @@ def main(argv=None) -> int:
     p.add_argument("--qkv", type=int, default=2048)
     p.add_argument("--vocab", type=int, default=151936)
     p.add_argument("--reps", type=int, default=20)
+    p.add_argument("--shapes", nargs="+", default=None, help="only these products (qkv o gate_up down lm_head)")
     args = p.parse_args(argv)
     import torch
     from .. import ops
@@ -39,7 +40,7 @@ def main(argv=None) -> int:
 
     for m in args.rows:
         for name, n, k in shapes:
-            if name == "lm_head" and m > 64:
+            if (name == "lm_head" and m > 64) or (args.shapes and name not in args.shapes):
                 continue
             x = (torch.randn(m, k, device=dev) * 0.5).to(torch.bfloat16)
             w = (torch.randn(n, k, device=dev) * 0.05).to(torch.bfloat16)
@@ -50,6 +51,13 @@ def main(argv=None) -> int:
                 row["tcgen05_swapped_us"] = round(timed(lambda: ops.gemm_tcgen05(x, w, None, out, swapped=True)), 2)
             if m >= 64:
                 row["tcgen05_normal_us"] = round(timed(lambda: ops.gemm_tcgen05(x, w, None, out, swapped=False)), 2)
+                row["tcgen05_tiles_us"] = round(timed(lambda: ops.gemm_tcgen05_tiles(x, w, None, out, pairs=False)), 2)
+                row["tcgen05_pairs_us"] = round(timed(lambda: ops.gemm_tcgen05_tiles(x, w, None, out, pairs=True)), 2)
+                if name == "gate_up":
+                    act = torch.empty(m, n // 2, dtype=torch.bfloat16, device=dev)
+                    row["cublas_plus_silu_mul_us"] = round(timed(lambda: (torch.mm(x, w.t(), out=out), ops.silu_mul(out, act))), 2)
+                    row["tcgen05_tiles_silu_mul_us"] = round(timed(lambda: ops.gemm_tcgen05_tiles(x, w, None, act, silu_mul=True, pairs=False)), 2)
+                    row["tcgen05_pairs_silu_mul_us"] = round(timed(lambda: ops.gemm_tcgen05_tiles(x, w, None, act, silu_mul=True, pairs=True)), 2)
             if m <= 16:
                 row["smallm_us"] = round(timed(lambda: ops.gemm_smallm(x, w, None, out)), 2)
             best = min(v for kk, v in row.items() if kk.endswith("_us"))

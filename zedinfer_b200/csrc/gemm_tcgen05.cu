@@ -47,9 +47,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             "selp.u32 %0, 1, 0, p;\n\t}\n"
             : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
-        if ((it & 1023) == 1023 && *gave_up) return false;
+        if ((it & 1023) == 1023 && gave_up && *gave_up) return false;
     }
     return false;
+}
+// One lane of a converged warp.  The issuing roles run their loops with the whole warp and elect the lane per
+// instruction: from a divergent branch (if (lane == 0)) every tcgen05.mma took about 100 clocks to issue and
+// stalled the issuer, which a 128 x 256 x 16 product (128 clocks) cannot hide.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}\n" : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* gave_up) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, gave_up));      // one answer for the whole warp
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
     asm volatile(
@@ -71,6 +82,17 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr) : "memory");
 }
 
@@ -129,24 +151,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t tmem_d = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0) {
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                const int s = kb % STAGES;
-                if (kb >= STAGES && !mbar_wait(empty0 + 8 * s, ((kb / STAGES) - 1) & 1, &gave_up)) { atomicExch(p.status, 1); gave_up = 1; break; }
+        for (int kb = 0; kb < k_blocks; ++kb) {
+            const int s = kb % STAGES;
+            if (kb >= STAGES && !mbar_wait_warp(empty0 + 8 * s, ((kb / STAGES) - 1) & 1, &gave_up)) { if (lane == 0) { atomicExch(p.status, 1); gave_up = 1; } break; }
+            if (elect_one()) {
                 const uint32_t sa = tc_smem_u32(stages + (size_t)s * STAGE_BYTES), sb = sa + A_BYTES;
                 mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
                 tma_load_2d(sa, &map_a, kb * TC_BK, a0, full0 + 8 * s);
                 tma_load_2d(sb, &map_b, kb * TC_BK, b0, full0 + 8 * s);
             }
+            __syncwarp();
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
-            bool ok = true;
-            for (int kb = 0; kb < k_blocks && ok; ++kb) {
-                const int s = kb % STAGES;
-                if (!mbar_wait(full0 + 8 * s, (kb / STAGES) & 1, &gave_up)) { atomicExch(p.status, 2); gave_up = 1; ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+            const int s = kb % STAGES;
+            if (!mbar_wait_warp(full0 + 8 * s, (kb / STAGES) & 1, &gave_up)) { if (lane == 0) { atomicExch(p.status, 2); gave_up = 1; } break; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (elect_one()) {
                 const uint32_t sa = tc_smem_u32(stages + (size_t)s * STAGE_BYTES), sb = sa + A_BYTES;
                 const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sb);
 #pragma unroll
@@ -154,8 +176,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     umma_bf16(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
                 umma_commit(empty0 + 8 * s);               // stage s may be refilled once these MMAs have read it
             }
-            umma_commit(accum);                            // arrives when every MMA above has retired (at once if none ran)
+            __syncwarp();
         }
+        if (elect_one()) umma_commit(accum);               // arrives when every MMA above has retired (at once if none ran)
+        __syncwarp();
     } else {
         // epilogue: warp w owns TMEM lanes 32*(w % 4) .. +31, i.e. rows a0 + 32*(w % 4) + lane of the tile
         const int quad = warp & 3;
@@ -211,6 +235,390 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_d), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
+// ---- the persistent form for many rows -----------------------------------------------------------------
+// One CTA per SM walks over 128 x BN tiles of C (BN a multiple of 16 up to 256, chosen per call).  The
+// accumulator is double-buffered in TMEM (2 x 256 columns): while the epilogue warps read tile i out of
+// one buffer, the MMA warp already fills the other with tile i+1, and the TMA ring runs on across tile
+// borders.  Tiles are numbered with the row tile fastest, so the CTAs of one wave share a few column
+// tiles of W (read once from HBM, then from L2) and all of X.
+//
+// The B operand of a tile is loaded as two boxes of BN/2 rows.  plain: rows n0.. and n0+BN/2.. of W.
+// silu_mul: W = [gate; up] stacked, rows n0.. of the gate half and the same rows of the up half, so the
+// accumulator holds gate in columns [0, BN/2) and up in [BN/2, BN) for the same BN/2 outputs, and the
+// epilogue writes silu(gate) * up without the two halves ever reaching memory.
+#define TP_STAGES 4
+#define TP_A_BYTES (TC_BM * TC_BK * 2)
+#define TP_B_BYTES (256 * TC_BK * 2)
+#define TP_STAGE_BYTES (TP_A_BYTES + TP_B_BYTES)
+#define TP_SMEM ((size_t)TP_STAGES * TP_STAGE_BYTES + (2 * TP_STAGES + 4) * 8 + 16)
+
+struct TpParams {
+    void* C;
+    const bf16* bias;
+    int* status;
+    long long ldc;
+    int M, N, K;                // N: columns of C (silu_mul: the intermediate size)
+    int c_is_f32, silu_mul;
+    int bn;                     // accumulator columns per tile
+    int up_row0;                // silu_mul: first row of the up half in W
+    int tiles_m, tiles_n;
+};
+
+__device__ __forceinline__ void tp_store16(const TpParams& p, long long base, int n, const float (&v)[16]) {
+    // 16 consecutive columns n .. n+15 of one row of C
+    if (!p.c_is_f32 && n + 16 <= p.N && ((base & 7) == 0) && (((uintptr_t)p.C & 15) == 0)) {
+        store8(reinterpret_cast<bf16*>(p.C) + base, v);
+        store8(reinterpret_cast<bf16*>(p.C) + base + 8, v + 8);
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        if (n + j >= p.N) break;
+        if (p.c_is_f32) reinterpret_cast<float*>(p.C)[base + j] = v[j];
+        else reinterpret_cast<bf16*>(p.C)[base + j] = __float2bfloat16_rn(v[j]);
+    }
+}
+
+// The epilogue of one tile for one thread: row m of C, accumulator columns at taddr.  A tcgen05.ld takes
+// several hundred clocks while the MMAs of the next tile keep TMEM busy, so the loads of 64 columns are
+// issued together before one wait, not 16 by 16.
+__device__ __forceinline__ void tp_epilogue_row(const TpParams& p, uint32_t taddr, int m, int nt) {
+    const int half = p.bn >> 1;
+    if (p.silu_mul) {
+        const int n0 = nt * half;
+#pragma unroll 1
+        for (int c0 = 0; c0 < half; c0 += 32) {
+            uint32_t g[1][32], u[1][32];
+#pragma unroll
+            for (int q = 0; q < 1; ++q)
+                if (c0 + 32 * q < half) { tmem_ld32(taddr + (uint32_t)(c0 + 32 * q), g[q]); tmem_ld32(taddr + (uint32_t)(half + c0 + 32 * q), u[q]); }
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            if (m >= p.M) continue;
+#pragma unroll
+            for (int q = 0; q < 1; ++q) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int c = c0 + 32 * q + 16 * h;
+                    if (c >= half || n0 + c >= p.N) continue;
+                    float v[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float gv = __uint_as_float(g[q][16 * h + j]);
+                        v[j] = __fdividef(gv, 1.0f + __expf(-gv)) * __uint_as_float(u[q][16 * h + j]);
+                    }
+                    tp_store16(p, (long long)m * p.ldc + n0 + c, n0 + c, v);
+                }
+            }
+        }
+    } else {
+        const int n0 = nt * p.bn;
+#pragma unroll 1
+        for (int c0 = 0; c0 < p.bn; c0 += 64) {
+            uint32_t r[2][32];
+#pragma unroll
+            for (int q = 0; q < 2; ++q)
+                if (c0 + 32 * q < p.bn) tmem_ld32(taddr + (uint32_t)(c0 + 32 * q), r[q]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            if (m >= p.M) continue;
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int c = c0 + 32 * q + 16 * h;
+                    if (c >= p.bn || n0 + c >= p.N) continue;
+                    float v[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        v[j] = __uint_as_float(r[q][16 * h + j]) + ((p.bias && n0 + c + j < p.N) ? __bfloat162float(p.bias[n0 + c + j]) : 0.0f);
+                    tp_store16(p, (long long)m * p.ldc + n0 + c, n0 + c, v);
+                }
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TpParams p) {
+    extern __shared__ __align__(1024) unsigned char tc_smem[];
+    unsigned char* stages = tc_smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tc_smem + (size_t)TP_STAGES * TP_STAGE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TP_STAGES + 4);
+    __shared__ volatile int gave_up;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_blocks = (p.K + TC_BK - 1) / TC_BK;
+    const int n_tiles = p.tiles_m * p.tiles_n;
+    const int half = p.bn >> 1;
+    const uint32_t full0 = tc_smem_u32(bars), empty0 = tc_smem_u32(bars + TP_STAGES);
+    const uint32_t tfull0 = tc_smem_u32(bars + 2 * TP_STAGES), tempty0 = tc_smem_u32(bars + 2 * TP_STAGES + 2);
+
+    if (threadIdx.x == 0) {
+        gave_up = 0;
+        for (int s = 0; s < TP_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        const uint32_t stage_tx = TP_A_BYTES + (uint32_t)p.bn * TC_BK * 2;
+        uint32_t kbg = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            const int m0 = (tile % p.tiles_m) * TC_BM, nt = tile / p.tiles_m;
+            const int row_b0 = p.silu_mul ? nt * half : nt * p.bn;
+            const int row_b1 = p.silu_mul ? p.up_row0 + nt * half : nt * p.bn + half;
+            for (int kb = 0; kb < k_blocks; ++kb, ++kbg) {
+                const uint32_t s = kbg % TP_STAGES;
+                if (kbg >= TP_STAGES && !mbar_wait_warp(empty0 + 8 * s, ((kbg / TP_STAGES) - 1) & 1, &gave_up)) {
+                    if (lane == 0) { atomicExch(p.status, 1); gave_up = 1; }
+                    ok = false; break;
+                }
+                if (elect_one()) {
+                    const uint32_t sa = tc_smem_u32(stages + (size_t)s * TP_STAGE_BYTES), sb = sa + TP_A_BYTES;
+                    mbar_expect_tx(full0 + 8 * s, stage_tx);
+                    tma_load_2d(sa, &map_a, kb * TC_BK, m0, full0 + 8 * s);
+                    tma_load_2d(sb, &map_b, kb * TC_BK, row_b0, full0 + 8 * s);
+                    tma_load_2d(sb + (uint32_t)half * TC_BK * 2, &map_b, kb * TC_BK, row_b1, full0 + 8 * s);
+                }
+                __syncwarp();
+            }
+        }
+        if (!ok || gave_up) {
+            // copies that were started but never consumed: let them land before the CTA's memory goes away
+            const uint32_t last = kbg < TP_STAGES ? kbg : TP_STAGES;
+            for (uint32_t i = 0; i < last; ++i) {
+                const uint32_t g = kbg - 1 - i, s = g % TP_STAGES;
+                mbar_wait(full0 + 8 * s, (g / TP_STAGES) & 1, nullptr);
+            }
+        }
+    } else if (warp == 1) {
+        const uint32_t idesc = umma_idesc_bf16(TC_BM, p.bn);
+        uint32_t kbg = 0;
+        bool ok = true;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
+            const uint32_t buf = it & 1;
+            if (it >= 2 && !mbar_wait_warp(tempty0 + 8 * buf, ((it >> 1) - 1) & 1, &gave_up)) {
+                if (lane == 0) { atomicExch(p.status, 4); gave_up = 1; }
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const uint32_t tmem_d = tmem_base + buf * 256u;
+            for (int kb = 0; kb < k_blocks; ++kb, ++kbg) {
+                const uint32_t s = kbg % TP_STAGES;
+                if (!mbar_wait_warp(full0 + 8 * s, (kbg / TP_STAGES) & 1, &gave_up)) {
+                    if (lane == 0) { atomicExch(p.status, 2); gave_up = 1; }
+                    ok = false; break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                if (elect_one()) {
+                    const uint32_t sa = tc_smem_u32(stages + (size_t)s * TP_STAGE_BYTES), sb = sa + TP_A_BYTES;
+                    const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sb);
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        umma_bf16(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(empty0 + 8 * s);
+                    if (kb == k_blocks - 1) umma_commit(tfull0 + 8 * buf);
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+            const uint32_t buf = it & 1;
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * buf, (it >> 1) & 1, &gave_up));
+            if (!ok) { if (lane == 0) { atomicExch(p.status, 3); gave_up = 1; } break; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int m = (tile % p.tiles_m) * TC_BM + quad * 32 + lane, nt = tile / p.tiles_m;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * 256u;
+            tp_epilogue_row(p, taddr, m, nt);
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tempty0 + 8 * buf) : "memory");
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ---- the persistent form on pairs of SMs (cta_group::2) -------------------------------------------------
+// Two CTAs of a cluster work on one 256 x BN tile: each loads its own 128 rows of X and only HALF of the
+// tile's rows of W (BN/2), the MMA issued by the first CTA of the pair reads both halves out of both
+// shared memories, and each CTA ends up with its 128 rows of the accumulator in its own TMEM.  A CTA thus
+// pulls 32 KB instead of 48 KB from L2 for the same 128 x 256 x 64 products, which is what bounds the
+// single-CTA form, and the ring holds six stages instead of four.
+//   silu_mul: the first CTA loads the tile's gate rows, the second its up rows.
+// Barriers: the TMA loads of both CTAs complete on the first CTA's full[s]; tcgen05.commit signals
+// empty[s] and tmem_full[b] in both CTAs; the epilogue warps of both arrive on the first CTA's tmem_empty[b].
+#define TQ_STAGES 6
+#define TQ_STAGE_BYTES (2 * TP_A_BYTES)
+#define TQ_SMEM ((size_t)TQ_STAGES * TQ_STAGE_BYTES + (2 * TQ_STAGES + 4) * 8 + 16)
+
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t cluster_id_x() { uint32_t r; asm volatile("mov.u32 %0, %%clusterid.x;\n" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t cluster_count_x() { uint32_t r; asm volatile("mov.u32 %0, %%nclusterid.x;\n" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+    uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(addr), "r"(rank)); return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the barrier at this offset in both CTAs of the pair once the MMAs issued so far have retired
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TpParams p) {
+    extern __shared__ __align__(1024) unsigned char tc_smem[];
+    unsigned char* stages = tc_smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tc_smem + (size_t)TQ_STAGES * TQ_STAGE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TQ_STAGES + 4);
+    __shared__ volatile int gave_up;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int first_tile = (int)cluster_id_x(), tile_step = (int)cluster_count_x();
+    const int k_blocks = (p.K + TC_BK - 1) / TC_BK;
+    const int n_tiles = p.tiles_m * p.tiles_n;             // tiles_m counts 256-row tiles here
+    const int half = p.bn >> 1;
+    const uint32_t full0 = tc_smem_u32(bars), empty0 = tc_smem_u32(bars + TQ_STAGES);
+    const uint32_t tfull0 = tc_smem_u32(bars + 2 * TQ_STAGES), tempty0 = tc_smem_u32(bars + 2 * TQ_STAGES + 2);
+
+    if (threadIdx.x == 0) {
+        gave_up = 0;
+        for (int s = 0; s < TQ_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {       // one warp of each CTA of the pair takes part; both get the same columns
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                                    // the peer's barriers exist before anything signals them
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        const uint32_t stage_tx = TP_A_BYTES + (uint32_t)half * TC_BK * 2;      // per CTA
+        uint32_t kbg = 0;
+        bool ok = true;
+        for (int tile = first_tile; tile < n_tiles && ok; tile += tile_step) {
+            const int m0 = (tile % p.tiles_m) * 256 + (int)rank * TC_BM, nt = tile / p.tiles_m;
+            const int row_b = p.silu_mul ? (rank == 0 ? nt * half : p.up_row0 + nt * half) : nt * p.bn + (int)rank * half;
+            for (int kb = 0; kb < k_blocks; ++kb, ++kbg) {
+                const uint32_t s = kbg % TQ_STAGES;
+                if (kbg >= TQ_STAGES && !mbar_wait_warp(empty0 + 8 * s, ((kbg / TQ_STAGES) - 1) & 1, &gave_up)) {
+                    if (lane == 0) { atomicExch(p.status, 1); gave_up = 1; }
+                    ok = false; break;
+                }
+                if (elect_one()) {
+                    const uint32_t sa = tc_smem_u32(stages + (size_t)s * TQ_STAGE_BYTES), sb = sa + TP_A_BYTES;
+                    const uint32_t lead_full = mapa_shared(full0 + 8 * s, 0);
+                    if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * stage_tx);
+                    tma_load_2d_pair(sa, &map_a, kb * TC_BK, m0, lead_full);
+                    tma_load_2d_pair(sb, &map_b, kb * TC_BK, row_b, lead_full);
+                }
+                __syncwarp();
+            }
+        }
+        if (rank == 0 && (!ok || gave_up)) {
+            // copies of either CTA that were started but never consumed: let them land before the pair leaves
+            const uint32_t last = kbg < TQ_STAGES ? kbg : TQ_STAGES;
+            for (uint32_t i = 0; i < last; ++i) {
+                const uint32_t g = kbg - 1 - i, s = g % TQ_STAGES;
+                mbar_wait(full0 + 8 * s, (g / TQ_STAGES) & 1, nullptr);
+            }
+        }
+    } else if (warp == 1) {
+        if (rank == 0) {
+            const uint32_t idesc = umma_idesc_bf16(256, p.bn);
+            uint32_t kbg = 0;
+            bool ok = true;
+            int it = 0;
+            for (int tile = first_tile; tile < n_tiles && ok; tile += tile_step, ++it) {
+                const uint32_t buf = it & 1;
+                if (it >= 2 && !mbar_wait_warp(tempty0 + 8 * buf, ((it >> 1) - 1) & 1, &gave_up)) {
+                    if (lane == 0) { atomicExch(p.status, 4); gave_up = 1; }
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t tmem_d = tmem_base + buf * 256u;
+                for (int kb = 0; kb < k_blocks; ++kb, ++kbg) {
+                    const uint32_t s = kbg % TQ_STAGES;
+                    if (!mbar_wait_warp(full0 + 8 * s, (kbg / TQ_STAGES) & 1, &gave_up)) {
+                        if (lane == 0) { atomicExch(p.status, 2); gave_up = 1; }
+                        ok = false; break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    if (elect_one()) {
+                        const uint32_t sa = tc_smem_u32(stages + (size_t)s * TQ_STAGE_BYTES), sb = sa + TP_A_BYTES;
+                        const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sb);
+#pragma unroll
+                        for (int k = 0; k < TC_BK / 16; ++k)
+                            umma_bf16_pair(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_commit_pair(empty0 + 8 * s);
+                        if (kb == k_blocks - 1) umma_commit_pair(tfull0 + 8 * buf);
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        int it = 0;
+        for (int tile = first_tile; tile < n_tiles; tile += tile_step, ++it) {
+            const uint32_t buf = it & 1;
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * buf, (it >> 1) & 1, &gave_up));
+            if (!ok) { if (lane == 0) { atomicExch(p.status, 3); gave_up = 1; } break; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int m = (tile % p.tiles_m) * 256 + (int)rank * TC_BM + quad * 32 + lane, nt = tile / p.tiles_m;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * 256u;
+            tp_epilogue_row(p, taddr, m, nt);
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(mapa_shared(tempty0 + 8 * buf, 0)) : "memory");
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                                    // neither CTA's memory goes away while the other may read it
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
     }
 }
 
@@ -289,4 +697,122 @@ ZI_EXPORT int zi_gemm_tcgen05(const void* X, const void* W, const void* bias, vo
         case 128: return tc_launch<128, 6>(ma, mb, p, tiles_a, tiles_b, stream);
         default: return tc_launch<256, 4>(ma, mb, p, tiles_a, tiles_b, stream);
     }
+}
+
+// Cost of one 16-deep MMA step of a 128 x bn tile in SM clocks: the tensor pipe needs bn / 2, shared memory
+// has to deliver the A (4 KB) and B (32 bn bytes) operands at 128 bytes a clock.
+static int tp_step_cost(int bn) { const int pipe = bn / 2, smem = 32 + bn / 4; return pipe > smem ? pipe : smem; }
+
+// C[M,N] = X[M,K] . W^T with the persistent kernel.  epilogue 0: W is [N,K], optional bias[N].
+// epilogue 1 (silu_mul): W is [2N,K] = [gate; up], C = silu(X.gate^T) * (X.up^T), no bias.
+// bn_hint: 0 lets the call choose the tile width; else a multiple of 16 (32 for silu_mul) up to 256.
+ZI_EXPORT int zi_gemm_tcgen05_tiles(const void* X, const void* W, const void* bias, void* C, int c_dtype, int* status, int M, int N,
+                                    int K, long long ldx, long long ldw, long long ldc, int epilogue, int bn_hint, int num_sms,
+                                    cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0) return zi_fail("gemm_tcgen05: K=%d must be positive", K);
+    if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return zi_fail("gemm_tcgen05: K and the row strides must be multiples of 8 elements (16 bytes) for TMA; got K=%d ldx=%lld ldw=%lld", K, ldx, ldw);
+    if (((uintptr_t)X | (uintptr_t)W) & 15) return zi_fail("gemm_tcgen05: operands must be 16-byte aligned");
+    if (c_dtype != ZI_F32 && c_dtype != ZI_BF16) return zi_fail("gemm_tcgen05: unknown output dtype %d", c_dtype);
+    if (epilogue != 0 && epilogue != 1) return zi_fail("gemm_tcgen05: unknown epilogue %d", epilogue);
+    if (epilogue == 1 && bias) return zi_fail("gemm_tcgen05: the silu_mul epilogue takes no bias");
+    if (!status) return zi_fail("gemm_tcgen05: a status word is required");
+    if (num_sms <= 0) return zi_fail("gemm_tcgen05: num_sms=%d must be positive", num_sms);
+    if (tc_init()) return 1;
+    const int step = epilogue == 1 ? 32 : 16;              // silu_mul: both halves are multiples of 16 columns
+    const int tiles_m = (M + TC_BM - 1) / TC_BM;
+    int bn = bn_hint;
+    if (bn == 0) {
+        long long best = -1;
+        for (int cand = 256; cand >= step; cand -= step) {
+            const int cols = epilogue == 1 ? cand / 2 : cand;
+            const long long tiles = (long long)tiles_m * ((N + cols - 1) / cols);
+            const long long cost = ((tiles + num_sms - 1) / num_sms) * tp_step_cost(cand);
+            if (best < 0 || cost < best) { best = cost; bn = cand; }
+        }
+    }
+    if (bn < step || bn > 256 || bn % step) return zi_fail("gemm_tcgen05: tile width %d must be a multiple of %d up to 256", bn, step);
+    TpParams p;
+    p.C = C; p.bias = (const bf16*)bias; p.status = status; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
+    p.c_is_f32 = c_dtype == ZI_F32; p.silu_mul = epilogue; p.bn = bn; p.up_row0 = N;
+    p.tiles_m = tiles_m;
+    const int cols = epilogue == 1 ? bn / 2 : bn;
+    p.tiles_n = (N + cols - 1) / cols;
+    const long long n_tiles = (long long)p.tiles_m * p.tiles_n;
+    if (n_tiles > 0x7fffffffLL) return zi_fail("gemm_tcgen05: too many tiles");
+    CUtensorMap ma, mb;
+    if (tc_make_map(&ma, X, M, K, ldx, TC_BM)) return 1;
+    if (tc_make_map(&mb, W, epilogue == 1 ? 2LL * N : N, K, ldw, bn / 2)) return 1;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TP_SMEM);
+        if (e != cudaSuccess) return zi_fail("gemm_tcgen05: cannot reserve %zu bytes of shared memory: %s", TP_SMEM, cudaGetErrorString(e));
+        attr_set = true;
+    }
+    const int grid = (int)(n_tiles < num_sms ? n_tiles : num_sms);
+    gemm_tcgen05_persistent_kernel<<<grid, TC_THREADS, TP_SMEM, stream>>>(ma, mb, p);
+    return zi_check_launch("gemm_tcgen05_persistent");
+}
+
+static int tq_step_cost(int bn) { const int pipe = bn / 2, smem = 32 + bn / 8; return pipe > smem ? pipe : smem; }
+
+// The same product on pairs of SMs (256-row tiles).  Arguments as zi_gemm_tcgen05_tiles, without num_sms:
+// the number of pairs that fit on the device at once is asked of the runtime.
+ZI_EXPORT int zi_gemm_tcgen05_pairs(const void* X, const void* W, const void* bias, void* C, int c_dtype, int* status, int M, int N,
+                                    int K, long long ldx, long long ldw, long long ldc, int epilogue, int bn_hint, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0) return zi_fail("gemm_tcgen05: K=%d must be positive", K);
+    if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return zi_fail("gemm_tcgen05: K and the row strides must be multiples of 8 elements (16 bytes) for TMA; got K=%d ldx=%lld ldw=%lld", K, ldx, ldw);
+    if (((uintptr_t)X | (uintptr_t)W) & 15) return zi_fail("gemm_tcgen05: operands must be 16-byte aligned");
+    if (c_dtype != ZI_F32 && c_dtype != ZI_BF16) return zi_fail("gemm_tcgen05: unknown output dtype %d", c_dtype);
+    if (epilogue != 0 && epilogue != 1) return zi_fail("gemm_tcgen05: unknown epilogue %d", epilogue);
+    if (epilogue == 1 && bias) return zi_fail("gemm_tcgen05: the silu_mul epilogue takes no bias");
+    if (!status) return zi_fail("gemm_tcgen05: a status word is required");
+    if (tc_init()) return 1;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = TQ_SMEM; cfg.stream = stream; cfg.attrs = attr; cfg.numAttrs = 1;
+    static int max_pairs = 0;
+    if (max_pairs == 0) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TQ_SMEM);
+        if (e != cudaSuccess) return zi_fail("gemm_tcgen05: cannot reserve %zu bytes of shared memory: %s", TQ_SMEM, cudaGetErrorString(e));
+        int sms = 0, dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cfg.gridDim = dim3(sms > 1 ? sms & ~1 : 2);
+        int n = 0;
+        e = cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_kernel, &cfg);
+        if (e != cudaSuccess || n <= 0) return zi_fail("gemm_tcgen05: no pair of CTAs of this kernel fits on the device (%s)", cudaGetErrorString(e));
+        max_pairs = n;
+    }
+    const int step = epilogue == 1 ? 32 : 16;
+    const int tiles_m = (M + 255) / 256;
+    int bn = bn_hint;
+    if (bn == 0) {
+        long long best = -1;
+        for (int cand = 256; cand >= step; cand -= step) {
+            const int cols = epilogue == 1 ? cand / 2 : cand;
+            const long long tiles = (long long)tiles_m * ((N + cols - 1) / cols);
+            const long long cost = ((tiles + max_pairs - 1) / max_pairs) * tq_step_cost(cand);
+            if (best < 0 || cost < best) { best = cost; bn = cand; }
+        }
+    }
+    if (bn < step || bn > 256 || bn % step) return zi_fail("gemm_tcgen05: tile width %d must be a multiple of %d up to 256", bn, step);
+    TpParams p;
+    p.C = C; p.bias = (const bf16*)bias; p.status = status; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
+    p.c_is_f32 = c_dtype == ZI_F32; p.silu_mul = epilogue; p.bn = bn; p.up_row0 = N;
+    p.tiles_m = tiles_m;
+    const int cols = epilogue == 1 ? bn / 2 : bn;
+    p.tiles_n = (N + cols - 1) / cols;
+    const long long n_tiles = (long long)p.tiles_m * p.tiles_n;
+    if (n_tiles > 0x7fffffffLL) return zi_fail("gemm_tcgen05: too many tiles");
+    CUtensorMap ma, mb;
+    if (tc_make_map(&ma, X, M, K, ldx, TC_BM)) return 1;
+    if (tc_make_map(&mb, W, epilogue == 1 ? 2LL * N : N, K, ldw, bn / 2)) return 1;
+    cfg.gridDim = dim3(2 * (unsigned)(n_tiles < max_pairs ? n_tiles : max_pairs));
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel, ma, mb, p);
+    if (e != cudaSuccess) return zi_fail("gemm_tcgen05_pairs: launch failed: %s", cudaGetErrorString(e));
+    return zi_check_launch("gemm_tcgen05_pairs");
 }

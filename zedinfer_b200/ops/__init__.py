@@ -25,7 +25,7 @@ _gemm_tcgen05 = Library("gemm_tcgen05")
 SMALL_M_ROWS = 16                # the weight-streaming kernel takes up to this many rows
 
 __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "silu_mul", "cast",
-           "gemm_nt", "linear", "gemm_smallm", "gemm_tcgen05", "tcgen05_status", "can_fuse_silu_mul", "paged_attention", "attention", "decode_attention", "prefill_attention", "argmax", "sample", "repetition_penalty", "advance_decode"]
+           "gemm_nt", "linear", "gemm_smallm", "gemm_tcgen05", "gemm_tcgen05_tiles", "tcgen05_status", "can_fuse_silu_mul", "paged_attention", "attention", "decode_attention", "prefill_attention", "argmax", "sample", "repetition_penalty", "advance_decode"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
@@ -209,6 +209,44 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     _gemm_tcgen05.call("zi_gemm_tcgen05", ptr(x), ptr(w), ptr(bias), ptr(out), c_int(dtype_code(out.dtype)),
                        ptr(_tc_status(x.device)), c_int(m), c_int(n), c_int(k), c_ll(x.stride(0)), c_ll(w.stride(0)),
                        c_ll(out.stride(0)), c_int(1 if swapped else 0), stream())
+
+
+_sm_count: Dict = {}
+
+
+def _num_sms(device) -> int:
+    if device not in _sm_count:
+        _sm_count[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _sm_count[device]
+
+
+def gemm_tcgen05_tiles(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                       silu_mul: bool = False, tile_width: int = 0, pairs: Optional[bool] = None) -> None:
+    """``out = x @ w.T + bias`` for many rows: one persistent CTA per SM walks 128-row tiles, the accumulator
+    double-buffered in TMEM so that the epilogue of a tile overlaps the products of the next.
+
+    With ``silu_mul`` the weight is ``[gate; up]`` stacked (``[2 * n, k]``) and ``out[m, n] = silu(x.gate^T) *
+    (x.up^T)``; neither half is written to memory.  ``tile_width`` (accumulator columns per tile) is chosen by
+    the call when 0.  ``pairs``: two SMs share a 256-row tile and each loads only half of its weight rows
+    (``cta_group::2``); the default for more than 128 rows.
+    """
+    need_cuda(x, w, bias, out)
+    m, k = x.shape
+    n = out.shape[1]
+    if w.shape != ((2 * n if silu_mul else n), k) or out.shape[0] != m or out.stride(1) != 1 or x.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError(f"gemm_tcgen05_tiles: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or (bias is not None and bias.dtype != torch.bfloat16):
+        raise KernelError("gemm_tcgen05_tiles: bfloat16 operands only")
+    if pairs is None:
+        pairs = m > 128
+    if pairs:
+        _gemm_tcgen05.call("zi_gemm_tcgen05_pairs", ptr(x), ptr(w), ptr(bias), ptr(out), c_int(dtype_code(out.dtype)),
+                           ptr(_tc_status(x.device)), c_int(m), c_int(n), c_int(k), c_ll(x.stride(0)), c_ll(w.stride(0)),
+                           c_ll(out.stride(0)), c_int(1 if silu_mul else 0), c_int(tile_width), stream())
+        return
+    _gemm_tcgen05.call("zi_gemm_tcgen05_tiles", ptr(x), ptr(w), ptr(bias), ptr(out), c_int(dtype_code(out.dtype)),
+                       ptr(_tc_status(x.device)), c_int(m), c_int(n), c_int(k), c_ll(x.stride(0)), c_ll(w.stride(0)),
+                       c_ll(out.stride(0)), c_int(1 if silu_mul else 0), c_int(tile_width), c_int(_num_sms(x.device)), stream())
 
 
 def tcgen05_status(device) -> int:
