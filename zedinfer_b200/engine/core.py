@@ -14,6 +14,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from .. import ops
 from ..cache.manager import CacheManager, RequestCache
 from ..config.registry import load_model_config
 from ..parts.base import StepContext
@@ -314,6 +315,7 @@ class EngineCore:
         else:
             ctx, want = self.build_context(entries, rcs)
             logits = self.model.forward(ctx, self.views, want)
+            ops.raise_if_tcgen05_failed(self.device)
         for e, rc in zip(entries, rcs):
             self.cache.commit(rc, rc.length + len(e.tokens))
         return logits

@@ -25,7 +25,7 @@ _gemm_tcgen05 = Library("gemm_tcgen05")
 SMALL_M_ROWS = 16                # the weight-streaming kernel takes up to this many rows
 
 __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "silu_mul", "cast",
-           "gemm_nt", "linear", "gemm_smallm", "gemm_tcgen05", "gemm_tcgen05_tiles", "tcgen05_status", "can_fuse_silu_mul", "paged_attention", "attention", "decode_attention", "prefill_attention", "argmax", "sample", "repetition_penalty", "advance_decode"]
+           "gemm_nt", "linear", "gemm_smallm", "gemm_tcgen05", "gemm_tcgen05_tiles", "tcgen05_status", "linear_silu_mul", "raise_if_tcgen05_failed", "paged_attention", "attention", "decode_attention", "prefill_attention", "argmax", "sample", "repetition_penalty", "advance_decode"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
@@ -258,15 +258,53 @@ def tcgen05_status(device) -> int:
     return v
 
 
-def can_fuse_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, bias: Optional[torch.Tensor]) -> bool:
-    return bias is None and _small_m_ok(x, w_gate_up)
+TC_MIN_ROWS = 1024               # rows from which the tcgen05 kernel takes a plain bfloat16 product
+TC_FUSED_MIN_ROWS = 128          # ... and a gate/up product with the activation in its epilogue
+_tc_launched: Dict = {}
+
+
+def _tc_ok(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and (bias is None or bias.dtype == torch.bfloat16)
+            and out.dtype in (torch.bfloat16, torch.float32) and x.shape[1] % 8 == 0
+            and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1 and x.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def raise_if_tcgen05_failed(device) -> None:
+    """After a step that launched tcgen05 products: synchronise and fail loudly if a bounded wait ran out."""
+    device = torch.device(device)
+    if _tc_launched.pop(device, False):
+        code = tcgen05_status(device)
+        if code:
+            raise KernelError(f"gemm_tcgen05: a bounded wait ran out inside the kernel (role {code}); the step's output is not valid")
+
+
+def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """``out = silu(x @ gate.T + b_gate) * (x @ up.T + b_up)`` with ``w_gate_up = [gate; up]`` stacked.
+
+    bfloat16 without bias: the activation runs in the product's epilogue (weight-streaming kernel up to 16 rows,
+    tcgen05 kernel from ``TC_FUSED_MIN_ROWS``), so neither half reaches memory.  Otherwise: product, then the
+    elementwise kernel.
+    """
+    need_cuda(x, w_gate_up, bias, out)
+    if bias is None and _small_m_ok(x, w_gate_up):
+        gemm_smallm(x, w_gate_up, None, out, silu_mul=True)
+        return
+    if bias is None and x.shape[0] >= TC_FUSED_MIN_ROWS and out.dtype == torch.bfloat16 and _tc_ok(x, w_gate_up, None, out):
+        gemm_tcgen05_tiles(x, w_gate_up, None, out, silu_mul=True)
+        _tc_launched[x.device] = True
+        return
+    gate_up = torch.empty((x.shape[0], w_gate_up.shape[0]), dtype=out.dtype, device=x.device)
+    linear(x, w_gate_up, bias, gate_up)
+    silu_mul(gate_up, out)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
-    """``out = x @ w.T + bias``; picks the kernel by operand types.
+    """``out = x @ w.T + bias``; picks the kernel by operand types and the number of rows.
 
     * any float32 operand: the SIMT kernel (true 32-bit arithmetic);
     * bfloat16 x bfloat16 with at most 16 rows (decode steps): the weight-streaming tensor-core kernel;
+    * bfloat16 x bfloat16 from ``TC_MIN_ROWS`` rows (prefill): the tcgen05 kernel on pairs of SMs;
     * bfloat16 x bfloat16 otherwise: cuBLAS with float32 accumulation, the library product the
       reference's engine uses as well; the output may be bfloat16 or float32.
     """
@@ -274,6 +312,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and (bias is None or bias.dtype == torch.bfloat16):
         if _small_m_ok(x, w) and out.stride(1) == 1:
             gemm_smallm(x, w, bias, out)
+            return
+        if x.shape[0] >= TC_MIN_ROWS and _tc_ok(x, w, bias, out):
+            gemm_tcgen05_tiles(x, w, bias, out)
+            _tc_launched[x.device] = True
             return
         if out.dtype == torch.bfloat16:
             if bias is not None:

@@ -50,12 +50,7 @@ class GatedMLP(FeedForward):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         n = x.shape[0]
         act = ctx.empty(n, self.intermediate_size)
-        if ops.can_fuse_silu_mul(x, self.w_gate_up, self.b_gate_up):
-            ops.gemm_smallm(x, self.w_gate_up, None, act, silu_mul=True)      # activation in the product's epilogue
-        else:
-            gate_up = ctx.empty(n, 2 * self.intermediate_size)
-            ops.linear(x, self.w_gate_up, self.b_gate_up, gate_up)
-            ops.silu_mul(gate_up, act)
+        ops.linear_silu_mul(x, self.w_gate_up, self.b_gate_up, act)     # activation in the product's epilogue where it can be
         out = ctx.empty(n, self.hidden_size)
         ops.linear(act, self.w_down, self.b_down, out)
         return out
