@@ -136,13 +136,16 @@ def plain_attention_rows(q, k, v, positions, scale, window):
     """q [n, nh, hd] at the given positions of a sequence whose k, v are [L, nkv, hd]."""
     out = torch.zeros_like(q)
     nh, nkv = q.shape[1], k.shape[1]
-    for i, p in enumerate(positions):
-        lo = max(0, p - window + 1) if window else 0
-        for h in range(nh):
-            kvh = h // (nh // nkv)
-            s = (k[lo:p + 1, kvh] @ q[i, h]) * scale
-            pr = torch.softmax(s, dim=0)
-            out[i, h] = pr @ v[lo:p + 1, kvh]
+    pos = torch.tensor(list(positions))
+    keys = torch.arange(k.shape[0])
+    seen = keys[None, :] <= pos[:, None]
+    if window:
+        seen &= keys[None, :] > pos[:, None] - window
+    for h in range(nh):
+        kvh = h // (nh // nkv)
+        s = (q[:, h] @ k[:, kvh].t()) * scale
+        s = s.masked_fill(~seen, float("-inf"))
+        out[:, h] = torch.softmax(s, dim=1) @ v[:, kvh]
     return out
 
 
@@ -304,37 +307,49 @@ def test_decode_attention_mma(nh, nkv, hd, ps, window):
     assert float((out2.float() - out.float()).abs().max()) < 2e-2
 
 
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
 @pytest.mark.parametrize("nh,nkv,hd,ps,window", [(12, 2, 128, 16, None), (3, 1, 64, 4, None), (5, 5, 128, 24, None),
-                                                  (6, 2, 64, 16, 50), (12, 2, 128, 16, 130)])
-def test_prefill_attention_mma(nh, nkv, hd, ps, window):
+                                                  (6, 2, 64, 16, 50), (12, 2, 128, 16, 130), (4, 2, 64, 128, None),
+                                                  (6, 1, 128, 8, 260), (2, 1, 128, 64, None)])
+def test_prefill_attention_tensor_cores(nh, nkv, hd, ps, window, kernel):
     from zedinfer_b200 import ops
+    if kernel == "tcgen05" and not ops.tcgen05_attention_ok(hd, ps):
+        pytest.skip("page size outside what the tcgen05 kernel takes; the engine uses the mma.sync kernel there")
     t = torch.bfloat16
-    lens = [200, 70, 64, 333, 1]
+    lens = [200, 70, 64, 333, 1, 1100, 1100]
     pool, view, tables, ks, vs, page_stride, kv_stride = build_cache(len(lens), lens, nkv, hd, ps, t, seed=6)
-    # portions: (request, first position, count).  Whole prompts, a portion in mid-prompt, one decoded token.
-    portions = [(0, 0, 200), (1, 60, 10), (2, 0, 64), (3, 130, 203), (4, 0, 1), ]
+    # portions: (request, first position, count).  Whole prompts, portions in mid-prompt, one decoded token, a long
+    # prompt (nine key tiles: every ring of the tcgen05 kernel turns over several times) and a late portion of one.
+    portions = [(0, 0, 200), (1, 60, 10), (2, 0, 64), (3, 130, 203), (4, 0, 1), (5, 0, 1100), (6, 517, 583)]
     g = torch.Generator().manual_seed(4)
     qs, pos, tiles = [], [], []
     n = 0
+    rows = ops.PREFILL_TILE_ROWS
     for si, (r, p0, cnt) in enumerate(portions):
-        for q0 in range(0, cnt, 64):
-            tiles.append((n + q0, min(64, cnt - q0), si))
+        for q0 in range(0, cnt, rows):
+            tiles.append((n + q0, min(rows, cnt - q0), si))
         for i in range(cnt):
             qs.append(torch.randn(nh, hd, generator=g))
             pos.append(p0 + i)
         n += cnt
     q = torch.stack(qs)
-    # the last query of request 3 looks hard at one far key (or the first key inside its window)
+    # the last query of request 3 looks hard at one far key (or the first key inside its window), and so does the
+    # last query of the long prompt at a key of its first tile
     far = 7 if not window else 332 - window + 1
     q[200 + 10 + 64 + 202, :, :] = ks[3][far, 0][None, :] * 4.0
+    far5 = 5 if not window else 1099 - window + 1
+    q[200 + 10 + 64 + 203 + 1 + 1099, :, :] = ks[5][far5, 0][None, :] * 4.0
     qd = q.to(t).to(dev())
     seg_tables = torch.stack([tables[r] for r, _, _ in portions])
-    out = torch.empty(n, nh * hd, dtype=t, device=dev())
+    out = torch.full((n, nh * hd), float("nan"), dtype=t, device=dev())
     scale = 1.0 / math.sqrt(hd)
-    ops.prefill_attention(qd, view, out, seg_tables, torch.tensor(tiles, dtype=torch.int32, device=dev()),
-                          torch.tensor(pos, dtype=torch.int32, device=dev()), nh, nkv, hd, ps, page_stride, kv_stride,
-                          window, scale)
+    fn = ops.prefill_attention if kernel == "mma" else ops.prefill_attention_tcgen05
+    fn(qd, view, out, seg_tables, torch.tensor(tiles, dtype=torch.int32, device=dev()),
+       torch.tensor(pos, dtype=torch.int32, device=dev()), nh, nkv, hd, ps, page_stride, kv_stride, window, scale)
+    torch.cuda.synchronize()
+    assert ops.tcgen05_status(dev()) == 0
     got = out.float().cpu().view(n, nh, hd)
+    assert torch.isfinite(got).all()
     qf = qd.float().cpu()
     i = 0
     for r, p0, cnt in portions:
@@ -342,66 +357,3 @@ def test_prefill_attention_mma(nh, nkv, hd, ps, window):
         err = float((got[i:i + cnt] - ref).abs().max())
         assert err < 2e-2, (r, p0, cnt, err)
         i += cnt
-
-
-def test_attention_kernels_refuse_what_they_cannot_do():
-    from zedinfer_b200 import ops
-    t = torch.bfloat16
-    pool, view, tables, ks, vs, page_stride, kv_stride = build_cache(1, [10], 1, 32, 4, t)
-    q = torch.zeros(1, 2, 32, dtype=t, device=dev())
-    out = torch.empty(1, 64, dtype=t, device=dev())
-    z = torch.zeros(1, dtype=torch.int32, device=dev())
-    with pytest.raises(ops.KernelError, match="head_dim 64 or 128"):
-        ops.decode_attention(q, view, out, tables, z, z, 2, 1, 32, 4, page_stride, kv_stride, None, 1.0)
-    with pytest.raises(ops.KernelError, match="multiple of 8"):
-        ops.paged_attention(torch.zeros(1, 2, 12, dtype=t, device=dev()), view, torch.empty(1, 24, dtype=t, device=dev()),
-                            tables, z, z, 2, 1, 12, 4, page_stride, kv_stride, None, 1.0)
-    with pytest.raises(ops.KernelError, match="cannot share"):
-        ops.paged_attention(torch.zeros(1, 3, 32, dtype=t, device=dev()), view, torch.empty(1, 96, dtype=t, device=dev()),
-                            tables, z, z, 3, 2, 32, 4, page_stride, kv_stride, None, 1.0)
-    with pytest.raises(ops.KernelError, match="GPU only"):
-        ops.silu_mul(torch.zeros(2, 4), torch.zeros(2, 2))
-
-
-@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("n,k", [(1000, 96), (2048, 1536), (1536, 8960), (50, 64)])
-def test_gemm_smallm(m, n, k):
-    from zedinfer_b200 import ops
-    x = rand(m, k, dtype=torch.bfloat16)
-    w = rand(n, k, dtype=torch.bfloat16, seed=1, scale=0.05)
-    b = rand(n, dtype=torch.bfloat16, seed=2)
-    ref = x.double().cpu() @ w.double().cpu().t()
-    for out_dtype, bias in ((torch.bfloat16, b), (torch.float32, None)):
-        out = torch.full((m, n), float("nan"), dtype=out_dtype, device=dev())
-        ops.gemm_smallm(x, w, bias, out)
-        r = (ref + b.double().cpu()) if bias is not None else ref
-        tol = 2e-2 if out_dtype == torch.bfloat16 else 2e-3
-        assert torch.allclose(out.double().cpu(), r, atol=tol * 3, rtol=tol)
-        # a token's result does not depend on how many tokens are in the step
-        if m > 1:
-            one = torch.empty(1, n, dtype=out_dtype, device=dev())
-            ops.gemm_smallm(x[m - 1:m], w, bias, one)
-            assert torch.equal(one[0], out[m - 1])
-    # ops.linear routes here for few rows and agrees with the SIMT product
-    out_l = torch.empty(m, n, dtype=torch.float32, device=dev())
-    ops.linear(x, w, None, out_l)
-    out_s = torch.empty(m, n, dtype=torch.float32, device=dev())
-    ops.gemm_nt(x, w, None, out_s)
-    assert torch.allclose(out_l, out_s, atol=2e-3, rtol=2e-3)
-
-
-@pytest.mark.parametrize("m,inter,k", [(1, 176, 64), (8, 8960, 1536), (13, 200, 96)])
-def test_gemm_smallm_fused_activation(m, inter, k):
-    from zedinfer_b200 import ops
-    x = rand(m, k, dtype=torch.bfloat16)
-    w = rand(2 * inter, k, dtype=torch.bfloat16, seed=3, scale=0.1)
-    fused = torch.empty(m, inter, dtype=torch.bfloat16, device=dev())
-    ops.gemm_smallm(x, w, None, fused, silu_mul=True)
-    gu = torch.empty(m, 2 * inter, dtype=torch.bfloat16, device=dev())
-    ops.gemm_smallm(x, w, None, gu)
-    unfused = torch.empty_like(fused)
-    ops.silu_mul(gu, unfused)
-    assert torch.equal(fused, unfused)                   # same sums, same roundings
-    g = (x.double().cpu() @ w[:inter].double().cpu().t()).float().to(torch.bfloat16).float()
-    u = (x.double().cpu() @ w[inter:].double().cpu().t()).float().to(torch.bfloat16).float()
-    assert torch.allclose(fused.float().cpu(), P.swiglu(g, u), atol=3e-2, rtol=3e-2)

@@ -143,7 +143,8 @@ class CacheManager:
         self.set_num_pages(num_pages)
         self.device, self.dtype = torch.device(device), dtype
         for g in self.groups:
-            g.tensor = torch.empty((num_pages + 1, len(g.calls), 2, g.n_kv_heads, self.page_size, g.head_dim),
+            # zeroed: attention multiplies slots that hold nothing yet by probability 0, which must not meet NaN bits
+            g.tensor = torch.zeros((num_pages + 1, len(g.calls), 2, g.n_kv_heads, self.page_size, g.head_dim),
                                    dtype=dtype, device=device)
         for call, need in self._state_needs.items():
             self._state_tensors[call] = torch.zeros((self.max_requests,) + tuple(need.shape), dtype=need.dtype,

@@ -383,8 +383,12 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ ca
     constexpr int TILE_BYTES = TILE_KEYS * HD * 2;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     // tiles later in a portion see more keys: start them first so that the short ones fill the tail
-    const int tile = gridDim.x - 1 - blockIdx.x;
-    const int n0 = tiles[tile * 3], rows = tiles[tile * 3 + 1], seg = tiles[tile * 3 + 2];
+    // a tile of the list holds up to 128 rows; this block takes one half of 64
+    const int slot = gridDim.x - 1 - blockIdx.x;
+    const int tile = slot >> 1, half_rows = (slot & 1) * 64;
+    const int n0 = tiles[tile * 3] + half_rows, seg = tiles[tile * 3 + 2];
+    const int rows = tiles[tile * 3 + 1] - half_rows < 64 ? tiles[tile * 3 + 1] - half_rows : 64;
+    if (rows <= 0) return;
     const int h = blockIdx.y;
     const int kvh = h / (n_heads / n_kv_heads);
     const int p0 = pos[n0];                                       // positions of a portion are consecutive
@@ -551,7 +555,7 @@ ZI_EXPORT int zi_prefill_attention(const void* q, const void* cache, void* out, 
     if (n_tiles <= 0) return 0;
     if (check_common("prefill_attention", n_heads, n_kv_heads, head_dim, page_size, max_blocks)) return 1;
     if (n_heads > 65535) return zi_fail("prefill_attention: %d heads are more than one launch takes", n_heads);
-    dim3 grid(n_tiles, n_heads);
+    dim3 grid(2 * n_tiles, n_heads);          // two 64-row halves per tile of the list
     const float scale2 = scale * LOG2E;
     const int shift = page_shift_of(page_size);
     if (head_dim == 128) {

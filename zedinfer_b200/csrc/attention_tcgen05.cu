@@ -1,0 +1,403 @@
+// Causal attention of portions of prompts over the paged cache on the 5th-generation tensor cores
+// (bfloat16, head size 64 or 128, pages of 8..128 tokens that divide 128).
+//
+// One CTA takes 128 consecutive query rows of one portion and one head and walks over the keys in tiles of 128:
+//   S = Q . K^T      tcgen05.mma, 128 x 128, both operands K-major in shared memory, S in TMEM (two buffers)
+//   P = exp2(S - m)  four warps, one thread per query row: tcgen05.ld the row, running maximum and sum in
+//                    registers, P written as bfloat16 into shared memory in the 128-byte-swizzled K-major layout
+//   O += P . V       tcgen05.mma, 128 x head size, V straight from its pages as an MN-major operand, O in TMEM
+// K and V tiles come page by page through one 5-d tensor map of the layer's cache (TMA, 128-byte swizzle):
+// the 32 lanes of the producer warp each issue one page-half, the block table gives the page.  Queries come
+// through a 2-d map of the step's q matrix.
+//
+// O stays in TMEM for the whole row of tiles.  Its rescaling when the maximum grows is done lazily: only when
+// a row's maximum exceeds the value in use by more than 2^8, the four warps multiply their O rows in TMEM
+// (tcgen05.ld / st) and their sums by 2^(old - new); otherwise P is simply computed against the older maximum,
+// which changes no result, since sum and O share it and the final division cancels it.
+//
+// Order of the MMAs: QK(0), QK(1), PV(0), QK(2), PV(1), ... so the scores of the next tile are computed while
+// the softmax warps work on this one.  Barriers (all waits bounded, as in the matrix product): q_full,
+// k_full/k_empty[2], v_full/v_empty[2], s_full/s_empty[2], p_full, pv_done.
+//
+// Keys a row must not see (beyond its position, before its window) get probability 0.  Cache slots that hold
+// nothing yet are multiplied by 0 as well, so the pool must never hold NaN bit patterns: it is allocated
+// zeroed, and pages that are used again hold finite values.
+#include "tcgen05.cuh"
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+ZI_DEFINE_LAST_ERROR(attention_tcgen05)
+
+#define FA_ROWS 128
+#define FA_KEYS 128
+#define FA_THREADS 192
+#define FA_LAZY_LOG2 8.0f
+
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];\n"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ float fa_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+// MN-major operand (V: rows are keys, the head dimension is contiguous), 128-byte swizzle: groups of 8 keys are
+// 1024 bytes apart (stride offset); the two 64-wide halves of a 128-wide head are 128 keys x 128 bytes apart
+// (leading offset).
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t lead_bytes) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)(lead_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+struct FaParams {
+    bf16* out;
+    const int* tables;
+    const int* tiles;
+    const int* pos;
+    int* status;
+    int n_heads, n_kv_heads, page_size, max_blocks, window;
+    float scale2;                  // softmax scale x log2(e)
+};
+
+template <int HD>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const FaParams p) {
+    constexpr int HH = HD / 64;                               // 64-wide halves of a head
+    constexpr int SUB = FA_KEYS * 128;                        // bytes of one [128 rows x 128 bytes] sub-tile
+    constexpr int TILE_BYTES = FA_KEYS * HD * 2;              // one K or V tile, or Q
+    extern __shared__ __align__(1024) unsigned char fa_smem[];
+    unsigned char* sQ = fa_smem;
+    unsigned char* sK = sQ + TILE_BYTES;                      // two stages
+    unsigned char* sV = sK + 2 * TILE_BYTES;                  // two stages
+    unsigned char* sP = sV + 2 * TILE_BYTES;                  // [128 rows x 128 keys] bfloat16, two sub-tiles
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * SUB);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+    __shared__ volatile int gave_up;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t b0 = tc_smem_u32(bars);
+    const uint32_t q_full = b0, k_full = b0 + 8, k_empty = b0 + 24, v_full = b0 + 40, v_empty = b0 + 56,
+                   s_full = b0 + 72, s_empty = b0 + 88, p_full = b0 + 104, pv_done = b0 + 112;       // 15 barriers
+    // the later tiles of a portion see more keys: start them first
+    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int n0 = p.tiles[tile * 3], rows = p.tiles[tile * 3 + 1], seg = p.tiles[tile * 3 + 2];
+    const int h = blockIdx.y, kvh = h / (p.n_heads / p.n_kv_heads);
+    const int p0 = p.pos[n0], p_last = p0 + rows - 1;         // positions of a tile are consecutive
+    const int lo_tile = (p.window > 0 && p0 - p.window + 1 > 0) ? p0 - p.window + 1 : 0;
+    const int kt_begin = lo_tile / FA_KEYS, n_kt = p_last / FA_KEYS - kt_begin + 1;
+
+    if (threadIdx.x == 0) {
+        gave_up = 0;
+        for (int i = 0; i < 15; ++i) mbar_init(b0 + 8 * i, (i >= 11 && i <= 13) ? 4 : 1);      // s_empty[2], p_full: one arrival per softmax warp
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_o = tmem_base + 256u;
+
+    if (warp == 0) {
+        // ---- producer ---------------------------------------------------------------------------------------
+        if (elect_one()) {
+            mbar_expect_tx(q_full, TILE_BYTES);
+#pragma unroll
+            for (int hh = 0; hh < HH; ++hh) tma_load_2d(tc_smem_u32(sQ) + hh * SUB, &map_q, h * HD + hh * 64, n0, q_full);
+        }
+        __syncwarp();
+        const int* table = p.tables + (size_t)seg * p.max_blocks;
+        const int ppt = FA_KEYS / p.page_size;                // pages per tile
+        const int ops = 2 * ppt * HH;
+        int issued = 0;
+        for (int j = 0; j < n_kt; ++j) {
+            const int st = j & 1;
+            if (j >= 2) {
+                const uint32_t par = ((j >> 1) - 1) & 1;
+                if (!mbar_wait_warp(k_empty + 8 * st, par, &gave_up) || !mbar_wait_warp(v_empty + 8 * st, par, &gave_up)) {
+                    if (lane == 0) { atomicExch(p.status, 11); gave_up = 1; }
+                    break;
+                }
+            }
+            if (elect_one()) { mbar_expect_tx(k_full + 8 * st, TILE_BYTES); mbar_expect_tx(v_full + 8 * st, TILE_BYTES); }
+            __syncwarp();
+            const int blk0 = (kt_begin + j) * ppt;
+            for (int op = lane; op < ops; op += 32) {
+                const int kv = op / (ppt * HH), rem = op - kv * (ppt * HH), pg = rem / HH, hh = rem - pg * HH;
+                const int blk = blk0 + pg;
+                const int page = blk < p.max_blocks ? table[blk] : -1;       // -1: outside the map, reads zeros
+                const uint32_t dst = tc_smem_u32(kv ? sV : sK) + st * TILE_BYTES + hh * SUB + pg * p.page_size * 128;
+                tma_load_5d(dst, &map_kv, hh * 64, 0, kvh, kv, page, (kv ? v_full : k_full) + 8 * st);
+            }
+            __syncwarp();
+            issued = j + 1;
+        }
+        if (gave_up) {      // copies in flight: let them land before the CTA's memory goes away
+            mbar_wait(q_full, 0, nullptr);
+            for (int j = issued > 2 ? issued - 2 : 0; j < issued; ++j) {
+                mbar_wait(k_full + 8 * (j & 1), (j >> 1) & 1, nullptr);
+                mbar_wait(v_full + 8 * (j & 1), (j >> 1) & 1, nullptr);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer -------------------------------------------------------------------------------------
+        constexpr uint32_t idesc_qk = umma_idesc_bf16(FA_ROWS, FA_KEYS);
+        constexpr uint32_t idesc_pv = umma_idesc_bf16(FA_ROWS, HD) | (1u << 16);      // B operand MN-major
+        bool ok = mbar_wait_warp(q_full, 0, &gave_up);
+        if (!ok && lane == 0) { atomicExch(p.status, 12); gave_up = 1; }
+        auto issue_qk = [&](int j) -> bool {
+            const int st = j & 1;
+            if (!mbar_wait_warp(k_full + 8 * st, (j >> 1) & 1, &gave_up)) return false;
+            if (j >= 2 && !mbar_wait_warp(s_empty + 8 * st, ((j >> 1) - 1) & 1, &gave_up)) return false;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (elect_one()) {
+                const uint32_t a0 = tc_smem_u32(sQ), k0 = tc_smem_u32(sK) + st * TILE_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint32_t off = (ks >> 2) * SUB + (ks & 3) * 32;
+                    umma_bf16(tmem_base + st * 128u, umma_desc_sw128(a0 + off), umma_desc_sw128(k0 + off), idesc_qk, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(s_full + 8 * st);
+                umma_commit(k_empty + 8 * st);
+            }
+            __syncwarp();
+            return true;
+        };
+        auto issue_pv = [&](int j) -> bool {
+            const int st = j & 1;
+            if (!mbar_wait_warp(p_full, j & 1, &gave_up)) return false;
+            if (!mbar_wait_warp(v_full + 8 * st, (j >> 1) & 1, &gave_up)) return false;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (elect_one()) {
+                const uint32_t a0 = tc_smem_u32(sP), v0 = tc_smem_u32(sV) + st * TILE_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < FA_KEYS / 16; ++ks)
+                    umma_bf16(tmem_o, umma_desc_sw128(a0 + (ks >> 2) * SUB + (ks & 3) * 32), umma_desc_mn_sw128(v0 + ks * 2048, SUB), idesc_pv,
+                              (j > 0 || ks > 0) ? 1u : 0u);
+                umma_commit(pv_done);
+                umma_commit(v_empty + 8 * st);
+            }
+            __syncwarp();
+            return true;
+        };
+        if (ok) ok = issue_qk(0);
+        for (int j = 0; j < n_kt && ok; ++j) {
+            if (j + 1 < n_kt) ok = issue_qk(j + 1);
+            if (ok) ok = issue_pv(j);
+        }
+        if (!ok && lane == 0) { atomicExch(p.status, 13); gave_up = 1; }
+    } else {
+        // ---- softmax: one thread per query row --------------------------------------------------------------
+        const int quad = warp & 3, r = quad * 32 + lane;
+        const int qpos = p0 + r;
+        const int lo = (p.window > 0 && qpos - p.window + 1 > 0) ? qpos - p.window + 1 : 0;
+        const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+        float m_run = -INFINITY, m_used = -INFINITY, l = 0.0f;
+        bool ok = true;
+        uint32_t s[4][32];
+        for (int j = 0; j < n_kt; ++j) {
+            const int st = j & 1, key0 = (kt_begin + j) * FA_KEYS;
+            if (!mbar_wait_warp(s_full + 8 * st, (j >> 1) & 1, &gave_up)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) tmem_ld32(tmem_base + lane_base + st * 128u + q4 * 32, s[q4]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(s_empty + 8 * st) : "memory");
+            // keys this row must not see; whole tiles below the diagonal and inside the window need no test
+            const bool need_mask = key0 + FA_KEYS - 1 > p0 || (p.window > 0 && key0 < p_last - p.window + 1);
+            float m_tile = -INFINITY;
+            if (need_mask) {
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4)
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int kp = key0 + q4 * 32 + c;
+                        if (kp > qpos || kp < lo) s[q4][c] = __float_as_uint(-INFINITY);
+                        m_tile = fmaxf(m_tile, __uint_as_float(s[q4][c]));
+                    }
+            } else {
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4)
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) m_tile = fmaxf(m_tile, __uint_as_float(s[q4][c]));
+            }
+            const float m_new = fmaxf(m_run, m_tile * p.scale2);
+            const bool grow = m_new > m_used + FA_LAZY_LOG2;            // false while both are -inf
+            const bool any_grow = __any_sync(0xffffffffu, grow);
+            if (j > 0) {
+                if (!mbar_wait_warp(pv_done, (j - 1) & 1, &gave_up)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                if (any_grow) {
+                    const float f = grow ? fa_exp2(m_used - m_new) : 1.0f;      // 0 when nothing was seen before
+                    l *= f;
+#pragma unroll 1
+                    for (int c = 0; c < HD; c += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(tmem_o + lane_base + c, o);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                        tmem_st32(tmem_o + lane_base + c, o);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+                }
+            }
+            if (grow) m_used = m_new;
+            m_run = m_new;
+            const float mu = m_used == -INFINITY ? 0.0f : m_used;       // nothing seen yet: every p is exp2(-inf) = 0
+            float sum = 0.0f;
+            const uint32_t row_base = tc_smem_u32(sP) + r * 128;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+#pragma unroll
+                for (int c8 = 0; c8 < 4; ++c8) {                         // 8 keys = one 16-byte chunk
+                    uint32_t packed[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float e0 = fa_exp2(fmaf(__uint_as_float(s[q4][c8 * 8 + 2 * i]), p.scale2, -mu));
+                        const float e1 = fa_exp2(fmaf(__uint_as_float(s[q4][c8 * 8 + 2 * i + 1]), p.scale2, -mu));
+                        sum += e0 + e1;
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+                        packed[i] = *reinterpret_cast<uint32_t*>(&b2);
+                    }
+                    const int ch16 = q4 * 4 + c8;                         // chunk 0..15 of the row; 8 per sub-tile
+                    const uint32_t addr = row_base + (ch16 >> 3) * SUB + (((ch16 & 7) ^ (r & 7)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3]) : "memory");
+                }
+            }
+            l += sum;
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");       // P is read by the tensor core's proxy
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(p_full) : "memory");
+        }
+        if (ok) ok = mbar_wait_warp(pv_done, (n_kt - 1) & 1, &gave_up);
+        if (!ok) {
+            if (lane == 0) { atomicExch(p.status, 14); gave_up = 1; }
+        } else {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            bf16* dst = p.out + ((size_t)(n0 + r) * p.n_heads + h) * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD; c += 32) {
+                uint32_t o[32];
+                tmem_ld32(tmem_o + lane_base + c, o);
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (r < rows) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        float v[8];
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) v[k] = __uint_as_float(o[i + k]) * inv;
+                        store8(dst + c + i, v);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------------------
+// Tensor maps are kept per (pointer, geometry): a layer's cache and the step's q buffer come back every step.
+typedef std::tuple<const void*, long long, long long, long long, long long, long long> FaMapKey;
+static std::map<FaMapKey, CUtensorMap> fa_maps;
+static std::mutex fa_maps_lock;
+
+static int fa_map_q(CUtensorMap* out, const void* q, long long n_tokens, long long width) {
+    std::lock_guard<std::mutex> g(fa_maps_lock);
+    const FaMapKey key(q, n_tokens, width, -1, -1, -1);
+    auto it = fa_maps.find(key);
+    if (it == fa_maps.end()) {
+        if (fa_maps.size() > 4096) fa_maps.clear();
+        CUtensorMap m;
+        if (tc_make_map(&m, q, n_tokens, width, width, FA_ROWS)) return 1;
+        it = fa_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return 0;
+}
+
+static int fa_map_kv(CUtensorMap* out, const void* cache, int head_dim, int page_size, int n_kv_heads, long long n_pages,
+                     long long page_stride, long long kv_stride) {
+    std::lock_guard<std::mutex> g(fa_maps_lock);
+    const FaMapKey key(cache, head_dim, page_size, n_kv_heads * (1LL << 32) + n_pages, page_stride, kv_stride);
+    auto it = fa_maps.find(key);
+    if (it == fa_maps.end()) {
+        if (fa_maps.size() > 4096) fa_maps.clear();
+        cuuint64_t dims[5] = {(cuuint64_t)head_dim, (cuuint64_t)page_size, (cuuint64_t)n_kv_heads, 2, (cuuint64_t)n_pages};
+        cuuint64_t strides[4] = {(cuuint64_t)head_dim * 2, (cuuint64_t)page_size * head_dim * 2, (cuuint64_t)kv_stride * 2, (cuuint64_t)page_stride * 2};
+        cuuint32_t box[5] = {64, (cuuint32_t)page_size, 1, 1, 1};
+        cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+        CUtensorMap m;
+        CUresult r = tc_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return zi_fail("prefill_attention_tcgen05: cuTensorMapEncodeTiled failed with code %d (head %d, page %d, kv heads %d, pages %lld, strides %lld %lld)",
+                           (int)r, head_dim, page_size, n_kv_heads, n_pages, page_stride, kv_stride);
+        it = fa_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return 0;
+}
+
+// tiles: int32 [n_tiles, 3] = (first token, rows <= 128, segment).  status: one int of device memory, zero before;
+// non-zero afterwards means a bounded wait ran out (11 producer, 12/13 MMA issuer, 14 softmax).
+ZI_EXPORT int zi_prefill_attention_tcgen05(const void* q, const void* cache, void* out, const int* tables, const int* tiles,
+                                           const int* pos, int* status, int n_tokens, int n_tiles, int n_heads, int n_kv_heads,
+                                           int head_dim, int page_size, int max_blocks, long long n_pages, long long page_stride,
+                                           long long kv_stride, int window, float scale, cudaStream_t stream) {
+    if (n_tiles <= 0 || n_tokens <= 0) return 0;
+    if (head_dim != 64 && head_dim != 128) return zi_fail("prefill_attention_tcgen05: head_dim %d is not 64 or 128", head_dim);
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return zi_fail("prefill_attention_tcgen05: %d heads over %d key-value heads", n_heads, n_kv_heads);
+    if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1))) return zi_fail("prefill_attention_tcgen05: page size %d is not a power of two from 8 to 128", page_size);
+    if (n_heads > 65535) return zi_fail("prefill_attention_tcgen05: %d heads are more than one launch takes", n_heads);
+    if (((uintptr_t)q | (uintptr_t)cache | (uintptr_t)out) & 15) return zi_fail("prefill_attention_tcgen05: q, cache and out must be 16-byte aligned");
+    if ((page_stride | kv_stride) & 7) return zi_fail("prefill_attention_tcgen05: cache strides must be multiples of 8 elements");
+    if (!status) return zi_fail("prefill_attention_tcgen05: a status word is required");
+    if (tc_init()) return 1;
+    CUtensorMap mq, mkv;
+    if (fa_map_q(&mq, q, n_tokens, (long long)n_heads * head_dim)) return 1;
+    if (fa_map_kv(&mkv, cache, head_dim, page_size, n_kv_heads, n_pages, page_stride, kv_stride)) return 1;
+    FaParams p;
+    p.out = (bf16*)out; p.tables = tables; p.tiles = tiles; p.pos = pos; p.status = status;
+    p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.max_blocks = max_blocks; p.window = window;
+    p.scale2 = scale * 1.4426950408889634f;
+    const dim3 grid(n_tiles, n_heads);
+    const size_t smem = (size_t)5 * FA_KEYS * head_dim * 2 + 2 * FA_KEYS * 128 + 15 * 8 + 16;
+    cudaError_t e;
+    if (head_dim == 128) {
+        e = cudaFuncSetAttribute(prefill_attention_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return zi_fail("prefill_attention_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        prefill_attention_tcgen05_kernel<128><<<grid, FA_THREADS, smem, stream>>>(mq, mkv, p);
+    } else {
+        e = cudaFuncSetAttribute(prefill_attention_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return zi_fail("prefill_attention_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        prefill_attention_tcgen05_kernel<64><<<grid, FA_THREADS, smem, stream>>>(mq, mkv, p);
+    }
+    return zi_check_launch("prefill_attention_tcgen05");
+}

@@ -41,6 +41,7 @@ SOURCES: Dict[str, str] = {
     "attention_mma": "attention_mma.cu",
     "gemm_smallm": "gemm_smallm.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
+    "attention_tcgen05": "attention_tcgen05.cu",
 }
 EXTRA_FLAGS: Dict[str, List[str]] = {}
 EXTRA_LIBS: Dict[str, List[str]] = {}

@@ -121,7 +121,7 @@ def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache]
     n_groups = len(cache.groups)
     n_want = sum(len(e.want) for e in entries)
     # layout: ids | pos | tok_seg | want rows | slots | attention tiles | tables[g]...
-    tile_rows = 64
+    tile_rows = ops.PREFILL_TILE_ROWS
     n_tiles = sum(-(-len(e.tokens) // tile_rows) for e in entries) + pad_segments
     off_ids, off_pos, off_seg = 0, n_tok, 2 * n_tok
     off_want = 3 * n_tok

@@ -22,10 +22,11 @@ _sampling = Library("sampling")
 _attention_mma = Library("attention_mma")
 _gemm_smallm = Library("gemm_smallm")
 _gemm_tcgen05 = Library("gemm_tcgen05")
+_attention_tcgen05 = Library("attention_tcgen05")
 SMALL_M_ROWS = 16                # the weight-streaming kernel takes up to this many rows
 
 __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "silu_mul", "cast",
-           "gemm_nt", "linear", "gemm_smallm", "gemm_tcgen05", "gemm_tcgen05_tiles", "tcgen05_status", "linear_silu_mul", "raise_if_tcgen05_failed", "paged_attention", "attention", "decode_attention", "prefill_attention", "argmax", "sample", "repetition_penalty", "advance_decode"]
+           "gemm_nt", "linear", "gemm_smallm", "gemm_tcgen05", "gemm_tcgen05_tiles", "tcgen05_status", "linear_silu_mul", "raise_if_tcgen05_failed", "paged_attention", "attention", "decode_attention", "prefill_attention", "prefill_attention_tcgen05", "argmax", "sample", "repetition_penalty", "advance_decode"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
@@ -347,7 +348,7 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tab
                             c_ll(kv_stride), c_int(window or 0), c_float(scale), stream())
 
 
-PREFILL_TILE_ROWS = 64           # query rows per thread block of the prefill kernel
+PREFILL_TILE_ROWS = 128          # query rows per entry of a step's tile list
 
 
 def decode_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
@@ -370,8 +371,8 @@ def decode_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, ta
 def prefill_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
                       tiles: torch.Tensor, pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                       page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float) -> None:
-    """Portions of prompts, bfloat16, tensor cores.  ``tiles`` int32 ``[n_tiles, 3]``: (first token, rows <= 64,
-    segment); the positions of a tile's tokens are consecutive."""
+    """Portions of prompts, bfloat16, ``mma.sync`` tensor-core path.  ``tiles`` int32 ``[n_tiles, 3]``: (first token,
+    rows <= 128, segment); the positions of a tile's tokens are consecutive.  Takes any page size and windows."""
     need_cuda(q, cache, out, tables, tiles, pos)
     need_int32("tables", tables), need_int32("tiles", tiles), need_int32("pos", pos)
     need_contiguous("q", q), need_contiguous("out", out), need_contiguous("tiles", tiles)
@@ -383,13 +384,36 @@ def prefill_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, t
                         c_float(scale), stream())
 
 
+def prefill_attention_tcgen05(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
+                              tiles: torch.Tensor, pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                              page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float) -> None:
+    """Portions of prompts, bfloat16, on tcgen05: scores and outputs accumulate in TMEM, K and V pages arrive by
+    TMA through the block table.  Same arguments as :func:`prefill_attention`; head_dim 64 or 128, pages of a power
+    of two from 8 to 128 tokens.  A bounded wait that runs out is reported by :func:`tcgen05_status`."""
+    need_cuda(q, cache, out, tables, tiles, pos)
+    need_int32("tables", tables), need_int32("tiles", tiles), need_int32("pos", pos)
+    need_contiguous("q", q), need_contiguous("out", out), need_contiguous("tiles", tiles)
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("prefill_attention_tcgen05: bfloat16 only")
+    _attention_tcgen05.call("zi_prefill_attention_tcgen05", ptr(q), ptr(cache), ptr(out), ptr(tables), ptr(tiles), ptr(pos),
+                            ptr(_tc_status(q.device)), c_int(q.shape[0]), c_int(tiles.shape[0]), c_int(n_heads),
+                            c_int(n_kv_heads), c_int(head_dim), c_int(page_size), c_int(tables.shape[1]),
+                            c_ll(cache.shape[0]), c_ll(page_stride), c_ll(kv_stride), c_int(window or 0), c_float(scale), stream())
+    _tc_launched[q.device] = True
+
+
+def tcgen05_attention_ok(head_dim: int, page_size: int) -> bool:
+    return head_dim in (64, 128) and 8 <= page_size <= 128 and page_size & (page_size - 1) == 0
+
+
 def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
               window: Optional[int], scale: float) -> None:
     """Attention of a step's tokens over the cache (``cache`` is a CallCacheView, ``ctx`` a StepContext).
 
     Picks a kernel by dtype and by the shape of the step; all of them compute the same function.
-    bfloat16 with head_dim 64 or 128 runs on the tensor cores (decode-only steps on the chunked decode
-    kernel, anything else on the tiled prefill kernel); float32 and other head sizes on the general kernel.
+    bfloat16 with head_dim 64 or 128 runs on the tensor cores: decode-only steps on the cluster decode kernel,
+    anything else on the tcgen05 prefill kernel (pages of 8..128 tokens) or the ``mma.sync`` prefill kernel (other
+    page sizes); float32 and other head sizes on the general kernel.
     """
     tables = ctx.tables[cache.group]
     if q.dtype == torch.bfloat16 and head_dim in (64, 128):
@@ -399,6 +423,10 @@ def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv
                              cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
             return
         tiles = ctx.extras.get("attn_tiles")
+        if tiles is not None and tcgen05_attention_ok(head_dim, cache.page_size):
+            prefill_attention_tcgen05(q, cache.tensor, out, tables, tiles, ctx.positions, n_heads, n_kv_heads, head_dim,
+                                      cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
+            return
         if tiles is not None:
             prefill_attention(q, cache.tensor, out, tables, tiles, ctx.positions, n_heads, n_kv_heads, head_dim,
                               cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
