@@ -1,14 +1,15 @@
 // Causal attention of portions of prompts over the paged cache on the 5th-generation tensor cores
-// (bfloat16, head size 64 or 128, pages of 8..128 tokens that divide 128).
+// (bfloat16, head size 64 or 128, pages of a power of two from 8 to 128 tokens).
 //
 // One CTA takes 128 consecutive query rows of one portion and one head and walks over the keys in tiles of 128:
-//   S = Q . K^T      tcgen05.mma, 128 x 128, both operands K-major in shared memory, S in TMEM (two buffers)
+//   S = Q . K^T      tcgen05.mma, 128 x 128; Q sits in TMEM (A operand), K in shared memory; S in TMEM, two buffers
 //   P = exp2(S - m)  four warps, one thread per query row: tcgen05.ld the row, running maximum and sum in
-//                    registers, P written as bfloat16 into shared memory in the 128-byte-swizzled K-major layout
+//                    registers, P written back to TMEM as bfloat16 pairs (tcgen05.st), the A operand of the next product
 //   O += P . V       tcgen05.mma, 128 x head size, V straight from its pages as an MN-major operand, O in TMEM
-// K and V tiles come page by page through one 5-d tensor map of the layer's cache (TMA, 128-byte swizzle):
-// the 32 lanes of the producer warp each issue one page-half, the block table gives the page.  Queries come
-// through a 2-d map of the step's q matrix.
+// With both A operands in TMEM, shared memory only takes the K and V tiles from TMA and feeds them to the
+// tensor core once each; with A operands in shared memory as well its bandwidth, not the tensor pipe, set the pace.
+// K and V tiles come page by page through one 5-d tensor map of the layer's cache (128-byte swizzle): the lanes
+// of the producer warp each issue one page-half, the block table gives the page.
 //
 // O stays in TMEM for the whole row of tiles.  Its rescaling when the maximum grows is done lazily: only when
 // a row's maximum exceeds the value in use by more than 2^8, the four warps multiply their O rows in TMEM
@@ -17,7 +18,7 @@
 //
 // Order of the MMAs: QK(0), QK(1), PV(0), QK(2), PV(1), ... so the scores of the next tile are computed while
 // the softmax warps work on this one.  Barriers (all waits bounded, as in the matrix product): q_full,
-// k_full/k_empty[2], v_full/v_empty[2], s_full/s_empty[2], p_full, pv_done.
+// k_full/k_empty[3], v_full/v_empty[3], s_full/s_empty[2], p_full, pv_done.
 //
 // Keys a row must not see (beyond its position, before its window) get probability 0.  Cache slots that hold
 // nothing yet are multiplied by 0 as well, so the pool must never hold NaN bit patterns: it is allocated
@@ -32,8 +33,11 @@ ZI_DEFINE_LAST_ERROR(attention_tcgen05)
 
 #define FA_ROWS 128
 #define FA_KEYS 128
-#define FA_THREADS 192
+#define FA_THREADS 256           // warps: 0, 6 and 7 load, 1 issues the MMAs, 2..5 are the softmax
 #define FA_LAZY_LOG2 8.0f
+#define FA_KSTAGES 3
+#define FA_VSTAGES 3
+#define FA_NBARS (1 + 2 * FA_KSTAGES + 2 * FA_VSTAGES + 6)
 
 __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint32_t bar) {
     asm volatile(
@@ -62,7 +66,17 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint3
     return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)(lead_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 
+// A operand in TMEM: row m in lane m, elements 2c and 2c+1 of a row in column c; 16 elements of K = 8 columns.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 struct FaParams {
+    const bf16* q;
     bf16* out;
     const int* tables;
     const int* tiles;
@@ -72,36 +86,44 @@ struct FaParams {
     float scale2;                  // softmax scale x log2(e)
 };
 
+// TMEM columns of a CTA: two score buffers, the output, and the two A operands (bfloat16 pairs, one row per lane)
+#define FA_COL_S 0
+#define FA_COL_O 256
+#define FA_COL_Q 384
+#define FA_COL_P 448
+
 template <int HD>
 __global__ void __launch_bounds__(FA_THREADS, 1)
-prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const FaParams p) {
+prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, const FaParams p) {
     constexpr int HH = HD / 64;                               // 64-wide halves of a head
     constexpr int SUB = FA_KEYS * 128;                        // bytes of one [128 rows x 128 bytes] sub-tile
-    constexpr int TILE_BYTES = FA_KEYS * HD * 2;              // one K or V tile, or Q
+    constexpr int TILE_BYTES = FA_KEYS * HD * 2;              // one K or V tile
     extern __shared__ __align__(1024) unsigned char fa_smem[];
-    unsigned char* sQ = fa_smem;
-    unsigned char* sK = sQ + TILE_BYTES;                      // two stages
-    unsigned char* sV = sK + 2 * TILE_BYTES;                  // two stages
-    unsigned char* sP = sV + 2 * TILE_BYTES;                  // [128 rows x 128 keys] bfloat16, two sub-tiles
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * SUB);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+    unsigned char* sK = fa_smem;                              // FA_KSTAGES stages
+    unsigned char* sV = sK + FA_KSTAGES * TILE_BYTES;         // FA_VSTAGES stages
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + FA_VSTAGES * TILE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + FA_NBARS);
     __shared__ volatile int gave_up;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t b0 = tc_smem_u32(bars);
-    const uint32_t q_full = b0, k_full = b0 + 8, k_empty = b0 + 24, v_full = b0 + 40, v_empty = b0 + 56,
-                   s_full = b0 + 72, s_empty = b0 + 88, p_full = b0 + 104, pv_done = b0 + 112;       // 15 barriers
-    // the later tiles of a portion see more keys: start them first
-    const int tile = gridDim.x - 1 - blockIdx.x;
+    const uint32_t q_full = b0, k_full = q_full + 8, k_empty = k_full + 8 * FA_KSTAGES, v_full = k_empty + 8 * FA_KSTAGES,
+                   v_empty = v_full + 8 * FA_VSTAGES, s_full = v_empty + 8 * FA_VSTAGES, s_empty = s_full + 16,
+                   p_full = s_empty + 16, pv_done = p_full + 8;
+    const int tile = gridDim.y - 1 - blockIdx.y;              // heads run fastest, so the heavy tiles of all heads start first
     const int n0 = p.tiles[tile * 3], rows = p.tiles[tile * 3 + 1], seg = p.tiles[tile * 3 + 2];
-    const int h = blockIdx.y, kvh = h / (p.n_heads / p.n_kv_heads);
+    const int h = blockIdx.x, kvh = h / (p.n_heads / p.n_kv_heads);
     const int p0 = p.pos[n0], p_last = p0 + rows - 1;         // positions of a tile are consecutive
     const int lo_tile = (p.window > 0 && p0 - p.window + 1 > 0) ? p0 - p.window + 1 : 0;
     const int kt_begin = lo_tile / FA_KEYS, n_kt = p_last / FA_KEYS - kt_begin + 1;
 
     if (threadIdx.x == 0) {
         gave_up = 0;
-        for (int i = 0; i < 15; ++i) mbar_init(b0 + 8 * i, (i >= 11 && i <= 13) ? 4 : 1);      // s_empty[2], p_full: one arrival per softmax warp
+        for (int i = 0; i < FA_NBARS; ++i) {
+            const uint32_t bar = b0 + 8 * i;
+            const bool per_warp = bar == q_full || bar == s_empty || bar == s_empty + 8 || bar == p_full;   // one arrival per softmax warp
+            mbar_init(bar, per_warp ? 4 : 1);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 1) {
@@ -112,87 +134,93 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_o = tmem_base + 256u;
 
-    if (warp == 0) {
-        // ---- producer ---------------------------------------------------------------------------------------
-        if (elect_one()) {
-            mbar_expect_tx(q_full, TILE_BYTES);
-#pragma unroll
-            for (int hh = 0; hh < HH; ++hh) tma_load_2d(tc_smem_u32(sQ) + hh * SUB, &map_q, h * HD + hh * 64, n0, q_full);
-        }
-        __syncwarp();
+    if (warp == 0 || warp >= 6) {
+        // ---- producers: K(0), K(1), V(0), K(2), V(1), ...: a K tile is asked for well ahead of its scores ---------
+        // A lane's TMA instruction takes some 60 clocks to issue and a warp's lanes issue one after another, so the
+        // 16 or 32 page-halves of a tile are dealt to three warps; all of them follow the same barriers.
+        const int prod = warp == 0 ? 0 : warp - 5;            // 0..2
         const int* table = p.tables + (size_t)seg * p.max_blocks;
         const int ppt = FA_KEYS / p.page_size;                // pages per tile
-        const int ops = 2 * ppt * HH;
-        int issued = 0;
-        for (int j = 0; j < n_kt; ++j) {
-            const int st = j & 1;
-            if (j >= 2) {
-                const uint32_t par = ((j >> 1) - 1) & 1;
-                if (!mbar_wait_warp(k_empty + 8 * st, par, &gave_up) || !mbar_wait_warp(v_empty + 8 * st, par, &gave_up)) {
-                    if (lane == 0) { atomicExch(p.status, 11); gave_up = 1; }
-                    break;
-                }
-            }
-            if (elect_one()) { mbar_expect_tx(k_full + 8 * st, TILE_BYTES); mbar_expect_tx(v_full + 8 * st, TILE_BYTES); }
+        int k_issued = 0, v_issued = 0;
+        // one page-half per lane (at most 16 pages x 2 halves).  A tile's page numbers are read from the block table
+        // one tile ahead, so that load's latency does not sit between a freed stage and its refill.
+        const int my_pg = lane / HH, my_hh = lane - my_pg * HH;
+        const bool my_op = lane < ppt * HH && lane % 3 == prod;
+        auto page_of = [&](int j) -> int {
+            const int blk = (kt_begin + j) * ppt + my_pg;
+            return (my_op && j < n_kt && blk < p.max_blocks) ? table[blk] : -1;      // -1: outside the map, reads zeros
+        };
+        auto load_tile = [&](int j, int kv, int page) {
+            const int st = kv ? (j % FA_VSTAGES) : (j % FA_KSTAGES);
+            const uint32_t bar = (kv ? v_full : k_full) + 8 * st;
+            if (prod == 0 && elect_one()) mbar_expect_tx(bar, TILE_BYTES);
             __syncwarp();
-            const int blk0 = (kt_begin + j) * ppt;
-            for (int op = lane; op < ops; op += 32) {
-                const int kv = op / (ppt * HH), rem = op - kv * (ppt * HH), pg = rem / HH, hh = rem - pg * HH;
-                const int blk = blk0 + pg;
-                const int page = blk < p.max_blocks ? table[blk] : -1;       // -1: outside the map, reads zeros
-                const uint32_t dst = tc_smem_u32(kv ? sV : sK) + st * TILE_BYTES + hh * SUB + pg * p.page_size * 128;
-                tma_load_5d(dst, &map_kv, hh * 64, 0, kvh, kv, page, (kv ? v_full : k_full) + 8 * st);
+            if (my_op) {
+                const uint32_t dst = tc_smem_u32(kv ? sV : sK) + st * TILE_BYTES + my_hh * SUB + my_pg * p.page_size * 128;
+                tma_load_5d(dst, &map_kv, my_hh * 64, 0, kvh, kv, page, bar);
             }
             __syncwarp();
-            issued = j + 1;
+        };
+        bool ok = true;
+        int page_next = page_of(0), page_prev = -1;
+        for (int j = 0; j <= n_kt && ok; ++j) {
+            const int page_cur = page_next;
+            page_next = page_of(j + 1);
+            if (j < n_kt) {                   // K(j)
+                if (j >= FA_KSTAGES && !mbar_wait_warp(k_empty + 8 * (j % FA_KSTAGES), ((j / FA_KSTAGES) - 1) & 1, &gave_up)) { ok = false; break; }
+                load_tile(j, 0, page_cur);
+                k_issued = j + 1;
+            }
+            if (j >= 1) {                     // V(j - 1)
+                const int jv = j - 1;
+                if (jv >= FA_VSTAGES && !mbar_wait_warp(v_empty + 8 * (jv % FA_VSTAGES), ((jv / FA_VSTAGES) - 1) & 1, &gave_up)) { ok = false; break; }
+                load_tile(jv, 1, page_prev);
+                v_issued = jv + 1;
+            }
+            page_prev = page_cur;
         }
-        if (gave_up) {      // copies in flight: let them land before the CTA's memory goes away
-            mbar_wait(q_full, 0, nullptr);
-            for (int j = issued > 2 ? issued - 2 : 0; j < issued; ++j) {
-                mbar_wait(k_full + 8 * (j & 1), (j >> 1) & 1, nullptr);
-                mbar_wait(v_full + 8 * (j & 1), (j >> 1) & 1, nullptr);
-            }
+        if (!ok && lane == 0) { atomicExch(p.status, 11); gave_up = 1; }
+        if (gave_up && prod == 0) {      // copies in flight: let them land before the CTA's memory goes away
+            for (int j = k_issued > FA_KSTAGES ? k_issued - FA_KSTAGES : 0; j < k_issued; ++j)
+                mbar_wait(k_full + 8 * (j % FA_KSTAGES), (j / FA_KSTAGES) & 1, nullptr);
+            for (int j = v_issued > FA_VSTAGES ? v_issued - FA_VSTAGES : 0; j < v_issued; ++j)
+                mbar_wait(v_full + 8 * (j % FA_VSTAGES), (j / FA_VSTAGES) & 1, nullptr);
         }
     } else if (warp == 1) {
-        // ---- MMA issuer -------------------------------------------------------------------------------------
+        // ---- MMA issuer: QK(0), QK(1), PV(0), QK(2), PV(1), ... ---------------------------------------------------
+        // Both products take their A operand (Q, P) from TMEM, so shared memory serves only K and V.  The loops
+        // stay lean (descriptors are a base plus a constant, the lane is elected per instruction): a 128 x 128 x 16
+        // product lasts 64 clocks and its issue must not take longer.
         constexpr uint32_t idesc_qk = umma_idesc_bf16(FA_ROWS, FA_KEYS);
         constexpr uint32_t idesc_pv = umma_idesc_bf16(FA_ROWS, HD) | (1u << 16);      // B operand MN-major
+        const uint32_t tq = tmem_base + FA_COL_Q, tp = tmem_base + FA_COL_P, to = tmem_base + FA_COL_O;
+        const uint64_t dk_base = umma_desc_sw128(tc_smem_u32(sK)), dv_base = umma_desc_mn_sw128(tc_smem_u32(sV), SUB);
         bool ok = mbar_wait_warp(q_full, 0, &gave_up);
-        if (!ok && lane == 0) { atomicExch(p.status, 12); gave_up = 1; }
         auto issue_qk = [&](int j) -> bool {
-            const int st = j & 1;
-            if (!mbar_wait_warp(k_full + 8 * st, (j >> 1) & 1, &gave_up)) return false;
+            const int st = j & 1, kst = j % FA_KSTAGES;
+            if (!mbar_wait_warp(k_full + 8 * kst, (j / FA_KSTAGES) & 1, &gave_up)) return false;
             if (j >= 2 && !mbar_wait_warp(s_empty + 8 * st, ((j >> 1) - 1) & 1, &gave_up)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            if (elect_one()) {
-                const uint32_t a0 = tc_smem_u32(sQ), k0 = tc_smem_u32(sK) + st * TILE_BYTES;
+            const uint64_t dk = dk_base + (uint64_t)(kst * (TILE_BYTES >> 4));
+            const uint32_t ts = tmem_base + FA_COL_S + st * 128u;
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * SUB + (ks & 3) * 32;
-                    umma_bf16(tmem_base + st * 128u, umma_desc_sw128(a0 + off), umma_desc_sw128(k0 + off), idesc_qk, ks > 0 ? 1u : 0u);
-                }
-                umma_commit(s_full + 8 * st);
-                umma_commit(k_empty + 8 * st);
-            }
+            for (int ks = 0; ks < HD / 16; ++ks)
+                if (elect_one()) umma_bf16_ts(ts, tq + ks * 8, dk + (uint64_t)(((ks >> 2) * SUB + (ks & 3) * 32) >> 4), idesc_qk, ks > 0 ? 1u : 0u);
+            if (elect_one()) { umma_commit(s_full + 8 * st); umma_commit(k_empty + 8 * kst); }
             __syncwarp();
             return true;
         };
         auto issue_pv = [&](int j) -> bool {
-            const int st = j & 1;
+            const int vst = j % FA_VSTAGES;
             if (!mbar_wait_warp(p_full, j & 1, &gave_up)) return false;
-            if (!mbar_wait_warp(v_full + 8 * st, (j >> 1) & 1, &gave_up)) return false;
+            if (!mbar_wait_warp(v_full + 8 * vst, (j / FA_VSTAGES) & 1, &gave_up)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            if (elect_one()) {
-                const uint32_t a0 = tc_smem_u32(sP), v0 = tc_smem_u32(sV) + st * TILE_BYTES;
+            const uint64_t dv = dv_base + (uint64_t)(vst * (TILE_BYTES >> 4));
 #pragma unroll
-                for (int ks = 0; ks < FA_KEYS / 16; ++ks)
-                    umma_bf16(tmem_o, umma_desc_sw128(a0 + (ks >> 2) * SUB + (ks & 3) * 32), umma_desc_mn_sw128(v0 + ks * 2048, SUB), idesc_pv,
-                              (j > 0 || ks > 0) ? 1u : 0u);
-                umma_commit(pv_done);
-                umma_commit(v_empty + 8 * st);
-            }
+            for (int ks = 0; ks < FA_KEYS / 16; ++ks)
+                if (elect_one()) umma_bf16_ts(to, tp + ks * 8, dv + (uint64_t)((ks * 2048) >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+            if (elect_one()) { umma_commit(pv_done); umma_commit(v_empty + 8 * vst); }
             __syncwarp();
             return true;
         };
@@ -203,11 +231,28 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
         if (!ok && lane == 0) { atomicExch(p.status, 13); gave_up = 1; }
     } else {
-        // ---- softmax: one thread per query row --------------------------------------------------------------
+        // ---- softmax: one thread per query row --------------------------------------------------------------------
         const int quad = warp & 3, r = quad * 32 + lane;
         const int qpos = p0 + r;
         const int lo = (p.window > 0 && qpos - p.window + 1 > 0) ? qpos - p.window + 1 : 0;
-        const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+        {   // the row of Q goes straight from memory into TMEM, two bfloat16 per column; rows beyond the tile are zero
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)(n0 + r) * p.n_heads + h) * HD);
+#pragma unroll
+            for (int c = 0; c < HD / 2; c += 32) {
+                uint32_t w[32];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint4 v = r < rows ? src[c / 4 + i] : make_uint4(0, 0, 0, 0);
+                    w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+                }
+                tmem_st32(lane_base + FA_COL_Q + c, w);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(q_full) : "memory");
+        }
         float m_run = -INFINITY, m_used = -INFINITY, l = 0.0f;
         bool ok = true;
         uint32_t s[4][32];
@@ -216,14 +261,16 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             if (!mbar_wait_warp(s_full + 8 * st, (j >> 1) & 1, &gave_up)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) tmem_ld32(tmem_base + lane_base + st * 128u + q4 * 32, s[q4]);
+            for (int q4 = 0; q4 < 4; ++q4) tmem_ld32(lane_base + FA_COL_S + st * 128u + q4 * 32, s[q4]);
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(s_empty + 8 * st) : "memory");
             // keys this row must not see; whole tiles below the diagonal and inside the window need no test
             const bool need_mask = key0 + FA_KEYS - 1 > p0 || (p.window > 0 && key0 < p_last - p.window + 1);
-            float m_tile = -INFINITY;
+            float mx[8];                                     // eight chains, not one of 128 dependent maxima
+#pragma unroll
+            for (int i = 0; i < 8; ++i) mx[i] = -INFINITY;
             if (need_mask) {
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4)
@@ -231,60 +278,54 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     for (int c = 0; c < 32; ++c) {
                         const int kp = key0 + q4 * 32 + c;
                         if (kp > qpos || kp < lo) s[q4][c] = __float_as_uint(-INFINITY);
-                        m_tile = fmaxf(m_tile, __uint_as_float(s[q4][c]));
+                        mx[c & 7] = fmaxf(mx[c & 7], __uint_as_float(s[q4][c]));
                     }
             } else {
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4)
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) m_tile = fmaxf(m_tile, __uint_as_float(s[q4][c]));
+                    for (int c = 0; c < 32; ++c) mx[c & 7] = fmaxf(mx[c & 7], __uint_as_float(s[q4][c]));
             }
+            const float m_tile = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
             const float m_new = fmaxf(m_run, m_tile * p.scale2);
             const bool grow = m_new > m_used + FA_LAZY_LOG2;            // false while both are -inf
             const bool any_grow = __any_sync(0xffffffffu, grow);
+            const float f = grow ? fa_exp2(m_used - m_new) : 1.0f;      // 0 when nothing was seen before
+            if (grow) m_used = m_new;
+            m_run = m_new;
+            const float mu = m_used == -INFINITY ? 0.0f : m_used;       // nothing seen yet: every p is exp2(-inf) = 0
+            float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            uint32_t pk[2][32];                                          // the row of P, two bfloat16 per word
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float e0 = fa_exp2(fmaf(__uint_as_float(s[q4][2 * i]), p.scale2, -mu));
+                    const float e1 = fa_exp2(fmaf(__uint_as_float(s[q4][2 * i + 1]), p.scale2, -mu));
+                    sums[i & 3] += e0 + e1;
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+                    pk[q4 >> 1][(q4 & 1) * 16 + i] = *reinterpret_cast<uint32_t*>(&b2);
+                }
+            // only now the product of the tile before must be done: it read P and wrote O
             if (j > 0) {
                 if (!mbar_wait_warp(pv_done, (j - 1) & 1, &gave_up)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 if (any_grow) {
-                    const float f = grow ? fa_exp2(m_used - m_new) : 1.0f;      // 0 when nothing was seen before
-                    l *= f;
 #pragma unroll 1
                     for (int c = 0; c < HD; c += 32) {
                         uint32_t o[32];
-                        tmem_ld32(tmem_o + lane_base + c, o);
+                        tmem_ld32(lane_base + FA_COL_O + c, o);
                         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
                         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-                        tmem_st32(tmem_o + lane_base + c, o);
+                        tmem_st32(lane_base + FA_COL_O + c, o);
                     }
-                    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
                 }
             }
-            if (grow) m_used = m_new;
-            m_run = m_new;
-            const float mu = m_used == -INFINITY ? 0.0f : m_used;       // nothing seen yet: every p is exp2(-inf) = 0
-            float sum = 0.0f;
-            const uint32_t row_base = tc_smem_u32(sP) + r * 128;
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-#pragma unroll
-                for (int c8 = 0; c8 < 4; ++c8) {                         // 8 keys = one 16-byte chunk
-                    uint32_t packed[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float e0 = fa_exp2(fmaf(__uint_as_float(s[q4][c8 * 8 + 2 * i]), p.scale2, -mu));
-                        const float e1 = fa_exp2(fmaf(__uint_as_float(s[q4][c8 * 8 + 2 * i + 1]), p.scale2, -mu));
-                        sum += e0 + e1;
-                        __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
-                        packed[i] = *reinterpret_cast<uint32_t*>(&b2);
-                    }
-                    const int ch16 = q4 * 4 + c8;                         // chunk 0..15 of the row; 8 per sub-tile
-                    const uint32_t addr = row_base + (ch16 >> 3) * SUB + (((ch16 & 7) ^ (r & 7)) << 4);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3]) : "memory");
-                }
-            }
-            l += sum;
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");       // P is read by the tensor core's proxy
+            l = l * f + ((sums[0] + sums[1]) + (sums[2] + sums[3]));
+            tmem_st32(lane_base + FA_COL_P, pk[0]);
+            tmem_st32(lane_base + FA_COL_P + 32, pk[1]);
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(p_full) : "memory");
@@ -299,7 +340,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll 1
             for (int c = 0; c < HD; c += 32) {
                 uint32_t o[32];
-                tmem_ld32(tmem_o + lane_base + c, o);
+                tmem_ld32(lane_base + FA_COL_O + c, o);
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
                 if (r < rows) {
 #pragma unroll
@@ -326,20 +367,6 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 typedef std::tuple<const void*, long long, long long, long long, long long, long long> FaMapKey;
 static std::map<FaMapKey, CUtensorMap> fa_maps;
 static std::mutex fa_maps_lock;
-
-static int fa_map_q(CUtensorMap* out, const void* q, long long n_tokens, long long width) {
-    std::lock_guard<std::mutex> g(fa_maps_lock);
-    const FaMapKey key(q, n_tokens, width, -1, -1, -1);
-    auto it = fa_maps.find(key);
-    if (it == fa_maps.end()) {
-        if (fa_maps.size() > 4096) fa_maps.clear();
-        CUtensorMap m;
-        if (tc_make_map(&m, q, n_tokens, width, width, FA_ROWS)) return 1;
-        it = fa_maps.emplace(key, m).first;
-    }
-    *out = it->second;
-    return 0;
-}
 
 static int fa_map_kv(CUtensorMap* out, const void* cache, int head_dim, int page_size, int n_kv_heads, long long n_pages,
                      long long page_stride, long long kv_stride) {
@@ -375,29 +402,28 @@ ZI_EXPORT int zi_prefill_attention_tcgen05(const void* q, const void* cache, voi
     if (head_dim != 64 && head_dim != 128) return zi_fail("prefill_attention_tcgen05: head_dim %d is not 64 or 128", head_dim);
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return zi_fail("prefill_attention_tcgen05: %d heads over %d key-value heads", n_heads, n_kv_heads);
     if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1))) return zi_fail("prefill_attention_tcgen05: page size %d is not a power of two from 8 to 128", page_size);
-    if (n_heads > 65535) return zi_fail("prefill_attention_tcgen05: %d heads are more than one launch takes", n_heads);
+    if (n_tiles > 65535) return zi_fail("prefill_attention_tcgen05: %d tiles are more than one launch takes", n_tiles);
     if (((uintptr_t)q | (uintptr_t)cache | (uintptr_t)out) & 15) return zi_fail("prefill_attention_tcgen05: q, cache and out must be 16-byte aligned");
     if ((page_stride | kv_stride) & 7) return zi_fail("prefill_attention_tcgen05: cache strides must be multiples of 8 elements");
     if (!status) return zi_fail("prefill_attention_tcgen05: a status word is required");
     if (tc_init()) return 1;
-    CUtensorMap mq, mkv;
-    if (fa_map_q(&mq, q, n_tokens, (long long)n_heads * head_dim)) return 1;
+    CUtensorMap mkv;
     if (fa_map_kv(&mkv, cache, head_dim, page_size, n_kv_heads, n_pages, page_stride, kv_stride)) return 1;
     FaParams p;
-    p.out = (bf16*)out; p.tables = tables; p.tiles = tiles; p.pos = pos; p.status = status;
+    p.q = (const bf16*)q; p.out = (bf16*)out; p.tables = tables; p.tiles = tiles; p.pos = pos; p.status = status;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.max_blocks = max_blocks; p.window = window;
     p.scale2 = scale * 1.4426950408889634f;
-    const dim3 grid(n_tiles, n_heads);
-    const size_t smem = (size_t)5 * FA_KEYS * head_dim * 2 + 2 * FA_KEYS * 128 + 15 * 8 + 16;
+    const dim3 grid(n_heads, n_tiles);
+    const size_t smem = (size_t)(FA_KSTAGES + FA_VSTAGES) * FA_KEYS * head_dim * 2 + FA_NBARS * 8 + 16;
     cudaError_t e;
     if (head_dim == 128) {
         e = cudaFuncSetAttribute(prefill_attention_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return zi_fail("prefill_attention_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        prefill_attention_tcgen05_kernel<128><<<grid, FA_THREADS, smem, stream>>>(mq, mkv, p);
+        prefill_attention_tcgen05_kernel<128><<<grid, FA_THREADS, smem, stream>>>(mkv, p);
     } else {
         e = cudaFuncSetAttribute(prefill_attention_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return zi_fail("prefill_attention_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        prefill_attention_tcgen05_kernel<64><<<grid, FA_THREADS, smem, stream>>>(mq, mkv, p);
+        prefill_attention_tcgen05_kernel<64><<<grid, FA_THREADS, smem, stream>>>(mkv, p);
     }
     return zi_check_launch("prefill_attention_tcgen05");
 }
