@@ -201,13 +201,15 @@ def measure_decode_device(core, cfg, batch, steps, warmup):
     return {"tok_s": batch * 1000.0 / ms, "ms": ms, "mean_ctx": mean_ctx, "launches": g.launches * steps}
 
 
-def measure_decode_e2e(core, cfg, batch, steps, warmup):
-    """The same steps through the public entry point: host tokens in, sampled tokens out, every step."""
+def measure_decode_e2e(core, cfg, batch, steps, warmup, run_ahead=True):
+    """The same steps through the public entry point: sampled tokens out every step.  With ``run_ahead`` (the
+    engine's default) a decode step takes its input tokens on the device from the step before and the host reads
+    each step's tokens while the next one runs; without it the host sends every step's tokens itself."""
     import torch
     from zedinfer_b200 import GenerationConfig, SchedulerConfig
     from zedinfer_b200.engine import InferenceEngine, InferenceRequest, RequestPhase
     sc = SchedulerConfig(max_batch_tokens=4096, max_prefill_tokens=2048, max_batch_requests=max(batch, 1),
-                         kv_block_size=PAGE_SIZE, cuda_graphs=True)
+                         kv_block_size=PAGE_SIZE, cuda_graphs=True, run_ahead=run_ahead)
     engine = InferenceEngine(core, sc)
     prompts = random_prompts(batch, PROMPT_LEN, cfg["vocab_size"], SEED + batch)
     gen = GenerationConfig(max_new_tokens=CONTEXT - PROMPT_LEN, use_argmax=True, ignore_eos=True)
@@ -232,7 +234,8 @@ def measure_decode_e2e(core, cfg, batch, steps, warmup):
     h2d = (core._ring.bytes_staged - h2d0) / steps
     for r in reqs:
         engine.scheduler.cancel(r)
-    engine.step()
+    while engine.has_work():
+        engine.step()
     for r in reqs:
         core.end(r.request_id)
     return {"tok_s": batch * steps / dt, "ms": dt * 1000.0 / steps, "h2d": int(h2d), "d2h": 4 * batch}
@@ -279,6 +282,7 @@ def main():
     prefill = measure_prefill(core, cfg, args.layers, warmup=3, reps=5, pk=pk)
     dev = measure_decode_device(core, cfg, args.batch, steps, warmup)
     e2e = measure_decode_e2e(core, cfg, args.batch, steps, warmup)
+    e2e_sync = measure_decode_e2e(core, cfg, args.batch, steps, warmup, run_ahead=False)
     points = {}
     if not args.no_points:
         for b in (1, 64):
@@ -301,7 +305,9 @@ def main():
                    "l2": "inputs larger than L2 (weights 3.1 GB per step)", "peaks": pk["source"]},
         "clocks": clocks.summary(),
         "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "ms_per_step": round(e2e["ms"], 4),
-                "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
+                "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                "host_in_step": {"value": round(e2e_sync["tok_s"], 1), "ms_per_step": round(e2e_sync["ms"], 4),
+                                 "h2d_bytes_per_step": e2e_sync["h2d"]}},
         "gpu_launches": dev["launches"],
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",

@@ -127,6 +127,43 @@ def test_top_k_one_is_greedy_and_stop_token_ends(models):
     assert r.finish_reason == "stop" and r.output_ids == greedy[:first + 1]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_ahead_of_the_host_changes_no_token(models, dtype):
+    """Steady decode launches the next step before the host has read this one's tokens.  Same tokens as with the
+    host in step, with greedy and with sampled requests side by side, with requests of different lengths (one ends
+    early, one by a stop token while a step with its row is already in flight) and with pages that run out."""
+    from zedinfer_b200 import GenerationConfig, InferenceRequest, SchedulerConfig
+    from zedinfer_b200.engine import InferenceEngine
+    prompts = [list(range(1, 8)), list(range(20, 33)), [5], list(range(40, 49))]
+    configs = [GenerationConfig(max_new_tokens=40, ignore_eos=True),
+               GenerationConfig(max_new_tokens=11, use_argmax=False, temperature=0.8, top_k=20, seed=7, ignore_eos=True),
+               GenerationConfig(max_new_tokens=25),                               # stops at the stop token set below
+               GenerationConfig(max_new_tokens=33, use_argmax=False, temperature=1.1, top_p=0.9, seed=9, ignore_eos=True)]
+
+    def run(ahead, pages):
+        engine = InferenceEngine.create(models["A"], SchedulerConfig(num_kv_pages=pages, kv_block_size=4, max_batch_requests=4,
+                                                                     run_ahead=ahead), dtype=dtype)
+        stop = plain_greedy(models["A"], prompts[2], 9)[8] if dtype == "float32" else None
+        if stop is not None:
+            engine.scheduler.stop_token_ids = frozenset([stop])
+        futures = [engine.submit_async(InferenceRequest(p, c)) for p, c in zip(prompts, configs)]
+        engine.run_loop()
+        assert engine.cache_stats()["live_requests"] == 0
+        assert engine.cache_stats()["free_pages"] == [pages] * engine.cache_stats()["groups"]
+        return [f.result() for f in futures], engine
+
+    base, e0 = run(False, 64)
+    assert e0.steps_run_ahead == 0
+    for pages in (64, 24):                 # 24 pages: the youngest request is preempted in mid-decode
+        got, e1 = run(True, pages)
+        assert e1.steps_run_ahead > 10
+        for a, b in zip(base, got):
+            assert a.output_ids == b.output_ids and a.finish_reason == b.finish_reason
+    if dtype == "float32":
+        assert base[2].finish_reason == "stop" and len(base[2].output_ids) <= 9
+        assert base[0].output_ids == plain_greedy(models["A"], prompts[0], 40)
+
+
 def test_preemption_recomputes_and_gives_the_same_tokens(models):
     """So few pages that the youngest request is taken off the GPU in mid-decode and recomputed later."""
     from zedinfer_b200 import GenerationConfig, SchedulerConfig

@@ -25,6 +25,7 @@ class SchedulerConfig:
     on_exhaust: str = "preempt"         # pages run out during decode: "preempt" the youngest, or "fail"
     generation_reserve: int = 0         # tokens beyond the prompt reserved at admission (reference: min(max_new, 256))
     cuda_graphs: bool = True            # capture decode-only steps
+    run_ahead: bool = True              # launch the next decode step before the host has read this one's tokens
 
     def validate(self) -> None:
         if self.max_batch_tokens <= 0 or self.max_batch_requests <= 0 or self.max_prefill_tokens <= 0:

@@ -304,6 +304,28 @@ class EngineCore:
             self._decode_graphs[bucket] = g
         return g
 
+    def step_ahead(self, request_ids: Sequence, sampled: torch.Tensor) -> Optional[torch.Tensor]:
+        """One more decode step for exactly the requests of the decode step just launched, fed on the device with
+        the tokens that step chose (``sampled``, int32, one per request) so the host need not have read them yet.
+        Returns the logits, or None when this cannot be done (other requests in the captured step's rows, no page
+        left): the caller then takes the ordinary path."""
+        from ..cache.pool import OutOfPages
+        rcs = [self.cache.get(rid) for rid in request_ids]
+        if not rcs or any(rc is None for rc in rcs) or not self.cuda_graphs or len(rcs) > self.max_requests:
+            return None
+        g = self.decode_graph(len(rcs))
+        if not g.holds(rcs) or any(rc.length + 1 > self.max_seq_len for rc in rcs):
+            return None
+        try:
+            for rc in rcs:
+                self.cache.ensure(rc, rc.length + 1)
+        except OutOfPages:
+            return None
+        logits = g.run_ahead(rcs, sampled)
+        for rc in rcs:
+            self.cache.commit(rc, rc.length + 1)
+        return logits
+
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one batch; returns float32 logits ``[wanted, vocab]`` on the device, or None if nothing is wanted."""
         if not entries:

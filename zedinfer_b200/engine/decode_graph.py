@@ -130,5 +130,36 @@ class DecodeGraph:
         self.graph.replay()
         return self.logits[:len(entries)]
 
+    def holds(self, rcs: Sequence) -> bool:
+        """The last fill put exactly these requests into the first rows."""
+        return len(rcs) == self._n_filled and all(sig is not None and sig[0] == rc.request_id
+                                                  for sig, rc in zip(self._slot_sig, rcs))
+
+    def run_ahead(self, rcs: Sequence, sampled: torch.Tensor) -> torch.Tensor:
+        """The step after the one just run, for the same requests, before the host knows their tokens: ids and
+        positions move on the device (``sampled`` holds the tokens chosen by the last step); only block tables
+        that changed go up."""
+        n = len(rcs)
+        b, width, ng = self.bucket, self.core.table_width, len(self.core.cache.groups)
+        h = self.host
+        dirty = False
+        for i, rc in enumerate(rcs):
+            sig = (rc.request_id, rc.version)
+            if self._slot_sig[i] == sig:
+                continue
+            self._slot_sig[i] = sig
+            dirty = True
+            for g in range(ng):
+                tab = rc.tables[g]
+                base = self.off_tab + (g * b + i) * width
+                h[base: base + len(tab)] = tab
+                h[base + len(tab): base + width] = 0
+        if dirty:
+            head = self.off_seg                               # ids and positions stay as the device has them
+            self.core._ring.stage_into(h[head:], self.dev[head:])
+        ops.advance_decode(self.ctx.token_ids, self.ctx.positions, sampled, n)
+        self.graph.replay()
+        return self.logits[:n]
+
     def replay(self) -> None:
         self.graph.replay()

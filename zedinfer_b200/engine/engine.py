@@ -44,7 +44,9 @@ class InferenceEngine:
         self.scheduler = Scheduler(scheduler_config, core.cache, core.max_seq_len, core.spec.eos_token_ids)
         self.sampler = Sampler(core.device)
         self.steps_run = 0
+        self.steps_run_ahead = 0
         self.on_step: Optional[Callable[[ScheduledBatch], None]] = None
+        self._pending: Optional[Tuple[ScheduledBatch, object]] = None     # a launched step whose tokens are on their way
 
     @classmethod
     def create(cls, model_path: str, scheduler_config: Optional[SchedulerConfig] = None, dtype="bfloat16",
@@ -80,11 +82,11 @@ class InferenceEngine:
 
     # ---- the loop ---------------------------------------------------------------------------
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self._pending is not None or self.scheduler.has_work()
 
     def run_loop(self) -> None:
         """Step until every submitted request has finished (src/zedinfer/serving_loop.cpp:424-430)."""
-        while self.scheduler.has_work():
+        while self.has_work():
             self.step()
 
     def entries_for(self, batch: ScheduledBatch) -> List[StepEntry]:
@@ -97,17 +99,38 @@ class InferenceEngine:
         return entries
 
     def step(self) -> bool:
-        """schedule → forward → sample → process results.  Returns False when there was nothing to do."""
-        batch = self.scheduler.schedule()
-        if batch.empty():
-            return self.scheduler.has_work()
-        if self.on_step is not None:
-            self.on_step(batch)
+        """schedule → forward → sample → process results.  Returns False when there was nothing to do.
+
+        While a steady decode runs (the same requests step after step, nothing waiting), the next step is launched
+        before this one's tokens have reached the host: it takes them on the device.  The host then reads this
+        step's tokens while the GPU already works, so its bookkeeping costs no GPU time.  A request that ends with
+        this step's token has a row in the step launched ahead; that row's result is dropped.
+        """
+        pending = self._pending
+        self._pending = None
+        if pending is None:
+            batch = self.scheduler.schedule()
+            if batch.empty():
+                return self.scheduler.has_work()
+            if self.on_step is not None:
+                self.on_step(batch)
+            try:
+                logits = self.core.step(self.entries_for(batch))
+                rows = batch.rows_wanted()
+                chosen = self.sampler.launch(logits, [r for r, _ in rows]) if rows else None
+            except Exception as e:                       # keep serving: fail what was in the step
+                self.scheduler.fail_batch(batch, f"step failed: {e}")
+                if isinstance(e, (torch.cuda.OutOfMemoryError, KeyboardInterrupt)):
+                    raise
+                return True
+            pending = (batch, chosen)
+        batch, chosen = pending
         try:
-            logits = self.core.step(self.entries_for(batch))
-            rows = batch.rows_wanted()
-            tokens = self.sampler.sample(logits, [r for r, _ in rows]) if rows else []
-        except Exception as e:                       # keep serving: fail what was in the step
+            if chosen is not None and self._may_run_ahead(batch):
+                self._pending = self._launch_ahead(batch, chosen)
+            tokens = chosen.wait() if chosen is not None else []
+        except Exception as e:
+            self._pending = None
             self.scheduler.fail_batch(batch, f"step failed: {e}")
             if isinstance(e, (torch.cuda.OutOfMemoryError, KeyboardInterrupt)):
                 raise
@@ -115,6 +138,29 @@ class InferenceEngine:
         self.scheduler.process_results(batch, tokens)
         self.steps_run += 1
         return True
+
+    def _may_run_ahead(self, batch: ScheduledBatch) -> bool:
+        """A pure decode step whose requests all go on unless this step's token ends them, and nothing is waiting."""
+        if not self.scheduler_config.run_ahead or not self.core.cuda_graphs or batch.prefill_requests:
+            return False
+        if self.scheduler.waiting or len(batch.decode_requests) != len(self.scheduler.active):
+            return False
+        for r in batch.decode_requests:
+            if r.cancelled or r.phase == RequestPhase.COMPLETE or len(r.output_ids) + 2 > r.max_new_tokens:
+                return False
+            if not r.config.use_argmax and r.config.repetition_penalty != 1.0:
+                return False
+        return True
+
+    def _launch_ahead(self, batch: ScheduledBatch, chosen) -> Optional[Tuple[ScheduledBatch, object]]:
+        logits = self.core.step_ahead([r.request_id for r in batch.decode_requests], chosen.device_tokens)
+        if logits is None:
+            return None
+        nxt = ScheduledBatch(decode_requests=list(batch.decode_requests))
+        if self.on_step is not None:
+            self.on_step(nxt)
+        self.steps_run_ahead += 1
+        return nxt, self.sampler.launch(logits, nxt.decode_requests, ahead=1)
 
     # ---- measurement (src/zedinfer/profiler.cpp:119-162) ------------------------------------
     def profile(self, prefill_len: int, decode_len: int, seed: int = 12345) -> Tuple[float, float]:

@@ -461,11 +461,15 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: torch.Tensor, t
                    c_int(rows), c_int(logits.shape[1]), c_ll(logits.stride(0)), stream())
 
 
-def advance_decode(ids: torch.Tensor, pos: torch.Tensor, sampled: torch.Tensor) -> None:
-    """Hand the chosen tokens to the next decode step: ``ids := sampled``, ``pos += 1``."""
+def advance_decode(ids: torch.Tensor, pos: torch.Tensor, sampled: torch.Tensor, rows: Optional[int] = None) -> None:
+    """Hand the chosen tokens to the next decode step: ``ids := sampled``, ``pos += 1`` for the first ``rows`` rows
+    (all of ``ids`` by default)."""
     need_cuda(ids, pos, sampled)
     need_int32("ids", ids), need_int32("pos", pos), need_int32("sampled", sampled)
-    _sampling.call("zi_advance_decode", ptr(ids), ptr(pos), ptr(sampled), c_int(ids.numel()), stream())
+    n = ids.numel() if rows is None else int(rows)
+    if n > min(ids.numel(), pos.numel(), sampled.numel()):
+        raise KernelError(f"advance_decode: {n} rows of ids {ids.numel()}, pos {pos.numel()}, sampled {sampled.numel()}")
+    _sampling.call("zi_advance_decode", ptr(ids), ptr(pos), ptr(sampled), c_int(n), stream())
 
 
 def repetition_penalty(logits_row: torch.Tensor, tokens: torch.Tensor, penalty: float) -> None:

@@ -37,33 +37,69 @@ def fresh_seed() -> int:
     return int.from_bytes(os.urandom(8), "little") | 1
 
 
+class PendingTokens:
+    """Tokens chosen on the device and on their way to the host; ``wait()`` returns them as a list."""
+
+    def __init__(self, device_tokens: torch.Tensor, host: torch.Tensor, event: torch.cuda.Event):
+        self.device_tokens, self._host, self._event = device_tokens, host, event
+
+    def wait(self) -> List[int]:
+        self._event.synchronize()
+        return self._host.tolist()
+
+
 class Sampler:
     def __init__(self, device: torch.device):
         self.device = device
+        self._pinned: List[torch.Tensor] = []
+        self._turn = 0
+
+    def _host_buffer(self, rows: int) -> torch.Tensor:
+        """One of a few pinned buffers, taken in turn (a copy is waited for before its buffer comes round again)."""
+        if not self._pinned:
+            self._pinned = [torch.empty(256, dtype=torch.int32).pin_memory() for _ in range(4)]
+        self._turn = (self._turn + 1) % len(self._pinned)
+        if self._pinned[self._turn].numel() < rows:
+            self._pinned[self._turn] = torch.empty(rows, dtype=torch.int32).pin_memory()
+        return self._pinned[self._turn][:rows]
 
     def sample(self, logits: torch.Tensor, requests: Sequence) -> List[int]:
         """One token per row of ``logits`` (float32 ``[rows, vocab]``); ``requests[i]`` gives row i's options."""
+        return self.launch(logits, requests).wait()
+
+    def launch(self, logits: torch.Tensor, requests: Sequence, ahead: int = 0) -> PendingTokens:
+        """Choose the tokens on the device and start their copy to the host without waiting for it.
+
+        ``ahead``: how many tokens of each request are chosen but not yet appended to ``output_ids`` (1 when this
+        step was launched before the host read the step before it); it moves the index of the random draw.
+        """
         rows = logits.shape[0]
         if rows != len(requests):
             raise ValueError(f"{rows} rows of logits for {len(requests)} requests")
         out = torch.empty(rows, dtype=torch.int32, device=self.device)
         if all(r.config.use_argmax for r in requests):
             ops.argmax(logits, out)
-            return out.cpu().tolist()
-        par = np.zeros((4, rows), dtype=np.float32)      # temperature, top_p, uniform, top_k (as int bits)
-        top_k = np.zeros(rows, dtype=np.int32)
-        for i, r in enumerate(requests):
-            c = r.config
-            if c.use_argmax:
-                par[0, i], par[1, i] = 0.0, 1.0
-                continue
-            par[0, i], par[1, i] = c.temperature, c.top_p
-            par[2, i] = uniform_for(r.sample_seed, len(r.output_ids))
-            top_k[i] = c.top_k
-            if c.repetition_penalty != 1.0 and r.output_ids:
-                recent = torch.tensor(r.output_ids, dtype=torch.int32).to(self.device, non_blocking=True)
-                ops.repetition_penalty(logits[i], recent, c.repetition_penalty)
-        fl = torch.from_numpy(par[:3].copy()).to(self.device, non_blocking=True)
-        tk = torch.from_numpy(top_k).to(self.device, non_blocking=True)
-        ops.sample(logits, out, fl[0], tk, fl[1], fl[2])
-        return out.cpu().tolist()
+        else:
+            par = np.zeros((4, rows), dtype=np.float32)      # temperature, top_p, uniform, top_k (as int bits)
+            top_k = np.zeros(rows, dtype=np.int32)
+            for i, r in enumerate(requests):
+                c = r.config
+                if c.use_argmax:
+                    par[0, i], par[1, i] = 0.0, 1.0
+                    continue
+                par[0, i], par[1, i] = c.temperature, c.top_p
+                par[2, i] = uniform_for(r.sample_seed, len(r.output_ids) + ahead)
+                top_k[i] = c.top_k
+                if c.repetition_penalty != 1.0 and r.output_ids:
+                    if ahead:
+                        raise ValueError("a repetition penalty needs the tokens of the step before on the host")
+                    recent = torch.tensor(r.output_ids, dtype=torch.int32).to(self.device, non_blocking=True)
+                    ops.repetition_penalty(logits[i], recent, c.repetition_penalty)
+            fl = torch.from_numpy(par[:3].copy()).to(self.device, non_blocking=True)
+            tk = torch.from_numpy(top_k).to(self.device, non_blocking=True)
+            ops.sample(logits, out, fl[0], tk, fl[1], fl[2])
+        host = self._host_buffer(rows)
+        host.copy_(out, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return PendingTokens(out, host, event)
