@@ -76,6 +76,52 @@ rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const
     }
 }
 
+// The same with 8 elements per thread and access (16-byte loads and stores for bfloat16, 32-byte for float32):
+// taken whenever the width is a multiple of 8 and the rows are aligned, whatever the number of rows, so a row's
+// sum has one order however the step was cut.
+template <typename TD, typename TW, typename TO>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_vec8_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const TW* __restrict__ w,
+                    TO* __restrict__ out, const int* __restrict__ row_idx, float eps, int hidden,
+                    int write_residual) {
+    extern __shared__ float row[];           // hidden floats
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    pdl_trigger_early();
+    pdl_wait();
+    const size_t src = row_idx ? (size_t)row_idx[r] : (size_t)r;
+    float* res = residual + src * hidden;
+    const TD* d = delta ? delta + src * hidden : nullptr;
+    const bool wb = d && write_residual && !row_idx;
+    float ss = 0.0f;
+    for (int j = threadIdx.x * 8; j < hidden; j += NORM_THREADS * 8) {
+        float x[8];
+        load8(res + j, x);
+        if (d) {
+            float dv[8];
+            load8(d + j, dv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = x[i] + dv[i];
+            if (wb) store8(res + j, x);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
+        store8(row + j, x);
+    }
+    ss = block_sum(ss, scratch);
+    pdl_trigger_late();
+    const float rstd = 1.0f / sqrtf(ss / (float)hidden + eps);
+    TO* o = out + (size_t)r * hidden;
+    for (int j = threadIdx.x * 8; j < hidden; j += NORM_THREADS * 8) {
+        float x[8], wv[8];
+        load8(row + j, x);
+        load8(w + j, wv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = (wv[i] * x[i]) * rstd;
+        store8(o + j, x);
+    }
+}
+
 // Plain norm of a tensor that is not the float32 residual (used by parts tested alone).
 template <typename TX, typename TW, typename TO>
 __global__ void __launch_bounds__(NORM_THREADS)
@@ -116,8 +162,9 @@ ZI_EXPORT int zi_add_rmsnorm(void* residual, const void* delta, int delta_dtype,
     if (rows <= 0) return 0;
     if (hidden <= 0) return zi_fail("rmsnorm: width %d must be positive", hidden);
     const size_t smem = (size_t)hidden * sizeof(float);
+    const bool vec = hidden % 8 == 0 && (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) & 31) == 0;
     ZI_DISPATCH(delta_dtype, TD, ZI_DISPATCH(w_dtype, TW, ZI_DISPATCH(out_dtype, TO, {
-        auto fn = rmsnorm_kernel<TD, TW, TO>;
+        auto fn = vec ? rmsnorm_vec8_kernel<TD, TW, TO> : rmsnorm_kernel<TD, TW, TO>;
         if (norm_smem_ok(hidden, (const void*)fn)) return 1;
         zi_launch(fn, dim3(rows), dim3(NORM_THREADS), smem, stream, (float*)residual, (const TD*)delta, (const TW*)w,
                   (TO*)out, row_idx, eps, hidden, write_residual);
@@ -193,12 +240,68 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_
                                  : page_base + (size_t)(h - n_heads) * page_size * head_dim;
             const float a = ld_dep_f32<T>(src + k), b = ld_dep_f32<T>(src + k + half);
             const float c = cs[k], sn = cs[half + k];
-            dst[k] = from_f32<T>(a * c - b * sn);
-            dst[k + half] = from_f32<T>(b * c + a * sn);
+            // explicit roundings: this kernel and the 8-wide one below must agree to the bit
+            dst[k] = from_f32<T>(__fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn)));
+            dst[k + half] = from_f32<T>(__fadd_rn(__fmul_rn(b, c), __fmul_rn(a, sn)));
         } else {
             T* dst = page_base + kv_stride + (size_t)(h - n_heads - n_kv_heads) * page_size * head_dim;
             dst[k] = ld_dep(src + k);
             dst[k + half] = ld_dep(src + k + half);
+        }
+    }
+}
+
+// The same for many tokens with 8 elements per access: one block per token, a thread takes 8 consecutive
+// elements of a head's first half and the 8 that pair with them in its second half.  The arithmetic per element is
+// the one above, so both kernels give the same bits.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_append_vec8_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ cache,
+                        const int* __restrict__ tables, const int* __restrict__ tok_seg,
+                        const int* __restrict__ pos, const float* __restrict__ inv_freq,
+                        int row_stride, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                        int max_blocks, long long page_stride, long long kv_stride, int write_kv) {
+    extern __shared__ float cs[];            // cos[half], sin[half]
+    const int n = blockIdx.x;
+    const int half = head_dim >> 1, half8 = half >> 3;
+    const int total_heads = n_heads + (write_kv ? 2 * n_kv_heads : 0);
+    const int p = pos[n];
+    for (int k = threadIdx.x; k < half; k += blockDim.x) {
+        float s, c;
+        sincosf((float)p * inv_freq[k], &s, &c);
+        cs[k] = c;
+        cs[half + k] = s;
+    }
+    __syncthreads();
+    T* page_base = nullptr;
+    if (write_kv) {
+        const int seg = tok_seg[n];
+        const int page = tables[(size_t)seg * max_blocks + p / page_size];
+        page_base = cache + (size_t)page * page_stride + (size_t)(p % page_size) * head_dim;
+    }
+    const T* row = qkv + (size_t)n * row_stride;
+    for (int idx = threadIdx.x; idx < total_heads * half8; idx += blockDim.x) {
+        const int h = idx / half8, k = (idx - h * half8) * 8;
+        const T* src = row + (size_t)h * head_dim;
+        float a[8], b[8];
+        load8(src + k, a);
+        load8(src + k + half, b);
+        if (h < n_heads + n_kv_heads) {
+            T* dst = h < n_heads ? q_out + ((size_t)n * n_heads + h) * head_dim
+                                 : page_base + (size_t)(h - n_heads) * page_size * head_dim;
+            float lo[8], hi[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float c = cs[k + i], sn = cs[half + k + i];
+                lo[i] = __fsub_rn(__fmul_rn(a[i], c), __fmul_rn(b[i], sn));
+                hi[i] = __fadd_rn(__fmul_rn(b[i], c), __fmul_rn(a[i], sn));
+            }
+            store8(dst + k, lo);
+            store8(dst + k + half, hi);
+        } else {
+            T* dst = page_base + kv_stride + (size_t)(h - n_heads - n_kv_heads) * page_size * head_dim;
+            store8(dst + k, a);
+            store8(dst + k + half, b);
         }
     }
 }
@@ -214,6 +317,16 @@ ZI_EXPORT int zi_rope_append(const void* qkv, void* q_out, void* cache, int dtyp
     const int total_heads = n_heads + 2 * n_kv_heads;
     if (total_heads > 65535) return zi_fail("rope: too many heads for one launch");
     const int hpb = n_tokens <= 64 ? 1 : total_heads;
+    const int vec_align = dtype == ZI_BF16 ? 15 : 31;
+    if (hpb != 1 && head_dim % 16 == 0 && row_stride % 8 == 0 && page_stride % 8 == 0 && kv_stride % 8 == 0 &&
+        (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)cache) & vec_align) == 0) {
+        const size_t smem8 = (size_t)head_dim * sizeof(float);
+        ZI_DISPATCH(dtype, T, {
+            rope_append_vec8_kernel<T><<<n_tokens, 256, smem8, stream>>>((const T*)qkv, (T*)q_out, (T*)cache, tables, tok_seg, pos,
+                inv_freq, row_stride, n_heads, n_kv_heads, head_dim, page_size, max_blocks, page_stride, kv_stride, write_kv);
+        });
+        return zi_check_launch("rope_append");
+    }
     dim3 grid(n_tokens, (total_heads + hpb - 1) / hpb);
     const int threads = hpb == 1 ? (head_dim >= 128 ? 64 : 32) : 256;
     const size_t smem = (size_t)head_dim * sizeof(float);
