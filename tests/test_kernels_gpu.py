@@ -275,13 +275,16 @@ def test_repetition_penalty():
 
 
 # ---- tensor-core attention (bfloat16, head_dim 64 / 128) -------------------------------------------------
+@pytest.mark.parametrize("kernel", ["cp_async", "tma"])
 @pytest.mark.parametrize("nh,nkv,hd,ps,window", [(12, 2, 128, 16, None), (7, 1, 64, 4, None), (20, 1, 128, 16, None),
                                                   (4, 4, 64, 24, None), (12, 2, 128, 16, 300), (6, 3, 64, 8, 70),
-                                                  (28, 4, 128, 32, None)])
-def test_decode_attention_mma(nh, nkv, hd, ps, window):
+                                                  (28, 4, 128, 32, None), (6, 2, 128, 64, 900), (3, 1, 64, 128, None)])
+def test_decode_attention_mma(nh, nkv, hd, ps, window, kernel):
     from zedinfer_b200 import ops
+    if kernel == "tma" and not ops.tcgen05_attention_ok(hd, ps):
+        pytest.skip("page size outside what the TMA kernel takes; the engine uses the cp.async kernel there")
     t = torch.bfloat16
-    lens = [1, 255, 256, 257, 700, 64, 513, 1500]    # around tile edges (64), fewer tiles than blocks, several rounds
+    lens = [1, 255, 256, 257, 700, 64, 513, 1500, 5000, 33]   # around tile edges, fewer tiles than blocks, several rounds
     pool, view, tables, ks, vs, page_stride, kv_stride = build_cache(len(lens), lens, nkv, hd, ps, t, seed=5)
     g = torch.Generator().manual_seed(9)
     q = torch.randn(len(lens), nh, hd, generator=g)
@@ -294,7 +297,10 @@ def test_decode_attention_mma(nh, nkv, hd, ps, window):
     seg = torch.arange(n, dtype=torch.int32, device=dev())
     out = torch.empty(n, nh * hd, dtype=t, device=dev())
     scale = 1.0 / math.sqrt(hd)
-    ops.decode_attention(qd, view, out, tables, seg, pos, nh, nkv, hd, ps, page_stride, kv_stride, window, scale)
+    fn = ops.decode_attention if kernel == "cp_async" else ops.decode_attention_tma
+    fn(qd, view, out, tables, seg, pos, nh, nkv, hd, ps, page_stride, kv_stride, window, scale)
+    torch.cuda.synchronize()
+    assert ops.tcgen05_status(dev()) == 0
     got = out.float().cpu().view(n, nh, hd)
     qf = qd.float().cpu()
     for r in range(n):

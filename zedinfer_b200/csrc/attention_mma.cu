@@ -19,7 +19,7 @@
 // Cache addressing (one call's slice of the pool): element (page, kv, kvh, off, d) lives at
 //   cache + page*page_stride + kv*kv_stride + (kvh*page_size + off)*head_dim + d.
 #define ZI_PDL_BIT 4
-#include "zi_common.cuh"
+#include "tcgen05.cuh"
 
 #include <cooperative_groups.h>
 
@@ -370,6 +370,253 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
 }
 
 // =======================================================================================
+// decode, tiles by TMA
+// =======================================================================================
+// The same cluster of DEC_CLUSTER blocks per (request, key/value head) and the same merge, but the keys are dealt
+// out in tiles of 32 to single WARPS (tile g goes to block g % 8, warp (g / 8) % 4), and every warp runs on its
+// own: its tiles come by TMA through the 5-d tensor map of the layer's cache (pages straight from the block
+// table, 128-byte swizzle) into a ring of its own with an mbarrier per stage, so there is no block-wide barrier
+// in the loop and a whole warp's share of a 3,000-key context is in flight at once.  A warp works on 32 keys per
+// step instead of 16, which halves the number of dependent ldmatrix -> mma -> softmax -> mma chains.
+// Page numbers are read 32 at a time, ahead of the tiles they belong to.  Keys outside what the query may see
+// are masked by position; their cache slots hold finite stale values (the pool is allocated zeroed).
+#define DT_STAGES 3
+
+// byte offset of 16-byte chunk c of row `row` in a [hd halves][rows][128 bytes] tile as TMA writes it
+template <int ROWS> __device__ __forceinline__ uint32_t swz_tma(int row, int c) {
+    return (uint32_t)((c >> 3) * (ROWS * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4));
+}
+template <int HD, int NKT>      // NKT * 8 keys per tile
+__device__ __forceinline__ void qk_scores_tma(float (&S)[NKT][4], const uint32_t (&qf)[HD / 16][4], uint32_t sK, int lane) {
+#pragma unroll
+    for (int nt = 0; nt < NKT; ++nt) {
+        S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.0f;
+        const int row = nt * 8 + (lane & 7);
+#pragma unroll
+        for (int kk = 0; kk < HD / 32; ++kk) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4(b0, b1, b2, b3, sK + swz_tma<NKT * 8>(row, kk * 4 + (lane >> 3)));
+            mma_bf16(S[nt], qf[2 * kk], b0, b1);
+            mma_bf16(S[nt], qf[2 * kk + 1], b2, b3);
+        }
+    }
+}
+template <int HD, int NKT>
+__device__ __forceinline__ void pv_accumulate_tma(float (&O)[HD / 8][4], const float (&S)[NKT][4], uint32_t sV, int lane) {
+#pragma unroll
+    for (int kt = 0; kt < NKT / 2; ++kt) {
+        uint32_t a[4];
+        a[0] = pack_bf16(S[2 * kt][0], S[2 * kt][1]);
+        a[1] = pack_bf16(S[2 * kt][2], S[2 * kt][3]);
+        a[2] = pack_bf16(S[2 * kt + 1][0], S[2 * kt + 1][1]);
+        a[3] = pack_bf16(S[2 * kt + 1][2], S[2 * kt + 1][3]);
+        const int row = kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+        for (int dn = 0; dn < HD / 16; ++dn) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(b0, b1, b2, b3, sV + swz_tma<NKT * 8>(row, dn * 2 + (lane >> 4)));
+            mma_bf16(O[2 * dn], a, b0, b1);
+            mma_bf16(O[2 * dn + 1], a, b2, b3);
+        }
+    }
+}
+
+template <int HD, int DT_KEYS>
+__global__ void __launch_bounds__(ATT_THREADS)
+decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q, bf16* __restrict__ out,
+                            const int* __restrict__ tables, const int* __restrict__ tok_seg, const int* __restrict__ pos,
+                            int* __restrict__ status, int n_heads, int n_kv_heads, int q_blocks, int page_size,
+                            int box_rows, int max_blocks, int window, float scale2) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    constexpr int HH = HD / 64;
+    constexpr int TILE_BYTES = DT_KEYS * HD * 2;                  // K or V of one tile
+    constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    constexpr int OS = HD + 8;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rank = blockIdx.x;
+    const int kvh = blockIdx.y / q_blocks, qb = blockIdx.y - kvh * q_blocks;
+    const int n = blockIdx.z;
+    const int group = n_heads / n_kv_heads;
+    const int P = pos[n];
+    const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
+    const int t_lo = lo / DT_KEYS, t_hi = P / DT_KEYS;
+    const int first = rank + DEC_CLUSTER * warp;                  // this warp's first tile, counted from t_lo
+    const int n_mine = (t_hi - t_lo - first >= 0) ? (t_hi - t_lo - first) / (DEC_CLUSTER * 4) + 1 : 0;
+    const int* table = tables + (size_t)tok_seg[n] * max_blocks;
+
+    // shared memory: ring [4 warps][DT_STAGES][K tile | V tile] (1024-aligned) | Q [16][HD] | mbarriers | result of
+    // this block m[16], l[16], O[16][OS]; the merge of the four warps overlays the ring afterwards
+    unsigned char* ring = smem_raw;
+    unsigned char* q_raw = ring + 4 * DT_STAGES * STAGE_BYTES;
+    const uint32_t sQ = smem_u32(q_raw);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(q_raw + 16 * HD * 2);
+    float* res_m = reinterpret_cast<float*>(bars + 4 * DT_STAGES);
+    float* res_l = res_m + 16;
+    float* res_o = res_l + 16;
+    const uint32_t my_ring = smem_u32(ring) + warp * DT_STAGES * STAGE_BYTES;
+    const uint32_t my_bars = smem_u32(bars) + warp * DT_STAGES * 8;
+
+    if (lane == 0)
+        for (int s = 0; s < DT_STAGES; ++s) mbar_init(my_bars + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    __syncwarp();
+
+    // page numbers of this warp's tiles, 32 at a time: entry e = tile * ppt + page of the tile
+    const int ppt = DT_KEYS / box_rows;                           // TMA boxes (pages, or parts of one page) per tile
+    const int ops = 2 * ppt * HH;                                 // loads per tile: k|v x pages x halves
+    int id_base = 0, id_reg = -1;
+    auto load_ids = [&](int base) {
+        id_base = base;
+        const int e = base + lane, tl = e / ppt, pg = e - tl * ppt;
+        int v = -1;
+        if (tl < n_mine) {
+            const int key0 = (t_lo + first + tl * DEC_CLUSTER * 4) * DT_KEYS + pg * box_rows;
+            const int blk = key0 / page_size;
+            if (blk < max_blocks) v = table[blk];
+        }
+        id_reg = v;
+    };
+    auto issue = [&](int tl) {
+        const int st = tl % DT_STAGES;
+        if ((tl + 1) * ppt > id_base + 32) load_ids(tl * ppt);
+        const uint32_t bar = my_bars + 8 * st;
+        if (lane == 0) mbar_expect_tx(bar, STAGE_BYTES);
+        __syncwarp();
+        const int kv = lane / (ppt * HH), rem = lane - kv * (ppt * HH), pg = rem / HH, hh = rem - pg * HH;
+        const int page = __shfl_sync(0xffffffffu, id_reg, (tl * ppt + pg - id_base) & 31);
+        if (lane < ops) {
+            const int key0 = (t_lo + first + tl * DEC_CLUSTER * 4) * DT_KEYS + pg * box_rows;
+            const uint32_t dst = my_ring + st * STAGE_BYTES + kv * TILE_BYTES + hh * (DT_KEYS * 128) + pg * box_rows * 128;
+            tma_load_5d(dst, &map_kv, hh * 64, key0 % page_size, kvh, kv, page, bar);
+        }
+        __syncwarp();
+    };
+    if (n_mine > 0) load_ids(0);
+    for (int s = 0; s < DT_STAGES && s < n_mine; ++s) issue(s);
+
+    const int rows_valid = (group - qb * 16) < 16 ? (group - qb * 16) : 16;
+    for (int i = threadIdx.x; i < 16 * (HD / 8); i += ATT_THREADS) {
+        const int row = i / (HD / 8), c = i - row * (HD / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < rows_valid) {
+            const int h = kvh * group + qb * 16 + row;
+            v = *reinterpret_cast<const uint4*>(q + ((size_t)n * n_heads + h) * HD + c * 8);
+        }
+        *reinterpret_cast<uint4*>(q_raw + swz<HD>(row, c)) = v;
+    }
+    __syncthreads();
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+        ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3],
+                    sQ + swz<HD>((lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
+
+    float O[HD / 8][4];
+#pragma unroll
+    for (int dn = 0; dn < HD / 8; ++dn) O[dn][0] = O[dn][1] = O[dn][2] = O[dn][3] = 0.0f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+
+    bool ok = true;
+    int failed_at = 0;
+    for (int i = 0; i < n_mine; ++i) {
+        const int st = i % DT_STAGES;
+        if (!mbar_wait_warp(my_bars + 8 * st, (i / DT_STAGES) & 1, nullptr)) { ok = false; failed_at = i; break; }
+        const uint32_t sK = my_ring + st * STAGE_BYTES, sV = sK + TILE_BYTES;
+        const int key0 = (t_lo + first + i * DEC_CLUSTER * 4) * DT_KEYS;
+        float S[DT_KEYS / 8][4];
+        qk_scores_tma<HD, DT_KEYS / 8>(S, qf, sK, lane);
+        if (key0 >= lo && key0 + DT_KEYS - 1 <= P) softmax_step<HD, DT_KEYS / 8, false>(S, O, m, l, key0, lane, lo, P, lo, P, scale2);
+        else softmax_step<HD, DT_KEYS / 8, true>(S, O, m, l, key0, lane, lo, P, lo, P, scale2);
+        pv_accumulate_tma<HD, DT_KEYS / 8>(O, S, sV, lane);
+        __syncwarp();                                             // every lane has read the stage
+        if (i + DT_STAGES < n_mine) issue(i + DT_STAGES);
+    }
+    if (!ok) {
+        if (lane == 0) atomicExch(status, 31);
+        // loads in flight must land before the block's memory goes away: wait (bounded) for the tiles asked for
+        for (int j = failed_at; j < n_mine && j < failed_at + DT_STAGES; ++j) mbar_wait(my_bars + 8 * (j % DT_STAGES), (j / DT_STAGES) & 1, nullptr);
+        m[0] = m[1] = -INFINITY; l[0] = l[1] = 0.0f;
+    }
+    __syncthreads();                                              // all warps are done with the ring
+    m[0] *= scale2;
+    m[1] *= scale2;
+    l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1); l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
+    l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1); l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+
+    // merge the four warps in warp order through the memory of the ring: first one factor per (warp, row) ...
+    float* red_m = reinterpret_cast<float*>(ring);               // [4][16]
+    float* red_l = red_m + 64;                                    // [4][16]
+    float* red_f = red_l + 64;                                    // [4][16] 2^(m_w - M)
+    float* red_o = red_f + 64;                                    // [4][16][OS]
+    const int g = lane >> 2, tq = lane & 3;
+    if (tq == 0) {
+        red_m[warp * 16 + g] = m[0]; red_m[warp * 16 + g + 8] = m[1];
+        red_l[warp * 16 + g] = l[0]; red_l[warp * 16 + g + 8] = l[1];
+    }
+#pragma unroll
+    for (int dn = 0; dn < HD / 8; ++dn) {
+        *reinterpret_cast<float2*>(red_o + ((size_t)warp * 16 + g) * OS + dn * 8 + tq * 2) = make_float2(O[dn][0], O[dn][1]);
+        *reinterpret_cast<float2*>(red_o + ((size_t)warp * 16 + g + 8) * OS + dn * 8 + tq * 2) = make_float2(O[dn][2], O[dn][3]);
+    }
+    __syncthreads();
+    if (threadIdx.x < 16) {
+        const int row = threadIdx.x;
+        float Mr = -INFINITY;
+        for (int w = 0; w < 4; ++w) Mr = fmaxf(Mr, red_m[w * 16 + row]);
+        const float ur = Mr == -INFINITY ? 0.0f : Mr;
+        float Lr = 0.0f;
+        for (int w = 0; w < 4; ++w) {
+            const float f = exp2f(red_m[w * 16 + row] - ur);
+            red_f[w * 16 + row] = f;
+            Lr += red_l[w * 16 + row] * f;
+        }
+        res_m[row] = Mr;
+        res_l[row] = Lr;
+    }
+    __syncthreads();
+    // ... then the weighted sums
+    for (int i = threadIdx.x; i < 16 * (HD / 4); i += ATT_THREADS) {
+        const int row = i / (HD / 4), d = (i - row * (HD / 4)) * 4;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = red_f[w * 16 + row];
+            const float4 v = *reinterpret_cast<const float4*>(red_o + ((size_t)w * 16 + row) * OS + d);
+            acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+        }
+        *reinterpret_cast<float4*>(res_o + (size_t)row * OS + d) = acc;
+    }
+    cluster.sync();                                               // every block's (m, l, O) is in place
+    constexpr int DW = HD / DEC_CLUSTER;
+    for (int i = threadIdx.x; i < rows_valid * DW; i += ATT_THREADS) {
+        const int row = i / DW, d = rank * DW + (i - row * DW);
+        float pm[DEC_CLUSTER], pl[DEC_CLUSTER], po[DEC_CLUSTER];
+#pragma unroll
+        for (int r = 0; r < DEC_CLUSTER; ++r) {
+            const float* rm = cluster.map_shared_rank(res_m, r);
+            pm[r] = rm[row];
+            pl[r] = rm[16 + row];
+            po[r] = rm[32 + (size_t)row * OS + d];
+        }
+        float M = -INFINITY;
+#pragma unroll
+        for (int r = 0; r < DEC_CLUSTER; ++r) M = fmaxf(M, pm[r]);
+        float acc = 0.0f, L = 0.0f;
+#pragma unroll
+        for (int r = 0; r < DEC_CLUSTER; ++r) {
+            const float f = exp2f(pm[r] - M);                     // blocks without keys: exp2(-inf) = 0
+            L += pl[r] * f;
+            acc += po[r] * f;
+        }
+        const int h = kvh * group + qb * 16 + row;
+        out[((size_t)n * n_heads + h) * HD + d] = __float2bfloat16_rn(acc / L);
+    }
+    cluster.sync();                                               // nobody leaves while its memory is still read
+}
+
+// =======================================================================================
 // prefill
 // =======================================================================================
 // tiles [n_tiles, 3] = (index of the tile's first token, number of rows (1..64), segment).  grid (n_tiles, n_heads).
@@ -546,6 +793,71 @@ ZI_EXPORT int zi_decode_attention(const void* q, const void* cache, void* out, c
     }
     if (e != cudaSuccess) { cudaGetLastError(); return zi_fail("decode_attention: launch failed: %s", cudaGetErrorString(e)); }
     return zi_check_launch("decode_attention");
+}
+
+// The same with tiles by TMA.  n_pages: pages in the pool (the extent of the tensor map); status: one int of device
+// memory, zero before; 31 afterwards means a bounded wait for a tile ran out and the output is not valid.
+template <int HD, int KEYS>
+static size_t dt_smem() { return 4 * DT_STAGES * 2 * KEYS * HD * 2 + 16 * HD * 2 + 4 * DT_STAGES * 8 + (32 + 16 * (HD + 8)) * 4; }
+
+// clusters of the kernel the device holds at once (a cluster needs its eight SMs inside one GPC); asked once
+template <int HD, int KEYS>
+static int dt_max_clusters() {
+    static int cached = 0;
+    if (cached) return cached;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = DEC_CLUSTER; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cfg.gridDim = dim3(DEC_CLUSTER, 64, 1); cfg.blockDim = dim3(ATT_THREADS); cfg.dynamicSmemBytes = dt_smem<HD, KEYS>();
+    if (set_smem(decode_attention_tma_kernel<HD, KEYS>, cfg.dynamicSmemBytes, "decode_attention_tma")) return -1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, decode_attention_tma_kernel<HD, KEYS>, &cfg) != cudaSuccess) { cudaGetLastError(); return -1; }
+    cached = n > 0 ? n : -1;
+    return cached;
+}
+
+template <int HD, int KEYS>
+static cudaError_t dt_launch(dim3 grid, cudaStream_t stream, const CUtensorMap& mkv, const void* q, void* out, const int* tables,
+                             const int* tok_seg, const int* pos, int* status, int n_heads, int n_kv_heads, int q_blocks, int page_size,
+                             int box_rows, int max_blocks, int window, float scale2) {
+    if (set_smem(decode_attention_tma_kernel<HD, KEYS>, dt_smem<HD, KEYS>(), "decode_attention_tma")) return cudaErrorInvalidValue;
+    return launch_cluster(decode_attention_tma_kernel<HD, KEYS>, grid, dim3(ATT_THREADS), dt_smem<HD, KEYS>(), stream, mkv, (const bf16*)q,
+                          (bf16*)out, tables, tok_seg, pos, status, n_heads, n_kv_heads, q_blocks, page_size, box_rows, max_blocks, window, scale2);
+}
+
+ZI_EXPORT int zi_decode_attention_tma(const void* q, const void* cache, void* out, const int* tables, const int* tok_seg,
+                                      const int* pos, int* status, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                      int page_size, int max_blocks, long long n_pages, long long page_stride,
+                                      long long kv_stride, int window, float scale, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (check_common("decode_attention_tma", n_heads, n_kv_heads, head_dim, page_size, max_blocks)) return 1;
+    if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1))) return zi_fail("decode_attention_tma: page size %d is not a power of two from 8 to 128", page_size);
+    if (n_tokens > 65535) return zi_fail("decode_attention_tma: %d tokens are more than one launch takes (65535)", n_tokens);
+    if (((uintptr_t)q | (uintptr_t)cache) & 15) return zi_fail("decode_attention_tma: q and cache must be 16-byte aligned");
+    if ((page_stride | kv_stride) & 7) return zi_fail("decode_attention_tma: cache strides must be multiples of 8 elements");
+    if (!status) return zi_fail("decode_attention_tma: a status word is required");
+    const int group = n_heads / n_kv_heads, q_blocks = (group + 15) / 16;
+    if (n_kv_heads * q_blocks > 65535) return zi_fail("decode_attention_tma: too many head blocks for one launch");
+    if (tc_init()) return 1;
+    // tiles of 32 keys while all clusters of the step fit on the device at once, else tiles of 16
+    const long long clusters = (long long)n_kv_heads * q_blocks * n_tokens;
+    const int fit32 = head_dim == 128 ? dt_max_clusters<128, 32>() : dt_max_clusters<64, 32>();
+    const int keys = (fit32 > 0 && clusters <= fit32) ? 32 : 16;
+    const int box_rows = page_size < keys ? page_size : keys;
+    CUtensorMap mkv;
+    if (tc_map_kv_pages(&mkv, cache, head_dim, page_size, n_kv_heads, n_pages, page_stride, kv_stride, box_rows)) return 1;
+    dim3 grid(DEC_CLUSTER, n_kv_heads * q_blocks, n_tokens);
+    const float scale2 = scale * LOG2E;
+    cudaError_t e;
+    if (head_dim == 128 && keys == 32) e = dt_launch<128, 32>(grid, stream, mkv, q, out, tables, tok_seg, pos, status, n_heads, n_kv_heads, q_blocks, page_size, box_rows, max_blocks, window, scale2);
+    else if (head_dim == 128) e = dt_launch<128, 16>(grid, stream, mkv, q, out, tables, tok_seg, pos, status, n_heads, n_kv_heads, q_blocks, page_size, box_rows, max_blocks, window, scale2);
+    else if (keys == 32) e = dt_launch<64, 32>(grid, stream, mkv, q, out, tables, tok_seg, pos, status, n_heads, n_kv_heads, q_blocks, page_size, box_rows, max_blocks, window, scale2);
+    else e = dt_launch<64, 16>(grid, stream, mkv, q, out, tables, tok_seg, pos, status, n_heads, n_kv_heads, q_blocks, page_size, box_rows, max_blocks, window, scale2);
+    if (e != cudaSuccess) { cudaGetLastError(); return zi_fail("decode_attention_tma: launch failed: %s", cudaGetErrorString(e)); }
+    return zi_check_launch("decode_attention_tma");
 }
 
 ZI_EXPORT int zi_prefill_attention(const void* q, const void* cache, void* out, const int* tables, const int* tiles,

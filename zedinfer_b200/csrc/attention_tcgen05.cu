@@ -25,10 +25,6 @@
 // zeroed, and pages that are used again hold finite values.
 #include "tcgen05.cuh"
 
-#include <map>
-#include <mutex>
-#include <tuple>
-
 ZI_DEFINE_LAST_ERROR(attention_tcgen05)
 
 #define FA_ROWS 128
@@ -39,11 +35,6 @@ ZI_DEFINE_LAST_ERROR(attention_tcgen05)
 #define FA_VSTAGES 3
 #define FA_NBARS (1 + 2 * FA_KSTAGES + 2 * FA_VSTAGES + 6)
 
-__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];\n"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar) : "memory");
-}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
@@ -363,35 +354,6 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, con
 }
 
 // ---- host side -----------------------------------------------------------------------------------------
-// Tensor maps are kept per (pointer, geometry): a layer's cache and the step's q buffer come back every step.
-typedef std::tuple<const void*, long long, long long, long long, long long, long long> FaMapKey;
-static std::map<FaMapKey, CUtensorMap> fa_maps;
-static std::mutex fa_maps_lock;
-
-static int fa_map_kv(CUtensorMap* out, const void* cache, int head_dim, int page_size, int n_kv_heads, long long n_pages,
-                     long long page_stride, long long kv_stride) {
-    std::lock_guard<std::mutex> g(fa_maps_lock);
-    const FaMapKey key(cache, head_dim, page_size, n_kv_heads * (1LL << 32) + n_pages, page_stride, kv_stride);
-    auto it = fa_maps.find(key);
-    if (it == fa_maps.end()) {
-        if (fa_maps.size() > 4096) fa_maps.clear();
-        cuuint64_t dims[5] = {(cuuint64_t)head_dim, (cuuint64_t)page_size, (cuuint64_t)n_kv_heads, 2, (cuuint64_t)n_pages};
-        cuuint64_t strides[4] = {(cuuint64_t)head_dim * 2, (cuuint64_t)page_size * head_dim * 2, (cuuint64_t)kv_stride * 2, (cuuint64_t)page_stride * 2};
-        cuuint32_t box[5] = {64, (cuuint32_t)page_size, 1, 1, 1};
-        cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-        CUtensorMap m;
-        CUresult r = tc_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box, estr,
-                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS)
-            return zi_fail("prefill_attention_tcgen05: cuTensorMapEncodeTiled failed with code %d (head %d, page %d, kv heads %d, pages %lld, strides %lld %lld)",
-                           (int)r, head_dim, page_size, n_kv_heads, n_pages, page_stride, kv_stride);
-        it = fa_maps.emplace(key, m).first;
-    }
-    *out = it->second;
-    return 0;
-}
-
 // tiles: int32 [n_tiles, 3] = (first token, rows <= 128, segment).  status: one int of device memory, zero before;
 // non-zero afterwards means a bounded wait ran out (11 producer, 12/13 MMA issuer, 14 softmax).
 ZI_EXPORT int zi_prefill_attention_tcgen05(const void* q, const void* cache, void* out, const int* tables, const int* tiles,
@@ -408,7 +370,7 @@ ZI_EXPORT int zi_prefill_attention_tcgen05(const void* q, const void* cache, voi
     if (!status) return zi_fail("prefill_attention_tcgen05: a status word is required");
     if (tc_init()) return 1;
     CUtensorMap mkv;
-    if (fa_map_kv(&mkv, cache, head_dim, page_size, n_kv_heads, n_pages, page_stride, kv_stride)) return 1;
+    if (tc_map_kv_pages(&mkv, cache, head_dim, page_size, n_kv_heads, n_pages, page_stride, kv_stride, page_size)) return 1;
     FaParams p;
     p.q = (const bf16*)q; p.out = (bf16*)out; p.tables = tables; p.tiles = tiles; p.pos = pos; p.status = status;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.max_blocks = max_blocks; p.window = window;

@@ -7,6 +7,10 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <map>
+#include <mutex>
+#include <tuple>
+
 #define TC_WAIT_LIMIT (1u << 24)
 
 __device__ __forceinline__ uint32_t tc_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -145,3 +149,40 @@ static inline int tc_make_map(CUtensorMap* map, const void* ptr, long long rows,
     return 0;
 }
 
+
+// A layer's slice of the paged cache as a 5-d tensor: (head_dim, token in page, key-value head, k|v, page), with
+// boxes of 64 elements x box_rows tokens, 128-byte swizzle.  Element (page, kv, kvh, off, d) lives at
+// cache + page*page_stride + kv*kv_stride + (kvh*page_size + off)*head_dim + d.  A page coordinate outside
+// [0, n_pages) reads zeros.  Maps are kept per (pointer, geometry): a layer's cache comes back every step.
+typedef std::tuple<const void*, long long, long long, long long, long long, long long> TcMapKey;
+static std::map<TcMapKey, CUtensorMap> tc_kv_maps;
+static std::mutex tc_kv_maps_lock;
+
+static inline int tc_map_kv_pages(CUtensorMap* out, const void* cache, int head_dim, int page_size, int n_kv_heads, long long n_pages,
+                                  long long page_stride, long long kv_stride, int box_rows) {
+    std::lock_guard<std::mutex> g(tc_kv_maps_lock);
+    const TcMapKey key(cache, head_dim * 1024LL + box_rows, page_size, n_kv_heads * (1LL << 32) + n_pages, page_stride, kv_stride);
+    auto it = tc_kv_maps.find(key);
+    if (it == tc_kv_maps.end()) {
+        if (tc_kv_maps.size() > 4096) tc_kv_maps.clear();
+        cuuint64_t dims[5] = {(cuuint64_t)head_dim, (cuuint64_t)page_size, (cuuint64_t)n_kv_heads, 2, (cuuint64_t)n_pages};
+        cuuint64_t strides[4] = {(cuuint64_t)head_dim * 2, (cuuint64_t)page_size * head_dim * 2, (cuuint64_t)kv_stride * 2, (cuuint64_t)page_stride * 2};
+        cuuint32_t box[5] = {64, (cuuint32_t)box_rows, 1, 1, 1};
+        cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+        CUtensorMap m;
+        CUresult r = tc_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return zi_fail("paged cache tensor map: cuTensorMapEncodeTiled failed with code %d (head %d, page %d, box rows %d, kv heads %d, pages %lld, strides %lld %lld)",
+                           (int)r, head_dim, page_size, box_rows, n_kv_heads, n_pages, page_stride, kv_stride);
+        it = tc_kv_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return 0;
+}
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];\n"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar) : "memory");
+}

@@ -26,7 +26,7 @@ _attention_tcgen05 = Library("attention_tcgen05")
 SMALL_M_ROWS = 16                # the weight-streaming kernel takes up to this many rows
 
 __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "silu_mul", "cast",
-           "gemm_nt", "linear", "gemm_smallm", "gemm_tcgen05", "gemm_tcgen05_tiles", "tcgen05_status", "linear_silu_mul", "raise_if_tcgen05_failed", "paged_attention", "attention", "decode_attention", "prefill_attention", "prefill_attention_tcgen05", "argmax", "sample", "repetition_penalty", "advance_decode"]
+           "gemm_nt", "linear", "gemm_smallm", "gemm_tcgen05", "gemm_tcgen05_tiles", "tcgen05_status", "status_word", "linear_silu_mul", "raise_if_tcgen05_failed", "paged_attention", "attention", "decode_attention", "decode_attention_tma", "prefill_attention", "prefill_attention_tcgen05", "argmax", "sample", "repetition_penalty", "advance_decode"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
@@ -250,6 +250,11 @@ def gemm_tcgen05_tiles(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Te
                        c_ll(out.stride(0)), c_int(1 if silu_mul else 0), c_int(tile_width), c_int(_num_sms(x.device)), stream())
 
 
+def status_word(device) -> torch.Tensor:
+    """The device word (int32 ``[1]``) in which the kernels with bounded waits report one that ran out; 0 = fine."""
+    return _tc_status(torch.device(device))
+
+
 def tcgen05_status(device) -> int:
     """0, or the code of the role whose bounded wait ran out (1 producer, 2 MMA issuer, 3 epilogue); resets it."""
     st = _tc_status(torch.device(device))
@@ -368,6 +373,25 @@ def decode_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, ta
                         c_float(scale), stream())
 
 
+def decode_attention_tma(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
+                         tok_seg: torch.Tensor, pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                         page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float) -> None:
+    """One query token per request, bfloat16: the cluster kernel with 32-key tiles dealt to single warps, each
+    fed by TMA through the block table into a ring of its own.  Same arguments as :func:`decode_attention`;
+    head_dim 64 or 128, pages of a power of two from 8 to 128 tokens.  A bounded wait that runs out is reported by
+    :func:`tcgen05_status`."""
+    need_cuda(q, cache, out, tables, tok_seg, pos)
+    need_int32("tables", tables), need_int32("tok_seg", tok_seg), need_int32("pos", pos)
+    need_contiguous("q", q), need_contiguous("out", out)
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("decode_attention_tma: bfloat16 only")
+    _attention_mma.call("zi_decode_attention_tma", ptr(q), ptr(cache), ptr(out), ptr(tables), ptr(tok_seg), ptr(pos),
+                        ptr(_tc_status(q.device)), c_int(q.shape[0]), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
+                        c_int(page_size), c_int(tables.shape[1]), c_ll(cache.shape[0]), c_ll(page_stride), c_ll(kv_stride),
+                        c_int(window or 0), c_float(scale), stream())
+    _tc_launched[q.device] = True
+
+
 def prefill_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
                       tiles: torch.Tensor, pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                       page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float) -> None:
@@ -418,6 +442,10 @@ def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv
     tables = ctx.tables[cache.group]
     if q.dtype == torch.bfloat16 and head_dim in (64, 128):
         n = q.shape[0]
+        if ctx.decode_only and tcgen05_attention_ok(head_dim, cache.page_size):
+            decode_attention_tma(q, cache.tensor, out, tables, ctx.tok_seg, ctx.positions, n_heads, n_kv_heads, head_dim,
+                                 cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
+            return
         if ctx.decode_only:
             decode_attention(q, cache.tensor, out, tables, ctx.tok_seg, ctx.positions, n_heads, n_kv_heads, head_dim,
                              cache.page_size, cache.page_stride, cache.kv_stride, window, scale)

@@ -44,8 +44,14 @@ class PendingTokens:
         self.device_tokens, self._host, self._event = device_tokens, host, event
 
     def wait(self) -> List[int]:
+        """The tokens; raises if a kernel of the step reported that one of its bounded waits ran out (the last
+        element of the copy is the kernels' status word)."""
         self._event.synchronize()
-        return self._host.tolist()
+        values = self._host.tolist()
+        if values[-1] != 0:
+            ops.tcgen05_status(self.device_tokens.device)            # reads and clears the word
+            raise ops.KernelError(f"a bounded wait ran out inside a kernel of this step (code {values[-1]}); its output is not valid")
+        return values[:-1]
 
 
 class Sampler:
@@ -98,8 +104,9 @@ class Sampler:
             fl = torch.from_numpy(par[:3].copy()).to(self.device, non_blocking=True)
             tk = torch.from_numpy(top_k).to(self.device, non_blocking=True)
             ops.sample(logits, out, fl[0], tk, fl[1], fl[2])
-        host = self._host_buffer(rows)
-        host.copy_(out, non_blocking=True)
+        host = self._host_buffer(rows + 1)
+        host[:rows].copy_(out, non_blocking=True)
+        host[rows:].copy_(ops.status_word(self.device), non_blocking=True)
         event = torch.cuda.Event()
         event.record()
         return PendingTokens(out, host, event)
