@@ -73,3 +73,40 @@ def test_float32_is_the_same_however_it_is_cut(models, name):
     for other in outs[1:]:
         for key, ref in outs[0].items():
             assert torch.equal(ref, other[key]), f"{key} differs between cuts"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_takes_the_many_row_kernels(models, dtype, monkeypatch):
+    """1,024 tokens in one step: in bfloat16 every product of the step runs on the tcgen05 kernels for many rows
+    (SM pairs, SiLU-mul epilogue) and the attention on its tcgen05 kernel with eight key tiles; the logits at the
+    first, the last and a few positions in between (tile edges among them) are the plain implementation's."""
+    from zedinfer_b200 import ops
+    from zedinfer_b200.engine.core import EngineCore, StepEntry
+    cfg, _ = tiny.CONFIGS["D"]
+    calls = {"tiles": 0, "attention": 0}
+    real_tiles, real_attn = ops.gemm_tcgen05_tiles, ops.prefill_attention_tcgen05
+
+    def counted_tiles(*a, **k):
+        calls["tiles"] += 1
+        return real_tiles(*a, **k)
+
+    def counted_attn(*a, **k):
+        calls["attention"] += 1
+        return real_attn(*a, **k)
+
+    monkeypatch.setattr(ops, "gemm_tcgen05_tiles", counted_tiles)
+    monkeypatch.setattr(ops, "prefill_attention_tcgen05", counted_attn)
+    rng = random.Random(21)
+    toks = [rng.randrange(cfg["vocab_size"]) for _ in range(1024)]
+    want = [0, 1, 127, 128, 129, 511, 640, 1000, 1023]
+    core = EngineCore(models["D"], dtype, page_size=16, num_pages=64, max_requests=2)
+    logits = core.step([StepEntry("long", toks, want)]).float().cpu()
+    core.end("long")
+    exp = expected_logits(models["D"], {"long": toks}, dtype)["long"]
+    for row, p in enumerate(want):
+        d = float((logits[row] - exp[p]).abs().max())
+        assert d <= TOL[dtype], (p, d)
+    if dtype == "bfloat16":
+        assert calls["tiles"] == 4 * cfg["num_hidden_layers"] and calls["attention"] == cfg["num_hidden_layers"]
+    else:
+        assert calls["tiles"] == 0 and calls["attention"] == 0
