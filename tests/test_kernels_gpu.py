@@ -363,3 +363,48 @@ def test_prefill_attention_tensor_cores(nh, nkv, hd, ps, window, kernel):
         err = float((got[i:i + cnt] - ref).abs().max())
         assert err < 2e-2, (r, p0, cnt, err)
         i += cnt
+
+
+@pytest.mark.parametrize("m,nh,nkv,hd,hidden,ps,with_bias", [(8, 12, 2, 128, 1536, 16, True), (1, 3, 1, 32, 96, 8, True),
+                                                             (16, 4, 4, 64, 160, 4, False), (11, 6, 3, 48, 224, 16, True)])
+def test_product_with_rotation_and_append_equals_the_separate_kernels(m, nh, nkv, hd, hidden, ps, with_bias):
+    """The decode q/k/v product with RoPE and the cache append in its epilogue gives the bits of product, then
+    rotation kernel: q and every cache page are compared exactly."""
+    from zedinfer_b200 import ops
+    g = torch.Generator().manual_seed(m + hd)
+    t = torch.bfloat16
+    width = (nh + 2 * nkv) * hd
+    x = (torch.randn(m, hidden, generator=g) * 0.7).to(t).to(dev())
+    w = (torch.randn(width, hidden, generator=g) * 0.08).to(t).to(dev())
+    b = (torch.randn(width, generator=g) * 0.3).to(t).to(dev()) if with_bias else None
+    positions = torch.tensor([(37 * i + 5) % 200 for i in range(m)], dtype=torch.int32, device=dev())
+    blocks = 200 // ps + 1
+    tables = torch.randperm(m * blocks, generator=g).to(torch.int32).view(m, blocks).to(dev())
+    seg = torch.arange(m, dtype=torch.int32, device=dev())
+    inv_freq = (1.0 / torch.pow(torch.tensor(10000.0), torch.arange(0, hd, 2, dtype=torch.float32) / hd)).to(dev())
+    pools, qs = [], []
+    for fused in (False, True):
+        pool = torch.full((m * blocks + 1, 2, 2, nkv, ps, hd), 7.0, dtype=t, device=dev())
+        view = pool[:, 1]
+        q = torch.full((m, nh, hd), float("nan"), dtype=t, device=dev())
+        if fused:
+            cs = torch.empty(m, hd, dtype=torch.float32, device=dev())
+            ops.rope_table(positions, inv_freq, cs)
+            ops.gemm_smallm_rope(x, w, b, cs, q, view, tables, seg, positions, nh, nkv, hd, ps, pool.stride(0), pool.stride(2))
+        else:
+            qkv = torch.empty(m, width, dtype=t, device=dev())
+            ops.gemm_smallm(x, w, b, qkv)
+            ops.rope_append(qkv, q, view, tables, seg, positions, inv_freq, nh, nkv, hd, ps, pool.stride(0), pool.stride(2))
+        torch.cuda.synchronize()
+        pools.append(pool), qs.append(q)
+    assert torch.isfinite(qs[1].float()).all()
+    assert torch.equal(qs[0], qs[1])
+    assert torch.equal(pools[0], pools[1])
+    # and the product itself is right: rotate the float64 product on the host
+    ref = x.double().cpu() @ w.double().cpu().t() + (b.double().cpu() if with_bias else 0.0)
+    ref = ref.to(t).double().view(m, nh + 2 * nkv, hd)[:, :nh]
+    ang = positions.cpu().double()[:, None] * inv_freq.cpu().double()[None, :]
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    a, bb = ref[..., :hd // 2], ref[..., hd // 2:]
+    want = torch.cat([a * cos - bb * sin, bb * cos + a * sin], dim=-1)
+    assert float((qs[1].double().cpu() - want).abs().max()) < 3e-2 * max(1.0, float(want.abs().max()))

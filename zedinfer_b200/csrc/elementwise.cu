@@ -338,6 +338,27 @@ ZI_EXPORT int zi_rope_append(const void* qkv, void* q_out, void* cache, int dtyp
     return zi_check_launch("rope_append");
 }
 
+// cos and sin of every token's angles, once per step for all layers: out[n, k] = cos(pos[n] * inv_freq[k]),
+// out[n, half + k] = sin(...), the same sincosf of the same float32 angle as the kernels above.
+__global__ void rope_table_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq, float* __restrict__ out,
+                                  int n_tokens, int half) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_tokens * half) return;
+    const int n = i / half, k = i - n * half;
+    float s, c;
+    sincosf((float)pos[n] * inv_freq[k], &s, &c);
+    out[(size_t)n * 2 * half + k] = c;
+    out[(size_t)n * 2 * half + half + k] = s;
+}
+
+ZI_EXPORT int zi_rope_table(const int* pos, const float* inv_freq, float* out, int n_tokens, int head_dim, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (head_dim <= 0 || (head_dim & 1)) return zi_fail("rope_table: head_dim=%d must be positive and even", head_dim);
+    const int total = n_tokens * (head_dim / 2);
+    rope_table_kernel<<<(total + 255) / 256, 256, 0, stream>>>(pos, inv_freq, out, n_tokens, head_dim / 2);
+    return zi_check_launch("rope_table");
+}
+
 // ---------------------------------------------------------------------------------------
 // SiLU-mul: out[n, j] = up * gate / (1 + exp(-gate)),  gate = x[n, j], up = x[n, inter + j]
 // (src/backend/ops/swiglu/cpu/swiglu_cpu.cpp:13-20)

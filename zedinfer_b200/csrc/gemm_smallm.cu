@@ -46,9 +46,11 @@ __device__ __forceinline__ uint4 ldg_stream(const bf16* p) {
 template <int NT>
 __device__ __forceinline__ void accumulate_rows(float (&acc)[NT][4], const bf16* __restrict__ W, const bf16* __restrict__ X,
                                                 int row0, int n_rows, int M, int step_begin, int step_end,
-                                                long long ldw, long long ldx, int warp, int lane, bool first_pass) {
+                                                long long ldw, long long ldx, int warp, int lane, bool first_pass,
+                                                int pair = 8) {
+    // pair: distance between the two groups of 8 weight rows a block works on (8: sixteen consecutive rows)
     const int g = lane >> 2, tq = lane & 3;
-    const int r0 = min(row0 + g, n_rows - 1), r1 = min(row0 + g + 8, n_rows - 1);
+    const int r0 = min(row0 + g, n_rows - 1), r1 = min(row0 + g + pair, n_rows - 1);
     const bf16* w0 = W + (long long)r0 * ldw + tq * 8;
     const bf16* w1 = W + (long long)r1 * ldw + tq * 8;
     const bf16* xp[NT];
@@ -234,6 +236,111 @@ ZI_EXPORT int zi_gemm_smallm(const void* X, const void* W, const void* bias, voi
         else        { if (f32) launch<2, float, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); else launch<2, bf16, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); }
     }
     return zi_check_launch("gemm_smallm");
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// The q/k/v product of a decode step with the rotation by position and the append to the cache in its
+// epilogue: the projected q, k and v never make a round trip through memory and the step has one kernel less.
+//   W [(n_heads + 2 n_kv_heads) * head_dim, K]: q heads, then k heads, then v heads.
+// A block takes 8 dimensions d..d+7 of one head and the 8 that pair with them under rotate-half (d + half ..):
+// its sixteen weight rows are two groups of eight, `half` apart.  cs [M, head_dim] holds cos (first half) and sin
+// (second half) of every token's angles, made once per step for all layers.  The sums are rounded to bfloat16
+// before the rotation, as the separate kernels do, and the rotation uses the same explicit roundings, so both
+// ways give the same bits.
+// ---------------------------------------------------------------------------------------------------------
+struct RopeOut {
+    const float* cs;
+    bf16* q_out;
+    bf16* cache;
+    const int* tables;
+    const int* tok_seg;
+    const int* pos;
+    int n_heads, n_kv_heads, head_dim, page_size, max_blocks;
+    long long page_stride, kv_stride;
+};
+
+template <int NT>
+__global__ void __launch_bounds__(GS_THREADS)
+gemm_smallm_rope_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const bf16* __restrict__ bias,
+                        const RopeOut ro, int M, int K, long long ldx, long long ldw) {
+    __shared__ float red[GS_WARPS][16][NT * 8 + 1];
+    __shared__ int s_page[NT * 8], s_off[NT * 8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int half = ro.head_dim >> 1, tiles_per_head = half >> 3;
+    const int head = blockIdx.x / tiles_per_head, d0 = (blockIdx.x - head * tiles_per_head) * 8;
+    const int row0 = head * ro.head_dim + d0;
+    const int n_rows = (ro.n_heads + 2 * ro.n_kv_heads) * ro.head_dim;
+    if (threadIdx.x < M) {          // where each token's k and v go: asked for now, needed after the product
+        const int p = ro.pos[threadIdx.x];
+        s_page[threadIdx.x] = ro.tables[(size_t)ro.tok_seg[threadIdx.x] * ro.max_blocks + p / ro.page_size];
+        s_off[threadIdx.x] = p % ro.page_size;
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+    accumulate_rows<NT>(acc, W, X, row0, n_rows, M, 0, K / 32, ldw, ldx, warp, lane, false, half);
+    const int g = lane >> 2, tq = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        red[warp][g][nt * 8 + tq * 2] = acc[nt][0];
+        red[warp][g][nt * 8 + tq * 2 + 1] = acc[nt][1];
+        red[warp][g + 8][nt * 8 + tq * 2] = acc[nt][2];
+        red[warp][g + 8][nt * 8 + tq * 2 + 1] = acc[nt][3];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 8 * NT * 8; i += GS_THREADS) {
+        const int rr = i & 7, m = i >> 3;
+        if (m >= M) continue;
+        float a = 0.0f, b = 0.0f;
+#pragma unroll
+        for (int w = 0; w < GS_WARPS; ++w) { a += red[w][rr][m]; b += red[w][rr + 8][m]; }
+        const int d = d0 + rr;
+        if (bias) { a += __bfloat162float(bias[row0 + rr]); b += __bfloat162float(bias[row0 + half + rr]); }
+        a = __bfloat162float(__float2bfloat16_rn(a));
+        b = __bfloat162float(__float2bfloat16_rn(b));
+        float lo = a, hi = b;
+        if (head < ro.n_heads + ro.n_kv_heads) {
+            const float c = ro.cs[(size_t)m * ro.head_dim + d], sn = ro.cs[(size_t)m * ro.head_dim + half + d];
+            lo = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn));
+            hi = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, sn));
+        }
+        bf16* dst;
+        if (head < ro.n_heads) {
+            dst = ro.q_out + ((size_t)m * ro.n_heads + head) * ro.head_dim;
+        } else {
+            const bool is_v = head >= ro.n_heads + ro.n_kv_heads;
+            const int kh = head - ro.n_heads - (is_v ? ro.n_kv_heads : 0);
+            dst = ro.cache + (size_t)s_page[m] * ro.page_stride + (is_v ? ro.kv_stride : 0) +
+                  ((size_t)kh * ro.page_size + s_off[m]) * ro.head_dim;
+        }
+        dst[d] = __float2bfloat16_rn(lo);
+        dst[d + half] = __float2bfloat16_rn(hi);
+    }
+}
+
+// cs: float32 [M, head_dim] (cos | sin per token, see zi_rope_table); tables [segments, max_blocks]; the cache is one
+// call's slice of the pool.  bias may be null.
+ZI_EXPORT int zi_gemm_smallm_rope(const void* X, const void* W, const void* bias, const float* cs, void* q_out, void* cache,
+                                  const int* tables, const int* tok_seg, const int* pos, int M, int K, long long ldx,
+                                  long long ldw, int n_heads, int n_kv_heads, int head_dim, int page_size, int max_blocks,
+                                  long long page_stride, long long kv_stride, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (M > 16) return zi_fail("gemm_smallm_rope: M=%d rows; this kernel takes at most 16", M);
+    if (K <= 0 || K % 32 != 0) return zi_fail("gemm_smallm_rope: K=%d must be a positive multiple of 32", K);
+    if (ldx % 8 != 0 || ldw % 8 != 0) return zi_fail("gemm_smallm_rope: row strides (%lld, %lld) must be multiples of 8 elements", ldx, ldw);
+    if (((uintptr_t)X | (uintptr_t)W) & 15) return zi_fail("gemm_smallm_rope: operands must be 16-byte aligned");
+    if (head_dim <= 0 || head_dim % 16) return zi_fail("gemm_smallm_rope: head_dim=%d must be a positive multiple of 16", head_dim);
+    if (n_heads <= 0 || n_kv_heads <= 0 || page_size <= 0 || max_blocks <= 0) return zi_fail("gemm_smallm_rope: bad head counts, page size or table width");
+    if (!cs || !q_out || !cache || !tables || !tok_seg || !pos) return zi_fail("gemm_smallm_rope: a null pointer among cs, q_out, cache, tables, tok_seg, pos");
+    RopeOut ro;
+    ro.cs = cs; ro.q_out = (bf16*)q_out; ro.cache = (bf16*)cache; ro.tables = tables; ro.tok_seg = tok_seg; ro.pos = pos;
+    ro.n_heads = n_heads; ro.n_kv_heads = n_kv_heads; ro.head_dim = head_dim; ro.page_size = page_size; ro.max_blocks = max_blocks;
+    ro.page_stride = page_stride; ro.kv_stride = kv_stride;
+    const long long tiles = (long long)(n_heads + 2 * n_kv_heads) * (head_dim / 16);
+    if (tiles > 0x7fffffffLL) return zi_fail("gemm_smallm_rope: too many tiles");
+    if (M <= 8) gemm_smallm_rope_kernel<1><<<(unsigned)tiles, GS_THREADS, 0, stream>>>((const bf16*)X, (const bf16*)W, (const bf16*)bias, ro, M, K, ldx, ldw);
+    else gemm_smallm_rope_kernel<2><<<(unsigned)tiles, GS_THREADS, 0, stream>>>((const bf16*)X, (const bf16*)W, (const bf16*)bias, ro, M, K, ldx, ldw);
+    return zi_check_launch("gemm_smallm_rope");
 }
 
 // ---------------------------------------------------------------------------------------------------------

@@ -71,6 +71,7 @@ class Model:
     def forward(self, ctx: StepContext, cache_views: Mapping[int, CallCacheView],
                 logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Run the step's tokens through every call; return float32 logits of ``logit_rows`` (or None)."""
+        ctx.step_cache.clear()                 # what layers share (a step's rotation angles) belongs to one step
         h = torch.empty((ctx.n_tokens, self.spec.hidden_size), dtype=torch.float32, device=ctx.device)
         self.embedding.forward(ctx.token_ids, h)
         stream = ResidualStream(h)

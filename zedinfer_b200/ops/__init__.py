@@ -25,7 +25,7 @@ _gemm_tcgen05 = Library("gemm_tcgen05")
 _attention_tcgen05 = Library("attention_tcgen05")
 SMALL_M_ROWS = 16                # the weight-streaming kernel takes up to this many rows
 
-__all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "silu_mul", "cast",
+__all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "rope_table", "gemm_smallm_rope", "can_fuse_rope_product", "silu_mul", "cast",
            "gemm_nt", "linear", "gemm_smallm", "gemm_tcgen05", "gemm_tcgen05_tiles", "tcgen05_status", "status_word", "linear_silu_mul", "raise_if_tcgen05_failed", "paged_attention", "attention", "decode_attention", "decode_attention_tma", "prefill_attention", "prefill_attention_tcgen05", "argmax", "sample", "repetition_penalty", "advance_decode"]
 
 
@@ -99,6 +99,40 @@ def rope_append(qkv: torch.Tensor, q_out: torch.Tensor, cache: Optional[torch.Te
                       ptr(tok_seg), ptr(pos), ptr(inv_freq), c_int(n), c_int(qkv.stride(0)), c_int(n_heads),
                       c_int(n_kv_heads), c_int(head_dim), c_int(page_size), c_int(tables.shape[1]),
                       c_ll(page_stride), c_ll(kv_stride), c_int(1 if write_kv else 0), stream())
+
+
+def rope_table(pos: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[n] = cos | sin`` of ``float(pos[n]) * inv_freq`` (float32 ``[n, head_dim]``): a step's angles, made once."""
+    need_cuda(pos, inv_freq, out)
+    need_int32("pos", pos)
+    need_contiguous("out", out)
+    if inv_freq.dtype != torch.float32 or out.dtype != torch.float32 or out.shape != (pos.numel(), 2 * inv_freq.numel()):
+        raise KernelError(f"rope_table: pos {tuple(pos.shape)}, inv_freq {tuple(inv_freq.shape)}, out {tuple(out.shape)} do not agree")
+    _elementwise.call("zi_rope_table", ptr(pos), ptr(inv_freq), ptr(out), c_int(pos.numel()), c_int(2 * inv_freq.numel()), stream())
+
+
+def can_fuse_rope_product(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], cache: Optional[torch.Tensor]) -> bool:
+    """The q/k/v product of a decode step can take rotation and cache append into its epilogue."""
+    return (_small_m_ok(x, w) and (bias is None or bias.dtype == torch.bfloat16) and cache is not None
+            and cache.dtype == torch.bfloat16)
+
+
+def gemm_smallm_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], cs: torch.Tensor, q_out: torch.Tensor,
+                     cache: torch.Tensor, tables: torch.Tensor, tok_seg: torch.Tensor, pos: torch.Tensor, n_heads: int,
+                     n_kv_heads: int, head_dim: int, page_size: int, page_stride: int, kv_stride: int) -> None:
+    """``x @ w.T + bias`` for the stacked q/k/v weight of at most 16 tokens, rotated by position (``cs`` from
+    :func:`rope_table`), q written to ``q_out`` and k, v appended to the cache pages of each token's request."""
+    need_cuda(x, w, bias, cs, q_out, cache, tables, tok_seg, pos)
+    need_int32("tables", tables), need_int32("tok_seg", tok_seg), need_int32("pos", pos)
+    need_contiguous("q_out", q_out), need_contiguous("cs", cs)
+    m, k = x.shape
+    if w.shape != ((n_heads + 2 * n_kv_heads) * head_dim, k) or q_out.numel() != m * n_heads * head_dim or cs.shape != (m, head_dim):
+        raise KernelError(f"gemm_smallm_rope: x {tuple(x.shape)}, w {tuple(w.shape)}, q_out {tuple(q_out.shape)}, cs {tuple(cs.shape)} do not agree")
+    if not can_fuse_rope_product(x, w, bias, cache) or q_out.dtype != torch.bfloat16 or cs.dtype != torch.float32:
+        raise KernelError("gemm_smallm_rope: bfloat16 operands, at most 16 rows, K a multiple of 32, float32 angles")
+    _gemm_smallm.call("zi_gemm_smallm_rope", ptr(x), ptr(w), ptr(bias), ptr(cs), ptr(q_out), ptr(cache), ptr(tables), ptr(tok_seg),
+                      ptr(pos), c_int(m), c_int(k), c_ll(x.stride(0)), c_ll(w.stride(0)), c_int(n_heads), c_int(n_kv_heads),
+                      c_int(head_dim), c_int(page_size), c_int(tables.shape[1]), c_ll(page_stride), c_ll(kv_stride), stream())
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:

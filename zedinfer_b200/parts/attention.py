@@ -77,11 +77,13 @@ class AttentionMixer(Mixer):
         if cache.kind != "paged":
             raise RuntimeError("attention needs a paged key/value cache")
         n = x.shape[0]
-        qkv = ctx.empty(n, self.q_dim + 2 * self.kv_dim)
-        ops.linear(x, self.w_qkv, self.b_qkv, qkv)
         q = ctx.empty(n, self.num_heads, self.head_dim)
-        self.position.rotate_append(qkv, q, cache, ctx, self.num_heads, self.num_kv_heads, self.head_dim,
-                                    write_kv=owns_cache)
+        if not self.position.project_rotate_append(x, self.w_qkv, self.b_qkv, q, cache, ctx, self.num_heads,
+                                                   self.num_kv_heads, self.head_dim, write_kv=owns_cache):
+            qkv = ctx.empty(n, self.q_dim + 2 * self.kv_dim)
+            ops.linear(x, self.w_qkv, self.b_qkv, qkv)
+            self.position.rotate_append(qkv, q, cache, ctx, self.num_heads, self.num_kv_heads, self.head_dim,
+                                        write_kv=owns_cache)
         attn = ctx.empty(n, self.q_dim)
         ops.attention(q, cache, attn, ctx, self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale)
         out = ctx.empty(n, self.hidden_size)

@@ -55,6 +55,8 @@ class StepContext:
     decode_only: bool = False
     max_kv_len: int = 0                       # longest context (after this step) among the segments
     extras: Dict[str, Any] = field(default_factory=dict)   # device tensors of special paths (decode kernels)
+    step_cache: Dict[Any, Any] = field(default_factory=dict)   # what parts share across the layers of ONE step
+    #                                           (cleared by Model.forward; e.g. the step's rotation angles)
 
     def empty(self, *shape: int, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
@@ -93,6 +95,14 @@ class PositionEncoding(Part):
     def rotate_append(self, qkv: torch.Tensor, q_out: torch.Tensor, cache: CallCacheView, ctx: StepContext,
                       n_heads: int, n_kv_heads: int, head_dim: int, write_kv: bool) -> None:
         raise NotImplementedError
+
+    def project_rotate_append(self, x: torch.Tensor, w_qkv: torch.Tensor, b_qkv: Optional[torch.Tensor],
+                              q_out: torch.Tensor, cache: CallCacheView, ctx: StepContext, n_heads: int,
+                              n_kv_heads: int, head_dim: int, write_kv: bool) -> bool:
+        """Optional: the stacked q/k/v product, the position rule and the cache append in one kernel.  Returns
+        False when this encoding (or this step) has no such kernel; the mixer then does the product itself and
+        calls :meth:`rotate_append`."""
+        return False
 
 
 class Mixer(Part):

@@ -44,3 +44,23 @@ class RotaryPosition(PositionEncoding):
         ops.rope_append(qkv, q_out, cache.tensor, ctx.tables[cache.group], ctx.tok_seg, ctx.positions,
                         self._table(qkv.device), n_heads, n_kv_heads, head_dim, cache.page_size, cache.page_stride,
                         cache.kv_stride, write_kv=write_kv)
+
+    def project_rotate_append(self, x: torch.Tensor, w_qkv: torch.Tensor, b_qkv: Optional[torch.Tensor],
+                              q_out: torch.Tensor, cache: CallCacheView, ctx: StepContext, n_heads: int,
+                              n_kv_heads: int, head_dim: int, write_kv: bool) -> bool:
+        """Steps of at most 16 tokens in bfloat16 (decode): rotation and append run in the epilogue of the q/k/v
+        product.  The step's cosines and sines are made once and shared by every layer with the same theta and
+        head size."""
+        if not (write_kv and head_dim == self.head_dim
+                and ops.can_fuse_rope_product(x, w_qkv, b_qkv, cache.tensor)):
+            return False
+        key = ("rope_cs", self.theta, self.head_dim)
+        cs = ctx.step_cache.get(key)
+        if cs is None:
+            cs = torch.empty((x.shape[0], self.head_dim), dtype=torch.float32, device=x.device)
+            ops.rope_table(ctx.positions, self._table(x.device), cs)
+            ctx.step_cache[key] = cs
+        ops.gemm_smallm_rope(x, w_qkv, b_qkv, cs, q_out, cache.tensor, ctx.tables[cache.group], ctx.tok_seg,
+                             ctx.positions, n_heads, n_kv_heads, head_dim, cache.page_size, cache.page_stride,
+                             cache.kv_stride)
+        return True
