@@ -408,3 +408,31 @@ def test_product_with_rotation_and_append_equals_the_separate_kernels(m, nh, nkv
     a, bb = ref[..., :hd // 2], ref[..., hd // 2:]
     want = torch.cat([a * cos - bb * sin, bb * cos + a * sin], dim=-1)
     assert float((qs[1].double().cpu() - want).abs().max()) < 3e-2 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("batch", [1, 9])
+def test_decode_attention_tma_long_context(batch):
+    """20,000 keys: every warp walks more tiles than the 32 page numbers it reads at a time, with tiles of 32 keys
+    (one request: its clusters fit on the device at once) and of 16 keys (nine requests: they do not)."""
+    from zedinfer_b200 import ops
+    t = torch.bfloat16
+    nh, nkv, hd, ps = 4, 1, 64, 16
+    lens = [20000] + [300 + 7 * i for i in range(batch - 1)]
+    pool, view, tables, ks, vs, page_stride, kv_stride = build_cache(len(lens), lens, nkv, hd, ps, t, seed=12)
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(len(lens), nh, hd, generator=g)
+    q[0, :, :] = ks[0][17001, 0][None, :] * 4.0           # one far key must dominate
+    qd = q.to(t).to(dev())
+    n = len(lens)
+    pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=dev())
+    seg = torch.arange(n, dtype=torch.int32, device=dev())
+    out = torch.empty(n, nh * hd, dtype=t, device=dev())
+    scale = 1.0 / math.sqrt(hd)
+    ops.decode_attention_tma(qd, view, out, tables, seg, pos, nh, nkv, hd, ps, page_stride, kv_stride, None, scale)
+    torch.cuda.synchronize()
+    assert ops.tcgen05_status(dev()) == 0
+    got = out.float().cpu().view(n, nh, hd)
+    qf = qd.float().cpu()
+    for r in range(n):
+        ref = plain_attention_rows(qf[r:r + 1], ks[r], vs[r], [lens[r] - 1], scale, None)
+        assert float((got[r:r + 1] - ref).abs().max()) < 2e-2, (r, lens[r])
