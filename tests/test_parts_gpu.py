@@ -1,6 +1,6 @@
-"""Each part of a layer alone against its plain formula, and a toy mixer with state of its own, defined here,
-registered, built into a model, loaded and stepped without a change to the framework's files."""
-import json
+"""Each part of a layer alone against its plain formula, and toy parts defined here (a mixer with state of its
+own, a feed-forward that routes tokens to experts, another position rule), registered, built into models, loaded
+and stepped without a change to the framework's files."""import json
 import math
 import os
 import random
@@ -224,3 +224,142 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     finally:
         unregister_architecture("ToyForCausalLM")
         unregister("mixer", "toy_decay")
+
+
+# ---- a toy architecture with a routed feed-forward and another position rule ------------------------------
+def test_toy_routed_feed_forward_and_toy_position_rule(tmp_path):
+    """A feed-forward that routes each token to one of three experts (float32 router logits, top-1) and a position
+    rule that is not the model's (rotation by half the position: "interpolated" angles), both defined here,
+    registered, and used by a model of two layers whose second layer keeps the dense feed-forward and the usual
+    rule.  Logits under changing portions equal a plain computation of whole sequences."""
+    from zedinfer_b200 import ops
+    from zedinfer_b200.config import (LayerCall, LayerSpec, ModelSpec, PartSpec, register_architecture,
+                                      unregister_architecture)
+    from zedinfer_b200.engine.core import EngineCore, StepEntry
+    from zedinfer_b200.parts import FeedForward, PositionEncoding, register_feed_forward, register_position, unregister
+    from zedinfer_b200.weights import TensorSpec, write_random_model
+
+    @register_feed_forward("toy_top1")
+    class Top1Experts(FeedForward):
+        """y = expert_e(x) with e = argmax(router(x)); an expert is down(silu(up(x)))."""
+
+        def __init__(self, hidden_size, inner, experts):
+            self.h, self.inner, self.e = hidden_size, inner, experts
+
+        def tensor_specs(self):
+            specs = {"router.weight": TensorSpec((self.e, self.h))}
+            for i in range(self.e):
+                specs[f"experts.{i}.up.weight"] = TensorSpec((self.inner, self.h))
+                specs[f"experts.{i}.down.weight"] = TensorSpec((self.h, self.inner))
+            return specs
+
+        def bind(self, tensors):
+            self.router = tensors["router.weight"].float()
+            self.up = [tensors[f"experts.{i}.up.weight"] for i in range(self.e)]
+            self.down = [tensors[f"experts.{i}.down.weight"] for i in range(self.e)]
+
+        def forward(self, x, ctx):
+            logits = torch.empty((x.shape[0], self.e), dtype=torch.float32, device=x.device)
+            ops.linear(x.float(), self.router, None, logits)                  # router logits in float32
+            choice = torch.argmax(logits, dim=1)
+            out = torch.zeros_like(x)
+            for i in range(self.e):
+                rows = torch.nonzero(choice == i).flatten()
+                if rows.numel() == 0:
+                    continue
+                xi = x[rows].contiguous()
+                mid = torch.empty((rows.numel(), self.inner), dtype=x.dtype, device=x.device)
+                ops.linear(xi, self.up[i], None, mid)
+                mid = (mid.float() * torch.sigmoid(mid.float())).to(x.dtype)
+                yi = torch.empty((rows.numel(), self.h), dtype=x.dtype, device=x.device)
+                ops.linear(mid, self.down[i], None, yi)
+                out[rows] = yi
+            return out
+
+    @register_position("toy_half_rope")
+    class HalfRope(PositionEncoding):
+        """Rotate-half with angle = (position / 2) * inv_freq: the framework's rotation kernel, other constants."""
+
+        def __init__(self, head_dim, theta):
+            self.head_dim, self.theta, self._inv = head_dim, theta, None
+
+        def rotate_append(self, qkv, q_out, cache, ctx, n_heads, n_kv_heads, head_dim, write_kv):
+            if self._inv is None:
+                expo = torch.arange(0, head_dim, 2, dtype=torch.float32) / float(head_dim)
+                self._inv = (0.5 / torch.pow(torch.tensor(self.theta, dtype=torch.float32), expo)).to(qkv.device)
+            ops.rope_append(qkv, q_out, cache.tensor, ctx.tables[cache.group], ctx.tok_seg, ctx.positions, self._inv,
+                            n_heads, n_kv_heads, head_dim, cache.page_size, cache.page_stride, cache.kv_stride,
+                            write_kv=write_kv)
+
+    def build_spec(raw):
+        h = raw["hidden_size"]
+        norm = PartSpec("rmsnorm", {"size": h, "eps": raw["eps"]})
+
+        def attn(position):
+            return PartSpec("attention", {"hidden_size": h, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16,
+                                          "position": PartSpec(position, {"head_dim": 16, "theta": 10000.0})})
+        routed = PartSpec("toy_top1", {"hidden_size": h, "inner": raw["inter"], "experts": 3})
+        dense = PartSpec("gated_mlp", {"hidden_size": h, "intermediate_size": raw["inter"]})
+        prefixes = {"mixer": "mixer.", "ffn": "mlp.", "norm1": "ln1.", "norm2": "ln2."}
+        layers = (LayerSpec("pre_norm", attn("toy_half_rope"), routed, {"norm1": norm, "norm2": norm}, prefixes),
+                  LayerSpec("pre_norm", attn("rope"), dense, {"norm1": norm, "norm2": norm}, prefixes))
+        return ModelSpec("Toy2ForCausalLM", raw["vocab_size"], h, layers, (LayerCall(0), LayerCall(1)), norm, True,
+                         raw["max_position_embeddings"])
+
+    register_architecture("Toy2ForCausalLM", model_types=("toy2",), parse=lambda raw: raw, build_spec=build_spec)
+    try:
+        raw = {"architectures": ["Toy2ForCausalLM"], "hidden_size": 48, "inter": 72, "vocab_size": 211, "eps": 1e-5,
+               "max_position_embeddings": 128}
+        folder = write_random_model(raw, 6, str(tmp_path / "toy2"), dtype="float32", init_scale=5.0)
+        core = EngineCore(folder, "float32", page_size=4, num_pages=32, max_requests=3)
+        rng = random.Random(8)
+        reqs = {"a": [rng.randrange(211) for _ in range(23)], "b": [rng.randrange(211) for _ in range(10)]}
+        w = P.read_safetensors(os.path.join(folder, "model.safetensors"))
+
+        def plain(ids):
+            t = len(ids)
+            pos = torch.arange(t)
+            hdn = P.embedding(ids, w["embed_tokens.weight"])
+            for layer in (0, 1):
+                p = f"layers.{layer}."
+                x = P.rms_norm(hdn, w[p + "ln1.weight"], 1e-5)
+                q = P.linear(x, w[p + "mixer.q_proj.weight"], w[p + "mixer.q_proj.bias"]).view(t, 4, 16)
+                k = P.linear(x, w[p + "mixer.k_proj.weight"], w[p + "mixer.k_proj.bias"]).view(t, 2, 16)
+                v = P.linear(x, w[p + "mixer.v_proj.weight"], w[p + "mixer.v_proj.bias"]).view(t, 2, 16)
+                where = pos.float() / 2.0 if layer == 0 else pos
+                a = P.attention(P.rope(q, where, 10000.0), P.rope(k, where, 10000.0), v, 0.25)
+                hdn = hdn + P.linear(a.reshape(t, 64), w[p + "mixer.o_proj.weight"], None)
+                x = P.rms_norm(hdn, w[p + "ln2.weight"], 1e-5)
+                if layer == 0:
+                    choice = torch.argmax(P.linear(x, w[p + "mlp.router.weight"], None), dim=1)
+                    y = torch.zeros_like(x)
+                    for i in range(t):
+                        e = int(choice[i])
+                        mid = P.linear(x[i:i + 1], w[p + f"mlp.experts.{e}.up.weight"], None)
+                        y[i] = P.linear(mid * torch.sigmoid(mid), w[p + f"mlp.experts.{e}.down.weight"], None)[0]
+                else:
+                    y = P.linear(P.swiglu(P.linear(x, w[p + "mlp.gate_proj.weight"], None),
+                                          P.linear(x, w[p + "mlp.up_proj.weight"], None)),
+                                 w[p + "mlp.down_proj.weight"], None)
+                hdn = hdn + y
+            return P.linear(P.rms_norm(hdn, w["norm.weight"], 1e-5), w["embed_tokens.weight"], None), None
+
+        ref = {rid: plain(ids)[0] for rid, ids in reqs.items()}
+        cuts = [[("a", 6), ("b", 3)], [("a", 2), ("b", 7)], [("a", 11)], [("a", 4)]]
+        done = {"a": 0, "b": 0}
+        worst = 0.0
+        for cut in cuts:
+            entries = [StepEntry(rid, reqs[rid][done[rid]:done[rid] + n], list(range(n))) for rid, n in cut]
+            logits = core.step(entries).cpu()
+            row = 0
+            for rid, n in cut:
+                worst = max(worst, float((logits[row:row + n] - ref[rid][done[rid]:done[rid] + n]).abs().max()))
+                row += n
+                done[rid] += n
+        assert done == {"a": 23, "b": 10} and worst < 2e-4, worst
+        core.end("a"), core.end("b")
+        core.cache.check()
+    finally:
+        unregister_architecture("Toy2ForCausalLM")
+        unregister("ffn", "toy_top1")
+        unregister("position", "toy_half_rope")
