@@ -1,6 +1,7 @@
 """Each part of a layer alone against its plain formula, and toy parts defined here (a mixer with state of its
 own, a feed-forward that routes tokens to experts, another position rule), registered, built into models, loaded
-and stepped without a change to the framework's files."""import json
+and stepped without a change to the framework's files."""
+import json
 import math
 import os
 import random
