@@ -328,19 +328,17 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, con
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             bf16* dst = p.out + ((size_t)(n0 + r) * p.n_heads + h) * HD;
-#pragma unroll 1
-            for (int c = 0; c < HD; c += 32) {
-                uint32_t o[32];
-                tmem_ld32(lane_base + FA_COL_O + c, o);
-                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-                if (r < rows) {
+            // the whole row of O with one wait (the registers of the scores are free now)
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        float v[8];
+            for (int c = 0; c < HD; c += 32) tmem_ld32(lane_base + FA_COL_O + c, s[c / 32]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            if (r < rows) {
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) v[k] = __uint_as_float(o[i + k]) * inv;
-                        store8(dst + c + i, v);
-                    }
+                for (int c = 0; c < HD; c += 8) {
+                    float v[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) v[k] = __uint_as_float(s[c / 32][(c & 31) + k]) * inv;
+                    store8(dst + c, v);
                 }
             }
         }
