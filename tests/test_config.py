@@ -119,7 +119,7 @@ def test_another_architecture_can_be_registered():
 
 def test_engine_options():
     SchedulerConfig().validate()
-    assert SchedulerConfig().max_batch_tokens == 2048 and SchedulerConfig().max_prefill_tokens == 512
+    assert SchedulerConfig().max_batch_tokens == 2048 and SchedulerConfig().max_prefill_tokens == 2048
     assert SchedulerConfig().max_batch_requests == 64 and SchedulerConfig().kv_block_size == 16
     with pytest.raises(ValueError):
         SchedulerConfig(on_exhaust="swap").validate()

@@ -18,7 +18,9 @@ def add_engine_arguments(p: argparse.ArgumentParser) -> None:
                    help="bfloat16: serving kernels; float32: the true 32-bit path")
     p.add_argument("--max-batch-tokens", type=int, default=2048)
     p.add_argument("--max-batch-requests", type=int, default=64)
-    p.add_argument("--max-prefill-tokens", type=int, default=512)
+    p.add_argument("--max-prefill-tokens", type=int, default=2048,
+                   help="Prompt tokens one step may hold (the reference defaults to 512; steps of fewer than about "
+                        "1,000 tokens are bound by the host here)")
     p.add_argument("--kv-block-size", type=int, default=int(os.environ.get("ZEDINFER_KV_BLOCK_SIZE", "16")),
                    help="Tokens per cache page (the reference reads ZEDINFER_KV_BLOCK_SIZE)")
     p.add_argument("--kv-pages", type=int, default=None, help="Pages per cache group instead of a memory budget")

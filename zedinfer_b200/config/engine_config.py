@@ -15,7 +15,8 @@ from typing import Optional
 class SchedulerConfig:
     max_batch_tokens: int = 2048        # tokens one step may hold (decode + prefill portions)
     max_batch_requests: int = 64        # requests that may be live at once
-    max_prefill_tokens: int = 512       # prompt tokens one step may hold, shared by its prefills
+    max_prefill_tokens: int = 2048      # prompt tokens one step may hold, shared by its prefills (the reference: 512;
+    #                                     on this GPU a step below about 1,000 tokens is bound by the host's launches)
     max_queue_size: int = 256           # waiting requests; submit() raises "Queue full" above it
     gpu_memory_utilization: float = 0.9  # share of device memory the engine may use in total
     kv_block_size: int = 16             # tokens per page

@@ -29,8 +29,20 @@ def ptr(t: Optional[torch.Tensor]) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_device_index: Optional[int] = None
+
+
 def stream() -> c_void_p:
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The current CUDA stream of the current device as a raw handle.  Asked of torch on every launch (a capture
+    or a ``torch.cuda.stream`` block changes it), through the cheapest call torch offers: a step of a small batch
+    is bound by what the host spends per launch."""
+    global _device_index
+    if _raw_stream is None:
+        return c_void_p(torch.cuda.current_stream().cuda_stream)
+    if _device_index is None:
+        _device_index = torch.cuda.current_device()
+    return c_void_p(_raw_stream(_device_index))
 
 
 def need_cuda(*tensors: Optional[torch.Tensor]) -> None:
@@ -64,6 +76,7 @@ class Library:
     def __init__(self, name: str):
         self.name = name
         self._lib: Optional[ctypes.CDLL] = None
+        self._fns = {}
 
     @property
     def lib(self) -> ctypes.CDLL:
@@ -74,6 +87,9 @@ class Library:
     def call(self, fn_name: str, *args) -> None:
         global _launches
         _launches += 1
-        rc = getattr(self.lib, fn_name)(*args)
+        fn = self._fns.get(fn_name)
+        if fn is None:
+            fn = self._fns[fn_name] = getattr(self.lib, fn_name)
+        rc = fn(*args)
         if rc != 0:
             raise KernelError(f"{fn_name}: {build.last_error(self.name)}")
