@@ -270,12 +270,13 @@ def main():
     import torch
     from zedinfer_b200.csrc import build
     from zedinfer_b200.engine.core import EngineCore
-    build.compile_all(EngineCore.kernel_libraries("bfloat16"), verbose=False)
+    build.compile_all(EngineCore.kernel_libraries("bfloat16") + ["gemm_tcgen05", "attention_tcgen05"], verbose=False)
     cfg = dict(MODEL_1P5B, num_hidden_layers=args.layers)
     pk = peaks()
     max_batch = args.batch if args.no_points else max(args.batch, 64)
     core = EngineCore(None, "bfloat16", config=cfg, random_seed=SEED, page_size=PAGE_SIZE,
-                      max_tokens=max_batch * CONTEXT, max_requests=max_batch, max_seq_len=CONTEXT)
+                      max_tokens=max_batch * CONTEXT, max_requests=max_batch, max_seq_len=CONTEXT,
+                      cuda_graphs=True)             # the engine's default: recurring steps are replayed as graphs
 
     clocks = ClockSampler()
     clocks.start()

@@ -110,3 +110,50 @@ def test_a_long_prompt_takes_the_many_row_kernels(models, dtype, monkeypatch):
         assert calls["tiles"] == 4 * cfg["num_hidden_layers"] and calls["attention"] == cfg["num_hidden_layers"]
     else:
         assert calls["tiles"] == 0 and calls["attention"] == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "D"])
+def test_captured_steps_equal_eager_steps(models, name, dtype):
+    """With graphs on, a step whose counts (tokens, segments, tiles, wanted rows) come back is captured at its
+    second appearance and replayed afterwards; the logits are the eager ones to the last bit.  Portions of one
+    size repeat here, alone and beside decoding requests, and pages are freed and used again in between."""
+    from zedinfer_b200.engine.core import EngineCore
+    cfg, _ = tiny.CONFIGS[name]
+    requests = make_requests(cfg, [96, 96, 64, 96], seed=31)
+    ids = list(requests)
+    steps, k = [], 0
+    # r0 in portions of 16; then r1 in portions of 16 beside decoded tokens of nobody (same counts as before);
+    # then r2 and r3 in portions of 32 with r0's last tokens fed one by one beside them
+    for rid in ids[:2]:
+        toks = requests[rid]
+        for s0 in range(0, len(toks), 16):
+            steps.append({"step": k, "entries": [{"id": rid, "tokens": toks[s0:s0 + 16], "want": [15]}], "end": []})
+            k += 1
+        steps[-1]["end"] = [rid]
+    a, b = requests[ids[2]], requests[ids[3]]
+    for i in range(2):
+        steps.append({"step": k, "entries": [{"id": ids[2], "tokens": a[32 * i:32 * i + 32], "want": [0, 31]}], "end": []})
+        k += 1
+    for i in range(3):
+        steps.append({"step": k, "entries": [{"id": ids[2], "tokens": [a[0]], "want": [0]},
+                                             {"id": ids[3], "tokens": b[32 * i:32 * i + 32], "want": [31]}], "end": []})
+        k += 1
+    steps[-1]["end"] = [ids[2], ids[3]]
+    page = {"A": 4, "D": 16}[name]
+    outs = []
+    for graphs in (False, True):
+        core = EngineCore(models[name], dtype, page_size=page, num_pages=256 // page + 8, max_requests=4, cuda_graphs=graphs)
+        got = {}
+        for st in steps:
+            from zedinfer_b200.engine.core import StepEntry
+            logits = core.step([StepEntry(e["id"], e["tokens"], e["want"]) for e in st["entries"]])
+            got[st["step"]] = logits.float().cpu().clone()
+            for rid in st["end"]:
+                core.end(rid)
+        outs.append(got)
+        if graphs:
+            assert len(core._step_graphs) >= 3, list(core._step_graphs)
+        core.cache.check()
+    for key, ref in outs[0].items():
+        assert torch.equal(ref, outs[1][key]), f"step {key} differs between eager and captured"

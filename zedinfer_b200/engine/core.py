@@ -113,8 +113,10 @@ class PinnedStaging:
 
 def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache], cache: CacheManager,
                        table_width: int, dtype: torch.dtype, device: torch.device, vocab: int,
-                       ring: "PinnedStaging", pad_segments: int = 0) -> Tuple[StepContext, Optional[torch.Tensor]]:
-    """Flatten the entries into one device descriptor (a single host-to-device copy)."""
+                       ring: "PinnedStaging", pad_segments: int = 0,
+                       into: Optional[torch.Tensor] = None) -> Tuple[StepContext, Optional[torch.Tensor]]:
+    """Flatten the entries into one device descriptor (a single host-to-device copy).  ``into``: a device buffer
+    to hold the descriptor (a captured step's static buffer) instead of a fresh one; its length must fit."""
     n_seg = len(entries) + pad_segments
     n_tok = sum(len(e.tokens) for e in entries) + pad_segments
     width = table_width
@@ -169,7 +171,13 @@ def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache]
         n_tile_done += 1
         seg_start.append(t), seg_len.append(1), seg_pos0.append(0), slots.append(-1)
         t += 1
-    dev = ring.stage(host, device)
+    if into is None:
+        dev = ring.stage(host, device)
+    else:
+        if into.numel() != total:
+            raise ValueError(f"the step's descriptor has {total} entries, the static buffer {into.numel()}")
+        ring.stage_into(host, into)
+        dev = into
     tables = [dev[off_tab + g * n_seg * width: off_tab + (g + 1) * n_seg * width].view(n_seg, width)
               for g in range(n_groups)]
     ctx = StepContext(
@@ -179,6 +187,7 @@ def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache]
         seg_start_host=seg_start, seg_len_host=seg_len, seg_pos0_host=seg_pos0, slots_host=slots,
         decode_only=all(k == 1 for k in seg_len), max_kv_len=max(max_kv, 1))
     ctx.extras["attn_tiles"] = dev[off_tiles: off_tiles + 3 * n_tiles].view(n_tiles, 3)
+    ctx.extras["descriptor_len"] = total
     want = dev[off_want: off_want + n_want] if n_want else None
     return ctx, want
 
@@ -237,13 +246,17 @@ class EngineCore:
         self.cuda_graphs = bool(cuda_graphs)
         self.max_requests = int(max_requests)
         self._decode_graphs: Dict[int, "DecodeGraph"] = {}
+        self._step_graphs: Dict[tuple, "StepGraph"] = {}
+        self._step_seen: Dict[tuple, int] = {}
+        self._graph_pool = None
+        self.capture_safe = self.model.capture_safe()
 
     @staticmethod
     def kernel_libraries(dtype) -> List[str]:
         """The kernel libraries a run in ``dtype`` loads, for building them ahead of the first step."""
         libs = ["elementwise", "gemm_simt", "attention_generic", "sampling"]
         if parse_dtype(dtype) == torch.bfloat16:
-            libs += ["attention_mma", "gemm_smallm"]
+            libs += ["attention_mma", "gemm_smallm"]      # the tcgen05 libraries are built when a step first needs them
         return libs
 
     # ---- requests -------------------------------------------------------------------------
@@ -257,10 +270,42 @@ class EngineCore:
 
     # ---- the step -------------------------------------------------------------------------
     def build_context(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache],
-                      pad_segments: int = 0) -> Tuple[StepContext, Optional[torch.Tensor]]:
+                      pad_segments: int = 0, into: Optional[torch.Tensor] = None
+                      ) -> Tuple[StepContext, Optional[torch.Tensor]]:
         """Flatten the entries into one device descriptor (a single host-to-device copy)."""
         return build_step_context(entries, rcs, self.cache, self.table_width, self.dtype, self.device,
-                                  self.spec.vocab_size, self._ring, pad_segments)
+                                  self.spec.vocab_size, self._ring, pad_segments, into)
+
+    # Steps that are not pure decode are launched kernel by kernel, which costs the host a few milliseconds whatever
+    # their size.  Every launch of such a step depends on the step's counts alone, so a step whose counts come back
+    # (the full-size portions of a long prompt, the same portion beside the same number of decoding requests) is
+    # captured in a CUDA graph at its second appearance and replayed from then on.
+    MAX_STEP_GRAPHS = 12
+
+    def _step_signature(self, entries: Sequence[StepEntry]) -> tuple:
+        rows = ops.PREFILL_TILE_ROWS
+        return (sum(len(e.tokens) for e in entries), len(entries), sum(-(-len(e.tokens) // rows) for e in entries),
+                sum(len(e.want) for e in entries), all(len(e.tokens) == 1 for e in entries))
+
+    def _eager_or_captured(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache]) -> Optional[torch.Tensor]:
+        from .decode_graph import StepGraph
+        if not (self.cuda_graphs and self.capture_safe):
+            ctx, want = self.build_context(entries, rcs)
+            return self.model.forward(ctx, self.views, want)
+        sig = self._step_signature(entries)
+        g = self._step_graphs.get(sig)
+        if g is None:
+            seen = self._step_seen.get(sig, 0) + 1
+            self._step_seen[sig] = seen
+            if seen < 2 or len(self._step_graphs) >= self.MAX_STEP_GRAPHS:
+                if len(self._step_seen) > 4096:
+                    self._step_seen.clear()
+                ctx, want = self.build_context(entries, rcs)
+                return self.model.forward(ctx, self.views, want)
+            g = StepGraph(self, entries, rcs)
+            self._step_graphs[sig] = g
+        return g.run(entries, rcs)
+
 
     def prepare(self, entries: Sequence[StepEntry]) -> List[RequestCache]:
         """Open new requests and make sure every entry has pages for its tokens; all or nothing."""
@@ -311,7 +356,8 @@ class EngineCore:
         left): the caller then takes the ordinary path."""
         from ..cache.pool import OutOfPages
         rcs = [self.cache.get(rid) for rid in request_ids]
-        if not rcs or any(rc is None for rc in rcs) or not self.cuda_graphs or len(rcs) > self.max_requests:
+        if (not rcs or any(rc is None for rc in rcs) or not self.cuda_graphs or not self.capture_safe
+                or len(rcs) > self.max_requests):
             return None
         g = self.decode_graph(len(rcs))
         if not g.holds(rcs) or any(rc.length + 1 > self.max_seq_len for rc in rcs):
@@ -331,12 +377,11 @@ class EngineCore:
         if not entries:
             return None
         rcs = self.prepare(entries)
-        if (self.cuda_graphs and len(entries) <= self.max_requests
+        if (self.cuda_graphs and self.capture_safe and len(entries) <= self.max_requests
                 and all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries)):
             logits = self.decode_graph(len(entries)).run(entries, rcs)
         else:
-            ctx, want = self.build_context(entries, rcs)
-            logits = self.model.forward(ctx, self.views, want)
+            logits = self._eager_or_captured(entries, rcs)
             ops.raise_if_tcgen05_failed(self.device)
         for e, rc in zip(entries, rcs):
             self.cache.commit(rc, rc.length + len(e.tokens))

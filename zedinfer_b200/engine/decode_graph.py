@@ -163,3 +163,38 @@ class DecodeGraph:
 
     def replay(self) -> None:
         self.graph.replay()
+
+
+class StepGraph:
+    """Any step (portions of prompts, alone or beside decoding requests) captured as a CUDA graph.
+
+    Everything the step's kernels are launched with depends on its counts only: tokens, segments, attention tiles
+    and wanted rows.  Which token belongs to which request, the positions, the block tables and the tiles are
+    data in the step's descriptor, which lives in a static device buffer here and is rewritten before each replay.
+    The captured work is ``Model.forward``, as in the eager path.  All step graphs share one memory pool: they
+    replay one at a time, and a step's logits are read before the next replay.
+    """
+
+    def __init__(self, core, entries: Sequence, rcs: Sequence):
+        self.core = core
+        probe_ctx, _ = core.build_context(entries, rcs)               # only to learn the descriptor's length
+        self.dev = torch.zeros(probe_ctx.extras["descriptor_len"], dtype=torch.int32, device=core.device)
+        self.ctx, self.want = core.build_context(entries, rcs, into=self.dev)
+        if core._graph_pool is None:
+            core._graph_pool = torch.cuda.graph_pool_handle()
+        # the eager runs before this one loaded the libraries and let cuBLAS pick its kernels; capture
+        torch.cuda.synchronize()
+        ops._tc_launched.pop(core.device, None)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, pool=core._graph_pool):
+            self.logits = core.model.forward(self.ctx, core.views, self.want)
+        self.uses_status = bool(ops._tc_launched.get(core.device, False))
+
+    def run(self, entries: Sequence, rcs: Sequence) -> Optional[torch.Tensor]:
+        ctx, _ = self.core.build_context(entries, rcs, into=self.dev)     # same layout: the views are the captured ones
+        if ctx.n_tokens != self.ctx.n_tokens or ctx.n_segments != self.ctx.n_segments:
+            raise RuntimeError("a step was given to a graph captured for other counts")
+        self.graph.replay()
+        if self.uses_status:
+            ops._tc_launched[self.core.device] = True
+        return self.logits

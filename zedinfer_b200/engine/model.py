@@ -58,6 +58,12 @@ class Model:
             else:
                 part.bind(local)
 
+    def capture_safe(self) -> bool:
+        """Every part and arrangement of the model only launches kernels on the step's device tensors, so steps may
+        be captured in CUDA graphs (see ``Part.capture_safe``)."""
+        parts = [part for part, _ in self._part_prefixes()]
+        return all(getattr(x, "capture_safe", False) for x in parts + list(self.blocks))
+
     # ---- cache ------------------------------------------------------------------------------
     def cache_needs(self) -> List[Tuple[int, object]]:
         """(schedule index, need) for each call that owns a cache."""

@@ -28,6 +28,10 @@ from .mlp import _stack
 
 @register_mixer("attention")
 class AttentionMixer(Mixer):
+    @property
+    def capture_safe(self) -> bool:        # as safe as the position rule it was built with
+        return bool(getattr(self.position, "capture_safe", False))
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, qkv_bias: bool = True, out_bias: bool = False,
                  scale: Optional[float] = None, window: Optional[int] = None):

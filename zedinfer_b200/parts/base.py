@@ -71,6 +71,12 @@ class ResidualStream:
 
 # ---- part interfaces ------------------------------------------------------------------------
 class Part:
+    # True: ``forward`` only launches kernels whose arguments are device tensors of the step, with shapes that
+    # depend on the step's counts alone (tokens, segments, tiles, wanted rows), so the step may be captured in a
+    # CUDA graph and replayed for other steps of the same counts.  A part that loops on the host over the step's
+    # segments (``ctx.*_host``) must leave it False; the engine then runs every step of its model eagerly.
+    capture_safe = False
+
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         return {}
 
@@ -121,6 +127,7 @@ class FeedForward(Part):
 
 class Block:
     """Arrangement of a mixer, a feed-forward and norms around the residual stream."""
+    capture_safe = False                  # see Part.capture_safe; an arrangement says so for its own code
 
     def __init__(self, mixer: Mixer, ffn: FeedForward, norms: Mapping[str, Norm]):
         self.mixer, self.ffn, self.norms = mixer, ffn, dict(norms)

@@ -12,6 +12,8 @@ from .base import Block, ResidualStream, StepContext, register_block
 
 @register_block("pre_norm")
 class PreNormBlock(Block):
+    capture_safe = True
+
     def forward(self, stream: ResidualStream, ctx: StepContext, cache: CallCacheView, owns_cache: bool) -> None:
         n, hidden = stream.h.shape
         normed = ctx.empty(n, hidden)

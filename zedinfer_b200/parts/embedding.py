@@ -16,6 +16,8 @@ from .base import Part
 
 
 class TokenEmbedding(Part):
+    capture_safe = True
+
     def __init__(self, vocab_size: int, hidden_size: int, name: str = "embed_tokens.weight"):
         self.vocab_size, self.hidden_size, self.name = int(vocab_size), int(hidden_size), name
         self.table: Optional[torch.Tensor] = None
@@ -31,6 +33,8 @@ class TokenEmbedding(Part):
 
 
 class OutputHead(Part):
+    capture_safe = True
+
     def __init__(self, vocab_size: int, hidden_size: int, tied: bool, name: str = "lm_head.weight"):
         self.vocab_size, self.hidden_size, self.tied, self.name = int(vocab_size), int(hidden_size), bool(tied), name
         self.weight: Optional[torch.Tensor] = None

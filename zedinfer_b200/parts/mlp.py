@@ -20,6 +20,8 @@ def _stack(tensors):
 
 @register_feed_forward("gated_mlp")
 class GatedMLP(FeedForward):
+    capture_safe = True
+
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu", bias: bool = False):
         if activation != "silu":
             raise ValueError(f"gated_mlp: activation {activation!r} is not supported (only 'silu')")

@@ -13,6 +13,8 @@ from .base import Norm, ResidualStream, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
+    capture_safe = True
+
     def __init__(self, size: int, eps: float):
         if size <= 0:
             raise ValueError(f"rmsnorm: size={size} must be positive")

@@ -18,6 +18,8 @@ from .base import PositionEncoding, StepContext, register_position
 
 @register_position("rope")
 class RotaryPosition(PositionEncoding):
+    capture_safe = True
+
     def __init__(self, head_dim: int, theta: float):
         if head_dim <= 0 or head_dim % 2:
             raise ValueError(f"rope: head_dim={head_dim} must be positive and even")
