@@ -157,3 +157,36 @@ def test_captured_steps_equal_eager_steps(models, name, dtype):
         core.cache.check()
     for key, ref in outs[0].items():
         assert torch.equal(ref, outs[1][key]), f"step {key} differs between eager and captured"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_mixed_steps_with_padding_equal_eager_steps(models, dtype):
+    """Three decoding requests beside a prompt portion: the captured form pads the single tokens to four with a
+    token on the scratch page; logits are the eager ones to the last bit, and the padding leaves the cache alone."""
+    from zedinfer_b200.engine.core import EngineCore, StepEntry
+    cfg, _ = tiny.CONFIGS["D"]
+    requests = make_requests(cfg, [70, 70, 70, 128], seed=41)
+    ids = list(requests)
+    steps = [[(rid, requests[rid][:64], [63])] for rid in ids[:3]]
+    for i in range(4):
+        steps.append([(rid, [requests[rid][64 + i]], [0]) for rid in ids[:3]] +
+                     [(ids[3], requests[ids[3]][32 * i:32 * i + 32], [31])])
+    outs = []
+    for graphs in (False, True):
+        core = EngineCore(models["D"], dtype, page_size=16, num_pages=40, max_requests=4, cuda_graphs=graphs)
+        got = []
+        for st in steps:
+            got.append(core.step([StepEntry(*e) for e in st]).float().cpu().clone())
+        if graphs:
+            assert any(g.pad == 1 for g in core._step_graphs.values())
+        for rid in ids:
+            core.end(rid)
+        core.cache.check()
+        outs.append(got)
+    for i, (a, b) in enumerate(zip(*outs)):
+        assert torch.equal(a, b), f"step {i} differs between eager and captured"
+    exp = expected_logits(models["D"], requests, dtype)
+    last = outs[1][-1]                      # rows: r0, r1, r2 at position 67, r3 at position 127
+    for row, rid in enumerate(ids[:3]):
+        assert float((last[row] - exp[rid][67]).abs().max()) <= TOL[dtype]
+    assert float((last[3] - exp[ids[3]][127]).abs().max()) <= TOL[dtype]

@@ -282,30 +282,44 @@ class EngineCore:
     # captured in a CUDA graph at its second appearance and replayed from then on.
     MAX_STEP_GRAPHS = 12
 
-    def _step_signature(self, entries: Sequence[StepEntry]) -> tuple:
+    def _step_padding(self, entries: Sequence[StepEntry]) -> int:
+        """Single-token segments (decoding requests beside a prompt portion) are padded to a power of two with
+        tokens on the cache's scratch page, so that fewer different counts occur."""
+        singles = sum(1 for e in entries if len(e.tokens) == 1)
+        if singles == 0 or singles == len(entries):
+            return 0
+        bucket = 1
+        while bucket < singles:
+            bucket *= 2
+        return bucket - singles
+
+    def _step_signature(self, entries: Sequence[StepEntry], pad: int) -> tuple:
         rows = ops.PREFILL_TILE_ROWS
-        return (sum(len(e.tokens) for e in entries), len(entries), sum(-(-len(e.tokens) // rows) for e in entries),
-                sum(len(e.want) for e in entries), all(len(e.tokens) == 1 for e in entries))
+        return (sum(len(e.tokens) for e in entries) + pad, len(entries) + pad,
+                sum(-(-len(e.tokens) // rows) for e in entries) + pad, sum(len(e.want) for e in entries),
+                all(len(e.tokens) == 1 for e in entries))
 
     def _eager_or_captured(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache]) -> Optional[torch.Tensor]:
         from .decode_graph import StepGraph
         if not (self.cuda_graphs and self.capture_safe):
             ctx, want = self.build_context(entries, rcs)
             return self.model.forward(ctx, self.views, want)
-        sig = self._step_signature(entries)
-        g = self._step_graphs.get(sig)
+        pad = self._step_padding(entries)
+        sig = self._step_signature(entries, pad)
+        g = self._step_graphs.pop(sig, None)
         if g is None:
             seen = self._step_seen.get(sig, 0) + 1
             self._step_seen[sig] = seen
-            if seen < 2 or len(self._step_graphs) >= self.MAX_STEP_GRAPHS:
+            if seen < 2:
                 if len(self._step_seen) > 4096:
                     self._step_seen.clear()
-                ctx, want = self.build_context(entries, rcs)
+                ctx, want = self.build_context(entries, rcs, pad_segments=pad)     # the shape a capture would have
                 return self.model.forward(ctx, self.views, want)
-            g = StepGraph(self, entries, rcs)
-            self._step_graphs[sig] = g
+            while len(self._step_graphs) >= self.MAX_STEP_GRAPHS:                   # the least recently used one goes
+                del self._step_graphs[next(iter(self._step_graphs))]
+            g = StepGraph(self, entries, rcs, pad)
+        self._step_graphs[sig] = g                                                  # most recently used: last
         return g.run(entries, rcs)
-
 
     def prepare(self, entries: Sequence[StepEntry]) -> List[RequestCache]:
         """Open new requests and make sure every entry has pages for its tokens; all or nothing."""

@@ -175,11 +175,11 @@ class StepGraph:
     replay one at a time, and a step's logits are read before the next replay.
     """
 
-    def __init__(self, core, entries: Sequence, rcs: Sequence):
-        self.core = core
-        probe_ctx, _ = core.build_context(entries, rcs)               # only to learn the descriptor's length
+    def __init__(self, core, entries: Sequence, rcs: Sequence, pad_segments: int = 0):
+        self.core, self.pad = core, pad_segments
+        probe_ctx, _ = core.build_context(entries, rcs, pad_segments=pad_segments)   # only to learn the descriptor's length
         self.dev = torch.zeros(probe_ctx.extras["descriptor_len"], dtype=torch.int32, device=core.device)
-        self.ctx, self.want = core.build_context(entries, rcs, into=self.dev)
+        self.ctx, self.want = core.build_context(entries, rcs, pad_segments=pad_segments, into=self.dev)
         if core._graph_pool is None:
             core._graph_pool = torch.cuda.graph_pool_handle()
         # the eager runs before this one loaded the libraries and let cuBLAS pick its kernels; capture
@@ -191,7 +191,8 @@ class StepGraph:
         self.uses_status = bool(ops._tc_launched.get(core.device, False))
 
     def run(self, entries: Sequence, rcs: Sequence) -> Optional[torch.Tensor]:
-        ctx, _ = self.core.build_context(entries, rcs, into=self.dev)     # same layout: the views are the captured ones
+        pad = self.ctx.n_segments - len(entries)      # same counts, so the same layout: the views are the captured ones
+        ctx, _ = self.core.build_context(entries, rcs, pad_segments=pad, into=self.dev)
         if ctx.n_tokens != self.ctx.n_tokens or ctx.n_segments != self.ctx.n_segments:
             raise RuntimeError("a step was given to a graph captured for other counts")
         self.graph.replay()
