@@ -144,6 +144,7 @@ def test_captured_steps_equal_eager_steps(models, name, dtype):
     outs = []
     for graphs in (False, True):
         core = EngineCore(models[name], dtype, page_size=page, num_pages=256 // page + 8, max_requests=4, cuda_graphs=graphs)
+        core.GPU_BOUND_RATIO = float("inf")       # capture at the second appearance, however long the GPU takes
         got = {}
         for st in steps:
             from zedinfer_b200.engine.core import StepEntry
@@ -174,6 +175,7 @@ def test_captured_mixed_steps_with_padding_equal_eager_steps(models, dtype):
     outs = []
     for graphs in (False, True):
         core = EngineCore(models["D"], dtype, page_size=16, num_pages=40, max_requests=4, cuda_graphs=graphs)
+        core.GPU_BOUND_RATIO = float("inf")
         got = []
         for st in steps:
             got.append(core.step([StepEntry(*e) for e in st]).float().cpu().clone())
@@ -190,3 +192,22 @@ def test_captured_mixed_steps_with_padding_equal_eager_steps(models, dtype):
     for row, rid in enumerate(ids[:3]):
         assert float((last[row] - exp[rid][67]).abs().max()) <= TOL[dtype]
     assert float((last[3] - exp[ids[3]][127]).abs().max()) <= TOL[dtype]
+
+
+def test_a_step_shape_is_captured_only_if_the_host_is_the_slower_one(models):
+    """The first appearance of a step shape is timed on both sides.  A shape whose GPU time exceeds the host's
+    launch time by the ratio stays eager however often it comes back; any other is captured at its second
+    appearance and replayed from the third."""
+    from zedinfer_b200.engine.core import EngineCore, StepEntry
+    cfg, _ = tiny.CONFIGS["D"]
+    toks = make_requests(cfg, [96], seed=51)["r0"]
+    for ratio, graphs_after in ((0.0, [0, 0, 0]), (float("inf"), [0, 1, 1])):
+        core = EngineCore(models["D"], "bfloat16", page_size=16, num_pages=16, max_requests=2, cuda_graphs=True)
+        core.GPU_BOUND_RATIO = ratio
+        seen, outs = [], []
+        for i in range(3):
+            outs.append(core.step([StepEntry(("p", i), toks[:32], [31])]).float().cpu().clone())
+            core.end(("p", i))
+            seen.append(len(core._step_graphs))
+        assert seen == graphs_after, (ratio, seen)
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])

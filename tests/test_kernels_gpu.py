@@ -410,6 +410,37 @@ def test_product_with_rotation_and_append_equals_the_separate_kernels(m, nh, nkv
     assert float((qs[1].double().cpu() - want).abs().max()) < 3e-2 * max(1.0, float(want.abs().max()))
 
 
+@pytest.mark.parametrize("requests,window", [(10, None), (20, None), (40, None), (40, 200), (150, None)])
+def test_decode_attention_tma_cluster_sizes(requests, window):
+    """The more (request, key/value head) pairs a step has, the fewer blocks share one pair's keys: clusters of 8,
+    4, 2 and single blocks on a device of 148 SMs for 10, 20, 40 and more requests of 4 key/value heads.  Lengths
+    sit around tile edges, some shorter than one tile a block; one request looks hard at a far key."""
+    from zedinfer_b200 import ops
+    t = torch.bfloat16
+    nh, nkv, hd, ps = 8, 4, 64, 16
+    base = [1, 15, 16, 17, 255, 256, 257, 700, 64, 513, 1500, 33, 2049]
+    lens = [base[i % len(base)] + (i // len(base)) for i in range(requests)]
+    pool, view, tables, ks, vs, page_stride, kv_stride = build_cache(len(lens), lens, nkv, hd, ps, t, seed=21)
+    g = torch.Generator().manual_seed(4)
+    q = torch.randn(len(lens), nh, hd, generator=g)
+    far = 5 if not window else 700 - window
+    q[7, :, :] = ks[7][far, 0][None, :] * 4.0
+    qd = q.to(t).to(dev())
+    n = len(lens)
+    pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=dev())
+    seg = torch.arange(n, dtype=torch.int32, device=dev())
+    out = torch.empty(n, nh * hd, dtype=t, device=dev())
+    scale = 1.0 / math.sqrt(hd)
+    ops.decode_attention_tma(qd, view, out, tables, seg, pos, nh, nkv, hd, ps, page_stride, kv_stride, window, scale)
+    torch.cuda.synchronize()
+    assert ops.tcgen05_status(dev()) == 0
+    got = out.float().cpu().view(n, nh, hd)
+    qf = qd.float().cpu()
+    for r in range(n):
+        ref = plain_attention_rows(qf[r:r + 1], ks[r], vs[r], [lens[r] - 1], scale, window)
+        assert float((got[r:r + 1] - ref).abs().max()) < 2e-2, (r, lens[r])
+
+
 @pytest.mark.parametrize("batch", [1, 9])
 def test_decode_attention_tma_long_context(batch):
     """20,000 keys: every warp walks more tiles than the 32 page numbers it reads at a time, with tiles of 32 keys

@@ -5,7 +5,7 @@ from __future__ import annotations
 import argparse
 import sys
 
-from .common import add_engine_arguments, scheduler_config_from
+from .common import add_engine_arguments, create_engine
 
 
 def main(argv=None) -> int:
@@ -20,7 +20,7 @@ def main(argv=None) -> int:
         print("--decode-len/--max-tokens must be > 0 for benchmark runs", file=sys.stderr)
         return 1
     from ..engine import InferenceEngine
-    engine = InferenceEngine.create(args.model_path, scheduler_config_from(args), dtype=args.dtype)
+    engine = create_engine(args)
     for _ in range(2):                                                     # warm-up with the same lengths, twice:
         engine.profile(args.prefill_len, args.decode_len)                  # a recurring step is captured at its second run
     total_p = total_d = 0.0

@@ -10,6 +10,9 @@ from ..config.engine_config import SchedulerConfig
 
 def add_engine_arguments(p: argparse.ArgumentParser) -> None:
     p.add_argument("model_path", help="Path to the model directory (config.json + *.safetensors)")
+    p.add_argument("--random-weights", type=int, default=None, metavar="SEED",
+                   help="model_path may be a config.json alone: draw the weights on the device from this seed "
+                        "instead of reading *.safetensors (shapes too large to write out as a folder)")
     p.add_argument("--nvidia", action="store_true",
                    help="Use NVIDIA GPU backend (accepted for parity; this engine has no other backend)")
     p.add_argument("--gpu-memory-utilization", type=float, default=0.9,
@@ -36,6 +39,12 @@ def scheduler_config_from(args) -> SchedulerConfig:
                            gpu_memory_utilization=args.gpu_memory_utilization, kv_block_size=args.kv_block_size,
                            num_kv_pages=args.kv_pages, max_seq_len=args.max_seq_len, on_exhaust=args.on_exhaust,
                            cuda_graphs=not args.no_cuda_graphs)
+
+
+def create_engine(args):
+    from ..engine import InferenceEngine
+    return InferenceEngine.create(args.model_path, scheduler_config_from(args), dtype=args.dtype,
+                                  random_seed=args.random_weights)
 
 
 def parse_ids(text: str):

@@ -6,7 +6,7 @@ import argparse
 import sys
 import time
 
-from .common import add_engine_arguments, parse_ids, scheduler_config_from
+from .common import add_engine_arguments, create_engine, parse_ids
 
 
 def main(argv=None) -> int:
@@ -31,7 +31,7 @@ def main(argv=None) -> int:
     from ..engine import InferenceEngine
     t0 = time.perf_counter()
     try:
-        engine = InferenceEngine.create(args.model_path, scheduler_config_from(args), dtype=args.dtype)
+        engine = create_engine(args)
     except Exception as e:
         print(f"[ping] engine init failed: {e}", file=sys.stderr)
         return 3

@@ -1,4 +1,4 @@
-"""Run a few decode or prefill steps of a random-weight Qwen2-shaped model between cudaProfilerStart/Stop,
+"""Run a few decode, prefill or mixed steps of a random-weight Qwen2-shaped model between cudaProfilerStart/Stop,
 for ``ncu --profile-from-start off``.  Steps are launched kernel by kernel (no CUDA graph), so every
 kernel shows up as a launch of its own.  Prints the mean time of a step measured with CUDA events."""
 from __future__ import annotations
@@ -10,7 +10,8 @@ import sys
 
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="zedinfer-profile-step", description=__doc__)
-    p.add_argument("--mode", choices=["decode", "prefill"], default="decode")
+    p.add_argument("--mode", choices=["decode", "prefill", "mixed"], default="decode",
+                   help="mixed: --batch decoding requests beside a prompt portion of --tokens")
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=3072, help="decode: tokens already cached per request")
     p.add_argument("--tokens", type=int, default=2048, help="prefill: tokens of the portion")
@@ -30,24 +31,30 @@ def main(argv=None) -> int:
            "hidden_size": args.hidden, "num_attention_heads": args.heads, "num_key_value_heads": args.kv_heads,
            "head_dim": args.head_dim, "intermediate_size": args.intermediate, "vocab_size": args.vocab,
            "max_position_embeddings": 8192}
-    span = (args.context + args.steps + 8) if args.mode == "decode" else args.tokens
+    span = args.tokens if args.mode == "prefill" else max(args.context + args.steps + 8, args.tokens)
     core = EngineCore(None, "bfloat16", config=cfg, random_seed=3, page_size=16,
-                      max_tokens=args.batch * (span + 64), max_requests=max(args.batch, 1), max_seq_len=span + 64,
+                      max_tokens=(args.batch + 1) * (span + 64), max_requests=args.batch + 1, max_seq_len=span + 64,
                       cuda_graphs=args.graphs)
     g = torch.Generator().manual_seed(0)
     rand = lambda n: torch.randint(0, args.vocab, (n,), generator=g).tolist()      # noqa: E731
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if args.mode == "decode":
+    counter = [0]
+    if args.mode in ("decode", "mixed"):
         for r in range(args.batch):
             left = args.context
             while left > 0:
                 n = min(left, 2048)
                 core.step([StepEntry(r, rand(n), [])])
                 left -= n
+    if args.mode == "decode":
         step = lambda: core.step([StepEntry(r, rand(1), [0]) for r in range(args.batch)])   # noqa: E731
+    elif args.mode == "mixed":
+        def step():
+            rid = ("p", counter[0])
+            counter[0] += 1
+            core.step([StepEntry(r, rand(1), [0]) for r in range(args.batch)] + [StepEntry(rid, rand(args.tokens), [])])
+            core.end(rid)
     else:
-        counter = [0]
-
         def step():
             rid = ("p", counter[0])
             counter[0] += 1

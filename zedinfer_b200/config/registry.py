@@ -75,7 +75,8 @@ def resolve_architecture(raw: Mapping[str, Any]) -> Architecture:
 
 
 def read_config_json(model_dir: str) -> Dict[str, Any]:
-    path = os.path.join(model_dir, "config.json")
+    """The JSON object of ``model_dir/config.json``; ``model_dir`` may also name the JSON file itself."""
+    path = model_dir if os.path.isfile(model_dir) else os.path.join(model_dir, "config.json")
     if not os.path.isfile(path):
         raise ConfigError(f"Failed to open config file: {path}")
     with open(path, "r", encoding="utf-8") as f:

@@ -372,8 +372,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
 // =======================================================================================
 // decode, tiles by TMA
 // =======================================================================================
-// The same cluster of DEC_CLUSTER blocks per (request, key/value head) and the same merge, but the keys are dealt
-// out in tiles of 32 to single WARPS (tile g goes to block g % 8, warp (g / 8) % 4), and every warp runs on its
+// A cluster of CL blocks per (request, key/value head) and the same merge, but the keys are dealt
+// out in tiles of 32 to single WARPS (tile g goes to block g % CL, warp (g / CL) % 4), and every warp runs on its
 // own: its tiles come by TMA through the 5-d tensor map of the layer's cache (pages straight from the block
 // table, 128-byte swizzle) into a ring of its own with an mbarrier per stage, so there is no block-wide barrier
 // in the loop and a whole warp's share of a 3,000-key context is in flight at once.  A warp works on 32 keys per
@@ -421,7 +421,7 @@ __device__ __forceinline__ void pv_accumulate_tma(float (&O)[HD / 8][4], const f
     }
 }
 
-template <int HD, int DT_KEYS>
+template <int HD, int DT_KEYS, int CL>
 __global__ void __launch_bounds__(ATT_THREADS)
 decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q, bf16* __restrict__ out,
                             const int* __restrict__ tables, const int* __restrict__ tok_seg, const int* __restrict__ pos,
@@ -442,8 +442,8 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
     const int P = pos[n];
     const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
     const int t_lo = lo / DT_KEYS, t_hi = P / DT_KEYS;
-    const int first = rank + DEC_CLUSTER * warp;                  // this warp's first tile, counted from t_lo
-    const int n_mine = (t_hi - t_lo - first >= 0) ? (t_hi - t_lo - first) / (DEC_CLUSTER * 4) + 1 : 0;
+    const int first = rank + CL * warp;                  // this warp's first tile, counted from t_lo
+    const int n_mine = (t_hi - t_lo - first >= 0) ? (t_hi - t_lo - first) / (CL * 4) + 1 : 0;
     const int* table = tables + (size_t)tok_seg[n] * max_blocks;
 
     // shared memory: ring [4 warps][DT_STAGES][K tile | V tile] (1024-aligned) | Q [16][HD] | mbarriers | result of
@@ -472,7 +472,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
         const int e = base + lane, tl = e / ppt, pg = e - tl * ppt;
         int v = -1;
         if (tl < n_mine) {
-            const int key0 = (t_lo + first + tl * DEC_CLUSTER * 4) * DT_KEYS + pg * box_rows;
+            const int key0 = (t_lo + first + tl * CL * 4) * DT_KEYS + pg * box_rows;
             const int blk = key0 / page_size;
             if (blk < max_blocks) v = table[blk];
         }
@@ -487,7 +487,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
         const int kv = lane / (ppt * HH), rem = lane - kv * (ppt * HH), pg = rem / HH, hh = rem - pg * HH;
         const int page = __shfl_sync(0xffffffffu, id_reg, (tl * ppt + pg - id_base) & 31);
         if (lane < ops) {
-            const int key0 = (t_lo + first + tl * DEC_CLUSTER * 4) * DT_KEYS + pg * box_rows;
+            const int key0 = (t_lo + first + tl * CL * 4) * DT_KEYS + pg * box_rows;
             const uint32_t dst = my_ring + st * STAGE_BYTES + kv * TILE_BYTES + hh * (DT_KEYS * 128) + pg * box_rows * 128;
             tma_load_5d(dst, &map_kv, hh * 64, key0 % page_size, kvh, kv, page, bar);
         }
@@ -524,7 +524,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
         const int st = i % DT_STAGES;
         if (!mbar_wait_warp(my_bars + 8 * st, (i / DT_STAGES) & 1, nullptr)) { ok = false; failed_at = i; break; }
         const uint32_t sK = my_ring + st * STAGE_BYTES, sV = sK + TILE_BYTES;
-        const int key0 = (t_lo + first + i * DEC_CLUSTER * 4) * DT_KEYS;
+        const int key0 = (t_lo + first + i * CL * 4) * DT_KEYS;
         float S[DT_KEYS / 8][4];
         qk_scores_tma<HD, DT_KEYS / 8>(S, qf, sK, lane);
         if (key0 >= lo && key0 + DT_KEYS - 1 <= P) softmax_step<HD, DT_KEYS / 8, false>(S, O, m, l, key0, lane, lo, P, lo, P, scale2);
@@ -589,12 +589,12 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
         *reinterpret_cast<float4*>(res_o + (size_t)row * OS + d) = acc;
     }
     cluster.sync();                                               // every block's (m, l, O) is in place
-    constexpr int DW = HD / DEC_CLUSTER;
+    constexpr int DW = HD / CL;
     for (int i = threadIdx.x; i < rows_valid * DW; i += ATT_THREADS) {
         const int row = i / DW, d = rank * DW + (i - row * DW);
-        float pm[DEC_CLUSTER], pl[DEC_CLUSTER], po[DEC_CLUSTER];
+        float pm[CL], pl[CL], po[CL];
 #pragma unroll
-        for (int r = 0; r < DEC_CLUSTER; ++r) {
+        for (int r = 0; r < CL; ++r) {
             const float* rm = cluster.map_shared_rank(res_m, r);
             pm[r] = rm[row];
             pl[r] = rm[16 + row];
@@ -602,10 +602,10 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
         }
         float M = -INFINITY;
 #pragma unroll
-        for (int r = 0; r < DEC_CLUSTER; ++r) M = fmaxf(M, pm[r]);
+        for (int r = 0; r < CL; ++r) M = fmaxf(M, pm[r]);
         float acc = 0.0f, L = 0.0f;
 #pragma unroll
-        for (int r = 0; r < DEC_CLUSTER; ++r) {
+        for (int r = 0; r < CL; ++r) {
             const float f = exp2f(pm[r] - M);                     // blocks without keys: exp2(-inf) = 0
             L += pl[r] * f;
             acc += po[r] * f;
@@ -800,7 +800,8 @@ ZI_EXPORT int zi_decode_attention(const void* q, const void* cache, void* out, c
 template <int HD, int KEYS>
 static size_t dt_smem() { return 4 * DT_STAGES * 2 * KEYS * HD * 2 + 16 * HD * 2 + 4 * DT_STAGES * 8 + (32 + 16 * (HD + 8)) * 4; }
 
-// clusters of the kernel the device holds at once (a cluster needs its eight SMs inside one GPC); asked once
+// clusters of eight blocks of the kernel that the device holds at once (a cluster needs its SMs inside one GPC);
+// asked once
 template <int HD, int KEYS>
 static int dt_max_clusters() {
     static int cached = 0;
@@ -812,20 +813,42 @@ static int dt_max_clusters() {
     attr[0].val.clusterDim.x = DEC_CLUSTER; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
     cfg.gridDim = dim3(DEC_CLUSTER, 64, 1); cfg.blockDim = dim3(ATT_THREADS); cfg.dynamicSmemBytes = dt_smem<HD, KEYS>();
-    if (set_smem(decode_attention_tma_kernel<HD, KEYS>, cfg.dynamicSmemBytes, "decode_attention_tma")) return -1;
+    if (set_smem(decode_attention_tma_kernel<HD, KEYS, DEC_CLUSTER>, cfg.dynamicSmemBytes, "decode_attention_tma")) return -1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, decode_attention_tma_kernel<HD, KEYS>, &cfg) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (cudaOccupancyMaxActiveClusters(&n, decode_attention_tma_kernel<HD, KEYS, DEC_CLUSTER>, &cfg) != cudaSuccess) { cudaGetLastError(); return -1; }
     cached = n > 0 ? n : -1;
     return cached;
 }
 
-template <int HD, int KEYS>
-static cudaError_t dt_launch(dim3 grid, cudaStream_t stream, const CUtensorMap& mkv, const void* q, void* out, const int* tables,
-                             const int* tok_seg, const int* pos, int* status, int n_heads, int n_kv_heads, int q_blocks, int page_size,
-                             int box_rows, int max_blocks, int window, float scale2) {
-    if (set_smem(decode_attention_tma_kernel<HD, KEYS>, dt_smem<HD, KEYS>(), "decode_attention_tma")) return cudaErrorInvalidValue;
-    return launch_cluster(decode_attention_tma_kernel<HD, KEYS>, grid, dim3(ATT_THREADS), dt_smem<HD, KEYS>(), stream, mkv, (const bf16*)q,
-                          (bf16*)out, tables, tok_seg, pos, status, n_heads, n_kv_heads, q_blocks, page_size, box_rows, max_blocks, window, scale2);
+struct DtArgs {
+    const CUtensorMap* mkv; const void* q; void* out; const int* tables; const int* tok_seg; const int* pos; int* status;
+    int n_tokens, n_heads, n_kv_heads, q_blocks, page_size, box_rows, max_blocks, window; float scale2; cudaStream_t stream;
+};
+
+template <int HD, int KEYS, int CL>
+static cudaError_t dt_launch(const DtArgs& a) {
+    if (set_smem(decode_attention_tma_kernel<HD, KEYS, CL>, dt_smem<HD, KEYS>(), "decode_attention_tma")) return cudaErrorInvalidValue;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CL; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cfg.gridDim = dim3(CL, a.n_kv_heads * a.q_blocks, a.n_tokens); cfg.blockDim = dim3(ATT_THREADS);
+    cfg.dynamicSmemBytes = dt_smem<HD, KEYS>(); cfg.stream = a.stream;
+    return cudaLaunchKernelEx(&cfg, decode_attention_tma_kernel<HD, KEYS, CL>, *a.mkv, (const bf16*)a.q, (bf16*)a.out, a.tables,
+                              a.tok_seg, a.pos, a.status, a.n_heads, a.n_kv_heads, a.q_blocks, a.page_size, a.box_rows,
+                              a.max_blocks, a.window, a.scale2);
+}
+template <int HD>
+static cudaError_t dt_dispatch(const DtArgs& a, int keys, int cl) {
+    if (keys == 32) return dt_launch<HD, 32, DEC_CLUSTER>(a);
+    switch (cl) {
+        case 8: return dt_launch<HD, 16, 8>(a);
+        case 4: return dt_launch<HD, 16, 4>(a);
+        case 2: return dt_launch<HD, 16, 2>(a);
+        default: return dt_launch<HD, 16, 1>(a);
+    }
 }
 
 ZI_EXPORT int zi_decode_attention_tma(const void* q, const void* cache, void* out, const int* tables, const int* tok_seg,
@@ -842,20 +865,30 @@ ZI_EXPORT int zi_decode_attention_tma(const void* q, const void* cache, void* ou
     const int group = n_heads / n_kv_heads, q_blocks = (group + 15) / 16;
     if (n_kv_heads * q_blocks > 65535) return zi_fail("decode_attention_tma: too many head blocks for one launch");
     if (tc_init()) return 1;
-    // tiles of 32 keys while all clusters of the step fit on the device at once, else tiles of 16
-    const long long clusters = (long long)n_kv_heads * q_blocks * n_tokens;
+    // A (request, key/value head) is one unit of work.  Few units: clusters of eight blocks share a unit's keys, in
+    // tiles of 32 keys while all clusters fit on the device at once, else of 16 (two blocks to an SM).  More units
+    // fill the device by themselves: the cluster is then the largest of 8, 4, 2, 1 with which all blocks still run
+    // at once, so that a block's fixed cost (start, merge of its warps, cluster exchange) is spread over more keys.
+    // Measured at 1,100 cached tokens, 4 key/value heads: 48 requests 47 us with clusters of 8, 25 us with single
+    // blocks; 16 requests 15 us with 8, 10 us with 4.
+    const long long units = (long long)n_kv_heads * q_blocks * n_tokens;
     const int fit32 = head_dim == 128 ? dt_max_clusters<128, 32>() : dt_max_clusters<64, 32>();
-    const int keys = (fit32 > 0 && clusters <= fit32) ? 32 : 16;
+    const int keys = (fit32 > 0 && units <= fit32) ? 32 : 16;
+    static int slots = 0;                                         // blocks of the 16-key form that run at once: two to an SM
+    if (slots == 0) {
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        slots = 2 * (sms > 0 ? sms : 1);
+    }
+    int cl = 8;
+    while (cl > 1 && units * cl > slots) cl >>= 1;
     const int box_rows = page_size < keys ? page_size : keys;
     CUtensorMap mkv;
     if (tc_map_kv_pages(&mkv, cache, head_dim, page_size, n_kv_heads, n_pages, page_stride, kv_stride, box_rows)) return 1;
-    dim3 grid(DEC_CLUSTER, n_kv_heads * q_blocks, n_tokens);
-    const float scale2 = scale * LOG2E;
-    cudaError_t e;
-    if (head_dim == 128 && keys == 32) e = dt_launch<128, 32>(grid, stream, mkv, q, out, tables, tok_seg, pos, status, n_heads, n_kv_heads, q_blocks, page_size, box_rows, max_blocks, window, scale2);
-    else if (head_dim == 128) e = dt_launch<128, 16>(grid, stream, mkv, q, out, tables, tok_seg, pos, status, n_heads, n_kv_heads, q_blocks, page_size, box_rows, max_blocks, window, scale2);
-    else if (keys == 32) e = dt_launch<64, 32>(grid, stream, mkv, q, out, tables, tok_seg, pos, status, n_heads, n_kv_heads, q_blocks, page_size, box_rows, max_blocks, window, scale2);
-    else e = dt_launch<64, 16>(grid, stream, mkv, q, out, tables, tok_seg, pos, status, n_heads, n_kv_heads, q_blocks, page_size, box_rows, max_blocks, window, scale2);
+    DtArgs a = {&mkv, q, out, tables, tok_seg, pos, status, n_tokens, n_heads, n_kv_heads, q_blocks, page_size, box_rows,
+                max_blocks, window, scale * LOG2E, stream};
+    const cudaError_t e = head_dim == 128 ? dt_dispatch<128>(a, keys, cl) : dt_dispatch<64>(a, keys, cl);
     if (e != cudaSuccess) { cudaGetLastError(); return zi_fail("decode_attention_tma: launch failed: %s", cudaGetErrorString(e)); }
     return zi_check_launch("decode_attention_tma");
 }

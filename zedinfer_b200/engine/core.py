@@ -8,6 +8,7 @@ and the benchmark all go through this one function.
 """
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -122,9 +123,20 @@ def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache]
     width = table_width
     n_groups = len(cache.groups)
     n_want = sum(len(e.want) for e in entries)
+    # Single-token entries at the head of a step that also holds longer ones (decoding requests beside a prompt
+    # portion) are left to the decode attention kernel; the padding tokens stand right behind them, so that their
+    # number depends on the step's counts alone.  Attention tiles cover the rest.
+    lead_real = lead = 0
+    if any(len(e.tokens) != 1 for e in entries):
+        while len(entries[lead_real].tokens) == 1:
+            lead_real += 1
+        lead = lead_real + pad_segments
     # layout: ids | pos | tok_seg | want rows | slots | attention tiles | tables[g]...
     tile_rows = ops.PREFILL_TILE_ROWS
-    n_tiles = sum(-(-len(e.tokens) // tile_rows) for e in entries) + pad_segments
+    if lead:
+        n_tiles = sum(-(-len(e.tokens) // tile_rows) for e in entries[lead_real:])
+    else:
+        n_tiles = sum(-(-len(e.tokens) // tile_rows) for e in entries) + pad_segments
     off_ids, off_pos, off_seg = 0, n_tok, 2 * n_tok
     off_want = 3 * n_tok
     off_slots = off_want + n_want
@@ -135,9 +147,27 @@ def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache]
     seg_start, seg_len, seg_pos0, slots = [], [], [], []
     t = 0
     w = 0
+    s = 0
     max_kv = 0
     n_tile_done = 0
-    for s, (e, rc) in enumerate(zip(entries, rcs)):
+    scratch = cache.scratch_page if cache.groups else 0
+
+    def pad_tokens(t, s, n_tile_done):           # padding: one token each at position 0 of the scratch page
+        for _ in range(pad_segments):
+            host[off_seg + t] = s
+            host[off_slots + s] = -1
+            for g in range(n_groups):
+                host[off_tab + (g * n_seg + s) * width] = scratch
+            if not lead:
+                host[off_tiles + 3 * n_tile_done: off_tiles + 3 * n_tile_done + 3] = (t, 1, s)
+                n_tile_done += 1
+            seg_start.append(t), seg_len.append(1), seg_pos0.append(0), slots.append(-1)
+            t, s = t + 1, s + 1
+        return t, s, n_tile_done
+
+    for i, (e, rc) in enumerate(zip(entries, rcs)):
+        if lead and i == lead_real:
+            t, s, n_tile_done = pad_tokens(t, s, n_tile_done)
         toks = np.asarray(e.tokens, dtype=np.int64)
         k = toks.size
         if k and (toks.min() < 0 or toks.max() >= vocab):
@@ -155,22 +185,16 @@ def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache]
             tab = rc.tables[g]
             base = off_tab + (g * n_seg + s) * width
             host[base: base + len(tab)] = tab
-        for q0 in range(0, k, tile_rows):
-            host[off_tiles + 3 * n_tile_done: off_tiles + 3 * n_tile_done + 3] = (t + q0, min(tile_rows, k - q0), s)
-            n_tile_done += 1
+        if not (lead and i < lead_real):
+            for q0 in range(0, k, tile_rows):
+                host[off_tiles + 3 * n_tile_done: off_tiles + 3 * n_tile_done + 3] = (t + q0, min(tile_rows, k - q0), s)
+                n_tile_done += 1
         seg_start.append(t), seg_len.append(k), seg_pos0.append(rc.length), slots.append(rc.slot)
         max_kv = max(max_kv, rc.length + k)
         t += k
-    scratch = cache.scratch_page if cache.groups else 0
-    for s in range(len(entries), n_seg):         # padding: one token at position 0 of the scratch page
-        host[off_seg + t] = s
-        host[off_slots + s] = -1
-        for g in range(n_groups):
-            host[off_tab + (g * n_seg + s) * width] = scratch
-        host[off_tiles + 3 * n_tile_done: off_tiles + 3 * n_tile_done + 3] = (t, 1, s)
-        n_tile_done += 1
-        seg_start.append(t), seg_len.append(1), seg_pos0.append(0), slots.append(-1)
-        t += 1
+        s += 1
+    if not lead:
+        t, s, n_tile_done = pad_tokens(t, s, n_tile_done)
     if into is None:
         dev = ring.stage(host, device)
     else:
@@ -187,10 +211,19 @@ def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache]
         seg_start_host=seg_start, seg_len_host=seg_len, seg_pos0_host=seg_pos0, slots_host=slots,
         decode_only=all(k == 1 for k in seg_len), max_kv_len=max(max_kv, 1))
     ctx.extras["attn_tiles"] = dev[off_tiles: off_tiles + 3 * n_tiles].view(n_tiles, 3)
+    ctx.extras["leading_singles"] = lead
     ctx.extras["descriptor_len"] = total
     want = dev[off_want: off_want + n_want] if n_want else None
     return ctx, want
 
+
+
+class _SeenStep:
+    """What is known of a step shape that has no graph: appearances, and the first one's timing."""
+    __slots__ = ("count", "host_ms", "events", "gpu_bound")
+
+    def __init__(self):
+        self.count, self.host_ms, self.events, self.gpu_bound = 0, 0.0, None, None
 
 
 class EngineCore:
@@ -247,7 +280,7 @@ class EngineCore:
         self.max_requests = int(max_requests)
         self._decode_graphs: Dict[int, "DecodeGraph"] = {}
         self._step_graphs: Dict[tuple, "StepGraph"] = {}
-        self._step_seen: Dict[tuple, int] = {}
+        self._step_seen: Dict[tuple, _SeenStep] = {}
         self._graph_pool = None
         self.capture_safe = self.model.capture_safe()
 
@@ -280,7 +313,8 @@ class EngineCore:
     # their size.  Every launch of such a step depends on the step's counts alone, so a step whose counts come back
     # (the full-size portions of a long prompt, the same portion beside the same number of decoding requests) is
     # captured in a CUDA graph at its second appearance and replayed from then on.
-    MAX_STEP_GRAPHS = 12
+    MAX_STEP_GRAPHS = 32
+    GPU_BOUND_RATIO = 1.25          # device time over host launch time from which a step shape is left eager
 
     def _step_padding(self, entries: Sequence[StepEntry]) -> int:
         """Single-token segments (decoding requests beside a prompt portion) are padded to a power of two with
@@ -294,12 +328,25 @@ class EngineCore:
         return bucket - singles
 
     def _step_signature(self, entries: Sequence[StepEntry], pad: int) -> tuple:
+        """The counts that every launch of the step depends on: tokens, segments, the single-token entries at its
+        head (padding included) that the decode attention kernel takes, attention tiles of the rest, wanted rows."""
         rows = ops.PREFILL_TILE_ROWS
-        return (sum(len(e.tokens) for e in entries) + pad, len(entries) + pad,
-                sum(-(-len(e.tokens) // rows) for e in entries) + pad, sum(len(e.want) for e in entries),
-                all(len(e.tokens) == 1 for e in entries))
+        lens = [len(e.tokens) for e in entries]
+        lead = 0
+        if any(k != 1 for k in lens):
+            while lens[lead] == 1:
+                lead += 1
+            tiles = sum(-(-k // rows) for k in lens[lead:])
+            lead += pad
+        else:
+            tiles = len(lens) + pad
+        return (sum(lens) + pad, len(lens) + pad, lead, tiles, sum(len(e.want) for e in entries), lead == 0 and all(k == 1 for k in lens))
 
     def _eager_or_captured(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache]) -> Optional[torch.Tensor]:
+        """A step whose counts recur is replayed as a CUDA graph, if that can gain anything: its first appearance
+        runs eagerly between two events and with a clock on the host.  If the GPU took clearly longer over it than
+        the host took to launch it, the host keeps ahead of the GPU anyway, and the shape stays eager for good (a
+        capture costs several eager launches).  Else it is captured at its second appearance."""
         from .decode_graph import StepGraph
         if not (self.cuda_graphs and self.capture_safe):
             ctx, want = self.build_context(entries, rcs)
@@ -308,18 +355,37 @@ class EngineCore:
         sig = self._step_signature(entries, pad)
         g = self._step_graphs.pop(sig, None)
         if g is None:
-            seen = self._step_seen.get(sig, 0) + 1
-            self._step_seen[sig] = seen
-            if seen < 2:
+            seen = self._step_seen.get(sig)
+            if seen is None:
                 if len(self._step_seen) > 4096:
                     self._step_seen.clear()
+                seen = self._step_seen[sig] = _SeenStep()
+            if seen.gpu_bound is None and seen.events is not None and seen.events[1].query():
+                seen.gpu_bound = seen.events[0].elapsed_time(seen.events[1]) > self.GPU_BOUND_RATIO * seen.host_ms
+                seen.events = None
+            if seen.count == 0 or seen.gpu_bound or (seen.gpu_bound is None and seen.events is not None):
+                first = seen.count == 0
+                seen.count += 1
+                if first:
+                    seen.events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                    seen.events[0].record()
+                    t0 = time.perf_counter()
                 ctx, want = self.build_context(entries, rcs, pad_segments=pad)     # the shape a capture would have
-                return self.model.forward(ctx, self.views, want)
+                logits = self.model.forward(ctx, self.views, want)
+                if first:
+                    seen.host_ms = (time.perf_counter() - t0) * 1000.0
+                    seen.events[1].record()
+                return logits
             while len(self._step_graphs) >= self.MAX_STEP_GRAPHS:                   # the least recently used one goes
                 del self._step_graphs[next(iter(self._step_graphs))]
             g = StepGraph(self, entries, rcs, pad)
         self._step_graphs[sig] = g                                                  # most recently used: last
         return g.run(entries, rcs)
+
+    def check_kernels(self) -> None:
+        """Wait for the device and raise if a kernel with bounded waits gave up since the last check.  Steps do not
+        wait for this themselves: the word travels with the sampled tokens, and whoever reads logits calls this."""
+        ops.raise_if_tcgen05_failed(self.device)
 
     def prepare(self, entries: Sequence[StepEntry]) -> List[RequestCache]:
         """Open new requests and make sure every entry has pages for its tokens; all or nothing."""
@@ -396,7 +462,6 @@ class EngineCore:
             logits = self.decode_graph(len(entries)).run(entries, rcs)
         else:
             logits = self._eager_or_captured(entries, rcs)
-            ops.raise_if_tcgen05_failed(self.device)
         for e, rc in zip(entries, rcs):
             self.cache.commit(rc, rc.length + len(e.tokens))
         return logits

@@ -50,12 +50,20 @@ class InferenceEngine:
 
     @classmethod
     def create(cls, model_path: str, scheduler_config: Optional[SchedulerConfig] = None, dtype="bfloat16",
-               device="cuda:0") -> "InferenceEngine":
+               device="cuda:0", random_seed: Optional[int] = None) -> "InferenceEngine":
+        """``model_path``: a folder with config.json and *.safetensors.  With ``random_seed`` it may be a config.json
+        alone (or a folder that holds one): the weights are then drawn on the device from that seed, which is how
+        shapes too large to write out as a folder are measured."""
         cfg = scheduler_config or SchedulerConfig()
         cfg.validate()
-        core = EngineCore(model_path, dtype, page_size=cfg.kv_block_size, num_pages=cfg.num_kv_pages,
-                          gpu_memory_utilization=cfg.gpu_memory_utilization, max_requests=cfg.max_batch_requests,
-                          max_seq_len=cfg.max_seq_len, device=device)
+        sizes = dict(page_size=cfg.kv_block_size, num_pages=cfg.num_kv_pages,
+                     gpu_memory_utilization=cfg.gpu_memory_utilization, max_requests=cfg.max_batch_requests,
+                     max_seq_len=cfg.max_seq_len, device=device)
+        if random_seed is None:
+            core = EngineCore(model_path, dtype, **sizes)
+        else:
+            from ..config.registry import read_config_json
+            core = EngineCore(None, dtype, config=read_config_json(model_path), random_seed=int(random_seed), **sizes)
         return cls(core, cfg)
 
     # ---- intake -----------------------------------------------------------------------------

@@ -65,10 +65,12 @@ def main(argv: Optional[List[str]] = None) -> int:
         logits = core.step(entries) if entries else None
         if logits is not None:
             arr = logits.to("cpu").numpy().astype("<f4", copy=False)
+            core.check_kernels()
             tmp = os.path.join(args.out, f".{step}.f32.tmp")
             arr.tofile(tmp)
             os.replace(tmp, os.path.join(args.out, f"{step}.f32"))
         else:
+            core.check_kernels()
             torch.cuda.synchronize()
         for rid in obj.get("end", []):
             core.end(rid)

@@ -469,8 +469,8 @@ def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv
     """Attention of a step's tokens over the cache (``cache`` is a CallCacheView, ``ctx`` a StepContext).
 
     Picks a kernel by dtype and by the shape of the step; all of them compute the same function.
-    bfloat16 with head_dim 64 or 128 runs on the tensor cores: decode-only steps on the cluster decode kernel,
-    anything else on the tcgen05 prefill kernel (pages of 8..128 tokens) or the ``mma.sync`` prefill kernel (other
+    bfloat16 with head_dim 64 or 128 runs on the tensor cores: decode-only steps, and the single tokens at the head
+    of a mixed step, on the cluster decode kernel, anything else on the tcgen05 prefill kernel (pages of 8..128 tokens) or the ``mma.sync`` prefill kernel (other
     page sizes); float32 and other head sizes on the general kernel.
     """
     tables = ctx.tables[cache.group]
@@ -485,6 +485,11 @@ def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv
                              cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
             return
         tiles = ctx.extras.get("attn_tiles")
+        lead = ctx.extras.get("leading_singles", 0) if tiles is not None else 0
+        if lead:                                  # decoding requests beside a prompt portion: their own kernel
+            fn = decode_attention_tma if tcgen05_attention_ok(head_dim, cache.page_size) else decode_attention
+            fn(q[:lead], cache.tensor, out[:lead], tables, ctx.tok_seg[:lead], ctx.positions[:lead], n_heads, n_kv_heads,
+               head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
         if tiles is not None and tcgen05_attention_ok(head_dim, cache.page_size):
             prefill_attention_tcgen05(q, cache.tensor, out, tables, tiles, ctx.positions, n_heads, n_kv_heads, head_dim,
                                       cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
