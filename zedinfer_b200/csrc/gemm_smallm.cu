@@ -68,14 +68,29 @@ __device__ __forceinline__ void accumulate_rows(float (&acc)[NT][4], const bf16*
             b[u] = ldg_stream(w1 + k);
         }
         if (!waited) { pdl_wait(); waited = true; }
+        if constexpr (NT == 1) {
+            // The activations of the whole batch are asked for before the first product needs one: a load that
+            // stands only where its value is used puts an L2 round trip in front of every pair of products, during
+            // which the warp has no weight load in flight.  Measured at 8 rows: the 7B-class gate/up product
+            // 50 -> 45 us, its down product 35 -> 29 us.  (With 16 tokens the same change made it slower.)
+            uint4 x[GS_UNROLL];
 #pragma unroll
-        for (int u = 0; u < GS_UNROLL; ++u) {
-            const int k = (s + u * GS_WARPS) * 32;
+            for (int u = 0; u < GS_UNROLL; ++u) x[u] = ld_dep16(xp[0] + (s + u * GS_WARPS) * 32);
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const uint4 x = ld_dep16(xp[nt] + k);
-                mma_bf16_16816(acc[nt], a[u].x, b[u].x, a[u].y, b[u].y, x.x, x.y);
-                mma_bf16_16816(acc[nt], a[u].z, b[u].z, a[u].w, b[u].w, x.z, x.w);
+            for (int u = 0; u < GS_UNROLL; ++u) {
+                mma_bf16_16816(acc[0], a[u].x, b[u].x, a[u].y, b[u].y, x[u].x, x[u].y);
+                mma_bf16_16816(acc[0], a[u].z, b[u].z, a[u].w, b[u].w, x[u].z, x[u].w);
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < GS_UNROLL; ++u) {
+                const int k = (s + u * GS_WARPS) * 32;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const uint4 x = ld_dep16(xp[nt] + k);
+                    mma_bf16_16816(acc[nt], a[u].x, b[u].x, a[u].y, b[u].y, x.x, x.y);
+                    mma_bf16_16816(acc[nt], a[u].z, b[u].z, a[u].w, b[u].w, x.z, x.w);
+                }
             }
         }
     }

@@ -113,7 +113,7 @@ def rope_table(pos: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> 
 
 def can_fuse_rope_product(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], cache: Optional[torch.Tensor]) -> bool:
     """The q/k/v product of a decode step can take rotation and cache append into its epilogue."""
-    return (_small_m_ok(x, w) and (bias is None or bias.dtype == torch.bfloat16) and cache is not None
+    return (_small_m_ok(x, w, fused=True) and (bias is None or bias.dtype == torch.bfloat16) and cache is not None
             and cache.dtype == torch.bfloat16)
 
 
@@ -171,7 +171,17 @@ def gemm_nt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
                     c_ll(out.stride(0)), stream())
 
 
-def _small_m_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+SMALL_M_WIDE_ELEMENTS = 16 << 20     # weight elements up to which 9..16 rows stay on the streaming kernel
+
+
+def _small_m_ok(x: torch.Tensor, w: torch.Tensor, fused: bool = False) -> bool:
+    """The weight-streaming kernel takes this product.  Up to 8 rows it is the fastest form measured for every
+    shape tried (1.5B- to 32B-class layers, at or above the library's rate); with 9 to 16 rows it reads the
+    activations twice and falls behind the library on large weights (7B-class down product: 36 us against 30),
+    so it keeps those only for weights up to ``SMALL_M_WIDE_ELEMENTS`` elements, twice that where it saves a
+    kernel by its epilogue (``fused``: activation, or rotation and cache append)."""
+    if x.shape[0] > 8 and w.shape[0] * w.shape[1] > SMALL_M_WIDE_ELEMENTS * (2 if fused else 1):
+        return False
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= SMALL_M_ROWS
             and x.shape[1] % 32 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0
             and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
@@ -327,7 +337,7 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, bias: Optional[tor
     elementwise kernel.
     """
     need_cuda(x, w_gate_up, bias, out)
-    if bias is None and _small_m_ok(x, w_gate_up):
+    if bias is None and _small_m_ok(x, w_gate_up, fused=True):
         gemm_smallm(x, w_gate_up, None, out, silu_mul=True)
         return
     if bias is None and x.shape[0] >= TC_FUSED_MIN_ROWS and out.dtype == torch.bfloat16 and _tc_ok(x, w_gate_up, None, out):
