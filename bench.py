@@ -289,6 +289,7 @@ def main():
         for b in (1, 64):
             points[f"decode_b{b}"] = round(measure_decode_device(core, cfg, b, min(steps, 128), warmup)["tok_s"], 1)
     clocks.stop()
+    core.check_kernels()            # a bounded wait that ran out inside a kernel would make the numbers void
 
     step_bytes = weight_bytes_per_step(cfg, args.layers) + args.batch * dev["mean_ctx"] * kv_bytes_per_token(cfg, args.layers)
     achieved = step_bytes / (dev["ms"] * 1e-3) / 1e9

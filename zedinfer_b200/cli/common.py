@@ -42,9 +42,14 @@ def scheduler_config_from(args) -> SchedulerConfig:
 
 
 def create_engine(args):
+    import sys
     from ..engine import InferenceEngine
-    return InferenceEngine.create(args.model_path, scheduler_config_from(args), dtype=args.dtype,
-                                  random_seed=args.random_weights)
+    engine = InferenceEngine.create(args.model_path, scheduler_config_from(args), dtype=args.dtype,
+                                    random_seed=args.random_weights)
+    st = engine.cache_stats()
+    print(f"[engine] cache: {st['pages_per_group']} pages of {st['page_size']} tokens ({st['pages_per_group'] * st['page_size']} "
+          f"tokens, {st['pool_bytes'] / 2**30:.2f} GiB)", file=sys.stderr)
+    return engine
 
 
 def parse_ids(text: str):

@@ -262,6 +262,7 @@ class EngineCore:
         if num_pages is None and max_tokens is not None:
             num_pages = (int(max_tokens) + self.page_size - 1) // self.page_size
         if num_pages is None:
+            torch.cuda.empty_cache()        # what loading freed again (tensors stacked into one) is free for the pool
             free, total = torch.cuda.mem_get_info(self.device)
             budget = int(total * gpu_memory_utilization) - (total - free)
             # leave room for the activations of a step
@@ -385,7 +386,10 @@ class EngineCore:
     def check_kernels(self) -> None:
         """Wait for the device and raise if a kernel with bounded waits gave up since the last check.  Steps do not
         wait for this themselves: the word travels with the sampled tokens, and whoever reads logits calls this."""
-        ops.raise_if_tcgen05_failed(self.device)
+        ops._tc_launched.pop(self.device, None)
+        code = ops.tcgen05_status(self.device)          # reads the word: waits for everything launched so far
+        if code:
+            raise ops.KernelError(f"a bounded wait ran out inside a kernel (code {code}); the step's output is not valid")
 
     def prepare(self, entries: Sequence[StepEntry]) -> List[RequestCache]:
         """Open new requests and make sure every entry has pages for its tokens; all or nothing."""

@@ -193,12 +193,13 @@ class InferenceEngine:
                 ops.argmax(logits, out)
                 tok = int(out.item())
             end.record()
-            torch.cuda.synchronize()
+            self.core.check_kernels()
         finally:
             self.core.end(rid)
         return start.elapsed_time(mid), mid.elapsed_time(end)
 
     def cache_stats(self) -> dict:
         c = self.core.cache
-        return {"page_size": c.page_size, "pages_per_group": c.num_pages, "free_pages": c.free_pages(),
+        pool = sum(g.tensor.numel() * g.tensor.element_size() for g in c.groups if g.tensor is not None)
+        return {"page_size": c.page_size, "pages_per_group": c.num_pages, "pool_bytes": pool, "free_pages": c.free_pages(),
                 "live_requests": c.num_live, "groups": len(c.groups), "preemptions": self.scheduler.num_preemptions}
