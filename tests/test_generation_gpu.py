@@ -238,3 +238,32 @@ def test_trace_run_program(models, tmp_path, dtype):
                 row += 1
             progress[e["id"]] = base + len(e["tokens"])
     assert worst < (2e-4 if dtype == "float32" else 6e-2), worst
+
+
+# ---- the command-line programs -------------------------------------------------------------------------
+def test_ping_prints_the_plain_greedy_tokens(models, capsys):
+    from zedinfer_b200.cli import ping
+    cfg, _ = tiny.CONFIGS["B"]
+    prompt = [3, 141, 59, 26, 535, 89, 79]
+    rc = ping.main([models["B"], "--dtype", "float32", "--prompt", " ".join(map(str, prompt)), "--max-new-tokens", "6",
+                    "--kv-pages", "16", "--kv-block-size", "8"])
+    assert rc == 0
+    printed = capsys.readouterr().out.strip().splitlines()[-1]
+    assert [int(t) for t in printed.split()] == plain_greedy(models["B"], prompt, 6)
+
+
+def test_bench_programs_run_from_a_bare_config_with_weights_drawn_on_the_device(tmp_path, capsys):
+    """--random-weights: the model path is a config.json alone; batch_bench draws prompt lengths from a range and
+    reports steps, first-token times and preemptions."""
+    from zedinfer_b200.cli import batch_bench, bench
+    cfg, _ = tiny.CONFIGS["D"]
+    path = tmp_path / "config.json"
+    path.write_text(json.dumps(cfg))
+    common = [str(path), "--random-weights", "7", "--kv-pages", "40", "--max-seq-len", "128"]
+    assert bench.main(common + ["-p", "24", "-d", "5", "-r", "1"]) == 0
+    out = capsys.readouterr().out
+    assert "Prefill:" in out and "Decode :" in out
+    assert batch_bench.main(common + ["-b", "5", "-p", "6", "--prefill-len-max", "40", "-d", "7", "-r", "1",
+                                      "--warmup-rounds", "1", "--max-prefill-tokens", "16"]) == 0
+    out = capsys.readouterr().out
+    assert "5 requests, 35 tokens generated" in out and "Preemptions" in out and "First token" in out
