@@ -94,15 +94,41 @@ __device__ __forceinline__ void accumulate_rows(float (&acc)[NT][4], const bf16*
             }
         }
     }
-    for (; s < steps; s += GS_WARPS) {
-        const int k = s * 32;
-        const uint4 a = ldg_stream(w0 + k), b = ldg_stream(w1 + k);
-        if (!waited) { pdl_wait(); waited = true; }
+    if constexpr (NT == 1) {
+        // the up to GS_UNROLL - 1 steps that are left go as one batch too: one trip to memory, not one per step
+        if (s < steps) {
+            uint4 a[GS_UNROLL - 1], b[GS_UNROLL - 1], x[GS_UNROLL - 1];
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            const uint4 x = ld_dep16(xp[nt] + k);
-            mma_bf16_16816(acc[nt], a.x, b.x, a.y, b.y, x.x, x.y);
-            mma_bf16_16816(acc[nt], a.z, b.z, a.w, b.w, x.z, x.w);
+            for (int u = 0; u < GS_UNROLL - 1; ++u) {
+                if (s + u * GS_WARPS < steps) {
+                    const int k = (s + u * GS_WARPS) * 32;
+                    a[u] = ldg_stream(w0 + k);
+                    b[u] = ldg_stream(w1 + k);
+                }
+            }
+            if (!waited) { pdl_wait(); waited = true; }
+#pragma unroll
+            for (int u = 0; u < GS_UNROLL - 1; ++u)
+                if (s + u * GS_WARPS < steps) x[u] = ld_dep16(xp[0] + (s + u * GS_WARPS) * 32);
+#pragma unroll
+            for (int u = 0; u < GS_UNROLL - 1; ++u) {
+                if (s + u * GS_WARPS < steps) {
+                    mma_bf16_16816(acc[0], a[u].x, b[u].x, a[u].y, b[u].y, x[u].x, x[u].y);
+                    mma_bf16_16816(acc[0], a[u].z, b[u].z, a[u].w, b[u].w, x[u].z, x[u].w);
+                }
+            }
+        }
+    } else {
+        for (; s < steps; s += GS_WARPS) {
+            const int k = s * 32;
+            const uint4 a = ldg_stream(w0 + k), b = ldg_stream(w1 + k);
+            if (!waited) { pdl_wait(); waited = true; }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint4 x = ld_dep16(xp[nt] + k);
+                mma_bf16_16816(acc[nt], a.x, b.x, a.y, b.y, x.x, x.y);
+                mma_bf16_16816(acc[nt], a.z, b.z, a.w, b.w, x.z, x.w);
+            }
         }
     }
     if (!waited) pdl_wait();
@@ -114,7 +140,7 @@ __device__ __forceinline__ void accumulate_rows(float (&acc)[NT][4], const bf16*
 // pairs weight and activation of the same k.
 
 template <int NT, typename TC, bool SILU_MUL>
-__global__ void __launch_bounds__(GS_THREADS)
+__global__ void __launch_bounds__(GS_THREADS, NT == 1 ? 4 : 3)
 gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const bf16* __restrict__ bias,
                    TC* __restrict__ C, float* __restrict__ part, int* __restrict__ counters, int M, int N, int K,
                    long long ldx, long long ldw, long long ldc) {
@@ -275,7 +301,7 @@ struct RopeOut {
 };
 
 template <int NT>
-__global__ void __launch_bounds__(GS_THREADS)
+__global__ void __launch_bounds__(GS_THREADS, NT == 1 ? 4 : 3)
 gemm_smallm_rope_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const bf16* __restrict__ bias,
                         const RopeOut ro, int M, int K, long long ldx, long long ldw) {
     __shared__ float red[GS_WARPS][16][NT * 8 + 1];
