@@ -241,6 +241,24 @@ def measure_decode_e2e(core, cfg, batch, steps, warmup, run_ahead=True):
     return {"tok_s": batch * steps / dt, "ms": dt * 1000.0 / steps, "h2d": int(h2d), "d2h": 4 * batch}
 
 
+def measure_head(core, cfg, rows, reps=20):
+    """Milliseconds of the output head's product alone at `rows` rows (its weight is larger than L2, so every call
+    streams it from memory): what the step's time and bytes are reduced by for the figure without the head."""
+    import torch
+    x = (torch.randn(rows, cfg["hidden_size"], device=core.device) * 0.5).to(torch.bfloat16)
+    logits = torch.empty(rows, cfg["vocab_size"], dtype=torch.float32, device=core.device)
+    for _ in range(3):
+        core.model.head.forward(x, logits)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(reps):
+        core.model.head.forward(x, logits)
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--gpus", type=int, default=1)
@@ -288,11 +306,14 @@ def main():
     if not args.no_points:
         for b in (1, 64):
             points[f"decode_b{b}"] = round(measure_decode_device(core, cfg, b, min(steps, 128), warmup)["tok_s"], 1)
+    head_ms = measure_head(core, cfg, args.batch)
     clocks.stop()
     core.check_kernels()            # a bounded wait that ran out inside a kernel would make the numbers void
 
     step_bytes = weight_bytes_per_step(cfg, args.layers) + args.batch * dev["mean_ctx"] * kv_bytes_per_token(cfg, args.layers)
     achieved = step_bytes / (dev["ms"] * 1e-3) / 1e9
+    head_bytes = 2 * cfg["vocab_size"] * cfg["hidden_size"]
+    layers_achieved = (step_bytes - head_bytes) / (max(dev["ms"] - head_ms, 1e-6) * 1e-3) / 1e9
     line = {
         "metric": "decode_tokens_per_s", "value": round(dev["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1,
         "steps": steps, "warmup": warmup, "ms_per_step": round(dev["ms"], 4), "higher_is_better": True,
@@ -313,7 +334,9 @@ def main():
         "gpu_launches": dev["launches"],
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+                     "frac": round(achieved / pk["hbm_gbs"], 4),
+                     "without_head": {"head_ms": round(head_ms, 4), "achieved": round(layers_achieved, 1),
+                                      "frac": round(layers_achieved / pk["hbm_gbs"], 4)}},
         "points": points,
     }
     print(json.dumps(line))
