@@ -267,3 +267,18 @@ def test_bench_programs_run_from_a_bare_config_with_weights_drawn_on_the_device(
                                       "--warmup-rounds", "1", "--max-prefill-tokens", "16"]) == 0
     out = capsys.readouterr().out
     assert "5 requests, 35 tokens generated" in out and "Preemptions" in out and "First token" in out
+
+
+def test_consistency_program_finds_float32_bit_equal_however_it_is_cut(tmp_path, capsys):
+    """bin/zedinfer-consistency on a tiny configuration: whole, tail decoded, changing portions and mixed with page
+    reuse; it returns 0 only if every float32 logit is the same bit pattern in all four."""
+    from zedinfer_b200.cli import consistency
+    cfg, _ = tiny.CONFIGS["D"]
+    path = tmp_path / "config.json"
+    path.write_text(json.dumps(dict(cfg, max_position_embeddings=512)))
+    assert consistency.main([str(path), "--random-weights", "5", "--tokens", "150", "--requests", "6"]) == 0
+    lines = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
+    assert {(l["dtype"], l["mode"]) for l in lines} >= {("float32", "tail"), ("float32", "portions"), ("float32", "mixed"),
+                                                        ("bfloat16", "mixed"), ("bfloat16", "whole")}
+    assert all(l["values_not_bit_equal"] == 0 for l in lines if l["dtype"] == "float32")
+    assert all(l["worst_abs_diff"] < 6e-2 for l in lines if l["dtype"] == "bfloat16")
