@@ -124,7 +124,7 @@ def test_top_k_one_is_greedy_and_stop_token_ends(models):
     engine.scheduler.stop_token_ids = frozenset([greedy[2]])
     r = engine.generate_tokens(prompt, GenerationConfig(max_new_tokens=6))
     first = greedy.index(greedy[2])
-    assert r.finish_reason == "stop" and r.output_ids == greedy[:first + 1]
+    assert r.finish_reason == "stop" and r.output_ids == greedy[:first + 1], (r.finish_reason, r.error, r.output_ids)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -282,3 +282,37 @@ def test_consistency_program_finds_float32_bit_equal_however_it_is_cut(tmp_path,
                                                         ("bfloat16", "mixed"), ("bfloat16", "whole")}
     assert all(l["values_not_bit_equal"] == 0 for l in lines if l["dtype"] == "float32")
     assert all(l["worst_abs_diff"] < 6e-2 for l in lines if l["dtype"] == "bfloat16")
+
+
+def test_a_capture_survives_the_collection_of_an_engine_that_is_gone(models):
+    """An engine that was dropped leaves its CUDA graphs in reference cycles; if Python's collector destroys them in
+    the middle of another engine's capture, that capture is lost ("operation not permitted when stream is
+    capturing").  Captures therefore collect before they start.  Here the old engine's graphs are kept from the
+    collector until the new engine captures, and a collection is forced inside every captured forward pass."""
+    import gc
+    from zedinfer_b200 import GenerationConfig, SchedulerConfig
+    from zedinfer_b200.engine import InferenceEngine
+    prompt = [3, 1, 4, 1, 5, 9, 2, 6]
+    gc.collect()
+    gc.disable()
+    try:
+        e1 = InferenceEngine.create(models["A"], SchedulerConfig(num_kv_pages=32, kv_block_size=4), dtype="float32")
+        for _ in range(2):
+            assert e1.generate_tokens(prompt, GenerationConfig(max_new_tokens=5, ignore_eos=True)).error is None
+        assert e1.core._decode_graphs
+        del e1                                     # its graphs stay behind, uncollected
+        e2 = InferenceEngine.create(models["A"], SchedulerConfig(num_kv_pages=32, kv_block_size=4), dtype="float32")
+        e2.core.GPU_BOUND_RATIO = float("inf")     # the prompt's step is captured at its second appearance
+        forward = e2.core.model.forward
+
+        def forward_with_a_collection(*args, **kw):
+            if torch.cuda.is_current_stream_capturing():
+                gc.collect()
+            return forward(*args, **kw)
+        e2.core.model.forward = forward_with_a_collection
+        for _ in range(3):
+            r = e2.generate_tokens(prompt, GenerationConfig(max_new_tokens=5, ignore_eos=True))
+            assert r.error is None and r.finish_reason == "length", (r.finish_reason, r.error)
+        assert e2.core._step_graphs
+    finally:
+        gc.enable()

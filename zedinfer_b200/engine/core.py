@@ -122,7 +122,10 @@ def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache]
     n_tok = sum(len(e.tokens) for e in entries) + pad_segments
     width = table_width
     n_groups = len(cache.groups)
-    n_want = sum(len(e.want) for e in entries)
+    # padding tokens want their logits too (rows nobody reads, at the end of the wanted rows): the number of wanted
+    # rows then depends on the padded count of single tokens, not on how many of them are real
+    n_real_want = sum(len(e.want) for e in entries)
+    n_want = n_real_want + pad_segments
     # Single-token entries at the head of a step that also holds longer ones (decoding requests beside a prompt
     # portion) are left to the decode attention kernel; the padding tokens stand right behind them, so that their
     # number depends on the step's counts alone.  Attention tiles cover the rest.
@@ -152,8 +155,11 @@ def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache]
     n_tile_done = 0
     scratch = cache.scratch_page if cache.groups else 0
 
+    pad_rows = []
+
     def pad_tokens(t, s, n_tile_done):           # padding: one token each at position 0 of the scratch page
         for _ in range(pad_segments):
+            pad_rows.append(t)
             host[off_seg + t] = s
             host[off_slots + s] = -1
             for g in range(n_groups):
@@ -195,6 +201,7 @@ def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache]
         s += 1
     if not lead:
         t, s, n_tile_done = pad_tokens(t, s, n_tile_done)
+    host[off_want + w: off_want + w + len(pad_rows)] = pad_rows
     if into is None:
         dev = ring.stage(host, device)
     else:
@@ -212,6 +219,7 @@ def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache]
         decode_only=all(k == 1 for k in seg_len), max_kv_len=max(max_kv, 1))
     ctx.extras["attn_tiles"] = dev[off_tiles: off_tiles + 3 * n_tiles].view(n_tiles, 3)
     ctx.extras["leading_singles"] = lead
+    ctx.extras["real_want"] = n_real_want
     ctx.extras["descriptor_len"] = total
     want = dev[off_want: off_want + n_want] if n_want else None
     return ctx, want
@@ -341,7 +349,8 @@ class EngineCore:
             lead += pad
         else:
             tiles = len(lens) + pad
-        return (sum(lens) + pad, len(lens) + pad, lead, tiles, sum(len(e.want) for e in entries), lead == 0 and all(k == 1 for k in lens))
+        return (sum(lens) + pad, len(lens) + pad, lead, tiles, sum(len(e.want) for e in entries) + pad,
+                lead == 0 and all(k == 1 for k in lens))
 
     def _eager_or_captured(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache]) -> Optional[torch.Tensor]:
         """A step whose counts recur is replayed as a CUDA graph, if that can gain anything: its first appearance
@@ -376,7 +385,8 @@ class EngineCore:
                 if first:
                     seen.host_ms = (time.perf_counter() - t0) * 1000.0
                     seen.events[1].record()
-                return logits
+                real = ctx.extras["real_want"]                                      # the rows of padding tokens are dropped
+                return None if logits is None or real == 0 else logits[:real]
             while len(self._step_graphs) >= self.MAX_STEP_GRAPHS:                   # the least recently used one goes
                 del self._step_graphs[next(iter(self._step_graphs))]
             g = StepGraph(self, entries, rcs, pad)

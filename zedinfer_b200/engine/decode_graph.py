@@ -13,6 +13,8 @@ the benchmark uses this to time the device alone.
 """
 from __future__ import annotations
 
+import contextlib
+import gc
 from typing import List, Optional, Sequence
 
 import numpy as np
@@ -20,6 +22,23 @@ import torch
 
 from .. import ops
 from ..parts.base import StepContext
+
+
+@contextlib.contextmanager
+def capturing(graph: "torch.cuda.CUDAGraph", pool=None):
+    """``torch.cuda.graph`` with Python's cycle collector held still.  A collection that starts in the middle of a
+    capture may destroy the CUDA graphs of an engine that is gone (they sit in reference cycles with it), and
+    destroying a graph is not allowed while a stream captures: the capture is lost with "operation not permitted
+    when stream is capturing".  So: collect first, then capture with the collector off."""
+    gc.collect()
+    was_enabled = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph, pool=pool):
+            yield
+    finally:
+        if was_enabled:
+            gc.enable()
 
 
 class DecodeGraph:
@@ -59,7 +78,7 @@ class DecodeGraph:
         self.graph = torch.cuda.CUDAGraph()
         from ..ops import _lib
         before = _lib.launch_count()
-        with torch.cuda.graph(self.graph):
+        with capturing(self.graph):
             self.logits = self._body()
         self.launches = _lib.launch_count() - before
 
@@ -186,7 +205,7 @@ class StepGraph:
         torch.cuda.synchronize()
         ops._tc_launched.pop(core.device, None)
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph, pool=core._graph_pool):
+        with capturing(self.graph, pool=core._graph_pool):
             self.logits = core.model.forward(self.ctx, core.views, self.want)
         self.uses_status = bool(ops._tc_launched.get(core.device, False))
 
@@ -198,4 +217,5 @@ class StepGraph:
         self.graph.replay()
         if self.uses_status:
             ops._tc_launched[self.core.device] = True
-        return self.logits
+        real = ctx.extras["real_want"]                    # the rows of padding tokens are dropped
+        return None if self.logits is None or real == 0 else self.logits[:real]
