@@ -76,11 +76,14 @@ def test_float32_is_the_same_however_it_is_cut(models, name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_a_long_prompt_takes_the_many_row_kernels(models, dtype, monkeypatch):
-    """1,024 tokens in one step: in bfloat16 every product of the step runs on the tcgen05 kernels for many rows
-    (SM pairs, SiLU-mul epilogue) and the attention on its tcgen05 kernel with eight key tiles; the logits at the
-    first, the last and a few positions in between (tile edges among them) are the plain implementation's."""
+@pytest.mark.parametrize("plain_products", [False, True])
+def test_a_long_prompt_takes_the_many_row_kernels(models, dtype, plain_products, monkeypatch):
+    """1,024 tokens in one step: in bfloat16 the gate/up product runs on the tcgen05 kernel for many rows (SM pairs,
+    SiLU-mul epilogue), with ``ops.TC_PLAIN_PRODUCTS`` the other three products of a layer too, and the attention
+    on its tcgen05 kernel with eight key tiles; the logits at the first, the last and a few positions in between
+    (tile edges among them) are the plain implementation's."""
     from zedinfer_b200 import ops
+    monkeypatch.setattr(ops, "TC_PLAIN_PRODUCTS", plain_products)
     from zedinfer_b200.engine.core import EngineCore, StepEntry
     cfg, _ = tiny.CONFIGS["D"]
     calls = {"tiles": 0, "attention": 0}
@@ -107,7 +110,8 @@ def test_a_long_prompt_takes_the_many_row_kernels(models, dtype, monkeypatch):
         d = float((logits[row] - exp[p]).abs().max())
         assert d <= TOL[dtype], (p, d)
     if dtype == "bfloat16":
-        assert calls["tiles"] == 4 * cfg["num_hidden_layers"] and calls["attention"] == cfg["num_hidden_layers"]
+        assert calls["tiles"] == (4 if plain_products else 1) * cfg["num_hidden_layers"]
+        assert calls["attention"] == cfg["num_hidden_layers"]
     else:
         assert calls["tiles"] == 0 and calls["attention"] == 0
 

@@ -308,7 +308,8 @@ def tcgen05_status(device) -> int:
     return v
 
 
-TC_MIN_ROWS = 1024               # rows from which the tcgen05 kernel takes a plain bfloat16 product
+TC_PLAIN_PRODUCTS = False        # plain bfloat16 products of many rows on the tcgen05 kernel instead of the library
+TC_MIN_ROWS = 1024               # ... from this many rows, where switched on
 TC_FUSED_MIN_ROWS = 128          # ... and a gate/up product with the activation in its epilogue
 _tc_launched: Dict = {}
 
@@ -354,16 +355,20 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
 
     * any float32 operand: the SIMT kernel (true 32-bit arithmetic);
     * bfloat16 x bfloat16 with at most 16 rows (decode steps): the weight-streaming tensor-core kernel;
-    * bfloat16 x bfloat16 from ``TC_MIN_ROWS`` rows (prefill): the tcgen05 kernel on pairs of SMs;
     * bfloat16 x bfloat16 otherwise: cuBLAS with float32 accumulation, the library product the
-      reference's engine uses as well; the output may be bfloat16 or float32.
+      reference's engine uses as well; the output may be bfloat16 or float32.  With ``TC_PLAIN_PRODUCTS`` set,
+      products of ``TC_MIN_ROWS`` rows or more run on the tcgen05 kernel (pairs of SMs) instead.  Timed back to
+      back in a graph the library is ahead on plain products (2,048 rows of the 1.5B-class layer: q/k/v 12.0
+      against 14.5 us, output 9.6 against 13.7, down 42.1 against 46.5; the whole 2,048-token step 5.39 against
+      5.75 ms), so the tcgen05 kernel is kept for the gate/up product, where its SiLU-mul epilogue saves a kernel
+      and a round trip of the activations through memory (:func:`linear_silu_mul`).
     """
     need_cuda(x, w, bias, out)
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and (bias is None or bias.dtype == torch.bfloat16):
         if _small_m_ok(x, w) and out.stride(1) == 1:
             gemm_smallm(x, w, bias, out)
             return
-        if x.shape[0] >= TC_MIN_ROWS and _tc_ok(x, w, bias, out):
+        if TC_PLAIN_PRODUCTS and x.shape[0] >= TC_MIN_ROWS and _tc_ok(x, w, bias, out):
             gemm_tcgen05_tiles(x, w, bias, out)
             _tc_launched[x.device] = True
             return
