@@ -24,9 +24,13 @@ def main(argv=None) -> int:
     p.add_argument("--intermediate", type=int, default=8960)
     p.add_argument("--vocab", type=int, default=151936)
     p.add_argument("--graphs", action="store_true", help="decode through the captured step instead")
+    p.add_argument("--tcgen05-plain-products", action="store_true",
+                   help="plain products of 1,024 rows or more on the tcgen05 kernel instead of the library")
     args = p.parse_args(argv)
     import torch
+    from .. import ops
     from ..engine.core import EngineCore, StepEntry
+    ops.TC_PLAIN_PRODUCTS = bool(args.tcgen05_plain_products)
     cfg = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": args.layers,
            "hidden_size": args.hidden, "num_attention_heads": args.heads, "num_key_value_heads": args.kv_heads,
            "head_dim": args.head_dim, "intermediate_size": args.intermediate, "vocab_size": args.vocab,
