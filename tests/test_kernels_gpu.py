@@ -442,9 +442,13 @@ def test_decode_attention_tma_cluster_sizes(requests, window):
 
 
 @pytest.mark.parametrize("batch", [1, 9])
-def test_decode_attention_tma_long_context(batch):
+@pytest.mark.parametrize("shared,window", [(False, None), (True, None), (True, 9000)])
+def test_decode_attention_tma_long_context(batch, shared, window):
     """20,000 keys: every warp walks more tiles than the 32 page numbers it reads at a time, with tiles of 32 keys
-    (one request: its clusters fit on the device at once) and of 16 keys (nine requests: they do not)."""
+    (one request: its clusters fit on the device at once) and of 16 keys (nine requests: they do not).  ``shared``:
+    the call is told how long the longest context is, and several clusters share the long request's keys (four at
+    20,000 keys, two inside a window of 9,000) while the short requests of the same step keep one cluster each; a
+    second kernel adds the parts."""
     from zedinfer_b200 import ops
     t = torch.bfloat16
     nh, nkv, hd, ps = 4, 1, 64, 16
@@ -457,13 +461,14 @@ def test_decode_attention_tma_long_context(batch):
     n = len(lens)
     pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=dev())
     seg = torch.arange(n, dtype=torch.int32, device=dev())
-    out = torch.empty(n, nh * hd, dtype=t, device=dev())
+    out = torch.full((n, nh * hd), float("nan"), dtype=t, device=dev())
     scale = 1.0 / math.sqrt(hd)
-    ops.decode_attention_tma(qd, view, out, tables, seg, pos, nh, nkv, hd, ps, page_stride, kv_stride, None, scale)
+    ops.decode_attention_tma(qd, view, out, tables, seg, pos, nh, nkv, hd, ps, page_stride, kv_stride, window, scale,
+                             max_kv_len=max(lens) if shared else 0)
     torch.cuda.synchronize()
     assert ops.tcgen05_status(dev()) == 0
     got = out.float().cpu().view(n, nh, hd)
     qf = qd.float().cpu()
     for r in range(n):
-        ref = plain_attention_rows(qf[r:r + 1], ks[r], vs[r], [lens[r] - 1], scale, None)
+        ref = plain_attention_rows(qf[r:r + 1], ks[r], vs[r], [lens[r] - 1], scale, window)
         assert float((got[r:r + 1] - ref).abs().max()) < 2e-2, (r, lens[r])

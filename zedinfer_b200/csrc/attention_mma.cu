@@ -421,12 +421,44 @@ __device__ __forceinline__ void pv_accumulate_tma(float (&O)[HD / 8][4], const f
     }
 }
 
+// How many of the n_splits clusters that a launch provides for one (request, key/value head) are at work for a
+// request with `tiles` visible tiles: the same answer in the attention kernel and in the merge kernel.
+__device__ __forceinline__ int dt_effective_splits(int tiles, int n_splits, int min_split_tiles) {
+    if (n_splits <= 1) return 1;
+    const int e = tiles / min_split_tiles;
+    return e < 1 ? 1 : (e > n_splits ? n_splits : e);
+}
+
+// Adds the parts of the clusters that shared one request's keys, in the order of the keys: grid (tokens, heads),
+// HD threads.  Requests whose keys one cluster took alone have their output already.
+template <int HD>
+__global__ void __launch_bounds__(HD)
+decode_attention_merge_kernel(const float* __restrict__ part, bf16* __restrict__ out, const int* __restrict__ pos,
+                              int n_heads, int window, int dt_keys, int n_splits, int min_split_tiles) {
+    const int n = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+    const int P = pos[n];
+    const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
+    const int eff = dt_effective_splits(P / dt_keys - lo / dt_keys + 1, n_splits, min_split_tiles);
+    if (eff == 1) return;
+    const float* src = part + ((size_t)n * n_heads + h) * n_splits * (HD + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < eff; ++s) M = fmaxf(M, src[(size_t)s * (HD + 2)]);
+    float acc = 0.0f, L = 0.0f;
+    for (int s = 0; s < eff; ++s) {
+        const float f = exp2f(src[(size_t)s * (HD + 2)] - M);
+        L += src[(size_t)s * (HD + 2) + 1] * f;
+        acc += src[(size_t)s * (HD + 2) + 2 + d] * f;
+    }
+    out[((size_t)n * n_heads + h) * HD + d] = __float2bfloat16_rn(acc / L);
+}
+
 template <int HD, int DT_KEYS, int CL>
 __global__ void __launch_bounds__(ATT_THREADS)
 decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q, bf16* __restrict__ out,
                             const int* __restrict__ tables, const int* __restrict__ tok_seg, const int* __restrict__ pos,
                             int* __restrict__ status, int n_heads, int n_kv_heads, int q_blocks, int page_size,
-                            int box_rows, int max_blocks, int window, float scale2) {
+                            int box_rows, int max_blocks, int window, float scale2, int n_splits, int min_split_tiles,
+                            float* __restrict__ part) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -436,12 +468,20 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
     constexpr int OS = HD + 8;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int rank = blockIdx.x;
-    const int kvh = blockIdx.y / q_blocks, qb = blockIdx.y - kvh * q_blocks;
+    const int split = blockIdx.y % n_splits, unit = blockIdx.y / n_splits;
+    const int kvh = unit / q_blocks, qb = unit - kvh * q_blocks;
     const int n = blockIdx.z;
     const int group = n_heads / n_kv_heads;
     const int P = pos[n];
     const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
-    const int t_lo = lo / DT_KEYS, t_hi = P / DT_KEYS;
+    // The visible tiles may be shared out over several clusters (long contexts of few requests, see dt_splits): as
+    // many of the n_splits as leave each at least min_split_tiles tiles.  Clusters beyond that number have nothing
+    // to do; with more than one at work each leaves (m, l, O) in `part` and decode_attention_merge_kernel adds them.
+    const int v_lo = lo / DT_KEYS, v_hi = P / DT_KEYS;
+    const int eff = dt_effective_splits(v_hi - v_lo + 1, n_splits, min_split_tiles);
+    if (split >= eff) return;
+    const int per = (v_hi - v_lo + eff) / eff;
+    const int t_lo = v_lo + split * per, t_hi = min(v_hi, t_lo + per - 1);
     const int first = rank + CL * warp;                  // this warp's first tile, counted from t_lo
     const int n_mine = (t_hi - t_lo - first >= 0) ? (t_hi - t_lo - first) / (CL * 4) + 1 : 0;
     const int* table = tables + (size_t)tok_seg[n] * max_blocks;
@@ -611,7 +651,13 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
             acc += po[r] * f;
         }
         const int h = kvh * group + qb * 16 + row;
-        out[((size_t)n * n_heads + h) * HD + d] = __float2bfloat16_rn(acc / L);
+        if (eff == 1) {
+            out[((size_t)n * n_heads + h) * HD + d] = __float2bfloat16_rn(acc / L);
+        } else {
+            float* dst = part + (((size_t)n * n_heads + h) * n_splits + split) * (HD + 2);
+            dst[2 + d] = acc;
+            if (d == 0) { dst[0] = M; dst[1] = L; }
+        }
     }
     cluster.sync();                                               // nobody leaves while its memory is still read
 }
@@ -823,6 +869,7 @@ static int dt_max_clusters() {
 struct DtArgs {
     const CUtensorMap* mkv; const void* q; void* out; const int* tables; const int* tok_seg; const int* pos; int* status;
     int n_tokens, n_heads, n_kv_heads, q_blocks, page_size, box_rows, max_blocks, window; float scale2; cudaStream_t stream;
+    int n_splits, min_split_tiles; float* part;
 };
 
 template <int HD, int KEYS, int CL>
@@ -834,11 +881,11 @@ static cudaError_t dt_launch(const DtArgs& a) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CL; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    cfg.gridDim = dim3(CL, a.n_kv_heads * a.q_blocks, a.n_tokens); cfg.blockDim = dim3(ATT_THREADS);
+    cfg.gridDim = dim3(CL, a.n_kv_heads * a.q_blocks * a.n_splits, a.n_tokens); cfg.blockDim = dim3(ATT_THREADS);
     cfg.dynamicSmemBytes = dt_smem<HD, KEYS>(); cfg.stream = a.stream;
     return cudaLaunchKernelEx(&cfg, decode_attention_tma_kernel<HD, KEYS, CL>, *a.mkv, (const bf16*)a.q, (bf16*)a.out, a.tables,
                               a.tok_seg, a.pos, a.status, a.n_heads, a.n_kv_heads, a.q_blocks, a.page_size, a.box_rows,
-                              a.max_blocks, a.window, a.scale2);
+                              a.max_blocks, a.window, a.scale2, a.n_splits, a.min_split_tiles, a.part);
 }
 template <int HD>
 static cudaError_t dt_dispatch(const DtArgs& a, int keys, int cl) {
@@ -851,29 +898,24 @@ static cudaError_t dt_dispatch(const DtArgs& a, int keys, int cl) {
     }
 }
 
-ZI_EXPORT int zi_decode_attention_tma(const void* q, const void* cache, void* out, const int* tables, const int* tok_seg,
-                                      const int* pos, int* status, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                                      int page_size, int max_blocks, long long n_pages, long long page_stride,
-                                      long long kv_stride, int window, float scale, cudaStream_t stream) {
-    if (n_tokens <= 0) return 0;
-    if (check_common("decode_attention_tma", n_heads, n_kv_heads, head_dim, page_size, max_blocks)) return 1;
-    if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1))) return zi_fail("decode_attention_tma: page size %d is not a power of two from 8 to 128", page_size);
-    if (n_tokens > 65535) return zi_fail("decode_attention_tma: %d tokens are more than one launch takes (65535)", n_tokens);
-    if (((uintptr_t)q | (uintptr_t)cache) & 15) return zi_fail("decode_attention_tma: q and cache must be 16-byte aligned");
-    if ((page_stride | kv_stride) & 7) return zi_fail("decode_attention_tma: cache strides must be multiples of 8 elements");
-    if (!status) return zi_fail("decode_attention_tma: a status word is required");
-    const int group = n_heads / n_kv_heads, q_blocks = (group + 15) / 16;
-    if (n_kv_heads * q_blocks > 65535) return zi_fail("decode_attention_tma: too many head blocks for one launch");
-    if (tc_init()) return 1;
-    // A (request, key/value head) is one unit of work.  Few units: clusters of eight blocks share a unit's keys, in
-    // tiles of 32 keys while all clusters fit on the device at once, else of 16 (two blocks to an SM).  More units
-    // fill the device by themselves: the cluster is then the largest of 8, 4, 2, 1 with which all blocks still run
-    // at once, so that a block's fixed cost (start, merge of its warps, cluster exchange) is spread over more keys.
-    // Measured at 1,100 cached tokens, 4 key/value heads: 48 requests 47 us with clusters of 8, 25 us with single
-    // blocks; 16 requests 15 us with 8, 10 us with 4.
+// How a step's decode attention is laid out: tiles of 32 or 16 keys, blocks per cluster, clusters per (request,
+// key/value head).
+//   A (request, key/value head) is one unit of work.  Few units: clusters of eight blocks share a unit's keys, in
+//   tiles of 32 keys while all clusters fit on the device at once, else of 16 (two blocks to an SM).  More units
+//   fill the device by themselves: the cluster is then the largest of 8, 4, 2, 1 with which all blocks still run
+//   at once, so that a block's fixed cost (start, merge of its warps, cluster exchange) is spread over more keys.
+//   Measured at 1,100 cached tokens, 4 key/value heads: 48 requests 47 us with clusters of 8, 25 us with single
+//   blocks; 16 requests 15 us with 8, 10 us with 4.
+//   Very few units with long contexts leave most of the device idle (one request of 2 key/value heads and 32,768
+//   tokens: 16 blocks, 0.8 TB/s): then several clusters share a unit, each taking at least DT_SPLIT_KEYS keys, as
+//   far as the longest context of the step (max_kv_len) and the free SMs allow, and a second kernel adds their
+//   parts.
+#define DT_SPLIT_KEYS 4096
+#define DT_MAX_SPLITS 16
+struct DtPlan { int keys, cl, splits, min_split_tiles; };
+static int dt_plan(DtPlan* p, int n_tokens, int n_kv_heads, int q_blocks, int head_dim, int max_kv_len) {
     const long long units = (long long)n_kv_heads * q_blocks * n_tokens;
     const int fit32 = head_dim == 128 ? dt_max_clusters<128, 32>() : dt_max_clusters<64, 32>();
-    const int keys = (fit32 > 0 && units <= fit32) ? 32 : 16;
     static int slots = 0;                                         // blocks of the 16-key form that run at once: two to an SM
     if (slots == 0) {
         int dev = 0, sms = 0;
@@ -883,13 +925,61 @@ ZI_EXPORT int zi_decode_attention_tma(const void* q, const void* cache, void* ou
     }
     int cl = 8;
     while (cl > 1 && units * cl > slots) cl >>= 1;
+    long long splits = max_kv_len / DT_SPLIT_KEYS;
+    if (splits > slots / (units * cl)) splits = slots / (units * cl);
+    if (splits > DT_MAX_SPLITS) splits = DT_MAX_SPLITS;
+    if (splits < 2) splits = 1;
+    p->keys = (fit32 > 0 && units * splits <= fit32) ? 32 : 16;
+    p->cl = cl;
+    p->splits = (int)splits;
+    p->min_split_tiles = DT_SPLIT_KEYS / p->keys;
+    return 0;
+}
+
+// Floats of scratch a call needs for the parts of clusters that share a request (0: none).
+ZI_EXPORT long long zi_decode_attention_tma_part_floats(int n_tokens, int n_heads, int n_kv_heads, int head_dim, int max_kv_len) {
+    if (n_tokens <= 0 || n_heads <= 0 || n_kv_heads <= 0 || (head_dim != 64 && head_dim != 128) || tc_init()) return 0;
+    DtPlan p;
+    dt_plan(&p, n_tokens, n_kv_heads, (n_heads / n_kv_heads + 15) / 16, head_dim, max_kv_len);
+    return p.splits > 1 ? (long long)n_tokens * n_heads * p.splits * (head_dim + 2) : 0;
+}
+
+// max_kv_len: an upper bound of the cached tokens of the step's requests (decides how many clusters may share one
+// request); part / part_floats: scratch as zi_decode_attention_tma_part_floats says, may be null when that is 0.
+ZI_EXPORT int zi_decode_attention_tma(const void* q, const void* cache, void* out, const int* tables, const int* tok_seg,
+                                      const int* pos, int* status, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                      int page_size, int max_blocks, long long n_pages, long long page_stride,
+                                      long long kv_stride, int window, float scale, int max_kv_len, float* part,
+                                      long long part_floats, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (check_common("decode_attention_tma", n_heads, n_kv_heads, head_dim, page_size, max_blocks)) return 1;
+    if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1))) return zi_fail("decode_attention_tma: page size %d is not a power of two from 8 to 128", page_size);
+    if (n_tokens > 65535) return zi_fail("decode_attention_tma: %d tokens are more than one launch takes (65535)", n_tokens);
+    if (((uintptr_t)q | (uintptr_t)cache) & 15) return zi_fail("decode_attention_tma: q and cache must be 16-byte aligned");
+    if ((page_stride | kv_stride) & 7) return zi_fail("decode_attention_tma: cache strides must be multiples of 8 elements");
+    if (!status) return zi_fail("decode_attention_tma: a status word is required");
+    const int group = n_heads / n_kv_heads, q_blocks = (group + 15) / 16;
+    if (tc_init()) return 1;
+    DtPlan plan;
+    dt_plan(&plan, n_tokens, n_kv_heads, q_blocks, head_dim, max_kv_len);
+    if (plan.splits > 1) {
+        const long long need = (long long)n_tokens * n_heads * plan.splits * (head_dim + 2);
+        if (!part || part_floats < need) return zi_fail("decode_attention_tma: %d clusters share a request and need %lld floats of scratch, got %lld", plan.splits, need, part ? part_floats : 0LL);
+    }
+    if ((long long)n_kv_heads * q_blocks * plan.splits > 65535) return zi_fail("decode_attention_tma: too many head blocks for one launch");
+    const int keys = plan.keys;
     const int box_rows = page_size < keys ? page_size : keys;
     CUtensorMap mkv;
     if (tc_map_kv_pages(&mkv, cache, head_dim, page_size, n_kv_heads, n_pages, page_stride, kv_stride, box_rows)) return 1;
     DtArgs a = {&mkv, q, out, tables, tok_seg, pos, status, n_tokens, n_heads, n_kv_heads, q_blocks, page_size, box_rows,
-                max_blocks, window, scale * LOG2E, stream};
-    const cudaError_t e = head_dim == 128 ? dt_dispatch<128>(a, keys, cl) : dt_dispatch<64>(a, keys, cl);
+                max_blocks, window, scale * LOG2E, stream, plan.splits, plan.min_split_tiles, part};
+    cudaError_t e = head_dim == 128 ? dt_dispatch<128>(a, keys, plan.cl) : dt_dispatch<64>(a, keys, plan.cl);
     if (e != cudaSuccess) { cudaGetLastError(); return zi_fail("decode_attention_tma: launch failed: %s", cudaGetErrorString(e)); }
+    if (plan.splits > 1) {
+        const dim3 grid(n_tokens, n_heads);
+        if (head_dim == 128) decode_attention_merge_kernel<128><<<grid, 128, 0, stream>>>(part, (bf16*)out, pos, n_heads, window, keys, plan.splits, plan.min_split_tiles);
+        else decode_attention_merge_kernel<64><<<grid, 64, 0, stream>>>(part, (bf16*)out, pos, n_heads, window, keys, plan.splits, plan.min_split_tiles);
+    }
     return zi_check_launch("decode_attention_tma");
 }
 

@@ -424,20 +424,35 @@ def decode_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, ta
 
 def decode_attention_tma(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
                          tok_seg: torch.Tensor, pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
-                         page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float) -> None:
+                         page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float,
+                         max_kv_len: int = 0) -> None:
     """One query token per request, bfloat16: the cluster kernel with 32-key tiles dealt to single warps, each
     fed by TMA through the block table into a ring of its own.  Same arguments as :func:`decode_attention`;
-    head_dim 64 or 128, pages of a power of two from 8 to 128 tokens.  A bounded wait that runs out is reported by
+    head_dim 64 or 128, pages of a power of two from 8 to 128 tokens.  ``max_kv_len``: an upper bound of the cached
+    tokens of the step's requests; with few requests and long contexts several clusters then share one request's
+    keys and a second kernel adds their parts (0: never).  A bounded wait that runs out is reported by
     :func:`tcgen05_status`."""
     need_cuda(q, cache, out, tables, tok_seg, pos)
     need_int32("tables", tables), need_int32("tok_seg", tok_seg), need_int32("pos", pos)
     need_contiguous("q", q), need_contiguous("out", out)
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("decode_attention_tma: bfloat16 only")
+    part, part_floats = None, 0
+    if max_kv_len > 0:
+        lib = _attention_mma.lib
+        lib.zi_decode_attention_tma_part_floats.restype = c_ll
+        part_floats = int(lib.zi_decode_attention_tma_part_floats(c_int(q.shape[0]), c_int(n_heads), c_int(n_kv_heads),
+                                                                   c_int(head_dim), c_int(int(max_kv_len))))
+        if part_floats:
+            key = ("decode_parts", q.device)
+            if key not in _scratch or _scratch[key].numel() < part_floats:
+                _scratch[key] = torch.empty(part_floats, dtype=torch.float32, device=q.device)
+            part = _scratch[key]
     _attention_mma.call("zi_decode_attention_tma", ptr(q), ptr(cache), ptr(out), ptr(tables), ptr(tok_seg), ptr(pos),
                         ptr(_tc_status(q.device)), c_int(q.shape[0]), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
                         c_int(page_size), c_int(tables.shape[1]), c_ll(cache.shape[0]), c_ll(page_stride), c_ll(kv_stride),
-                        c_int(window or 0), c_float(scale), stream())
+                        c_int(window or 0), c_float(scale), c_int(int(max_kv_len) if part_floats else 0), ptr(part),
+                        c_ll(part_floats), stream())
     _tc_launched[q.device] = True
 
 
@@ -493,7 +508,8 @@ def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv
         n = q.shape[0]
         if ctx.decode_only and tcgen05_attention_ok(head_dim, cache.page_size):
             decode_attention_tma(q, cache.tensor, out, tables, ctx.tok_seg, ctx.positions, n_heads, n_kv_heads, head_dim,
-                                 cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
+                                 cache.page_size, cache.page_stride, cache.kv_stride, window, scale,
+                                 max_kv_len=min(ctx.max_kv_len, window) if window else ctx.max_kv_len)
             return
         if ctx.decode_only:
             decode_attention(q, cache.tensor, out, tables, ctx.tok_seg, ctx.positions, n_heads, n_kv_heads, head_dim,
