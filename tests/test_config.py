@@ -134,3 +134,50 @@ def test_engine_options():
     assert resolve_max_new_tokens(5, 10, 100) == 5
     with pytest.raises(ValueError, match="no room"):
         resolve_max_new_tokens(5, 100, 100)
+
+
+# ---- the engine's default sampling (src/zedinfer/engine.cpp:49-126) ---------------------------------------
+def _gen_folder(tmp_path, body):
+    import json
+    (tmp_path / "generation_config.json").write_text(body if isinstance(body, str) else json.dumps(body))
+    return str(tmp_path)
+
+
+def test_sampling_defaults_follow_generation_config_json(tmp_path):
+    from zedinfer_b200.config import sampling_defaults
+    assert sampling_defaults(None, {}).use_argmax                         # no folder
+    assert sampling_defaults(str(tmp_path), {}).use_argmax                # no file
+    d = _gen_folder(tmp_path, {"do_sample": True, "temperature": 0.6, "top_k": 20, "top_p": 0.95})
+    g = sampling_defaults(d, {})
+    assert (g.use_argmax, g.temperature, g.top_k, g.top_p, g.repetition_penalty, g.seed) == (False, 0.6, 20, 0.95, 1.0, 0)
+    assert g.has_sampling_override
+    g = sampling_defaults(_gen_folder(tmp_path, {"do_sample": True, "repetition_penalty": 1.1, "seed": 7}), {})
+    assert (g.use_argmax, g.temperature, g.repetition_penalty, g.seed) == (False, 1.0, 1.1, 7)
+    assert sampling_defaults(_gen_folder(tmp_path, {"do_sample": False, "temperature": 0.6}), {}).use_argmax
+    assert sampling_defaults(_gen_folder(tmp_path, {"temperature": 0.6}), {}).use_argmax       # do_sample absent
+    assert sampling_defaults(_gen_folder(tmp_path, "{ not json"), {}).use_argmax
+    assert sampling_defaults(_gen_folder(tmp_path, {"do_sample": True, "top_p": 1.5}), {}).use_argmax   # does not validate
+    assert sampling_defaults(_gen_folder(tmp_path, {"do_sample": True, "temperature": 0.0}), {}).use_argmax
+
+
+def test_sampling_defaults_environment_overrides(tmp_path):
+    from zedinfer_b200.config import sampling_defaults
+    d = _gen_folder(tmp_path, {"do_sample": True, "temperature": 0.6, "repetition_penalty": 1.05})
+    assert sampling_defaults(d, {"ZEDINFER_FORCE_ARGMAX": "1"}).use_argmax
+    assert not sampling_defaults(d, {"ZEDINFER_FORCE_ARGMAX": "0"}).use_argmax
+    assert not sampling_defaults(d, {"ZEDINFER_FORCE_ARGMAX": ""}).use_argmax
+    assert sampling_defaults(d, {"ZEDINFER_REPETITION_PENALTY": "1.3"}).repetition_penalty == 1.3
+    assert sampling_defaults(d, {"ZEDINFER_REPETITION_PENALTY": "x"}).repetition_penalty == 1.05
+
+
+def test_a_request_without_sampling_options_takes_the_engines_default():
+    from zedinfer_b200.config import GenerationConfig
+    default = GenerationConfig(use_argmax=False, temperature=0.6, top_k=20, top_p=0.9, seed=3)
+    plain = GenerationConfig(max_new_tokens=5, ignore_eos=True)
+    assert not plain.has_sampling_override
+    r = plain.with_sampling_of(default)
+    assert (r.max_new_tokens, r.ignore_eos, r.use_argmax, r.temperature, r.top_k, r.top_p, r.seed) == (5, True, False, 0.6, 20, 0.9, 3)
+    own = GenerationConfig(max_new_tokens=5, use_argmax=False, temperature=1.3)
+    assert own.has_sampling_override and own.with_sampling_of(default) is own
+    greedy = GenerationConfig(max_new_tokens=5, has_sampling_override=True)      # insists on greedy
+    assert greedy.with_sampling_of(default).use_argmax

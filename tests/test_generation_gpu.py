@@ -316,3 +316,32 @@ def test_a_capture_survives_the_collection_of_an_engine_that_is_gone(models):
         assert e2.core._step_graphs
     finally:
         gc.enable()
+
+
+def test_engine_default_sampling_comes_from_generation_config_json(models, tmp_path, monkeypatch):
+    """A folder whose generation_config.json says do_sample: a request without sampling options is sampled with the
+    folder's values (same tokens as a request that states them), ZEDINFER_FORCE_ARGMAX brings greedy back, and a
+    request that insists on greedy gets it (src/zedinfer/engine.cpp:49-126, src/zedinfer/scheduler.cpp:576-601)."""
+    import shutil
+    from zedinfer_b200 import GenerationConfig, SchedulerConfig
+    from zedinfer_b200.engine import InferenceEngine
+    folder = tmp_path / "with_generation_config"
+    shutil.copytree(models["B"], folder)
+    (folder / "generation_config.json").write_text(json.dumps(
+        {"do_sample": True, "temperature": 1.4, "top_k": 30, "top_p": 0.97, "seed": 11}))
+    prompt = [3, 141, 59, 26, 535, 89, 79]
+    sc = SchedulerConfig(num_kv_pages=32, kv_block_size=8)
+    monkeypatch.delenv("ZEDINFER_FORCE_ARGMAX", raising=False)
+    engine = InferenceEngine.create(str(folder), sc, dtype="float32")
+    assert not engine.default_generation.use_argmax and engine.default_generation.top_k == 30
+    by_default = engine.generate_tokens(prompt, GenerationConfig(max_new_tokens=12, ignore_eos=True)).output_ids
+    stated = engine.generate_tokens(prompt, GenerationConfig(max_new_tokens=12, ignore_eos=True, use_argmax=False,
+                                                             temperature=1.4, top_k=30, top_p=0.97, seed=11)).output_ids
+    greedy = plain_greedy(models["B"], prompt, 12)
+    assert by_default == stated and by_default != greedy
+    insisted = engine.generate_tokens(prompt, GenerationConfig(max_new_tokens=12, ignore_eos=True,
+                                                               has_sampling_override=True)).output_ids
+    assert insisted == greedy
+    monkeypatch.setenv("ZEDINFER_FORCE_ARGMAX", "1")
+    forced = InferenceEngine.create(str(folder), sc, dtype="float32")
+    assert forced.generate_tokens(prompt, GenerationConfig(max_new_tokens=12, ignore_eos=True)).output_ids == greedy

@@ -17,7 +17,9 @@ def main(argv=None) -> int:
     p.add_argument("--max-new-tokens", "--max-tokens", dest="max_new_tokens", type=int, default=0,
                    help="Maximum number of new tokens to generate (0 = unlimited)")
     p.add_argument("--stream", action="store_true", help="Print token ids as they are generated")
-    p.add_argument("--temperature", type=float, default=0.0, help="0 = greedy")
+    p.add_argument("--temperature", type=float, default=None,
+                   help="0 = greedy; not given (and no other sampling option): the engine's default, which follows the "
+                        "folder's generation_config.json as in the reference (greedy without one)")
     p.add_argument("--top-k", type=int, default=0)
     p.add_argument("--top-p", type=float, default=1.0)
     p.add_argument("--repetition-penalty", type=float, default=1.0)
@@ -36,10 +38,17 @@ def main(argv=None) -> int:
         print(f"[ping] engine init failed: {e}", file=sys.stderr)
         return 3
     print(f"[ping] engine initialized in {(time.perf_counter() - t0) * 1000:.0f} ms", file=sys.stderr)
-    greedy = args.temperature <= 0.0
-    gc = GenerationConfig(max_new_tokens=args.max_new_tokens, use_argmax=greedy,
-                          temperature=args.temperature if not greedy else 1.0, top_k=args.top_k, top_p=args.top_p,
-                          repetition_penalty=args.repetition_penalty, seed=args.seed, ignore_eos=args.ignore_eos)
+    own = (args.temperature is not None or args.top_k != 0 or args.top_p != 1.0 or args.repetition_penalty != 1.0
+           or args.seed != 0)
+    if not own:
+        gc = GenerationConfig(max_new_tokens=args.max_new_tokens, ignore_eos=args.ignore_eos)
+    else:
+        # sampling options without a temperature sample at temperature 1; --temperature 0 is greedy
+        greedy = args.temperature is not None and args.temperature <= 0.0
+        gc = GenerationConfig(max_new_tokens=args.max_new_tokens, use_argmax=greedy,
+                              temperature=args.temperature if args.temperature and not greedy else 1.0, top_k=args.top_k,
+                              top_p=args.top_p, repetition_penalty=args.repetition_penalty, seed=args.seed,
+                              ignore_eos=args.ignore_eos, has_sampling_override=True)
     cb = (lambda tok: print(tok, end=" ", flush=True)) if args.stream else None
     try:
         result = engine.generate_tokens(parse_ids(args.prompt), gc, stream_callback=cb)

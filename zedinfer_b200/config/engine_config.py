@@ -7,8 +7,8 @@ tokenizer front-end and are not here).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
-from typing import Optional
+from dataclasses import dataclass, replace
+from typing import Mapping, Optional
 
 
 @dataclass
@@ -47,14 +47,33 @@ class SchedulerConfig:
 
 @dataclass
 class GenerationConfig:
+    """Per-request options (include/zedinfer/generation_types.hpp:20-90).  As in the reference, the sampling fields
+    count only with ``has_sampling_override``; a request without it is sampled by the engine's default, which comes
+    from the model folder's generation_config.json (:func:`sampling_defaults`; greedy when there is none).  Giving
+    any sampling field another value than its default sets the flag; say ``has_sampling_override=True`` to insist on
+    greedy against a folder that asks for sampling."""
     max_new_tokens: int = 0            # 0 = until the context is full
-    use_argmax: bool = True            # greedy; the reference's engine default when do_sample is unset
+    use_argmax: bool = True            # greedy
     temperature: float = 1.0
     top_k: int = 0                     # 0 = off
     top_p: float = 1.0                 # 1 = off
     repetition_penalty: float = 1.0    # on generated tokens only
     seed: int = 0                      # 0 = a fresh seed per request
     ignore_eos: bool = False           # addition: run to max_new_tokens (benchmarks with random weights)
+    has_sampling_override: bool = False
+
+    def __post_init__(self) -> None:
+        if (not self.use_argmax or self.temperature != 1.0 or self.top_k != 0 or self.top_p != 1.0
+                or self.repetition_penalty != 1.0 or self.seed != 0):
+            self.has_sampling_override = True
+
+    def with_sampling_of(self, default: "GenerationConfig") -> "GenerationConfig":
+        """This request's options with the engine's default sampling, unless the request brought its own."""
+        if self.has_sampling_override:
+            return self
+        return replace(self, use_argmax=default.use_argmax, temperature=default.temperature, top_k=default.top_k,
+                       top_p=default.top_p, repetition_penalty=default.repetition_penalty, seed=default.seed,
+                       has_sampling_override=True)
 
     def validate(self) -> None:
         # src/zedinfer/generation_types.cpp:13-25 and src/frontend/sampler/sampler.cpp:24-38
@@ -86,3 +105,42 @@ def resolve_max_new_tokens(requested: int, used_context_tokens: int, max_seq_len
     if requested == 0 or requested > remaining:
         return remaining
     return requested
+
+
+def sampling_defaults(model_dir: Optional[str], environ: Optional[Mapping[str, str]] = None) -> GenerationConfig:
+    """The engine's default sampling, as the reference derives it (src/zedinfer/engine.cpp:49-126):
+
+    * ``ZEDINFER_FORCE_ARGMAX`` set to anything but "" or "0": greedy, whatever the folder says;
+    * no generation_config.json in the folder, ``do_sample`` false or absent, a file that does not parse, or values
+      that do not validate: greedy;
+    * else ``temperature`` / ``top_k`` / ``top_p`` / ``repetition_penalty`` (1.0 if absent) / ``seed`` (0 if
+      absent) from the file, with ``ZEDINFER_REPETITION_PENALTY`` overriding the penalty.
+    """
+    import json
+    import os
+    env = os.environ if environ is None else environ
+    greedy = GenerationConfig(use_argmax=True, has_sampling_override=True)
+    force = env.get("ZEDINFER_FORCE_ARGMAX", "")
+    if force not in ("", "0"):
+        return greedy
+    path = os.path.join(model_dir, "generation_config.json") if model_dir and os.path.isdir(model_dir) else None
+    if path is None or not os.path.isfile(path):
+        return greedy
+    try:
+        with open(path, "r", encoding="utf-8") as f:
+            j = json.load(f)
+        if not isinstance(j, dict) or not j.get("do_sample", False):
+            return greedy
+        cfg = GenerationConfig(use_argmax=False, temperature=float(j.get("temperature", 1.0)), top_k=int(j.get("top_k", 0)),
+                               top_p=float(j.get("top_p", 1.0)), repetition_penalty=float(j.get("repetition_penalty", 1.0)),
+                               seed=int(j.get("seed", 0)), has_sampling_override=True)
+        rp = env.get("ZEDINFER_REPETITION_PENALTY", "")
+        if rp != "":
+            try:
+                cfg.repetition_penalty = float(rp)
+            except ValueError:
+                pass                            # the reference keeps the file's value when the variable does not parse
+        cfg.validate()
+        return cfg
+    except (OSError, ValueError, TypeError):
+        return greedy

@@ -14,7 +14,7 @@ from typing import Callable, List, Optional, Sequence, Tuple
 
 import torch
 
-from ..config.engine_config import GenerationConfig, SchedulerConfig
+from ..config.engine_config import GenerationConfig, SchedulerConfig, sampling_defaults
 from ..sampling.sampler import Sampler, fresh_seed
 from .core import EngineCore, StepEntry
 from .request import GenerationResult, InferenceRequest, RequestPhase
@@ -46,6 +46,8 @@ class InferenceEngine:
         self.steps_run = 0
         self.steps_run_ahead = 0
         self.on_step: Optional[Callable[[ScheduledBatch], None]] = None
+        # how a request is sampled that brings no sampling options of its own (GenerationConfig.has_sampling_override)
+        self.default_generation = GenerationConfig(use_argmax=True, has_sampling_override=True)
         self._pending: Optional[Tuple[ScheduledBatch, object]] = None     # a launched step whose tokens are on their way
 
     @classmethod
@@ -64,10 +66,13 @@ class InferenceEngine:
         else:
             from ..config.registry import read_config_json
             core = EngineCore(None, dtype, config=read_config_json(model_path), random_seed=int(random_seed), **sizes)
-        return cls(core, cfg)
+        engine = cls(core, cfg)
+        engine.default_generation = sampling_defaults(model_path)      # the folder's generation_config.json, if any
+        return engine
 
     # ---- intake -----------------------------------------------------------------------------
     def submit_async(self, request: InferenceRequest) -> RequestFuture:
+        request.config = request.config.with_sampling_of(self.default_generation)
         request.sample_seed = request.config.seed if request.config.seed != 0 else fresh_seed()
         request.arrival_time = time.perf_counter()
         self.scheduler.submit(request)
