@@ -9,6 +9,7 @@ Requests are token ids in, token ids out: tokenizer and chat templates are not p
 """
 from __future__ import annotations
 
+import os
 import time
 from typing import Callable, List, Optional, Sequence, Tuple
 
@@ -16,6 +17,7 @@ import torch
 
 from ..config.engine_config import GenerationConfig, SchedulerConfig, sampling_defaults
 from ..sampling.sampler import Sampler, fresh_seed
+from ..cache.pool import OutOfPages
 from .core import EngineCore, StepEntry
 from .request import GenerationResult, InferenceRequest, RequestPhase
 from .scheduler import ScheduledBatch, Scheduler
@@ -68,7 +70,23 @@ class InferenceEngine:
             core = EngineCore(None, dtype, config=read_config_json(model_path), random_seed=int(random_seed), **sizes)
         engine = cls(core, cfg)
         engine.default_generation = sampling_defaults(model_path)      # the folder's generation_config.json, if any
+        if os.environ.get("ZEDINFER_DISABLE_WARMUP") is None:            # as the reference (src/zedinfer/engine.cpp:506-516)
+            engine.warmup()
         return engine
+
+    def warmup(self) -> None:
+        """A short prompt and a few decode steps of random ids: kernel libraries are compiled and loaded and the
+        decode step for one request is captured before the first real request comes.  Skipped when the pool is too
+        small for it; a failure here is left for the first request to report."""
+        c = self.core.cache
+        room = min(self.core.max_seq_len, min(c.free_pages()) * c.page_size if c.groups else self.core.max_seq_len)
+        n = min(16, room - 4)
+        if n < 2:
+            return
+        try:
+            self.profile(n, 3)
+        except (OutOfPages, ValueError):
+            pass
 
     # ---- intake -----------------------------------------------------------------------------
     def submit_async(self, request: InferenceRequest) -> RequestFuture:

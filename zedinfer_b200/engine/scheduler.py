@@ -22,12 +22,17 @@ manager's bookkeeping, so it is tested without a GPU.
 from __future__ import annotations
 
 import collections
+import os
+import sys
 import threading
 import time
 from dataclasses import dataclass, field
 from typing import Deque, List, Optional, Sequence, Tuple
 
 from ..cache.manager import CacheManager
+
+# ZEDINFER_DUMP_TOKEN_IDS=1: every committed token id goes to stderr (src/zedinfer/scheduler.cpp:561-564); read once
+_DUMP_TOKEN_IDS = os.environ.get("ZEDINFER_DUMP_TOKEN_IDS", "")[:1] == "1"
 from ..cache.pool import OutOfPages
 from ..config.engine_config import SchedulerConfig, resolve_max_new_tokens
 from .request import InferenceRequest, RequestPhase
@@ -220,6 +225,8 @@ class Scheduler:
                     req.first_token_time = now
                     req.stats.prefill_time_ms = (now - (req.first_scheduled_time or req.arrival_time)) * 1000.0
             req.output_ids.append(tok)
+            if _DUMP_TOKEN_IDS:
+                print(f"[token] request={req.request_id} index={len(req.output_ids) - 1} id={tok}", file=sys.stderr)
             req.prefill_progress = len(req.sequence()) - 1        # all but the token just sampled are cached
             if req.stream_callback is not None:
                 req.stream_callback(tok)
