@@ -3,7 +3,9 @@ examples (examples/ping.cpp:31-79, examples/bench.cpp:23-60, examples/serve.cpp:
 from __future__ import annotations
 
 import argparse
+import logging
 import os
+import sys
 
 from ..config.engine_config import SchedulerConfig
 
@@ -31,6 +33,44 @@ def add_engine_arguments(p: argparse.ArgumentParser) -> None:
     p.add_argument("--on-exhaust", choices=["preempt", "fail"], default="preempt",
                    help="When pages run out during decode: preempt the youngest request, or fail it as the reference does")
     p.add_argument("--no-cuda-graphs", action="store_true", help="Launch decode steps kernel by kernel")
+    add_logging_arguments(p)
+
+
+_LEVELS = {"none": logging.CRITICAL + 10, "fatal": logging.CRITICAL, "error": logging.ERROR, "warning": logging.WARNING,
+           "info": logging.INFO, "debug": logging.DEBUG, "verbose": logging.DEBUG - 5}
+log = logging.getLogger("zedinfer_b200")
+
+
+def add_logging_arguments(p: argparse.ArgumentParser, default_log_file: str = "", default_level: str = "info") -> None:
+    """The reference's logging options (include/utils/logging_cli.hpp:11-38); an empty --log-file writes no file."""
+    p.add_argument("--log-level", choices=sorted(_LEVELS, key=_LEVELS.get), default=default_level,
+                   help="Log level: none, fatal, error, warning, info, debug, verbose")
+    p.add_argument("--log-file", default=default_log_file, help="Path to the log file")
+    p.add_argument("--log-to-console", dest="log_to_console", action="store_true", default=True,
+                   help="Mirror logs to stderr (default)")
+    p.add_argument("--no-log-to-console", dest="log_to_console", action="store_false",
+                   help="Disable stderr log mirroring")
+    p.add_argument("--log-append", action="store_true", help="Append to --log-file instead of replacing it")
+    p.add_argument("--log-overwrite", action="store_true", help="Replace --log-file on startup (default)")
+
+
+def setup_logging(args) -> logging.Logger:
+    log.handlers.clear()
+    log.propagate = False
+    log.setLevel(_LEVELS[getattr(args, "log_level", "info")])
+    fmt = logging.Formatter("%(message)s")
+    if getattr(args, "log_to_console", True):
+        h = logging.StreamHandler(sys.stderr)
+        h.setFormatter(fmt)
+        log.addHandler(h)
+    path = getattr(args, "log_file", "")
+    if path:
+        h = logging.FileHandler(path, mode="a" if getattr(args, "log_append", False) and not getattr(args, "log_overwrite", False) else "w")
+        h.setFormatter(logging.Formatter("%(asctime)s %(levelname)s %(message)s"))
+        log.addHandler(h)
+    if not log.handlers:
+        log.addHandler(logging.NullHandler())
+    return log
 
 
 def scheduler_config_from(args) -> SchedulerConfig:
@@ -42,13 +82,16 @@ def scheduler_config_from(args) -> SchedulerConfig:
 
 
 def create_engine(args):
-    import sys
     from ..engine import InferenceEngine
+    setup_logging(args)
     engine = InferenceEngine.create(args.model_path, scheduler_config_from(args), dtype=args.dtype,
                                     random_seed=args.random_weights)
     st = engine.cache_stats()
-    print(f"[engine] cache: {st['pages_per_group']} pages of {st['page_size']} tokens ({st['pages_per_group'] * st['page_size']} "
-          f"tokens, {st['pool_bytes'] / 2**30:.2f} GiB)", file=sys.stderr)
+    log.info(f"[engine] cache: {st['pages_per_group']} pages of {st['page_size']} tokens "
+             f"({st['pages_per_group'] * st['page_size']} tokens, {st['pool_bytes'] / 2**30:.2f} GiB)")
+    d = engine.default_generation
+    log.info("[engine] default sampling: " + ("greedy" if d.use_argmax else
+             f"temperature={d.temperature} top_k={d.top_k} top_p={d.top_p} repetition_penalty={d.repetition_penalty}"))
     return engine
 
 

@@ -6,7 +6,7 @@ import argparse
 import sys
 import time
 
-from .common import add_engine_arguments, create_engine, parse_ids
+from .common import add_engine_arguments, create_engine, log, parse_ids
 
 
 def main(argv=None) -> int:
@@ -37,7 +37,7 @@ def main(argv=None) -> int:
     except Exception as e:
         print(f"[ping] engine init failed: {e}", file=sys.stderr)
         return 3
-    print(f"[ping] engine initialized in {(time.perf_counter() - t0) * 1000:.0f} ms", file=sys.stderr)
+    log.info(f"[ping] engine initialized in {(time.perf_counter() - t0) * 1000:.0f} ms")
     own = (args.temperature is not None or args.top_k != 0 or args.top_p != 1.0 or args.repetition_penalty != 1.0
            or args.seed != 0)
     if not own:
@@ -60,9 +60,9 @@ def main(argv=None) -> int:
     else:
         print(" ".join(str(t) for t in result.output_ids))
     s = result.stats
-    print(f"[ping] finish={result.finish_reason} prompt={s.prompt_tokens} generated={s.generated_tokens} "
-          f"prefill={s.prefill_time_ms:.2f} ms ({s.prefill_tokens_per_second():.1f} tok/s) "
-          f"decode={s.decode_time_ms:.2f} ms ({s.decode_tokens_per_second():.1f} tok/s)", file=sys.stderr)
+    log.info(f"[ping] finish={result.finish_reason} prompt={s.prompt_tokens} generated={s.generated_tokens} "
+             f"prefill={s.prefill_time_ms:.2f} ms ({s.prefill_tokens_per_second():.1f} tok/s) "
+             f"decode={s.decode_time_ms:.2f} ms ({s.decode_tokens_per_second():.1f} tok/s)")
     if result.error:
         print(f"[ping] error: {result.error}", file=sys.stderr)
         return 2
