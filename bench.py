@@ -238,7 +238,7 @@ def measure_decode_e2e(core, cfg, batch, steps, warmup, run_ahead=True):
         engine.step()
     for r in reqs:
         core.end(r.request_id)
-    return {"tok_s": batch * steps / dt, "ms": dt * 1000.0 / steps, "h2d": int(h2d), "d2h": 4 * batch}
+    return {"tok_s": batch * steps / dt, "ms": dt * 1000.0 / steps, "h2d": int(h2d), "d2h": 4 * (batch + 1)}      # the tokens and the kernels' status word
 
 
 def measure_head(core, cfg, rows, reps=20):

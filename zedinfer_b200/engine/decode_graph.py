@@ -65,7 +65,8 @@ class DecodeGraph:
             seg_start_host=list(range(b)), seg_len_host=[1] * b, seg_pos0_host=[0] * b, slots_host=[-1] * b,
             decode_only=True, max_kv_len=core.max_seq_len)
         self.want = d[self.off_want: self.off_want + b]
-        self.sampled = torch.zeros(b, dtype=torch.int32, device=core.device)
+        # loop: the tokens chosen by the step, and behind them the kernels' status word as the step left it
+        self.sampled = torch.zeros(b + 1, dtype=torch.int32, device=core.device)
         self.launches = 0
         # warm up on a side stream (loads the libraries, lets cuBLAS pick its kernels), then capture
         side = torch.cuda.Stream(device=core.device)
@@ -85,8 +86,10 @@ class DecodeGraph:
     def _body(self) -> torch.Tensor:
         logits = self.core.model.forward(self.ctx, self.core.views, self.want)
         if self.loop:
-            ops.argmax(logits, self.sampled)
-            ops.advance_decode(self.ctx.token_ids, self.ctx.positions, self.sampled)
+            b = self.bucket
+            ops.argmax(logits, self.sampled[:b])
+            self.sampled[b:].copy_(ops.status_word(self.core.device))
+            ops.advance_decode(self.ctx.token_ids, self.ctx.positions, self.sampled[:b])
         return logits
 
     def _pad_rows(self, first: int) -> None:
@@ -99,8 +102,7 @@ class DecodeGraph:
         for g in range(ng):
             base = self.off_tab + g * b * width
             rows = h[base: base + b * width].reshape(b, width)
-            rows[first:, :] = 0
-            rows[first:, 0] = scratch
+            rows[first:, :] = scratch          # wherever a padding row's position points (a looping graph moves it on)
 
     def fill(self, tokens: Sequence[int], rcs: Sequence, reserve_ahead: int = 0) -> None:
         """Refresh the static buffers for these requests (one token each) and upload what changed.
@@ -176,7 +178,8 @@ class DecodeGraph:
         if dirty:
             head = self.off_seg                               # ids and positions stay as the device has them
             self.core._ring.stage_into(h[head:], self.dev[head:])
-        ops.advance_decode(self.ctx.token_ids, self.ctx.positions, sampled, n)
+        if not self.loop:                                     # a looping graph has moved ids and positions on itself
+            ops.advance_decode(self.ctx.token_ids, self.ctx.positions, sampled, n)
         self.graph.replay()
         return self.logits[:n]
 

@@ -146,9 +146,16 @@ class InferenceEngine:
             if self.on_step is not None:
                 self.on_step(batch)
             try:
-                logits = self.core.step(self.entries_for(batch))
-                rows = batch.rows_wanted()
-                chosen = self.sampler.launch(logits, [r for r, _ in rows]) if rows else None
+                entries = self.entries_for(batch)
+                chosen = None
+                if not batch.prefill_requests and all(r.config.use_argmax for r in batch.decode_requests):
+                    picked = self.core.step_greedy(entries)          # step and choice in one graph, where that goes
+                    if picked is not None:
+                        chosen = self.sampler.from_step(picked, len(entries))
+                if chosen is None:
+                    logits = self.core.step(entries)
+                    rows = batch.rows_wanted()
+                    chosen = self.sampler.launch(logits, [r for r, _ in rows]) if rows else None
             except Exception as e:                       # keep serving: fail what was in the step
                 self.scheduler.fail_batch(batch, f"step failed: {e}")
                 if isinstance(e, (torch.cuda.OutOfMemoryError, KeyboardInterrupt)):
@@ -184,14 +191,18 @@ class InferenceEngine:
         return True
 
     def _launch_ahead(self, batch: ScheduledBatch, chosen) -> Optional[Tuple[ScheduledBatch, object]]:
-        logits = self.core.step_ahead([r.request_id for r in batch.decode_requests], chosen.device_tokens)
-        if logits is None:
+        fused = chosen.chosen_with_step
+        out = self.core.step_ahead([r.request_id for r in batch.decode_requests], None if fused else chosen.device_tokens,
+                                   greedy=fused)
+        if out is None:
             return None
         nxt = ScheduledBatch(decode_requests=list(batch.decode_requests))
         if self.on_step is not None:
             self.on_step(nxt)
         self.steps_run_ahead += 1
-        return nxt, self.sampler.launch(logits, nxt.decode_requests, ahead=1)
+        if fused:
+            return nxt, self.sampler.from_step(out, len(nxt.decode_requests))
+        return nxt, self.sampler.launch(out, nxt.decode_requests, ahead=1)
 
     # ---- measurement (src/zedinfer/profiler.cpp:119-162) ------------------------------------
     def profile(self, prefill_len: int, decode_len: int, seed: int = 12345) -> Tuple[float, float]:

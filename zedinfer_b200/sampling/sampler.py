@@ -9,7 +9,7 @@ uniform number of a draw is a function of (request seed, index of the generated 
 from __future__ import annotations
 
 import os
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -40,8 +40,11 @@ def fresh_seed() -> int:
 class PendingTokens:
     """Tokens chosen on the device and on their way to the host; ``wait()`` returns them as a list."""
 
-    def __init__(self, device_tokens: torch.Tensor, host: torch.Tensor, event: torch.cuda.Event):
+    def __init__(self, device_tokens: torch.Tensor, host: torch.Tensor, event: torch.cuda.Event,
+                 rows: Optional[int] = None, chosen_with_step: bool = False):
         self.device_tokens, self._host, self._event = device_tokens, host, event
+        self._rows = host.numel() - 1 if rows is None else rows
+        self.chosen_with_step = chosen_with_step        # the step's own graph chose the tokens (EngineCore.step_greedy)
 
     def wait(self) -> List[int]:
         """The tokens; raises if a kernel of the step reported that one of its bounded waits ran out (the last
@@ -51,7 +54,7 @@ class PendingTokens:
         if values[-1] != 0:
             ops.tcgen05_status(self.device_tokens.device)            # reads and clears the word
             raise ops.KernelError(f"a bounded wait ran out inside a kernel of this step (code {values[-1]}); its output is not valid")
-        return values[:-1]
+        return values[:self._rows]
 
 
 class Sampler:
@@ -68,6 +71,15 @@ class Sampler:
         if self._pinned[self._turn].numel() < rows:
             self._pinned[self._turn] = torch.empty(rows, dtype=torch.int32).pin_memory()
         return self._pinned[self._turn][:rows]
+
+    def from_step(self, tokens_and_status: torch.Tensor, rows: int) -> PendingTokens:
+        """Tokens that the step's own graph chose (``EngineCore.step_greedy``): int32 on the device, the first
+        ``rows`` entries the tokens, the last the kernels' status word.  Starts their copy to the host."""
+        host = self._host_buffer(tokens_and_status.numel())
+        host.copy_(tokens_and_status, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return PendingTokens(tokens_and_status[:rows], host, event, rows=rows, chosen_with_step=True)
 
     def sample(self, logits: torch.Tensor, requests: Sequence) -> List[int]:
         """One token per row of ``logits`` (float32 ``[rows, vocab]``); ``requests[i]`` gives row i's options."""
