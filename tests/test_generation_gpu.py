@@ -345,3 +345,27 @@ def test_engine_default_sampling_comes_from_generation_config_json(models, tmp_p
     monkeypatch.setenv("ZEDINFER_FORCE_ARGMAX", "1")
     forced = InferenceEngine.create(str(folder), sc, dtype="float32")
     assert forced.generate_tokens(prompt, GenerationConfig(max_new_tokens=12, ignore_eos=True)).output_ids == greedy
+
+
+def test_greedy_batch_chooses_inside_the_captured_step(models):
+    """Five greedy requests of different lengths (a bucket of eight: three rows of padding whose positions move on
+    with the others'), decoded with the choice and the hand-over inside the captured step and with steps launched
+    ahead of the host: every request gets the plain implementation's tokens, and the pool is whole afterwards."""
+    from zedinfer_b200 import GenerationConfig, InferenceRequest, SchedulerConfig
+    from zedinfer_b200.engine import InferenceEngine
+    cfg, _ = tiny.CONFIGS["B"]
+    rng = random.Random(77)
+    prompts = [[rng.randrange(cfg["vocab_size"]) for _ in range(n)] for n in (5, 19, 2, 33, 11)]
+    news = [40, 23, 31, 9, 40]
+    engine = InferenceEngine.create(models["B"], SchedulerConfig(num_kv_pages=64, kv_block_size=8, max_batch_requests=8),
+                                    dtype="float32")
+    futs = [engine.submit_async(InferenceRequest(p, GenerationConfig(max_new_tokens=n, ignore_eos=True)))
+            for p, n in zip(prompts, news)]
+    engine.run_loop()
+    for p, n, f in zip(prompts, news, futs):
+        r = f.result()
+        assert r.error is None and r.output_ids == plain_greedy(models["B"], p, n)
+    assert any(greedy for (_, greedy) in engine.core._decode_graphs)
+    assert engine.steps_run_ahead > 10
+    engine.core.cache.check()
+    assert engine.core.cache.num_live == 0
