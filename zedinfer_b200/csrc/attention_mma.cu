@@ -382,9 +382,11 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
 // are masked by position; their cache slots hold finite stale values (the pool is allocated zeroed).
 #define DT_STAGES 3
 
-// byte offset of 16-byte chunk c of row `row` in a [hd halves][rows][128 bytes] tile as TMA writes it
+// A stage of the ring holds one tile as [hd halves][keys | values][rows][128 bytes], so that one TMA box may bring the
+// keys and the values of a half together.  Byte offset of 16-byte chunk c of row `row` of the keys (the values are
+// ROWS * 128 bytes further on):
 template <int ROWS> __device__ __forceinline__ uint32_t swz_tma(int row, int c) {
-    return (uint32_t)((c >> 3) * (ROWS * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4));
+    return (uint32_t)((c >> 3) * (2 * ROWS * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4));
 }
 template <int HD, int NKT>      // NKT * 8 keys per tile
 __device__ __forceinline__ void qk_scores_tma(float (&S)[NKT][4], const uint32_t (&qf)[HD / 16][4], uint32_t sK, int lane) {
@@ -458,7 +460,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
                             const int* __restrict__ tables, const int* __restrict__ tok_seg, const int* __restrict__ pos,
                             int* __restrict__ status, int n_heads, int n_kv_heads, int q_blocks, int page_size,
                             int box_rows, int max_blocks, int window, float scale2, int n_splits, int min_split_tiles,
-                            float* __restrict__ part) {
+                            float* __restrict__ part, int kv_box) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -505,7 +507,9 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
 
     // page numbers of this warp's tiles, 32 at a time: entry e = tile * ppt + page of the tile
     const int ppt = DT_KEYS / box_rows;                           // TMA boxes (pages, or parts of one page) per tile
-    const int ops = 2 * ppt * HH;                                 // loads per tile: k|v x pages x halves
+    // loads per tile: k|v x pages x halves, or, where a tile lies in one page and the map's box takes keys and values
+    // together (kv_box), one per half: issuing a load costs the lane about 60 clocks
+    const int ops = kv_box ? HH : 2 * ppt * HH;
     int id_base = 0, id_reg = -1;
     auto load_ids = [&](int base) {
         id_base = base;
@@ -524,11 +528,12 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
         const uint32_t bar = my_bars + 8 * st;
         if (lane == 0) mbar_expect_tx(bar, STAGE_BYTES);
         __syncwarp();
-        const int kv = lane / (ppt * HH), rem = lane - kv * (ppt * HH), pg = rem / HH, hh = rem - pg * HH;
+        const int kv = kv_box ? 0 : lane / (ppt * HH), rem = lane - kv * (ppt * HH);
+        const int pg = kv_box ? 0 : rem / HH, hh = kv_box ? lane : rem - pg * HH;
         const int page = __shfl_sync(0xffffffffu, id_reg, (tl * ppt + pg - id_base) & 31);
         if (lane < ops) {
             const int key0 = (t_lo + first + tl * CL * 4) * DT_KEYS + pg * box_rows;
-            const uint32_t dst = my_ring + st * STAGE_BYTES + kv * TILE_BYTES + hh * (DT_KEYS * 128) + pg * box_rows * 128;
+            const uint32_t dst = my_ring + st * STAGE_BYTES + hh * (2 * DT_KEYS * 128) + kv * (DT_KEYS * 128) + pg * box_rows * 128;
             tma_load_5d(dst, &map_kv, hh * 64, key0 % page_size, kvh, kv, page, bar);
         }
         __syncwarp();
@@ -563,7 +568,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
     for (int i = 0; i < n_mine; ++i) {
         const int st = i % DT_STAGES;
         if (!mbar_wait_warp(my_bars + 8 * st, (i / DT_STAGES) & 1, nullptr)) { ok = false; failed_at = i; break; }
-        const uint32_t sK = my_ring + st * STAGE_BYTES, sV = sK + TILE_BYTES;
+        const uint32_t sK = my_ring + st * STAGE_BYTES, sV = sK + DT_KEYS * 128;
         const int key0 = (t_lo + first + i * CL * 4) * DT_KEYS;
         float S[DT_KEYS / 8][4];
         qk_scores_tma<HD, DT_KEYS / 8>(S, qf, sK, lane);
@@ -869,7 +874,7 @@ static int dt_max_clusters() {
 struct DtArgs {
     const CUtensorMap* mkv; const void* q; void* out; const int* tables; const int* tok_seg; const int* pos; int* status;
     int n_tokens, n_heads, n_kv_heads, q_blocks, page_size, box_rows, max_blocks, window; float scale2; cudaStream_t stream;
-    int n_splits, min_split_tiles; float* part;
+    int n_splits, min_split_tiles; float* part; int kv_box;
 };
 
 template <int HD, int KEYS, int CL>
@@ -885,7 +890,7 @@ static cudaError_t dt_launch(const DtArgs& a) {
     cfg.dynamicSmemBytes = dt_smem<HD, KEYS>(); cfg.stream = a.stream;
     return cudaLaunchKernelEx(&cfg, decode_attention_tma_kernel<HD, KEYS, CL>, *a.mkv, (const bf16*)a.q, (bf16*)a.out, a.tables,
                               a.tok_seg, a.pos, a.status, a.n_heads, a.n_kv_heads, a.q_blocks, a.page_size, a.box_rows,
-                              a.max_blocks, a.window, a.scale2, a.n_splits, a.min_split_tiles, a.part);
+                              a.max_blocks, a.window, a.scale2, a.n_splits, a.min_split_tiles, a.part, a.kv_box);
 }
 template <int HD>
 static cudaError_t dt_dispatch(const DtArgs& a, int keys, int cl) {
@@ -969,10 +974,11 @@ ZI_EXPORT int zi_decode_attention_tma(const void* q, const void* cache, void* ou
     if ((long long)n_kv_heads * q_blocks * plan.splits > 65535) return zi_fail("decode_attention_tma: too many head blocks for one launch");
     const int keys = plan.keys;
     const int box_rows = page_size < keys ? page_size : keys;
+    const int kv_box = box_rows == keys ? 1 : 0;                  // a tile lies in one page: keys and values in one box
     CUtensorMap mkv;
-    if (tc_map_kv_pages(&mkv, cache, head_dim, page_size, n_kv_heads, n_pages, page_stride, kv_stride, box_rows)) return 1;
+    if (tc_map_kv_pages(&mkv, cache, head_dim, page_size, n_kv_heads, n_pages, page_stride, kv_stride, box_rows, kv_box ? 2 : 1)) return 1;
     DtArgs a = {&mkv, q, out, tables, tok_seg, pos, status, n_tokens, n_heads, n_kv_heads, q_blocks, page_size, box_rows,
-                max_blocks, window, scale * LOG2E, stream, plan.splits, plan.min_split_tiles, part};
+                max_blocks, window, scale * LOG2E, stream, plan.splits, plan.min_split_tiles, part, kv_box};
     cudaError_t e = head_dim == 128 ? dt_dispatch<128>(a, keys, plan.cl) : dt_dispatch<64>(a, keys, plan.cl);
     if (e != cudaSuccess) { cudaGetLastError(); return zi_fail("decode_attention_tma: launch failed: %s", cudaGetErrorString(e)); }
     if (plan.splits > 1) {

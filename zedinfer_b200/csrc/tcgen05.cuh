@@ -159,15 +159,16 @@ static std::map<TcMapKey, CUtensorMap> tc_kv_maps;
 static std::mutex tc_kv_maps_lock;
 
 static inline int tc_map_kv_pages(CUtensorMap* out, const void* cache, int head_dim, int page_size, int n_kv_heads, long long n_pages,
-                                  long long page_stride, long long kv_stride, int box_rows) {
+                                  long long page_stride, long long kv_stride, int box_rows, int box_kv = 1) {
+    // box_kv 2: one box holds the keys and the values of its rows (the keys' rows first)
     std::lock_guard<std::mutex> g(tc_kv_maps_lock);
-    const TcMapKey key(cache, head_dim * 1024LL + box_rows, page_size, n_kv_heads * (1LL << 32) + n_pages, page_stride, kv_stride);
+    const TcMapKey key(cache, head_dim * 1024LL + box_rows + (box_kv == 2 ? 512 : 0), page_size, n_kv_heads * (1LL << 32) + n_pages, page_stride, kv_stride);
     auto it = tc_kv_maps.find(key);
     if (it == tc_kv_maps.end()) {
         if (tc_kv_maps.size() > 4096) tc_kv_maps.clear();
         cuuint64_t dims[5] = {(cuuint64_t)head_dim, (cuuint64_t)page_size, (cuuint64_t)n_kv_heads, 2, (cuuint64_t)n_pages};
         cuuint64_t strides[4] = {(cuuint64_t)head_dim * 2, (cuuint64_t)page_size * head_dim * 2, (cuuint64_t)kv_stride * 2, (cuuint64_t)page_stride * 2};
-        cuuint32_t box[5] = {64, (cuuint32_t)box_rows, 1, 1, 1};
+        cuuint32_t box[5] = {64, (cuuint32_t)box_rows, 1, (cuuint32_t)(box_kv == 2 ? 2 : 1), 1};
         cuuint32_t estr[5] = {1, 1, 1, 1, 1};
         CUtensorMap m;
         CUresult r = tc_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box, estr,
