@@ -18,6 +18,7 @@
 // never makes a round trip through memory.
 #define ZI_PDL_BIT 2
 #include "zi_common.cuh"
+#include <cooperative_groups.h>
 
 ZI_DEFINE_LAST_ERROR(gemm_smallm)
 
@@ -143,12 +144,13 @@ template <int NT, typename TC, bool SILU_MUL>
 __global__ void __launch_bounds__(GS_THREADS, NT == 1 ? 4 : 3)
 gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const bf16* __restrict__ bias,
                    TC* __restrict__ C, float* __restrict__ part, int* __restrict__ counters, int M, int N, int K,
-                   long long ldx, long long ldw, long long ldc) {
+                   long long ldx, long long ldw, long long ldc, int cluster_reduce) {
     // N: number of output columns.  With SILU_MUL, W has 2*N rows (gate rows, then up rows).
     // gridDim.y > 1: K is cut into gridDim.y ranges, one block each; the blocks of a column tile leave their
     // sums in `part` [gridDim.y][16][N] and the last one to arrive adds them in range order.
     __shared__ float red[SILU_MUL ? 2 : 1][GS_WARPS][16][NT * 8 + 1];
     __shared__ int is_last;
+    __shared__ float tile_sum[16][NT * 8 + 1];      // cluster_reduce: this block's sums, read by the first block of the cluster
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row0 = blockIdx.x * 16;
     const int ksplit = gridDim.y, ks = blockIdx.y;
@@ -181,7 +183,24 @@ gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const
     }
     pdl_trigger_late();
     __syncthreads();
-    if (ksplit > 1) {
+    namespace cg = cooperative_groups;
+    if (ksplit > 1 && cluster_reduce) {
+        // The blocks of a column tile are one thread-block cluster (launched so): each leaves its sums in its own
+        // shared memory, and the first adds them in range order through distributed shared memory.  Against the way
+        // through global memory below this saves a fence, an atomic round trip and a read back from L2.
+        for (int i = threadIdx.x; i < 16 * NT * 8; i += GS_THREADS) {
+            const int r = i % 16, m = i / 16;
+            float v = 0.0f;
+#pragma unroll
+            for (int w = 0; w < GS_WARPS; ++w) v += red[0][w][r][m];
+            tile_sum[r][m] = v;
+        }
+        cg::this_cluster().sync();
+        if (ks != 0) {
+            cg::this_cluster().sync();                  // stay until the first block has read
+            return;
+        }
+    } else if (ksplit > 1) {
         // leave this block's sums, then find out whether it is the last of its column tile
         for (int i = threadIdx.x; i < 16 * NT * 8; i += GS_THREADS) {
             const int r = i % 16, m = i / 16;
@@ -207,7 +226,9 @@ gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const
         const int n = row0 + r;
         if (n >= N || m >= M) continue;
         float v = 0.0f;
-        if (ksplit > 1) {
+        if (ksplit > 1 && cluster_reduce) {
+            for (int k2 = 0; k2 < ksplit; ++k2) v += cg::this_cluster().map_shared_rank(&tile_sum[0][0], k2)[r * (NT * 8 + 1) + m];
+        } else if (ksplit > 1) {
             for (int k2 = 0; k2 < ksplit; ++k2) v += ld_l2(part + ((size_t)k2 * 16 + m) * N + n);
         } else {
 #pragma unroll
@@ -225,13 +246,29 @@ gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const
         }
         C[(long long)m * ldc + n] = from_f32<TC>(v);
     }
+    if (ksplit > 1 && cluster_reduce) cg::this_cluster().sync();
 }
 
 template <int NT, typename TC, bool SILU>
 static void launch(const void* X, const void* W, const void* bias, void* C, float* part, int* counters, int ksplit,
                    int M, int N, int K, long long ldx, long long ldw, long long ldc, cudaStream_t stream) {
+    if (ksplit > 1 && ksplit <= 8) {
+        // the K ranges of a column tile as one cluster along y: their sums meet in distributed shared memory
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3((N + 15) / 16, ksplit);
+        cfg.blockDim = dim3(GS_THREADS);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = ksplit; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<NT, TC, SILU>, (const bf16*)X, (const bf16*)W, (const bf16*)bias, (TC*)C,
+                               part, counters, M, N, K, ldx, ldw, ldc, 1) == cudaSuccess) return;
+        cudaGetLastError();                             // no cluster of that shape here: the way through global memory
+    }
     zi_launch(gemm_smallm_kernel<NT, TC, SILU>, dim3((N + 15) / 16, ksplit), dim3(GS_THREADS), 0, stream,
-              (const bf16*)X, (const bf16*)W, (const bf16*)bias, (TC*)C, part, counters, M, N, K, ldx, ldw, ldc);
+              (const bf16*)X, (const bf16*)W, (const bf16*)bias, (TC*)C, part, counters, M, N, K, ldx, ldw, ldc, 0);
 }
 
 // How many ranges K is cut into: a function of the weight's shape only.  Few column tiles (narrow outputs)
@@ -241,7 +278,9 @@ ZI_EXPORT int zi_gemm_smallm_ksplit(int N, int K, int silu_mul) {
     if (silu_mul || tiles >= 296) return 1;
     int ks = (296 + tiles - 1) / tiles;
     if (ks > 8) ks = 8;
-    while (ks > 1 && steps / ks < 8 * GS_WARPS) --ks;      // a split costs a round trip: keep 8 k-steps per warp
+    // a split costs a cluster exchange: keep 6 k-steps per warp (K = 1,536 stays whole: 3.9 us against 4.4 us cut in
+    // two; K = 3,584 is cut in two: 7.6 us against 8.5 us whole)
+    while (ks > 1 && steps / ks < 6 * GS_WARPS) --ks;
     return ks < 1 ? 1 : ks;
 }
 
