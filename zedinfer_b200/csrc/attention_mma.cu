@@ -474,6 +474,19 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
     const int kvh = unit / q_blocks, qb = unit - kvh * q_blocks;
     const int n = blockIdx.z;
     const int group = n_heads / n_kv_heads;
+    const int first = rank + CL * warp;                  // this warp's first tile, counted from the first of its cluster
+    // tok_seg null: token n is segment n (every decode step of the engine).  Without a window and without sharing, a
+    // warp's tiles start at key 0 whatever the position is, so its first page numbers are asked for together with
+    // the position instead of after it: one trip to memory less before the first tile can be fetched.
+    const int* table = tables + (size_t)(tok_seg ? tok_seg[n] : n) * max_blocks;
+    const int ppt = DT_KEYS / box_rows;                           // TMA boxes (pages, or parts of one page) per tile
+    const bool ids_ahead = window == 0 && n_splits == 1;
+    int id_base = 0, id_reg = -1;
+    if (ids_ahead) {
+        const int tl = lane / ppt, pg = lane - tl * ppt;
+        const int blk = ((first + tl * CL * 4) * DT_KEYS + pg * box_rows) / page_size;
+        if (blk < max_blocks) id_reg = table[blk];
+    }
     const int P = pos[n];
     const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
     // The visible tiles may be shared out over several clusters (long contexts of few requests, see dt_splits): as
@@ -484,9 +497,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
     if (split >= eff) return;
     const int per = (v_hi - v_lo + eff) / eff;
     const int t_lo = v_lo + split * per, t_hi = min(v_hi, t_lo + per - 1);
-    const int first = rank + CL * warp;                  // this warp's first tile, counted from t_lo
     const int n_mine = (t_hi - t_lo - first >= 0) ? (t_hi - t_lo - first) / (CL * 4) + 1 : 0;
-    const int* table = tables + (size_t)tok_seg[n] * max_blocks;
 
     // shared memory: ring [4 warps][DT_STAGES][K tile | V tile] (1024-aligned) | Q [16][HD] | mbarriers | result of
     // this block m[16], l[16], O[16][OS]; the merge of the four warps overlays the ring afterwards
@@ -506,11 +517,9 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
     __syncwarp();
 
     // page numbers of this warp's tiles, 32 at a time: entry e = tile * ppt + page of the tile
-    const int ppt = DT_KEYS / box_rows;                           // TMA boxes (pages, or parts of one page) per tile
     // loads per tile: k|v x pages x halves, or, where a tile lies in one page and the map's box takes keys and values
     // together (kv_box), one per half: issuing a load costs the lane about 60 clocks
     const int ops = kv_box ? HH : 2 * ppt * HH;
-    int id_base = 0, id_reg = -1;
     auto load_ids = [&](int base) {
         id_base = base;
         const int e = base + lane, tl = e / ppt, pg = e - tl * ppt;
@@ -538,7 +547,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
         }
         __syncwarp();
     };
-    if (n_mine > 0) load_ids(0);
+    if (n_mine > 0 && !ids_ahead) load_ids(0);
     for (int s = 0; s < DT_STAGES && s < n_mine; ++s) issue(s);
 
     const int rows_valid = (group - qb * 16) < 16 ? (group - qb * 16) : 16;

@@ -423,17 +423,20 @@ def decode_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, ta
 
 
 def decode_attention_tma(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
-                         tok_seg: torch.Tensor, pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                         tok_seg: Optional[torch.Tensor], pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                          page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float,
                          max_kv_len: int = 0) -> None:
     """One query token per request, bfloat16: the cluster kernel with 32-key tiles dealt to single warps, each
     fed by TMA through the block table into a ring of its own.  Same arguments as :func:`decode_attention`;
     head_dim 64 or 128, pages of a power of two from 8 to 128 tokens.  ``max_kv_len``: an upper bound of the cached
-    tokens of the step's requests; with few requests and long contexts several clusters then share one request's
+    tokens of the step's requests; ``tok_seg`` None: token n belongs to row n of ``tables`` (every decode step of the
+    engine; the kernel then asks for its first page numbers without waiting for anything).  With few requests and long contexts several clusters then share one request's
     keys and a second kernel adds their parts (0: never).  A bounded wait that runs out is reported by
     :func:`tcgen05_status`."""
     need_cuda(q, cache, out, tables, tok_seg, pos)
-    need_int32("tables", tables), need_int32("tok_seg", tok_seg), need_int32("pos", pos)
+    need_int32("tables", tables), need_int32("pos", pos)
+    if tok_seg is not None:
+        need_int32("tok_seg", tok_seg)
     need_contiguous("q", q), need_contiguous("out", out)
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("decode_attention_tma: bfloat16 only")
@@ -507,7 +510,8 @@ def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv
     if q.dtype == torch.bfloat16 and head_dim in (64, 128):
         n = q.shape[0]
         if ctx.decode_only and tcgen05_attention_ok(head_dim, cache.page_size):
-            decode_attention_tma(q, cache.tensor, out, tables, ctx.tok_seg, ctx.positions, n_heads, n_kv_heads, head_dim,
+            # in a step of single tokens, token n is segment n
+            decode_attention_tma(q, cache.tensor, out, tables, None, ctx.positions, n_heads, n_kv_heads, head_dim,
                                  cache.page_size, cache.page_stride, cache.kv_stride, window, scale,
                                  max_kv_len=min(ctx.max_kv_len, window) if window else ctx.max_kv_len)
             return
@@ -518,9 +522,12 @@ def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv
         tiles = ctx.extras.get("attn_tiles")
         lead = ctx.extras.get("leading_singles", 0) if tiles is not None else 0
         if lead:                                  # decoding requests beside a prompt portion: their own kernel
-            fn = decode_attention_tma if tcgen05_attention_ok(head_dim, cache.page_size) else decode_attention
-            fn(q[:lead], cache.tensor, out[:lead], tables, ctx.tok_seg[:lead], ctx.positions[:lead], n_heads, n_kv_heads,
-               head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
+            if tcgen05_attention_ok(head_dim, cache.page_size):     # the leading single tokens are segments 0 .. lead - 1
+                decode_attention_tma(q[:lead], cache.tensor, out[:lead], tables, None, ctx.positions[:lead], n_heads,
+                                     n_kv_heads, head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
+            else:
+                decode_attention(q[:lead], cache.tensor, out[:lead], tables, ctx.tok_seg[:lead], ctx.positions[:lead], n_heads,
+                                 n_kv_heads, head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
         if tiles is not None and tcgen05_attention_ok(head_dim, cache.page_size):
             prefill_attention_tcgen05(q, cache.tensor, out, tables, tiles, ctx.positions, n_heads, n_kv_heads, head_dim,
                                       cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
