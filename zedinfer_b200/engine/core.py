@@ -20,6 +20,7 @@ from ..cache.manager import CacheManager, RequestCache
 from ..config.registry import load_model_config
 from ..parts.base import StepContext
 from ..weights.loader import load_weights
+from .descriptor import pack_step, step_padding, step_signature
 from .model import Model
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -116,92 +117,18 @@ def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache]
                        table_width: int, dtype: torch.dtype, device: torch.device, vocab: int,
                        ring: "PinnedStaging", pad_segments: int = 0,
                        into: Optional[torch.Tensor] = None) -> Tuple[StepContext, Optional[torch.Tensor]]:
-    """Flatten the entries into one device descriptor (a single host-to-device copy).  ``into``: a device buffer
-    to hold the descriptor (a captured step's static buffer) instead of a fresh one; its length must fit."""
-    n_seg = len(entries) + pad_segments
-    n_tok = sum(len(e.tokens) for e in entries) + pad_segments
-    width = table_width
+    """Flatten the entries into one device descriptor (a single host-to-device copy; the layout is
+    ``descriptor.pack_step``'s).  ``into``: a device buffer to hold the descriptor (a captured step's static buffer)
+    instead of a fresh one; its length must fit."""
     n_groups = len(cache.groups)
-    # padding tokens want their logits too (rows nobody reads, at the end of the wanted rows): the number of wanted
-    # rows then depends on the padded count of single tokens, not on how many of them are real
-    n_real_want = sum(len(e.want) for e in entries)
-    n_want = n_real_want + pad_segments
-    # Single-token entries at the head of a step that also holds longer ones (decoding requests beside a prompt
-    # portion) are left to the decode attention kernel; the padding tokens stand right behind them, so that their
-    # number depends on the step's counts alone.  Attention tiles cover the rest.
-    lead_real = lead = 0
-    if any(len(e.tokens) != 1 for e in entries):
-        while len(entries[lead_real].tokens) == 1:
-            lead_real += 1
-        lead = lead_real + pad_segments
-    # layout: ids | pos | tok_seg | want rows | slots | attention tiles | tables[g]...
-    tile_rows = ops.PREFILL_TILE_ROWS
-    if lead:
-        n_tiles = sum(-(-len(e.tokens) // tile_rows) for e in entries[lead_real:])
-    else:
-        n_tiles = sum(-(-len(e.tokens) // tile_rows) for e in entries) + pad_segments
-    off_ids, off_pos, off_seg = 0, n_tok, 2 * n_tok
-    off_want = 3 * n_tok
-    off_slots = off_want + n_want
-    off_tiles = off_slots + n_seg
-    off_tab = off_tiles + 3 * n_tiles
-    total = off_tab + n_groups * n_seg * width
-    host = np.zeros(total, dtype=np.int32)
-    seg_start, seg_len, seg_pos0, slots = [], [], [], []
-    t = 0
-    w = 0
-    s = 0
-    max_kv = 0
-    n_tile_done = 0
-    scratch = cache.scratch_page if cache.groups else 0
-
-    pad_rows = []
-
-    def pad_tokens(t, s, n_tile_done):           # padding: one token each at position 0 of the scratch page
-        for _ in range(pad_segments):
-            pad_rows.append(t)
-            host[off_seg + t] = s
-            host[off_slots + s] = -1
-            for g in range(n_groups):
-                host[off_tab + (g * n_seg + s) * width] = scratch
-            if not lead:
-                host[off_tiles + 3 * n_tile_done: off_tiles + 3 * n_tile_done + 3] = (t, 1, s)
-                n_tile_done += 1
-            seg_start.append(t), seg_len.append(1), seg_pos0.append(0), slots.append(-1)
-            t, s = t + 1, s + 1
-        return t, s, n_tile_done
-
-    for i, (e, rc) in enumerate(zip(entries, rcs)):
-        if lead and i == lead_real:
-            t, s, n_tile_done = pad_tokens(t, s, n_tile_done)
-        toks = np.asarray(e.tokens, dtype=np.int64)
-        k = toks.size
-        if k and (toks.min() < 0 or toks.max() >= vocab):
-            raise ValueError(f"request {e.request_id!r}: token id outside [0, {vocab})")
-        host[off_ids + t: off_ids + t + k] = toks
-        host[off_pos + t: off_pos + t + k] = np.arange(rc.length, rc.length + k, dtype=np.int32)
-        host[off_seg + t: off_seg + t + k] = s
-        for j in e.want:
-            if not 0 <= j < k:
-                raise ValueError(f"request {e.request_id!r}: wanted place {j} is outside its {k} tokens")
-            host[off_want + w] = t + j
-            w += 1
-        host[off_slots + s] = rc.slot
-        for g in range(n_groups):
-            tab = rc.tables[g]
-            base = off_tab + (g * n_seg + s) * width
-            host[base: base + len(tab)] = tab
-        if not (lead and i < lead_real):
-            for q0 in range(0, k, tile_rows):
-                host[off_tiles + 3 * n_tile_done: off_tiles + 3 * n_tile_done + 3] = (t + q0, min(tile_rows, k - q0), s)
-                n_tile_done += 1
-        seg_start.append(t), seg_len.append(k), seg_pos0.append(rc.length), slots.append(rc.slot)
-        max_kv = max(max_kv, rc.length + k)
-        t += k
-        s += 1
-    if not lead:
-        t, s, n_tile_done = pad_tokens(t, s, n_tile_done)
-    host[off_want + w: off_want + w + len(pad_rows)] = pad_rows
+    host, lay = pack_step([e.request_id for e in entries], [e.tokens for e in entries], [e.want for e in entries],
+                          [rc.length for rc in rcs], [rc.slot for rc in rcs], [rc.tables for rc in rcs], n_groups,
+                          table_width, vocab, cache.scratch_page if cache.groups else 0, ops.PREFILL_TILE_ROWS, pad_segments)
+    n_seg, n_tok, width, total = lay.n_seg, lay.n_tok, lay.width, lay.total
+    off_ids, off_pos, off_seg, off_want = lay.off_ids, lay.off_pos, lay.off_seg, lay.off_want
+    off_slots, off_tiles, off_tab = lay.off_slots, lay.off_tiles, lay.off_tab
+    n_want, n_real_want, n_tiles, lead = lay.n_want, lay.n_real_want, lay.n_tiles, lay.lead
+    seg_start, seg_len, seg_pos0, slots, max_kv = lay.seg_start, lay.seg_len, lay.seg_pos0, lay.slots, lay.max_kv
     if into is None:
         dev = ring.stage(host, device)
     else:
@@ -327,31 +254,11 @@ class EngineCore:
     GPU_BOUND_RATIO = 1.25          # device time over host launch time from which a step shape is left eager
 
     def _step_padding(self, entries: Sequence[StepEntry]) -> int:
-        """Single-token segments (decoding requests beside a prompt portion) are padded to a power of two with
-        tokens on the cache's scratch page, so that fewer different counts occur."""
-        singles = sum(1 for e in entries if len(e.tokens) == 1)
-        if singles == 0 or singles == len(entries):
-            return 0
-        bucket = 1
-        while bucket < singles:
-            bucket *= 2
-        return bucket - singles
+        return step_padding([len(e.tokens) for e in entries])
 
     def _step_signature(self, entries: Sequence[StepEntry], pad: int) -> tuple:
-        """The counts that every launch of the step depends on: tokens, segments, the single-token entries at its
-        head (padding included) that the decode attention kernel takes, attention tiles of the rest, wanted rows."""
-        rows = ops.PREFILL_TILE_ROWS
-        lens = [len(e.tokens) for e in entries]
-        lead = 0
-        if any(k != 1 for k in lens):
-            while lens[lead] == 1:
-                lead += 1
-            tiles = sum(-(-k // rows) for k in lens[lead:])
-            lead += pad
-        else:
-            tiles = len(lens) + pad
-        return (sum(lens) + pad, len(lens) + pad, lead, tiles, sum(len(e.want) for e in entries) + pad,
-                lead == 0 and all(k == 1 for k in lens))
+        return step_signature([len(e.tokens) for e in entries], sum(len(e.want) for e in entries), pad,
+                              ops.PREFILL_TILE_ROWS)
 
     def _eager_or_captured(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache]) -> Optional[torch.Tensor]:
         """A step whose counts recur is replayed as a CUDA graph, if that can gain anything: its first appearance
