@@ -181,3 +181,24 @@ def test_failed_step_fails_its_requests_and_serving_goes_on():
     s.submit(b)
     _, _ = run_step(s, cache)
     assert b.output_ids == [7]
+
+
+def test_a_raising_stream_callback_ends_its_own_request_only():
+    s, cache = make()
+    seen = []
+
+    def bad(tok):
+        seen.append(tok)
+        if len(seen) == 2:
+            raise RuntimeError("consumer went away")
+    a = InferenceRequest(list(range(1, 6)), GenerationConfig(max_new_tokens=5), stream_callback=bad)
+    b = req(5, max_new=5)
+    s.submit(a), s.submit(b)
+    for _ in range(12):
+        if not s.has_work():
+            break
+        run_step(s, cache)
+    assert a.finish_reason == "error" and "stream callback raised" in a.error and len(a.output_ids) == 2
+    assert b.finish_reason == "length" and len(b.output_ids) == 5
+    cache.check()
+    assert cache.num_live == 0

@@ -229,7 +229,16 @@ class Scheduler:
                 print(f"[token] request={req.request_id} index={len(req.output_ids) - 1} id={tok}", file=sys.stderr)
             req.prefill_progress = len(req.sequence()) - 1        # all but the token just sampled are cached
             if req.stream_callback is not None:
-                req.stream_callback(tok)
+                try:
+                    req.stream_callback(tok)
+                except Exception as e:             # the caller's code: this request ends, the others go on
+                    if req in self.active:
+                        self.active.remove(req)
+                    with self._lock:
+                        if req in self.waiting:
+                            self.waiting.remove(req)
+                    self._complete(req, "error", f"stream callback raised: {e!r}")
+                    continue
             if req.cancelled:
                 self._finish_active(req, "cancelled")
             elif tok in self.stop_token_ids and not req.config.ignore_eos:
