@@ -338,31 +338,35 @@ class EngineCore:
             raise
         return rcs
 
-    def decode_graph(self, n: int, greedy: bool = False) -> "DecodeGraph":
+    def decode_graph(self, n: int, greedy: bool = False, sample: bool = False) -> "DecodeGraph":
         """The captured decode step for ``n`` requests (bucket: the next power of two).  ``greedy``: the form that
-        also chooses the most likely token of every row and hands it to the next step on the device."""
+        also chooses the most likely token of every row and hands it to the next step on the device; ``sample``: the
+        same with a draw by each row's own options."""
         from .decode_graph import DecodeGraph
         bucket = 1
         while bucket < n:
             bucket *= 2
         bucket = min(bucket, max(self.max_requests, n))
-        key = (bucket, bool(greedy))
+        key = (bucket, "sample" if sample else bool(greedy))
         g = self._decode_graphs.get(key)
         if g is None:
-            g = DecodeGraph(self, bucket, loop=bool(greedy))
+            g = DecodeGraph(self, bucket, loop=bool(greedy), sample=bool(sample))
             self._decode_graphs[key] = g
         return g
 
-    def step_greedy(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step_greedy(self, entries: Sequence[StepEntry], sampling=None) -> Optional[torch.Tensor]:
         """A decode-only step of requests that all take their most likely token: step and choice are one captured
-        graph.  Returns int32 ``[bucket + 1]`` on the device (bucket >= n): the requests' tokens in the first n places,
+        graph.  ``sampling``: ``(par, top_k)`` as ``DecodeGraph.set_sampling`` takes them; the rows are then drawn by
+        their own options instead (the sampling kernel inside the graph).  Returns int32 ``[bucket + 1]`` on the device (bucket >= n): the requests' tokens in the first n places,
         the kernels' status word in the last; or None when the step is not of that kind (the caller then uses
         :meth:`step` and samples himself)."""
         if not (entries and self.cuda_graphs and self.capture_safe and len(entries) <= self.max_requests
                 and all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries)):
             return None
         rcs = self.prepare(entries)
-        g = self.decode_graph(len(entries), greedy=True)
+        g = self.decode_graph(len(entries), greedy=sampling is None, sample=sampling is not None)
+        if sampling is not None:
+            g.set_sampling(*sampling)
         g.run(entries, rcs)
         self._last_decode_graph = g
         for rc in rcs:
@@ -373,19 +377,20 @@ class EngineCore:
     def _chosen(g: "DecodeGraph", n: int) -> torch.Tensor:
         return g.sampled            # [bucket + 1]: the first n entries are the requests' tokens, the last the status word
 
-    def step_ahead(self, request_ids: Sequence, sampled: Optional[torch.Tensor], greedy: bool = False
-                   ) -> Optional[torch.Tensor]:
+    def step_ahead(self, request_ids: Sequence, sampled: Optional[torch.Tensor], greedy: bool = False,
+                   sampling=None) -> Optional[torch.Tensor]:
         """One more decode step for exactly the requests of the decode step just launched, fed on the device with
         the tokens that step chose (``sampled``, int32, one per request) so the host need not have read them yet.
         Returns the logits, or None when this cannot be done (other requests in the captured step's rows, no page
-        left): the caller then takes the ordinary path.  ``greedy``: the step before came from :meth:`step_greedy`
-        (its graph has handed the tokens on itself); the return value is then as that method's."""
+        left): the caller then takes the ordinary path.  ``greedy`` / ``sampling``: the step before came from
+        :meth:`step_greedy` in that form (its graph has handed the tokens on itself); the return value is then as that
+        method's."""
         from ..cache.pool import OutOfPages
         rcs = [self.cache.get(rid) for rid in request_ids]
         if (not rcs or any(rc is None for rc in rcs) or not self.cuda_graphs or not self.capture_safe
                 or len(rcs) > self.max_requests):
             return None
-        g = self.decode_graph(len(rcs), greedy=greedy)
+        g = self.decode_graph(len(rcs), greedy=greedy and sampling is None, sample=sampling is not None)
         if (not g.holds(rcs) or g is not self._last_decode_graph
                 or any(rc.length + 1 > self.max_seq_len for rc in rcs)):
             return None
@@ -394,10 +399,12 @@ class EngineCore:
                 self.cache.ensure(rc, rc.length + 1)
         except OutOfPages:
             return None
+        if sampling is not None:
+            g.set_sampling(*sampling)
         logits = g.run_ahead(rcs, sampled)
         for rc in rcs:
             self.cache.commit(rc, rc.length + 1)
-        return self._chosen(g, len(rcs)) if greedy else logits
+        return self._chosen(g, len(rcs)) if (greedy or sampling is not None) else logits
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one batch; returns float32 logits ``[wanted, vocab]`` on the device, or None if nothing is wanted."""

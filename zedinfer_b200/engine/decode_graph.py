@@ -42,8 +42,11 @@ def capturing(graph: "torch.cuda.CUDAGraph", pool=None):
 
 
 class DecodeGraph:
-    def __init__(self, core, bucket: int, loop: bool = False):
-        self.core, self.bucket, self.loop = core, bucket, loop
+    def __init__(self, core, bucket: int, loop: bool = False, sample: bool = False):
+        """``loop``: the graph also chooses a token per row and hands it to the next step on the device; the most
+        likely token, or with ``sample`` a draw with the row's temperature, top-k, top-p and uniform number, which
+        :meth:`set_sampling` brings before a replay (rows of temperature 0 take the most likely token)."""
+        self.core, self.bucket, self.loop, self.sample = core, bucket, loop or sample, sample
         b, width, ng = bucket, core.table_width, len(core.cache.groups)
         self.off_ids, self.off_pos, self.off_seg, self.off_want, self.off_slots = 0, b, 2 * b, 3 * b, 4 * b
         self.off_tab = 5 * b
@@ -67,6 +70,12 @@ class DecodeGraph:
         self.want = d[self.off_want: self.off_want + b]
         # loop: the tokens chosen by the step, and behind them the kernels' status word as the step left it
         self.sampled = torch.zeros(b + 1, dtype=torch.int32, device=core.device)
+        # sample: temperature | top_p | uniform (float32 bits) | top_k, one row of b each, sent in one copy
+        self.par_host = np.zeros(4 * b, dtype=np.int32)
+        self.par_host[b: 2 * b] = np.float32(1.0).view(np.int32)
+        self.par = torch.zeros(4 * b, dtype=torch.int32, device=core.device)
+        if sample:
+            core._ring.stage_into(self.par_host, self.par)
         self.launches = 0
         # warm up on a side stream (loads the libraries, lets cuBLAS pick its kernels), then capture
         side = torch.cuda.Stream(device=core.device)
@@ -87,10 +96,26 @@ class DecodeGraph:
         logits = self.core.model.forward(self.ctx, self.core.views, self.want)
         if self.loop:
             b = self.bucket
-            ops.argmax(logits, self.sampled[:b])
+            if self.sample:
+                fl = self.par[:3 * b].view(torch.float32)
+                ops.sample(logits, self.sampled[:b], fl[:b], self.par[3 * b:], fl[b: 2 * b], fl[2 * b: 3 * b])
+            else:
+                ops.argmax(logits, self.sampled[:b])
             self.sampled[b:].copy_(ops.status_word(self.core.device))
             ops.advance_decode(self.ctx.token_ids, self.ctx.positions, self.sampled[:b])
         return logits
+
+    def set_sampling(self, par: np.ndarray, top_k: np.ndarray) -> None:
+        """``par`` float32 ``[3, n]`` (temperature, top_p, uniform number) and ``top_k`` int32 ``[n]`` for the first n
+        rows of the next replay; the rows behind them are greedy."""
+        b, n = self.bucket, par.shape[1]
+        h = self.par_host
+        h[:] = 0
+        h[b: 2 * b] = np.float32(1.0).view(np.int32)
+        for k in range(3):
+            h[k * b: k * b + n] = np.ascontiguousarray(par[k], dtype=np.float32).view(np.int32)
+        h[3 * b: 3 * b + n] = top_k
+        self.core._ring.stage_into(h, self.par)
 
     def _pad_rows(self, first: int) -> None:
         b, width, ng = self.bucket, self.core.table_width, len(self.core.cache.groups)

@@ -148,10 +148,17 @@ class InferenceEngine:
             try:
                 entries = self.entries_for(batch)
                 chosen = None
-                if not batch.prefill_requests and all(r.config.use_argmax for r in batch.decode_requests):
-                    picked = self.core.step_greedy(entries)          # step and choice in one graph, where that goes
+                if not batch.prefill_requests and batch.decode_requests:
+                    # step and choice in one graph, where that goes: greedy rows by argmax, else each row's own draw
+                    sampling = None
+                    fused = True
+                    if not all(r.config.use_argmax for r in batch.decode_requests):
+                        sampling = self.sampler.params(batch.decode_requests)
+                        fused = sampling is not None
+                    picked = self.core.step_greedy(entries, sampling) if fused else None
                     if picked is not None:
                         chosen = self.sampler.from_step(picked, len(entries))
+                        chosen.drawn = sampling is not None
                 if chosen is None:
                     logits = self.core.step(entries)
                     rows = batch.rows_wanted()
@@ -192,8 +199,11 @@ class InferenceEngine:
 
     def _launch_ahead(self, batch: ScheduledBatch, chosen) -> Optional[Tuple[ScheduledBatch, object]]:
         fused = chosen.chosen_with_step
+        sampling = None
+        if fused and getattr(chosen, "drawn", False):
+            sampling = self.sampler.params(batch.decode_requests, ahead=1)
         out = self.core.step_ahead([r.request_id for r in batch.decode_requests], None if fused else chosen.device_tokens,
-                                   greedy=fused)
+                                   greedy=fused, sampling=sampling)
         if out is None:
             return None
         nxt = ScheduledBatch(decode_requests=list(batch.decode_requests))
@@ -201,7 +211,9 @@ class InferenceEngine:
             self.on_step(nxt)
         self.steps_run_ahead += 1
         if fused:
-            return nxt, self.sampler.from_step(out, len(nxt.decode_requests))
+            pending = self.sampler.from_step(out, len(nxt.decode_requests))
+            pending.drawn = sampling is not None
+            return nxt, pending
         return nxt, self.sampler.launch(out, nxt.decode_requests, ahead=1)
 
     # ---- measurement (src/zedinfer/profiler.cpp:119-162) ------------------------------------

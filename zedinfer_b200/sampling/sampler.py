@@ -45,6 +45,7 @@ class PendingTokens:
         self.device_tokens, self._host, self._event = device_tokens, host, event
         self._rows = host.numel() - 1 if rows is None else rows
         self.chosen_with_step = chosen_with_step        # the step's own graph chose the tokens (EngineCore.step_greedy)
+        self.drawn = False                              # ... by the rows' own sampling options, not all by argmax
 
     def wait(self) -> List[int]:
         """The tokens; raises if a kernel of the step reported that one of its bounded waits ran out (the last
@@ -80,6 +81,26 @@ class Sampler:
         event = torch.cuda.Event()
         event.record()
         return PendingTokens(tokens_and_status[:rows], host, event, rows=rows, chosen_with_step=True)
+
+    @staticmethod
+    def params(requests: Sequence, ahead: int = 0):
+        """The rows' options as arrays: float32 ``[3, rows]`` (temperature, 0 for greedy rows; top_p; the uniform
+        number of this draw) and int32 ``[rows]`` (top_k); None if a row needs a repetition penalty, which works on
+        the logits with the tokens generated so far and is not part of these."""
+        rows = len(requests)
+        par = np.zeros((3, rows), dtype=np.float32)
+        par[1, :] = 1.0
+        top_k = np.zeros(rows, dtype=np.int32)
+        for i, r in enumerate(requests):
+            c = r.config
+            if c.use_argmax:
+                continue
+            if c.repetition_penalty != 1.0:
+                return None
+            par[0, i], par[1, i] = c.temperature, c.top_p
+            par[2, i] = uniform_for(r.sample_seed, len(r.output_ids) + ahead)
+            top_k[i] = c.top_k
+        return par, top_k
 
     def sample(self, logits: torch.Tensor, requests: Sequence) -> List[int]:
         """One token per row of ``logits`` (float32 ``[rows, vocab]``); ``requests[i]`` gives row i's options."""
