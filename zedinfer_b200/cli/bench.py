@@ -19,7 +19,6 @@ def main(argv=None) -> int:
     if args.decode_len <= 0:
         print("--decode-len/--max-tokens must be > 0 for benchmark runs", file=sys.stderr)
         return 1
-    from ..engine import InferenceEngine
     engine = create_engine(args)
     for _ in range(2):                                                     # warm-up with the same lengths, twice:
         engine.profile(args.prefill_len, args.decode_len)                  # a recurring step is captured at its second run

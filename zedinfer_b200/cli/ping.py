@@ -30,7 +30,6 @@ def main(argv=None) -> int:
         print("--max-new-tokens/--max-tokens must be >= 0", file=sys.stderr)
         return 1
     from .. import GenerationConfig
-    from ..engine import InferenceEngine
     t0 = time.perf_counter()
     try:
         engine = create_engine(args)

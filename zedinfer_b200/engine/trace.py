@@ -42,7 +42,6 @@ def main(argv: Optional[List[str]] = None) -> int:
         return 2
     os.makedirs(args.out, exist_ok=True)
 
-    import numpy as np
     import torch  # noqa: F401
 
     from ..csrc import build

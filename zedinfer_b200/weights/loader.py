@@ -14,7 +14,7 @@ float32, which is exact.  Integer tables become int32.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Mapping, Optional, Tuple
+from typing import Dict, List, Mapping, Tuple
 
 import torch
 
