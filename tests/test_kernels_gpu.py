@@ -63,6 +63,19 @@ def test_rmsnorm_and_fused_add(hidden, dtype):
     assert torch.allclose(out4.float().cpu(), P.rms_norm(x.float().cpu(), w.float().cpu(), eps), atol=tol, rtol=tol)
 
 
+@pytest.mark.parametrize("types", [("float32", "float32", "float32"), ("bfloat16", "bfloat16", "bfloat16"),
+                                   ("float32", "bfloat16", "float32")])
+def test_add(types):
+    from zedinfer_b200 import ops
+    a = rand(7, 1003, dtype=DT[types[0]], scale=3.0)
+    b = rand(7, 1003, dtype=DT[types[1]], seed=1)
+    out = torch.empty(7, 1003, dtype=DT[types[2]], device=dev())
+    ops.add(a, b, out)
+    assert torch.equal(out, (a.float() + b.float()).to(DT[types[2]]))
+    with pytest.raises(ops.KernelError, match="shapes"):
+        ops.add(a, b[:3].contiguous(), out)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("rows,inter", [(5, 176), (3, 8960), (1, 7)])
 def test_silu_mul(dtype, rows, inter):

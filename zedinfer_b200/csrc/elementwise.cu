@@ -424,3 +424,26 @@ ZI_EXPORT int zi_cast(const void* in, int in_dtype, void* out, int out_dtype, lo
     }););
     return zi_check_launch("cast");
 }
+
+// ---------------------------------------------------------------------------------------
+// out = a + b, elementwise, in float32 with one rounding (src/backend/ops/add/cpu/add_cpu.cpp; the reference's GPU
+// kernel adds in the storage type).  The engine folds its residual adds into the norm that follows them; this
+// stands alone for callers of the op.
+// ---------------------------------------------------------------------------------------
+template <typename TA, typename TB, typename TO>
+__global__ void add_kernel(const TA* __restrict__ a, const TB* __restrict__ b, TO* __restrict__ out, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = from_f32<TO>(to_f32<TA>(a[i]) + to_f32<TB>(b[i]));
+}
+
+ZI_EXPORT int zi_add(const void* a, int a_dtype, const void* b, int b_dtype, void* out, int out_dtype, long long total,
+                     cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const int threads = 256;
+    const long long want = (total + threads - 1) / threads;
+    const int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
+    ZI_DISPATCH(a_dtype, TA, ZI_DISPATCH(b_dtype, TB, ZI_DISPATCH(out_dtype, TO, {
+        add_kernel<TA, TB, TO><<<blocks, threads, 0, stream>>>((const TA*)a, (const TB*)b, (TO*)out, (size_t)total);
+    });););
+    return zi_check_launch("add");
+}

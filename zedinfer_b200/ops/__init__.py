@@ -25,7 +25,7 @@ _gemm_tcgen05 = Library("gemm_tcgen05")
 _attention_tcgen05 = Library("attention_tcgen05")
 SMALL_M_ROWS = 16                # the weight-streaming kernel takes up to this many rows
 
-__all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "rope_table", "gemm_smallm_rope", "can_fuse_rope_product", "silu_mul", "cast",
+__all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "rope_table", "gemm_smallm_rope", "can_fuse_rope_product", "silu_mul", "add", "cast",
            "gemm_nt", "linear", "gemm_smallm", "gemm_tcgen05", "gemm_tcgen05_tiles", "tcgen05_status", "status_word", "linear_silu_mul", "raise_if_tcgen05_failed", "paged_attention", "attention", "decode_attention", "decode_attention_tma", "prefill_attention", "prefill_attention_tcgen05", "argmax", "sample", "repetition_penalty", "advance_decode"]
 
 
@@ -143,6 +143,16 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
         raise KernelError(f"silu_mul: gate_up {tuple(gate_up.shape)} vs out {tuple(out.shape)}")
     _elementwise.call("zi_silu_mul", ptr(gate_up), ptr(out), c_int(dtype_code(out.dtype)), c_int(rows),
                       c_int(two_i // 2), stream())
+
+
+def add(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = a + b`` elementwise (float32 or bfloat16 each), added in float32 with one rounding."""
+    need_cuda(a, b, out)
+    need_contiguous("a", a), need_contiguous("b", b), need_contiguous("out", out)
+    if a.shape != b.shape or a.shape != out.shape:
+        raise KernelError(f"add: shapes {tuple(a.shape)}, {tuple(b.shape)}, {tuple(out.shape)} differ")
+    _elementwise.call("zi_add", ptr(a), c_int(dtype_code(a.dtype)), ptr(b), c_int(dtype_code(b.dtype)), ptr(out),
+                      c_int(dtype_code(out.dtype)), c_ll(a.numel()), stream())
 
 
 def cast(x: torch.Tensor, out: torch.Tensor) -> None:
