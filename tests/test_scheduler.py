@@ -202,3 +202,21 @@ def test_a_raising_stream_callback_ends_its_own_request_only():
     assert b.finish_reason == "length" and len(b.output_ids) == 5
     cache.check()
     assert cache.num_live == 0
+
+
+def test_a_preempted_request_waits_behind_the_one_in_mid_prompt():
+    """Pages run out while another request is in the middle of its prompt: that request holds its pages and is the
+    only one the admission looks at, so the preempted one queues behind it; both finish.  (At the very head it would
+    find too few free pages with nothing running, and fail as one that can never fit.)"""
+    s, cache = make(pages=8, page_size=4, max_prefill_tokens=4, max_batch_tokens=64)
+    a, b = req(8, max_new=20), req(20, max_new=3)
+    s.submit(a), s.submit(b)
+    for _ in range(200):
+        if not s.has_work():
+            break
+        run_step(s, cache)
+    assert s.num_preemptions >= 1 and a.stats.preemptions >= 1
+    assert a.finish_reason == "length" and a.error is None and len(a.output_ids) == 20
+    assert b.finish_reason == "length" and len(b.output_ids) == 3
+    cache.check()
+    assert cache.num_live == 0

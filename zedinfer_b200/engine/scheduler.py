@@ -115,7 +115,13 @@ class Scheduler:
         req.stats.preemptions += 1
         self.num_preemptions += 1
         self.active.remove(req)
-        self.waiting.appendleft(req)
+        # to the head of the queue, but behind a request that is in the middle of its prompt: that one holds its
+        # pages and is the only one the admission looks at, so it has to stay first or neither could go on
+        with self._lock:
+            at = 0
+            while at < len(self.waiting) and self.waiting[at].cache is not None:
+                at += 1
+            self.waiting.insert(at, req)
 
     def cancel(self, req: InferenceRequest) -> None:
         req.cancelled = True
