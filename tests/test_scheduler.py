@@ -220,3 +220,33 @@ def test_a_preempted_request_waits_behind_the_one_in_mid_prompt():
     assert b.finish_reason == "length" and len(b.output_ids) == 3
     cache.check()
     assert cache.num_live == 0
+
+
+def test_random_workloads_always_finish_when_every_request_fits_alone():
+    """Random prompts, limits, portion sizes and pool sizes (never smaller than the largest request needs alone):
+    with preemption every request finishes with all its tokens, no page is lost, and the number of steps stays
+    within what recomputation can cost."""
+    import random
+    rng = random.Random(4)
+    for trial in range(150):
+        page = rng.choice([2, 4, 8])
+        n = rng.randrange(1, 10)
+        prompts = [rng.randrange(1, 40) for _ in range(n)]
+        news = [rng.randrange(1, 25) for _ in range(n)]
+        biggest = max(-(-(p + m) // page) for p, m in zip(prompts, news))
+        total = sum(-(-(p + m) // page) for p, m in zip(prompts, news))
+        pages = max(biggest, int(total * rng.choice([0.3, 0.6, 1.0]))) + rng.randrange(0, 2)
+        s, cache = make(pages=pages, page_size=page, max_seq_len=128, max_prefill_tokens=rng.choice([3, 8, 64]),
+                        max_batch_tokens=rng.choice([16, 64]), max_batch_requests=rng.choice([2, 4, 64]))
+        reqs = [req(p, max_new=m) for p, m in zip(prompts, news)]
+        for r in reqs:
+            s.submit(r)
+        steps = 0
+        while s.has_work():
+            run_step(s, cache)
+            steps += 1
+            assert steps < 20000, (trial, "no progress")
+        for r, m in zip(reqs, news):
+            assert r.finish_reason == "length" and r.error is None and len(r.output_ids) == m, (trial, r.error)
+        cache.check()
+        assert cache.num_live == 0
