@@ -250,3 +250,36 @@ def test_random_workloads_always_finish_when_every_request_fits_alone():
             assert r.finish_reason == "length" and r.error is None and len(r.output_ids) == m, (trial, r.error)
         cache.check()
         assert cache.num_live == 0
+
+
+def test_random_workloads_with_failures_and_cancellations_lose_no_page():
+    """The reference's policy (fail the request whose decode finds no page) and requests cancelled at random moments:
+    every request ends one way or another, nothing stays live, and the pool is whole."""
+    import random
+    rng = random.Random(11)
+    for trial in range(120):
+        page = rng.choice([2, 4, 8])
+        n = rng.randrange(1, 10)
+        prompts = [rng.randrange(1, 40) for _ in range(n)]
+        news = [rng.randrange(1, 25) for _ in range(n)]
+        total = sum(-(-(p + m) // page) for p, m in zip(prompts, news))
+        pages = max(2, int(total * rng.choice([0.2, 0.5, 1.0])))
+        s, cache = make(pages=pages, page_size=page, max_seq_len=128, max_prefill_tokens=rng.choice([3, 8, 64]),
+                        max_batch_tokens=rng.choice([16, 64]), max_batch_requests=rng.choice([2, 4, 64]),
+                        on_exhaust=rng.choice(["fail", "preempt"]))
+        reqs = [req(p, max_new=m) for p, m in zip(prompts, news)]
+        for r in reqs:
+            s.submit(r)
+        steps = 0
+        while s.has_work():
+            if rng.random() < 0.1:
+                s.cancel(rng.choice(reqs))
+            run_step(s, cache)
+            steps += 1
+            assert steps < 20000, (trial, "no progress")
+        for r, m in zip(reqs, news):
+            assert r.finish_reason in ("length", "error", "cancelled"), (trial, r.finish_reason)
+            if r.finish_reason == "length":
+                assert len(r.output_ids) == m
+        cache.check()
+        assert cache.num_live == 0
