@@ -13,8 +13,9 @@ fails right away (tests/zedinfer/test_scheduler_sampling.cpp:104-131 of the refe
 When pages run out while decoding, the reference fails the request
 (src/zedinfer/scheduler.cpp:293-318).  Here that is ``on_exhaust="fail"``; the default
 ``"preempt"`` takes the youngest running request off the GPU instead: its pages are freed, and it
-goes back to the head of the queue with prompt := prompt + generated, to be recomputed when pages
-are free again.  Older requests therefore always finish.
+goes back to the head of the queue (behind a request that is in the middle of its prompt, which holds
+its pages) with prompt := prompt + generated, to be recomputed when pages are free again.  Older
+requests therefore always finish.
 
 The scheduler decides on the host and never touches the device: it works against the cache
 manager's bookkeeping, so it is tested without a GPU.
