@@ -181,3 +181,32 @@ def test_a_request_without_sampling_options_takes_the_engines_default():
     assert own.has_sampling_override and own.with_sampling_of(default) is own
     greedy = GenerationConfig(max_new_tokens=5, has_sampling_override=True)      # insists on greedy
     assert greedy.with_sampling_of(default).use_argmax
+
+
+# ---- command-line options (examples/ping.cpp:31-79, examples/serve.cpp:44-46, include/utils/logging_cli.hpp:11-38) ----
+def test_command_line_options_map_to_the_scheduler_config(tmp_path, monkeypatch):
+    import argparse
+    import logging
+    from zedinfer_b200.cli.common import add_engine_arguments, scheduler_config_from, setup_logging
+    monkeypatch.delenv("ZEDINFER_KV_BLOCK_SIZE", raising=False)
+    p = argparse.ArgumentParser()
+    add_engine_arguments(p)
+    a = p.parse_args(["/m"])
+    sc = scheduler_config_from(a)
+    assert (sc.max_batch_tokens, sc.max_batch_requests, sc.gpu_memory_utilization, sc.kv_block_size) == (2048, 64, 0.9, 16)
+    assert sc.on_exhaust == "preempt" and sc.cuda_graphs and a.random_weights is None and a.dtype == "bfloat16"
+    a = p.parse_args(["/m", "--max-batch-tokens", "512", "--max-batch-requests", "8", "--max-prefill-tokens", "128",
+                      "--kv-block-size", "32", "--kv-pages", "100", "--max-seq-len", "4096", "--on-exhaust", "fail",
+                      "--no-cuda-graphs", "--gpu-memory-utilization", "0.5", "--random-weights", "7", "--dtype", "float32",
+                      "--log-level", "debug", "--log-file", str(tmp_path / "z.log"), "--no-log-to-console"])
+    sc = scheduler_config_from(a)
+    assert (sc.max_batch_tokens, sc.max_batch_requests, sc.max_prefill_tokens, sc.kv_block_size, sc.num_kv_pages,
+            sc.max_seq_len, sc.on_exhaust, sc.cuda_graphs, sc.gpu_memory_utilization) == (512, 8, 128, 32, 100, 4096, "fail",
+                                                                                           False, 0.5)
+    sc.validate()
+    log = setup_logging(a)
+    log.debug("to the file only")
+    assert log.level == logging.DEBUG and "to the file only" in (tmp_path / "z.log").read_text()
+    for h in list(log.handlers):
+        h.close()
+        log.removeHandler(h)
