@@ -12,7 +12,9 @@ path never calls, and a ``main.cpp`` that feeds weights and token ids in and wri
     python tests/golden/make_golden.py /path/to/zedinfer
 
 writes ``model/`` (config.json, model.safetensors, float32), ``ids.json``, ``logits_whole.npy`` (the whole
-prompt in one forward) and ``logits_chunk5.npy`` (the prompt in portions of 5 with a growing past length).
+prompt in one forward), ``logits_chunk5.npy`` (the prompt in portions of 5 with a growing past length) and
+``sampler_cases.json`` (rows of logits with sampling options, and what the reference's own sampler keeps of them:
+tokens and renormalised probabilities after repetition penalty, temperature, softmax, top-k and top-p).
 tests/test_plain.py compares the plain implementation with them.
 """
 import glob
@@ -63,8 +65,66 @@ def build(ref: str, out_dir: str) -> str:
     return exe
 
 
+SAMPLER_VOCAB = 97
+SAMPLER_CASES = [      # temperature, top_k, top_p, repetition_penalty, recently generated tokens
+    (0.7, 0, 1.0, 1.0, []), (1.0, 5, 1.0, 1.0, []), (0.8, 0, 0.9, 1.0, []), (1.3, 20, 0.6, 1.0, []),
+    (1.0, 0, 1.0, 1.3, [3, 50, 96]), (0.6, 12, 0.85, 1.5, [7, 7, 21, 60, 0]), (2.0, 1, 1.0, 1.0, []),
+    (0.9, 96, 0.999, 1.1, [1, 2, 3, 4, 5, 6, 7, 8]),
+]
+
+
+def make_sampler_golden(ref: str, nj: str, tmp: str) -> None:
+    """The reference's own GeneralSampler::truncatedDist (src/frontend/sampler/sampler.cpp:195-247), compiled
+    unmodified for the CPU, on a few rows of logits: writes ``sampler_cases.json`` (inputs and its answers)."""
+    src = [f"{ref}/src/frontend/sampler/sampler.cpp", f"{ref}/src/backend/tensor/tensor.cpp",
+           f"{ref}/src/backend/device/runtime_api.cpp", f"{ref}/src/backend/device/cpu/cpu_runtime_api.cpp",
+           f"{ref}/src/backend/ops/rearrange/op.cpp", f"{ref}/src/utils/types.cpp", f"{ref}/src/backend/ops/sample/op.cpp",
+           f"{ref}/src/backend/ops/argmax/op.cpp"]
+    src += glob.glob(f"{ref}/src/backend/core/*/*.cpp") + glob.glob(f"{ref}/src/backend/ops/rearrange/cpu/*.cpp")
+    src += glob.glob(f"{ref}/src/backend/ops/argmax/cpu/*.cpp")
+    harness = os.path.join(HERE, "ref_harness")
+    exe = os.path.join(tmp, "ref_sampler")
+    subprocess.run(["g++", "-std=c++17", "-O2", "-march=native", "-fopenmp", "-Wno-unknown-pragmas",
+                    "-I", os.path.join(harness, "shim"), "-I", f"{ref}/include", "-I", nj,
+                    os.path.join(harness, "sampler_main.cpp")] + sorted(src) + ["-o", exe], check=True)
+    g = torch.Generator().manual_seed(321)
+    cases = []
+    lines = [f"vocab {SAMPLER_VOCAB}"]
+    for temperature, top_k, top_p, penalty, recent in SAMPLER_CASES:
+        logits = (torch.randn(SAMPLER_VOCAB, generator=g) * 2.5).tolist()
+        lines.append(f"case {temperature} {top_k} {top_p} {penalty} {len(recent)} " + " ".join(map(str, recent)))
+        lines.append(" ".join(repr(float(np.float32(v))) for v in logits))
+        cases.append({"temperature": temperature, "top_k": top_k, "top_p": top_p, "repetition_penalty": penalty,
+                      "recent": recent, "logits": [float(np.float32(v)) for v in logits]})
+    with open(os.path.join(tmp, "cases.txt"), "w") as f:
+        f.write("\n".join(lines) + "\n")
+    subprocess.run([exe, os.path.join(tmp, "cases.txt"), os.path.join(tmp, "dist.txt")], check=True)
+    with open(os.path.join(tmp, "dist.txt")) as f:
+        rows = f.read().split("\n")
+    i = 0
+    for case in cases:
+        _, _, n = rows[i].split()
+        kept = [rows[i + 1 + k].split() for k in range(int(n))]
+        case["kept_tokens"] = [int(t) for t, _ in kept]
+        case["kept_probs"] = [float(p) for _, p in kept]
+        i += 1 + int(n)
+    with open(os.path.join(HERE, "sampler_cases.json"), "w") as f:
+        json.dump({"vocab": SAMPLER_VOCAB, "cases": cases}, f)
+    print("sampler_cases", [len(c["kept_tokens"]) for c in cases])
+
+
+def find_nlohmann() -> str:
+    for cand in glob.glob(os.path.join(sys.prefix, "lib", "python*", "site-packages", "include", "cudnn_frontend",
+                                       "thirdparty")):
+        if os.path.isfile(os.path.join(cand, "nlohmann", "json.hpp")):
+            return cand
+    raise SystemExit("nlohmann/json.hpp not found (the reference's nlohmann_json submodule is empty)")
+
+
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2 or not os.path.isdir(sys.argv[1]):
+        sys.exit("usage: make_golden.py <checkout of tianyuxbear/zedinfer>")
+    ref = sys.argv[1]
     from zedinfer_b200.weights import SafetensorsFile, canonical_name, write_random_model
     model_dir = os.path.join(HERE, "model")
     write_random_model(CONFIG, SEED, model_dir, dtype="float32", init_scale=8.0)
@@ -73,6 +133,7 @@ def main():
     with open(os.path.join(HERE, "ids.json"), "w") as f:
         json.dump(ids, f)
     with tempfile.TemporaryDirectory() as tmp:
+        make_sampler_golden(ref, find_nlohmann(), tmp)
         exe = build(ref, tmp)
         st = SafetensorsFile(os.path.join(model_dir, "model.safetensors"))
         c = CONFIG

@@ -5,7 +5,7 @@ function is written from the formulas of the reference, cited as file:line of
 tianyuxbear/zedinfer.
 
 ``tests/golden/`` holds logits that the reference's own CPU forward produced for a tiny
-random model; ``tests/test_plain_vs_golden.py`` checks this file against them.
+random model; ``tests/test_plain.py`` checks this file against them.
 """
 from __future__ import annotations
 
@@ -190,6 +190,92 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], ids: List[int],
 
 def load(model_dir: str):
     return read_config(model_dir), read_safetensors(os.path.join(model_dir, "model.safetensors"))
+
+
+# ---------------------------------------------------------------------------------------------
+# random weights without a folder
+# ---------------------------------------------------------------------------------------------
+_U64 = (1 << 64) - 1
+
+
+def _as_i64(v: int) -> int:
+    v &= _U64
+    return v - (1 << 64) if v >= (1 << 63) else v
+
+
+def _splitmix(z: int) -> int:
+    z &= _U64
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _U64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _U64
+    return z ^ (z >> 31)
+
+
+def random_values(seed: int, name: str, shape, std: float, plus_one: bool = False, device="cpu") -> torch.Tensor:
+    """The engine's random-weights rule, restated (the reference has none; it draws token ids only,
+    src/zedinfer/profiler.cpp:79-84).  Element i of tensor ``name`` is twelve 16-bit fields of three
+    splitmix64 words of (key + (3 i + j) * golden), summed and centred: ``x = (2 s - 12 * 65535) / 2^17``;
+    the value is ``x * std`` (``1 + x * std`` for norm weights), float32.  Integer arithmetic up to one exact
+    conversion, so ``device`` (where the arithmetic runs; the result comes back to the CPU) changes no bit."""
+    h = 0xCBF29CE484222325
+    for b in name.encode():
+        h = ((h ^ b) * 0x100000001B3) & _U64
+    key = _splitmix(h ^ _splitmix(seed))
+    n = 1
+    for d in shape:
+        n *= int(d)
+    out = torch.empty(n, dtype=torch.float32, device=device)
+    srl = lambda z, k: (z >> k) & ((1 << (64 - k)) - 1)                      # noqa: E731  (logical shift)
+    step = 1 << 18 if str(device) == "cpu" else 1 << 24
+    for lo in range(0, n, step):
+        i3 = torch.arange(lo, min(lo + step, n), dtype=torch.int64, device=device) * 3
+        total = torch.zeros_like(i3)
+        for j in range(3):
+            z = (i3 + j) * _as_i64(0x9E3779B97F4A7C15) + _as_i64(key)
+            z = (z ^ srl(z, 30)) * _as_i64(0xBF58476D1CE4E5B9)
+            z = (z ^ srl(z, 27)) * _as_i64(0x94D049BB133111EB)
+            z = z ^ srl(z, 31)
+            pairs = (z & 0x0000FFFF0000FFFF) + (srl(z, 16) & 0x0000FFFF0000FFFF)   # fields 0+1 and 2+3, side by side
+            total += (pairs & 0xFFFFFFFF) + srl(pairs, 32)
+        out[lo: lo + i3.numel()] = (2 * total - 12 * 65535).float() / 131072.0
+    out *= float(torch.tensor(std, dtype=torch.float32))
+    if plus_one:
+        out += 1.0
+    return out.view(tuple(shape)).cpu()
+
+
+def random_weights(cfg: dict, seed: int, init_scale: float = 1.0, dtype: Optional[torch.dtype] = None,
+                   device="cpu") -> Dict[str, torch.Tensor]:
+    """Every tensor of a Qwen2 model of ``cfg`` (the dict of :func:`read_config`) drawn with ``seed``:
+    projections, biases and embeddings N(0, 0.02 * init_scale), norm weights 1 + N(0, 0.01); ``dtype``
+    rounds them as a stored model would (None: float32).  Returned as float32."""
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    qd, kd = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
+    shapes = {"embed_tokens.weight": (v, h), "norm.weight": (h,)}
+    if not cfg["tie_word_embeddings"]:
+        shapes["lm_head.weight"] = (v, h)
+    for layer in range(cfg["num_hidden_layers"]):
+        p = f"layers.{layer}."
+        shapes.update({p + "input_layernorm.weight": (h,), p + "post_attention_layernorm.weight": (h,),
+                       p + "self_attn.q_proj.weight": (qd, h), p + "self_attn.q_proj.bias": (qd,),
+                       p + "self_attn.k_proj.weight": (kd, h), p + "self_attn.k_proj.bias": (kd,),
+                       p + "self_attn.v_proj.weight": (kd, h), p + "self_attn.v_proj.bias": (kd,),
+                       p + "self_attn.o_proj.weight": (h, qd), p + "mlp.gate_proj.weight": (i, h),
+                       p + "mlp.up_proj.weight": (i, h), p + "mlp.down_proj.weight": (h, i)})
+    out = {}
+    for name, shape in shapes.items():
+        norm = name.endswith("norm.weight") or name.endswith("layernorm.weight")
+        t = random_values(seed, name, shape, 0.01 if norm else 0.02 * init_scale, plus_one=norm, device=device)
+        out[name] = round_to(t, dtype)
+    return out
+
+
+def config_from_dict(j: dict) -> dict:
+    """:func:`read_config` for a config.json that is already a dict."""
+    import tempfile
+    with tempfile.TemporaryDirectory() as tmp:
+        with open(os.path.join(tmp, "config.json"), "w") as f:
+            json.dump(j, f)
+        return read_config(tmp)
 
 
 # ---------------------------------------------------------------------------------------------

@@ -42,3 +42,12 @@ def first_bad(got, expected, requests, tol):
             if not d <= tol:
                 return rid, p, d
     return None
+
+
+def first_bad_wanted(got, expected, tol):
+    """As :func:`first_bad`, over the positions that were asked for (``got``'s keys) instead of every position."""
+    for (rid, p), row in sorted(got.items(), key=lambda kv: (str(kv[0][0]), kv[0][1])):
+        d = float((row - expected[rid][p]).abs().max())
+        if not d <= tol:
+            return rid, p, d
+    return None

@@ -155,3 +155,19 @@ def test_budget_to_pages():
     per_page = 28 * 2 * 2 * 16 * 128 * 2
     assert m.bytes_per_page_all_groups(torch.bfloat16) == per_page
     assert m.pages_for_budget(per_page * 101, torch.bfloat16) == 100      # one page is the scratch page
+
+
+def test_a_reopened_request_id_is_another_request():
+    """Captured decode steps skip the upload of a row's block table while (request id, serial, version) is unchanged.
+    An id that is closed and opened again (preemption does that) starts at version 0 again, so the serial must
+    differ, or the row would keep the old request's pages."""
+    m = CacheManager([(0, PagedKVNeed(2, 16))], page_size=4)
+    m.set_num_pages(8)
+    a = m.open("x")
+    m.ensure(a, 6)
+    first = (a.request_id, a.serial, a.version)
+    m.close(a)
+    b = m.open("x")
+    m.ensure(b, 6)
+    assert (b.request_id, b.version) == (first[0], first[2]) and b.serial != first[1]
+    assert (b.request_id, b.serial, b.version) != first

@@ -122,3 +122,15 @@ def test_bad_input_is_refused():
         pack_step(["a"], [[5, 7000]], [[1]], [0], [0], [[[1]]], 1, 4, 5000, SCRATCH, TILE)
     with pytest.raises(ValueError, match="wanted place"):
         pack_step(["a"], [[5, 6]], [[2]], [0], [0], [[[1]]], 1, 4, 5000, SCRATCH, TILE)
+
+
+def test_pages_given_back_behind_a_window_are_shown_as_the_scratch_page():
+    """A block-table entry of -1 (the window has passed the page and the pool has it back) never reaches a kernel:
+    the descriptor shows the scratch page there, so no address or TMA coordinate is formed from -1."""
+    tokens = [[5, 6, 7], [9]]
+    tables = [[[-1, -1, 40, 41], [3, 4, 5, 6]], [[-1, 8], [7, 8]]]      # group 0 has a window, group 1 has none
+    host, lay = pack_step(["a", "b"], tokens, [[2], [0]], [50, 20], [-1, -1], tables, 2, 6, 100, SCRATCH, TILE, 0)
+    tab = host[lay.off_tab:].reshape(2, lay.n_seg, lay.width)
+    assert tab[0, 0].tolist() == [SCRATCH, SCRATCH, 40, 41, 0, 0] and tab[1, 0].tolist() == [3, 4, 5, 6, 0, 0]
+    assert tab[0, 1].tolist() == [SCRATCH, 8, 0, 0, 0, 0] and tab[1, 1].tolist() == [7, 8, 0, 0, 0, 0]
+    assert (host[lay.off_tab:] >= 0).all()

@@ -10,7 +10,7 @@ import torch
 import tiny
 import traces
 from plain import qwen2_plain as P
-from replay_util import compare, first_bad, run_trace
+from replay_util import compare, first_bad, first_bad_wanted, run_trace
 
 pytestmark = pytest.mark.gpu
 
@@ -37,11 +37,12 @@ def expected_logits(model_dir, requests, dtype):
     return {rid: P.forward(cfg, w, toks, act) for rid, toks in requests.items()}
 
 
-LENGTHS = {"A": [7, 13, 70, 45], "B": [1, 17, 40, 90], "C": [60, 5, 100, 33], "D": [50, 130, 9]}
+LENGTHS = {"A": [7, 13, 70, 45], "B": [1, 17, 40, 90], "C": [60, 5, 100, 33], "D": [50, 130, 9], "E": [33, 150, 80],
+           "F": [150, 47, 260, 90]}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 @pytest.mark.parametrize("family", ["whole", "tail", "chunks", "mixed"])
 def test_cuts_match_plain(models, name, dtype, family):
     from zedinfer_b200.engine.core import EngineCore
@@ -49,7 +50,7 @@ def test_cuts_match_plain(models, name, dtype, family):
     requests = make_requests(cfg, LENGTHS[name] + ([64, 31, 77] if family == "mixed" else []), seed=11)
     steps = {"whole": traces.whole, "tail": traces.tail_decode, "chunks": traces.chunks,
              "mixed": traces.mixed}[family](requests)
-    page = {"A": 4, "B": 8, "C": 16, "D": 16}[name]
+    page = {"A": 4, "B": 8, "C": 16, "D": 16, "E": 16, "F": 16}[name]
     need = traces.max_live_tokens(steps, round_to=page)
     core = EngineCore(models[name], dtype, page_size=page, num_pages=need // page, max_requests=4)
     got = run_trace(core, steps)
@@ -60,7 +61,39 @@ def test_cuts_match_plain(models, name, dtype, family):
     assert core.cache.num_live == 0 and all(g.pool.num_used == 0 for g in core.cache.groups)
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,max_live", [("D", 12), ("D", 40), ("E", 12), ("E", 40), ("F", 12)])
+def test_many_decoding_requests_match_plain(models, name, max_live, dtype, graphs):
+    """Steps as a scheduler makes them with many requests live: decode-only steps of up to 12 and up to 40 rows
+    (9 to 16 rows: the two-tile form of the weight-streaming product; 17 and more: library products with separate
+    rotation and activation kernels, decode attention with smaller clusters), one prompt portion beside up to 37
+    decoding requests, requests that sit steps out, and a pool that later requests fill again.  With graphs the
+    decode-only steps replay the captured buckets 16, 32 and 64 with rows of padding, and mixed steps whose counts
+    come back are captured too.  Every wanted logit is the plain implementation's."""
+    from zedinfer_b200.engine.core import EngineCore
+    cfg, _ = tiny.CONFIGS[name]
+    rng = random.Random(77 + max_live)
+    n_req = max_live + max_live // 3
+    lengths = [rng.randint(50, 110) for _ in range(n_req)]
+    requests = make_requests(cfg, lengths, seed=13)
+    steps = traces.decode_heavy(requests, seed=5, max_live=max_live, tail=(44, 64) if max_live > 16 else (8, 24))
+    rows = [len(st["entries"]) for st in steps if all(len(e["tokens"]) == 1 for e in st["entries"])]
+    assert max(rows) > (16 if max_live > 16 else 8)
+    need = traces.max_live_tokens(steps, round_to=16)
+    core = EngineCore(models[name], dtype, page_size=16, num_pages=need // 16, max_requests=64, cuda_graphs=graphs)
+    core.GPU_BOUND_RATIO = float("inf")
+    got = run_trace(core, steps)
+    exp = expected_logits(models[name], requests, dtype)
+    bad = first_bad_wanted(got, exp, TOL[dtype])
+    assert bad is None, f"first wrong position {bad}"
+    assert len(got) > sum(min(len(t) - 1, 8) for t in requests.values())
+    if graphs:
+        assert {g.bucket for g in core._decode_graphs.values()} >= ({16, 32, 64} if max_live > 16 else {8, 16})
+    assert core.cache.num_live == 0 and all(g.pool.num_used == 0 for g in core.cache.groups)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "F"])
 def test_float32_is_the_same_however_it_is_cut(models, name):
     """In float32 every sum has one order, so the cuts agree to the last bit."""
     from zedinfer_b200.engine.core import EngineCore

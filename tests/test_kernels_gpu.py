@@ -145,6 +145,16 @@ def build_cache(n_req, lens, nkv, hd, ps, dtype, seed=0, n_calls=2, call=1):
     return pool, view, tables.to(dev()), ks, vs, pool.stride(0), pool.stride(2)
 
 
+def release_behind_window(tables, first_positions, window, ps, junk_page):
+    """What the engine shows the kernels once a window has passed a page and the page was given back: the entry
+    points at the scratch page, here ``junk_page`` (the pool's last page, which no request owns and which holds
+    1000.0 like every stale page).  ``first_positions[r]``: the earliest query position of row r in the step."""
+    t = tables.clone()
+    for r, p0 in enumerate(first_positions):
+        t[r, :max(0, p0 - window + 1) // ps] = junk_page
+    return t
+
+
 def plain_attention_rows(q, k, v, positions, scale, window):
     """q [n, nh, hd] at the given positions of a sequence whose k, v are [L, nkv, hd]."""
     out = torch.zeros_like(q)
@@ -311,6 +321,8 @@ def test_decode_attention_mma(nh, nkv, hd, ps, window, kernel):
     out = torch.empty(n, nh * hd, dtype=t, device=dev())
     scale = 1.0 / math.sqrt(hd)
     fn = ops.decode_attention if kernel == "cp_async" else ops.decode_attention_tma
+    if window:          # pages wholly behind the window were given back: the tables show the scratch page there
+        tables = release_behind_window(tables, [l - 1 for l in lens], window, ps, pool.shape[0] - 1)
     fn(qd, view, out, tables, seg, pos, nh, nkv, hd, ps, page_stride, kv_stride, window, scale)
     torch.cuda.synchronize()
     assert ops.tcgen05_status(dev()) == 0
@@ -360,6 +372,8 @@ def test_prefill_attention_tensor_cores(nh, nkv, hd, ps, window, kernel):
     q[200 + 10 + 64 + 203 + 1 + 1099, :, :] = ks[5][far5, 0][None, :] * 4.0
     qd = q.to(t).to(dev())
     seg_tables = torch.stack([tables[r] for r, _, _ in portions])
+    if window:          # pages wholly behind the window of a portion's first query were given back
+        seg_tables = release_behind_window(seg_tables, [p0 for _, p0, _ in portions], window, ps, pool.shape[0] - 1)
     out = torch.full((n, nh * hd), float("nan"), dtype=t, device=dev())
     scale = 1.0 / math.sqrt(hd)
     fn = ops.prefill_attention if kernel == "mma" else ops.prefill_attention_tcgen05
@@ -489,3 +503,57 @@ def test_decode_attention_tma_long_context(batch, shared, window):
     for r in range(n):
         ref = plain_attention_rows(qf[r:r + 1], ks[r], vs[r], [lens[r] - 1], scale, window)
         assert float((got[r:r + 1] - ref).abs().max()) < 2e-2, (r, lens[r])
+
+
+def _attention_args(nh, nkv, hd, ps, misalign=False):
+    """Operands of a small step for the attention entry points: 3 requests, one token each."""
+    t = torch.bfloat16
+    lens = [40, 17, 100]
+    pool, view, tables, ks, vs, page_stride, kv_stride = build_cache(len(lens), lens, nkv, hd, ps, t, seed=3)
+    n = len(lens)
+    store = torch.zeros(n * nh * hd + 8, dtype=t, device=dev())
+    q = (store[1:1 + n * nh * hd] if misalign else store[:n * nh * hd]).view(n, nh, hd)     # 2 bytes off when asked
+    pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=dev())
+    seg = torch.arange(n, dtype=torch.int32, device=dev())
+    tiles = torch.tensor([(i, 1, i) for i in range(n)], dtype=torch.int32, device=dev())
+    out = torch.zeros(n, nh * hd, dtype=t, device=dev())
+    return q, view, out, tables, seg, pos, tiles, page_stride, kv_stride
+
+
+def test_attention_kernels_refuse_what_they_cannot_do():
+    """A size that an attention entry point does not take is refused on the host with a message that names it;
+    nothing is launched.  Head size 96 (the tensor-core kernels take 64 and 128), pages of 24 tokens (the TMA and
+    tcgen05 forms take powers of two from 8 to 128), operands that are not 16-byte aligned, head counts that do not
+    divide; the general kernel refuses a head size that is no multiple of 8."""
+    from zedinfer_b200 import ops
+    scale = 0.1
+    q, view, out, tables, seg, pos, tiles, pst, kst = _attention_args(6, 2, 96, 16)
+    for call, what in ((lambda: ops.decode_attention(q, view, out, tables, seg, pos, 6, 2, 96, 16, pst, kst, None, scale), "head_dim 64 or 128, got 96"),
+                       (lambda: ops.decode_attention_tma(q, view, out, tables, seg, pos, 6, 2, 96, 16, pst, kst, None, scale), "head_dim 64 or 128, got 96"),
+                       (lambda: ops.prefill_attention(q, view, out, tables, tiles, pos, 6, 2, 96, 16, pst, kst, None, scale), "head_dim 64 or 128, got 96"),
+                       (lambda: ops.prefill_attention_tcgen05(q, view, out, tables, tiles, pos, 6, 2, 96, 16, pst, kst, None, scale), "head_dim 96 is not 64 or 128")):
+        with pytest.raises(ops.KernelError, match=what):
+            call()
+    q, view, out, tables, seg, pos, tiles, pst, kst = _attention_args(4, 2, 64, 24)
+    with pytest.raises(ops.KernelError, match="page size 24 is not a power of two from 8 to 128"):
+        ops.decode_attention_tma(q, view, out, tables, seg, pos, 4, 2, 64, 24, pst, kst, None, scale)
+    with pytest.raises(ops.KernelError, match="page size 24 is not a power of two from 8 to 128"):
+        ops.prefill_attention_tcgen05(q, view, out, tables, tiles, pos, 4, 2, 64, 24, pst, kst, None, scale)
+    ops.decode_attention(q, view, out, tables, seg, pos, 4, 2, 64, 24, pst, kst, None, scale)       # the cp.async form takes them
+    ops.prefill_attention(q, view, out, tables, tiles, pos, 4, 2, 64, 24, pst, kst, None, scale)
+    q, view, out, tables, seg, pos, tiles, pst, kst = _attention_args(4, 2, 64, 16, misalign=True)
+    assert q.data_ptr() % 16 == 2
+    with pytest.raises(ops.KernelError, match="16-byte aligned"):
+        ops.decode_attention_tma(q, view, out, tables, seg, pos, 4, 2, 64, 16, pst, kst, None, scale)
+    with pytest.raises(ops.KernelError, match="16-byte aligned"):
+        ops.prefill_attention_tcgen05(q, view, out, tables, tiles, pos, 4, 2, 64, 16, pst, kst, None, scale)
+    q, view, out, tables, seg, pos, tiles, pst, kst = _attention_args(5, 2, 64, 16)
+    with pytest.raises(ops.KernelError, match="5 query heads cannot share 2 key/value heads"):
+        ops.decode_attention_tma(q, view, out, tables, seg, pos, 5, 2, 64, 16, pst, kst, None, scale)
+    with pytest.raises(ops.KernelError, match="5 heads over 2 key-value heads"):
+        ops.prefill_attention_tcgen05(q, view, out, tables, tiles, pos, 5, 2, 64, 16, pst, kst, None, scale)
+    q, view, out, tables, seg, pos, tiles, pst, kst = _attention_args(2, 1, 20, 16)
+    with pytest.raises(ops.KernelError, match="head_dim=20 must be a multiple of 8"):
+        ops.paged_attention(q, view, out, tables, seg, pos, 2, 1, 20, 16, pst, kst, None, scale)
+    torch.cuda.synchronize()
+    assert ops.tcgen05_status(dev()) == 0

@@ -79,3 +79,24 @@ def test_bfloat16_rounding_points_change_little():
         ids = json.load(f)
     a, b = P.forward(cfg, w, ids), P.forward(cfg, w, ids, torch.bfloat16)
     assert 0 < float((a - b).abs().max()) < 0.15
+
+
+def test_sampling_distribution_matches_the_reference_sampler():
+    """``tests/golden/sampler_cases.json``: what tianyuxbear/zedinfer's own GeneralSampler::truncatedDist keeps of a
+    row of logits (src/frontend/sampler/sampler.cpp:195-247, compiled unmodified by tests/golden/make_golden.py):
+    the same tokens survive top-k and top-p here, with the same renormalised probabilities, after the same
+    repetition penalty (applied once per listed token, twice for one that is listed twice) and temperature."""
+    with open(os.path.join(GOLDEN, "sampler_cases.json")) as f:
+        gold = json.load(f)
+    assert len(gold["cases"]) >= 8
+    for c in gold["cases"]:
+        logits = torch.tensor(c["logits"], dtype=torch.float32)
+        d = P.sampling_distribution(logits, c["temperature"], c["top_k"], c["top_p"], recent=c["recent"],
+                                    repetition_penalty=c["repetition_penalty"])
+        kept = torch.nonzero(d > 0).flatten().tolist()
+        assert sorted(kept) == sorted(c["kept_tokens"]), (c["temperature"], c["top_k"], c["top_p"])
+        ref = torch.zeros_like(d)
+        ref[torch.tensor(c["kept_tokens"])] = torch.tensor(c["kept_probs"], dtype=torch.float32)
+        assert float((d - ref).abs().max()) < 1e-6
+        # the reference lists what it keeps by falling probability
+        assert all(a >= b for a, b in zip(c["kept_probs"], c["kept_probs"][1:]))

@@ -1,0 +1,118 @@
+"""The engine against the plain implementation at the layer sizes of the 1.5B-class benchmark model: hidden 1,536,
+12 query heads over 2 key/value heads of 128, intermediate 8,960, vocabulary 151,936, untied head, 2 of its 28
+layers (depth repeats the same kernels; width is what the tiny models cannot show).  The weights are drawn, not
+stored: the engine draws them on the GPU from (seed 3, tensor name, element index), the plain implementation draws
+them on the CPU with its own restatement of that rule, and the two must hold the same bits before any logit is
+compared.  Requests of a few hundred tokens go through the four ways of cutting the work, in float32 and bfloat16.
+"""
+import random
+
+import pytest
+import torch
+
+import traces
+from plain import qwen2_plain as P
+from replay_util import first_bad, first_bad_wanted, run_trace
+
+pytestmark = pytest.mark.gpu
+
+LAYERS, OF_LAYERS = 2, 28
+REAL = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": LAYERS, "hidden_size": 1536, "num_attention_heads": 12, "num_key_value_heads": 2,
+    "head_dim": 128, "intermediate_size": 8960, "vocab_size": 151936, "rope_theta": 10000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "use_sliding_window": False,
+    "max_position_embeddings": 4096,
+}
+SEED = 3
+# Absolute, on logits whose largest magnitude is about 4 here (weights N(0, 0.02), width 1,536): the same figures as
+# the tiny models' tests use on logits of magnitude 3.
+TOL = {"float32": 2e-4, "bfloat16": 6e-2}
+LENGTHS = [260, 150, 330]
+EXTRA = [64, 100]                 # the mixed family's later requests, which take the pages of finished ones
+
+
+def make_requests(lengths, seed):
+    rng = random.Random(seed)
+    return {f"r{i}": [rng.randrange(REAL["vocab_size"]) for _ in range(n)] for i, n in enumerate(lengths)}
+
+
+@pytest.fixture(scope="module")
+def plain_model():
+    cfg = P.config_from_dict(REAL)
+    drawn = P.random_weights(cfg, SEED, device="cuda:0")      # integer arithmetic: the same bits as on the CPU, in a second
+    return cfg, {"float32": drawn, "bfloat16": {k: P.round_to(v, torch.bfloat16) for k, v in drawn.items()}}
+
+
+@pytest.fixture(scope="module")
+def expected(plain_model):
+    cfg, weights = plain_model
+    requests = make_requests(LENGTHS + EXTRA, seed=17)
+    out = {}
+    for dtype, act in (("float32", None), ("bfloat16", torch.bfloat16)):
+        out[dtype] = {rid: P.forward(cfg, weights[dtype], toks, act) for rid, toks in requests.items()}
+    return requests, out
+
+
+def test_the_engine_and_the_plain_implementation_draw_the_same_weights(plain_model):
+    """Device, host and the plain restatement of the rule agree bit for bit, tensor by tensor."""
+    from zedinfer_b200.engine.model import Model
+    from zedinfer_b200.config.registry import resolve_architecture
+    from zedinfer_b200.weights.random_init import draw_tensor, unit_normal
+    cfg, weights = plain_model
+    arch = resolve_architecture(REAL)
+    specs = Model(arch.build_spec(arch.parse(dict(REAL)))).tensor_specs()
+    assert set(specs) == set(weights["float32"])
+    for name in ("lm_head.weight", "embed_tokens.weight", "norm.weight", "layers.1.mlp.down_proj.weight",
+                 "layers.0.self_attn.k_proj.bias", "layers.1.input_layernorm.weight"):
+        on_gpu = draw_tensor(SEED, name, specs[name], torch.float32, "cuda:0").cpu()
+        assert torch.equal(on_gpu, weights["float32"][name]), name
+        assert torch.equal(draw_tensor(SEED, name, specs[name], torch.bfloat16, "cuda:0").float().cpu(), weights["bfloat16"][name]), name
+    a = unit_normal(SEED, "layers.0.mlp.up_proj.weight", 100_000, "cuda:0", first=5_000_000).cpu()
+    b = unit_normal(SEED, "layers.0.mlp.up_proj.weight", 100_000, "cpu", first=5_000_000)
+    assert torch.equal(a, b)
+    on_cpu = P.random_values(SEED, "lm_head.weight", (2000, 1536), 0.02)            # the plain rule on the host
+    assert torch.equal(on_cpu, weights["float32"]["lm_head.weight"][:2000])
+    x = weights["float32"]["layers.0.mlp.gate_proj.weight"]
+    assert abs(float(x.mean())) < 1e-4 and abs(float(x.std()) - 0.02) < 2e-4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("family", ["whole", "tail", "chunks", "mixed"])
+def test_cuts_match_plain_at_benchmark_layer_sizes(expected, family, dtype):
+    from zedinfer_b200.engine.core import EngineCore
+    all_requests, exp = expected
+    names = [f"r{i}" for i in range(len(LENGTHS) + (len(EXTRA) if family == "mixed" else 0))]
+    requests = {rid: all_requests[rid] for rid in names}
+    steps = {"whole": traces.whole, "tail": traces.tail_decode, "chunks": traces.chunks,
+             "mixed": traces.mixed}[family](requests)
+    need = traces.max_live_tokens(steps, round_to=16)
+    core = EngineCore(None, dtype, config=dict(REAL), random_seed=SEED, page_size=16, num_pages=need // 16, max_requests=4)
+    assert core.spec.vocab_size == 151936 and len(core.spec.layers) == LAYERS < OF_LAYERS
+    got = run_trace(core, steps)
+    core.check_kernels()
+    bad = first_bad(got, exp[dtype], requests, TOL[dtype])
+    assert bad is None, f"first wrong position {bad}"
+    assert core.cache.num_live == 0 and all(g.pool.num_used == 0 for g in core.cache.groups)
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_twelve_decoding_requests_at_benchmark_layer_sizes(plain_model, graphs):
+    """Decode-only steps of 9 to 12 rows at full width in bfloat16: the two-tile form of the weight-streaming product
+    where the weight is small enough (down, output, q/k/v with rotation and append, gate/up with the activation), the
+    library for the head; a prompt portion beside them."""
+    from zedinfer_b200.engine.core import EngineCore
+    cfg, weights = plain_model
+    rng = random.Random(5)
+    requests = make_requests([rng.randint(30, 70) for _ in range(15)], seed=23)
+    steps = traces.decode_heavy(requests, seed=9, max_live=12, tail=(6, 14))
+    assert max(len(st["entries"]) for st in steps if all(len(e["tokens"]) == 1 for e in st["entries"])) > 8
+    need = traces.max_live_tokens(steps, round_to=16)
+    core = EngineCore(None, "bfloat16", config=dict(REAL), random_seed=SEED, page_size=16, num_pages=need // 16,
+                      max_requests=16, cuda_graphs=graphs)
+    core.GPU_BOUND_RATIO = float("inf")
+    got = run_trace(core, steps)
+    core.check_kernels()
+    exp = {rid: P.forward(cfg, weights["bfloat16"], toks, torch.bfloat16) for rid, toks in requests.items()}
+    bad = first_bad_wanted(got, exp, TOL["bfloat16"])
+    assert bad is None, f"first wrong position {bad}"

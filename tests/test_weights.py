@@ -139,3 +139,45 @@ def test_folder_errors(tmp_path):
     save_file({"x": torch.zeros(2)}, str(b))
     with pytest.raises(WeightsError, match="more than once"):
         load_weights(str(tmp_path), {"x": TensorSpec((2,))}, torch.float32, "cpu")
+
+
+def test_one_rule_draws_the_weights_everywhere(tmp_path):
+    """(seed, tensor name, element index) decides a value: the folder that ``write_random_model`` writes, the tensors
+    ``random_tensors`` draws directly (what the engine does on the device, without a folder), any piece of a tensor
+    drawn on its own, and the plain implementation's restatement of the rule all hold the same bits."""
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from plain import qwen2_plain as P
+    from zedinfer_b200.weights.random_init import draw_tensor, unit_normal
+    d = tiny.make_model_dir(tmp_path, "B")
+    _, _, spec = load_model_config(d)
+    specs = Model(spec).tensor_specs()
+    stored = load_weights(d, specs, torch.bfloat16, "cpu")
+    seed = tiny.CONFIGS["B"][1]
+    direct = random_tensors(specs, seed, torch.bfloat16, tiny.INIT_SCALE)
+    assert set(direct) == set(stored) and all(torch.equal(direct[k], stored[k]) for k in stored)
+    cfg, _ = P.load(d)
+    plain = P.random_weights(cfg, seed, tiny.INIT_SCALE, torch.bfloat16)
+    assert set(plain) == set(stored) and all(torch.equal(plain[k], stored[k].float()) for k in stored)
+    whole = unit_normal(5, "layers.7.mlp.up_proj.weight", 3000, "cpu")
+    piece = unit_normal(5, "layers.7.mlp.up_proj.weight", 1000, "cpu", first=1500)
+    assert torch.equal(whole[1500:2500], piece)
+    assert not torch.equal(whole[:1000], unit_normal(5, "layers.8.mlp.up_proj.weight", 1000, "cpu"))
+    big = unit_normal(11, "embed_tokens.weight", 400_000, "cpu")
+    assert abs(float(big.mean())) < 5e-3 and abs(float(big.std()) - 1.0) < 5e-3 and float(big.abs().max()) < 6.0
+    norm = draw_tensor(2, "norm.weight", specs["norm.weight"], torch.float32, "cpu")
+    assert abs(float(norm.mean()) - 1.0) < 5e-3 and 0.005 < float(norm.std()) < 0.015
+
+
+def test_a_scratch_buffer_that_a_graph_may_hold_is_never_given_back():
+    """A captured step has its scratch buffer's address baked in.  When a later call needs more, the old buffer is
+    kept alive beside the new one instead of going back to the allocator, and growth at least doubles."""
+    from zedinfer_b200 import ops
+    key = ("test_scratch", "cpu")
+    ops._scratch.pop(key, None)
+    first = ops._grown_scratch(key, 100, "cpu")
+    assert ops._grown_scratch(key, 80, "cpu") is first
+    second = ops._grown_scratch(key, 101, "cpu")
+    assert second is not first and second.numel() >= 200
+    assert any(t is first for t in ops._retired)
+    ops._scratch.pop(key, None)

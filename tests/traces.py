@@ -76,6 +76,48 @@ def mixed(requests, seed=0, max_live=4, decode_tail=8):
     return steps
 
 
+def decode_heavy(requests, seed=0, max_live=12, tail=(8, 24), sit_out=0.1, portion=64):
+    """Many decoding requests at a time, as a scheduler runs them: every step feeds one token of each decoding
+    request (a request sits a step out now and then) and, while someone is still in his prompt, one portion of that
+    prompt beside them.  Once all are admitted the steps are decode-only with up to ``max_live`` rows, and as requests
+    end without successors the number of rows falls through every batch size down to one.  Logits are wanted at the
+    last prompt token and at every decoded token.  ``tail``: how many of its last tokens a request decodes."""
+    rng = random.Random(seed)
+    pending = list(requests.items())
+    live, tails = {}, {}
+    steps = []
+    while pending or live:
+        while pending and len(live) < max_live:
+            rid, toks = pending.pop(0)
+            live[rid] = 0
+            tails[rid] = min(len(toks) - 1, rng.randint(*tail))
+        entries, ended = [], []
+        in_prompt = next((rid for rid in live if live[rid] < len(requests[rid]) - tails[rid]), None)
+        for rid in list(live):
+            toks, done = requests[rid], live[rid]
+            head = len(toks) - tails[rid]
+            if done < head:
+                if rid != in_prompt:
+                    continue
+                c = min(portion, head - done)
+                entries.append({"id": rid, "tokens": list(toks[done:done + c]), "want": [c - 1] if done + c == head else []})
+            else:
+                if len(live) > 1 and rng.random() < sit_out:
+                    continue
+                c = 1
+                entries.append({"id": rid, "tokens": [toks[done]], "want": [0]})
+            live[rid] = done + c
+            if live[rid] == len(toks):
+                ended.append(rid)
+        if not entries:
+            continue
+        entries.sort(key=lambda e: len(e["tokens"]) != 1)          # decoding requests first, as the engine batches
+        steps.append({"step": len(steps), "entries": entries, "end": ended})
+        for rid in ended:
+            del live[rid]
+    return steps
+
+
 def max_live_tokens(steps, round_to=64):
     """The most tokens live requests hold at any time, each request's count rounded up to ``round_to``."""
     held, best = {}, 0

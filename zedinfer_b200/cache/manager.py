@@ -15,6 +15,7 @@ captured decode step write there.
 """
 from __future__ import annotations
 
+import itertools
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -63,10 +64,12 @@ class PagedGroup:
 
 class RequestCache:
     """What one live request holds: its committed length, a block table per group, a state slot."""
-    __slots__ = ("request_id", "length", "tables", "slot", "closed", "version")
+    __slots__ = ("request_id", "length", "tables", "slot", "closed", "version", "serial")
+    _serials = itertools.count(1)
 
     def __init__(self, request_id, n_groups: int, slot: int):
         self.request_id = request_id
+        self.serial = next(RequestCache._serials)   # never comes back in this process, unlike a request id that is reopened
         self.length = 0
         self.version = 0                      # bumped whenever a block table changes (pages added or given back)
         self.tables: List[List[int]] = [[] for _ in range(n_groups)]

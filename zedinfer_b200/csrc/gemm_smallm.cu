@@ -251,8 +251,9 @@ gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const
 
 template <int NT, typename TC, bool SILU>
 static void launch(const void* X, const void* W, const void* bias, void* C, float* part, int* counters, int ksplit,
-                   int M, int N, int K, long long ldx, long long ldw, long long ldc, cudaStream_t stream) {
-    if (ksplit > 1 && ksplit <= 8) {
+                   int M, int N, int K, long long ldx, long long ldw, long long ldc, cudaStream_t stream,
+                   bool through_clusters = true) {
+    if (through_clusters && ksplit > 1 && ksplit <= 8) {
         // the K ranges of a column tile as one cluster along y: their sums meet in distributed shared memory
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof(cfg));
@@ -451,6 +452,17 @@ static int zi_noalloc_setup(int device, void** base) {
     return 0;
 }
 
+// 0 (default): the K ranges of a column tile meet in distributed shared memory where a cluster of that shape can be
+// launched, and the array only serves where it cannot.  1: the sums always go through the array (partial sums
+// written to it, counted, and added by the block that arrives last).  Both give the same bits.  Returns the
+// setting it replaces.  Process-wide; not meant to be flipped while calls are in flight on another thread.
+static int zi_noalloc_through_array = 0;
+ZI_EXPORT int zi_gemm_smallm_noalloc_reduction(int through_array) {
+    const int before = zi_noalloc_through_array;
+    zi_noalloc_through_array = through_array ? 1 : 0;
+    return before;
+}
+
 ZI_EXPORT int zi_gemm_smallm_noalloc(const void* X, const void* W, const void* bias, void* C, int c_dtype, int M, int N,
                                      int K, long long ldx, long long ldw, long long ldc, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
@@ -465,9 +477,10 @@ ZI_EXPORT int zi_gemm_smallm_noalloc(const void* X, const void* W, const void* b
     int* counters = nullptr;
     if (ksplit > 1) {
         const long long need = (long long)ksplit * 16 * N;
-        if (need > ZI_NOALLOC_PART_FLOATS || tiles > ZI_NOALLOC_COUNTER_INTS || ksplit > ZI_NOALLOC_MAX_SPLIT)
-            return zi_fail("gemm_smallm_noalloc: N=%d, K=%d is cut into %d K ranges and needs %lld floats of scratch; "
-                           "the built-in array holds %d (N up to %d)", N, K, ksplit, need, ZI_NOALLOC_PART_FLOATS, ZI_NOALLOC_MAX_N);
+        if (need > ZI_NOALLOC_PART_FLOATS || tiles > ZI_NOALLOC_COUNTER_INTS)
+            return zi_fail("gemm_smallm_noalloc: N=%d, K=%d is cut into %d K ranges whose sums take %lld floats (and %d counters); "
+                           "the built-in array holds %d floats and %d counters", N, K, ksplit, need, tiles,
+                           ZI_NOALLOC_PART_FLOATS, ZI_NOALLOC_COUNTER_INTS);
         int device = -1;
         cudaError_t e = cudaGetDevice(&device);
         if (e != cudaSuccess) return zi_fail("gemm_smallm_noalloc: cudaGetDevice failed: %s", cudaGetErrorString(e));
@@ -479,8 +492,8 @@ ZI_EXPORT int zi_gemm_smallm_noalloc(const void* X, const void* W, const void* b
         e = cudaMemsetAsync(counters, 0, (size_t)tiles * sizeof(int), stream);
         if (e != cudaSuccess) return zi_fail("gemm_smallm_noalloc: clearing the counters failed: %s", cudaGetErrorString(e));
     }
-    const bool f32 = c_dtype == ZI_F32;
-    if (M <= 8) { if (f32) launch<1, float, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); else launch<1, bf16, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); }
-    else        { if (f32) launch<2, float, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); else launch<2, bf16, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); }
+    const bool f32 = c_dtype == ZI_F32, cl = !zi_noalloc_through_array;
+    if (M <= 8) { if (f32) launch<1, float, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream, cl); else launch<1, bf16, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream, cl); }
+    else        { if (f32) launch<2, float, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream, cl); else launch<2, bf16, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream, cl); }
     return zi_check_launch("gemm_smallm_noalloc");
 }

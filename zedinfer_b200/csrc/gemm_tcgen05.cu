@@ -1,7 +1,8 @@
 // C[M,N] = X[M,K] . W[N,K]^T (+ bias[N]) for bfloat16 operands on the 5th-generation tensor cores:
 // tcgen05.mma issued by one thread per CTA, operands staged in shared memory by TMA
 // (cp.async.bulk.tensor, 128-byte swizzle), the float32 accumulator in tensor memory (TMEM), read back
-// with tcgen05.ld for the epilogue.  cta_group::1, no multicast.
+// with tcgen05.ld for the epilogue.  Single CTAs (cta_group::1) in the first two entry points, pairs of SMs
+// (cta_group::2) in the third; no load uses cluster multicast.
 //
 // One CTA computes one 128 x BN tile of D = A . B^T, A and B both K-major ([rows, K] row-major):
 //   normal  : A = X (tokens), B = W (outputs);  D[m, n] = C[m, n]                    (prefill, many rows)

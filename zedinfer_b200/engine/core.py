@@ -20,6 +20,7 @@ from ..cache.manager import CacheManager, RequestCache
 from ..config.registry import load_model_config
 from ..parts.base import StepContext
 from ..weights.loader import load_weights
+from ..weights.random_init import random_tensors
 from .descriptor import pack_step, step_padding, step_signature
 from .model import Model
 
@@ -49,23 +50,6 @@ def require_gpu(device) -> torch.device:
     if dev.type != "cuda":
         raise RuntimeError(f"zedinfer_b200 runs on an NVIDIA GPU only, not on {dev}")
     return dev
-
-
-def _random_tensors_on_device(specs, seed: int, dtype: torch.dtype, device) -> Dict[str, torch.Tensor]:
-    """Random weights drawn on the device by each tensor's init rule (see weights/random_init.py)."""
-    gen = torch.Generator(device=device)
-    out: Dict[str, torch.Tensor] = {}
-    for i, name in enumerate(sorted(specs)):
-        spec = specs[name]
-        if spec.optional:
-            continue
-        gen.manual_seed((seed * 1000003 + i) & 0x7fffffffffff)
-        rule, std = spec.init
-        t = torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device) * std
-        if rule == "one_plus_normal":
-            t += 1.0
-        out[name] = t.to(dtype)
-    return out
 
 
 class PinnedStaging:
@@ -171,7 +155,8 @@ class EngineCore:
         instead; neither: whatever ``gpu_memory_utilization`` of the device leaves after the weights.
 
         ``model_dir=None`` with ``config`` (a config.json dict) and ``random_seed`` builds the model with
-        random weights drawn on the device, without a folder (benchmarks of large shapes)."""
+        random weights drawn on the device, without a folder (benchmarks of large shapes); the values are those
+        that ``write_random_model(config, random_seed, ...)`` writes (weights/random_init.py)."""
         self.device = require_gpu(device)
         self.dtype = parse_dtype(dtype)
         torch.cuda.set_device(self.device)
@@ -187,7 +172,7 @@ class EngineCore:
             self.config = self.arch.parse(config)
             self.spec = self.arch.build_spec(self.config)
             self.model = Model(self.spec)
-            tensors = _random_tensors_on_device(self.model.tensor_specs(), random_seed, self.dtype, self.device)
+            tensors = random_tensors(self.model.tensor_specs(), random_seed, self.dtype, device=self.device)
         self.model.bind(tensors, self.dtype, self.device)
         del tensors
         self.page_size = int(page_size)

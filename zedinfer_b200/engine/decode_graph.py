@@ -129,6 +129,17 @@ class DecodeGraph:
             rows = h[base: base + b * width].reshape(b, width)
             rows[first:, :] = scratch          # wherever a padding row's position points (a looping graph moves it on)
 
+    def _write_tables(self, i: int, rc) -> None:
+        """Row ``i`` of every group's block table := the request's pages; entries that a window has passed and given
+        back (-1) point at the scratch page, whose keys the kernels mask like any other outside the window."""
+        b, width, h = self.bucket, self.core.table_width, self.host
+        scratch = self.core.cache.scratch_page
+        for g in range(len(self.core.cache.groups)):
+            tab = np.asarray(rc.tables[g], dtype=np.int32)
+            base = self.off_tab + (g * b + i) * width
+            h[base: base + tab.size] = np.where(tab < 0, scratch, tab)
+            h[base + tab.size: base + width] = 0
+
     def fill(self, tokens: Sequence[int], rcs: Sequence, reserve_ahead: int = 0) -> None:
         """Refresh the static buffers for these requests (one token each) and upload what changed.
 
@@ -148,17 +159,13 @@ class DecodeGraph:
         tables_dirty = False
         sigs = self._slot_sig
         for i, rc in enumerate(rcs):
-            sig = (rc.request_id, rc.version)
+            sig = (rc.request_id, rc.serial, rc.version)
             if sigs[i] == sig:
                 continue
             sigs[i] = sig
             tables_dirty = True
             h[self.off_slots + i] = rc.slot
-            for g in range(ng):
-                tab = rc.tables[g]
-                base = self.off_tab + (g * b + i) * width
-                h[base: base + len(tab)] = tab
-                h[base + len(tab): base + width] = 0
+            self._write_tables(i, rc)
         if n != self._n_filled:
             self._pad_rows(n)
             for i in range(n, b):
@@ -178,7 +185,7 @@ class DecodeGraph:
 
     def holds(self, rcs: Sequence) -> bool:
         """The last fill put exactly these requests into the first rows."""
-        return len(rcs) == self._n_filled and all(sig is not None and sig[0] == rc.request_id
+        return len(rcs) == self._n_filled and all(sig is not None and sig[:2] == (rc.request_id, rc.serial)
                                                   for sig, rc in zip(self._slot_sig, rcs))
 
     def run_ahead(self, rcs: Sequence, sampled: torch.Tensor) -> torch.Tensor:
@@ -190,16 +197,12 @@ class DecodeGraph:
         h = self.host
         dirty = False
         for i, rc in enumerate(rcs):
-            sig = (rc.request_id, rc.version)
+            sig = (rc.request_id, rc.serial, rc.version)
             if self._slot_sig[i] == sig:
                 continue
             self._slot_sig[i] = sig
             dirty = True
-            for g in range(ng):
-                tab = rc.tables[g]
-                base = self.off_tab + (g * b + i) * width
-                h[base: base + len(tab)] = tab
-                h[base + len(tab): base + width] = 0
+            self._write_tables(i, rc)
         if dirty:
             head = self.off_seg                               # ids and positions stay as the device has them
             self.core._ring.stage_into(h[head:], self.dev[head:])

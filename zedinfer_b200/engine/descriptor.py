@@ -133,9 +133,11 @@ def pack_step(names: Sequence, tokens: Sequence[Sequence[int]], wants: Sequence[
             w += 1
         host[off_slots + s] = slots[i]
         for g in range(n_groups):
-            tab = tables[i][g]
+            tab = np.asarray(tables[i][g], dtype=np.int32)
             base = off_tab + (g * n_seg + s) * width
-            host[base: base + len(tab)] = tab
+            # a page that a window has passed and given back (-1) is shown to the kernels as the scratch page:
+            # its keys are masked anyway, and no kernel ever forms an address or a TMA coordinate from -1
+            host[base: base + tab.size] = np.where(tab < 0, scratch_page, tab)
         if not (lead and i < lead_real):
             for q0 in range(0, k, tile_rows):
                 host[off_tiles + 3 * tile: off_tiles + 3 * tile + 3] = (t + q0, min(tile_rows, k - q0), s)

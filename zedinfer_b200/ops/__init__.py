@@ -8,12 +8,15 @@ reduced-precision matrix mode can slip in.
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import Dict, Optional
 
 import torch
 
 from ._lib import (BF16, F32, KernelError, Library, c_float, c_int, c_ll, dtype_code, need_contiguous, need_cuda,
                    need_int32, ptr, stream)
+
+# Library products keep float32 sums: without this cuBLAS may pick split-K kernels that add partial sums in bfloat16.
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
 _elementwise = Library("elementwise")
 _gemm_simt = Library("gemm_simt")
@@ -237,6 +240,23 @@ def _smallm_scratch(device, n: int, k: int, silu_mul: bool):
     return part, counters
 
 
+_retired: list = []
+
+
+def _grown_scratch(key, floats: int, device) -> torch.Tensor:
+    """A float32 scratch buffer of at least ``floats`` entries for ``key``, grown on demand.  A CUDA graph captured
+    earlier has the old buffer's address baked in and goes on writing there when it is replayed, so a buffer that is
+    outgrown is never given back to the allocator: it is kept (``_retired``) for the life of the process.  Growth
+    at least doubles the size, so all retired buffers together stay smaller than the live one."""
+    cur = _scratch.get(key)
+    if cur is None or cur.numel() < floats:
+        if cur is not None:
+            _retired.append(cur)
+            floats = max(floats, 2 * cur.numel())
+        cur = _scratch[key] = torch.empty(floats, dtype=torch.float32, device=device)
+    return cur
+
+
 def _tc_status(device) -> torch.Tensor:
     key = ("tc_status", device)
     if key not in _scratch:
@@ -457,10 +477,7 @@ def decode_attention_tma(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
         part_floats = int(lib.zi_decode_attention_tma_part_floats(c_int(q.shape[0]), c_int(n_heads), c_int(n_kv_heads),
                                                                    c_int(head_dim), c_int(int(max_kv_len))))
         if part_floats:
-            key = ("decode_parts", q.device)
-            if key not in _scratch or _scratch[key].numel() < part_floats:
-                _scratch[key] = torch.empty(part_floats, dtype=torch.float32, device=q.device)
-            part = _scratch[key]
+            part = _grown_scratch(("decode_parts", q.device), part_floats, q.device)
     _attention_mma.call("zi_decode_attention_tma", ptr(q), ptr(cache), ptr(out), ptr(tables), ptr(tok_seg), ptr(pos),
                         ptr(_tc_status(q.device)), c_int(q.shape[0]), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
                         c_int(page_size), c_int(tables.shape[1]), c_ll(cache.shape[0]), c_ll(page_stride), c_ll(kv_stride),
