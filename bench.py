@@ -176,8 +176,7 @@ def measure_decode_device(core, cfg, batch, steps, warmup):
     prompts = random_prompts(batch, PROMPT_LEN, cfg["vocab_size"], SEED + batch)
     rids, first = prefill_requests(core, prompts, f"dev{batch}")
     rcs = [core.request(r) for r in rids]
-    mid = (PROMPT_LEN + CONTEXT) // 2
-    start = max(PROMPT_LEN, min(mid - steps // 2, CONTEXT - steps - warmup - 1))
+    start = decode_start(steps, warmup)
     total_new = (start - PROMPT_LEN) + warmup + steps
     for rc in rcs:
         core.cache.ensure(rc, rc.length + total_new + 1)
@@ -187,18 +186,37 @@ def measure_decode_device(core, cfg, batch, steps, warmup):
         g.replay()
     for _ in range(warmup):
         g.replay()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # exactly `steps` steps between the first and the last event; events in between cut them into a few regions
+    # whose rates give the spread (an event costs nothing that a step would notice)
+    cuts = region_cuts(steps)
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(len(cuts) + 1)]
     torch.cuda.synchronize()
-    a.record()
-    for _ in range(steps):
-        g.replay()
-    b.record()
+    events[0].record()
+    done = 0
+    for k, upto in enumerate(cuts):
+        for _ in range(upto - done):
+            g.replay()
+        done = upto
+        events[k + 1].record()
     torch.cuda.synchronize()
-    ms = a.elapsed_time(b) / steps
+    ms = events[0].elapsed_time(events[-1]) / steps
+    per_region = [events[k].elapsed_time(events[k + 1]) / (cuts[k] - (cuts[k - 1] if k else 0)) for k in range(len(cuts))]
     for rid in rids:
         core.end(rid)
     mean_ctx = start + warmup + steps / 2.0
-    return {"tok_s": batch * 1000.0 / ms, "ms": ms, "mean_ctx": mean_ctx, "launches": g.launches * steps}
+    return {"tok_s": batch * 1000.0 / ms, "ms": ms, "mean_ctx": mean_ctx, "launches": g.launches * steps,
+            "spread": spread(per_region)}
+
+
+def region_cuts(steps, regions=5):
+    """Step counts at which the timed steps are cut into (at most) ``regions`` regions of equal length."""
+    regions = max(1, min(regions, steps))
+    return [steps * (k + 1) // regions for k in range(regions)]
+
+
+def spread(per_region_ms):
+    v = sorted(per_region_ms)
+    return {"regions": len(v), "ms_min": round(v[0], 4), "ms_median": round(v[len(v) // 2], 4), "ms_max": round(v[-1], 4)}
 
 
 def measure_decode_e2e(core, cfg, batch, steps, warmup, run_ahead=True):
@@ -225,12 +243,18 @@ def measure_decode_e2e(core, cfg, batch, steps, warmup, run_ahead=True):
     for _ in range(warmup):
         engine.step()
     h2d0 = core._ring.bytes_staged
+    cuts = region_cuts(steps)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    for _ in range(steps):
-        engine.step()
+    stamps, done = [t0], 0
+    for upto in cuts:                                # the host's clock at a few places on the way: the spread
+        for _ in range(upto - done):
+            engine.step()
+        done = upto
+        stamps.append(time.perf_counter())
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
+    per_region = [(stamps[k + 1] - stamps[k]) * 1000.0 / (cuts[k] - (cuts[k - 1] if k else 0)) for k in range(len(cuts))]
     h2d = (core._ring.bytes_staged - h2d0) / steps
     for r in reqs:
         engine.scheduler.cancel(r)
@@ -238,7 +262,8 @@ def measure_decode_e2e(core, cfg, batch, steps, warmup, run_ahead=True):
         engine.step()
     for r in reqs:
         core.end(r.request_id)
-    return {"tok_s": batch * steps / dt, "ms": dt * 1000.0 / steps, "h2d": int(h2d), "d2h": 4 * (batch + 1)}      # the tokens and the kernels' status word
+    return {"tok_s": batch * steps / dt, "ms": dt * 1000.0 / steps, "h2d": int(h2d), "d2h": 4 * (batch + 1),      # the tokens and the kernels' status word
+            "spread": spread(per_region)}
 
 
 def measure_head(core, cfg, rows, reps=20):
@@ -259,6 +284,86 @@ def measure_head(core, cfg, rows, reps=20):
     return a.elapsed_time(b) / reps
 
 
+REF_BENCH = os.path.join(ROOT, "baseline", "_ref", "ref_bench")
+
+
+def decode_start(steps, warmup):
+    mid = (PROMPT_LEN + CONTEXT) // 2
+    return max(PROMPT_LEN, min(mid - steps // 2, CONTEXT - steps - warmup - 1))
+
+
+def reference_arm(args):
+    """The same metric and sizes on tianyuxbear/zedinfer's own NVIDIA path: ``baseline/_ref/ref_bench`` is the
+    reference's unmodified transformer_forward, paged context, block pool, CUDA kernels, cuBLASLt product and
+    FlashInfer wrappers, compiled by ``baseline/ref_bench/build.py`` and driven as its profiler and serving loop drive
+    them (random bfloat16 weights of the same shapes, its own argmax sampler reading every request's token back each
+    step).  Nothing of zedinfer_b200 runs in this arm."""
+    def unavailable(why):
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    if args.gpus != 1:
+        return unavailable("the reference runs on one GPU")
+    if not (os.path.isfile(REF_BENCH) and os.access(REF_BENCH, os.X_OK)):
+        return unavailable("baseline/_ref/ref_bench is not built: tianyuxbear/zedinfer has no Python package to install "
+                           "(an xmake C++ project with empty submodules); `python baseline/ref_bench/build.py <checkout>` "
+                           "compiles its NVIDIA path with nvcc")
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+    cfg = dict(MODEL_1P5B, num_hidden_layers=args.layers)
+    pk = peaks()
+    start = decode_start(steps, warmup)
+    pts = [] if args.no_points else [1, 64]
+    jobs = [f"prefill:{PROMPT_LEN}:5:3", f"decode:{args.batch}:{start}:{steps}:{warmup}"]
+    jobs += [f"decode:{b}:{decode_start(min(steps, 128), warmup)}:{min(steps, 128)}:{warmup}" for b in pts]
+    cmd = [REF_BENCH] + [str(cfg[k]) for k in ("num_hidden_layers", "hidden_size", "intermediate_size", "vocab_size",
+                                                "num_attention_heads", "num_key_value_heads", "head_dim", "rope_theta",
+                                                "rms_norm_eps")] + [str(PAGE_SIZE)] + jobs
+    clocks = ClockSampler()
+    clocks.start()
+    try:
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=1500)
+    except subprocess.TimeoutExpired:
+        clocks.stop()
+        return unavailable("the reference's run did not end within 25 minutes")
+    clocks.stop()
+    rows = [ln.split() for ln in proc.stdout.splitlines() if ln.split() and ln.split()[0] in ("prefill", "decode")]
+    if proc.returncode != 0 or len(rows) != len(jobs):
+        tail = (proc.stderr or proc.stdout).strip().splitlines()[-1:] or ["no output"]
+        return unavailable(f"the reference's own run failed (exit {proc.returncode}): {tail[0][:200]}")
+    pre_ms = float(rows[0][2])
+    dec = {int(r[1]): float(r[4]) for r in rows[1:]}
+    ms = dec[args.batch]
+    mean_ctx = start + warmup + steps / 2.0
+    step_bytes = weight_bytes_per_step(cfg, args.layers) + args.batch * mean_ctx * kv_bytes_per_token(cfg, args.layers)
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    flops = prefill_flops(cfg, args.layers, PROMPT_LEN)
+    value = args.batch * 1000.0 / ms
+    line = {
+        "metric": "decode_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "impl": "reference",
+        "config": {"model": "qwen2-1.5b-class", "layers": args.layers, "layers_full": MODEL_1P5B["num_hidden_layers"],
+                   "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": args.batch,
+                   "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "mean_context_timed": round(mean_ctx, 1),
+                   "page_size": PAGE_SIZE, "weights": "random N(0,0.02)", "parallelism": "single-gpu",
+                   "l2": "inputs larger than L2 (weights 3.1 GB per step)", "peaks": pk["source"],
+                   "build": "nv-gpu + flashinfer, sm_100a", "timing": "host clock around device_synchronize"},
+        "clocks": clocks.summary(),
+        # the reference's step always takes its token ids from the host and reads every request's token back
+        "e2e": {"value": round(value, 1), "unit": "tokens/s", "ms_per_step": round(ms, 4),
+                "h2d_bytes_per_step": 12 * args.batch, "d2h_bytes_per_step": 8 * args.batch},
+        "gpu_launches": None,
+        "prefill": {"value": round(PROMPT_LEN / pre_ms * 1000.0, 1), "tokens": PROMPT_LEN, "ms": round(pre_ms, 3),
+                    "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": {f"decode_b{b}": round(b * 1000.0 / dec[b], 1) for b in pts},
+    }
+    print(json.dumps(line))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--gpus", type=int, default=1)
@@ -272,11 +377,7 @@ def main():
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference",
-                          "unavailable": "tianyuxbear/zedinfer does not install offline: it has no Python package at "
-                                         "its root (an xmake C++ project), xmake is absent and its third_party "
-                                         "submodules (flashinfer, cutlass, nlohmann_json, plog, argparse) are empty"}))
-        return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured")
         return 2
@@ -316,7 +417,7 @@ def main():
     layers_achieved = (step_bytes - head_bytes) / (max(dev["ms"] - head_ms, 1e-6) * 1e-3) / 1e9
     line = {
         "metric": "decode_tokens_per_s", "value": round(dev["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1,
-        "steps": steps, "warmup": warmup, "ms_per_step": round(dev["ms"], 4), "higher_is_better": True,
+        "steps": steps, "warmup": warmup, "ms_per_step": round(dev["ms"], 4), "spread": dev["spread"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
         "config": {"model": "qwen2-1.5b-class", "layers": args.layers, "layers_full": MODEL_1P5B["num_hidden_layers"],
                    "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
@@ -328,7 +429,7 @@ def main():
                    "l2": "inputs larger than L2 (weights 3.1 GB per step)", "peaks": pk["source"]},
         "clocks": clocks.summary(),
         "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "ms_per_step": round(e2e["ms"], 4),
-                "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"], "spread": e2e["spread"],
                 "host_in_step": {"value": round(e2e_sync["tok_s"], 1), "ms_per_step": round(e2e_sync["ms"], 4),
                                  "h2d_bytes_per_step": e2e_sync["h2d"]}},
         "gpu_launches": dev["launches"],

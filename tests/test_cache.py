@@ -171,3 +171,21 @@ def test_a_reopened_request_id_is_another_request():
     m.ensure(b, 6)
     assert (b.request_id, b.version) == (first[0], first[2]) and b.serial != first[1]
     assert (b.request_id, b.serial, b.version) != first
+
+
+def test_state_can_be_reset_and_copied_between_requests():
+    m = CacheManager([(0, StateNeed((3,), torch.float32)), (2, StateNeed((2, 2), torch.float32))], page_size=4, max_requests=3)
+    m.allocate_device(4, torch.float32, "cpu")
+    a, b = m.open("a"), m.open("b")
+    va, vb = m.view_for_call(0).tensor, m.view_for_call(2).tensor
+    va[a.slot] += 5.0
+    vb[a.slot] += 7.0
+    m.copy_state(a, b)
+    assert float(va[b.slot].sum()) == 15.0 and float(vb[b.slot].sum()) == 28.0
+    m.reset_state(a)
+    assert float(va[a.slot].abs().sum()) == 0.0 and float(vb[a.slot].abs().sum()) == 0.0
+    assert float(va[b.slot].sum()) == 15.0
+    m.close(a)
+    c = m.open("c")                      # takes a's slot: zeroed when it opens
+    assert c.slot == 0 or float(va[c.slot].abs().sum()) == 0.0
+    m.check()

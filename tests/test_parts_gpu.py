@@ -173,6 +173,9 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
         folder = write_random_model(raw, 4, str(tmp_path / "toy"), dtype="float32", init_scale=5.0)
         core = EngineCore(folder, "float32", page_size=4, num_pages=32, max_requests=3)
         assert len(core.cache.groups) == 1 and core.cache.slots.num_slots == 3
+        # the mixer loops over the step's segments on the host, so no step of this model is captured; the engine
+        # says which part that is due to
+        assert not core.capture_safe and core.capture_blockers == ["layers.0.mixer.DecayMixer"]
         rng = random.Random(2)
         reqs = {"a": [rng.randrange(300) for _ in range(21)], "b": [rng.randrange(300) for _ in range(9)]}
 
@@ -364,3 +367,147 @@ def test_toy_routed_feed_forward_and_toy_position_rule(tmp_path):
         unregister_architecture("Toy2ForCausalLM")
         unregister("ffn", "toy_top1")
         unregister("position", "toy_half_rope")
+
+
+# ---- a toy architecture whose two ends and whose positions are not the built-in ones ----------------------
+def test_toy_embedding_head_and_two_position_axes(tmp_path):
+    """An embedding that scales its rows, a head with a bias of its own, and a position rule that reads the second
+    of two position numbers per token, all defined here and named in the ModelSpec (``embedding=``, ``head=``,
+    ``position_width=2``); nothing under ``zedinfer_b200/`` knows them.  Logits under changing portions equal a plain
+    computation; greedy generation through the engine with captured decode steps (positions of both axes then move
+    on the device, step after step) gives the plain tokens."""
+    from zedinfer_b200 import GenerationConfig, SchedulerConfig, ops
+    from zedinfer_b200.config import (LayerCall, LayerSpec, ModelSpec, PartSpec, register_architecture,
+                                      unregister_architecture)
+    from zedinfer_b200.engine import InferenceEngine
+    from zedinfer_b200.engine.core import EngineCore, StepEntry
+    from zedinfer_b200.parts import (Embedding, Head, PositionEncoding, register_embedding, register_head,
+                                     register_position, unregister)
+    from zedinfer_b200.weights import TensorSpec, write_random_model
+
+    @register_embedding("toy_scaled_embedding")
+    class ScaledEmbedding(Embedding):
+        capture_safe = True
+
+        def __init__(self, vocab_size, hidden_size, scale):
+            self.v, self.h, self.scale, self.table = vocab_size, hidden_size, scale, None
+
+        def tensor_specs(self):
+            return {"tok.weight": TensorSpec((self.v, self.h))}
+
+        def bind(self, tensors):
+            self.table = tensors["tok.weight"].contiguous()
+
+        def forward(self, ids, out):
+            ops.embedding(self.table, ids, out)
+            out.mul_(self.scale)
+
+    @register_head("toy_biased_head")
+    class BiasedHead(Head):
+        capture_safe = True
+
+        def __init__(self, vocab_size, hidden_size):
+            self.v, self.h = vocab_size, hidden_size
+
+        def tensor_specs(self):
+            return {"out.weight": TensorSpec((self.v, self.h)), "out.bias": TensorSpec((self.v,))}
+
+        def bind(self, tensors, embedding=None):
+            assert embedding is None                      # this embedding offers nothing to tie to
+            self.w, self.b = tensors["out.weight"].contiguous(), tensors["out.bias"].contiguous()
+
+        def forward(self, x, out):
+            ops.linear(x, self.w, self.b, out)
+
+    @register_position("toy_second_axis_rope")
+    class SecondAxisRope(PositionEncoding):
+        """The framework's rotation kernel fed with the second position number of every token."""
+        capture_safe = True
+
+        def __init__(self, head_dim, theta):
+            self.head_dim, self.theta, self._inv = head_dim, theta, None
+
+        def rotate_append(self, qkv, q_out, cache, ctx, n_heads, n_kv_heads, head_dim, write_kv):
+            assert ctx.position_axes.shape == (2, ctx.n_tokens)
+            if self._inv is None:
+                expo = torch.arange(0, head_dim, 2, dtype=torch.float32) / float(head_dim)
+                self._inv = (1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float32), expo)).to(qkv.device)
+            ops.rope_append(qkv, q_out, cache.tensor, ctx.tables[cache.group], ctx.tok_seg, ctx.position_axes[1],
+                            self._inv, n_heads, n_kv_heads, head_dim, cache.page_size, cache.page_stride,
+                            cache.kv_stride, write_kv=write_kv)
+
+    H, V, INTER, SCALE = 48, 157, 80, 3.0
+
+    def build_spec(raw):
+        norm = PartSpec("rmsnorm", {"size": H, "eps": 1e-5})
+        attn = PartSpec("attention", {"hidden_size": H, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16,
+                                      "position": PartSpec("toy_second_axis_rope", {"head_dim": 16, "theta": 500.0})})
+        dense = PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": INTER})
+        prefixes = {"mixer": "mixer.", "ffn": "mlp.", "norm1": "ln1.", "norm2": "ln2."}
+        layer = LayerSpec("pre_norm", attn, dense, {"norm1": norm, "norm2": norm}, prefixes)
+        return ModelSpec("Toy3ForCausalLM", V, H, (layer, layer), (LayerCall(0), LayerCall(1)), norm, False,
+                         raw["max_position_embeddings"],
+                         embedding=PartSpec("toy_scaled_embedding", {"vocab_size": V, "hidden_size": H, "scale": SCALE}),
+                         head=PartSpec("toy_biased_head", {"vocab_size": V, "hidden_size": H}), position_width=2)
+
+    register_architecture("Toy3ForCausalLM", model_types=("toy3",), parse=lambda raw: raw, build_spec=build_spec)
+    try:
+        raw = {"architectures": ["Toy3ForCausalLM"], "max_position_embeddings": 128}
+        folder = write_random_model(raw, 4, str(tmp_path / "toy3"), dtype="float32", init_scale=5.0)
+        w = P.read_safetensors(os.path.join(folder, "model.safetensors"))
+        assert "tok.weight" in w and "out.bias" in w and "embed_tokens.weight" not in w
+
+        def plain(ids):
+            t = len(ids)
+            pos = torch.arange(t)
+            hdn = P.embedding(ids, w["tok.weight"]) * SCALE
+            for layer in (0, 1):
+                p = f"layers.{layer}."
+                x = P.rms_norm(hdn, w[p + "ln1.weight"], 1e-5)
+                q = P.linear(x, w[p + "mixer.q_proj.weight"], w[p + "mixer.q_proj.bias"]).view(t, 4, 16)
+                k = P.linear(x, w[p + "mixer.k_proj.weight"], w[p + "mixer.k_proj.bias"]).view(t, 2, 16)
+                v = P.linear(x, w[p + "mixer.v_proj.weight"], w[p + "mixer.v_proj.bias"]).view(t, 2, 16)
+                a = P.attention(P.rope(q, pos, 500.0), P.rope(k, pos, 500.0), v, 0.25)
+                hdn = hdn + P.linear(a.reshape(t, 64), w[p + "mixer.o_proj.weight"], None)
+                x = P.rms_norm(hdn, w[p + "ln2.weight"], 1e-5)
+                hdn = hdn + P.linear(P.swiglu(P.linear(x, w[p + "mlp.gate_proj.weight"], None),
+                                              P.linear(x, w[p + "mlp.up_proj.weight"], None)),
+                                     w[p + "mlp.down_proj.weight"], None)
+            return P.linear(P.rms_norm(hdn, w["norm.weight"], 1e-5), w["out.weight"], w["out.bias"])
+
+        core = EngineCore(folder, "float32", page_size=4, num_pages=32, max_requests=3)
+        assert core.capture_blockers == [] and core.spec.position_width == 2
+        rng = random.Random(3)
+        reqs = {"a": [rng.randrange(V) for _ in range(23)], "b": [rng.randrange(V) for _ in range(10)]}
+        ref = {rid: plain(ids) for rid, ids in reqs.items()}
+        done, worst = {"a": 0, "b": 0}, 0.0
+        for cut in [[("a", 6), ("b", 3)], [("a", 2), ("b", 7)], [("a", 11)], [("a", 4)]]:
+            entries = [StepEntry(rid, reqs[rid][done[rid]:done[rid] + n], list(range(n))) for rid, n in cut]
+            logits = core.step(entries).cpu()
+            row = 0
+            for rid, n in cut:
+                worst = max(worst, float((logits[row:row + n] - ref[rid][done[rid]:done[rid] + n]).abs().max()))
+                row += n
+                done[rid] += n
+        assert worst < 2e-4, worst
+        del core
+        # greedy generation, decode steps captured, tokens handed on and both position axes moved on the device
+        prompt, n_new = reqs["b"], 14
+        seq, expected = list(prompt), []
+        for _ in range(n_new):
+            expected.append(P.greedy(plain(seq)[-1]))
+            seq.append(expected[-1])
+        engine = InferenceEngine.create(folder, SchedulerConfig(num_kv_pages=32, kv_block_size=4, max_batch_requests=2,
+                                                                cuda_graphs=True), dtype="float32")
+        out = engine.generate_tokens(prompt, GenerationConfig(max_new_tokens=n_new, ignore_eos=True))
+        assert out.output_ids == expected
+        graphs = list(engine.core._decode_graphs.values())
+        assert graphs and all(g.ctx.position_axes.shape[0] == 2 for g in graphs)
+        for g in graphs:
+            axes = g.ctx.position_axes.cpu()
+            assert torch.equal(axes[0], axes[1])
+    finally:
+        unregister_architecture("Toy3ForCausalLM")
+        unregister("embedding", "toy_scaled_embedding")
+        unregister("head", "toy_biased_head")
+        unregister("position", "toy_second_axis_rope")

@@ -193,6 +193,21 @@ class CacheManager:
         self._requests[request_id] = rc
         return rc
 
+    def reset_state(self, rc: RequestCache) -> None:
+        """Zero the fixed-size state of ``rc`` in every call that keeps one (a request that starts over, e.g. after
+        preemption with the same slot); the reference's ``reset_slot`` (include/frontend/models/ssm_state_pool.hpp:61-131)."""
+        if rc.slot >= 0:
+            for t in self._state_tensors.values():
+                t[rc.slot].zero_()
+
+    def copy_state(self, src: RequestCache, dst: RequestCache) -> None:
+        """``dst``'s fixed-size state := ``src``'s, in every call that keeps one (a request that continues from
+        another's state); the reference's ``copy_slot_state``."""
+        if src.slot < 0 or dst.slot < 0:
+            raise ValueError("copy_state needs two requests that hold state slots")
+        for t in self._state_tensors.values():
+            t[dst.slot].copy_(t[src.slot])
+
     def get(self, request_id) -> Optional[RequestCache]:
         return self._requests.get(request_id)
 

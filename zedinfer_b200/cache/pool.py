@@ -72,7 +72,7 @@ class StateSlotPool:
 
     The verbs follow the reference's state pool (include/frontend/models/ssm_state_pool.hpp:61-131):
     acquire, release, number of free slots.  Resetting and copying a slot's contents belongs to
-    whoever owns the device tensors (the cache manager).
+    whoever owns the device tensors: ``CacheManager.reset_state`` and ``CacheManager.copy_state``.
     """
 
     def __init__(self, num_slots: int):

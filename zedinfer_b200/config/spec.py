@@ -73,12 +73,24 @@ class ModelSpec:
     head_name: str = "lm_head.weight"
     bos_token_id: Optional[int] = None
     eos_token_ids: Tuple[int, ...] = ()
+    # The parts at the two ends of the model, registered like every other part.  None: the plain table look-up
+    # ("token_embedding") and the bias-free product with the head weight, or the embedding table when tied
+    # ("output_head"), built from vocab_size, hidden_size, embed_name, head_name and tie_word_embeddings.
+    embedding: Optional[PartSpec] = None
+    head: Optional[PartSpec] = None
+    # How many position numbers a token carries (axes of a multi-axis position rule).  The step's descriptor, the
+    # captured decode step and the on-device hand-over between decode steps all carry this many per token; every
+    # axis of a text token holds its index in the request.  Parts read ``StepContext.position_axes`` ([width, tokens]);
+    # ``StepContext.positions`` is axis 0.
+    position_width: int = 1
 
     def validate(self) -> None:
         if self.vocab_size <= 0 or self.hidden_size <= 0:
             raise ValueError("vocab_size and hidden_size must be positive")
         if not self.layers:
             raise ValueError("a model needs at least one layer")
+        if self.position_width < 1:
+            raise ValueError(f"position_width={self.position_width} must be at least 1")
         for pos, call in enumerate(self.schedule):
             if not 0 <= call.layer < len(self.layers):
                 raise ValueError(f"schedule[{pos}] names layer {call.layer}, "

@@ -241,20 +241,24 @@ ZI_EXPORT int zi_sample(const float* logits, int* out, const float* temperature,
 }
 
 // Hand-over between decode steps that run back to back on the device: the chosen token becomes
-// the next input and every position moves on by one.
-__global__ void advance_decode_kernel(int* __restrict__ ids, int* __restrict__ pos, const int* __restrict__ sampled, int n) {
+// the next input and every position moves on by one.  A token may carry several position numbers (`axes`
+// runs, `axis_stride` elements apart); all of them move.
+__global__ void advance_decode_kernel(int* __restrict__ ids, int* __restrict__ pos, const int* __restrict__ sampled, int n,
+                                      int axes, long long axis_stride) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     pdl_trigger_early();
     pdl_wait();
     pdl_trigger_late();
     if (i < n) {
         ids[i] = ld_dep(sampled + i);
-        pos[i] += 1;
+        for (int a = 0; a < axes; ++a) pos[a * axis_stride + i] += 1;
     }
 }
 
-ZI_EXPORT int zi_advance_decode(int* ids, int* pos, const int* sampled, int n, cudaStream_t stream) {
+ZI_EXPORT int zi_advance_decode(int* ids, int* pos, const int* sampled, int n, int axes, long long axis_stride,
+                                cudaStream_t stream) {
     if (n <= 0) return 0;
-    zi_launch(advance_decode_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, ids, pos, (const int*)sampled, n);
+    if (axes < 1 || (axes > 1 && axis_stride < n)) return zi_fail("advance_decode: %d position axes %lld apart for %d rows", axes, axis_stride, n);
+    zi_launch(advance_decode_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, ids, pos, (const int*)sampled, n, axes, axis_stride);
     return zi_check_launch("advance_decode");
 }

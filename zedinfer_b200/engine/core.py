@@ -100,14 +100,16 @@ class PinnedStaging:
 def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache], cache: CacheManager,
                        table_width: int, dtype: torch.dtype, device: torch.device, vocab: int,
                        ring: "PinnedStaging", pad_segments: int = 0,
-                       into: Optional[torch.Tensor] = None) -> Tuple[StepContext, Optional[torch.Tensor]]:
+                       into: Optional[torch.Tensor] = None, pos_width: int = 1
+                       ) -> Tuple[StepContext, Optional[torch.Tensor]]:
     """Flatten the entries into one device descriptor (a single host-to-device copy; the layout is
     ``descriptor.pack_step``'s).  ``into``: a device buffer to hold the descriptor (a captured step's static buffer)
     instead of a fresh one; its length must fit."""
     n_groups = len(cache.groups)
     host, lay = pack_step([e.request_id for e in entries], [e.tokens for e in entries], [e.want for e in entries],
                           [rc.length for rc in rcs], [rc.slot for rc in rcs], [rc.tables for rc in rcs], n_groups,
-                          table_width, vocab, cache.scratch_page if cache.groups else 0, ops.PREFILL_TILE_ROWS, pad_segments)
+                          table_width, vocab, cache.scratch_page if cache.groups else 0, ops.PREFILL_TILE_ROWS, pad_segments,
+                          pos_width)
     n_seg, n_tok, width, total = lay.n_seg, lay.n_tok, lay.width, lay.total
     off_ids, off_pos, off_seg, off_want = lay.off_ids, lay.off_pos, lay.off_seg, lay.off_want
     off_slots, off_tiles, off_tab = lay.off_slots, lay.off_tiles, lay.off_tab
@@ -126,6 +128,7 @@ def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache]
         n_tokens=n_tok, n_segments=n_seg, dtype=dtype, device=device,
         token_ids=dev[off_ids: off_ids + n_tok], positions=dev[off_pos: off_pos + n_tok],
         tok_seg=dev[off_seg: off_seg + n_tok], tables=tables, slots=dev[off_slots: off_slots + n_seg],
+        position_axes=dev[off_pos: off_pos + pos_width * n_tok].view(pos_width, n_tok),
         seg_start_host=seg_start, seg_len_host=seg_len, seg_pos0_host=seg_pos0, slots_host=slots,
         decode_only=all(k == 1 for k in seg_len), max_kv_len=max(max_kv, 1))
     ctx.extras["attn_tiles"] = dev[off_tiles: off_tiles + 3 * n_tiles].view(n_tiles, 3)
@@ -204,7 +207,8 @@ class EngineCore:
         self._step_graphs: Dict[tuple, "StepGraph"] = {}
         self._step_seen: Dict[tuple, _SeenStep] = {}
         self._graph_pool = None
-        self.capture_safe = self.model.capture_safe()
+        self.capture_blockers = self.model.capture_blockers()     # the parts that keep steps from being captured, by name
+        self.capture_safe = not self.capture_blockers
 
     @staticmethod
     def kernel_libraries(dtype) -> List[str]:
@@ -229,7 +233,7 @@ class EngineCore:
                       ) -> Tuple[StepContext, Optional[torch.Tensor]]:
         """Flatten the entries into one device descriptor (a single host-to-device copy)."""
         return build_step_context(entries, rcs, self.cache, self.table_width, self.dtype, self.device,
-                                  self.spec.vocab_size, self._ring, pad_segments, into)
+                                  self.spec.vocab_size, self._ring, pad_segments, into, self.spec.position_width)
 
     # Steps that are not pure decode are launched kernel by kernel, which costs the host a few milliseconds whatever
     # their size.  Every launch of such a step depends on the step's counts alone, so a step whose counts come back

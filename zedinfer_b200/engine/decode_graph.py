@@ -48,8 +48,9 @@ class DecodeGraph:
         :meth:`set_sampling` brings before a replay (rows of temperature 0 take the most likely token)."""
         self.core, self.bucket, self.loop, self.sample = core, bucket, loop or sample, sample
         b, width, ng = bucket, core.table_width, len(core.cache.groups)
-        self.off_ids, self.off_pos, self.off_seg, self.off_want, self.off_slots = 0, b, 2 * b, 3 * b, 4 * b
-        self.off_tab = 5 * b
+        pw = self.pos_width = core.spec.position_width          # position numbers per token, one run of b per axis
+        self.off_ids, self.off_pos, self.off_seg = 0, b, (1 + pw) * b
+        self.off_want, self.off_slots, self.off_tab = self.off_seg + b, self.off_seg + 2 * b, self.off_seg + 3 * b
         total = self.off_tab + ng * b * width
         self.host = np.zeros(total, dtype=np.int32)
         self.host[self.off_seg: self.off_seg + b] = np.arange(b)
@@ -65,6 +66,7 @@ class DecodeGraph:
             n_tokens=b, n_segments=b, dtype=core.dtype, device=core.device,
             token_ids=d[self.off_ids: self.off_ids + b], positions=d[self.off_pos: self.off_pos + b],
             tok_seg=d[self.off_seg: self.off_seg + b], tables=tables, slots=d[self.off_slots: self.off_slots + b],
+            position_axes=d[self.off_pos: self.off_pos + pw * b].view(pw, b),
             seg_start_host=list(range(b)), seg_len_host=[1] * b, seg_pos0_host=[0] * b, slots_host=[-1] * b,
             decode_only=True, max_kv_len=core.max_seq_len)
         self.want = d[self.off_want: self.off_want + b]
@@ -102,7 +104,7 @@ class DecodeGraph:
             else:
                 ops.argmax(logits, self.sampled[:b])
             self.sampled[b:].copy_(ops.status_word(self.core.device))
-            ops.advance_decode(self.ctx.token_ids, self.ctx.positions, self.sampled[:b])
+            ops.advance_decode(self.ctx.token_ids, self.ctx.position_axes, self.sampled[:b])
         return logits
 
     def set_sampling(self, par: np.ndarray, top_k: np.ndarray) -> None:
@@ -122,7 +124,8 @@ class DecodeGraph:
         scratch = self.core.cache.scratch_page if ng else 0
         h = self.host
         h[self.off_ids + first: self.off_ids + b] = 0
-        h[self.off_pos + first: self.off_pos + b] = 0
+        for axis in range(self.pos_width):
+            h[self.off_pos + axis * b + first: self.off_pos + (axis + 1) * b] = 0
         h[self.off_slots + first: self.off_slots + b] = -1
         for g in range(ng):
             base = self.off_tab + g * b * width
@@ -155,7 +158,8 @@ class DecodeGraph:
         if n and (toks.min() < 0 or toks.max() >= vocab):
             raise ValueError(f"token id outside [0, {vocab})")
         h[self.off_ids: self.off_ids + n] = toks
-        h[self.off_pos: self.off_pos + n] = [rc.length for rc in rcs]
+        for axis in range(self.pos_width):
+            h[self.off_pos + axis * b: self.off_pos + axis * b + n] = [rc.length for rc in rcs]
         tables_dirty = False
         sigs = self._slot_sig
         for i, rc in enumerate(rcs):
@@ -207,7 +211,7 @@ class DecodeGraph:
             head = self.off_seg                               # ids and positions stay as the device has them
             self.core._ring.stage_into(h[head:], self.dev[head:])
         if not self.loop:                                     # a looping graph has moved ids and positions on itself
-            ops.advance_decode(self.ctx.token_ids, self.ctx.positions, sampled, n)
+            ops.advance_decode(self.ctx.token_ids, self.ctx.position_axes, sampled, n)
         self.graph.replay()
         return self.logits[:n]
 

@@ -1,7 +1,7 @@
 """The packed int32 descriptor of a step, built on the host with numpy alone (no device in here, so the layout is
 tested without a GPU).
 
-One array holds everything a step's kernels index by: ``ids | positions | token -> segment | wanted rows | state slots
+One array holds everything a step's kernels index by: ``ids | positions (one run per axis) | token -> segment | wanted rows | state slots
 | attention tiles | block tables of every cache group``.  It goes to the device in a single copy, and a captured step
 keeps it in a static buffer, so its length and every offset must depend on the step's *counts* alone
 (:func:`step_signature`), never on which requests or how many of the single tokens are real.
@@ -63,6 +63,7 @@ class StepLayout:
     total: int
     width: int
     n_groups: int
+    pos_width: int = 1
     max_kv: int = 1
     seg_start: List[int] = field(default_factory=list)
     seg_len: List[int] = field(default_factory=list)
@@ -72,10 +73,13 @@ class StepLayout:
 
 def pack_step(names: Sequence, tokens: Sequence[Sequence[int]], wants: Sequence[Sequence[int]], lengths: Sequence[int],
               slots: Sequence[int], tables: Sequence[Sequence[Sequence[int]]], n_groups: int, width: int, vocab: int,
-              scratch_page: int, tile_rows: int, pad_segments: int = 0) -> Tuple[np.ndarray, StepLayout]:
+              scratch_page: int, tile_rows: int, pad_segments: int = 0, pos_width: int = 1
+              ) -> Tuple[np.ndarray, StepLayout]:
     """``names[i]``: the request of entry i (for messages); ``tokens[i]`` its new tokens; ``wants[i]`` the places
     among them whose logits are wanted; ``lengths[i]`` the tokens it has in the cache; ``slots[i]`` its state slot;
-    ``tables[i][g]`` its page numbers in cache group g.  Returns the descriptor and where everything lies in it."""
+    ``tables[i][g]`` its page numbers in cache group g.  ``pos_width``: position numbers per token (the model's
+    ``position_width``); they lie axis by axis, ``pos_width`` runs of one number per token, and every axis of a token
+    holds its index in the request.  Returns the descriptor and where everything lies in it."""
     lens = [len(t) for t in tokens]
     n_seg = len(tokens) + pad_segments
     n_tok = sum(lens) + pad_segments
@@ -90,14 +94,14 @@ def pack_step(names: Sequence, tokens: Sequence[Sequence[int]], wants: Sequence[
         n_tiles = sum(-(-k // tile_rows) for k in lens[lead_real:])
     else:
         n_tiles = sum(-(-k // tile_rows) for k in lens) + pad_segments
-    off_ids, off_pos, off_seg = 0, n_tok, 2 * n_tok
-    off_want = 3 * n_tok
+    off_ids, off_pos, off_seg = 0, n_tok, (1 + pos_width) * n_tok
+    off_want = off_seg + n_tok
     off_slots = off_want + n_want
     off_tiles = off_slots + n_seg
     off_tab = off_tiles + 3 * n_tiles
     total = off_tab + n_groups * n_seg * width
     lay = StepLayout(n_tok, n_seg, n_want, n_real_want, n_tiles, lead, off_ids, off_pos, off_seg, off_want, off_slots,
-                     off_tiles, off_tab, total, width, n_groups)
+                     off_tiles, off_tab, total, width, n_groups, pos_width)
     host = np.zeros(total, dtype=np.int32)
     t = w = s = tile = 0
     pad_rows: List[int] = []
@@ -124,7 +128,8 @@ def pack_step(names: Sequence, tokens: Sequence[Sequence[int]], wants: Sequence[
         if k and (toks.min() < 0 or toks.max() >= vocab):
             raise ValueError(f"request {names[i]!r}: token id outside [0, {vocab})")
         host[off_ids + t: off_ids + t + k] = toks
-        host[off_pos + t: off_pos + t + k] = np.arange(lengths[i], lengths[i] + k, dtype=np.int32)
+        for axis in range(pos_width):
+            host[off_pos + axis * n_tok + t: off_pos + axis * n_tok + t + k] = np.arange(lengths[i], lengths[i] + k, dtype=np.int32)
         host[off_seg + t: off_seg + t + k] = s
         for j in wants[i]:
             if not 0 <= j < k:

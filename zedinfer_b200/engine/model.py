@@ -9,8 +9,8 @@ import torch
 
 from ..cache.manager import CallCacheView
 from ..config.spec import ModelSpec
+from ..config.spec import PartSpec
 from ..parts.base import Block, ResidualStream, StepContext, block_class, build_part
-from ..parts.embedding import OutputHead, TokenEmbedding
 from ..weights.loader import TensorSpec
 
 
@@ -25,9 +25,12 @@ class Model:
             ffn = build_part("ffn", layer.ffn)
             norms = {role: build_part("norm", ns) for role, ns in layer.norms.items()}
             self.blocks.append(cls(mixer, ffn, norms))
-        self.embedding = TokenEmbedding(spec.vocab_size, spec.hidden_size, spec.embed_name)
+        self.embedding = build_part("embedding", spec.embedding or PartSpec("token_embedding", {
+            "vocab_size": spec.vocab_size, "hidden_size": spec.hidden_size, "name": spec.embed_name}))
         self.final_norm = build_part("norm", spec.final_norm)
-        self.head = OutputHead(spec.vocab_size, spec.hidden_size, spec.tie_word_embeddings, spec.head_name)
+        self.head = build_part("head", spec.head or PartSpec("output_head", {
+            "vocab_size": spec.vocab_size, "hidden_size": spec.hidden_size, "tied": spec.tie_word_embeddings,
+            "name": spec.head_name}))
         self.dtype: Optional[torch.dtype] = None
         self.device: Optional[torch.device] = None
 
@@ -54,15 +57,28 @@ class Model:
         for part, prefix in self._part_prefixes():
             local = {name: tensors[prefix + name] for name in part.tensor_specs() if prefix + name in tensors}
             if part is self.head:
-                self.head.bind(local, embedding=self.embedding.table)
+                self.head.bind(local, embedding=self.embedding.tied_weight())
             else:
                 part.bind(local)
 
+    def capture_blockers(self) -> List[str]:
+        """The parts and arrangements that keep this model's steps from being captured in CUDA graphs (see
+        ``Part.capture_safe``), by name; empty when every step may be captured.  One such part switches graphs off
+        for every step of the model: each step is then launched kernel by kernel, which costs the host a few
+        milliseconds per step whatever the step's size."""
+        out = []
+        for part, prefix in self._part_prefixes():
+            if not getattr(part, "capture_safe", False):
+                out.append(f"{prefix or '(model) '}{type(part).__name__}")
+        for i, blk in enumerate(self.blocks):
+            if not getattr(blk, "capture_safe", False):
+                out.append(f"{self.spec.layer_prefix.format(i=i)}{type(blk).__name__}")
+        return out
+
     def capture_safe(self) -> bool:
         """Every part and arrangement of the model only launches kernels on the step's device tensors, so steps may
-        be captured in CUDA graphs (see ``Part.capture_safe``)."""
-        parts = [part for part, _ in self._part_prefixes()]
-        return all(getattr(x, "capture_safe", False) for x in parts + list(self.blocks))
+        be captured in CUDA graphs."""
+        return not self.capture_blockers()
 
     # ---- cache ------------------------------------------------------------------------------
     def cache_needs(self) -> List[Tuple[int, object]]:

@@ -595,13 +595,18 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: torch.Tensor, t
 
 def advance_decode(ids: torch.Tensor, pos: torch.Tensor, sampled: torch.Tensor, rows: Optional[int] = None) -> None:
     """Hand the chosen tokens to the next decode step: ``ids := sampled``, ``pos += 1`` for the first ``rows`` rows
-    (all of ``ids`` by default)."""
+    (all of ``ids`` by default).  ``pos`` is one position per token, or ``[axes, tokens]`` for a model whose tokens
+    carry several position numbers: every axis moves on by one."""
     need_cuda(ids, pos, sampled)
     need_int32("ids", ids), need_int32("pos", pos), need_int32("sampled", sampled)
     n = ids.numel() if rows is None else int(rows)
-    if n > min(ids.numel(), pos.numel(), sampled.numel()):
-        raise KernelError(f"advance_decode: {n} rows of ids {ids.numel()}, pos {pos.numel()}, sampled {sampled.numel()}")
-    _sampling.call("zi_advance_decode", ptr(ids), ptr(pos), ptr(sampled), c_int(n), stream())
+    axes, per_axis = (pos.shape[0], pos.shape[1]) if pos.dim() == 2 else (1, pos.numel())
+    if pos.dim() == 2 and (pos.stride(1) != 1 or (axes > 1 and pos.stride(0) < per_axis)):
+        raise KernelError(f"advance_decode: positions {tuple(pos.shape)} with strides {pos.stride()}")
+    if n > min(ids.numel(), per_axis, sampled.numel()):
+        raise KernelError(f"advance_decode: {n} rows of ids {ids.numel()}, pos {per_axis}, sampled {sampled.numel()}")
+    _sampling.call("zi_advance_decode", ptr(ids), ptr(pos), ptr(sampled), c_int(n), c_int(axes),
+                   c_ll(pos.stride(0) if pos.dim() == 2 else 0), stream())
 
 
 def repetition_penalty(logits_row: torch.Tensor, tokens: torch.Tensor, penalty: float) -> None:

@@ -12,6 +12,8 @@ it sits in.  The kinds are:
   step: ``forward(x, ctx, cache, owns_cache) -> y``.
 * **FeedForward** — works on each token alone: ``forward(x, ctx) -> y``.
 * **Block** — the arrangement of the above around the residual stream.
+* **Embedding** and **Head** — the two ends of the model: token ids to the residual stream, and the normed
+  hidden states of the wanted rows to logits.
 
 Every part declares the tensors it loads (``tensor_specs``: local name → shape and init
 rule) and receives them in ``bind``.  New kinds are added with the ``register_*`` functions
@@ -52,6 +54,7 @@ class StepContext:
     seg_len_host: Sequence[int]
     seg_pos0_host: Sequence[int]
     slots_host: Sequence[int]
+    position_axes: Optional[torch.Tensor] = None   # int32 [position_width, n_tokens]; row 0 is ``positions``
     decode_only: bool = False
     max_kv_len: int = 0                       # longest context (after this step) among the segments
     extras: Dict[str, Any] = field(default_factory=dict)   # device tensors of special paths (decode kernels)
@@ -94,6 +97,28 @@ class Norm(Part):
 
         With ``row_idx`` only those rows are produced and the stream is left as it is.
         """
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    """Token ids to the float32 residual stream: ``forward(ids, out[N, hidden])``.  ``tied_weight()`` is what a head
+    with tied weights may use as its own (None: nothing to share)."""
+
+    def forward(self, ids: torch.Tensor, out: torch.Tensor) -> None:
+        raise NotImplementedError
+
+    def tied_weight(self) -> Optional[torch.Tensor]:
+        return None
+
+
+class Head(Part):
+    """Normed hidden states of the wanted rows to float32 logits: ``forward(x[rows, hidden], out[rows, vocab])``.
+    ``bind`` also receives the embedding's ``tied_weight()``."""
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], embedding: Optional[torch.Tensor] = None) -> None:
+        raise NotImplementedError
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor) -> None:
         raise NotImplementedError
 
 
@@ -143,7 +168,7 @@ class Block:
 
 # ---- registries -----------------------------------------------------------------------------
 _REGISTRIES: Dict[str, Dict[str, Callable[..., Any]]] = {
-    "norm": {}, "position": {}, "mixer": {}, "ffn": {}, "block": {},
+    "norm": {}, "position": {}, "mixer": {}, "ffn": {}, "block": {}, "embedding": {}, "head": {},
 }
 
 
@@ -172,6 +197,14 @@ def register_feed_forward(kind: str):
 
 def register_block(kind: str):
     return _register("block", kind)
+
+
+def register_embedding(kind: str):
+    return _register("embedding", kind)
+
+
+def register_head(kind: str):
+    return _register("head", kind)
 
 
 def unregister(family: str, kind: str) -> None:

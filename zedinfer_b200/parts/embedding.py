@@ -12,10 +12,11 @@ import torch
 
 from .. import ops
 from ..weights.loader import TensorSpec
-from .base import Part
+from .base import Embedding, Head, register_embedding, register_head
 
 
-class TokenEmbedding(Part):
+@register_embedding("token_embedding")
+class TokenEmbedding(Embedding):
     capture_safe = True
 
     def __init__(self, vocab_size: int, hidden_size: int, name: str = "embed_tokens.weight"):
@@ -31,8 +32,12 @@ class TokenEmbedding(Part):
     def forward(self, ids: torch.Tensor, out: torch.Tensor) -> None:
         ops.embedding(self.table, ids, out)
 
+    def tied_weight(self) -> Optional[torch.Tensor]:
+        return self.table
 
-class OutputHead(Part):
+
+@register_head("output_head")
+class OutputHead(Head):
     capture_safe = True
 
     def __init__(self, vocab_size: int, hidden_size: int, tied: bool, name: str = "lm_head.weight"):
