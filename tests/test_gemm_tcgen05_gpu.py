@@ -106,3 +106,33 @@ def test_persistent_tiles_silu_mul(m, n, k, width, pairs):
 def test_persistent_tiles_many_tiles_per_cta_and_strides(pairs):
     check_tiles(2048, 17920, 1536, torch.bfloat16, False, pairs=pairs)   # 7.6 tiles per CTA: both TMEM buffers turn over
     check_tiles(4096, 1536, 264, torch.bfloat16, True, ld_pad=8, pairs=pairs)
+
+
+@pytest.mark.parametrize("rows", [32, 40, 100])
+def test_gate_up_of_few_rows_on_a_large_weight_takes_the_fused_kernel(rows, monkeypatch):
+    """From 32 rows the gate/up product of a large stacked weight runs on the tcgen05 kernel with the activation in
+    its epilogue (below 128 rows only large weights do; the limit is lowered here so that a small weight shows the
+    same path): one 128-row tile that is mostly empty, and the result of the product and the separate kernel."""
+    from zedinfer_b200 import ops
+    monkeypatch.setattr(ops, "TC_FUSED_LARGE_ELEMENTS", 1 << 16)
+    calls = {"n": 0}
+    real = ops.gemm_tcgen05_tiles
+
+    def counted(*a, **k):
+        calls["n"] += 1
+        return real(*a, **k)
+
+    monkeypatch.setattr(ops, "gemm_tcgen05_tiles", counted)
+    inter, hidden = 1000, 384
+    x, w = rand(rows, hidden, seed=5), rand(2 * inter, hidden, seed=6, scale=0.08)
+    out = torch.full((rows, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.linear_silu_mul(x, w, None, out)
+    torch.cuda.synchronize()
+    assert calls["n"] == 1 and ops.tcgen05_status(DEV) == 0
+    g = (x.double().cpu() @ w[:inter].double().cpu().t()).to(torch.bfloat16).double()
+    u = (x.double().cpu() @ w[inter:].double().cpu().t()).to(torch.bfloat16).double()
+    ref = u * g / (1.0 + torch.exp(-g))
+    assert torch.allclose(out.double().cpu(), ref, atol=3e-2, rtol=2e-2)
+    small = torch.empty(16, inter, dtype=torch.bfloat16, device=DEV)
+    ops.linear_silu_mul(x[:16].contiguous(), w, None, small)            # 16 rows: the weight-streaming kernel
+    assert calls["n"] == 1

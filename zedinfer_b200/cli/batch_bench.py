@@ -4,7 +4,7 @@
 Beyond the reference's options, ``--prefill-len-max`` draws each prompt's length uniformly from
 [--prefill-len, --prefill-len-max] (continuous batching of unequal requests), and the report adds the share of
 prompt tokens, the time to the first token, the steps taken and how often a request was taken off the GPU when
-pages ran out."""
+pages ran out, and the context (prompt + generated tokens) that the requests reached."""
 from __future__ import annotations
 
 import argparse
@@ -52,7 +52,7 @@ def main(argv=None) -> int:
     lens = f"{args.prefill_len}" if hi_len == args.prefill_len else f"{args.prefill_len}..{hi_len}"
     print(f"Config: batch_size={args.batch_size}, prefill={lens}, decode={args.decode_len}, rounds={args.rounds}")
     total_ms, total_tokens, total_prompt, total_steps, total_pre = 0.0, 0, 0, 0, 0
-    ttft, failed = [], 0
+    ttft, failed, reached = [], 0, []
     for r in range(args.rounds):
         work = prompts()
         steps0, pre0 = engine.steps_run, engine.scheduler.num_preemptions
@@ -64,6 +64,7 @@ def main(argv=None) -> int:
         results = [f.result() for f in futs]
         tokens = sum(len(x.output_ids) for x in results)
         failed += sum(1 for x in results if x.error)
+        reached += [len(ids) + len(x.output_ids) for ids, x in zip(work, results)]
         ttft += [x.stats.queue_time_ms + x.stats.prefill_time_ms for x in results if not x.error]
         total_ms, total_tokens = total_ms + ms, total_tokens + tokens
         total_prompt += sum(len(ids) for ids in work)
@@ -85,6 +86,11 @@ def main(argv=None) -> int:
         print(f"First token    : {sum(ttft) / len(ttft):8.2f} ms mean | {ttft[len(ttft) // 2]:8.2f} ms median | "
               f"{ttft[-1]:8.2f} ms max  (from submission)")
     print(f"Steps          : {total_steps / n:8.0f} per batch | {avg_ms / max(1.0, total_steps / n):8.3f} ms per step")
+    reached.sort()
+    print(f"Context reached: {reached[0]:8d} min | {reached[len(reached) // 2]:8d} median | {reached[-1]:8d} max  "
+          "(prompt + generated tokens per request)")
+    st = engine.cache_stats()
+    print(f"Cache pool     : {st['pages_per_group'] * st['page_size']:8d} tokens ({st['pool_bytes'] / 2**30:.1f} GiB)")
     print(f"Preemptions    : {total_pre:8d} | failed requests: {failed}")
     print("===================================================")
     return 0
