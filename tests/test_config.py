@@ -210,3 +210,17 @@ def test_command_line_options_map_to_the_scheduler_config(tmp_path, monkeypatch)
     for h in list(log.handlers):
         h.close()
         log.removeHandler(h)
+
+
+def test_a_layer_names_its_parts_by_role():
+    """Mixer and feed-forward are optional, further parts come under role names of their own, and no role is named twice."""
+    from zedinfer_b200.config import LayerSpec, PartSpec
+    norm = PartSpec("rmsnorm", {"size": 8, "eps": 1e-5})
+    mix = PartSpec("attention", {})
+    layer = LayerSpec("some_block", mix, None, {"norm1": norm}, {}, extra={"mixer2": ("mixer", mix), "gate_norm": ("norm", norm)})
+    assert [(role, family) for role, family, _ in layer.part_specs()] == [
+        ("mixer", "mixer"), ("norm1", "norm"), ("mixer2", "mixer"), ("gate_norm", "norm")]
+    assert LayerSpec("b", None, None, {}, {}).part_specs() == ()
+    for role in ("mixer", "norm1"):
+        with pytest.raises(ValueError, match="repeats a role"):
+            LayerSpec("b", mix, None, {"norm1": norm}, {}, extra={role: ("mixer", mix)}).part_specs()

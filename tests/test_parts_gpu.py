@@ -230,6 +230,136 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
         unregister("mixer", "toy_decay")
 
 
+def test_toy_arrangement_with_two_mixers_and_no_feed_forward(tmp_path):
+    """A layer is whatever parts its spec names under role names: here one with an attention mixer and a stateful toy
+    mixer side by side and no feed-forward at all, put together by an arrangement that the test registers.  Each
+    mixer has a cache of its own in each call of the layer (pages for one, a state slot for the other), and the
+    run order names that layer twice."""
+    from zedinfer_b200.cache import StateNeed
+    from zedinfer_b200.config import (LayerCall, LayerSpec, ModelSpec, PartSpec, register_architecture,
+                                      unregister_architecture)
+    from zedinfer_b200.engine.core import EngineCore, StepEntry
+    from zedinfer_b200.parts import Block, Mixer, register_block, register_mixer, unregister
+    from zedinfer_b200.weights import TensorSpec, write_random_model
+
+    @register_mixer("toy_decay2")
+    class DecayMixer(Mixer):
+        def __init__(self, hidden_size, decay):
+            self.hidden_size, self.decay = hidden_size, decay
+
+        def cache_need(self):
+            return StateNeed((self.hidden_size,), torch.float32)
+
+        def tensor_specs(self):
+            return {"mix.weight": TensorSpec((self.hidden_size, self.hidden_size))}
+
+        def bind(self, tensors):
+            self.w = tensors["mix.weight"].float()
+
+        def forward(self, x, ctx, cache, owns_cache):
+            out = torch.empty_like(x)
+            for start, n, slot in zip(ctx.seg_start_host, ctx.seg_len_host, ctx.slots_host):
+                s = cache.tensor[slot]
+                for i in range(start, start + n):
+                    s.mul_(self.decay).add_(x[i].float())
+                    out[i] = (s @ self.w.t()).to(x.dtype)
+            return out
+
+    @register_block("toy_side_by_side")
+    class SideBySide(Block):
+        """h = h + attention(norm1(h)) + decay(norm1(h)); nothing else."""
+
+        def forward(self, stream, ctx, caches, owns_cache):
+            normed = ctx.empty(*stream.h.shape)
+            self.norms["norm1"].forward_residual(stream, normed)
+            a = self.mixer.forward(normed, ctx, caches["mixer"], owns_cache)
+            b = self.parts()["mixer2"].forward(normed, ctx, caches["mixer2"], owns_cache)
+            stream.delta = a + b
+
+    def build_spec(raw):
+        h = raw["hidden_size"]
+        norm = PartSpec("rmsnorm", {"size": h, "eps": raw["eps"]})
+        ffn = PartSpec("gated_mlp", {"hidden_size": h, "intermediate_size": raw["inter"]})
+        attn = PartSpec("attention", {"hidden_size": h, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16,
+                                      "position": PartSpec("rope", {"head_dim": 16, "theta": 10000.0})})
+        toy = PartSpec("toy_decay2", {"hidden_size": h, "decay": raw["decay"]})
+        both = LayerSpec("toy_side_by_side", attn, None, {"norm1": norm}, {"mixer": "attn.", "mixer2": "decay.", "norm1": "ln1."},
+                         extra={"mixer2": ("mixer", toy)})
+        usual = LayerSpec("pre_norm", attn, ffn, {"norm1": norm, "norm2": norm},
+                          {"mixer": "mixer.", "ffn": "mlp.", "norm1": "ln1.", "norm2": "ln2."})
+        return ModelSpec("Toy4ForCausalLM", raw["vocab_size"], h, (both, usual), (LayerCall(0), LayerCall(1), LayerCall(0)),
+                         norm, True, raw["max_position_embeddings"])
+
+    register_architecture("Toy4ForCausalLM", model_types=("toy4",), parse=lambda raw: raw, build_spec=build_spec)
+    try:
+        raw = {"architectures": ["Toy4ForCausalLM"], "hidden_size": 48, "inter": 100, "vocab_size": 300, "eps": 1e-5,
+               "decay": 0.7, "max_position_embeddings": 128}
+        folder = write_random_model(raw, 6, str(tmp_path / "toy4"), dtype="float32", init_scale=5.0)
+        core = EngineCore(folder, "float32", page_size=4, num_pages=32, max_requests=3)
+        # three calls with pages (one group of three), two of them with a state slot as well
+        assert len(core.cache.groups) == 1 and len(core.cache.groups[0].calls) == 3 and core.cache.slots.num_slots == 3
+        assert set(core.views) == {0, 1, 2, (0, "mixer2"), (2, "mixer2")}
+        w = P.read_safetensors(os.path.join(folder, "model.safetensors"))
+        assert "layers.0.decay.mix.weight" in w and "layers.0.attn.q_proj.weight" in w and "layers.0.ln2.weight" not in w
+
+        def attention(x, p, t):
+            q = P.linear(x, w[p + "q_proj.weight"], w[p + "q_proj.bias"]).view(t, 4, 16)
+            k = P.linear(x, w[p + "k_proj.weight"], w[p + "k_proj.bias"]).view(t, 2, 16)
+            v = P.linear(x, w[p + "v_proj.weight"], w[p + "v_proj.bias"]).view(t, 2, 16)
+            pos = torch.arange(t)
+            a = P.attention(P.rope(q, pos, 10000.0), P.rope(k, pos, 10000.0), v, 0.25)
+            return P.linear(a.reshape(t, 64), w[p + "o_proj.weight"], None)
+
+        def plain(ids):
+            t = len(ids)
+            hdn = P.embedding(ids, w["embed_tokens.weight"])
+            for layer in (0, 1, 0):
+                p = f"layers.{layer}."
+                x = P.rms_norm(hdn, w[p + "ln1.weight"], 1e-5)
+                if layer == 0:
+                    s, ys = torch.zeros(48), []
+                    for i in range(t):
+                        s = 0.7 * s + x[i]
+                        ys.append(s @ w[p + "decay.mix.weight"].t())
+                    hdn = hdn + (attention(x, p + "attn.", t) + torch.stack(ys))
+                else:
+                    hdn = hdn + attention(x, p + "mixer.", t)
+                    x = P.rms_norm(hdn, w[p + "ln2.weight"], 1e-5)
+                    hdn = hdn + P.linear(P.swiglu(P.linear(x, w[p + "mlp.gate_proj.weight"], None),
+                                                  P.linear(x, w[p + "mlp.up_proj.weight"], None)),
+                                         w[p + "mlp.down_proj.weight"], None)
+            return P.linear(P.rms_norm(hdn, w["norm.weight"], 1e-5), w["embed_tokens.weight"], None)
+
+        rng = random.Random(8)
+        reqs = {"a": [rng.randrange(300) for _ in range(19)], "b": [rng.randrange(300) for _ in range(11)]}
+        ref = {rid: plain(ids) for rid, ids in reqs.items()}
+        cuts = [[("a", 4), ("b", 3)], [("b", 1), ("a", 7)], [("a", 1), ("b", 7)], [("a", 7)]]
+        done = {"a": 0, "b": 0}
+        worst = 0.0
+        for cut in cuts:
+            entries = [StepEntry(rid, reqs[rid][done[rid]:done[rid] + n], list(range(n))) for rid, n in cut]
+            logits = core.step(entries).cpu()
+            row = 0
+            for rid, n in cut:
+                worst = max(worst, float((logits[row:row + n] - ref[rid][done[rid]:done[rid] + n]).abs().max()))
+                row += n
+                done[rid] += n
+        assert done == {"a": 19, "b": 11} and worst < 2e-4, worst
+        core.end("a"), core.end("b")
+        core.cache.check()
+        assert core.cache.slots.num_free_slots == 3 and core.cache.groups[0].pool.num_used == 0
+        # the usual arrangement says which of its parts a layer lacks
+        bad = LayerSpec("pre_norm", PartSpec("toy_decay2", {"hidden_size": 48, "decay": 0.5}), None,
+                        {"norm1": PartSpec("rmsnorm", {"size": 48, "eps": 1e-5})}, {})
+        from zedinfer_b200.engine.model import Model
+        with pytest.raises(ValueError, match="ffn.*norm2"):
+            Model(ModelSpec("Toy4ForCausalLM", 300, 48, (bad,), (LayerCall(0),), PartSpec("rmsnorm", {"size": 48, "eps": 1e-5}), True, 128))
+    finally:
+        unregister_architecture("Toy4ForCausalLM")
+        unregister("mixer", "toy_decay2")
+        unregister("block", "toy_side_by_side")
+
+
 # ---- a toy architecture with a routed feed-forward and another position rule ------------------------------
 def test_toy_routed_feed_forward_and_toy_position_rule(tmp_path):
     """A feed-forward that routes each token to one of three experts (float32 router logits, top-1) and a position

@@ -82,14 +82,15 @@ class RequestCache:
 
 class CacheManager:
     def __init__(self, needs: Sequence[Tuple[int, object]], page_size: int, *, max_requests: int = 64):
-        """``needs``: (schedule index, need) for every call that owns a cache."""
+        """``needs``: (cache key, need) for every cache: the schedule index of the call that owns it, or any other
+        hashable key (a layer with a second mixer uses (index, role))."""
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size = page_size
         self.groups: List[PagedGroup] = []
-        self._call_group: Dict[int, Tuple[int, int]] = {}
-        self._state_needs: Dict[int, StateNeed] = {}
-        self._state_tensors: Dict[int, torch.Tensor] = {}
+        self._call_group: Dict[object, Tuple[int, int]] = {}
+        self._state_needs: Dict[object, StateNeed] = {}
+        self._state_tensors: Dict[object, torch.Tensor] = {}
         for call, need in needs:
             if need is None:
                 continue
@@ -157,7 +158,7 @@ class CacheManager:
     def scratch_page(self) -> int:
         return self.num_pages
 
-    def view_for_call(self, call: int) -> CallCacheView:
+    def view_for_call(self, call) -> CallCacheView:
         if call in self._call_group:
             gi, j = self._call_group[call]
             g = self.groups[gi]

@@ -30,18 +30,39 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """A layer: the arrangement (``block``) of a mixer, a feed-forward and norms.
+    """A layer: the arrangement (``block``) of its parts, each under a role name.
 
-    ``prefixes`` maps the role of each part inside the block (``"mixer"``,
-    ``"ffn"``, ``"norm1"``, ``"norm2"``, ...) to the tensor-name prefix below the
-    layer's own prefix, e.g. ``{"mixer": "self_attn.", "norm1": "input_layernorm."}``.
+    The usual layer has one mixer (role ``"mixer"``), one feed-forward (``"ffn"``) and norms (``"norm1"``,
+    ``"norm2"``, ...).  A layer may also have none of one (``mixer=None`` or ``ffn=None``) or more parts than
+    these: ``extra`` maps further role names to ``(family, spec)``, the family being one of the part registries
+    (``"mixer"``, ``"ffn"``, ``"norm"``, ``"position"``), e.g. ``{"mixer2": ("mixer", PartSpec("toy_decay", ...))}``.
+    Which roles an arrangement expects is the arrangement's business; every mixer of a layer, whatever its role,
+    gets a cache of its own per call.
+
+    ``prefixes`` maps each role to the tensor-name prefix below the layer's own prefix, e.g.
+    ``{"mixer": "self_attn.", "norm1": "input_layernorm."}``; a role without an entry uses ``"<role>."``.
     """
 
     block: str
-    mixer: PartSpec
-    ffn: PartSpec
+    mixer: Optional[PartSpec]
+    ffn: Optional[PartSpec]
     norms: Mapping[str, PartSpec]
     prefixes: Mapping[str, str]
+    extra: Mapping[str, Tuple[str, PartSpec]] = field(default_factory=dict)
+
+    def part_specs(self) -> Tuple[Tuple[str, str, PartSpec], ...]:
+        """(role, family, spec) of every part of the layer, in a fixed order."""
+        out = []
+        if self.mixer is not None:
+            out.append(("mixer", "mixer", self.mixer))
+        if self.ffn is not None:
+            out.append(("ffn", "ffn", self.ffn))
+        out.extend((role, "norm", ns) for role, ns in self.norms.items())
+        for role, (family, ps) in self.extra.items():
+            if role in ("mixer", "ffn") or role in self.norms:
+                raise ValueError(f"extra part {role!r} repeats a role the layer already has")
+            out.append((role, family, ps))
+        return tuple(out)
 
 
 @dataclass(frozen=True)

@@ -21,10 +21,14 @@ class Model:
         self.blocks: List[Block] = []
         for layer in spec.layers:
             cls = block_class(layer.block)
-            mixer = build_part("mixer", layer.mixer)
-            ffn = build_part("ffn", layer.ffn)
-            norms = {role: build_part("norm", ns) for role, ns in layer.norms.items()}
-            self.blocks.append(cls(mixer, ffn, norms))
+            self.blocks.append(cls({role: build_part(family, ps) for role, family, ps in layer.part_specs()}))
+        # the caches of each call, by the role of the mixer they belong to: the key of the usual mixer's cache is
+        # the index of the call that owns it, the key of any other mixer's cache is (that index, role)
+        self._call_caches: List[Dict[str, object]] = []
+        for pos, call in enumerate(spec.schedule):
+            owner = pos if call.cache_of is None else call.cache_of
+            self._call_caches.append({role: (owner if role == "mixer" else (owner, role))
+                                      for role in self.blocks[call.layer].mixers()})
         self.embedding = build_part("embedding", spec.embedding or PartSpec("token_embedding", {
             "vocab_size": spec.vocab_size, "hidden_size": spec.hidden_size, "name": spec.embed_name}))
         self.final_norm = build_part("norm", spec.final_norm)
@@ -33,6 +37,8 @@ class Model:
             "name": spec.head_name}))
         self.dtype: Optional[torch.dtype] = None
         self.device: Optional[torch.device] = None
+        self._views_of: Optional[Mapping[object, CallCacheView]] = None
+        self._views_by_call: List[Dict[str, CallCacheView]] = []
 
     # ---- tensors ----------------------------------------------------------------------------
     def _part_prefixes(self):
@@ -81,25 +87,29 @@ class Model:
         return not self.capture_blockers()
 
     # ---- cache ------------------------------------------------------------------------------
-    def cache_needs(self) -> List[Tuple[int, object]]:
-        """(schedule index, need) for each call that owns a cache."""
+    def cache_needs(self) -> List[Tuple[object, object]]:
+        """(cache key, need) for every cache of every call that owns its caches.  The key of a layer's usual mixer is
+        the call's index in the schedule; a further mixer of the layer has (index, role)."""
         out = []
         for pos, call in enumerate(self.spec.schedule):
             if call.cache_of is None:
-                out.append((pos, self.blocks[call.layer].mixer.cache_need()))
+                for role, mixer in self.blocks[call.layer].mixers().items():
+                    out.append((self._call_caches[pos][role], mixer.cache_need()))
         return out
 
     # ---- one step ---------------------------------------------------------------------------
-    def forward(self, ctx: StepContext, cache_views: Mapping[int, CallCacheView],
+    def forward(self, ctx: StepContext, cache_views: Mapping[object, CallCacheView],
                 logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Run the step's tokens through every call; return float32 logits of ``logit_rows`` (or None)."""
         ctx.step_cache.clear()                 # what layers share (a step's rotation angles) belongs to one step
         h = torch.empty((ctx.n_tokens, self.spec.hidden_size), dtype=torch.float32, device=ctx.device)
         self.embedding.forward(ctx.token_ids, h)
         stream = ResidualStream(h)
+        if self._views_of is not cache_views:          # the same mapping step after step: resolve the keys once
+            self._views_by_call = [{role: cache_views[key] for role, key in keys.items()} for keys in self._call_caches]
+            self._views_of = cache_views
         for pos, call in enumerate(self.spec.schedule):
-            owner = pos if call.cache_of is None else call.cache_of
-            self.blocks[call.layer].forward(stream, ctx, cache_views[owner], owns_cache=call.cache_of is None)
+            self.blocks[call.layer].forward(stream, ctx, self._views_by_call[pos], owns_cache=call.cache_of is None)
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         rows = logit_rows.numel()

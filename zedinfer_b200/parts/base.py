@@ -151,18 +151,26 @@ class FeedForward(Part):
 
 
 class Block:
-    """Arrangement of a mixer, a feed-forward and norms around the residual stream."""
+    """Arrangement of a layer's parts around the residual stream.  ``parts`` maps role names to built parts: the
+    usual ``"mixer"``, ``"ffn"`` and norms, or whatever else the layer's spec names.  ``forward`` receives the
+    caches of the call by the role of the mixer they belong to (``caches["mixer"]`` for the usual one)."""
     capture_safe = False                  # see Part.capture_safe; an arrangement says so for its own code
 
-    def __init__(self, mixer: Mixer, ffn: FeedForward, norms: Mapping[str, Norm]):
-        self.mixer, self.ffn, self.norms = mixer, ffn, dict(norms)
+    def __init__(self, parts: Mapping[str, Part]):
+        self._parts: Dict[str, Part] = dict(parts)
+        self.mixer: Optional[Mixer] = self._parts.get("mixer")
+        self.ffn: Optional[FeedForward] = self._parts.get("ffn")
+        self.norms: Dict[str, Norm] = {role: part for role, part in self._parts.items() if isinstance(part, Norm)}
 
     def parts(self) -> Dict[str, Part]:
-        out: Dict[str, Part] = {"mixer": self.mixer, "ffn": self.ffn}
-        out.update(self.norms)
-        return out
+        return dict(self._parts)
 
-    def forward(self, stream: ResidualStream, ctx: StepContext, cache: CallCacheView, owns_cache: bool) -> None:
+    def mixers(self) -> Dict[str, Mixer]:
+        """The layer's mixers by role: each gets a cache of its own in every call of the layer."""
+        return {role: part for role, part in self._parts.items() if isinstance(part, Mixer)}
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, caches: Mapping[str, CallCacheView],
+                owns_cache: bool) -> None:
         raise NotImplementedError
 
 

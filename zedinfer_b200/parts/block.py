@@ -6,6 +6,8 @@ The adds are fused into the norm that follows them: a branch output stays "pendi
 stream until the next norm folds it into the float32 residual."""
 from __future__ import annotations
 
+from typing import Mapping
+
 from ..cache.manager import CallCacheView
 from .base import Block, ResidualStream, StepContext, register_block
 
@@ -14,11 +16,18 @@ from .base import Block, ResidualStream, StepContext, register_block
 class PreNormBlock(Block):
     capture_safe = True
 
-    def forward(self, stream: ResidualStream, ctx: StepContext, cache: CallCacheView, owns_cache: bool) -> None:
+    def __init__(self, parts):
+        super().__init__(parts)
+        missing = [role for role in ("mixer", "ffn", "norm1", "norm2") if role not in self.parts()]
+        if missing:
+            raise ValueError(f"the pre_norm arrangement needs the parts {missing} as well")
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, caches: Mapping[str, CallCacheView],
+                owns_cache: bool) -> None:
         n, hidden = stream.h.shape
         normed = ctx.empty(n, hidden)
         self.norms["norm1"].forward_residual(stream, normed)
-        stream.delta = self.mixer.forward(normed, ctx, cache, owns_cache)
+        stream.delta = self.mixer.forward(normed, ctx, caches["mixer"], owns_cache)
         normed2 = ctx.empty(n, hidden)
         self.norms["norm2"].forward_residual(stream, normed2)
         stream.delta = self.ffn.forward(normed2, ctx)
