@@ -189,3 +189,64 @@ def test_state_can_be_reset_and_copied_between_requests():
     c = m.open("c")                      # takes a's slot: zeroed when it opens
     assert c.slot == 0 or float(va[c.slot].abs().sum()) == 0.0
     m.check()
+
+
+def test_a_group_with_a_window_gets_a_smaller_pool_when_steps_are_bounded():
+    """With a bound on the tokens a step adds to a request, a group of layers with a window holds at most window + bound
+    tokens of a request, so max_requests requests can never fill more than that many pages: its pool is cut to that,
+    its scratch page is its own, and a byte budget buys the other groups more pages."""
+    needs = [(0, PagedKVNeed(2, 16, None)), (1, PagedKVNeed(2, 16, 32)), (2, PagedKVNeed(2, 16, None))]
+    m = CacheManager(needs, 8, max_requests=3, max_step_tokens=16)
+    per_request = (32 + 16 + 8 - 2) // 8 + 1                       # 7 pages: 47 tokens starting anywhere in a page
+    m.set_num_pages(100)
+    assert [g.num_pages for g in m.groups] == [100, 3 * per_request] and m.scratch_pages == [100, 21]
+    assert m.free_pages() == [100, 21]
+    m.set_num_pages(10)                                            # never more than the others
+    assert [g.num_pages for g in m.groups] == [10, 10]
+    unbounded = CacheManager(needs, 8, max_requests=3)
+    unbounded.set_num_pages(100)
+    assert [g.num_pages for g in unbounded.groups] == [100, 100]
+    # the budget: the largest count whose pools (one scratch page each) fit
+    for budget in (10_000, 123_456, 5_000_000):
+        n = m.pages_for_budget(budget, torch.bfloat16)
+        assert m.pool_bytes(n, torch.bfloat16) <= budget < m.pool_bytes(n + 1, torch.bfloat16)
+        assert n >= unbounded.pages_for_budget(budget, torch.bfloat16)
+    assert m.pages_for_budget(5_000_000, torch.bfloat16) > unbounded.pages_for_budget(5_000_000, torch.bfloat16)
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_the_smaller_pool_of_a_windowed_group_never_runs_out_first(seed):
+    """Random requests in random portions of at most max_step_tokens, max_requests at a time: whenever a step is
+    refused for lack of pages, it is the group that keeps all keys that ran out."""
+    rng = random.Random(seed)
+    page, window, bound, live_max = 4, 10, 7, 3
+    m = CacheManager([(0, PagedKVNeed(1, 8, None)), (1, PagedKVNeed(1, 8, window))], page, max_requests=live_max,
+                     max_step_tokens=bound)
+    m.set_num_pages(60)
+    assert m.groups[1].num_pages < 60
+    live, serial = {}, 0
+    for _ in range(600):
+        if len(live) < live_max and rng.random() < 0.3:
+            serial += 1
+            live[serial] = (m.open(serial), rng.randrange(1, 120))
+        if not live:
+            continue
+        rid = rng.choice(list(live))
+        rc, total = live[rid]
+        n = min(rng.randrange(1, bound + 1), total - rc.length)
+        needed = m.pages_needed(rc, rc.length + n)
+        if m.can_ensure(rc, rc.length + n):
+            m.ensure(rc, rc.length + n)
+            m.commit(rc, rc.length + n)
+        else:
+            assert needed[0] > m.groups[0].pool.num_free and needed[1] <= m.groups[1].pool.num_free
+            m.close(rc)
+            del live[rid]
+            continue
+        if rc.length == total:
+            m.close(rc)
+            del live[rid]
+        m.check()
+    for rc, _ in list(live.values()):
+        m.close(rc)
+    assert m.free_pages() == [60, m.groups[1].num_pages]

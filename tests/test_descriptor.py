@@ -9,7 +9,7 @@ import pytest
 from zedinfer_b200.engine.descriptor import pack_step, step_padding, step_signature
 
 TILE = 128
-SCRATCH = 999
+SCRATCH = [999, 777]          # the scratch page of each group: pools of different sizes
 
 
 def make(lens, cached=None, wants=None, n_groups=2, width=48, pad=None, vocab=5000, seed=0):
@@ -59,7 +59,7 @@ def check(host, lay, tokens, cached, wants, tables, pad):
     for r in pad_rows:
         assert pos[r] == 0 and host[lay.off_slots + seg[r]] == -1
         for g in range(lay.n_groups):
-            assert host[lay.off_tab + (g * lay.n_seg + seg[r]) * lay.width] == SCRATCH
+            assert host[lay.off_tab + (g * lay.n_seg + seg[r]) * lay.width] == SCRATCH[g]
     assert sorted(seg[r] for r in pad_rows) == sorted(set(range(lay.n_seg)) - set(first_seg))
     # wanted rows: the real ones in the order of the entries, the padding's behind them
     want = list(host[lay.off_want: lay.off_want + lay.n_want])
@@ -131,6 +131,6 @@ def test_pages_given_back_behind_a_window_are_shown_as_the_scratch_page():
     tables = [[[-1, -1, 40, 41], [3, 4, 5, 6]], [[-1, 8], [7, 8]]]      # group 0 has a window, group 1 has none
     host, lay = pack_step(["a", "b"], tokens, [[2], [0]], [50, 20], [-1, -1], tables, 2, 6, 100, SCRATCH, TILE, 0)
     tab = host[lay.off_tab:].reshape(2, lay.n_seg, lay.width)
-    assert tab[0, 0].tolist() == [SCRATCH, SCRATCH, 40, 41, 0, 0] and tab[1, 0].tolist() == [3, 4, 5, 6, 0, 0]
-    assert tab[0, 1].tolist() == [SCRATCH, 8, 0, 0, 0, 0] and tab[1, 1].tolist() == [7, 8, 0, 0, 0, 0]
+    assert tab[0, 0].tolist() == [999, 999, 40, 41, 0, 0] and tab[1, 0].tolist() == [3, 4, 5, 6, 0, 0]
+    assert tab[0, 1].tolist() == [999, 8, 0, 0, 0, 0] and tab[1, 1].tolist() == [7, 8, 0, 0, 0, 0]
     assert (host[lay.off_tab:] >= 0).all()

@@ -61,6 +61,30 @@ def test_cuts_match_plain(models, name, dtype, family):
     assert core.cache.num_live == 0 and all(g.pool.num_used == 0 for g in core.cache.groups)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["C", "F"])
+@pytest.mark.parametrize("family", ["chunks", "mixed"])
+def test_a_windowed_group_with_a_pool_of_its_own_size(models, name, dtype, family):
+    """The engine is told the most tokens a step brings of one request; the layers with a window then share a pool
+    that is only as large as four requests can fill, with a scratch page of its own number, and the logits are
+    those of the plain implementation."""
+    from zedinfer_b200.engine.core import EngineCore
+    cfg, _ = tiny.CONFIGS[name]
+    requests = make_requests(cfg, LENGTHS[name] + ([64, 31, 77] if family == "mixed" else []), seed=13)
+    steps = {"chunks": traces.chunks, "mixed": traces.mixed}[family](requests)
+    bound = max(len(e["tokens"]) for st in steps for e in st["entries"])
+    window = cfg["sliding_window"]
+    per_request = (window + bound + 14) // 16 + 1
+    core = EngineCore(models[name], dtype, page_size=16, num_pages=8 * per_request, max_requests=4, max_step_tokens=bound)
+    sizes = {g.window: g.num_pages for g in core.cache.groups}
+    assert sizes == {None: 8 * per_request, window: 4 * per_request}
+    assert core.cache.scratch_pages == [g.num_pages for g in core.cache.groups]
+    got = run_trace(core, steps)
+    bad = first_bad(got, expected_logits(models[name], requests, dtype), requests, TOL[dtype])
+    assert bad is None, f"first wrong position {bad}"
+    assert core.cache.num_live == 0 and all(g.pool.num_used == 0 for g in core.cache.groups)
+
+
 @pytest.mark.parametrize("graphs", [False, True])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name,max_live", [("D", 12), ("D", 40), ("E", 12), ("E", 40), ("F", 12)])

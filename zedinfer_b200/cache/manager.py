@@ -57,6 +57,7 @@ class PagedGroup:
     calls: List[int] = field(default_factory=list)
     pool: Optional[PagePool] = None
     tensor: Optional[torch.Tensor] = None
+    num_pages: int = 0                  # pages of this group's pool; page ``num_pages`` of the tensor is the scratch page
 
     def page_elems(self, page_size: int) -> int:
         return len(self.calls) * 2 * self.n_kv_heads * page_size * self.head_dim
@@ -81,12 +82,17 @@ class RequestCache:
 
 
 class CacheManager:
-    def __init__(self, needs: Sequence[Tuple[int, object]], page_size: int, *, max_requests: int = 64):
+    def __init__(self, needs: Sequence[Tuple[int, object]], page_size: int, *, max_requests: int = 64,
+                 max_step_tokens: Optional[int] = None):
         """``needs``: (cache key, need) for every cache: the schedule index of the call that owns it, or any other
         hashable key (a layer with a second mixer uses (index, role))."""
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size = page_size
+        # The most tokens one step adds to one request, if the caller binds itself to that (a scheduler's token
+        # budget).  A group with a window then never holds more than ``window + max_step_tokens`` tokens of a request
+        # (what a step adds is only given back when the step commits), so its pool can be smaller than the others'.
+        self.max_step_tokens = max_step_tokens
         self.groups: List[PagedGroup] = []
         self._call_group: Dict[object, Tuple[int, int]] = {}
         self._state_needs: Dict[object, StateNeed] = {}
@@ -127,11 +133,35 @@ class CacheManager:
             total += n * torch.empty((), dtype=need.dtype).element_size() * self.max_requests
         return total
 
+    def group_pages(self, g: PagedGroup, num_pages: int) -> int:
+        """Pages of group ``g`` when the groups that keep all keys get ``num_pages``: as many, or, for a group with a
+        window under a bound on a step's tokens, what ``max_requests`` requests can hold at most."""
+        if g.window is None or self.max_step_tokens is None:
+            return num_pages
+        # window - 1 + step tokens, starting anywhere in a page
+        per_request = (g.window + self.max_step_tokens + self.page_size - 2) // self.page_size + 1
+        return max(1, min(num_pages, per_request * self.max_requests))
+
+    def pool_bytes(self, num_pages: int, dtype: torch.dtype) -> int:
+        item = torch.empty((), dtype=dtype).element_size()
+        return sum(g.page_elems(self.page_size) * (self.group_pages(g, num_pages) + 1) for g in self.groups) * item
+
     def pages_for_budget(self, budget_bytes: int, dtype: torch.dtype) -> int:
-        per = self.bytes_per_page_all_groups(dtype)
-        if per == 0:
+        """The largest page count of the groups without a window (each group has one scratch page more) whose pools
+        and state fit in ``budget_bytes``."""
+        if not self.groups:
             return 1
-        return max(0, (budget_bytes - self.state_bytes()) // per - 1)     # one scratch page per group
+        budget = budget_bytes - self.state_bytes()
+        lo, hi = 0, 1
+        while self.pool_bytes(hi, dtype) <= budget and hi < (1 << 40):
+            lo, hi = hi, hi * 2
+        while hi - lo > 1:
+            mid = (lo + hi) // 2
+            if self.pool_bytes(mid, dtype) <= budget:
+                lo = mid
+            else:
+                hi = mid
+        return lo
 
     def set_num_pages(self, num_pages: int) -> None:
         """Host bookkeeping only (tests of the manager and the scheduler need no device)."""
@@ -140,7 +170,8 @@ class CacheManager:
         if self._requests:
             raise RuntimeError("cannot resize the cache while requests are live")
         for g in self.groups:
-            g.pool = PagePool(num_pages)
+            g.num_pages = self.group_pages(g, num_pages)
+            g.pool = PagePool(g.num_pages)
         self.num_pages = num_pages
 
     def allocate_device(self, num_pages: int, dtype: torch.dtype, device) -> None:
@@ -148,15 +179,17 @@ class CacheManager:
         self.device, self.dtype = torch.device(device), dtype
         for g in self.groups:
             # zeroed: attention multiplies slots that hold nothing yet by probability 0, which must not meet NaN bits
-            g.tensor = torch.zeros((num_pages + 1, len(g.calls), 2, g.n_kv_heads, self.page_size, g.head_dim),
+            g.tensor = torch.zeros((g.num_pages + 1, len(g.calls), 2, g.n_kv_heads, self.page_size, g.head_dim),
                                    dtype=dtype, device=device)
         for call, need in self._state_needs.items():
             self._state_tensors[call] = torch.zeros((self.max_requests,) + tuple(need.shape), dtype=need.dtype,
                                                     device=device)
 
     @property
-    def scratch_page(self) -> int:
-        return self.num_pages
+    def scratch_pages(self) -> List[int]:
+        """Per group, the page behind the pool's last: padding rows write there, and block-table entries whose page
+        a window has given back point there."""
+        return [g.num_pages for g in self.groups]
 
     def view_for_call(self, call) -> CallCacheView:
         if call in self._call_group:

@@ -90,7 +90,7 @@ def main(argv=None) -> int:
     print(f"Context reached: {reached[0]:8d} min | {reached[len(reached) // 2]:8d} median | {reached[-1]:8d} max  "
           "(prompt + generated tokens per request)")
     st = engine.cache_stats()
-    print(f"Cache pool     : {st['pages_per_group'] * st['page_size']:8d} tokens ({st['pool_bytes'] / 2**30:.1f} GiB)")
+    print(f"Cache pool     : {st['pool_tokens']:8d} tokens ({st['pool_bytes'] / 2**30:.1f} GiB)")
     print(f"Preemptions    : {total_pre:8d} | failed requests: {failed}")
     print("===================================================")
     return 0

@@ -87,8 +87,8 @@ def create_engine(args):
     engine = InferenceEngine.create(args.model_path, scheduler_config_from(args), dtype=args.dtype,
                                     random_seed=args.random_weights)
     st = engine.cache_stats()
-    log.info(f"[engine] cache: {st['pages_per_group']} pages of {st['page_size']} tokens "
-             f"({st['pages_per_group'] * st['page_size']} tokens, {st['pool_bytes'] / 2**30:.2f} GiB)")
+    log.info(f"[engine] cache: pages of {st['page_size']} tokens, per group of layers {st['pages_per_group']} "
+             f"({st['pool_tokens']} tokens, {st['pool_bytes'] / 2**30:.2f} GiB)")
     d = engine.default_generation
     log.info("[engine] default sampling: " + ("greedy" if d.use_argmax else
              f"temperature={d.temperature} top_k={d.top_k} top_p={d.top_p} repetition_penalty={d.repetition_penalty}"))

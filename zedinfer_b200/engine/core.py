@@ -108,7 +108,7 @@ def build_step_context(entries: Sequence[StepEntry], rcs: Sequence[RequestCache]
     n_groups = len(cache.groups)
     host, lay = pack_step([e.request_id for e in entries], [e.tokens for e in entries], [e.want for e in entries],
                           [rc.length for rc in rcs], [rc.slot for rc in rcs], [rc.tables for rc in rcs], n_groups,
-                          table_width, vocab, cache.scratch_page if cache.groups else 0, ops.PREFILL_TILE_ROWS, pad_segments,
+                          table_width, vocab, cache.scratch_pages, ops.PREFILL_TILE_ROWS, pad_segments,
                           pos_width)
     n_seg, n_tok, width, total = lay.n_seg, lay.n_tok, lay.width, lay.total
     off_ids, off_pos, off_seg, off_want = lay.off_ids, lay.off_pos, lay.off_seg, lay.off_want
@@ -153,9 +153,12 @@ class EngineCore:
                  num_pages: Optional[int] = None, max_tokens: Optional[int] = None,
                  gpu_memory_utilization: float = 0.9, max_requests: int = 64, max_seq_len: Optional[int] = None,
                  device="cuda:0", cuda_graphs: bool = False, config: Optional[dict] = None,
-                 random_seed: Optional[int] = None):
-        """``num_pages``: pages per cache group; ``max_tokens``: size the pool for that many cached tokens
-        instead; neither: whatever ``gpu_memory_utilization`` of the device leaves after the weights.
+                 random_seed: Optional[int] = None, max_step_tokens: Optional[int] = None):
+        """``num_pages``: pages of each cache group that keeps all keys; ``max_tokens``: size the pool for that many
+        cached tokens instead; neither: whatever ``gpu_memory_utilization`` of the device leaves after the weights.
+        ``max_step_tokens``: the caller's promise that no step brings more tokens of one request than this (a
+        scheduler's token budget); groups of layers with a window then get pools only as large as ``max_requests``
+        requests can fill, and the memory goes to the other groups.
 
         ``model_dir=None`` with ``config`` (a config.json dict) and ``random_seed`` builds the model with
         random weights drawn on the device, without a folder (benchmarks of large shapes); the values are those
@@ -181,7 +184,8 @@ class EngineCore:
         self.page_size = int(page_size)
         self.max_seq_len = min(int(max_seq_len or self.spec.max_position_embeddings),
                                self.spec.max_position_embeddings)
-        self.cache = CacheManager(self.model.cache_needs(), self.page_size, max_requests=max_requests)
+        self.cache = CacheManager(self.model.cache_needs(), self.page_size, max_requests=max_requests,
+                                  max_step_tokens=max_step_tokens)
         if num_pages is None and max_tokens is not None:
             num_pages = (int(max_tokens) + self.page_size - 1) // self.page_size
         if num_pages is None:

@@ -121,7 +121,7 @@ class DecodeGraph:
 
     def _pad_rows(self, first: int) -> None:
         b, width, ng = self.bucket, self.core.table_width, len(self.core.cache.groups)
-        scratch = self.core.cache.scratch_page if ng else 0
+        scratch = self.core.cache.scratch_pages
         h = self.host
         h[self.off_ids + first: self.off_ids + b] = 0
         for axis in range(self.pos_width):
@@ -130,17 +130,17 @@ class DecodeGraph:
         for g in range(ng):
             base = self.off_tab + g * b * width
             rows = h[base: base + b * width].reshape(b, width)
-            rows[first:, :] = scratch          # wherever a padding row's position points (a looping graph moves it on)
+            rows[first:, :] = scratch[g]       # wherever a padding row's position points (a looping graph moves it on)
 
     def _write_tables(self, i: int, rc) -> None:
         """Row ``i`` of every group's block table := the request's pages; entries that a window has passed and given
         back (-1) point at the scratch page, whose keys the kernels mask like any other outside the window."""
         b, width, h = self.bucket, self.core.table_width, self.host
-        scratch = self.core.cache.scratch_page
+        scratch = self.core.cache.scratch_pages
         for g in range(len(self.core.cache.groups)):
             tab = np.asarray(rc.tables[g], dtype=np.int32)
             base = self.off_tab + (g * b + i) * width
-            h[base: base + tab.size] = np.where(tab < 0, scratch, tab)
+            h[base: base + tab.size] = np.where(tab < 0, scratch[g], tab)
             h[base + tab.size: base + width] = 0
 
     def fill(self, tokens: Sequence[int], rcs: Sequence, reserve_ahead: int = 0) -> None:

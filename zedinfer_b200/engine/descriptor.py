@@ -73,7 +73,7 @@ class StepLayout:
 
 def pack_step(names: Sequence, tokens: Sequence[Sequence[int]], wants: Sequence[Sequence[int]], lengths: Sequence[int],
               slots: Sequence[int], tables: Sequence[Sequence[Sequence[int]]], n_groups: int, width: int, vocab: int,
-              scratch_page: int, tile_rows: int, pad_segments: int = 0, pos_width: int = 1
+              scratch_pages: Sequence[int], tile_rows: int, pad_segments: int = 0, pos_width: int = 1
               ) -> Tuple[np.ndarray, StepLayout]:
     """``names[i]``: the request of entry i (for messages); ``tokens[i]`` its new tokens; ``wants[i]`` the places
     among them whose logits are wanted; ``lengths[i]`` the tokens it has in the cache; ``slots[i]`` its state slot;
@@ -113,7 +113,7 @@ def pack_step(names: Sequence, tokens: Sequence[Sequence[int]], wants: Sequence[
             host[off_seg + t] = s
             host[off_slots + s] = -1
             for g in range(n_groups):
-                host[off_tab + (g * n_seg + s) * width] = scratch_page
+                host[off_tab + (g * n_seg + s) * width] = scratch_pages[g]
             if not lead:
                 host[off_tiles + 3 * tile: off_tiles + 3 * tile + 3] = (t, 1, s)
                 tile += 1
@@ -142,7 +142,7 @@ def pack_step(names: Sequence, tokens: Sequence[Sequence[int]], wants: Sequence[
             base = off_tab + (g * n_seg + s) * width
             # a page that a window has passed and given back (-1) is shown to the kernels as the scratch page:
             # its keys are masked anyway, and no kernel ever forms an address or a TMA coordinate from -1
-            host[base: base + tab.size] = np.where(tab < 0, scratch_page, tab)
+            host[base: base + tab.size] = np.where(tab < 0, scratch_pages[g], tab)
         if not (lead and i < lead_real):
             for q0 in range(0, k, tile_rows):
                 host[off_tiles + 3 * tile: off_tiles + 3 * tile + 3] = (t + q0, min(tile_rows, k - q0), s)

@@ -62,7 +62,7 @@ class InferenceEngine:
         cfg.validate()
         sizes = dict(page_size=cfg.kv_block_size, num_pages=cfg.num_kv_pages,
                      gpu_memory_utilization=cfg.gpu_memory_utilization, max_requests=cfg.max_batch_requests,
-                     max_seq_len=cfg.max_seq_len, device=device)
+                     max_seq_len=cfg.max_seq_len, device=device, max_step_tokens=cfg.max_batch_tokens)
         if random_seed is None:
             core = EngineCore(model_path, dtype, **sizes)
         else:
@@ -247,5 +247,5 @@ class InferenceEngine:
     def cache_stats(self) -> dict:
         c = self.core.cache
         pool = sum(g.tensor.numel() * g.tensor.element_size() for g in c.groups if g.tensor is not None)
-        return {"page_size": c.page_size, "pages_per_group": c.num_pages, "pool_bytes": pool, "free_pages": c.free_pages(),
+        return {"page_size": c.page_size, "pages_per_group": [g.num_pages for g in c.groups], "pool_tokens": c.num_pages * c.page_size, "pool_bytes": pool, "free_pages": c.free_pages(),
                 "live_requests": c.num_live, "groups": len(c.groups), "preemptions": self.scheduler.num_preemptions}
