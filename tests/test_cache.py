@@ -250,3 +250,30 @@ def test_the_smaller_pool_of_a_windowed_group_never_runs_out_first(seed):
     for rc, _ in list(live.values()):
         m.close(rc)
     assert m.free_pages() == [60, m.groups[1].num_pages]
+
+
+def test_a_windowed_group_under_a_step_bound_takes_pages_only_as_far_as_the_next_step_reaches():
+    """A whole prompt reserved at admission takes all its pages in the groups that keep all keys, and in a group with
+    a window only those that the next step can write; the rest come step by step as the window gives pages back."""
+    m = CacheManager([(0, PagedKVNeed(1, 8, None)), (1, PagedKVNeed(1, 8, 12))], 4, max_requests=2, max_step_tokens=8)
+    m.set_num_pages(50)
+    assert [g.num_pages for g in m.groups] == [50, 2 * ((12 + 8 + 2) // 4 + 1)]       # 12 pages for the window's group
+    rc = m.open("long")
+    assert m.pages_needed(rc, 100) == [25, 2] and m.can_ensure(rc, 100)
+    m.ensure(rc, 100)                                   # far more tokens than the windowed pool could ever hold
+    assert [len(t) for t in rc.tables] == [25, 2]
+    done = 0
+    while done < 100:                                   # the prompt in steps of 8, each asking for its own tokens
+        n = min(8, 100 - done)
+        m.ensure(rc, done + n)
+        assert all(len(t) * 4 >= done + n for t in rc.tables)
+        m.commit(rc, done + n)
+        done += n
+        assert sum(1 for p in rc.tables[1] if p >= 0) <= (12 + 8 + 2) // 4 + 1
+        m.check()
+    other = m.open("second")
+    m.ensure(other, 8)
+    with pytest.raises(RuntimeError, match="2 requests are live"):
+        m.open("third")
+    m.close(rc), m.close(other)
+    assert m.free_pages() == [50, 12]

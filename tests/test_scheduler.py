@@ -283,3 +283,36 @@ def test_random_workloads_with_failures_and_cancellations_lose_no_page():
                 assert len(r.output_ids) == m
         cache.check()
         assert cache.num_live == 0
+
+
+def test_a_prompt_longer_than_the_windowed_pool_is_admitted_and_runs_through():
+    """Layers with a window have a pool of their own size (what max_batch_requests requests can hold under the step's
+    token budget).  A prompt with more pages than that pool is admitted all the same: the reservation takes the
+    window's group only as far as the next step reaches, and each step takes its own pages as the step function does."""
+    page, window, budget = 4, 12, 8
+    cache = CacheManager([(0, PagedKVNeed(1, 16, None)), (1, PagedKVNeed(1, 16, window))], page, max_requests=2,
+                         max_step_tokens=budget)
+    cache.set_num_pages(80)
+    assert cache.groups[1].num_pages == 2 * ((window + budget + 2) // page + 1) == 12
+    s = Scheduler(SchedulerConfig(kv_block_size=page, max_batch_tokens=budget, max_prefill_tokens=budget,
+                                  max_batch_requests=2), cache, 256, ())
+    a, b = req(100, max_new=6), req(30, max_new=3)          # 25 and 8 pages where all keys are kept
+    s.submit(a), s.submit(b)
+    held_most = 0
+    for _ in range(200):
+        batch = s.schedule()
+        if batch.empty():
+            break
+        for r in batch.decode_requests:                     # what EngineCore.prepare and step do
+            cache.ensure(r.cache, r.cache.length + 1)
+            cache.commit(r.cache, r.cache.length + 1)
+        for r, size in zip(batch.prefill_requests, batch.prefill_chunk_sizes):
+            assert size <= budget
+            cache.ensure(r.cache, r.cache.length + size)
+            cache.commit(r.cache, r.cache.length + size)
+        s.process_results(batch, [7] * len(batch.rows_wanted()))
+        cache.check()
+        held_most = max(held_most, cache.groups[1].pool.num_used)
+    assert a.phase == b.phase == RequestPhase.COMPLETE and a.finish_reason == b.finish_reason == "length"
+    assert len(a.output_ids) == 6 and len(b.output_ids) == 3 and s.num_preemptions == 0
+    assert 0 < held_most <= 12 and cache.free_pages() == [80, 12]

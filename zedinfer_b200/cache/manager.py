@@ -218,6 +218,9 @@ class CacheManager:
     def open(self, request_id) -> RequestCache:
         if request_id in self._requests:
             raise ValueError(f"request {request_id!r} is already live")
+        if self.max_step_tokens is not None and len(self._requests) >= self.max_requests:
+            raise RuntimeError(f"{self.max_requests} requests are live already: the pools of the groups with a window "
+                               "are sized for that many")
         slot = -1
         if self.slots.num_slots:
             slot = self.slots.acquire_slot()
@@ -256,10 +259,17 @@ class CacheManager:
         return first_token // self.page_size
 
     def pages_needed(self, rc: Optional[RequestCache], new_len: int) -> List[int]:
-        """Pages per group that ``ensure(rc, new_len)`` would take (``rc=None``: a fresh request)."""
-        want = (new_len + self.page_size - 1) // self.page_size
+        """Pages per group that ``ensure(rc, new_len)`` would take (``rc=None``: a fresh request).  A group with a
+        window under a bound on a step's tokens takes pages only as far as the next step can reach: what lies
+        further ahead (a whole prompt reserved at admission) it will take step by step, as the window gives the
+        pages behind it back, and its pool is sized so that this cannot fail."""
+        length = rc.length if rc is not None else 0
         out = []
         for gi, g in enumerate(self.groups):
+            reach = new_len
+            if g.window is not None and self.max_step_tokens is not None:
+                reach = min(new_len, length + self.max_step_tokens)
+            want = (reach + self.page_size - 1) // self.page_size
             have = len(rc.tables[gi]) if rc is not None else 0
             out.append(max(0, want - have))
         return out
