@@ -392,6 +392,35 @@ def test_prefill_attention_tensor_cores(nh, nkv, hd, ps, window, kernel):
         i += cnt
 
 
+@pytest.mark.parametrize("hd,window", [(128, None), (64, None), (128, 200)])
+def test_prefill_attention_tcgen05_with_scores_far_apart(hd, window):
+    """Scores of one row spread over hundreds of units (queries scaled up), so that most exponentials lie far
+    below the smallest float32: the part of them that the kernel computes by arithmetic instead of the
+    special-function unit holds its argument at -125 and must come out as nothing, not as a wrapped exponent.  A row
+    whose scores are all equal and a row with two equal maxima far above the rest are among them."""
+    from zedinfer_b200 import ops
+    t, nh, nkv, ps, L = torch.bfloat16, 4, 2, 16, 700
+    pool, view, tables, ks, vs, page_stride, kv_stride = build_cache(1, [L], nkv, hd, ps, t, seed=9)
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(L, nh, hd, generator=g) * 25.0                # score differences of several hundred
+    q[650] = 0.0                                                  # every score equal
+    q[651, :, :] = (ks[0][10, 0] + ks[0][400, 0])[None, :] * 20.0
+    qd = q.to(t).to(dev())
+    tiles = torch.tensor([(q0, min(128, L - q0), 0) for q0 in range(0, L, 128)], dtype=torch.int32, device=dev())
+    pos = torch.arange(L, dtype=torch.int32, device=dev())
+    seg_tables = tables if not window else release_behind_window(tables, [0], window, ps, pool.shape[0] - 1)
+    out = torch.full((L, nh * hd), float("nan"), dtype=t, device=dev())
+    scale = 1.0 / math.sqrt(hd)
+    ops.prefill_attention_tcgen05(qd, view, out, seg_tables, tiles, pos, nh, nkv, hd, ps, page_stride, kv_stride, window, scale)
+    torch.cuda.synchronize()
+    assert ops.tcgen05_status(dev()) == 0
+    got = out.float().cpu().view(L, nh, hd)
+    assert torch.isfinite(got).all()
+    ref = plain_attention_rows(qd.float().cpu().view(L, nh, hd), ks[0], vs[0], list(range(L)), scale, window)
+    err = (got - ref).abs().amax(dim=(1, 2))
+    assert float(err.max()) < 3e-2, (int(err.argmax()), float(err.max()))
+
+
 @pytest.mark.parametrize("m,nh,nkv,hd,hidden,ps,with_bias", [(8, 12, 2, 128, 1536, 16, True), (1, 3, 1, 32, 96, 8, True),
                                                              (16, 4, 4, 64, 160, 4, False), (11, 6, 3, 48, 224, 16, True)])
 def test_product_with_rotation_and_append_equals_the_separate_kernels(m, nh, nkv, hd, hidden, ps, with_bias):
