@@ -52,6 +52,33 @@ def test_greedy_generation_float32_equals_plain(models, name, graphs):
     assert engine.cache_stats()["free_pages"] == [40] * engine.cache_stats()["groups"]
 
 
+@pytest.mark.parametrize("graphs", [False, True])
+def test_generation_with_a_windowed_pool_smaller_than_the_prompts(models, graphs):
+    """Configuration C has a window of 24 on its upper layers.  With a token budget of 8 a step, those layers' pool is
+    what three requests can hold (window + budget each), fewer pages than the three prompts have together; the prompts go
+    through in portions, pages come back behind the window, and the tokens are those of the plain implementation."""
+    from zedinfer_b200 import GenerationConfig, SchedulerConfig
+    from zedinfer_b200.engine import InferenceEngine
+    cfg, _ = tiny.CONFIGS["C"]
+    rng = random.Random(4)
+    prompts = [[rng.randrange(cfg["vocab_size"]) for _ in range(n)] for n in (90, 61, 33)]
+    engine = InferenceEngine.create(models["C"], SchedulerConfig(num_kv_pages=80, kv_block_size=4, max_batch_requests=3,
+                                                                  max_batch_tokens=8, max_prefill_tokens=8, cuda_graphs=graphs),
+                                    dtype="float32")
+    per_request = (24 + 8 + 2) // 4 + 1
+    assert sorted(engine.cache_stats()["pages_per_group"]) == [3 * per_request, 80] and 3 * per_request < sum(-(-len(p) // 4) for p in prompts)
+    results = engine.generate_batch(prompts, GenerationConfig(max_new_tokens=6, ignore_eos=True))
+    for p, r in zip(prompts, results):
+        assert r.finish_reason == "length" and r.output_ids == plain_greedy(models["C"], p, 6)
+    st = engine.cache_stats()
+    assert st["live_requests"] == 0 and sorted(st["free_pages"]) == [3 * per_request, 80] and st["preemptions"] == 0
+    with pytest.raises(ValueError, match="max_step_tokens"):
+        from zedinfer_b200.engine.core import StepEntry
+        engine.core.step([StepEntry("too many at once", list(range(9)), [])])
+    ms_prompt, ms_decode = engine.profile(40, 4)            # the measuring call cuts its prompt to the bound as well
+    assert ms_prompt > 0 and ms_decode > 0 and engine.cache_stats()["live_requests"] == 0
+
+
 def test_single_request_and_first_tokens(models):
     """One-token prompts and the first positions of a sequence: nothing before them in the cache."""
     from zedinfer_b200 import GenerationConfig, SchedulerConfig

@@ -186,6 +186,14 @@ class CacheManager:
                                                     device=device)
 
     @property
+    def step_bound(self) -> Optional[int]:
+        """The most tokens of one request that a step may bring, where the pools rely on it (some group has a window
+        and the caller gave ``max_step_tokens``); None where nothing depends on it."""
+        if self.max_step_tokens is not None and any(g.window is not None for g in self.groups):
+            return self.max_step_tokens
+        return None
+
+    @property
     def scratch_pages(self) -> List[int]:
         """Per group, the page behind the pool's last: padding rows write there, and block-table entries whose page
         a window has given back point there."""
@@ -218,7 +226,7 @@ class CacheManager:
     def open(self, request_id) -> RequestCache:
         if request_id in self._requests:
             raise ValueError(f"request {request_id!r} is already live")
-        if self.max_step_tokens is not None and len(self._requests) >= self.max_requests:
+        if self.step_bound is not None and len(self._requests) >= self.max_requests:
             raise RuntimeError(f"{self.max_requests} requests are live already: the pools of the groups with a window "
                                "are sized for that many")
         slot = -1

@@ -311,9 +311,9 @@ class EngineCore:
             seen.add(e.request_id)
             if len(e.tokens) == 0:
                 raise ValueError(f"request {e.request_id!r} brings no tokens")
-            if self.cache.max_step_tokens is not None and len(e.tokens) > self.cache.max_step_tokens:
-                raise ValueError(f"request {e.request_id!r} brings {len(e.tokens)} tokens in one step; this engine was "
-                                 f"built for at most {self.cache.max_step_tokens} (max_step_tokens)")
+            if self.cache.step_bound is not None and len(e.tokens) > self.cache.step_bound:
+                raise ValueError(f"request {e.request_id!r} brings {len(e.tokens)} tokens in one step; the pools of this "
+                                 f"model's windowed layers were sized for at most {self.cache.step_bound} (max_step_tokens)")
         opened: List[RequestCache] = []
         rcs: List[RequestCache] = []
         try:

@@ -229,7 +229,10 @@ class InferenceEngine:
         try:
             torch.cuda.synchronize()
             start.record()
-            logits = self.core.step([StepEntry(rid, ids, [prefill_len - 1])])
+            bound = self.core.cache.step_bound or prefill_len      # portions, where the pools ask for them
+            for at in range(0, prefill_len, bound):
+                part = ids[at:at + bound]
+                logits = self.core.step([StepEntry(rid, part, [len(part) - 1] if at + bound >= prefill_len else [])])
             from .. import ops
             ops.argmax(logits, out)
             tok = int(out.item())
