@@ -22,8 +22,9 @@
 // which changes no result, since sum and O share it and the final division cancels it.
 //
 // Order of the MMAs: QK(0), QK(1), QK(2), PV(0), QK(3), PV(1), ...: the scores of a tile are asked for as soon as
-// the buffer of the tile two before is free, so they are there when the softmax warps finish the tile between.  Barriers (all waits bounded, as in the matrix product): q_full,
-// k_full/k_empty[3], v_full/v_empty[3], s_full/s_empty[2], p_full, pv_done.
+// the buffer of the tile two before is free, so they are there when the softmax warps finish the tile between.
+// Barriers (all waits bounded, as in the matrix product): q_full, k_full/k_empty[3], v_full/v_empty[3],
+// s_full/s_empty[2], p_full, pv_done.
 //
 // Keys a row must not see (beyond its position, before its window) get probability 0.  Cache slots that hold
 // nothing yet are multiplied by 0 as well, so the pool must never hold NaN bit patterns: it is allocated
