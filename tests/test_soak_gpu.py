@@ -1,5 +1,6 @@
 """Random workloads through InferenceEngine with captured steps, steps launched ahead of the host, prompts cut into
-small portions and pools small enough for preemption: greedy requests must produce the plain implementation's tokens,
+small portions, token budgets small enough that a windowed group's pool is cut to what the requests can hold, and
+pools small enough for preemption: greedy requests must produce the plain implementation's tokens,
 sampling requests the tokens of the same engine run step by step without graphs; no page may be lost."""
 import random
 
@@ -14,7 +15,7 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(scope="module")
 def models(tmp_path_factory):
     root = tmp_path_factory.mktemp("soak_models")
-    return {name: tiny.make_model_dir(root, name) for name in ("A", "B", "D")}
+    return {name: tiny.make_model_dir(root, name) for name in ("A", "B", "C", "D")}
 
 
 def plain_greedy(loaded, prompt, n_new):
@@ -27,14 +28,14 @@ def plain_greedy(loaded, prompt, n_new):
     return out
 
 
-@pytest.mark.parametrize("seed", [1, 2])
+@pytest.mark.parametrize("seed", [1, 2, 3])
 def test_random_workloads(models, seed):
     from zedinfer_b200 import GenerationConfig, InferenceEngine, InferenceRequest, SchedulerConfig
     rng = random.Random(seed)
     loaded = {n: P.load(models[n]) for n in models}
     preemptions = 0
     for trial in range(7):
-        name = rng.choice(["A", "B", "D"])
+        name = rng.choice(["A", "B", "C", "D"])      # C: a window on the upper layers, whose pool shrinks with the token budget
         cfg, _ = tiny.CONFIGS[name]
         page = rng.choice([4, 8, 16])
         n_req = rng.randrange(2, 9)
@@ -54,7 +55,8 @@ def test_random_workloads(models, seed):
         outs = []
         for graphs in (True, False):
             sc = SchedulerConfig(num_kv_pages=pages, kv_block_size=page, max_batch_requests=8,
-                                 max_prefill_tokens=rng.choice([5, 16, 64]) if graphs else 64, cuda_graphs=graphs,
+                                 max_prefill_tokens=rng.choice([5, 16, 64]) if graphs else 64,
+                                 max_batch_tokens=rng.choice([24, 2048]) if graphs else 2048, cuda_graphs=graphs,
                                  run_ahead=graphs)
             engine = InferenceEngine.create(models[name], sc, dtype="float32")
             futs = [engine.submit_async(InferenceRequest(p, g)) for p, g in zip(prompts, configs)]
