@@ -116,3 +116,61 @@ def test_twelve_decoding_requests_at_benchmark_layer_sizes(plain_model, graphs):
     exp = {rid: P.forward(cfg, weights["bfloat16"], toks, torch.bfloat16) for rid, toks in requests.items()}
     bad = first_bad_wanted(got, exp, TOL["bfloat16"])
     assert bad is None, f"first wrong position {bad}"
+
+
+# ---- the 7B-class layer sizes -----------------------------------------------------------------------------------
+LARGE = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 3584, "num_attention_heads": 28, "num_key_value_heads": 4,
+    "head_dim": 128, "intermediate_size": 18944, "vocab_size": 152064, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "use_sliding_window": False,
+    "max_position_embeddings": 4096,
+}
+
+
+# Weights of 0.65 x N(0, 0.02): the logits then have the magnitude of the 1.5B-class test's (largest about 4), which the
+# absolute tolerances are made for; at the full scale they are 1.5 times as large, and so is what bfloat16 adds.
+LARGE_INIT_SCALE = 0.65
+
+
+@pytest.fixture(scope="module")
+def plain_large():
+    cfg = P.config_from_dict(LARGE)
+    drawn = P.random_weights(cfg, SEED, init_scale=LARGE_INIT_SCALE, device="cuda:0")
+    return cfg, {k: P.round_to(v, torch.bfloat16) for k, v in drawn.items()}
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_forty_decoding_requests_at_7b_class_layer_sizes(plain_large, graphs, monkeypatch):
+    """Hidden 3,584, 28 query heads over 4 key/value heads, intermediate 18,944, 2 of 28 layers, bfloat16.  Decode-only
+    steps of up to 40 rows: the stacked gate/up weight has 136 M elements, so from 32 rows it goes to the tcgen05
+    kernel with the activation in its epilogue (for smaller weights that starts at 128 rows), below that to the
+    library and the separate kernel, up to 8 rows to the weight-streaming kernel with K cut in two for the narrow
+    outputs; prompt portions of 64 rows beside the decoding rows."""
+    from zedinfer_b200 import ops
+    from zedinfer_b200.engine.core import EngineCore
+    cfg, weights = plain_large
+    assert 2 * LARGE["intermediate_size"] * LARGE["hidden_size"] >= ops.TC_FUSED_LARGE_ELEMENTS
+    rng = random.Random(7)
+    requests = {f"q{i}": [rng.randrange(LARGE["vocab_size"]) for _ in range(rng.randint(50, 80))] for i in range(44)}
+    steps = traces.decode_heavy(requests, seed=4, max_live=40, tail=(34, 46))
+    sizes = {len(st["entries"]) for st in steps if all(len(e["tokens"]) == 1 for e in st["entries"])}
+    assert max(sizes) >= 32 and min(sizes) <= 8
+    need = traces.max_live_tokens(steps, round_to=16)
+    core = EngineCore(None, "bfloat16", config=dict(LARGE), random_seed=SEED, init_scale=LARGE_INIT_SCALE, page_size=16,
+                      num_pages=need // 16, max_requests=64, cuda_graphs=graphs)
+    core.GPU_BOUND_RATIO = float("inf")
+    fused_rows = set()
+    real = ops.gemm_tcgen05_tiles
+
+    def counted(x, *a, **k):
+        fused_rows.add(x.shape[0])
+        return real(x, *a, **k)
+
+    monkeypatch.setattr(ops, "gemm_tcgen05_tiles", counted)
+    got = run_trace(core, steps)
+    core.check_kernels()
+    exp = {rid: P.forward(cfg, weights, toks, torch.bfloat16) for rid, toks in requests.items()}
+    bad = first_bad_wanted(got, exp, TOL["bfloat16"])
+    assert bad is None, f"first wrong position {bad}"
+    assert fused_rows and min(fused_rows) >= 32 and any(r < 128 for r in fused_rows)      # the fused kernel took few rows too

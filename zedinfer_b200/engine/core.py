@@ -153,7 +153,8 @@ class EngineCore:
                  num_pages: Optional[int] = None, max_tokens: Optional[int] = None,
                  gpu_memory_utilization: float = 0.9, max_requests: int = 64, max_seq_len: Optional[int] = None,
                  device="cuda:0", cuda_graphs: bool = False, config: Optional[dict] = None,
-                 random_seed: Optional[int] = None, max_step_tokens: Optional[int] = None):
+                 random_seed: Optional[int] = None, max_step_tokens: Optional[int] = None,
+                 init_scale: float = 1.0):
         """``num_pages``: pages of each cache group that keeps all keys; ``max_tokens``: size the pool for that many
         cached tokens instead; neither: whatever ``gpu_memory_utilization`` of the device leaves after the weights.
         ``max_step_tokens``: the caller's promise that no step brings more tokens of one request than this (a
@@ -162,7 +163,7 @@ class EngineCore:
 
         ``model_dir=None`` with ``config`` (a config.json dict) and ``random_seed`` builds the model with
         random weights drawn on the device, without a folder (benchmarks of large shapes); the values are those
-        that ``write_random_model(config, random_seed, ...)`` writes (weights/random_init.py)."""
+        that ``write_random_model(config, random_seed, ..., init_scale=init_scale)`` writes (weights/random_init.py)."""
         self.device = require_gpu(device)
         self.dtype = parse_dtype(dtype)
         torch.cuda.set_device(self.device)
@@ -178,7 +179,8 @@ class EngineCore:
             self.config = self.arch.parse(config)
             self.spec = self.arch.build_spec(self.config)
             self.model = Model(self.spec)
-            tensors = random_tensors(self.model.tensor_specs(), random_seed, self.dtype, device=self.device)
+            tensors = random_tensors(self.model.tensor_specs(), random_seed, self.dtype, init_scale=init_scale,
+                                     device=self.device)
         self.model.bind(tensors, self.dtype, self.device)
         del tensors
         self.page_size = int(page_size)
