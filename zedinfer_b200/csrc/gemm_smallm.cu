@@ -346,6 +346,9 @@ gemm_smallm_rope_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, 
                         const RopeOut ro, int M, int K, long long ldx, long long ldw) {
     __shared__ float red[GS_WARPS][16][NT * 8 + 1];
     __shared__ int s_page[NT * 8], s_off[NT * 8];
+    // The decode attention kernel that follows may start now: it keeps away from what this kernel writes until it
+    // has waited for it to finish (dependent_wait() there).  Without such a successor this does nothing.
+    asm volatile("griddepcontrol.launch_dependents;\n" ::);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int half = ro.head_dim >> 1, tiles_per_head = half >> 3;
     const int head = blockIdx.x / tiles_per_head, d0 = (blockIdx.x - head * tiles_per_head) * 8;
