@@ -566,7 +566,8 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
         uint4 v = make_uint4(0, 0, 0, 0);
         if (row < rows_valid) {
             const int h = kvh * group + qb * 16 + row;
-            v = *reinterpret_cast<const uint4*>(q + ((size_t)n * n_heads + h) * HD + c * 8);
+            // through L2: Q was written while this kernel was already running, which the read-only path must not meet
+            v = __ldcg(reinterpret_cast<const uint4*>(q + ((size_t)n * n_heads + h) * HD + c * 8));
         }
         *reinterpret_cast<uint4*>(q_raw + swz<HD>(row, c)) = v;
     }
