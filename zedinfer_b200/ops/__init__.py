@@ -116,7 +116,7 @@ def rope_table(pos: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> 
 
 def can_fuse_rope_product(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], cache: Optional[torch.Tensor]) -> bool:
     """The q/k/v product of a decode step can take rotation and cache append into its epilogue."""
-    return (_small_m_ok(x, w, fused=True) and (bias is None or bias.dtype == torch.bfloat16) and cache is not None
+    return (_small_m_ok(x, w, fused="rope") and (bias is None or bias.dtype == torch.bfloat16) and cache is not None
             and cache.dtype == torch.bfloat16)
 
 
@@ -184,17 +184,39 @@ def gemm_nt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
                     c_ll(out.stride(0)), stream())
 
 
-SMALL_M_WIDE_ELEMENTS = 16 << 20     # weight elements up to which 9..16 rows stay on the streaming kernel
+# 9 to 16 rows on the weight-streaming kernel (two tiles of eight rows).  It reads the activations once per tile
+# and runs three blocks to an SM instead of four, and timed back to back in a graph against the library (plus the
+# kernel its epilogue would save) it wins only in these cases (us at 9 to 16 rows, streaming kernel / library):
+#   K cut at least three ways, up to 16 M elements      1.5B-class down 9.5-10.2 / 13.6  (7B-class output, cut in two: 13.7 / 8.2;
+#                                                       7B-class down 45 / 30; 1.5B-class output, not cut: 5.4 / 4.7)
+#   q/k/v with rotation and append, up to 8 M elements  1.5B-class 5.6 / 5.0 + the rotation kernel  (7B-class 15.0 / 8.7 + it)
+#   gate/up with the activation: never                  1.5B-class 17.6-18.6 / 13.5 with the activation kernel, 7B-class 58 / 49
+SMALL_M_WIDE_ELEMENTS = 16 << 20
+SMALL_M_WIDE_ROPE_ELEMENTS = 8 << 20
+SMALL_M_WIDE_MIN_KSPLIT = 3
+_ksplit_cache: Dict = {}
 
 
-def _small_m_ok(x: torch.Tensor, w: torch.Tensor, fused: bool = False) -> bool:
+def _ksplit(n: int, k: int) -> int:
+    key = (n, k)
+    if key not in _ksplit_cache:
+        _ksplit_cache[key] = int(_gemm_smallm.lib.zi_gemm_smallm_ksplit(c_int(n), c_int(k), c_int(0)))
+    return _ksplit_cache[key]
+
+
+def _small_m_ok(x: torch.Tensor, w: torch.Tensor, fused: Optional[str] = None) -> bool:
     """The weight-streaming kernel takes this product.  Up to 8 rows it is the fastest form measured for every
-    shape tried (1.5B- to 32B-class layers, at or above the library's rate); with 9 to 16 rows it reads the
-    activations twice and falls behind the library on large weights (7B-class down product: 36 us against 30),
-    so it keeps those only for weights up to ``SMALL_M_WIDE_ELEMENTS`` elements, twice that where it saves a
-    kernel by its epilogue (``fused``: activation, or rotation and cache append)."""
-    if x.shape[0] > 8 and w.shape[0] * w.shape[1] > SMALL_M_WIDE_ELEMENTS * (2 if fused else 1):
-        return False
+    shape tried (1.5B- to 32B-class layers, at or above the library's rate).  With 9 to 16 rows it keeps what the
+    table above says; ``fused``: ``"rope"`` (rotation and cache append in its epilogue), ``"silu"`` (activation)."""
+    if x.shape[0] > 8:
+        elements = w.shape[0] * w.shape[1]
+        if fused == "silu":
+            return False
+        if fused == "rope":
+            if elements > SMALL_M_WIDE_ROPE_ELEMENTS:
+                return False
+        elif elements > SMALL_M_WIDE_ELEMENTS or x.shape[1] % 32 != 0 or _ksplit(w.shape[0], w.shape[1]) < SMALL_M_WIDE_MIN_KSPLIT:
+            return False
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= SMALL_M_ROWS
             and x.shape[1] % 32 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0
             and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
@@ -373,7 +395,7 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, bias: Optional[tor
     us at 64 rows), so it takes those rows only for stacked weights of ``TC_FUSED_LARGE_ELEMENTS`` elements or more.
     """
     need_cuda(x, w_gate_up, bias, out)
-    if bias is None and _small_m_ok(x, w_gate_up, fused=True):
+    if bias is None and _small_m_ok(x, w_gate_up, fused="silu"):
         gemm_smallm(x, w_gate_up, None, out, silu_mul=True)
         return
     min_rows = TC_FUSED_MIN_ROWS_LARGE if w_gate_up.shape[0] * w_gate_up.shape[1] >= TC_FUSED_LARGE_ELEMENTS else TC_FUSED_MIN_ROWS
