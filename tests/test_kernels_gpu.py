@@ -392,6 +392,39 @@ def test_prefill_attention_tensor_cores(nh, nkv, hd, ps, window, kernel):
         i += cnt
 
 
+@pytest.mark.parametrize("rows,n,k", [(17, 1536, 8960), (64, 1536, 8960), (256, 896, 4864), (40, 3584, 18944)])
+def test_product_as_partial_sums_folded_by_the_norm(rows, n, k):
+    """A product whose result goes into the residual stream may come as float32 sums over four ranges of K; the norm
+    adds them in order, rounds the sum to bfloat16 as the whole product would have been rounded, and goes on as
+    with a bfloat16 branch output: residual and normed output equal those of that path up to the last bit of the
+    product's rounding, and both are right against float64."""
+    from zedinfer_b200 import ops
+    g = torch.Generator().manual_seed(rows + n)
+    x = (torch.randn(rows, k, generator=g) * 0.5).to(torch.bfloat16).to(dev())
+    w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16).to(dev())
+    wn = (1.0 + 0.1 * torch.randn(n, generator=g)).to(torch.bfloat16).to(dev())
+    h0 = torch.randn(rows, n, generator=g).to(dev())
+    parts = ops.linear_for_residual(x, w, None)
+    assert parts.dim() == 3 and parts.shape == (ops.RESIDUAL_K_PARTS, rows, n) and parts.dtype == torch.float32
+    h1, out1 = h0.clone(), torch.empty(rows, n, dtype=torch.bfloat16, device=dev())
+    ops.add_rmsnorm(h1, parts, wn, 1e-6, out1)
+    ref_delta = (x.double().cpu() @ w.double().cpu().t())
+    delta_bf = ref_delta.to(torch.bfloat16).double()
+    ref_h = h0.double().cpu() + delta_bf
+    assert float((h1.double().cpu() - ref_h).abs().max()) <= 2.0 * float(delta_bf.abs().max()) * 2 ** -8 + 1e-5
+    rstd = 1.0 / torch.sqrt((h1.double().cpu() ** 2).mean(dim=1, keepdim=True) + 1e-6)
+    ref_out = (wn.double().cpu() * h1.double().cpu()) * rstd
+    assert float((out1.double().cpu() - ref_out).abs().max()) < 2e-2
+    # the wanted-rows form reads the same sums and leaves the residual alone
+    idx = torch.tensor([rows - 1, 0, 3], dtype=torch.int32, device=dev())
+    h2, out2 = h0.clone(), torch.empty(3, n, dtype=torch.bfloat16, device=dev())
+    ops.add_rmsnorm(h2, parts, wn, 1e-6, out2, row_idx=idx, write_residual=False)
+    assert torch.equal(h2, h0) and torch.equal(out2, out1[idx.long()])
+    # few rows, a bias, or a short K: the product itself
+    assert ops.linear_for_residual(x[:8].contiguous(), w, None).shape == (8, n)
+    assert ops.linear_for_residual(x, w, torch.zeros(n, dtype=torch.bfloat16, device=dev())).shape == (rows, n)
+
+
 @pytest.mark.parametrize("hd,window", [(128, None), (64, None), (128, 200)])
 def test_prefill_attention_tcgen05_with_scores_far_apart(hd, window):
     """Scores of one row spread over hundreds of units (queries scaled up), so that most exponentials lie far

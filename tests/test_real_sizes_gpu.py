@@ -140,6 +140,38 @@ def plain_large():
     return cfg, {k: P.round_to(v, torch.bfloat16) for k, v in drawn.items()}
 
 
+def test_forty_decoding_requests_at_benchmark_layer_sizes(plain_model, monkeypatch):
+    """Decode-only steps of 17 to 40 rows at the 1.5B-class sizes, bfloat16, captured: the library's products, the
+    rotation and the activation as kernels of their own, and the down product as a batched product over four ranges of
+    K whose float32 sums the next norm adds (the last layer's by the final norm, at the wanted rows only)."""
+    from zedinfer_b200 import ops
+    from zedinfer_b200.engine.core import EngineCore
+    cfg, weights = plain_model
+    rng = random.Random(11)
+    requests = {f"p{i}": [rng.randrange(REAL["vocab_size"]) for _ in range(rng.randint(50, 80))] for i in range(44)}
+    steps = traces.decode_heavy(requests, seed=6, max_live=40, tail=(34, 46))
+    need = traces.max_live_tokens(steps, round_to=16)
+    core = EngineCore(None, "bfloat16", config=dict(REAL), random_seed=SEED, page_size=16, num_pages=need // 16,
+                      max_requests=64, cuda_graphs=True)
+    core.GPU_BOUND_RATIO = float("inf")
+    part_rows = set()
+    real = ops.linear_for_residual
+
+    def counted(x, w, bias):
+        y = real(x, w, bias)
+        if y.dim() == 3:
+            part_rows.add(x.shape[0])
+        return y
+
+    monkeypatch.setattr(ops, "linear_for_residual", counted)
+    got = run_trace(core, steps)
+    core.check_kernels()
+    exp = {rid: P.forward(cfg, weights["bfloat16"], toks, torch.bfloat16) for rid, toks in requests.items()}
+    bad = first_bad_wanted(got, exp, TOL["bfloat16"])
+    assert bad is None, f"first wrong position {bad}"
+    assert part_rows and min(part_rows) >= ops.RESIDUAL_PARTS_MIN_ROWS
+
+
 @pytest.mark.parametrize("graphs", [False, True])
 def test_forty_decoding_requests_at_7b_class_layer_sizes(plain_large, graphs, monkeypatch):
     """Hidden 3,584, 28 query heads over 4 key/value heads, intermediate 18,944, 2 of 28 layers, bfloat16.  Decode-only

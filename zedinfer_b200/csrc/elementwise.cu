@@ -122,6 +122,52 @@ rmsnorm_vec8_kernel(float* __restrict__ residual, const TD* __restrict__ delta, 
     }
 }
 
+// The branch output as partial sums: delta = parts[0] + parts[1] + ... (float32 [n_parts][rows][hidden], the
+// ranges of K of a product that was cut for more parallelism), added in that order and rounded to the output's type,
+// as the uncut product would have rounded its result; then as above.  hidden % 8 == 0, 32-byte aligned rows.
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_parts_vec8_kernel(float* __restrict__ residual, const float* __restrict__ parts, int n_parts, long long part_stride,
+                          const TW* __restrict__ w, TO* __restrict__ out, const int* __restrict__ row_idx, float eps,
+                          int hidden, int write_residual) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const size_t src = row_idx ? (size_t)row_idx[r] : (size_t)r;
+    float* res = residual + src * hidden;
+    const float* d = parts + src * hidden;
+    const bool wb = write_residual && !row_idx;
+    float ss = 0.0f;
+    for (int j = threadIdx.x * 8; j < hidden; j += NORM_THREADS * 8) {
+        float x[8], dv[8];
+        load8(res + j, x);
+        load8(d + j, dv);
+        for (int p = 1; p < n_parts; ++p) {
+            float more[8];
+            load8(d + (size_t)p * part_stride + j, more);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dv[i] += more[i];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = x[i] + to_f32<TO>(from_f32<TO>(dv[i]));
+        if (wb) store8(res + j, x);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
+        store8(row + j, x);
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = 1.0f / sqrtf(ss / (float)hidden + eps);
+    TO* o = out + (size_t)r * hidden;
+    for (int j = threadIdx.x * 8; j < hidden; j += NORM_THREADS * 8) {
+        float x[8], wv[8];
+        load8(row + j, x);
+        load8(w + j, wv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = (wv[i] * x[i]) * rstd;
+        store8(o + j, x);
+    }
+}
+
 // Plain norm of a tensor that is not the float32 residual (used by parts tested alone).
 template <typename TX, typename TW, typename TO>
 __global__ void __launch_bounds__(NORM_THREADS)
@@ -170,6 +216,25 @@ ZI_EXPORT int zi_add_rmsnorm(void* residual, const void* delta, int delta_dtype,
                   (TO*)out, row_idx, eps, hidden, write_residual);
     });););
     return zi_check_launch("add_rmsnorm");
+}
+
+// parts: float32 [n_parts][part_rows][hidden] (part_stride = part_rows * hidden elements); see rmsnorm_parts_vec8_kernel.
+ZI_EXPORT int zi_add_rmsnorm_parts(void* residual, const float* parts, int n_parts, long long part_stride, const void* w,
+                                   int w_dtype, void* out, int out_dtype, const int* row_idx, int rows, int hidden, float eps,
+                                   int write_residual, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0 || hidden % 8) return zi_fail("rmsnorm: partial sums need a width that is a positive multiple of 8, got %d", hidden);
+    if (n_parts < 1 || !parts) return zi_fail("rmsnorm: %d partial sums", n_parts);
+    if ((((uintptr_t)residual | (uintptr_t)parts | (uintptr_t)w | (uintptr_t)out) & 31) || (part_stride & 7))
+        return zi_fail("rmsnorm: partial sums, residual, weight and output must be 32-byte aligned");
+    const size_t smem = (size_t)hidden * sizeof(float);
+    ZI_DISPATCH(w_dtype, TW, ZI_DISPATCH(out_dtype, TO, {
+        auto fn = rmsnorm_parts_vec8_kernel<TW, TO>;
+        if (norm_smem_ok(hidden, (const void*)fn)) return 1;
+        fn<<<rows, NORM_THREADS, smem, stream>>>((float*)residual, parts, n_parts, part_stride, (const TW*)w, (TO*)out, row_idx,
+                                                  eps, hidden, write_residual);
+    }););
+    return zi_check_launch("add_rmsnorm_parts");
 }
 
 ZI_EXPORT int zi_rmsnorm(const void* x, int x_dtype, const void* w, int w_dtype, void* out, int out_dtype,

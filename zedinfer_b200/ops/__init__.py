@@ -29,7 +29,7 @@ _attention_tcgen05 = Library("attention_tcgen05")
 SMALL_M_ROWS = 16                # the weight-streaming kernel takes up to this many rows
 
 __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "rope_table", "gemm_smallm_rope", "can_fuse_rope_product", "silu_mul", "add", "cast",
-           "gemm_nt", "linear", "gemm_smallm", "gemm_tcgen05", "gemm_tcgen05_tiles", "tcgen05_status", "status_word", "linear_silu_mul", "raise_if_tcgen05_failed", "paged_attention", "attention", "decode_attention", "decode_attention_tma", "prefill_attention", "prefill_attention_tcgen05", "argmax", "sample", "repetition_penalty", "advance_decode"]
+           "gemm_nt", "linear", "linear_for_residual", "gemm_smallm", "gemm_tcgen05", "gemm_tcgen05_tiles", "tcgen05_status", "status_word", "linear_silu_mul", "raise_if_tcgen05_failed", "paged_attention", "attention", "decode_attention", "decode_attention_tma", "prefill_attention", "prefill_attention_tcgen05", "argmax", "sample", "repetition_penalty", "advance_decode"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
@@ -65,6 +65,21 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], w: torch.
         raise KernelError(f"add_rmsnorm: the residual stream is float32, got {residual.dtype}")
     need_contiguous("residual", residual), need_contiguous("w", w), need_contiguous("out", out)
     hidden = residual.shape[1]
+    if delta is not None and delta.dim() == 3:
+        # partial sums of a product whose K was cut (linear_for_residual): float32 [parts, rows, hidden]
+        need_contiguous("delta", delta)
+        if delta.dtype != torch.float32 or delta.shape[1:] != residual.shape:
+            raise KernelError(f"add_rmsnorm: partial sums {tuple(delta.shape)} {delta.dtype} vs residual {tuple(residual.shape)}")
+        if row_idx is not None:
+            need_int32("row_idx", row_idx), need_contiguous("row_idx", row_idx)
+        rows = row_idx.numel() if row_idx is not None else residual.shape[0]
+        if w.numel() != hidden or out.shape != (rows, hidden):
+            raise KernelError(f"add_rmsnorm: w {tuple(w.shape)} / out {tuple(out.shape)} do not fit {(rows, hidden)}")
+        _elementwise.call("zi_add_rmsnorm_parts", ptr(residual), ptr(delta), c_int(delta.shape[0]),
+                          c_ll(delta.shape[1] * hidden), ptr(w), c_int(dtype_code(w.dtype)), ptr(out),
+                          c_int(dtype_code(out.dtype)), ptr(row_idx), c_int(rows), c_int(hidden), c_float(eps),
+                          c_int(1 if write_residual else 0), stream())
+        return
     if delta is not None:
         need_contiguous("delta", delta)
         if delta.shape != residual.shape:
@@ -406,6 +421,40 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, bias: Optional[tor
     gate_up = torch.empty((x.shape[0], w_gate_up.shape[0]), dtype=out.dtype, device=x.device)
     linear(x, w_gate_up, bias, gate_up)
     silu_mul(gate_up, out)
+
+
+# A product whose result goes straight into the residual stream (output and down projections), with 17 to 256 rows:
+# the library's kernels for these few rows leave most of the GPU idle when the output is narrow (1.5B-class down
+# product, 64 rows: 13.8 us = 2.0 TB/s).  As a batched product over RESIDUAL_K_PARTS ranges of K with float32 results
+# it takes 7.8 us (7B-class: 30.8 -> 25.2 us; 0.5B-class sizes 8.9 -> 5.2; the 1.5B-class output projection 4.9 ->
+# 3.8), and the norm that folds the branch into
+# the stream adds the ranges on its way (add_rmsnorm), so no kernel is added.  Measured back to back in a graph;
+# from 257 rows the library's own choice is as good, and at 32B-class sizes (141 M elements) nothing is gained.
+RESIDUAL_K_PARTS = 4
+RESIDUAL_PARTS_MIN_ROWS, RESIDUAL_PARTS_MAX_ROWS = 17, 256
+RESIDUAL_PARTS_MAX_ELEMENTS = 80 << 20
+RESIDUAL_PARTS_MIN_K = 1024
+
+
+def linear_for_residual(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """``x @ w.T + bias`` for a result that the next norm adds to the residual stream: either the product itself
+    (``[rows, N]`` of x's type) or, where that is faster, float32 partial sums ``[parts, rows, N]`` over ranges of
+    K, which :func:`add_rmsnorm` adds in order and rounds as the product would have been rounded."""
+    rows, k = x.shape
+    n = w.shape[0]
+    if (bias is None and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and RESIDUAL_PARTS_MIN_ROWS <= rows <= RESIDUAL_PARTS_MAX_ROWS and k >= RESIDUAL_PARTS_MIN_K
+            and n * k <= RESIDUAL_PARTS_MAX_ELEMENTS and k % (8 * RESIDUAL_K_PARTS) == 0 and n % 8 == 0
+            and x.is_contiguous() and w.is_contiguous()):
+        need_cuda(x, w)
+        p = RESIDUAL_K_PARTS
+        parts = torch.empty((p, rows, n), dtype=torch.float32, device=x.device)
+        torch.bmm(x.view(rows, p, k // p).permute(1, 0, 2), w.view(n, p, k // p).permute(1, 2, 0),
+                  out_dtype=torch.float32, out=parts)
+        return parts
+    out = torch.empty((rows, n), dtype=x.dtype, device=x.device)
+    linear(x, w, bias, out)
+    return out
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:

@@ -78,6 +78,16 @@ class AttentionMixer(Mixer):
             self.b_o = tensors["o_proj.bias"].contiguous()
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CallCacheView, owns_cache: bool) -> torch.Tensor:
+        out = ctx.empty(x.shape[0], self.hidden_size)
+        ops.linear(self._attend(x, ctx, cache, owns_cache), self.w_o, self.b_o, out)
+        return out
+
+    def forward_for_residual(self, x: torch.Tensor, ctx: StepContext, cache: CallCacheView,
+                             owns_cache: bool) -> torch.Tensor:
+        return ops.linear_for_residual(self._attend(x, ctx, cache, owns_cache), self.w_o, self.b_o)
+
+    def _attend(self, x: torch.Tensor, ctx: StepContext, cache: CallCacheView, owns_cache: bool) -> torch.Tensor:
+        """Everything up to the output projection: ``[tokens, heads * head_dim]``."""
         if cache.kind != "paged":
             raise RuntimeError("attention needs a paged key/value cache")
         n = x.shape[0]
@@ -90,6 +100,4 @@ class AttentionMixer(Mixer):
                                         write_kv=owns_cache)
         attn = ctx.empty(n, self.q_dim)
         ops.attention(q, cache, attn, ctx, self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale)
-        out = ctx.empty(n, self.hidden_size)
-        ops.linear(attn, self.w_o, self.b_o, out)
-        return out
+        return attn

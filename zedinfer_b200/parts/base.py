@@ -67,7 +67,9 @@ class StepContext:
 
 @dataclass
 class ResidualStream:
-    """The float32 residual ``h`` and a branch output ``delta`` that is not added to it yet."""
+    """The float32 residual ``h`` and a branch output ``delta`` that is not added to it yet.  ``delta`` is
+    ``[tokens, hidden]`` of the step's type, or float32 partial sums ``[parts, tokens, hidden]`` of it (a product whose
+    K was cut, ``ops.linear_for_residual``), which the norm that folds it adds in order and rounds to the step's type."""
     h: torch.Tensor
     delta: Optional[torch.Tensor] = None
 
@@ -142,12 +144,25 @@ class Mixer(Part):
         return None
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CallCacheView, owns_cache: bool) -> torch.Tensor:
+        """``y [tokens, hidden]`` of x's type."""
         raise NotImplementedError
+
+    def forward_for_residual(self, x: torch.Tensor, ctx: StepContext, cache: CallCacheView,
+                             owns_cache: bool) -> torch.Tensor:
+        """Optional.  For an arrangement that puts the result straight into ``ResidualStream.delta``: the same as
+        :meth:`forward`, or float32 partial sums ``[parts, tokens, hidden]`` of it where that is faster (see
+        ``ops.linear_for_residual``); the norm that folds the branch adds them."""
+        return self.forward(x, ctx, cache, owns_cache)
 
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        """``y [tokens, hidden]`` of x's type."""
         raise NotImplementedError
+
+    def forward_for_residual(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        """Optional; as :meth:`Mixer.forward_for_residual`."""
+        return self.forward(x, ctx)
 
 
 class Block:

@@ -27,7 +27,7 @@ class PreNormBlock(Block):
         n, hidden = stream.h.shape
         normed = ctx.empty(n, hidden)
         self.norms["norm1"].forward_residual(stream, normed)
-        stream.delta = self.mixer.forward(normed, ctx, caches["mixer"], owns_cache)
+        stream.delta = self.mixer.forward_for_residual(normed, ctx, caches["mixer"], owns_cache)
         normed2 = ctx.empty(n, hidden)
         self.norms["norm2"].forward_residual(stream, normed2)
-        stream.delta = self.ffn.forward(normed2, ctx)
+        stream.delta = self.ffn.forward_for_residual(normed2, ctx)

@@ -49,10 +49,15 @@ class GatedMLP(FeedForward):
             self.b_gate_up = _stack([tensors["gate_proj.bias"], tensors["up_proj.bias"]])
             self.b_down = tensors["down_proj.bias"].contiguous()
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        n = x.shape[0]
-        act = ctx.empty(n, self.intermediate_size)
+    def _activation(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        act = ctx.empty(x.shape[0], self.intermediate_size)
         ops.linear_silu_mul(x, self.w_gate_up, self.b_gate_up, act)     # activation in the product's epilogue where it can be
-        out = ctx.empty(n, self.hidden_size)
-        ops.linear(act, self.w_down, self.b_down, out)
+        return act
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        out = ctx.empty(x.shape[0], self.hidden_size)
+        ops.linear(self._activation(x, ctx), self.w_down, self.b_down, out)
         return out
+
+    def forward_for_residual(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        return ops.linear_for_residual(self._activation(x, ctx), self.w_down, self.b_down)   # the product, or partial sums over K
