@@ -431,9 +431,13 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, bias: Optional[tor
 # the stream adds the ranges on its way (add_rmsnorm), so no kernel is added.  Measured back to back in a graph;
 # from 257 rows the library's own choice is as good, and at 32B-class sizes (141 M elements) nothing is gained.
 RESIDUAL_K_PARTS = 4
-RESIDUAL_PARTS_MIN_ROWS, RESIDUAL_PARTS_MAX_ROWS = 17, 256
-RESIDUAL_PARTS_MAX_ELEMENTS = 80 << 20
+RESIDUAL_PARTS_MIN_ROWS = 17
 RESIDUAL_PARTS_MIN_K = 1024
+# (most rows, most weight elements) for products with K >= 2 N (down: 1.5B-class 14.4 -> 9.7 us still at 256 rows,
+# 7B-class 39.6 -> 35.6) and for the others (output projection: 7B-class 8.5 -> 8.0 us at 128 rows, but 8.8 -> 10.1 at
+# 192; 32B-class, 26 M elements, 12.2 -> 13.9 at 128)
+RESIDUAL_PARTS_LONG_K = (256, 80 << 20)
+RESIDUAL_PARTS_SQUARE = (128, 16 << 20)
 
 
 def linear_for_residual(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
@@ -442,9 +446,10 @@ def linear_for_residual(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.T
     K, which :func:`add_rmsnorm` adds in order and rounds as the product would have been rounded."""
     rows, k = x.shape
     n = w.shape[0]
+    max_rows, max_elements = RESIDUAL_PARTS_LONG_K if k >= 2 * n else RESIDUAL_PARTS_SQUARE
     if (bias is None and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-            and RESIDUAL_PARTS_MIN_ROWS <= rows <= RESIDUAL_PARTS_MAX_ROWS and k >= RESIDUAL_PARTS_MIN_K
-            and n * k <= RESIDUAL_PARTS_MAX_ELEMENTS and k % (8 * RESIDUAL_K_PARTS) == 0 and n % 8 == 0
+            and RESIDUAL_PARTS_MIN_ROWS <= rows <= max_rows and k >= RESIDUAL_PARTS_MIN_K
+            and n * k <= max_elements and k % (8 * RESIDUAL_K_PARTS) == 0 and n % 8 == 0
             and x.is_contiguous() and w.is_contiguous()):
         need_cuda(x, w)
         p = RESIDUAL_K_PARTS
