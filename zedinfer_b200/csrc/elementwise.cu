@@ -44,6 +44,21 @@ ZI_EXPORT int zi_embedding(const void* table, int table_dtype, const int* ids, v
 // width alone.
 // ---------------------------------------------------------------------------------------
 #define NORM_THREADS 256
+#ifndef NORM_KEEP_ROWS
+#define NORM_KEEP_ROWS 256
+#endif
+__device__ __forceinline__ void load8_hint(const float* p, float* out, uint64_t policy) {
+    asm volatile("ld.global.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;\n"
+                 : "=f"(out[0]), "=f"(out[1]), "=f"(out[2]), "=f"(out[3]) : "l"(p), "l"(policy));
+    asm volatile("ld.global.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;\n"
+                 : "=f"(out[4]), "=f"(out[5]), "=f"(out[6]), "=f"(out[7]) : "l"(p + 4), "l"(policy));
+}
+__device__ __forceinline__ void store8_hint(float* p, const float* v, uint64_t policy) {
+    asm volatile("st.global.L2::cache_hint.v4.f32 [%0], {%1,%2,%3,%4}, %5;\n"
+                 ::"l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "l"(policy) : "memory");
+    asm volatile("st.global.L2::cache_hint.v4.f32 [%0], {%1,%2,%3,%4}, %5;\n"
+                 ::"l"(p + 4), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]), "l"(policy) : "memory");
+}
 template <typename TD, typename TW, typename TO>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const TW* __restrict__ w,
@@ -93,16 +108,21 @@ rmsnorm_vec8_kernel(float* __restrict__ residual, const TD* __restrict__ delta, 
     float* res = residual + src * hidden;
     const TD* d = delta ? delta + src * hidden : nullptr;
     const bool wb = d && write_residual && !row_idx;
+    // Many rows (a prompt portion): the residual stream is read again by the next norm, some 80 us and 150 MB of
+    // other traffic later; it asks L2 to let go of it last.
+    const bool keep = gridDim.x >= NORM_KEEP_ROWS;
+    uint64_t policy = 0;
+    if (keep) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;\n" : "=l"(policy));
     float ss = 0.0f;
     for (int j = threadIdx.x * 8; j < hidden; j += NORM_THREADS * 8) {
         float x[8];
-        load8(res + j, x);
+        if (keep) load8_hint(res + j, x, policy); else load8(res + j, x);
         if (d) {
             float dv[8];
             load8(d + j, dv);
 #pragma unroll
             for (int i = 0; i < 8; ++i) x[i] = x[i] + dv[i];
-            if (wb) store8(res + j, x);
+            if (wb) { if (keep) store8_hint(res + j, x, policy); else store8(res + j, x); }
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
