@@ -289,6 +289,44 @@ def test_sample_matches_plain_distribution(vocab):
             assert lo - 1e-4 <= u <= hi + 1e-4, (r, u, lo, hi)
 
 
+@pytest.mark.parametrize("vocab", [5, 8193, 40000])
+def test_sample_at_the_edges_of_its_rules(vocab):
+    """Ties at the k-th entry, -inf entries, k = 1, k beyond the row, a top_p that only the first entry meets,
+    rows below zero throughout; every row alone gives what it gives in the batch, call after call."""
+    from zedinfer_b200 import ops
+    g = torch.Generator().manual_seed(vocab)
+    base = torch.randn(vocab, generator=g) * 2.0
+    tied = base.clone(); tied[torch.randperm(vocab, generator=g)[:4]] = float(base.max()) + 1.0   # four equal firsts
+    holes = base.clone(); holes[::2] = -math.inf
+    below = -base.abs() - 3.0
+    one = torch.full((vocab,), -math.inf); one[vocab - 1] = 0.5                                   # a single finite entry
+    cases = [(tied, 0.9, 2, 1.0), (tied, 0.9, 0, 0.3), (holes, 1.1, 3, 1.0), (holes, 0.6, 0, 0.8), (base, 1.0, 1, 1.0),
+             (base, 1.0, vocab + 7, 1.0), (base, 0.8, 0, 1e-6), (below, 1.5, 4, 0.7), (one, 1.0, 0, 0.9), (one, 0.7, 3, 1.0)]
+    rows = len(cases)
+    logits = torch.stack([c[0] for c in cases]).to(dev())
+    temp = torch.tensor([c[1] for c in cases]).to(dev())
+    top_k = torch.tensor([c[2] for c in cases], dtype=torch.int32).to(dev())
+    top_p = torch.tensor([c[3] for c in cases]).to(dev())
+    for u in (0.0, 0.31, 0.62, 0.97):
+        uni = torch.full((rows,), u).to(dev())
+        out = torch.empty(rows, dtype=torch.int32, device=dev())
+        ops.sample(logits, out, temp, top_k, top_p, uni)
+        got = out.cpu().tolist()
+        again = torch.empty_like(out)
+        ops.sample(logits, again, temp, top_k, top_p, uni)
+        assert again.cpu().tolist() == got
+        for r, (row, t, k, p) in enumerate(cases):
+            dist = P.sampling_distribution(row, t, k, p)
+            assert dist[got[r]] > 0, f"row {r}: token {got[r]} is outside the kept set"
+            cum = torch.cumsum(dist.double(), 0)
+            lo, hi = float(cum[got[r]] - dist[got[r]].double()), float(cum[got[r]])
+            assert lo - 1e-4 <= u <= hi + 1e-4, (r, u, lo, hi)
+            alone = torch.empty(1, dtype=torch.int32, device=dev())
+            ops.sample(logits[r:r + 1], alone, temp[r:r + 1], top_k[r:r + 1], top_p[r:r + 1], uni[r:r + 1])
+            assert int(alone[0]) == got[r]
+    assert got[4] == P.greedy(base) and got[6] == P.greedy(base) and got[8] == vocab - 1 and got[9] == vocab - 1
+
+
 def test_repetition_penalty():
     from zedinfer_b200 import ops
     row = torch.tensor([2.0, -1.0, 0.5, 4.0, -3.0])

@@ -654,8 +654,10 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     need_int32("out", out)
     if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
         raise KernelError("argmax: logits must be float32 [rows, vocab] with contiguous rows")
-    _sampling.call("zi_argmax", ptr(logits), ptr(out), c_int(logits.shape[0]), c_int(logits.shape[1]),
-                   c_ll(logits.stride(0)), stream())
+    rows, vocab = logits.shape
+    slices = int(_sampling.lib.zi_argmax_slices(c_int(vocab)))
+    part = _grown_scratch(("argmax", logits.device), rows * slices * 2, logits.device) if slices > 1 else None
+    _sampling.call("zi_argmax", ptr(logits), ptr(out), c_int(rows), c_int(vocab), c_ll(logits.stride(0)), ptr(part), stream())
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
