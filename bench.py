@@ -172,7 +172,6 @@ def prefill_requests(core, prompts, tag):
 def measure_decode_device(core, cfg, batch, steps, warmup):
     """Device-only decode: the captured step with greedy choice and hand-over, replayed back to back."""
     import torch
-    from zedinfer_b200.engine.decode_graph import DecodeGraph
     prompts = random_prompts(batch, PROMPT_LEN, cfg["vocab_size"], SEED + batch)
     rids, first = prefill_requests(core, prompts, f"dev{batch}")
     rcs = [core.request(r) for r in rids]
@@ -180,7 +179,7 @@ def measure_decode_device(core, cfg, batch, steps, warmup):
     total_new = (start - PROMPT_LEN) + warmup + steps
     for rc in rcs:
         core.cache.ensure(rc, rc.length + total_new + 1)
-    g = DecodeGraph(core, batch, loop=True)
+    g = core.decode_graph(batch, greedy=True, longest=max(rc.length for rc in rcs) + total_new + 1)
     g.fill(first, rcs)
     for _ in range(start - PROMPT_LEN):
         g.replay()

@@ -117,6 +117,45 @@ def test_many_decoding_requests_match_plain(models, name, max_live, dtype, graph
     assert core.cache.num_live == 0 and all(g.pool.num_used == 0 for g in core.cache.groups)
 
 
+@pytest.mark.parametrize("graphs", [False, True])
+def test_decoding_across_the_length_from_which_clusters_share_a_request(graphs):
+    """A request decodes from below to above the context length from which the decode attention lets several
+    clusters share one request's keys, a short request beside it.  With graphs the step moves from the graph captured
+    for short contexts (no kernel that adds the clusters' parts) to the one captured for the longest sequence."""
+    from zedinfer_b200 import ops
+    from zedinfer_b200.engine.core import EngineCore
+    edge = ops.decode_attention_split_from()
+    cfg = dict(tiny.TINY_E, max_position_embeddings=edge + 300)
+    rng = random.Random(3)
+    tail = 40
+    requests = {"long": [rng.randrange(cfg["vocab_size"]) for _ in range(edge + 18)],
+                "short": [rng.randrange(cfg["vocab_size"]) for _ in range(90)]}
+    steps = []
+    for rid, toks in requests.items():
+        head = len(toks) - tail
+        steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": toks[:head], "want": [head - 1]}], "end": []})
+    for i in range(tail):
+        steps.append({"step": len(steps), "end": [],
+                      "entries": [{"id": rid, "tokens": [toks[len(toks) - tail + i]], "want": [0]} for rid, toks in requests.items()]})
+    steps[-1]["end"] = list(requests)
+    need = traces.max_live_tokens(steps, round_to=16)
+    scale = tiny.INIT_SCALES.get("E", tiny.INIT_SCALE)
+    core = EngineCore(None, "bfloat16", config=cfg, random_seed=11, page_size=16, num_pages=need // 16, max_requests=4,
+                      cuda_graphs=graphs, init_scale=scale)
+    got = run_trace(core, steps)
+    core.check_kernels()
+    pcfg = P.config_from_dict(cfg)
+    weights = {k: P.round_to(v, torch.bfloat16)
+               for k, v in P.random_weights(pcfg, 11, init_scale=scale, device="cuda:0").items()}
+    exp = {rid: P.forward(pcfg, weights, toks, torch.bfloat16).cpu() for rid, toks in requests.items()}
+    bad = first_bad_wanted(got, exp, TOL["bfloat16"])
+    assert bad is None, f"first wrong position {bad}"
+    assert len(got) == 2 * tail + 2
+    if graphs:
+        assert {key[2] for key in core._decode_graphs} == {edge - 1, edge + 300}
+    assert core.cache.num_live == 0
+
+
 @pytest.mark.parametrize("name", ["A", "B", "C", "D", "F"])
 def test_float32_is_the_same_however_it_is_cut(models, name):
     """In float32 every sum has one order, so the cuts agree to the last bit."""

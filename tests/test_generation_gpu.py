@@ -392,7 +392,7 @@ def test_greedy_batch_chooses_inside_the_captured_step(models):
     for p, n, f in zip(prompts, news, futs):
         r = f.result()
         assert r.error is None and r.output_ids == plain_greedy(models["B"], p, n)
-    assert any(greedy for (_, greedy) in engine.core._decode_graphs)
+    assert any(key[1] for key in engine.core._decode_graphs)
     assert engine.steps_run_ahead > 10
     engine.core.cache.check()
     assert engine.core.cache.num_live == 0

@@ -577,9 +577,9 @@ def test_decode_attention_tma_cluster_sizes(requests, window):
 def test_decode_attention_tma_long_context(batch, shared, window):
     """20,000 keys: every warp walks more tiles than the 32 page numbers it reads at a time, with tiles of 32 keys
     (one request: its clusters fit on the device at once) and of 16 keys (nine requests: they do not).  ``shared``:
-    the call is told how long the longest context is, and several clusters share the long request's keys (four at
-    20,000 keys, two inside a window of 9,000) while the short requests of the same step keep one cluster each; a
-    second kernel adds the parts."""
+    the call is told how long the longest context is, and several clusters share the long request's keys (sixteen
+    for one request of 20,000 keys, eight inside a window of 9,000, four when nine requests are in the step) while the
+    short requests of the same step keep one cluster each; a second kernel adds the parts."""
     from zedinfer_b200 import ops
     t = torch.bfloat16
     nh, nkv, hd, ps = 4, 1, 64, 16
@@ -602,6 +602,37 @@ def test_decode_attention_tma_long_context(batch, shared, window):
     qf = qd.float().cpu()
     for r in range(n):
         ref = plain_attention_rows(qf[r:r + 1], ks[r], vs[r], [lens[r] - 1], scale, window)
+        assert float((got[r:r + 1] - ref).abs().max()) < 2e-2, (r, lens[r])
+
+
+@pytest.mark.parametrize("nkv,hd", [(1, 64), (2, 128)])
+def test_decode_attention_tma_where_sharing_begins(nkv, hd):
+    """Contexts on both sides of the length from which clusters share a request (and of the tile that holds it), in
+    one step that is told the longest; each request's query points at one key near the end of its first quarter, which
+    belongs to another cluster than the newest key as soon as the request is shared."""
+    from zedinfer_b200 import ops
+    t = torch.bfloat16
+    nh, ps = 2 * nkv, 16
+    edge = ops.decode_attention_split_from()
+    lens = [edge - 17, edge - 1, edge, edge + 1, edge + 15, edge + 16, edge + 1030, 2 * edge - 1, 2 * edge + 5]
+    pool, view, tables, ks, vs, page_stride, kv_stride = build_cache(len(lens), lens, nkv, hd, ps, t, seed=21)
+    n = len(lens)
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(n, nh, hd, generator=g)
+    for r, l in enumerate(lens):
+        q[r, :, :] = ks[r][l // 4 - 3, 0][None, :] * 4.0
+    qd = q.to(t).to(dev())
+    pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=dev())
+    out = torch.full((n, nh * hd), float("nan"), dtype=t, device=dev())
+    scale = 1.0 / math.sqrt(hd)
+    ops.decode_attention_tma(qd, view, out, tables, None, pos, nh, nkv, hd, ps, page_stride, kv_stride, None, scale,
+                             max_kv_len=max(lens))
+    torch.cuda.synchronize()
+    assert ops.tcgen05_status(dev()) == 0
+    got = out.float().cpu().view(n, nh, hd)
+    qf = qd.float().cpu()
+    for r in range(n):
+        ref = plain_attention_rows(qf[r:r + 1], ks[r], vs[r], [lens[r] - 1], scale, None)
         assert float((got[r:r + 1] - ref).abs().max()) < 2e-2, (r, lens[r])
 
 

@@ -425,10 +425,14 @@ __device__ __forceinline__ void pv_accumulate_tma(float (&O)[HD / 8][4], const f
 
 // How many of the n_splits clusters that a launch provides for one (request, key/value head) are at work for a
 // request with `tiles` visible tiles: the same answer in the attention kernel and in the merge kernel.
+// Sharing pays from DT_SPLIT_FROM keys on (below that one cluster is as fast and the merge is saved); each cluster
+// then takes at least DT_SPLIT_KEYS keys.
+#define DT_SPLIT_KEYS 1024
+#define DT_SPLIT_FROM 4096
 __device__ __forceinline__ int dt_effective_splits(int tiles, int n_splits, int min_split_tiles) {
     if (n_splits <= 1) return 1;
     const int e = tiles / min_split_tiles;
-    return e < 1 ? 1 : (e > n_splits ? n_splits : e);
+    return e < DT_SPLIT_FROM / DT_SPLIT_KEYS ? 1 : (e > n_splits ? n_splits : e);
 }
 
 // Adds the parts of the clusters that shared one request's keys, in the order of the keys: grid (tokens, heads),
@@ -940,8 +944,9 @@ static cudaError_t dt_dispatch(const DtArgs& a, int keys, int cl) {
 //   Very few units with long contexts leave most of the device idle (one request of 2 key/value heads and 32,768
 //   tokens: 16 blocks, 0.8 TB/s): then several clusters share a unit, each taking at least DT_SPLIT_KEYS keys, as
 //   far as the longest context of the step (max_kv_len) and the free SMs allow, and a second kernel adds their
-//   parts.
-#define DT_SPLIT_KEYS 4096
+//   parts.  That second kernel costs a step of 28 layers about 0.07 ms even when no request is long enough to be
+//   shared (measured: 1.25 -> 1.32 ms at 8 requests), so a launch whose max_kv_len stays below DT_SPLIT_FROM plans
+//   none; one request of 8,192 tokens: 1.43 ms a step with clusters of 4,096 keys, 1.27 with clusters of 1,024.
 #define DT_MAX_SPLITS 16
 struct DtPlan { int keys, cl, splits, min_split_tiles; };
 static int dt_plan(DtPlan* p, int n_tokens, int n_kv_heads, int q_blocks, int head_dim, int max_kv_len) {
@@ -956,7 +961,7 @@ static int dt_plan(DtPlan* p, int n_tokens, int n_kv_heads, int q_blocks, int he
     }
     int cl = 8;
     while (cl > 1 && units * cl > slots) cl >>= 1;
-    long long splits = max_kv_len / DT_SPLIT_KEYS;
+    long long splits = max_kv_len < DT_SPLIT_FROM ? 1 : max_kv_len / DT_SPLIT_KEYS;
     if (splits > slots / (units * cl)) splits = slots / (units * cl);
     if (splits > DT_MAX_SPLITS) splits = DT_MAX_SPLITS;
     if (splits < 2) splits = 1;
@@ -966,6 +971,10 @@ static int dt_plan(DtPlan* p, int n_tokens, int n_kv_heads, int q_blocks, int he
     p->min_split_tiles = DT_SPLIT_KEYS / p->keys;
     return 0;
 }
+
+// The number of cached tokens from which a launch may let several clusters share a request (and then runs the
+// kernel that adds their parts): a caller that knows its requests stay below passes a smaller max_kv_len.
+ZI_EXPORT int zi_decode_attention_tma_split_from() { return DT_SPLIT_FROM; }
 
 // Floats of scratch a call needs for the parts of clusters that share a request (0: none).
 ZI_EXPORT long long zi_decode_attention_tma_part_floats(int n_tokens, int n_heads, int n_kv_heads, int head_dim, int max_kv_len) {

@@ -42,11 +42,14 @@ def capturing(graph: "torch.cuda.CUDAGraph", pool=None):
 
 
 class DecodeGraph:
-    def __init__(self, core, bucket: int, loop: bool = False, sample: bool = False):
+    def __init__(self, core, bucket: int, loop: bool = False, sample: bool = False, reach: Optional[int] = None):
         """``loop``: the graph also chooses a token per row and hands it to the next step on the device; the most
         likely token, or with ``sample`` a draw with the row's temperature, top-k, top-p and uniform number, which
-        :meth:`set_sampling` brings before a replay (rows of temperature 0 take the most likely token)."""
+        :meth:`set_sampling` brings before a replay (rows of temperature 0 take the most likely token).
+        ``reach``: the longest context (after the step) that a request of a replay may have; the core's longest
+        sequence if None.  Kernels plan their launches for it at capture."""
         self.core, self.bucket, self.loop, self.sample = core, bucket, loop or sample, sample
+        self.reach = core.max_seq_len if reach is None else min(int(reach), core.max_seq_len)
         b, width, ng = bucket, core.table_width, len(core.cache.groups)
         pw = self.pos_width = core.spec.position_width          # position numbers per token, one run of b per axis
         self.off_ids, self.off_pos, self.off_seg = 0, b, (1 + pw) * b
@@ -68,7 +71,7 @@ class DecodeGraph:
             tok_seg=d[self.off_seg: self.off_seg + b], tables=tables, slots=d[self.off_slots: self.off_slots + b],
             position_axes=d[self.off_pos: self.off_pos + pw * b].view(pw, b),
             seg_start_host=list(range(b)), seg_len_host=[1] * b, seg_pos0_host=[0] * b, slots_host=[-1] * b,
-            decode_only=True, max_kv_len=core.max_seq_len)
+            decode_only=True, max_kv_len=self.reach)
         self.want = d[self.off_want: self.off_want + b]
         # loop: the tokens chosen by the step, and behind them the kernels' status word as the step left it
         self.sampled = torch.zeros(b + 1, dtype=torch.int32, device=core.device)

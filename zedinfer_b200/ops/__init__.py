@@ -534,6 +534,12 @@ def decode_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, ta
                         c_float(scale), stream())
 
 
+def decode_attention_split_from() -> int:
+    """The number of cached tokens from which :func:`decode_attention_tma` lets several clusters share one request's
+    keys and launches the kernel that adds their parts: a step whose ``max_kv_len`` stays below it has neither."""
+    return int(_attention_mma.lib.zi_decode_attention_tma_split_from())
+
+
 def decode_attention_tma(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
                          tok_seg: Optional[torch.Tensor], pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                          page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float,
