@@ -289,6 +289,34 @@ def test_sample_matches_plain_distribution(vocab):
             assert lo - 1e-4 <= u <= hi + 1e-4, (r, u, lo, hi)
 
 
+@pytest.mark.parametrize("vocab", [3000, 151936])
+def test_sample_with_few_likely_tokens(vocab):
+    """Logits as a language model gives them: a few likely tokens and a long tail (probability ~ rank^-1.5, ranks
+    dealt at random over the vocabulary).  top-p then keeps tens of tokens, top-k a few, a large k thousands."""
+    from zedinfer_b200 import ops
+    g = torch.Generator().manual_seed(7)
+    cases = [(0.8, 0, 0.9), (1.0, 0, 0.5), (0.7, 40, 0.95), (1.0, 2500, 0.99), (1.2, 2500, 1.0), (0.9, 0, 0.999), (1.0, 7, 1.0)]
+    rows = len(cases)
+    rank = torch.stack([torch.randperm(vocab, generator=g) for _ in range(rows)]).float() + 1.0
+    logits = -1.5 * torch.log(rank) + 0.01 * torch.randn(rows, vocab, generator=g)
+    temp = torch.tensor([c[0] for c in cases]).to(dev())
+    top_k = torch.tensor([c[1] for c in cases], dtype=torch.int32).to(dev())
+    top_p = torch.tensor([c[2] for c in cases]).to(dev())
+    dl = logits.to(dev())
+    dists = [P.sampling_distribution(logits[r], *cases[r]) for r in range(rows)]
+    assert int((dists[0] > 0).sum()) < 500 and int((dists[3] > 0).sum()) > 300
+    for u in (0.0, 0.2, 0.45, 0.71, 0.93, 0.9999):
+        out = torch.empty(rows, dtype=torch.int32, device=dev())
+        ops.sample(dl, out, temp, top_k, top_p, torch.full((rows,), u).to(dev()))
+        got = out.cpu().tolist()
+        for r in range(rows):
+            dist = dists[r]
+            assert dist[got[r]] > 0, f"row {r}: token {got[r]} is outside the kept set"
+            cum = torch.cumsum(dist.double(), 0)
+            lo, hi = float(cum[got[r]] - dist[got[r]].double()), float(cum[got[r]])
+            assert lo - 1e-4 <= u <= hi + 1e-4, (r, u, lo, hi)
+
+
 @pytest.mark.parametrize("vocab", [5, 8193, 40000])
 def test_sample_at_the_edges_of_its_rules(vocab):
     """Ties at the k-th entry, -inf entries, k = 1, k beyond the row, a top_p that only the first entry meets,
