@@ -139,6 +139,51 @@ def test_temperature_sampling_is_deterministic_per_seed(models):
         seq.append(tok)
 
 
+def test_repetition_penalty_from_the_table_of_generated_tokens(models):
+    """Requests with a repetition penalty are sampled inside the captured step, run ahead of the host, from a table
+    on the device of what each has generated.  Same tokens as with the host in step and no graphs, also when pages
+    run out and the youngest request is taken off the GPU and comes back (its table is built anew); and each token
+    is the plain implementation's pick from the penalised logits."""
+    from zedinfer_b200 import GenerationConfig, InferenceRequest, SchedulerConfig
+    from zedinfer_b200.engine import InferenceEngine
+    from zedinfer_b200.sampling import uniform_for
+    prompts = [list(range(1, 8)), list(range(20, 33)), [5], list(range(40, 49))]
+    configs = [GenerationConfig(max_new_tokens=30, use_argmax=False, temperature=0.9, repetition_penalty=1.8, seed=3, ignore_eos=True),
+               GenerationConfig(max_new_tokens=36, use_argmax=False, temperature=0.8, top_k=6, repetition_penalty=1.3, seed=7, ignore_eos=True),
+               GenerationConfig(max_new_tokens=25, ignore_eos=True),
+               GenerationConfig(max_new_tokens=33, use_argmax=False, temperature=1.1, top_p=0.9, repetition_penalty=0.7, seed=9, ignore_eos=True)]
+
+    def run(ahead, graphs, pages):
+        engine = InferenceEngine.create(models["A"], SchedulerConfig(num_kv_pages=pages, kv_block_size=4, max_batch_requests=4,
+                                                                     run_ahead=ahead, cuda_graphs=graphs), dtype="float32")
+        futures = [engine.submit_async(InferenceRequest(p, c)) for p, c in zip(prompts, configs)]
+        engine.run_loop()
+        assert engine.cache_stats()["live_requests"] == 0
+        return [f.result() for f in futures], engine
+
+    base, e0 = run(False, False, 64)
+    assert e0.steps_run_ahead == 0 and all(r.error is None for r in base)
+    for pages in (64, 24):                 # 24 pages: the youngest request is preempted in mid-decode
+        got, e1 = run(True, True, pages)
+        assert e1.steps_run_ahead > 10
+        assert any(key[1] == "sample" for key in e1.core._decode_graphs)
+        if pages == 24:
+            assert e1.cache_stats()["preemptions"] > 0
+        for a, b in zip(base, got):
+            assert a.output_ids == b.output_ids and a.finish_reason == b.finish_reason
+    # a small top-k and a strong penalty: the same token seldom comes twice in a row
+    cfg, w = P.load(models["A"])
+    seq = list(prompts[1])
+    out = base[1].output_ids
+    for i, tok in enumerate(out):
+        dist = P.sampling_distribution(P.forward(cfg, w, seq)[-1], 0.8, 6, 1.0, recent=out[:i], repetition_penalty=1.3)
+        u = uniform_for(7, i)
+        cum = torch.cumsum(dist.double(), 0)
+        lo, hi = float(cum[tok] - dist[tok].double()), float(cum[tok])
+        assert dist[tok] > 0 and lo - 1e-4 <= u <= hi + 1e-4, (i, tok)
+        seq.append(tok)
+
+
 def test_top_k_one_is_greedy_and_stop_token_ends(models):
     from zedinfer_b200 import GenerationConfig, SchedulerConfig
     from zedinfer_b200.engine import InferenceEngine

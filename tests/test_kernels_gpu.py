@@ -363,6 +363,40 @@ def test_repetition_penalty():
     assert torch.allclose(d.cpu(), torch.tensor([1.0, -2.0, 0.5, 2.0, -3.0]))
 
 
+def test_repetition_penalty_from_a_table_of_counts():
+    """Counts kept per slot: a step's chosen tokens and a list of tokens are added, and the rows' logits are penalised
+    once per time the token was generated, as the loop over the generated tokens does; rows without a slot or with a
+    penalty of 1 keep their logits."""
+    from zedinfer_b200 import ops
+    vocab, slots_n = 1311, 5
+    g = torch.Generator().manual_seed(4)
+    logits = torch.randn(4, vocab, generator=g) * 3.0
+    logits[0, 17] = 0.0
+    counts = torch.zeros(slots_n, vocab, dtype=torch.int32, device=dev())
+    history = {3: [17, 5, 5, 900, 1310, 5], 0: [2, 2], 4: [7]}
+    for slot, toks in history.items():
+        ops.count_token_list(counts[slot], torch.tensor(toks[:-1], dtype=torch.int32, device=dev()))
+    slots = torch.tensor([3, -1, 0, 4], dtype=torch.int32, device=dev())
+    last = torch.tensor([history[3][-1], 11, history[0][-1], history[4][-1]], dtype=torch.int32, device=dev())
+    ops.count_tokens(counts, slots, last)
+    exp_counts = torch.zeros(slots_n, vocab, dtype=torch.int32)
+    for slot, toks in history.items():
+        for t in toks:
+            exp_counts[slot, t] += 1
+    assert torch.equal(counts.cpu(), exp_counts)
+    penalty = torch.tensor([1.7, 2.0, 0.6, 1.0], dtype=torch.float32, device=dev())
+    d = logits.to(dev())
+    ops.penalty_rows(d, counts, slots, penalty)
+    exp = logits.clone()
+    for row, (slot, pen) in enumerate(((3, 1.7), (None, 2.0), (0, 0.6), (4, 1.0))):
+        if slot is None:
+            continue
+        for t in history[slot]:
+            exp[row, t] = exp[row, t] / pen if exp[row, t] > 0 else exp[row, t] * pen
+    assert torch.equal(d.cpu(), exp)
+    assert float(d[0, 17]) == 0.0
+
+
 # ---- tensor-core attention (bfloat16, head_dim 64 / 128) -------------------------------------------------
 @pytest.mark.parametrize("kernel", ["cp_async", "tma"])
 @pytest.mark.parametrize("nh,nkv,hd,ps,window", [(12, 2, 128, 16, None), (7, 1, 64, 4, None), (20, 1, 128, 16, None),

@@ -155,6 +155,70 @@ ZI_EXPORT int zi_repetition_penalty(float* row, const int* tokens, int n, int vo
     return zi_check_launch("repetition_penalty");
 }
 
+// The same penalty from a table kept on the device: counts[slot][token] = how often the request in that slot has
+// generated the token.  A row's logits are penalised as many times as the token was generated (the reference's loop
+// over the generated tokens, src/frontend/sampler/sampler.cpp:439-451, in any order: a logit keeps its sign under
+// the penalty, so the order of the listings does not matter).  The host then never sends the generated tokens, and
+// a step that was launched before the host has read the step before it finds the table up to date.
+//   rows whose slot is negative or whose penalty is 1 are left alone.
+__global__ void penalty_rows_kernel(float* __restrict__ logits, const int* __restrict__ counts, const int* __restrict__ slots,
+                                    const float* __restrict__ penalty, int vocab, long long row_stride, long long count_stride) {
+    const int r = blockIdx.y;
+    const int slot = slots[r];
+    const float p = penalty[r];
+    if (slot < 0 || p == 1.0f || !(p > 0.0f)) return;
+    float* row = logits + (size_t)r * row_stride;
+    const int* cnt = counts + (size_t)slot * count_stride;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < vocab; i += gridDim.x * blockDim.x) {
+        int c = cnt[i];
+        if (c <= 0) continue;
+        float l = row[i];
+        for (; c > 0; --c) l = l > 0.0f ? l / p : l * p;
+        row[i] = l;
+    }
+}
+
+// counts[slots[r]][tokens[r]] += 1 for the rows whose slot is not negative: the tokens a step has just chosen.
+__global__ void count_tokens_kernel(int* __restrict__ counts, const int* __restrict__ slots, const int* __restrict__ tokens,
+                                    int rows, int vocab, long long count_stride) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    const int slot = slots[r], t = tokens[r];
+    if (slot < 0 || t < 0 || t >= vocab) return;
+    counts[(size_t)slot * count_stride + t] += 1;              // one row per slot: nobody else adds to this entry
+}
+
+// counts_row[tokens[j]] += 1 for a list of tokens (a request that comes back after its slot was given away).
+__global__ void count_token_list_kernel(int* __restrict__ counts_row, const int* __restrict__ tokens, int n, int vocab) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    const int t = tokens[j];
+    if (t >= 0 && t < vocab) atomicAdd(counts_row + t, 1);
+}
+
+ZI_EXPORT int zi_penalty_rows(float* logits, const int* counts, const int* slots, const float* penalty, int rows, int vocab,
+                              long long row_stride, long long count_stride, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0 || rows > 65535) return zi_fail("penalty_rows: rows=%d vocab=%d", rows, vocab);
+    int blocks = (vocab + 4 * 256 - 1) / (4 * 256);
+    if (blocks > 64) blocks = 64;
+    penalty_rows_kernel<<<dim3(blocks, rows), 256, 0, stream>>>(logits, counts, slots, penalty, vocab, row_stride, count_stride);
+    return zi_check_launch("penalty_rows");
+}
+
+ZI_EXPORT int zi_count_tokens(int* counts, const int* slots, const int* tokens, int rows, int vocab, long long count_stride,
+                              cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    count_tokens_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(counts, slots, tokens, rows, vocab, count_stride);
+    return zi_check_launch("count_tokens");
+}
+
+ZI_EXPORT int zi_count_token_list(int* counts_row, const int* tokens, int n, int vocab, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    count_token_list_kernel<<<(n + 255) / 256, 256, 0, stream>>>(counts_row, tokens, n, vocab);
+    return zi_check_launch("count_token_list");
+}
+
 // ---- sampling ---------------------------------------------------------------------------------------------
 // A cluster of eight blocks of 1,024 threads per row: block c walks the c-th eighth of the row, every thread with
 // eight independent loads in flight, and what the blocks find (best entry, sums, bin totals, masses) is exchanged

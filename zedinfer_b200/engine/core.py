@@ -16,7 +16,7 @@ import numpy as np
 import torch
 
 from .. import ops
-from ..cache.manager import CacheManager, RequestCache
+from ..cache.manager import CacheManager, RequestCache, StateNeed
 from ..config.registry import load_model_config
 from ..parts.base import StepContext
 from ..weights.loader import load_weights
@@ -148,18 +148,26 @@ class _SeenStep:
         self.count, self.host_ms, self.events, self.gpu_bound = 0, 0.0, None, None
 
 
+COUNTS_KEY = ("sampler", "generated_counts")      # the cache key of the sampler's per-request state
+
+
 class EngineCore:
     def __init__(self, model_dir: Optional[str], dtype="bfloat16", *, page_size: int = 16,
                  num_pages: Optional[int] = None, max_tokens: Optional[int] = None,
                  gpu_memory_utilization: float = 0.9, max_requests: int = 64, max_seq_len: Optional[int] = None,
                  device="cuda:0", cuda_graphs: bool = False, config: Optional[dict] = None,
                  random_seed: Optional[int] = None, max_step_tokens: Optional[int] = None,
-                 init_scale: float = 1.0):
+                 init_scale: float = 1.0, count_generated: bool = False):
         """``num_pages``: pages of each cache group that keeps all keys; ``max_tokens``: size the pool for that many
         cached tokens instead; neither: whatever ``gpu_memory_utilization`` of the device leaves after the weights.
         ``max_step_tokens``: the caller's promise that no step brings more tokens of one request than this (a
         scheduler's token budget); groups of layers with a window then get pools only as large as ``max_requests``
         requests can fill, and the memory goes to the other groups.
+
+        ``count_generated``: every request gets a slot of fixed-size state of the sampler's: how often it has
+        generated each token of the vocabulary (int32 ``[vocab]``, ``generated_counts``), zero when the request
+        starts.  The repetition penalty then works from that table on the device.  At most ``max_requests`` requests
+        are live at a time then.
 
         ``model_dir=None`` with ``config`` (a config.json dict) and ``random_seed`` builds the model with
         random weights drawn on the device, without a folder (benchmarks of large shapes); the values are those
@@ -186,8 +194,10 @@ class EngineCore:
         self.page_size = int(page_size)
         self.max_seq_len = min(int(max_seq_len or self.spec.max_position_embeddings),
                                self.spec.max_position_embeddings)
-        self.cache = CacheManager(self.model.cache_needs(), self.page_size, max_requests=max_requests,
-                                  max_step_tokens=max_step_tokens)
+        needs = list(self.model.cache_needs())
+        if count_generated:
+            needs.append((COUNTS_KEY, StateNeed((self.spec.vocab_size,), torch.int32)))
+        self.cache = CacheManager(needs, self.page_size, max_requests=max_requests, max_step_tokens=max_step_tokens)
         if num_pages is None and max_tokens is not None:
             num_pages = (int(max_tokens) + self.page_size - 1) // self.page_size
         if num_pages is None:
@@ -204,6 +214,8 @@ class EngineCore:
                                    f"(free {free >> 20} MiB of {total >> 20} MiB, utilization {gpu_memory_utilization})")
         self.cache.allocate_device(int(num_pages), self.dtype, self.device)
         self.views = {call: self.cache.view_for_call(call) for call, _ in self.model.cache_needs()}
+        # int32 [max_requests, vocab] or None: see count_generated
+        self.generated_counts = self.cache.view_for_call(COUNTS_KEY).tensor if count_generated else None
         self.table_width = max(1, (self.max_seq_len + self.page_size - 1) // self.page_size)
         self._ring = PinnedStaging()
         self.cuda_graphs = bool(cuda_graphs)

@@ -75,10 +75,11 @@ class DecodeGraph:
         self.want = d[self.off_want: self.off_want + b]
         # loop: the tokens chosen by the step, and behind them the kernels' status word as the step left it
         self.sampled = torch.zeros(b + 1, dtype=torch.int32, device=core.device)
-        # sample: temperature | top_p | uniform (float32 bits) | top_k, one row of b each, sent in one copy
-        self.par_host = np.zeros(4 * b, dtype=np.int32)
-        self.par_host[b: 2 * b] = np.float32(1.0).view(np.int32)
-        self.par = torch.zeros(4 * b, dtype=torch.int32, device=core.device)
+        # sample: temperature | top_p | uniform | repetition penalty (float32 bits) | top_k | slot of the request's
+        # table of generated tokens (-1: none kept), one row of b each, sent in one copy
+        self.par_host = np.zeros(6 * b, dtype=np.int32)
+        self._blank_par()
+        self.par = torch.zeros(6 * b, dtype=torch.int32, device=core.device)
         if sample:
             core._ring.stage_into(self.par_host, self.par)
         self.launches = 0
@@ -102,24 +103,37 @@ class DecodeGraph:
         if self.loop:
             b = self.bucket
             if self.sample:
-                fl = self.par[:3 * b].view(torch.float32)
-                ops.sample(logits, self.sampled[:b], fl[:b], self.par[3 * b:], fl[b: 2 * b], fl[2 * b: 3 * b])
+                fl = self.par[:4 * b].view(torch.float32)
+                counts, slots = self.core.generated_counts, self.par[5 * b:]
+                if counts is not None:
+                    ops.penalty_rows(logits, counts, slots, fl[3 * b:])
+                ops.sample(logits, self.sampled[:b], fl[:b], self.par[4 * b: 5 * b], fl[b: 2 * b], fl[2 * b: 3 * b])
+                if counts is not None:
+                    ops.count_tokens(counts, slots, self.sampled[:b])
             else:
                 ops.argmax(logits, self.sampled[:b])
             self.sampled[b:].copy_(ops.status_word(self.core.device))
             ops.advance_decode(self.ctx.token_ids, self.ctx.position_axes, self.sampled[:b])
         return logits
 
-    def set_sampling(self, par: np.ndarray, top_k: np.ndarray) -> None:
-        """``par`` float32 ``[3, n]`` (temperature, top_p, uniform number) and ``top_k`` int32 ``[n]`` for the first n
-        rows of the next replay; the rows behind them are greedy."""
+    def _blank_par(self) -> None:
+        b, h = self.bucket, self.par_host
+        h[:] = 0                                                  # temperature 0: greedy rows
+        h[b: 2 * b] = np.float32(1.0).view(np.int32)              # top_p
+        h[3 * b: 4 * b] = np.float32(1.0).view(np.int32)          # repetition penalty
+        h[5 * b:] = -1                                            # no table of generated tokens
+
+    def set_sampling(self, par: np.ndarray, ints: np.ndarray) -> None:
+        """``par`` float32 ``[4, n]`` (temperature, top_p, uniform number, repetition penalty) and ``ints`` int32
+        ``[2, n]`` (top_k, slot of the table of generated tokens or -1) for the first n rows of the next replay; the
+        rows behind them are greedy."""
         b, n = self.bucket, par.shape[1]
         h = self.par_host
-        h[:] = 0
-        h[b: 2 * b] = np.float32(1.0).view(np.int32)
-        for k in range(3):
+        self._blank_par()
+        for k in range(4):
             h[k * b: k * b + n] = np.ascontiguousarray(par[k], dtype=np.float32).view(np.int32)
-        h[3 * b: 3 * b + n] = top_k
+        h[4 * b: 4 * b + n] = ints[0]
+        h[5 * b: 5 * b + n] = ints[1]
         self.core._ring.stage_into(h, self.par)
 
     def _pad_rows(self, first: int) -> None:

@@ -44,7 +44,7 @@ class InferenceEngine:
         self.scheduler_config = scheduler_config
         core.cuda_graphs = bool(scheduler_config.cuda_graphs)
         self.scheduler = Scheduler(scheduler_config, core.cache, core.max_seq_len, core.spec.eos_token_ids)
-        self.sampler = Sampler(core.device)
+        self.sampler = Sampler(core.device, core)
         self.steps_run = 0
         self.steps_run_ahead = 0
         self.on_step: Optional[Callable[[ScheduledBatch], None]] = None
@@ -62,7 +62,8 @@ class InferenceEngine:
         cfg.validate()
         sizes = dict(page_size=cfg.kv_block_size, num_pages=cfg.num_kv_pages,
                      gpu_memory_utilization=cfg.gpu_memory_utilization, max_requests=cfg.max_batch_requests,
-                     max_seq_len=cfg.max_seq_len, device=device, max_step_tokens=cfg.max_batch_tokens)
+                     max_seq_len=cfg.max_seq_len, device=device, max_step_tokens=cfg.max_batch_tokens,
+                     count_generated=True)
         if random_seed is None:
             core = EngineCore(model_path, dtype, **sizes)
         else:
@@ -159,6 +160,8 @@ class InferenceEngine:
                     if picked is not None:
                         chosen = self.sampler.from_step(picked, len(entries))
                         chosen.drawn = sampling is not None
+                        if sampling is not None:
+                            self.sampler.counted(batch.decode_requests)
                 if chosen is None:
                     logits = self.core.step(entries)
                     rows = batch.rows_wanted()
@@ -193,8 +196,8 @@ class InferenceEngine:
         for r in batch.decode_requests:
             if r.cancelled or r.phase == RequestPhase.COMPLETE or len(r.output_ids) + 2 > r.max_new_tokens:
                 return False
-            if not r.config.use_argmax and r.config.repetition_penalty != 1.0:
-                return False
+            if not r.config.use_argmax and r.config.repetition_penalty != 1.0 and self.sampler.core is None:
+                return False          # the penalty needs the generated tokens on the host
         return True
 
     def _launch_ahead(self, batch: ScheduledBatch, chosen) -> Optional[Tuple[ScheduledBatch, object]]:
@@ -202,6 +205,8 @@ class InferenceEngine:
         sampling = None
         if fused and getattr(chosen, "drawn", False):
             sampling = self.sampler.params(batch.decode_requests, ahead=1)
+            if sampling is None:
+                return None
         out = self.core.step_ahead([r.request_id for r in batch.decode_requests], None if fused else chosen.device_tokens,
                                    greedy=fused, sampling=sampling)
         if out is None:
@@ -213,6 +218,8 @@ class InferenceEngine:
         if fused:
             pending = self.sampler.from_step(out, len(nxt.decode_requests))
             pending.drawn = sampling is not None
+            if sampling is not None:
+                self.sampler.counted(nxt.decode_requests)
             return nxt, pending
         return nxt, self.sampler.launch(out, nxt.decode_requests, ahead=1)
 

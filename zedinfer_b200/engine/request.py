@@ -57,6 +57,9 @@ class InferenceRequest:
         self.output_ids: List[int] = []
         self.phase = RequestPhase.WAITING
         self.prefill_progress = 0            # tokens of `sequence()` that are in the cache
+        # the sampler's record of the request's table of generated tokens on the device: which cache slot it was
+        # (the slot's serial) and how many tokens have been added to it
+        self.count_serial, self.counted = -1, 0
         self.finish_reason: Optional[str] = None
         self.error: Optional[str] = None
         self.cancelled = False

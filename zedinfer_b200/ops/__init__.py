@@ -683,6 +683,41 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: torch.Tensor, t
                    c_int(rows), c_int(logits.shape[1]), c_ll(logits.stride(0)), stream())
 
 
+def penalty_rows(logits: torch.Tensor, counts: torch.Tensor, slots: torch.Tensor, penalty: torch.Tensor) -> None:
+    """The repetition penalty from a table on the device: row r of ``logits`` (float32 ``[rows, vocab]``) is penalised
+    with ``penalty[r]`` once per time that the request in slot ``slots[r]`` has generated a token
+    (``counts`` int32 ``[slots, vocab]``); rows with a negative slot or a penalty of 1 are left alone."""
+    need_cuda(logits, counts, slots, penalty)
+    need_int32("counts", counts), need_int32("slots", slots)
+    rows = logits.shape[0]
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("penalty_rows: logits must be float32 [rows, vocab] with contiguous rows")
+    if counts.dim() != 2 or counts.shape[1] != logits.shape[1] or counts.stride(1) != 1:
+        raise KernelError(f"penalty_rows: counts {tuple(counts.shape)} do not match a vocabulary of {logits.shape[1]}")
+    if penalty.dtype != torch.float32 or penalty.numel() != rows or slots.numel() != rows:
+        raise KernelError("penalty_rows: slots (int32) and penalty (float32) need one entry per row")
+    _sampling.call("zi_penalty_rows", ptr(logits), ptr(counts), ptr(slots), ptr(penalty), c_int(rows), c_int(logits.shape[1]),
+                   c_ll(logits.stride(0)), c_ll(counts.stride(0)), stream())
+
+
+def count_tokens(counts: torch.Tensor, slots: torch.Tensor, tokens: torch.Tensor) -> None:
+    """``counts[slots[r], tokens[r]] += 1`` for the rows whose slot is not negative (each slot at most once)."""
+    need_cuda(counts, slots, tokens)
+    need_int32("counts", counts), need_int32("slots", slots), need_int32("tokens", tokens)
+    if counts.dim() != 2 or counts.stride(1) != 1 or slots.numel() != tokens.numel():
+        raise KernelError("count_tokens: counts [slots, vocab], one slot and one token per row")
+    _sampling.call("zi_count_tokens", ptr(counts), ptr(slots), ptr(tokens), c_int(tokens.numel()), c_int(counts.shape[1]),
+                   c_ll(counts.stride(0)), stream())
+
+
+def count_token_list(counts_row: torch.Tensor, tokens: torch.Tensor) -> None:
+    """``counts_row[t] += 1`` for every listed token (a token listed twice counts twice)."""
+    need_cuda(counts_row, tokens)
+    need_int32("counts_row", counts_row), need_int32("tokens", tokens)
+    need_contiguous("counts_row", counts_row)
+    _sampling.call("zi_count_token_list", ptr(counts_row), ptr(tokens), c_int(tokens.numel()), c_int(counts_row.numel()), stream())
+
+
 def advance_decode(ids: torch.Tensor, pos: torch.Tensor, sampled: torch.Tensor, rows: Optional[int] = None) -> None:
     """Hand the chosen tokens to the next decode step: ``ids := sampled``, ``pos += 1`` for the first ``rows`` rows
     (all of ``ids`` by default).  ``pos`` is one position per token, or ``[axes, tokens]`` for a model whose tokens

@@ -59,10 +59,48 @@ class PendingTokens:
 
 
 class Sampler:
-    def __init__(self, device: torch.device):
+    def __init__(self, device: torch.device, core=None):
+        """``core``: an ``EngineCore`` that keeps a table of generated tokens per request (``count_generated``); the
+        repetition penalty then works from that table on the device and the generated tokens never travel.  Without
+        it the tokens generated so far are sent with every step that penalises them."""
         self.device = device
+        self.core = core if core is not None and getattr(core, "generated_counts", None) is not None else None
         self._pinned: List[torch.Tensor] = []
         self._turn = 0
+
+    # ---- the table of generated tokens ---------------------------------------------------------
+    @staticmethod
+    def _penalised(r) -> bool:
+        return not r.config.use_argmax and r.config.repetition_penalty != 1.0
+
+    def _count_slot(self, r, ahead: int) -> Optional[int]:
+        """The slot of ``r``'s table of generated tokens, brought up to the ``len(r.output_ids) + ahead`` tokens that
+        have been chosen for it; -1 if ``r`` needs none; None if that cannot be done here (no table is kept, or the
+        table is behind while tokens are still on their way to the host)."""
+        if not self._penalised(r):
+            return -1
+        if self.core is None:
+            return None
+        rc = self.core.cache.get(r.request_id)
+        if rc is None or rc.slot < 0:
+            return None
+        if r.count_serial != rc.serial:                # a slot fresh from open(): zero
+            r.count_serial, r.counted = rc.serial, 0
+        expected = len(r.output_ids) + ahead
+        if r.counted != expected:
+            if ahead or r.counted > expected:
+                return None
+            missing = torch.tensor(r.output_ids[r.counted:], dtype=torch.int32).to(self.device, non_blocking=True)
+            ops.count_token_list(self.core.generated_counts[rc.slot], missing)
+            r.counted = expected
+        return rc.slot
+
+    def counted(self, requests: Sequence) -> None:
+        """A step has chosen one more token for each of these requests and added it to their tables."""
+        if self.core is not None:
+            for r in requests:
+                if self._penalised(r):
+                    r.counted += 1
 
     def _host_buffer(self, rows: int) -> torch.Tensor:
         """One of a few pinned buffers, taken in turn (a copy is waited for before its buffer comes round again)."""
@@ -82,25 +120,28 @@ class Sampler:
         event.record()
         return PendingTokens(tokens_and_status[:rows], host, event, rows=rows, chosen_with_step=True)
 
-    @staticmethod
-    def params(requests: Sequence, ahead: int = 0):
-        """The rows' options as arrays: float32 ``[3, rows]`` (temperature, 0 for greedy rows; top_p; the uniform
-        number of this draw) and int32 ``[rows]`` (top_k); None if a row needs a repetition penalty, which works on
-        the logits with the tokens generated so far and is not part of these."""
+    def params(self, requests: Sequence, ahead: int = 0):
+        """The rows' options as arrays: float32 ``[4, rows]`` (temperature, 0 for greedy rows; top_p; the uniform
+        number of this draw; repetition penalty) and int32 ``[2, rows]`` (top_k; the slot of the row's table of
+        generated tokens, -1 where no penalty applies).  None if a row needs a repetition penalty and no table is
+        kept (or it is not up to date): the penalty then works on the logits with the tokens from the host."""
         rows = len(requests)
-        par = np.zeros((3, rows), dtype=np.float32)
+        par = np.zeros((4, rows), dtype=np.float32)
         par[1, :] = 1.0
-        top_k = np.zeros(rows, dtype=np.int32)
+        par[3, :] = 1.0
+        ints = np.zeros((2, rows), dtype=np.int32)
+        ints[1, :] = -1
         for i, r in enumerate(requests):
             c = r.config
             if c.use_argmax:
                 continue
-            if c.repetition_penalty != 1.0:
+            slot = self._count_slot(r, ahead)
+            if slot is None:
                 return None
-            par[0, i], par[1, i] = c.temperature, c.top_p
+            par[0, i], par[1, i], par[3, i] = c.temperature, c.top_p, c.repetition_penalty
             par[2, i] = uniform_for(r.sample_seed, len(r.output_ids) + ahead)
-            top_k[i] = c.top_k
-        return par, top_k
+            ints[0, i], ints[1, i] = c.top_k, slot
+        return par, ints
 
     def sample(self, logits: torch.Tensor, requests: Sequence) -> List[int]:
         """One token per row of ``logits`` (float32 ``[rows, vocab]``); ``requests[i]`` gives row i's options."""
@@ -119,24 +160,37 @@ class Sampler:
         if all(r.config.use_argmax for r in requests):
             ops.argmax(logits, out)
         else:
-            par = np.zeros((4, rows), dtype=np.float32)      # temperature, top_p, uniform, top_k (as int bits)
-            top_k = np.zeros(rows, dtype=np.int32)
-            for i, r in enumerate(requests):
-                c = r.config
-                if c.use_argmax:
-                    par[0, i], par[1, i] = 0.0, 1.0
-                    continue
-                par[0, i], par[1, i] = c.temperature, c.top_p
-                par[2, i] = uniform_for(r.sample_seed, len(r.output_ids) + ahead)
-                top_k[i] = c.top_k
-                if c.repetition_penalty != 1.0 and r.output_ids:
-                    if ahead:
-                        raise ValueError("a repetition penalty needs the tokens of the step before on the host")
-                    recent = torch.tensor(r.output_ids, dtype=torch.int32).to(self.device, non_blocking=True)
-                    ops.repetition_penalty(logits[i], recent, c.repetition_penalty)
-            fl = torch.from_numpy(par[:3].copy()).to(self.device, non_blocking=True)
-            tk = torch.from_numpy(top_k).to(self.device, non_blocking=True)
-            ops.sample(logits, out, fl[0], tk, fl[1], fl[2])
+            sampling = self.params(requests, ahead)
+            if sampling is not None:
+                par, ints = sampling
+                fl = torch.from_numpy(par).to(self.device, non_blocking=True)
+                it = torch.from_numpy(ints).to(self.device, non_blocking=True)
+                if self.core is not None:
+                    ops.penalty_rows(logits, self.core.generated_counts, it[1], fl[3])
+                ops.sample(logits, out, fl[0], it[0], fl[1], fl[2])
+                if self.core is not None:
+                    ops.count_tokens(self.core.generated_counts, it[1], out)
+                    self.counted(requests)
+            else:
+                # no table of generated tokens: they go up with the step
+                par = np.zeros((3, rows), dtype=np.float32)      # temperature, top_p, uniform
+                par[1, :] = 1.0
+                top_k = np.zeros(rows, dtype=np.int32)
+                for i, r in enumerate(requests):
+                    c = r.config
+                    if c.use_argmax:
+                        continue
+                    par[0, i], par[1, i] = c.temperature, c.top_p
+                    par[2, i] = uniform_for(r.sample_seed, len(r.output_ids) + ahead)
+                    top_k[i] = c.top_k
+                    if c.repetition_penalty != 1.0 and r.output_ids:
+                        if ahead:
+                            raise ValueError("a repetition penalty needs the tokens of the step before on the host")
+                        recent = torch.tensor(r.output_ids, dtype=torch.int32).to(self.device, non_blocking=True)
+                        ops.repetition_penalty(logits[i], recent, c.repetition_penalty)
+                fl = torch.from_numpy(par).to(self.device, non_blocking=True)
+                tk = torch.from_numpy(top_k).to(self.device, non_blocking=True)
+                ops.sample(logits, out, fl[0], tk, fl[1], fl[2])
         host = self._host_buffer(rows + 1)
         host[:rows].copy_(out, non_blocking=True)
         host[rows:].copy_(ops.status_word(self.device), non_blocking=True)
