@@ -240,7 +240,7 @@ ZI_EXPORT int zi_count_token_list(int* counts_row, const int* tokens, int n, int
 // the threshold lies are few enough (SAMPLE_LIST), they are gathered into the first block's shared memory and the
 // rest (the exact k-th largest, top-p's running sums by size, the choice by index) is done there on a sorted list.
 // Three sweeps usually get top-k there, two or three get top-p there when a few tokens hold most of the mass.
-// 8 rows of 151,936 entries, a few likely tokens, top-k 20 + top-p 0.8: 39 us (18 sweeps the long way: 98 us).
+// 8 rows of 151,936 entries, a few likely tokens, top-k 20 + top-p 0.8: 36 us (18 sweeps the long way: 98 us).
 //
 // Choice (the long way).  A block's part of the row is cut into 32 stretches, one per warp, lanes on consecutive
 // entries; the blocks' and warps' kept masses locate the stretch that holds u * (kept mass), and that warp walks
@@ -292,12 +292,17 @@ __device__ __forceinline__ void sample_sweep(const float* __restrict__ row, int 
 struct Threshold { unsigned int key; bool exact; };
 template <bool MASS>
 __device__ Threshold find_threshold(cg::cluster_group& cluster, const float* __restrict__ row, int begin, int end,
-                                    float temp, float zmax, float need, unsigned int floor_key, float stop_at, float* acc,
-                                    SampleShare* share, int& turn, volatile unsigned int* s_prefix, volatile float* s_reach) {
+                                    float temp, float zmax, float need, unsigned int floor_key, float stop_at,
+                                    unsigned int kmax, float* acc, SampleShare* share, int& turn,
+                                    volatile unsigned int* s_prefix, volatile float* s_reach) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     unsigned int prefix = 0u;
     float above = 0.0f;                        // weight of the entries above the digits found so far (warp 0 keeps it)
     int top = 32;                              // the lowest bit resolved so far
+    // kmax: the largest key of the row.  The first digit is almost always kmax's own (sign and the upper bits of the
+    // exponent): the search begins below it, and starts over from the top only if kmax's bin alone falls short.
+    bool guessing = kmax != 0u;
+    if (guessing) { top = 32 - SAMPLE_BITS; prefix = kmax >> top << top; }
     while (top > 0) {
         // the digit of this sweep: bits [shift, top), top being the lowest bit resolved so far (the last digit is short)
         const int shift = top >= SAMPLE_BITS ? top - SAMPLE_BITS : 0;
@@ -331,21 +336,30 @@ __device__ Threshold find_threshold(cg::cluster_group& cluster, const float* __r
                 const float up = __shfl_down_sync(0xffffffffu, from_top, o);
                 if (lane + o < 32) from_top += up;
             }
-            // the highest bin that holds something and reaches the need with all above it; if none does (the
-            // whole is short of the need, or rounding), the lowest bin that holds something
-            const unsigned int held = __ballot_sync(0xffffffffu, t > 0.0f);
-            const unsigned int reach = __ballot_sync(0xffffffffu, t > 0.0f && above + from_top >= need);
-            const int digit = reach ? 31 - __clz(reach) : (held ? __ffs(held) - 1 : 0);
-            // entries above the chosen bin stay above for good
-            const float beyond = __shfl_sync(0xffffffffu, from_top - t, digit);
-            const float in_bin = __shfl_sync(0xffffffffu, t, digit);
-            above += digit < 31 ? beyond : 0.0f;
-            if (lane == 0) { *s_prefix = prefix | ((unsigned int)digit << shift); *s_reach = above + in_bin; }
+            const float whole = __shfl_sync(0xffffffffu, from_top, 0);
+            if (guessing && !(whole >= need)) {
+                if (lane == 0) *s_reach = -1.0f;                // the guessed bin does not hold the answer
+            } else {
+                // the highest bin that holds something and reaches the need with all above it; if none does (the
+                // whole is short of the need, or rounding), the lowest bin that holds something
+                const unsigned int held = __ballot_sync(0xffffffffu, t > 0.0f);
+                const unsigned int reach = __ballot_sync(0xffffffffu, t > 0.0f && above + from_top >= need);
+                const int digit = reach ? 31 - __clz(reach) : (held ? __ffs(held) - 1 : 0);
+                // entries above the chosen bin stay above for good
+                const float beyond = __shfl_sync(0xffffffffu, from_top - t, digit);
+                const float in_bin = __shfl_sync(0xffffffffu, t, digit);
+                above += digit < 31 ? beyond : 0.0f;
+                if (lane == 0) { *s_prefix = prefix | ((unsigned int)digit << shift); *s_reach = above + in_bin; }
+            }
         }
         turn ^= 1;
         __syncthreads();
-        prefix = *s_prefix;
         const float reach = *s_reach;
+        if (guessing) {
+            guessing = false;
+            if (reach < 0.0f) { prefix = 0u; top = 32; continue; }       // from the top (above is still 0)
+        }
+        prefix = *s_prefix;
         top = shift;
         if (stop_at > 0.0f) {
             // entries at or above the bin: counted, or (by mass) at most their mass over the least weight an entry
@@ -460,6 +474,7 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
         return;
     }
     const float zmax = top.v / temp;
+    const unsigned int kmax = order_key(top.v);
     float S = 0.0f;                            // total mass: the threads' sums brought to zmax, the blocks' in their order
     if (by_p) {
         s = block_sum(s > 0.0f ? s * expf(m - zmax) : 0.0f, fscratch);
@@ -477,10 +492,10 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
         // the search (for the k-th largest; without top-k, for the entry where top-p's mass is reached) stops as soon
         // as the entries at or above the bin where it lies are sure to fit the list
         const Threshold found = by_k
-            ? find_threshold<false>(cluster, row, cbegin, cend, temp, zmax, (float)k, 0u, (float)SAMPLE_LIST, acc, share,
-                                    turn, &s_prefix, &s_reach)
-            : find_threshold<true>(cluster, row, cbegin, cend, temp, zmax, p * S, 0u, (float)SAMPLE_LIST, acc, share,
-                                   turn, &s_prefix, &s_reach);
+            ? find_threshold<false>(cluster, row, cbegin, cend, temp, zmax, (float)k, 0u, (float)SAMPLE_LIST, kmax, acc,
+                                    share, turn, &s_prefix, &s_reach)
+            : find_threshold<true>(cluster, row, cbegin, cend, temp, zmax, p * S, 0u, (float)SAMPLE_LIST, kmax, acc,
+                                   share, turn, &s_prefix, &s_reach);
         thr_v = found.key;
         listed = by_k || !found.exact;
     }
@@ -573,8 +588,8 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
         // k-th largest, or top-p alone keeps thousands), and thr_v is exact.  The long way.
     }
     if (by_p && by_k) {
-        const unsigned int t = find_threshold<true>(cluster, row, cbegin, cend, temp, zmax, p * S, thr_v, 0.0f, acc, share,
-                                                    turn, &s_prefix, &s_reach).key;
+        const unsigned int t = find_threshold<true>(cluster, row, cbegin, cend, temp, zmax, p * S, thr_v, 0.0f, kmax, acc,
+                                                    share, turn, &s_prefix, &s_reach).key;
         if (t > thr_v) thr_v = t;
     }
     // the kept set in terms of z: everything whose z is at least the z of the threshold's entry
