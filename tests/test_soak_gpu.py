@@ -51,7 +51,8 @@ def test_random_workloads(models, seed):
             else:
                 configs.append(GenerationConfig(max_new_tokens=n, ignore_eos=True, use_argmax=False,
                                                 temperature=rng.choice([0.7, 1.3]), top_k=rng.choice([0, 20]),
-                                                top_p=rng.choice([1.0, 0.9]), seed=rng.randrange(1, 1000)))
+                                                top_p=rng.choice([1.0, 0.9]), seed=rng.randrange(1, 1000),
+                                                repetition_penalty=rng.choice([1.0, 1.0, 1.3, 0.8])))
         outs = []
         for graphs in (True, False):
             sc = SchedulerConfig(num_kv_pages=pages, kv_block_size=page, max_batch_requests=8,
