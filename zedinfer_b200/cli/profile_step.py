@@ -10,8 +10,12 @@ import sys
 
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="zedinfer-profile-step", description=__doc__)
-    p.add_argument("--mode", choices=["decode", "prefill", "mixed"], default="decode",
-                   help="mixed: --batch decoding requests beside a prompt portion of --tokens")
+    p.add_argument("--mode", choices=["decode", "prefill", "mixed", "sample"], default="decode",
+                   help="mixed: --batch decoding requests beside a prompt portion of --tokens; sample: the sampling "
+                        "kernel alone on --batch rows of --vocab logits with a few likely tokens and a long tail")
+    p.add_argument("--temperature", type=float, default=0.7, help="sample: the rows' temperature")
+    p.add_argument("--top-k", type=int, default=20, help="sample: the rows' top-k (0: none)")
+    p.add_argument("--top-p", type=float, default=0.8, help="sample: the rows' top-p (1: none)")
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=3072, help="decode: tokens already cached per request")
     p.add_argument("--tokens", type=int, default=2048, help="prefill: tokens of the portion")
@@ -30,6 +34,8 @@ def main(argv=None) -> int:
     import torch
     from .. import ops
     from ..engine.core import EngineCore, StepEntry
+    if args.mode == "sample":
+        return profile_sampling(args)
     ops.TC_PLAIN_PRODUCTS = bool(args.tcgen05_plain_products)
     cfg = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": args.layers,
            "hidden_size": args.hidden, "num_attention_heads": args.heads, "num_key_value_heads": args.kv_heads,
@@ -76,6 +82,37 @@ def main(argv=None) -> int:
     torch.cuda.profiler.stop()
     print(json.dumps({"mode": args.mode, "batch": args.batch, "layers": args.layers,
                       "ms_per_step": round(a.elapsed_time(b) / args.steps, 4)}))
+    return 0
+
+
+def profile_sampling(args) -> int:
+    """The sampling kernel alone: probability ~ rank^-1.5 with the ranks dealt at random over the vocabulary, the
+    largest logit 20."""
+    import torch
+    from .. import ops
+    dev = torch.device("cuda:0")
+    rows, vocab = args.batch, args.vocab
+    g = torch.Generator().manual_seed(0)
+    rank = torch.stack([torch.randperm(vocab, generator=g) for _ in range(rows)]).float() + 1.0
+    logits = (20.0 - 1.5 * torch.log(rank)).to(dev)
+    out = torch.empty(rows, dtype=torch.int32, device=dev)
+    temp = torch.full((rows,), args.temperature, device=dev)
+    top_k = torch.full((rows,), args.top_k, dtype=torch.int32, device=dev)
+    top_p = torch.full((rows,), args.top_p, device=dev)
+    uni = torch.rand(rows, generator=g).to(dev)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(3):
+        ops.sample(logits, out, temp, top_k, top_p, uni)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    a.record()
+    for _ in range(args.steps):
+        ops.sample(logits, out, temp, top_k, top_p, uni)
+    b.record()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print(json.dumps({"mode": "sample", "rows": rows, "vocab": vocab, "temperature": args.temperature, "top_k": args.top_k,
+                      "top_p": args.top_p, "us_per_call": round(a.elapsed_time(b) * 1000.0 / args.steps, 2)}))
     return 0
 
 

@@ -6,6 +6,8 @@
 //
 // Sampling, following src/frontend/sampler/sampler.cpp:195-265 and :410-490 in meaning:
 //   z_i = logit_i / temperature;  w_i = exp(z_i - max z);  S = sum w
+//     (w_i is computed as 2^((logit_i - max logit) * log2(e) / temperature), see Weigh; which entries equal the
+//     k-th or the last of top-p is still decided on z, the quotient)
 //   top-k keeps the k largest w (entries equal to the k-th largest are all kept);
 //   top-p then keeps the smallest set of largest entries whose mass reaches top_p * S,
 //     mass counted on the un-renormalised w, among the entries top-k kept;
@@ -251,7 +253,7 @@ namespace cg = cooperative_groups;
 #define SAMPLE_UNROLL 8
 #define SAMPLE_BITS 5
 #define SAMPLE_BINS (1 << SAMPLE_BITS)
-#define SAMPLE_WALK_UNROLL 4
+#define SAMPLE_WALK_UNROLL 8
 
 // What a block shows to the others of its cluster.  Two copies used in turn: a block writes copy n + 1 only after
 // the cluster barrier of exchange n + 1's predecessor, which every block passes after it has read copy n.
@@ -264,6 +266,14 @@ struct SampleShare {
 };
 
 __device__ __forceinline__ float sample_nan() { return __int_as_float(0x7fc00000); }
+
+// An entry's weight exp(z - max z), z = logit / temperature, computed as 2^((logit - max logit) * log2(e) / temperature):
+// the same number up to rounding (the difference of the logits is formed first, so near the maximum it is the more
+// accurate of the two), and a sweep over the row pays no division per entry.
+struct Weigh {
+    float vmax, c;                             // c = log2(e) / temperature
+    __device__ __forceinline__ float operator()(float v) const { return exp2f((v - vmax) * c); }
+};
 
 // f(v, i) for every entry of row[begin, end) that is not NaN; consecutive threads on consecutive entries,
 // SAMPLE_UNROLL loads in flight per thread.
@@ -283,7 +293,7 @@ __device__ __forceinline__ void sample_sweep(const float* __restrict__ row, int 
 }
 
 // The largest key t with weight{key >= max(t, floor_key)} >= need, where an entry's weight is 1 (MASS = false:
-// need is a count) or exp(z - zmax) (MASS = true); the smallest such key of the row if all of them together do
+// need is a count) or wt(logit) (MASS = true); the smallest such key of the row if all of them together do
 // not reach it, 0 if there is none.  The answer is the key of an entry of the row.  Every thread of every block of
 // the cluster calls it and gets the same answer.
 // stop_at > 0: the search ends as soon as the digits found so far leave at most stop_at (weight of) entries at or
@@ -292,7 +302,7 @@ __device__ __forceinline__ void sample_sweep(const float* __restrict__ row, int 
 struct Threshold { unsigned int key; bool exact; };
 template <bool MASS>
 __device__ Threshold find_threshold(cg::cluster_group& cluster, const float* __restrict__ row, int begin, int end,
-                                    float temp, float zmax, float need, unsigned int floor_key, float stop_at,
+                                    const Weigh wt, float need, unsigned int floor_key, float stop_at,
                                     unsigned int kmax, float* acc, SampleShare* share, int& turn,
                                     volatile unsigned int* s_prefix, volatile float* s_reach) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -314,7 +324,7 @@ __device__ Threshold find_threshold(cg::cluster_group& cluster, const float* __r
             if (key < floor_key) return;
             if (top < 32 && (key >> top) != (prefix >> top)) return;
             const unsigned int d = (key >> shift) & digit_mask;
-            acc[d * SAMPLE_THREADS + threadIdx.x] += MASS ? expf(v / temp - zmax) : 1.0f;
+            acc[d * SAMPLE_THREADS + threadIdx.x] += MASS ? wt(v) : 1.0f;
         });
         __syncthreads();
         {   // this block's total of bin `warp`: its columns in lane-strided order, then a fixed tree over the lanes
@@ -364,7 +374,7 @@ __device__ Threshold find_threshold(cg::cluster_group& cluster, const float* __r
         if (stop_at > 0.0f) {
             // entries at or above the bin: counted, or (by mass) at most their mass over the least weight an entry
             // there can have, with a margin for rounding
-            const float entries = MASS ? 1.02f * reach / expf(key_value(prefix) / temp - zmax) : reach;
+            const float entries = MASS ? 1.02f * reach / wt(key_value(prefix)) : reach;
             if (entries <= stop_at) break;
         }
     }
@@ -385,13 +395,11 @@ __device__ Threshold find_threshold(cg::cluster_group& cluster, const float* __r
 __device__ void sort_ascending(unsigned long long* a, int n2) {
     for (int k = 2; k <= n2; k <<= 1) {
         for (int j = k >> 1; j > 0; j >>= 1) {
-            for (int t = threadIdx.x; t < n2; t += SAMPLE_THREADS) {
-                const int o = t ^ j;
-                if (o > t) {
-                    const unsigned long long x = a[t], y = a[o];
-                    const bool up = (t & k) == 0;
-                    if ((x > y) == up) { a[t] = y; a[o] = x; }
-                }
+            for (int pair = threadIdx.x; pair < (n2 >> 1); pair += SAMPLE_THREADS) {
+                const int t = ((pair & ~(j - 1)) << 1) | (pair & (j - 1)), o = t | j;      // the pair's lower and upper place
+                const unsigned long long x = a[t], y = a[o];
+                const bool up = (t & k) == 0;
+                if ((x > y) == up) { a[t] = y; a[o] = x; }
             }
             __syncthreads();
         }
@@ -447,19 +455,33 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
     const int cbegin = min(vocab, rank * per * 32), cend = min(vocab, cbegin + per * 32);
     int turn = 0;
 
-    // One sweep for the largest entry of the row and, where top-p wants it, the total mass: every thread keeps the
-    // mass of its entries relative to the largest z it has met, and rescales when it meets a larger one.
+    // One sweep for the largest entry of the row and the mass of every warp's stretch (each warp walks its stretch,
+    // lanes on consecutive entries, SAMPLE_UNROLL loads in flight per lane): a lane keeps the mass of its entries
+    // relative to the largest z it has met, and rescales when it meets a larger one.  The masses give top-p its total;
+    // with neither top-k nor top-p at work they are the kept masses already, and the row is not swept again.
+    const int begin = min(cend, cbegin + warp * per), end = min(cend, begin + per);
+    const bool whole = sampled && !by_k && !by_p;              // everything is kept
     ArgPair top; top.v = -INFINITY; top.i = 0x7fffffff;
-    float m = -INFINITY, s = 0.0f;
-    sample_sweep(row, cbegin, cend, [&](float v, int i) {
-        ArgPair c; c.v = v; c.i = i;
-        top = better(top, c);
-        if (by_p) {
-            const float z = v / temp;
-            if (z > m) { s = s * expf(m - z) + 1.0f; m = z; }
-            else if (z > -INFINITY) s += expf(z - m);
+    float m = -INFINITY, s = 0.0f;                             // the lane's largest logit, its mass relative to that
+    const float wc = sampled ? 1.4426950408889634f / temp : 0.0f;
+    for (int base = begin; base < end; base += 32 * SAMPLE_UNROLL) {
+        float v[SAMPLE_UNROLL];
+#pragma unroll
+        for (int j = 0; j < SAMPLE_UNROLL; ++j) {
+            const int i = base + j * 32 + lane;
+            v[j] = i < end ? row[i] : sample_nan();
         }
-    });
+#pragma unroll
+        for (int j = 0; j < SAMPLE_UNROLL; ++j) {
+            if (v[j] != v[j]) continue;
+            ArgPair c; c.v = v[j]; c.i = base + j * 32 + lane;
+            top = better(top, c);
+            if (by_p || whole) {
+                if (v[j] > m) { s = s * exp2f((m - v[j]) * wc) + 1.0f; m = v[j]; }
+                else if (v[j] > -INFINITY) s += exp2f((v[j] - m) * wc);
+            }
+        }
+    }
     top = block_best(top, ascratch);
     if (threadIdx.x == 0) share[turn].best = top;
     cluster.sync();
@@ -473,15 +495,25 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
         cluster.sync();                        // nobody leaves while its memory is still read
         return;
     }
-    const float zmax = top.v / temp;
+    Weigh wt; wt.vmax = top.v; wt.c = wc;
     const unsigned int kmax = order_key(top.v);
-    float S = 0.0f;                            // total mass: the threads' sums brought to zmax, the blocks' in their order
+    float S = 0.0f;                            // total mass: the lanes' sums brought to the row's largest logit, stretches and blocks in their order
+    if (by_p || whole) {
+        float mine = s > 0.0f ? s * wt(m) : 0.0f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+        if (lane == 0) warp_mass[warp] = mine;
+        __syncthreads();
+    }
     if (by_p) {
-        s = block_sum(s > 0.0f ? s * expf(m - zmax) : 0.0f, fscratch);
-        if (threadIdx.x == 0) share[turn].sum = s;
+        if (threadIdx.x == 0) {
+            float mass = 0.0f;
+            for (int w = 0; w < 32; ++w) mass += warp_mass[w];
+            share[turn].sum = mass;
+        }
         cluster.sync();
-    #pragma unroll
-    for (int c = 0; c < SAMPLE_CLUSTER; ++c) S += cluster.map_shared_rank(&share[turn], c)->sum;
+#pragma unroll
+        for (int c = 0; c < SAMPLE_CLUSTER; ++c) S += cluster.map_shared_rank(&share[turn], c)->sum;
         turn ^= 1;
     }
 
@@ -492,9 +524,9 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
         // the search (for the k-th largest; without top-k, for the entry where top-p's mass is reached) stops as soon
         // as the entries at or above the bin where it lies are sure to fit the list
         const Threshold found = by_k
-            ? find_threshold<false>(cluster, row, cbegin, cend, temp, zmax, (float)k, 0u, (float)SAMPLE_LIST, kmax, acc,
+            ? find_threshold<false>(cluster, row, cbegin, cend, wt, (float)k, 0u, (float)SAMPLE_LIST, kmax, acc,
                                     share, turn, &s_prefix, &s_reach)
-            : find_threshold<true>(cluster, row, cbegin, cend, temp, zmax, p * S, 0u, (float)SAMPLE_LIST, kmax, acc,
+            : find_threshold<true>(cluster, row, cbegin, cend, wt, p * S, 0u, (float)SAMPLE_LIST, kmax, acc,
                                    share, turn, &s_prefix, &s_reach);
         thr_v = found.key;
         listed = by_k || !found.exact;
@@ -541,8 +573,8 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
                 if (by_k && n > 0) thr_v = (unsigned int)(~list[min(k, n) - 1] >> 32);
                 if (by_p) {
                     float w0 = 0.0f, w1 = 0.0f;
-                    if (e0 < n) { const unsigned int key = (unsigned int)(~list[e0] >> 32); if (key >= thr_v) w0 = expf(key_value(key) / temp - zmax); }
-                    if (e1 < n) { const unsigned int key = (unsigned int)(~list[e1] >> 32); if (key >= thr_v) w1 = expf(key_value(key) / temp - zmax); }
+                    if (e0 < n) { const unsigned int key = (unsigned int)(~list[e0] >> 32); if (key >= thr_v) w0 = wt(key_value(key)); }
+                    if (e1 < n) { const unsigned int key = (unsigned int)(~list[e1] >> 32); if (key >= thr_v) w1 = wt(key_value(key)); }
                     float all;
                     const float before0 = running_sum_before(w0, w1, fscratch, &all);
                     if (threadIdx.x == 0) s_first = 0x7fffffff;
@@ -553,19 +585,26 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
                     __syncthreads();
                     if (s_first < n) thr_v = (unsigned int)(~list[s_first] >> 32);      // never below the k-th largest
                 }
+                // the kept set in terms of z, as on the long way; in this order it is the list's first `kept` entries
+                const unsigned int thr = order_key(key_value(thr_v) / temp);
+                if (threadIdx.x == 0) s_last = -1;
                 __syncthreads();
-                // back to (index, key) for the order of the indices
-                for (int t = threadIdx.x; t < n2; t += SAMPLE_THREADS) {
+                if (e1 < n && order_key(key_value((unsigned int)(~list[e1] >> 32)) / temp) >= thr) atomicMax(&s_last, e1);
+                else if (e0 < n && order_key(key_value((unsigned int)(~list[e0] >> 32)) / temp) >= thr) atomicMax(&s_last, e0);
+                __syncthreads();
+                const int kept = s_last + 1;
+                int k2 = 2;
+                while (k2 < kept) k2 <<= 1;
+                // those back to (index, key), in the order of the indices
+                for (int t = threadIdx.x; t < k2; t += SAMPLE_THREADS) {
                     const unsigned long long e = ~list[t];
-                    list[t] = t < n ? (((0xffffffffull - (e & 0xffffffffull)) << 32) | (e >> 32)) : ~0ull;
+                    list[t] = t < kept ? (((0xffffffffull - (e & 0xffffffffull)) << 32) | (e >> 32)) : ~0ull;
                 }
                 __syncthreads();
-                sort_ascending(list, n2);
-                // the kept set in terms of z, as on the long way
-                const unsigned int thr = order_key(key_value(thr_v) / temp);
+                sort_ascending(list, k2);
                 float w0 = 0.0f, w1 = 0.0f;
-                if (e0 < n) { const float z = key_value((unsigned int)list[e0]) / temp; if (order_key(z) >= thr) w0 = expf(z - zmax); }
-                if (e1 < n) { const float z = key_value((unsigned int)list[e1]) / temp; if (order_key(z) >= thr) w1 = expf(z - zmax); }
+                if (e0 < kept) w0 = wt(key_value((unsigned int)list[e0]));
+                if (e1 < kept) w1 = wt(key_value((unsigned int)list[e1]));
                 float total;
                 const float before0 = running_sum_before(w0, w1, fscratch, &total);
                 if (threadIdx.x == 0) { s_first = 0x7fffffff; s_last = -1; }
@@ -577,7 +616,7 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
                 else if (w0 > 0.0f) atomicMax(&s_last, e0);
                 __syncthreads();
                 if (threadIdx.x == 0) {
-                    const int at = s_first < n ? s_first : s_last;                  // rounding overshoot: the last kept entry
+                    const int at = s_first < kept ? s_first : s_last;               // rounding overshoot: the last kept entry
                     out[r] = at >= 0 ? (int)(list[at] >> 32) : top.i;
                 }
             }
@@ -588,18 +627,29 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
         // k-th largest, or top-p alone keeps thousands), and thr_v is exact.  The long way.
     }
     if (by_p && by_k) {
-        const unsigned int t = find_threshold<true>(cluster, row, cbegin, cend, temp, zmax, p * S, thr_v, 0.0f, kmax, acc,
+        const unsigned int t = find_threshold<true>(cluster, row, cbegin, cend, wt, p * S, thr_v, 0.0f, kmax, acc,
                                                     share, turn, &s_prefix, &s_reach).key;
         if (t > thr_v) thr_v = t;
     }
-    // the kept set in terms of z: everything whose z is at least the z of the threshold's entry
-    unsigned int thr = 0u;
-    if (thr_v != 0u) thr = order_key(key_value(thr_v) / temp);
+    // the kept set in terms of z: everything whose z is at least the z of the threshold's entry.  z grows with the
+    // logit, so that is everything from some logit on: `cut`, found by stepping down from the threshold's logit while
+    // the quotient stays the same (a step or two; with a temperature so large that 64 steps do not reach the end,
+    // every entry is divided and compared instead).
+    unsigned int thr = 0u, cut = 0u;
+    bool by_cut = true;
+    if (thr_v != 0u) {
+        thr = order_key(key_value(thr_v) / temp);
+        cut = thr_v;
+        for (int step = 0; cut > 1u && order_key(key_value(cut - 1u) / temp) >= thr; ++step) {
+            if (step == 64) { by_cut = false; break; }
+            --cut;
+        }
+    }
+    auto is_kept = [&](float v) { return v == v && (by_cut ? order_key(v) >= cut : order_key(v / temp) >= thr); };
 
-    // kept mass of each warp's stretch, SAMPLE_UNROLL loads in flight per lane
-    const int begin = min(cend, cbegin + warp * per), end = min(cend, begin + per);
+    // kept mass of each warp's stretch (known already where everything is kept)
     float mine = 0.0f;
-    for (int base = begin; base < end; base += 32 * SAMPLE_UNROLL) {
+    for (int base = begin; base < end && !whole; base += 32 * SAMPLE_UNROLL) {
         float v[SAMPLE_UNROLL];
 #pragma unroll
         for (int j = 0; j < SAMPLE_UNROLL; ++j) {
@@ -607,14 +657,12 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
             v[j] = i < end ? row[i] : sample_nan();
         }
 #pragma unroll
-        for (int j = 0; j < SAMPLE_UNROLL; ++j) {
-            const float z = v[j] / temp;
-            if (z == z && order_key(z) >= thr) mine += expf(z - zmax);
-        }
+        for (int j = 0; j < SAMPLE_UNROLL; ++j)
+            if (is_kept(v[j])) mine += wt(v[j]);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
-    if (lane == 0) warp_mass[warp] = mine;
+    if (lane == 0 && !whole) warp_mass[warp] = mine;
     __syncthreads();
     if (threadIdx.x == 0) {
         float mass = 0.0f;
@@ -654,35 +702,47 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
     }
     __syncthreads();
     if (warp == s_owner) {
-        // this warp's stretch in index order, 32 entries at a time
+        // This warp's stretch in index order, SAMPLE_WALK_UNROLL runs of 32 entries at a time: their weights and the
+        // runs' masses first (independent of one another), then the runs in order until the running sum passes the
+        // target, and a prefix sum over the lanes of that run alone.
         float run = s_run;
         const float target = s_target;
         int pick = -1, last_kept = -1;
         for (int base = begin; base < end && pick < 0; base += 32 * SAMPLE_WALK_UNROLL) {
-            float v[SAMPLE_WALK_UNROLL];
+            float w[SAMPLE_WALK_UNROLL], mass[SAMPLE_WALK_UNROLL];
 #pragma unroll
             for (int j = 0; j < SAMPLE_WALK_UNROLL; ++j) {
                 const int i = base + j * 32 + lane;
-                v[j] = i < end ? row[i] : sample_nan();
+                w[j] = i < end ? row[i] : sample_nan();
             }
 #pragma unroll
             for (int j = 0; j < SAMPLE_WALK_UNROLL; ++j) {
-                const float z = v[j] / temp;
-                float w = 0.0f;
-                if (z == z && order_key(z) >= thr) w = expf(z - zmax);
-                float incl = w;                                 // inclusive prefix sum over the lanes
+                w[j] = is_kept(w[j]) ? wt(w[j]) : 0.0f;
+                mass[j] = w[j];
+            }
 #pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const float up = __shfl_up_sync(0xffffffffu, incl, o);
-                    if (lane >= o) incl += up;
+            for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+                for (int j = 0; j < SAMPLE_WALK_UNROLL; ++j) mass[j] += __shfl_xor_sync(0xffffffffu, mass[j], o);
+            }
+#pragma unroll
+            for (int j = 0; j < SAMPLE_WALK_UNROLL; ++j) {
+                if (pick >= 0 || !(mass[j] > 0.0f)) continue;                      // the same in every lane
+                const unsigned int kept = __ballot_sync(0xffffffffu, w[j] > 0.0f);
+                if (target < run + mass[j]) {
+                    float incl = w[j];                          // inclusive prefix sum over the lanes
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const float up = __shfl_up_sync(0xffffffffu, incl, o);
+                        if (lane >= o) incl += up;
+                    }
+                    const unsigned int hit = __ballot_sync(0xffffffffu, w[j] > 0.0f && target < run + incl);
+                    // rounding (the run's mass was added in another order): the run's last kept entry
+                    pick = base + j * 32 + (hit ? __ffs(hit) - 1 : 31 - __clz(kept));
+                } else {
+                    last_kept = base + j * 32 + (31 - __clz(kept));
+                    run += mass[j];
                 }
-                const unsigned int hit = __ballot_sync(0xffffffffu, w > 0.0f && target < run + incl);
-                const unsigned int kept = __ballot_sync(0xffffffffu, w > 0.0f);
-                if (pick < 0) {
-                    if (hit) pick = base + j * 32 + (__ffs(hit) - 1);
-                    else if (kept) last_kept = base + j * 32 + (31 - __clz(kept));
-                }
-                run += __shfl_sync(0xffffffffu, incl, 31);
             }
         }
         if (pick < 0) pick = last_kept;                         // rounding overshoot: the stretch's last kept entry
