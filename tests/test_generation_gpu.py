@@ -390,6 +390,19 @@ def test_a_capture_survives_the_collection_of_an_engine_that_is_gone(models):
         gc.enable()
 
 
+def test_profile_step_runs_a_small_step_of_each_kind(capsys):
+    """The program that stands between cudaProfilerStart and Stop for the ncu captures: every mode at a small size."""
+    from zedinfer_b200.cli import profile_step
+    small = ["--layers", "2", "--hidden", "256", "--heads", "4", "--kv-heads", "2", "--head-dim", "64",
+             "--intermediate", "512", "--vocab", "3000", "--steps", "1"]
+    for mode, more in (("decode", ["--batch", "3", "--context", "40"]), ("decode", ["--batch", "3", "--context", "40", "--graphs"]),
+                       ("prefill", ["--tokens", "70"]), ("mixed", ["--batch", "2", "--context", "30", "--tokens", "50"]),
+                       ("sample", ["--batch", "3"])):
+        assert profile_step.main(["--mode", mode] + more + small) == 0
+        line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+        assert line["mode"] == mode and (line.get("ms_per_step", 0) > 0 or line.get("us_per_call", 0) > 0)
+
+
 def test_engine_default_sampling_comes_from_generation_config_json(models, tmp_path, monkeypatch):
     """A folder whose generation_config.json says do_sample: a request without sampling options is sampled with the
     folder's values (same tokens as a request that states them), ZEDINFER_FORCE_ARGMAX brings greedy back, and a
