@@ -51,6 +51,37 @@ def test_prompt_is_cut_into_portions_and_blocks_the_queue():
     assert a.output_ids == [7, 7] and b.output_ids == [7]
 
 
+def test_admission_fills_every_free_place_and_never_more():
+    """max_batch_requests counts live requests once: a step admits as many short prompts as there are free places
+    (the reference counts those whose prompt ends in the step twice and admits half of them), a request in
+    mid-prompt takes the last place, and nobody is admitted beyond the limit."""
+    s, cache = make(pages=256, max_batch_requests=6, max_batch_tokens=64, max_prefill_tokens=64)
+    rs = [req(3, max_new=50) for _ in range(5)] + [req(40, max_new=50)] + [req(3, max_new=50) for _ in range(3)]
+    for r in rs:
+        s.submit(r)
+    batch, _ = run_step(s, cache)
+    assert batch.prefill_requests == rs[:6] and batch.prefill_chunk_sizes == [3] * 5 + [40]
+    assert len(s.active) == 6
+    batch, _ = run_step(s, cache)
+    assert batch.decode_requests == rs[:6] and batch.prefill_requests == [] and len(s.waiting) == 3
+    s.cancel(rs[0])
+    batch, _ = run_step(s, cache)                       # one place is free again: one more comes in
+    assert batch.prefill_requests == [rs[6]] and len(s.active) == 6 and len(s.waiting) == 2
+    # a long prompt takes the last place while it is still in portions
+    s2, cache2 = make(pages=256, max_batch_requests=2, max_batch_tokens=16, max_prefill_tokens=16)
+    a, b, c = req(3, max_new=50), req(30, max_new=50), req(3, max_new=50)
+    for r in (a, b, c):
+        s2.submit(r)
+    batch, _ = run_step(s2, cache2)
+    assert batch.prefill_requests == [a, b] and batch.prefill_chunk_sizes == [3, 13]
+    batch, _ = run_step(s2, cache2)
+    assert batch.decode_requests == [a] and batch.prefill_requests == [b] and batch.prefill_chunk_sizes == [15]
+    batch, _ = run_step(s2, cache2)
+    assert batch.prefill_requests == [b] and batch.prefill_chunk_sizes == [2] and len(s2.active) == 2
+    batch, _ = run_step(s2, cache2)
+    assert batch.decode_requests == [a, b] and batch.prefill_requests == [] and list(s2.waiting) == [c]
+
+
 def test_token_budget_covers_decode_and_prefill():
     s, cache = make(max_batch_tokens=6, max_prefill_tokens=512)
     rs = [req(3, max_new=50) for _ in range(4)]

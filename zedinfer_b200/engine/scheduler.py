@@ -180,7 +180,10 @@ class Scheduler:
                     self.waiting.popleft()
                     self._complete(req, "cancelled")
                     continue
-                if len(self.active) + len(batch.prefill_requests) >= self.config.max_batch_requests:
+                # Requests whose prompt ends in this step are in ``active`` already.  (The reference adds the step's
+                # prompt portions to that number once more, src/zedinfer/scheduler.cpp:338-341, and so admits half of
+                # the free places per step; the limit means the same here, the queue just empties sooner.)
+                if len(self.active) >= self.config.max_batch_requests:
                     break
                 if req.cache is None:
                     if not self.can_admit(req):
