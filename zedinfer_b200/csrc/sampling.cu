@@ -94,12 +94,32 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
 // (value, index), and one warp per row takes the best of those, the lowest index among equals as before.
 #define ARGMAX_SLICE 4096
 #define ARGMAX_MAX_SLICES 32
-__global__ void __launch_bounds__(SAMPLE_THREADS)
+#define ARGMAX_THREADS 512
+#define ARGMAX_UNROLL 8
+__global__ void __launch_bounds__(ARGMAX_THREADS)
 argmax_slices_kernel(const float* __restrict__ logits, ArgPair* __restrict__ part, int vocab, long long row_stride, int slices) {
     __shared__ ArgPair scratch[32];
     const int per = (vocab + slices - 1) / slices;
     const int begin = blockIdx.y * per, end = min(vocab, begin + per);
-    const ArgPair r = block_argmax(logits + (size_t)blockIdx.x * row_stride, begin, end, scratch);
+    const float* row = logits + (size_t)blockIdx.x * row_stride;
+    // a slice of 4,096 entries is one round of eight loads per thread, all of them in flight together
+    ArgPair best; best.v = -INFINITY; best.i = 0x7fffffff;
+    for (int base = begin; base < end; base += ARGMAX_THREADS * ARGMAX_UNROLL) {
+        float v[ARGMAX_UNROLL];
+#pragma unroll
+        for (int j = 0; j < ARGMAX_UNROLL; ++j) {
+            const int i = base + j * ARGMAX_THREADS + (int)threadIdx.x;
+            v[j] = i < end ? row[i] : -INFINITY;
+        }
+#pragma unroll
+        for (int j = 0; j < ARGMAX_UNROLL; ++j) {
+            const int i = base + j * ARGMAX_THREADS + (int)threadIdx.x;
+            if (i >= end) continue;
+            ArgPair c; c.v = v[j] != v[j] ? -INFINITY : v[j]; c.i = i;
+            best = better(best, c);
+        }
+    }
+    const ArgPair r = block_best(best, scratch);
     if (threadIdx.x == 0) part[(size_t)blockIdx.x * slices + blockIdx.y] = r;
 }
 __global__ void argmax_merge_kernel(const ArgPair* __restrict__ part, int* __restrict__ out, int slices) {
@@ -130,7 +150,7 @@ ZI_EXPORT int zi_argmax(const float* logits, int* out, int rows, int vocab, long
         return zi_check_launch("argmax");
     }
     if (rows > 65535) return zi_fail("argmax: %d rows are more than one launch takes", rows);
-    argmax_slices_kernel<<<dim3(rows, slices), SAMPLE_THREADS, 0, stream>>>(logits, (ArgPair*)part, vocab, row_stride, slices);
+    argmax_slices_kernel<<<dim3(rows, slices), ARGMAX_THREADS, 0, stream>>>(logits, (ArgPair*)part, vocab, row_stride, slices);
     argmax_merge_kernel<<<rows, 32, 0, stream>>>((const ArgPair*)part, out, slices);
     return zi_check_launch("argmax");
 }
