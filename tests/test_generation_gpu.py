@@ -390,6 +390,39 @@ def test_a_capture_survives_the_collection_of_an_engine_that_is_gone(models):
         gc.enable()
 
 
+def test_generation_across_the_length_where_the_decode_graph_changes(tmp_path):
+    """Requests that decode from below to above the context length from which the captured decode step plans for
+    clusters that share a request: the engine, running ahead of the host, moves from one captured graph to the other
+    (greedy and sampled rows), and the tokens are those of the engine without graphs."""
+    from zedinfer_b200 import GenerationConfig, InferenceRequest, SchedulerConfig, ops
+    from zedinfer_b200.engine import InferenceEngine
+    edge = ops.decode_attention_split_from()
+    cfg = dict(tiny.TINY_E, max_position_embeddings=edge + 200)
+    path = tmp_path / "config.json"
+    path.write_text(json.dumps(cfg))
+    rng = random.Random(11)
+    prompts = [[rng.randrange(cfg["vocab_size"]) for _ in range(n)] for n in (edge - 20, 50, edge - 33)]
+    configs = [GenerationConfig(max_new_tokens=45, ignore_eos=True),
+               GenerationConfig(max_new_tokens=45, ignore_eos=True),
+               GenerationConfig(max_new_tokens=60, use_argmax=False, temperature=0.8, top_k=30, repetition_penalty=1.2, seed=4, ignore_eos=True)]
+
+    def run(graphs):
+        sc = SchedulerConfig(num_kv_pages=(2 * edge + 600) // 16, kv_block_size=16, max_batch_requests=4, max_prefill_tokens=2048,
+                             max_batch_tokens=4096, cuda_graphs=graphs, run_ahead=graphs)
+        engine = InferenceEngine.create(str(path), sc, dtype="bfloat16", random_seed=9)
+        futures = [engine.submit_async(InferenceRequest(p, c)) for p, c in zip(prompts, configs)]
+        engine.run_loop()
+        return [f.result() for f in futures], engine
+
+    base, _ = run(False)
+    got, engine = run(True)
+    assert all(r.error is None for r in base + got)
+    for a, b in zip(base, got):
+        assert a.output_ids == b.output_ids
+    reaches = {key[2] for key in engine.core._decode_graphs}
+    assert reaches == {edge - 1, edge + 200} and engine.steps_run_ahead > 20
+
+
 def test_profile_step_runs_a_small_step_of_each_kind(capsys):
     """The program that stands between cudaProfilerStart and Stop for the ncu captures: every mode at a small size."""
     from zedinfer_b200.cli import profile_step
