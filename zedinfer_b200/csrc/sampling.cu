@@ -578,7 +578,10 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
             unsigned long long* list0 = cluster.map_shared_rank(list, 0);
             for (int e = threadIdx.x; e < s_count; e += SAMPLE_THREADS) list0[before + e] = local[e];
             cluster.sync();
-            if (rank == 0) {
+            // From here on nobody reads another block's memory: the others leave (and make room for the next rows'
+            // blocks) while the first finishes the row.
+            if (rank != 0) return;
+            {
                 int n2 = 2;
                 while (n2 < n) n2 <<= 1;
                 const int e0 = 2 * threadIdx.x, e1 = e0 + 1;           // this thread's two places in the sorted orders
@@ -640,7 +643,6 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
                     out[r] = at >= 0 ? (int)(list[at] >> 32) : top.i;
                 }
             }
-            cluster.sync();                    // nobody leaves while its memory is still read
             return;
         }
         // too many for the list: the search ran to its end without the kept set getting small (thousands tie with the
@@ -720,7 +722,7 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
         if (owner_block < 0 && rank == 0) out[r] = top.i;      // nothing kept anywhere: the most probable token
         s_owner = owner; s_run = run; s_target = target;
     }
-    __syncthreads();
+    cluster.sync();                            // every block has read the others' masses: nobody's memory is read from here on
     if (warp == s_owner) {
         // This warp's stretch in index order, SAMPLE_WALK_UNROLL runs of 32 entries at a time: their weights and the
         // runs' masses first (independent of one another), then the runs in order until the running sum passes the
@@ -768,7 +770,6 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
         if (pick < 0) pick = last_kept;                         // rounding overshoot: the stretch's last kept entry
         if (lane == 0) out[r] = pick >= 0 ? pick : top.i;
     }
-    cluster.sync();                            // nobody leaves while its memory is still read
 }
 
 ZI_EXPORT int zi_sample(const float* logits, int* out, const float* temperature, const int* top_k, const float* top_p,
