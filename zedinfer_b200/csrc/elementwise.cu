@@ -44,6 +44,10 @@ ZI_EXPORT int zi_embedding(const void* table, int table_dtype, const int* ids, v
 // width alone.
 // ---------------------------------------------------------------------------------------
 #define NORM_THREADS 256
+// Up to this many rows (decode steps) a norm asks for its weight together with the row instead of after the sum: one
+// trip to memory less in a kernel that is nothing else (20 us of a 28-layer step of 1.36 ms).  With many rows the
+// extra registers cost more than the trip.
+#define NORM_FEW_ROWS 64
 #ifndef NORM_KEEP_ROWS
 #define NORM_KEEP_ROWS 256
 #endif
@@ -107,13 +111,42 @@ rmsnorm_vec8_kernel(float* __restrict__ residual, const TD* __restrict__ delta, 
     const size_t src = row_idx ? (size_t)row_idx[r] : (size_t)r;
     float* res = residual + src * hidden;
     const TD* d = delta ? delta + src * hidden : nullptr;
-    const bool wb = d && write_residual && !row_idx;
+    const bool wb = d && (write_residual & 1) && !row_idx;
     // Many rows (a prompt portion): the residual stream is read again by the next norm, some 80 us and 150 MB of
     // other traffic later; it asks L2 to let go of it last.
     const bool keep = gridDim.x >= NORM_KEEP_ROWS;
     uint64_t policy = 0;
     if (keep) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;\n" : "=l"(policy));
     float ss = 0.0f;
+    if ((write_residual & 2) && hidden <= NORM_THREADS * 8) {
+        // Few rows (a decode step), one piece of the row per thread: the weight is asked for together with the row,
+        // not after the sum (one trip to memory instead of two in a kernel that is nothing but trips to memory).
+        const int j = threadIdx.x * 8;
+        float x[8], wv[8];
+        const bool mine = j < hidden;
+        if (mine) {
+            load8(res + j, x);
+            load8(w + j, wv);
+            if (d) {
+                float dv[8];
+                load8(d + j, dv);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[i] = x[i] + dv[i];
+                if (wb) store8(res + j, x);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
+        }
+        ss = block_sum(ss, scratch);
+        pdl_trigger_late();
+        const float rstd = 1.0f / sqrtf(ss / (float)hidden + eps);
+        if (mine) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = (wv[i] * x[i]) * rstd;
+            store8(out + (size_t)r * hidden + j, x);
+        }
+        return;
+    }
     for (int j = threadIdx.x * 8; j < hidden; j += NORM_THREADS * 8) {
         float x[8];
         if (keep) load8_hint(res + j, x, policy); else load8(res + j, x);
@@ -156,8 +189,42 @@ rmsnorm_parts_vec8_kernel(float* __restrict__ residual, const float* __restrict_
     const size_t src = row_idx ? (size_t)row_idx[r] : (size_t)r;
     float* res = residual + src * hidden;
     const float* d = parts + src * hidden;
-    const bool wb = write_residual && !row_idx;
+    const bool wb = (write_residual & 1) && !row_idx;
     float ss = 0.0f;
+    if ((write_residual & 2) && hidden <= NORM_THREADS * 8 && n_parts <= 4) {
+        // Few rows, one piece of the row per thread: the row, every partial sum and the weight are asked for
+        // together (one trip to memory; the loop below makes one per partial sum and one more for the weight).
+        const int j = threadIdx.x * 8;
+        float x[8], wv[8], dv[4][8];
+        const bool mine = j < hidden;
+        if (mine) {
+            load8(res + j, x);
+            load8(w + j, wv);
+#pragma unroll
+            for (int p = 0; p < 4; ++p)
+                if (p < n_parts) load8(d + (size_t)p * part_stride + j, dv[p]);
+#pragma unroll
+            for (int p = 1; p < 4; ++p) {
+                if (p < n_parts) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) dv[0][i] += dv[p][i];
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = x[i] + to_f32<TO>(from_f32<TO>(dv[0][i]));
+            if (wb) store8(res + j, x);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
+        }
+        ss = block_sum(ss, scratch);
+        const float rstd = 1.0f / sqrtf(ss / (float)hidden + eps);
+        if (mine) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = (wv[i] * x[i]) * rstd;
+            store8(out + (size_t)r * hidden + j, x);
+        }
+        return;
+    }
     for (int j = threadIdx.x * 8; j < hidden; j += NORM_THREADS * 8) {
         float x[8], dv[8];
         load8(res + j, x);
@@ -233,7 +300,7 @@ ZI_EXPORT int zi_add_rmsnorm(void* residual, const void* delta, int delta_dtype,
         auto fn = vec ? rmsnorm_vec8_kernel<TD, TW, TO> : rmsnorm_kernel<TD, TW, TO>;
         if (norm_smem_ok(hidden, (const void*)fn)) return 1;
         zi_launch(fn, dim3(rows), dim3(NORM_THREADS), smem, stream, (float*)residual, (const TD*)delta, (const TW*)w,
-                  (TO*)out, row_idx, eps, hidden, write_residual);
+                  (TO*)out, row_idx, eps, hidden, (write_residual ? 1 : 0) | ((vec && rows <= NORM_FEW_ROWS) ? 2 : 0));
     });););
     return zi_check_launch("add_rmsnorm");
 }
@@ -252,7 +319,7 @@ ZI_EXPORT int zi_add_rmsnorm_parts(void* residual, const float* parts, int n_par
         auto fn = rmsnorm_parts_vec8_kernel<TW, TO>;
         if (norm_smem_ok(hidden, (const void*)fn)) return 1;
         fn<<<rows, NORM_THREADS, smem, stream>>>((float*)residual, parts, n_parts, part_stride, (const TW*)w, (TO*)out, row_idx,
-                                                  eps, hidden, write_residual);
+                                                  eps, hidden, (write_residual ? 1 : 0) | (rows <= NORM_FEW_ROWS ? 2 : 0));
     }););
     return zi_check_launch("add_rmsnorm_parts");
 }
