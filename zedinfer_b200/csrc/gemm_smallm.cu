@@ -340,12 +340,19 @@ struct RopeOut {
     long long page_stride, kv_stride;
 };
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+
 template <int NT>
 __global__ void __launch_bounds__(GS_THREADS, NT == 1 ? 4 : 3)
 gemm_smallm_rope_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const bf16* __restrict__ bias,
                         const RopeOut ro, int M, int K, long long ldx, long long ldw) {
     __shared__ float red[GS_WARPS][16][NT * 8 + 1];
     __shared__ int s_page[NT * 8], s_off[NT * 8];
+    __shared__ __align__(16) float s_cs[NT * 8][16];         // per token: cos of this block's 8 columns | sin of them
+    __shared__ __align__(16) bf16 s_bias[2][8];              // bias of the 8 columns and of the 8 that pair with them
     // The decode attention kernel that follows may start now: it keeps away from what this kernel writes until it
     // has waited for it to finish (dependent_wait() there).  Without such a successor this does nothing.
     asm volatile("griddepcontrol.launch_dependents;\n" ::);
@@ -359,6 +366,20 @@ gemm_smallm_rope_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, 
         s_page[threadIdx.x] = ro.tables[(size_t)ro.tok_seg[threadIdx.x] * ro.max_blocks + p / ro.page_size];
         s_off[threadIdx.x] = p % ro.page_size;
     }
+    // So are the angles and the bias of this block's columns: copied into shared memory behind the product's back
+    // (16 bytes a copy) instead of being fetched when the sums are ready, one more trip to memory at the kernel's end.
+    {
+        const int t = (int)threadIdx.x - 64;                // warps 2 and up: the first two ask for pages above
+        if (t >= 0 && t < M * 4) {
+            const int m = t >> 2, part = t & 3;             // cos low, cos high, sin low, sin high
+            const float* src = ro.cs + (size_t)m * ro.head_dim + (part < 2 ? 0 : half) + d0 + (part & 1) * 4;
+            cp_async16(&s_cs[m][part * 4], src);
+        } else if (bias && t >= M * 4 && t < M * 4 + 2) {
+            const int which = t - M * 4;
+            cp_async16(&s_bias[which][0], bias + row0 + (which ? half : 0));
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    }
     float acc[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
@@ -371,6 +392,7 @@ gemm_smallm_rope_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, 
         red[warp][g + 8][nt * 8 + tq * 2] = acc[nt][2];
         red[warp][g + 8][nt * 8 + tq * 2 + 1] = acc[nt][3];
     }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();
     for (int i = threadIdx.x; i < 8 * NT * 8; i += GS_THREADS) {
         const int rr = i & 7, m = i >> 3;
@@ -379,12 +401,12 @@ gemm_smallm_rope_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, 
 #pragma unroll
         for (int w = 0; w < GS_WARPS; ++w) { a += red[w][rr][m]; b += red[w][rr + 8][m]; }
         const int d = d0 + rr;
-        if (bias) { a += __bfloat162float(bias[row0 + rr]); b += __bfloat162float(bias[row0 + half + rr]); }
+        if (bias) { a += __bfloat162float(s_bias[0][rr]); b += __bfloat162float(s_bias[1][rr]); }
         a = __bfloat162float(__float2bfloat16_rn(a));
         b = __bfloat162float(__float2bfloat16_rn(b));
         float lo = a, hi = b;
         if (head < ro.n_heads + ro.n_kv_heads) {
-            const float c = ro.cs[(size_t)m * ro.head_dim + d], sn = ro.cs[(size_t)m * ro.head_dim + half + d];
+            const float c = s_cs[m][rr], sn = s_cs[m][8 + rr];
             lo = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn));
             hi = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, sn));
         }
@@ -420,6 +442,7 @@ ZI_EXPORT int zi_gemm_smallm_rope(const void* X, const void* W, const void* bias
     ro.cs = cs; ro.q_out = (bf16*)q_out; ro.cache = (bf16*)cache; ro.tables = tables; ro.tok_seg = tok_seg; ro.pos = pos;
     ro.n_heads = n_heads; ro.n_kv_heads = n_kv_heads; ro.head_dim = head_dim; ro.page_size = page_size; ro.max_blocks = max_blocks;
     ro.page_stride = page_stride; ro.kv_stride = kv_stride;
+    if (((uintptr_t)cs & 15) || ((uintptr_t)bias & 15)) return zi_fail("gemm_smallm_rope: cs and bias must be 16-byte aligned (they are copied 16 bytes at a time)");
     const long long tiles = (long long)(n_heads + 2 * n_kv_heads) * (head_dim / 16);
     if (tiles > 0x7fffffffLL) return zi_fail("gemm_smallm_rope: too many tiles");
     if (M <= 8) gemm_smallm_rope_kernel<1><<<(unsigned)tiles, GS_THREADS, 0, stream>>>((const bf16*)X, (const bf16*)W, (const bf16*)bias, ro, M, K, ldx, ldw);

@@ -131,8 +131,8 @@ def rope_table(pos: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> 
 
 def can_fuse_rope_product(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], cache: Optional[torch.Tensor]) -> bool:
     """The q/k/v product of a decode step can take rotation and cache append into its epilogue."""
-    return (_small_m_ok(x, w, fused="rope") and (bias is None or bias.dtype == torch.bfloat16) and cache is not None
-            and cache.dtype == torch.bfloat16)
+    return (_small_m_ok(x, w, fused="rope") and (bias is None or (bias.dtype == torch.bfloat16 and bias.data_ptr() % 16 == 0))
+            and cache is not None and cache.dtype == torch.bfloat16)
 
 
 def gemm_smallm_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], cs: torch.Tensor, q_out: torch.Tensor,
