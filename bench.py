@@ -57,7 +57,7 @@ def peaks():
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,clocks.mem,power.draw")
 
     def __init__(self):
         self.samples, self.proc, self.thread = [], None, None
@@ -88,7 +88,7 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        mhz, mx, reasons = [], 0, set()
+        mhz, mx, reasons, mem, watts = [], 0, set(), [], []
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for s in self.samples:
             try:
@@ -99,9 +99,15 @@ class ClockSampler:
             for name, v in zip(names, s[2:6]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
-        mhz.sort()
+            for column, into in ((6, mem), (7, watts)):          # memory clock and power: what the SM clock does not show
+                try:
+                    into.append(float(s[column]))
+                except (ValueError, IndexError):
+                    pass
+        mhz.sort(), mem.sort(), watts.sort()
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx or None,
-                "reasons": sorted(reasons), "samples": len(mhz)}
+                "reasons": sorted(reasons), "samples": len(mhz),
+                "mem_mhz": int(mem[len(mem) // 2]) if mem else None, "watts": int(watts[len(watts) // 2]) if watts else None}
 
 
 def weight_bytes_per_step(cfg, layers):
