@@ -347,3 +347,64 @@ def test_a_prompt_longer_than_the_windowed_pool_is_admitted_and_runs_through():
     assert a.phase == b.phase == RequestPhase.COMPLETE and a.finish_reason == b.finish_reason == "length"
     assert len(a.output_ids) == 6 and len(b.output_ids) == 3 and s.num_preemptions == 0
     assert 0 < held_most <= 12 and cache.free_pages() == [80, 12]
+
+
+# ---- the sampler's record of the table of generated tokens (host side only; the kernels are stood in for) -------
+def test_the_samplers_record_of_the_generated_tokens_table(monkeypatch):
+    """Which slot a request's table is in, when the host sends tokens up (a request that comes back after its slot was
+    given away) and when it cannot answer (no table kept; the table behind while tokens are still on their way)."""
+    import torch
+    from zedinfer_b200 import ops
+    from zedinfer_b200.sampling.sampler import Sampler
+
+    class FakeRc:
+        def __init__(self, slot, serial):
+            self.slot, self.serial = slot, serial
+
+    class FakeCache:
+        def __init__(self):
+            self.rcs = {}
+
+        def get(self, rid):
+            return self.rcs.get(rid)
+
+    class FakeCore:
+        def __init__(self, vocab):
+            self.generated_counts = torch.zeros(4, vocab, dtype=torch.int32)
+            self.cache = FakeCache()
+
+    added = []
+
+    def count_token_list(row, tokens):
+        added.append(tokens.tolist())
+        for t in tokens.tolist():
+            row[t] += 1
+    monkeypatch.setattr(ops, "count_token_list", count_token_list)
+    core = FakeCore(50)
+    sampler = Sampler(torch.device("cpu"), core)
+    r = req(3, use_argmax=False, temperature=0.8, repetition_penalty=1.3, seed=5)
+    greedy = req(3)
+    plain = req(3, use_argmax=False, temperature=0.8, seed=5)
+    core.cache.rcs[r.request_id] = FakeRc(slot=2, serial=11)
+    assert sampler._count_slot(greedy, 0) == -1 and sampler._count_slot(plain, 0) == -1
+    assert sampler._count_slot(r, 0) == 2 and (r.count_serial, r.counted) == (11, 0) and added == []
+    sampler.counted([r, greedy, plain])                  # the step chose a token for each; only r keeps a table
+    assert r.counted == 1 and greedy.counted == 0 and plain.counted == 0
+    assert sampler._count_slot(r, 1) == 2                # a step launched ahead: one token chosen, none read yet
+    r.output_ids.append(7)
+    assert sampler._count_slot(r, 0) == 2 and added == []
+    par, ints = sampler.params([greedy, r, plain])
+    assert ints.tolist() == [[0, 0, 0], [-1, 2, -1]] and par[3].tolist() == [1.0, pytest.approx(1.3), 1.0]
+    assert par[0].tolist() == [0.0, pytest.approx(0.8), pytest.approx(0.8)]
+    # the table is behind while a token is still on its way: no answer, the caller takes the ordinary path
+    assert sampler._count_slot(r, 2) is None and sampler.params([r], ahead=2) is None
+    # taken off the GPU and back in another slot, zeroed: the host sends what was generated so far
+    sampler.counted([r])
+    r.output_ids.extend([9, 7])
+    core.cache.rcs[r.request_id] = FakeRc(slot=0, serial=12)
+    assert sampler._count_slot(r, 0) == 0 and added == [[7, 9, 7]] and (r.count_serial, r.counted) == (12, 3)
+    assert core.generated_counts[0, 7] == 2 and core.generated_counts[0, 9] == 1 and int(core.generated_counts.sum()) == 3
+    # no table kept: a penalised request cannot be answered, the others can
+    bare = Sampler(torch.device("cpu"))
+    assert bare._count_slot(r, 0) is None and bare._count_slot(plain, 0) == -1 and bare.params([r]) is None
+    assert bare.params([plain, greedy])[1].tolist() == [[0, 0], [-1, -1]]
