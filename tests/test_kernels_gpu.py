@@ -243,6 +243,18 @@ def test_rope_append(dtype, nh, nkv, hd, ps):
         assert torch.equal(pool[page, call, 1, :, off].float().cpu(), v[i].to(t).float())
         touched[page, call, :, :, off] = True
     assert float(pool.float().cpu()[~touched].abs().max()) == 0.0          # nothing else was written
+    # the same with the step's table of angles in place of a sincosf per layer: bit for bit what the kernel above wrote
+    cs = torch.empty(n, hd, dtype=torch.float32, device=dev())
+    pos_d = torch.tensor(pos, dtype=torch.int32, device=dev())
+    ops.rope_table(pos_d, inv, cs)
+    pool2, q2 = torch.zeros_like(pool), torch.empty_like(q_out)
+    ops.rope_append(qkv, q2, pool2[:, call], tables, torch.tensor(seg, dtype=torch.int32, device=dev()), pos_d, inv, nh, nkv,
+                    hd, ps, pool2.stride(0), pool2.stride(2), cs=cs)
+    assert torch.equal(q2, q_out) and torch.equal(pool2, pool)
+    q3 = torch.empty_like(q_out)                                          # a layer that writes no keys or values
+    ops.rope_append(qkv, q3, None, tables, torch.tensor(seg, dtype=torch.int32, device=dev()), pos_d, inv, nh, nkv, hd, ps,
+                    0, 0, write_kv=False, cs=cs)
+    assert torch.equal(q3, q_out)
 
 
 def test_argmax_ties_and_rows():

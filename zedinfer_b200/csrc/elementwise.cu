@@ -403,6 +403,42 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_
     }
 }
 
+// Few tokens with the step's table of angles (cs [n_tokens, head_dim]: cos | sin, from rope_table_kernel, the same
+// sincosf of the same angle): one block per (token, head), a thread per pair of elements.  Everything that does not
+// depend on anything else (position, segment, the pair, its cosine and sine) is asked for at once; only the page number
+// waits for position and segment.  Two trips to memory instead of four, and no sincosf per layer.
+template <typename T>
+__global__ void rope_append_few_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ cache,
+                                       const int* __restrict__ tables, const int* __restrict__ tok_seg,
+                                       const int* __restrict__ pos, const float* __restrict__ cs,
+                                       int row_stride, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                       int max_blocks, long long page_stride, long long kv_stride) {
+    const int n = blockIdx.x, h = blockIdx.y;
+    const int half = head_dim >> 1;
+    const int k = threadIdx.x;
+    if (k >= half) return;
+    const T* src = qkv + (size_t)n * row_stride + (size_t)h * head_dim;
+    const int p = pos[n], seg = tok_seg[n];
+    const float a = to_f32<T>(src[k]), b = to_f32<T>(src[k + half]);
+    const float c = cs[(size_t)n * head_dim + k], sn = cs[(size_t)n * head_dim + half + k];
+    T* dst;
+    if (h < n_heads) {
+        dst = q_out + ((size_t)n * n_heads + h) * head_dim;
+    } else {
+        const int page = tables[(size_t)seg * max_blocks + p / page_size];
+        const bool is_v = h >= n_heads + n_kv_heads;
+        dst = cache + (size_t)page * page_stride + (is_v ? kv_stride : 0) +
+              ((size_t)(h - n_heads - (is_v ? n_kv_heads : 0)) * page_size + (size_t)(p % page_size)) * head_dim;
+    }
+    if (h < n_heads + n_kv_heads) {
+        dst[k] = from_f32<T>(__fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn)));
+        dst[k + half] = from_f32<T>(__fadd_rn(__fmul_rn(b, c), __fmul_rn(a, sn)));
+    } else {
+        dst[k] = from_f32<T>(a);
+        dst[k + half] = from_f32<T>(b);
+    }
+}
+
 // The same for many tokens with 8 elements per access: one block per token, a thread takes 8 consecutive
 // elements of a head's first half and the 8 that pair with them in its second half.  The arithmetic per element is
 // the one above, so both kernels give the same bits.
@@ -475,16 +511,27 @@ rope_append_vec8_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __r
     }
 }
 
+// cs: null, or the step's table of angles [n_tokens, head_dim] (zi_rope_table of these positions and inv_freq); few
+// tokens then take their cosines and sines from it.
 ZI_EXPORT int zi_rope_append(const void* qkv, void* q_out, void* cache, int dtype, const int* tables,
                              const int* tok_seg, const int* pos, const float* inv_freq, int n_tokens,
                              int row_stride, int n_heads, int n_kv_heads, int head_dim, int page_size,
                              int max_blocks, long long page_stride, long long kv_stride, int write_kv,
-                             cudaStream_t stream) {
+                             const float* cs, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (head_dim <= 0 || (head_dim & 1)) return zi_fail("rope: head_dim=%d must be positive and even", head_dim);
     if (n_heads <= 0 || n_kv_heads <= 0 || page_size <= 0) return zi_fail("rope: bad head counts or page size");
     const int total_heads = n_heads + 2 * n_kv_heads;
     if (total_heads > 65535) return zi_fail("rope: too many heads for one launch");
+    if (cs && n_tokens <= 64 && head_dim <= 2048) {
+        const int heads = n_heads + (write_kv ? 2 * n_kv_heads : 0);
+        const int threads = ((head_dim / 2 + 31) / 32) * 32;
+        ZI_DISPATCH(dtype, T, {
+            rope_append_few_kernel<T><<<dim3(n_tokens, heads), threads, 0, stream>>>((const T*)qkv, (T*)q_out, (T*)cache, tables,
+                tok_seg, pos, cs, row_stride, n_heads, n_kv_heads, head_dim, page_size, max_blocks, page_stride, kv_stride);
+        });
+        return zi_check_launch("rope_append");
+    }
     const int hpb = n_tokens <= 64 ? 1 : total_heads;
     const int vec_align = dtype == ZI_BF16 ? 15 : 31;
     if (hpb != 1 && head_dim % 16 == 0 && row_stride % 8 == 0 && page_stride % 8 == 0 && kv_stride % 8 == 0 &&

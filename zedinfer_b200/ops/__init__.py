@@ -97,11 +97,19 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], w: torch.
                       c_int(1 if write_residual else 0), stream())
 
 
+ROPE_TABLE_MAX_TOKENS = 64       # steps of at most this many tokens rotate with the step's table of angles
+
+
 def rope_append(qkv: torch.Tensor, q_out: torch.Tensor, cache: Optional[torch.Tensor], tables: torch.Tensor,
                 tok_seg: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, n_heads: int, n_kv_heads: int,
-                head_dim: int, page_size: int, page_stride: int, kv_stride: int, write_kv: bool = True) -> None:
-    """Rotate q (and k) by position and append k, v to the cache pages of each token's request."""
-    need_cuda(qkv, q_out, cache, tables, tok_seg, pos, inv_freq)
+                head_dim: int, page_size: int, page_stride: int, kv_stride: int, write_kv: bool = True,
+                cs: Optional[torch.Tensor] = None) -> None:
+    """Rotate q (and k) by position and append k, v to the cache pages of each token's request.  ``cs``: the step's
+    table of angles (:func:`rope_table` of ``pos`` and ``inv_freq``); steps of at most 64 tokens then read their cosines
+    and sines there instead of computing them in every layer."""
+    need_cuda(qkv, q_out, cache, tables, tok_seg, pos, inv_freq, cs)
+    if cs is not None and (cs.dtype != torch.float32 or cs.shape != (qkv.shape[0], head_dim) or not cs.is_contiguous()):
+        raise KernelError(f"rope_append: cs {tuple(cs.shape)} must be contiguous float32 [{qkv.shape[0]}, {head_dim}]")
     need_int32("tables", tables), need_int32("tok_seg", tok_seg), need_int32("pos", pos)
     need_contiguous("q_out", q_out)
     n = qkv.shape[0]
@@ -116,7 +124,7 @@ def rope_append(qkv: torch.Tensor, q_out: torch.Tensor, cache: Optional[torch.Te
     _elementwise.call("zi_rope_append", ptr(qkv), ptr(q_out), ptr(cache), c_int(dtype_code(qkv.dtype)), ptr(tables),
                       ptr(tok_seg), ptr(pos), ptr(inv_freq), c_int(n), c_int(qkv.stride(0)), c_int(n_heads),
                       c_int(n_kv_heads), c_int(head_dim), c_int(page_size), c_int(tables.shape[1]),
-                      c_ll(page_stride), c_ll(kv_stride), c_int(1 if write_kv else 0), stream())
+                      c_ll(page_stride), c_ll(kv_stride), c_int(1 if write_kv else 0), ptr(cs), stream())
 
 
 def rope_table(pos: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> None:

@@ -43,9 +43,22 @@ class RotaryPosition(PositionEncoding):
                       n_heads: int, n_kv_heads: int, head_dim: int, write_kv: bool) -> None:
         if head_dim != self.head_dim:
             raise ValueError(f"rope was built for head_dim={self.head_dim}, the mixer has {head_dim}")
+        # few tokens (a decode step beyond what the product's epilogue takes): the step's angles, made once
+        cs = self._step_angles(ctx, qkv.device) if qkv.shape[0] <= ops.ROPE_TABLE_MAX_TOKENS else None
         ops.rope_append(qkv, q_out, cache.tensor, ctx.tables[cache.group], ctx.tok_seg, ctx.positions,
                         self._table(qkv.device), n_heads, n_kv_heads, head_dim, cache.page_size, cache.page_stride,
-                        cache.kv_stride, write_kv=write_kv)
+                        cache.kv_stride, write_kv=write_kv, cs=cs)
+
+    def _step_angles(self, ctx: StepContext, device: torch.device) -> torch.Tensor:
+        """cos | sin of every token's angles, float32 ``[tokens, head_dim]``: made by the first layer of a step that
+        asks, shared by every layer with the same theta and head size."""
+        key = ("rope_cs", self.theta, self.head_dim)
+        cs = ctx.step_cache.get(key)
+        if cs is None:
+            cs = torch.empty((ctx.positions.numel(), self.head_dim), dtype=torch.float32, device=device)
+            ops.rope_table(ctx.positions, self._table(device), cs)
+            ctx.step_cache[key] = cs
+        return cs
 
     def project_rotate_append(self, x: torch.Tensor, w_qkv: torch.Tensor, b_qkv: Optional[torch.Tensor],
                               q_out: torch.Tensor, cache: CallCacheView, ctx: StepContext, n_heads: int,
@@ -56,12 +69,7 @@ class RotaryPosition(PositionEncoding):
         if not (write_kv and head_dim == self.head_dim
                 and ops.can_fuse_rope_product(x, w_qkv, b_qkv, cache.tensor)):
             return False
-        key = ("rope_cs", self.theta, self.head_dim)
-        cs = ctx.step_cache.get(key)
-        if cs is None:
-            cs = torch.empty((x.shape[0], self.head_dim), dtype=torch.float32, device=x.device)
-            ops.rope_table(ctx.positions, self._table(x.device), cs)
-            ctx.step_cache[key] = cs
+        cs = self._step_angles(ctx, x.device)
         ops.gemm_smallm_rope(x, w_qkv, b_qkv, cs, q_out, cache.tensor, ctx.tables[cache.group], ctx.tok_seg,
                              ctx.positions, n_heads, n_kv_heads, head_dim, cache.page_size, cache.page_stride,
                              cache.kv_stride)
