@@ -540,6 +540,7 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
     // thresholds as keys of logits
     unsigned int thr_v = 0u;
     bool listed = false;                       // the search stopped early (or was for top-k): what is kept may fit the list
+    bool exact = true;                         // thr_v is the threshold itself, not the lowest key of the bin where it lies
     if (by_k || by_p) {
         // the search (for the k-th largest; without top-k, for the entry where top-p's mass is reached) stops as soon
         // as the entries at or above the bin where it lies are sure to fit the list
@@ -549,6 +550,7 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
             : find_threshold<true>(cluster, row, cbegin, cend, wt, p * S, 0u, (float)SAMPLE_LIST, kmax, acc,
                                    share, turn, &s_prefix, &s_reach);
         thr_v = found.key;
+        exact = found.exact;
         listed = by_k || !found.exact;
     }
     if (listed) {
@@ -647,6 +649,14 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, const flo
         }
         // too many for the list: the search ran to its end without the kept set getting small (thousands tie with the
         // k-th largest, or top-p alone keeps thousands), and thr_v is exact.  The long way.
+        if (!exact) {
+            // (A search that stopped early promised that the list would do.  Should that promise ever be broken, the
+            // bin's lowest key must not pass for the threshold: search again, to the end.)
+            thr_v = by_k ? find_threshold<false>(cluster, row, cbegin, cend, wt, (float)k, 0u, 0.0f, kmax, acc, share, turn,
+                                                 &s_prefix, &s_reach).key
+                         : find_threshold<true>(cluster, row, cbegin, cend, wt, p * S, 0u, 0.0f, kmax, acc, share, turn,
+                                                &s_prefix, &s_reach).key;
+        }
     }
     if (by_p && by_k) {
         const unsigned int t = find_threshold<true>(cluster, row, cbegin, cend, wt, p * S, thr_v, 0.0f, kmax, acc,
